@@ -1,0 +1,558 @@
+// Implicit-GEMM convolution / GEMM on the 5th-generation tensor cores (sm_100a).
+//
+// One persistent, warp-specialised kernel serves conv2d (any KHxKW, stride 1/2,
+// zero padding), 1x1 convolutions and plain row-major GEMMs (a GEMM is a 1x1
+// convolution over a 1 x M "image"):
+//
+//   warp 0   TMA producer : for every (tap, 64-channel slab) one 4-D tiled
+//            cp.async.bulk.tensor load of a  tile_h x tile_w x 64ch  activation
+//            patch (NHWC) - the tap offset is a coordinate offset and the
+//            zero padding is TMA's out-of-bounds fill, so no im2col buffer
+//            exists - plus one 2-D load of the BN x 64 weight slab.
+//   warp 1   MMA issuer   : tcgen05.mma kind::f16, 128 x BN x 16 per instruction,
+//            accumulators double-buffered in TMEM (2 x BN fp32 columns).
+//   warps 2-5 epilogue    : tcgen05.ld TMEM -> registers, + bias, (+ residual),
+//            activation, cast, 16-byte stores straight into the (possibly
+//            channel-offset, i.e. concat-fused) NHWC output.
+//
+// Replaces what the reference delegates to TensorRT / cuDNN / cuBLAS
+// (fastdeploy/runtime/backends/tensorrt/trt_backend.cc:347 enqueueV2).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <vector>
+
+#include "fdb_common.h"
+#include "sm100_ptx.cuh"
+
+namespace fdb {
+
+constexpr int kBM = 128;       // tile rows = TMEM lanes
+constexpr int kBK = 64;        // K elements per pipeline stage (128-byte rows)
+constexpr int kThreads = 192;  // 6 warps
+
+// C ABI descriptor (mirrored by ctypes in fastdeploy_b200/ops/conv_gemm.py).
+struct ConvGemmDesc {
+  const void* x;         // NHWC input, already offset to the first used channel
+  const void* w;         // packed weights [Cout][KH*KW][cin_pad], K-major
+  const float* bias;     // [Cout] fp32 or null
+  const void* residual;  // same dtype as x, NHWC with res_ld, or null
+  void* y;               // NHWC output, already offset to the first written channel
+  int* status;           // device int, receives a KernelStatus on failure
+  int dtype;             // kF16 | kBF16 : x, w, residual
+  int out_dtype;         // kF16 | kBF16 | kF32
+  int N, H, W, Cin, x_ld;
+  int Ho, Wo, Cout, y_ld;
+  int KH, KW, stride, pad_h, pad_w;
+  int res_ld, res_mode;  // 0 none, 1 add before activation, 2 add after activation
+  int act;
+  float act_alpha, act_beta;
+  int tile_w, tile_h;    // 0 = choose
+  int block_n;           // 0 = choose (32/64/128/256)
+  int max_ctas;          // 0 = one per SM
+};
+
+struct ConvGemmParams {
+  const float* bias;
+  const void* residual;
+  void* y;
+  int* status;
+  int Ho, Wo, Cout, y_ld, res_ld, res_mode, out_dtype, in_bf16;
+  int KH, KW, stride, pad_h, pad_w;
+  int tw, th, tiles_w, tiles_h, n_tiles, total_tiles;
+  int kb_per_tap, k_iters;
+  int act;
+  float act_alpha, act_beta;
+  uint32_t a_bytes;
+  uint32_t idesc;
+  int y_vec, res_vec;
+};
+
+__device__ __forceinline__ float apply_act(float x, int act, float alpha, float beta) {
+  switch (act) {
+    case kActRelu: return fmaxf(x, 0.f);
+    case kActSilu: return __fdividef(x, 1.f + __expf(-x));
+    case kActHardSwish: return x * fminf(fmaxf(x + 3.f, 0.f), 6.f) * (1.f / 6.f);
+    case kActHardSigmoid: return fminf(fmaxf(alpha * x + beta, 0.f), 1.f);
+    case kActSigmoid: return __fdividef(1.f, 1.f + __expf(-x));
+    case kActGelu: return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+    case kActRelu6: return fminf(fmaxf(x, 0.f), 6.f);
+    case kActLeakyRelu: return x > 0.f ? x : alpha * x;
+    case kActTanh: return tanhf(x);
+    default: return x;
+  }
+}
+
+__device__ __forceinline__ void load8_as_float(const void* ptr, bool bf16, bool vec, int nvalid,
+                                               float (&r)[8]) {
+  if (vec && nvalid == 8) {
+    uint4 u = *reinterpret_cast<const uint4*>(ptr);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (bf16) {
+        __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[j]);
+        float2 f = __bfloat1622float2(h);
+        r[2 * j] = f.x; r[2 * j + 1] = f.y;
+      } else {
+        __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+        float2 f = __half22float2(h);
+        r[2 * j] = f.x; r[2 * j + 1] = f.y;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (j < nvalid) {
+        r[j] = bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ptr)[j])
+                    : __half2float(reinterpret_cast<const __half*>(ptr)[j]);
+      } else {
+        r[j] = 0.f;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void store8(void* ptr, int out_dtype, bool vec, int nvalid,
+                                       const float (&x)[8]) {
+  if (out_dtype == kF32) {
+    float* o = reinterpret_cast<float*>(ptr);
+    if (vec && nvalid == 8) {
+      reinterpret_cast<float4*>(o)[0] = make_float4(x[0], x[1], x[2], x[3]);
+      reinterpret_cast<float4*>(o)[1] = make_float4(x[4], x[5], x[6], x[7]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < nvalid) o[j] = x[j];
+    }
+    return;
+  }
+  const bool bf16 = out_dtype == kBF16;
+  if (vec && nvalid == 8) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (bf16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+        w[j] = *reinterpret_cast<uint32_t*>(&h);
+      } else {
+        __half2 h = __floats2half2_rn(x[2 * j], x[2 * j + 1]);
+        w[j] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+    *reinterpret_cast<uint4*>(ptr) = make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (j < nvalid) {
+        if (bf16) reinterpret_cast<__nv_bfloat16*>(ptr)[j] = __float2bfloat16_rn(x[j]);
+        else reinterpret_cast<__half*>(ptr)[j] = __float2half_rn(x[j]);
+      }
+    }
+  }
+}
+
+template <int BN>
+struct KernelCfg {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kTmemCols = BN * 2 < 32 ? 32 : BN * 2;
+  static constexpr int kBarBytes = 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;  // +1024: alignment slack
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const ConvGemmParams p) {
+  using Cfg = KernelCfg<BN>;
+  constexpr int S = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);
+  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
+  auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * S + a); };
+  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * S + 2 + a); };
+  const uint32_t tile0 = smem_u32(smem);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t armed = 0, armed_parity = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+        const int n_tile = tile % p.n_tiles;
+        int m_tile = tile / p.n_tiles;
+        const int twi = m_tile % p.tiles_w; m_tile /= p.tiles_w;
+        const int thi = m_tile % p.tiles_h;
+        const int img = m_tile / p.tiles_h;
+        const int x0 = twi * p.tw * p.stride - p.pad_w;
+        const int y0 = thi * p.th * p.stride - p.pad_h;
+        int kcol = 0;
+        for (int kh = 0; ok && kh < p.KH; ++kh) {
+          for (int kw = 0; ok && kw < p.KW; ++kw) {
+            for (int kb = 0; kb < p.kb_per_tap; ++kb, kcol += kBK) {
+              if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, kStatusTimeoutProducer)) {
+                ok = false;
+                break;
+              }
+              mbar_arrive_expect_tx(full_bar(s), p.a_bytes + Cfg::kBBytes);
+              armed |= 1u << s;
+              armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
+              const uint32_t a_dst = tile0 + s * Cfg::kStageBytes;
+              tma_load_4d(a_dst, &tmA, full_bar(s), kb * kBK, x0 + kw, y0 + kh, img);
+              tma_load_2d(a_dst + Cfg::kABytes, &tmB, full_bar(s), kcol, n_tile * BN);
+              if (++s == S) { s = 0; ph ^= 1; }
+            }
+          }
+        }
+      }
+      if (!ok) {
+        // Aborting: give the copies already issued a bounded chance to land
+        // before the CTA exits and its shared memory is handed to another CTA.
+        for (int i = 0; i < S; ++i) {
+          if (!(armed & (1u << i))) continue;
+          const uint32_t par = (armed_parity >> i) & 1u;
+          for (int it = 0; it < (1 << 16); ++it)
+            if (mbar_try_wait(full_bar(i), par)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, kStatusTimeoutMma)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int k = 0; k < p.k_iters; ++k) {
+          if (!mbar_wait(full_bar(s), ph, abort_flag, kStatusTimeoutMma)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = tile0 + s * Cfg::kStageBytes;
+          const uint64_t adesc = make_kmajor_desc(a_addr, 128);
+          const uint64_t bdesc = make_kmajor_desc(a_addr + Cfg::kABytes, 128);
+#pragma unroll
+          for (int kk = 0; kk < kBK / 16; ++kk) {
+            // +32 bytes per 16-element K step inside the 128-byte swizzle atom
+            umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, p.idesc, (k | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(s));
+          if (++s == S) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const bool in_bf16 = p.in_bf16 != 0;
+    const int out_es = p.out_dtype == kF32 ? 4 : 2;
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+      const int n_tile = tile % p.n_tiles;
+      int m_tile = tile / p.n_tiles;
+      const int twi = m_tile % p.tiles_w; m_tile /= p.tiles_w;
+      const int thi = m_tile % p.tiles_h;
+      const int img = m_tile / p.tiles_h;
+      if (!mbar_wait(tfull_bar(acc), acc_ph, abort_flag, kStatusTimeoutEpilogue)) break;
+      tc_fence_after();
+      const int row = q * 32 + lane;
+      const int rh = row / p.tw, rw = row - rh * p.tw;
+      const int oh = thi * p.th + rh, ow = twi * p.tw + rw;
+      const bool valid = rh < p.th && oh < p.Ho && ow < p.Wo;
+      const size_t pix = (static_cast<size_t>(img) * p.Ho + oh) * p.Wo + ow;
+      uint8_t* yrow = reinterpret_cast<uint8_t*>(p.y) + pix * p.y_ld * out_es;
+      const uint8_t* rrow =
+          reinterpret_cast<const uint8_t*>(p.residual) + pix * p.res_ld * 2;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n_tile * BN + c * 32;
+        if (col0 >= p.Cout) break;
+        uint32_t v[32];
+        tmem_ld_32x32(t_row + c * 32, v);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int co = col0 + g * 8;
+            const int nvalid = min(8, p.Cout - co);
+            if (nvalid > 0) {
+              float x[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(v[g * 8 + j]);
+              if (p.bias != nullptr) {
+                if (nvalid == 8) {
+                  const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + co));
+                  const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + co) + 1);
+                  x[0] += b0.x; x[1] += b0.y; x[2] += b0.z; x[3] += b0.w;
+                  x[4] += b1.x; x[5] += b1.y; x[6] += b1.z; x[7] += b1.w;
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j)
+                    if (j < nvalid) x[j] += __ldg(p.bias + co + j);
+                }
+              }
+              float r[8];
+              if (p.res_mode != 0) load8_as_float(rrow + co * 2, in_bf16, p.res_vec != 0, nvalid, r);
+              if (p.res_mode == 1) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) x[j] += r[j];
+              }
+              if (p.act != kActNone) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) x[j] = apply_act(x[j], p.act, p.act_alpha, p.act_beta);
+              }
+              if (p.res_mode == 2) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) x[j] += r[j];
+              }
+              store8(yrow + static_cast<size_t>(co) * out_es, p.out_dtype, p.y_vec != 0, nvalid, x);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      acc ^= 1;
+      if (acc == 0) acc_ph ^= 1;
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, *abort_flag);
+}
+
+// ------------------------------------------------------------------ host side
+struct ConvGemmOp : Op {
+  alignas(64) CUtensorMap tmA;
+  alignas(64) CUtensorMap tmB;
+  ConvGemmParams prm;
+  int block_n = 0;
+  int grid = 0;
+  int launch(cudaStream_t stream) override;
+};
+
+template <int BN>
+static int launch_bn(ConvGemmOp* op, cudaStream_t stream) {
+  using Cfg = KernelCfg<BN>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  FDB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    FDB_CUDA_OK(cudaFuncSetAttribute(conv_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg::kSmemBytes));
+    attr_set[dev] = true;
+  }
+  conv_gemm_kernel<BN><<<op->grid, kThreads, Cfg::kSmemBytes, stream>>>(op->tmA, op->tmB, op->prm);
+  FDB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int ConvGemmOp::launch(cudaStream_t stream) {
+  switch (block_n) {
+    case 32: return launch_bn<32>(this, stream);
+    case 64: return launch_bn<64>(this, stream);
+    case 128: return launch_bn<128>(this, stream);
+    case 256: return launch_bn<256>(this, stream);
+  }
+  set_error("conv_gemm: bad block_n");
+  return -1;
+}
+
+// Picks the output-pixel tile (tile_w x tile_h <= 128) that wastes the fewest MMA rows.
+static void choose_tile(int Ho, int Wo, int stride, int* tw_out, int* th_out) {
+  double best = -1.0;
+  int btw = 1, bth = 1;
+  for (int tw = 1; tw <= std::min(Wo, kBM); ++tw) {
+    if (tw * stride > 256) break;
+    int th = std::min(kBM / tw, Ho);
+    if (th * stride > 256) th = 256 / stride;
+    if (th < 1) continue;
+    const long tiles = static_cast<long>((Wo + tw - 1) / tw) * ((Ho + th - 1) / th);
+    const double util = static_cast<double>(Ho) * Wo / (static_cast<double>(tiles) * kBM);
+    if (util > best + 1e-9 || (util > best - 1e-9 && tw > btw)) {
+      best = util;
+      btw = tw;
+      bth = th;
+    }
+  }
+  *tw_out = btw;
+  *th_out = bth;
+}
+
+static int choose_block_n(int Cout, long m_tiles, int sms) {
+  const int cands[4] = {256, 128, 64, 32};
+  int pick = 32;
+  for (int i = 0; i < 4; ++i) {
+    const int bn = cands[i];
+    const int nt = (Cout + bn - 1) / bn;
+    const double waste = static_cast<double>(nt) * bn / Cout;
+    if (waste > 1.2 && bn > 32) continue;
+    pick = bn;
+    // keep every SM busy when a smaller tile would
+    if (m_tiles * nt >= sms || bn == 32) break;
+    // otherwise try the next smaller candidate, but remember this one
+    bool smaller_helps = false;
+    for (int j = i + 1; j < 4; ++j) {
+      const int nt2 = (Cout + cands[j] - 1) / cands[j];
+      if (static_cast<double>(nt2) * cands[j] / Cout <= 1.2 && m_tiles * nt2 > m_tiles * nt) {
+        smaller_helps = true;
+        break;
+      }
+    }
+    if (!smaller_helps) break;
+  }
+  return pick;
+}
+
+}  // namespace fdb
+
+using namespace fdb;
+
+FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
+  if (d->dtype != kF16 && d->dtype != kBF16) { set_error("conv_gemm: dtype must be fp16/bf16"); return nullptr; }
+  if (d->Cin % 8 != 0 || d->x_ld % 8 != 0) { set_error("conv_gemm: Cin and x_ld must be multiples of 8"); return nullptr; }
+  if ((reinterpret_cast<uintptr_t>(d->x) & 15) || (reinterpret_cast<uintptr_t>(d->w) & 15)) {
+    set_error("conv_gemm: x and w must be 16-byte aligned"); return nullptr;
+  }
+  if (d->stride < 1 || d->stride > 8) { set_error("conv_gemm: stride must be in [1,8]"); return nullptr; }
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) { set_error("conv_gemm: cuTensorMapEncodeTiled unavailable"); return nullptr; }
+
+  auto* op = new ConvGemmOp();
+  ConvGemmParams& p = op->prm;
+  int tw = d->tile_w, th = d->tile_h;
+  if (tw <= 0 || th <= 0) choose_tile(d->Ho, d->Wo, d->stride, &tw, &th);
+  if (tw * th > kBM || tw * d->stride > 256 || th * d->stride > 256) {
+    set_error("conv_gemm: tile too large"); delete op; return nullptr;
+  }
+  p.tw = tw; p.th = th;
+  p.tiles_w = (d->Wo + tw - 1) / tw;
+  p.tiles_h = (d->Ho + th - 1) / th;
+  const long m_tiles = static_cast<long>(p.tiles_w) * p.tiles_h * d->N;
+  const int sms = sm_count();
+  int bn = d->block_n > 0 ? d->block_n : choose_block_n(d->Cout, m_tiles, sms);
+  if (bn != 32 && bn != 64 && bn != 128 && bn != 256) { set_error("conv_gemm: block_n"); delete op; return nullptr; }
+  op->block_n = bn;
+  p.n_tiles = (d->Cout + bn - 1) / bn;
+  const long total = m_tiles * p.n_tiles;
+  if (total > 0x7fffffffL) { set_error("conv_gemm: too many tiles"); delete op; return nullptr; }
+  p.total_tiles = static_cast<int>(total);
+  p.kb_per_tap = (d->Cin + kBK - 1) / kBK;
+  p.k_iters = d->KH * d->KW * p.kb_per_tap;
+  p.bias = d->bias; p.residual = d->residual; p.y = d->y; p.status = d->status;
+  p.Ho = d->Ho; p.Wo = d->Wo; p.Cout = d->Cout; p.y_ld = d->y_ld;
+  p.res_ld = d->res_ld; p.res_mode = d->residual ? d->res_mode : 0;
+  p.out_dtype = d->out_dtype; p.in_bf16 = d->dtype == kBF16;
+  p.KH = d->KH; p.KW = d->KW; p.stride = d->stride; p.pad_h = d->pad_h; p.pad_w = d->pad_w;
+  p.act = d->act; p.act_alpha = d->act_alpha; p.act_beta = d->act_beta;
+  p.a_bytes = static_cast<uint32_t>(tw * th * kBK * 2);
+  p.idesc = make_idesc(d->dtype == kBF16 ? 1u : 0u, kBM, bn);
+  const int out_es = d->out_dtype == kF32 ? 4 : 2;
+  p.y_vec = (reinterpret_cast<uintptr_t>(d->y) % 16 == 0) && ((d->y_ld * out_es) % 16 == 0) &&
+            (d->bias == nullptr || reinterpret_cast<uintptr_t>(d->bias) % 16 == 0);
+  p.res_vec = d->residual && (reinterpret_cast<uintptr_t>(d->residual) % 16 == 0) && (d->res_ld % 8 == 0);
+  // The bias fast path reads float4 pairs; fall back to scalars when misaligned.
+  if (d->bias != nullptr && reinterpret_cast<uintptr_t>(d->bias) % 16 != 0) {
+    set_error("conv_gemm: bias must be 16-byte aligned"); delete op; return nullptr;
+  }
+  int grid = static_cast<int>(std::min<long>(total, d->max_ctas > 0 ? d->max_ctas : sms));
+  op->grid = std::max(grid, 1);
+
+  const CUtensorMapDataType tdt =
+      d->dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  {
+    cuuint64_t dims[4] = {(cuuint64_t)d->Cin, (cuuint64_t)d->W, (cuuint64_t)d->H, (cuuint64_t)d->N};
+    cuuint64_t strides[3] = {(cuuint64_t)d->x_ld * 2, (cuuint64_t)d->W * d->x_ld * 2,
+                             (cuuint64_t)d->H * d->W * d->x_ld * 2};
+    cuuint32_t box[4] = {(cuuint32_t)kBK, (cuuint32_t)(tw * d->stride), (cuuint32_t)(th * d->stride), 1};
+    cuuint32_t estr[4] = {1, (cuuint32_t)d->stride, (cuuint32_t)d->stride, 1};
+    CUresult r = enc(&op->tmA, tdt, 4, const_cast<void*>(d->x), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_error("conv_gemm: encode activation tensor map failed, CUresult " + std::to_string((int)r));
+      delete op; return nullptr;
+    }
+  }
+  {
+    const cuuint64_t ktot = (cuuint64_t)d->KH * d->KW * p.kb_per_tap * kBK;
+    cuuint64_t dims[2] = {ktot, (cuuint64_t)d->Cout};
+    cuuint64_t strides[1] = {ktot * 2};
+    cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)bn};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&op->tmB, tdt, 2, const_cast<void*>(d->w), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_error("conv_gemm: encode weight tensor map failed, CUresult " + std::to_string((int)r));
+      delete op; return nullptr;
+    }
+  }
+  return op;
+}
+
+// Introspection for tests and the autotuner: tile_w, tile_h, block_n, grid, total tiles.
+FDB_API void fdb_conv_gemm_info(void* handle, int* out5) {
+  auto* op = static_cast<ConvGemmOp*>(handle);
+  out5[0] = op->prm.tw; out5[1] = op->prm.th; out5[2] = op->block_n; out5[3] = op->grid;
+  out5[4] = op->prm.total_tiles;
+}

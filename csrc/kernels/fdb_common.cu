@@ -1,0 +1,104 @@
+// Error slot, driver entry point lookup, launch-list ("plan") executor.
+#include "fdb_common.h"
+
+#include <mutex>
+#include <vector>
+
+namespace fdb {
+
+static thread_local std::string g_err;
+void set_error(const std::string& msg) { g_err = msg; }
+const char* get_error() { return g_err.c_str(); }
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, []() {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+// A plan is an ordered launch list. The executor builds it once per
+// (model, shape bucket); replay is one native call that issues every kernel on
+// the given stream, so it can be captured into a CUDA graph as a whole.
+struct Plan {
+  std::vector<Op*> ops;
+  std::vector<bool> owned;
+  unsigned long long launches = 0;
+};
+
+}  // namespace fdb
+
+FDB_API const char* fdb_last_error() { return fdb::get_error(); }
+
+FDB_API void* fdb_plan_create() { return new fdb::Plan(); }
+
+FDB_API void fdb_plan_add(void* plan, void* op, int take_ownership) {
+  auto* p = static_cast<fdb::Plan*>(plan);
+  p->ops.push_back(static_cast<fdb::Op*>(op));
+  p->owned.push_back(take_ownership != 0);
+}
+
+FDB_API int fdb_plan_size(void* plan) { return (int)static_cast<fdb::Plan*>(plan)->ops.size(); }
+
+FDB_API unsigned long long fdb_plan_launch_count(void* plan) {
+  return static_cast<fdb::Plan*>(plan)->launches;
+}
+
+FDB_API int fdb_plan_run(void* plan, void* stream) {
+  auto* p = static_cast<fdb::Plan*>(plan);
+  for (size_t i = 0; i < p->ops.size(); ++i) {
+    int rc = p->ops[i]->launch((cudaStream_t)stream);
+    if (rc != 0) {
+      fdb::set_error("plan op " + std::to_string(i) + " failed: " + fdb::get_error());
+      return rc;
+    }
+  }
+  p->launches += p->ops.size();
+  return 0;
+}
+
+// Runs ops [begin, end) only; used by the per-layer profiler.
+FDB_API int fdb_plan_run_range(void* plan, int begin, int end, void* stream) {
+  auto* p = static_cast<fdb::Plan*>(plan);
+  if (begin < 0) begin = 0;
+  if (end > (int)p->ops.size()) end = (int)p->ops.size();
+  for (int i = begin; i < end; ++i) {
+    int rc = p->ops[i]->launch((cudaStream_t)stream);
+    if (rc != 0) return rc;
+  }
+  p->launches += (end > begin) ? (end - begin) : 0;
+  return 0;
+}
+
+FDB_API void fdb_plan_destroy(void* plan) {
+  auto* p = static_cast<fdb::Plan*>(plan);
+  for (size_t i = 0; i < p->ops.size(); ++i)
+    if (p->owned[i]) delete p->ops[i];
+  delete p;
+}
+
+FDB_API int fdb_op_launch(void* op, void* stream) {
+  return static_cast<fdb::Op*>(op)->launch((cudaStream_t)stream);
+}
+
+FDB_API void fdb_op_destroy(void* op) { delete static_cast<fdb::Op*>(op); }
+
+FDB_API int fdb_sm_count() { return fdb::sm_count(); }

@@ -1,0 +1,129 @@
+"""Builds the native libraries in-tree with nvcc / g++ (no JIT cache involved).
+
+Two shared objects are produced next to this file:
+
+* ``libfdb200_kernels.so`` - every CUDA kernel, compiled only for sm_100a
+  (``-gencode arch=compute_100a,code=sm_100a``), exposing a plain C ABI.
+* ``libfdb200_cpu.so`` - the host-side runtime pieces written in C++
+  (post-processing oracles, tokenizer, schedulers, crypto, C API).
+
+Run ``python -m fastdeploy_b200._native.build`` to (re)build; objects are cached
+by source mtime under ``build/``.
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import glob
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+CSRC = os.path.join(ROOT, "csrc")
+OBJ_DIR = os.path.join(ROOT, "build", "obj")
+
+KERNEL_LIB = os.path.join(HERE, "libfdb200_kernels.so")
+CPU_LIB = os.path.join(HERE, "libfdb200_cpu.so")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+    "-Xptxas", "-v",
+]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-pthread", "-Wall"]
+
+
+def _nvcc() -> str:
+    cand = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(cand):
+        raise RuntimeError("nvcc not found")
+    return cand
+
+
+def _newer(src: str, dst: str, deps: list[str]) -> bool:
+    if not os.path.exists(dst):
+        return True
+    t = os.path.getmtime(dst)
+    return any(os.path.getmtime(p) > t for p in [src] + deps)
+
+
+def _compile(cmd: list[str], log_path: str) -> tuple[int, str]:
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    with open(log_path, "w") as f:
+        f.write(" ".join(cmd) + "\n" + proc.stdout)
+    return proc.returncode, proc.stdout
+
+
+def build_kernels(verbose: bool = False, force: bool = False) -> str:
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    srcs = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cu")))
+    hdrs = glob.glob(os.path.join(CSRC, "kernels", "*.h")) + glob.glob(os.path.join(CSRC, "kernels", "*.cuh"))
+    nvcc = _nvcc()
+    jobs = []
+    objs = []
+    for s in srcs:
+        o = os.path.join(OBJ_DIR, os.path.basename(s) + ".o")
+        objs.append(o)
+        if force or _newer(s, o, hdrs):
+            jobs.append((s, [nvcc] + NVCC_FLAGS + ["-I", os.path.join(CSRC, "kernels"), "-c", s, "-o", o],
+                         o + ".log"))
+    with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
+        futs = {ex.submit(_compile, cmd, log): src for src, cmd, log in jobs}
+        for fut in cf.as_completed(futs):
+            rc, out = fut.result()
+            if verbose or rc != 0:
+                print(out)
+            if rc != 0:
+                raise RuntimeError(f"nvcc failed on {futs[fut]}")
+    if force or jobs or not os.path.exists(KERNEL_LIB):
+        cmd = [nvcc, "-shared", "-o", KERNEL_LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a",
+                                                           "-cudart", "static"]
+        rc, out = _compile(cmd, os.path.join(OBJ_DIR, "link_kernels.log"))
+        if rc != 0:
+            print(out)
+            raise RuntimeError("linking libfdb200_kernels.so failed")
+    return KERNEL_LIB
+
+
+def build_cpu(verbose: bool = False, force: bool = False) -> str:
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    srcs = sorted(glob.glob(os.path.join(CSRC, "cpu", "*.cc")) + glob.glob(os.path.join(CSRC, "capi", "*.cc")))
+    if not srcs:
+        return ""
+    hdrs = glob.glob(os.path.join(CSRC, "cpu", "*.h")) + glob.glob(os.path.join(CSRC, "capi", "*.h"))
+    cxx = shutil.which("g++") or "g++"
+    jobs = []
+    objs = []
+    for s in srcs:
+        o = os.path.join(OBJ_DIR, "cpu_" + os.path.basename(s) + ".o")
+        objs.append(o)
+        if force or _newer(s, o, hdrs):
+            jobs.append((s, [cxx] + CXX_FLAGS + ["-I", os.path.join(CSRC, "cpu"), "-I", os.path.join(CSRC, "capi"),
+                                                 "-c", s, "-o", o], o + ".log"))
+    with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
+        futs = {ex.submit(_compile, cmd, log): src for src, cmd, log in jobs}
+        for fut in cf.as_completed(futs):
+            rc, out = fut.result()
+            if verbose or rc != 0:
+                print(out)
+            if rc != 0:
+                raise RuntimeError(f"g++ failed on {futs[fut]}")
+    if force or jobs or not os.path.exists(CPU_LIB):
+        cmd = [cxx, "-shared", "-o", CPU_LIB] + objs + ["-pthread"]
+        rc, out = _compile(cmd, os.path.join(OBJ_DIR, "link_cpu.log"))
+        if rc != 0:
+            print(out)
+            raise RuntimeError("linking libfdb200_cpu.so failed")
+    return CPU_LIB
+
+
+def build_all(verbose: bool = False, force: bool = False) -> None:
+    build_kernels(verbose=verbose, force=force)
+    build_cpu(verbose=verbose, force=force)
+
+
+if __name__ == "__main__":
+    build_all(verbose="-v" in sys.argv, force="-f" in sys.argv)
+    print("built:", KERNEL_LIB, CPU_LIB if os.path.exists(CPU_LIB) else "")

@@ -1,0 +1,135 @@
+"""tcgen05 implicit-GEMM convolution / GEMM (csrc/kernels/conv_gemm_sm100.cu).
+
+Activations are NHWC fp16/bf16; weights are packed ``[Cout, KH*KW*cin_pad]``
+(K-major, ``cin_pad`` = Cin rounded up to 64). A GEMM ``y[M,N] = x[M,K] @ w[N,K]^T``
+is the 1x1 case over a ``1 x M`` image. This is the op the reference hands to
+TensorRT / Paddle Inference / ONNX Runtime
+(fastdeploy/runtime/backends/tensorrt/trt_backend.cc:347).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _native
+from .base import ACT, NativeOp, StatusWord, dtype_code
+
+K_BLOCK = 64
+
+
+class _ConvGemmDesc(ctypes.Structure):
+    _fields_ = [
+        ("x", ctypes.c_void_p), ("w", ctypes.c_void_p), ("bias", ctypes.c_void_p),
+        ("residual", ctypes.c_void_p), ("y", ctypes.c_void_p), ("status", ctypes.c_void_p),
+        ("dtype", ctypes.c_int), ("out_dtype", ctypes.c_int),
+        ("N", ctypes.c_int), ("H", ctypes.c_int), ("W", ctypes.c_int), ("Cin", ctypes.c_int), ("x_ld", ctypes.c_int),
+        ("Ho", ctypes.c_int), ("Wo", ctypes.c_int), ("Cout", ctypes.c_int), ("y_ld", ctypes.c_int),
+        ("KH", ctypes.c_int), ("KW", ctypes.c_int), ("stride", ctypes.c_int), ("pad_h", ctypes.c_int),
+        ("pad_w", ctypes.c_int),
+        ("res_ld", ctypes.c_int), ("res_mode", ctypes.c_int),
+        ("act", ctypes.c_int), ("act_alpha", ctypes.c_float), ("act_beta", ctypes.c_float),
+        ("tile_w", ctypes.c_int), ("tile_h", ctypes.c_int), ("block_n", ctypes.c_int), ("max_ctas", ctypes.c_int),
+    ]
+
+
+def _lib():
+    lib = _native.kernels()
+    if not getattr(lib, "_conv_gemm_ready", False):
+        lib.fdb_conv_gemm_create.restype = ctypes.c_void_p
+        lib.fdb_conv_gemm_create.argtypes = [ctypes.POINTER(_ConvGemmDesc)]
+        lib.fdb_conv_gemm_info.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]
+        lib._conv_gemm_ready = True
+    return lib
+
+
+def pack_conv_weight(w: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """``[Cout, Cin, KH, KW]`` -> ``[Cout, KH*KW*cin_pad]`` with zero-padded channels."""
+    cout, cin, kh, kw = w.shape
+    cin_pad = (cin + K_BLOCK - 1) // K_BLOCK * K_BLOCK
+    out = torch.zeros(cout, kh, kw, cin_pad, dtype=dtype, device=w.device)
+    out[..., :cin] = w.permute(0, 2, 3, 1).to(dtype)
+    return out.reshape(cout, kh * kw * cin_pad).contiguous()
+
+
+def pack_linear_weight(w: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """``[N, K]`` (torch Linear layout) -> K padded to a multiple of 64."""
+    n, k = w.shape
+    return pack_conv_weight(w.reshape(n, k, 1, 1), dtype)
+
+
+class ConvGemm(NativeOp):
+    """One planned convolution launch. All tensors are fixed at construction."""
+
+    def __init__(self, x: torch.Tensor, w_packed: torch.Tensor, y: torch.Tensor, *,
+                 in_shape: Tuple[int, int, int, int], out_hw: Tuple[int, int], cout: int,
+                 kernel: Tuple[int, int] = (1, 1), stride: int = 1, pad: Tuple[int, int] = (0, 0),
+                 bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+                 res_mode: int = 0, act: Optional[str] = None, act_alpha: float = 0.0, act_beta: float = 0.0,
+                 x_ld: Optional[int] = None, y_ld: Optional[int] = None, res_ld: Optional[int] = None,
+                 status: Optional[StatusWord] = None, tile: Tuple[int, int] = (0, 0), block_n: int = 0,
+                 max_ctas: int = 0, name: str = "conv_gemm"):
+        n, h, w_, cin = in_shape
+        d = _ConvGemmDesc()
+        self.status = status or StatusWord(x.device)
+        d.x, d.w, d.y = x.data_ptr(), w_packed.data_ptr(), y.data_ptr()
+        d.bias = bias.data_ptr() if bias is not None else None
+        d.residual = residual.data_ptr() if residual is not None else None
+        d.status = self.status.ptr
+        d.dtype, d.out_dtype = dtype_code(x.dtype), dtype_code(y.dtype)
+        d.N, d.H, d.W, d.Cin = n, h, w_, cin
+        d.x_ld = x_ld if x_ld is not None else cin
+        d.Ho, d.Wo, d.Cout = out_hw[0], out_hw[1], cout
+        d.y_ld = y_ld if y_ld is not None else cout
+        d.KH, d.KW, d.stride, d.pad_h, d.pad_w = kernel[0], kernel[1], stride, pad[0], pad[1]
+        d.res_ld = res_ld if res_ld is not None else cout
+        d.res_mode = res_mode if residual is not None else 0
+        d.act, d.act_alpha, d.act_beta = ACT[act], act_alpha, act_beta
+        d.tile_w, d.tile_h, d.block_n, d.max_ctas = tile[0], tile[1], block_n, max_ctas
+        if bias is not None:
+            assert bias.dtype == torch.float32
+        if residual is not None:
+            assert residual.dtype == x.dtype
+        assert w_packed.dtype == x.dtype
+        handle = _lib().fdb_conv_gemm_create(ctypes.byref(d))
+        super().__init__(handle, [x, w_packed, y, bias, residual, self.status], name)
+
+    def info(self):
+        out = (ctypes.c_int * 5)()
+        _lib().fdb_conv_gemm_info(self.handle, out)
+        return dict(tile_w=out[0], tile_h=out[1], block_n=out[2], grid=out[3], tiles=out[4])
+
+
+def conv2d_nhwc(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, *, stride: int = 1,
+                pad: int = 0, act: Optional[str] = None, residual: Optional[torch.Tensor] = None,
+                res_mode: int = 0, out_dtype: Optional[torch.dtype] = None, **kw) -> torch.Tensor:
+    """Eager convenience wrapper: ``x`` NHWC, ``weight`` ``[Cout,Cin,KH,KW]`` (any float dtype)."""
+    n, h, w_, cin = x.shape
+    cout, _, kh, kwid = weight.shape
+    ho = (h + 2 * pad - kh) // stride + 1
+    wo = (w_ + 2 * pad - kwid) // stride + 1
+    wp = pack_conv_weight(weight, x.dtype)
+    y = torch.empty(n, ho, wo, cout, dtype=out_dtype or x.dtype, device=x.device)
+    b = bias.float().contiguous() if bias is not None else None
+    op = ConvGemm(x, wp, y, in_shape=(n, h, w_, cin), out_hw=(ho, wo), cout=cout, kernel=(kh, kwid), stride=stride,
+                  pad=(pad, pad), bias=b, residual=residual, res_mode=res_mode, act=act, **kw)
+    op.launch()
+    op.status.check("conv2d_nhwc")
+    return y
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, *, act: Optional[str] = None,
+           residual: Optional[torch.Tensor] = None, res_mode: int = 0, out_dtype: Optional[torch.dtype] = None,
+           **kw) -> torch.Tensor:
+    """Eager ``act(x @ weight.T + bias)`` for ``x [M,K]``, ``weight [N,K]``."""
+    m, k = x.shape
+    nout = weight.shape[0]
+    wp = pack_linear_weight(weight, x.dtype)
+    y = torch.empty(m, nout, dtype=out_dtype or x.dtype, device=x.device)
+    b = bias.float().contiguous() if bias is not None else None
+    op = ConvGemm(x, wp, y, in_shape=(1, 1, m, k), out_hw=(1, m), cout=nout, bias=b, residual=residual,
+                  res_mode=res_mode, act=act, **kw)
+    op.launch()
+    op.status.check("linear")
+    return y

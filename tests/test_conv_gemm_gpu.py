@@ -1,0 +1,113 @@
+"""tcgen05 implicit-GEMM conv / GEMM against a plain PyTorch fp32 reference."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref_conv(x_nhwc, w, b, stride, pad, act, residual=None, res_mode=0):
+    x = x_nhwc.float().permute(0, 3, 1, 2)
+    y = torch.nn.functional.conv2d(x, w.float(), b.float() if b is not None else None, stride=stride, padding=pad)
+    y = y.permute(0, 2, 3, 1)
+    if residual is not None and res_mode == 1:
+        y = y + residual.float()
+    if act == "silu":
+        y = torch.nn.functional.silu(y)
+    elif act == "relu":
+        y = torch.relu(y)
+    elif act == "gelu":
+        y = torch.nn.functional.gelu(y)
+    elif act == "hard_swish":
+        y = torch.nn.functional.hardswish(y)
+    if residual is not None and res_mode == 2:
+        y = y + residual.float()
+    return y
+
+
+def _check(y, ref, tol=2e-2):
+    err = (y.float() - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err / scale < tol, f"max abs err {err} vs scale {scale}"
+
+
+@pytest.mark.parametrize("m,k,n", [(128, 64, 32), (256, 128, 64), (300, 192, 80), (1000, 768, 768), (4096, 1024, 2304),
+                                   (257, 1280, 5120)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_linear(m, k, n, dtype):
+    from fastdeploy_b200.ops.conv_gemm import linear
+    torch.manual_seed(0)
+    x = (torch.randn(m, k, device="cuda") * 0.5).to(dtype)
+    w = (torch.randn(n, k, device="cuda") * 0.05).to(dtype)
+    b = torch.randn(n, device="cuda")
+    y = linear(x, w, b, act="gelu")
+    ref = torch.nn.functional.gelu(x.float() @ w.float().t() + b)
+    _check(y, ref)
+
+
+@pytest.mark.parametrize("block_n", [32, 64, 128, 256])
+def test_linear_block_n(block_n):
+    from fastdeploy_b200.ops.conv_gemm import linear
+    torch.manual_seed(1)
+    x = (torch.randn(520, 256, device="cuda") * 0.5).half()
+    w = (torch.randn(264, 256, device="cuda") * 0.05).half()
+    y = linear(x, w, None, block_n=block_n, out_dtype=torch.float32)
+    _check(y, x.float() @ w.float().t())
+
+
+@pytest.mark.parametrize("cfg", [
+    # n, h, w, cin, cout, k, stride, pad, act
+    (2, 16, 16, 64, 64, 1, 1, 0, None),
+    (2, 16, 16, 64, 64, 3, 1, 1, "silu"),
+    (3, 20, 20, 128, 96, 3, 1, 1, "relu"),
+    (2, 40, 40, 96, 192, 3, 1, 1, "silu"),
+    (1, 33, 47, 32, 40, 3, 1, 1, "hard_swish"),
+    (2, 24, 24, 16, 24, 5, 1, 2, None),
+])
+def test_conv_stride1(cfg):
+    from fastdeploy_b200.ops.conv_gemm import conv2d_nhwc
+    n, h, w_, cin, cout, k, s, p, act = cfg
+    torch.manual_seed(2)
+    x = (torch.randn(n, h, w_, cin, device="cuda") * 0.5).half()
+    w = (torch.randn(cout, cin, k, k, device="cuda") * (1.0 / (cin * k * k) ** 0.5)).half()
+    b = torch.randn(cout, device="cuda") * 0.1
+    y = conv2d_nhwc(x, w, b, stride=s, pad=p, act=act)
+    _check(y, _ref_conv(x, w, b, s, p, act))
+
+
+@pytest.mark.parametrize("cfg", [
+    (2, 16, 16, 64, 64, 3, 2, 1, "silu"),
+    (2, 40, 40, 64, 128, 3, 2, 1, "silu"),
+    (1, 33, 47, 32, 48, 3, 2, 1, None),
+    (2, 32, 32, 64, 64, 1, 2, 0, None),
+])
+def test_conv_stride2(cfg):
+    from fastdeploy_b200.ops.conv_gemm import conv2d_nhwc
+    n, h, w_, cin, cout, k, s, p, act = cfg
+    torch.manual_seed(3)
+    x = (torch.randn(n, h, w_, cin, device="cuda") * 0.5).half()
+    w = (torch.randn(cout, cin, k, k, device="cuda") * (1.0 / (cin * k * k) ** 0.5)).half()
+    b = torch.randn(cout, device="cuda") * 0.1
+    y = conv2d_nhwc(x, w, b, stride=s, pad=p, act=act)
+    _check(y, _ref_conv(x, w, b, s, p, act))
+
+
+@pytest.mark.parametrize("res_mode", [1, 2])
+def test_conv_residual_and_concat_slice(res_mode):
+    """Residual epilogue, and writing into / reading from a channel slice of a wider buffer."""
+    from fastdeploy_b200.ops.conv_gemm import ConvGemm, pack_conv_weight
+    torch.manual_seed(4)
+    n, h, w_, cin, cout = 2, 20, 20, 64, 64
+    xbuf = (torch.randn(n, h, w_, 128, device="cuda") * 0.5).half()
+    x = xbuf[..., 64:]                      # input = upper channel half of a concat buffer
+    ybuf = torch.zeros(n, h, w_, 192, device="cuda", dtype=torch.float16)
+    res = (torch.randn(n, h, w_, cout, device="cuda") * 0.5).half()
+    w = (torch.randn(cout, cin, 3, 3, device="cuda") * 0.04).half()
+    b = torch.randn(cout, device="cuda") * 0.1
+    op = ConvGemm(x, pack_conv_weight(w, torch.float16), ybuf[..., 128:], in_shape=(n, h, w_, cin), out_hw=(h, w_),
+                  cout=cout, kernel=(3, 3), stride=1, pad=(1, 1), bias=b, residual=res, res_mode=res_mode,
+                  act="silu", x_ld=128, y_ld=192)
+    op.launch()
+    op.status.check()
+    ref = _ref_conv(x.contiguous(), w, b, 1, 1, "silu", res, res_mode)
+    _check(ybuf[..., 128:], ref)
+    assert float(ybuf[..., :128].abs().max()) == 0.0
