@@ -11,7 +11,7 @@
 //            exists - plus one 2-D load of the BN x 64 weight slab.
 //   warp 1   MMA issuer   : tcgen05.mma kind::f16, 128 x BN x 16 per instruction,
 //            accumulators double-buffered in TMEM (2 x BN fp32 columns).
-//   warps 2-5 epilogue    : tcgen05.ld TMEM -> registers, + bias, (+ residual),
+//   warps 2-9 epilogue    : tcgen05.ld TMEM -> registers, + bias, (+ residual),
 //            activation, cast, 16-byte stores straight into the (possibly
 //            channel-offset, i.e. concat-fused) NHWC output.
 //
@@ -30,7 +30,8 @@ namespace fdb {
 
 constexpr int kBM = 128;       // tile rows = TMEM lanes
 constexpr int kBK = 64;        // K elements per pipeline stage (128-byte rows)
-constexpr int kThreads = 192;  // 6 warps
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpiWarps;  // producer + MMA + 8 epilogue warps
 
 // C ABI descriptor (mirrored by ctypes in fastdeploy_b200/ops/conv_gemm.py).
 struct ConvGemmDesc {
@@ -51,6 +52,9 @@ struct ConvGemmDesc {
   int tile_w, tile_h;    // 0 = choose
   int block_n;           // 0 = choose (32/64/128/256)
   int max_ctas;          // 0 = one per SM
+  long long x_n_stride;  // elements between images (0 = H*W*x_ld)
+  long long y_n_stride;  // elements between images (0 = Ho*Wo*y_ld)
+  long long res_n_stride;
 };
 
 struct ConvGemmParams {
@@ -67,21 +71,94 @@ struct ConvGemmParams {
   uint32_t a_bytes;
   uint32_t idesc;
   int y_vec, res_vec;
+  long long y_n_stride, res_n_stride;
 };
 
-__device__ __forceinline__ float apply_act(float x, int act, float alpha, float beta) {
+// Generic activation (runtime code); the hot ones have dedicated template paths.
+__device__ __forceinline__ void apply_act8(float (&x)[8], int act, float alpha, float beta) {
   switch (act) {
-    case kActRelu: return fmaxf(x, 0.f);
-    case kActSilu: return __fdividef(x, 1.f + __expf(-x));
-    case kActHardSwish: return x * fminf(fmaxf(x + 3.f, 0.f), 6.f) * (1.f / 6.f);
-    case kActHardSigmoid: return fminf(fmaxf(alpha * x + beta, 0.f), 1.f);
-    case kActSigmoid: return __fdividef(1.f, 1.f + __expf(-x));
-    case kActGelu: return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
-    case kActRelu6: return fminf(fmaxf(x, 0.f), 6.f);
-    case kActLeakyRelu: return x > 0.f ? x : alpha * x;
-    case kActTanh: return tanhf(x);
-    default: return x;
+    case kActRelu:
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = fmaxf(x[j], 0.f);
+      break;
+    case kActSilu:
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = __fdividef(x[j], 1.f + __expf(-x[j]));
+      break;
+    case kActHardSwish:
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = x[j] * fminf(fmaxf(x[j] + 3.f, 0.f), 6.f) * (1.f / 6.f);
+      break;
+    case kActHardSigmoid:
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = fminf(fmaxf(alpha * x[j] + beta, 0.f), 1.f);
+      break;
+    case kActSigmoid:
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = __fdividef(1.f, 1.f + __expf(-x[j]));
+      break;
+    case kActGelu:
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = 0.5f * x[j] * (1.f + erff(x[j] * 0.70710678118654752f));
+      break;
+    case kActRelu6:
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = fminf(fmaxf(x[j], 0.f), 6.f);
+      break;
+    case kActLeakyRelu:
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = x[j] > 0.f ? x[j] : alpha * x[j];
+      break;
+    case kActTanh:
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = tanhf(x[j]);
+      break;
+    default:
+      break;
   }
+}
+
+// x * sigmoid(x) = h * tanh(h) + h with h = x/2 : one MUFU op per two elements.
+__device__ __forceinline__ uint32_t silu_f16x2(uint32_t x) {
+  uint32_t h, t, y;
+  asm("mul.f16x2 %0, %1, %2;" : "=r"(h) : "r"(x), "r"(0x38003800u));
+  asm("tanh.approx.f16x2 %0, %1;" : "=r"(t) : "r"(h));
+  asm("fma.rn.f16x2 %0, %1, %2, %1;" : "=r"(y) : "r"(h), "r"(t));
+  return y;
+}
+__device__ __forceinline__ uint32_t silu_bf16x2(uint32_t x) {
+  uint32_t h, t, y;
+  asm("mul.bf16x2 %0, %1, %2;" : "=r"(h) : "r"(x), "r"(0x3F003F00u));
+  asm("tanh.approx.bf16x2 %0, %1;" : "=r"(t) : "r"(h));
+  asm("fma.rn.bf16x2 %0, %1, %2, %1;" : "=r"(y) : "r"(h), "r"(t));
+  return y;
+}
+__device__ __forceinline__ float silu_f32(float x) {
+  float h = 0.5f * x, t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(h));
+  return fmaf(h, t, h);
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b, bool bf16) {
+  if (bf16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b, bool bf16) {
+  if (bf16) {
+    __nv_bfloat162 r = __hadd2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  __half2 r = __hadd2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t relu2(uint32_t a, bool bf16) {
+  uint32_t y;
+  if (bf16) asm("max.bf16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(0u));
+  else asm("max.f16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(0u));
+  return y;
 }
 
 __device__ __forceinline__ void load8_as_float(const void* ptr, bool bf16, bool vec, int nvalid,
@@ -92,12 +169,10 @@ __device__ __forceinline__ void load8_as_float(const void* ptr, bool bf16, bool 
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       if (bf16) {
-        __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[j]);
-        float2 f = __bfloat1622float2(h);
+        float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
         r[2 * j] = f.x; r[2 * j + 1] = f.y;
       } else {
-        __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
-        float2 f = __half22float2(h);
+        float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
         r[2 * j] = f.x; r[2 * j + 1] = f.y;
       }
     }
@@ -114,43 +189,107 @@ __device__ __forceinline__ void load8_as_float(const void* ptr, bool bf16, bool 
   }
 }
 
-__device__ __forceinline__ void store8(void* ptr, int out_dtype, bool vec, int nvalid,
-                                       const float (&x)[8]) {
+// Slow, fully general store of up to 8 values (tails, misaligned rows, fp32 output).
+__device__ __noinline__ void store8_general(void* ptr, int out_dtype, bool vec, int nvalid,
+                                            const float* x) {
   if (out_dtype == kF32) {
     float* o = reinterpret_cast<float*>(ptr);
     if (vec && nvalid == 8) {
       reinterpret_cast<float4*>(o)[0] = make_float4(x[0], x[1], x[2], x[3]);
       reinterpret_cast<float4*>(o)[1] = make_float4(x[4], x[5], x[6], x[7]);
     } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (j < nvalid) o[j] = x[j];
+      for (int j = 0; j < nvalid; ++j) o[j] = x[j];
     }
     return;
   }
-  const bool bf16 = out_dtype == kBF16;
-  if (vec && nvalid == 8) {
-    uint32_t w[4];
+  for (int j = 0; j < nvalid; ++j) {
+    if (out_dtype == kBF16) reinterpret_cast<__nv_bfloat16*>(ptr)[j] = __float2bfloat16_rn(x[j]);
+    else reinterpret_cast<__half*>(ptr)[j] = __float2half_rn(x[j]);
+  }
+}
+
+// Template activation codes: the three hot ones are compiled in, the rest go
+// through the runtime switch of the generic instantiation.
+constexpr int kTplGeneric = -1;
+
+// One group of 8 consecutive output channels of one output pixel.
+template <int ACT>
+__device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParams& p, int co,
+                                          uint8_t* yrow, const uint8_t* rrow, bool in_bf16,
+                                          int out_es) {
+  const int nvalid = min(8, p.Cout - co);
+  if (nvalid <= 0) return;
+  float x[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (bf16) {
-        __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
-        w[j] = *reinterpret_cast<uint32_t*>(&h);
-      } else {
-        __half2 h = __floats2half2_rn(x[2 * j], x[2 * j + 1]);
-        w[j] = *reinterpret_cast<uint32_t*>(&h);
-      }
-    }
-    *reinterpret_cast<uint4*>(ptr) = make_uint4(w[0], w[1], w[2], w[3]);
-  } else {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (j < nvalid) {
-        if (bf16) reinterpret_cast<__nv_bfloat16*>(ptr)[j] = __float2bfloat16_rn(x[j]);
-        else reinterpret_cast<__half*>(ptr)[j] = __float2half_rn(x[j]);
-      }
+  for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(v[j]);
+  if (p.bias != nullptr) {
+    if (nvalid == 8) {
+      const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + co));
+      const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + co) + 1);
+      x[0] += b0.x; x[1] += b0.y; x[2] += b0.z; x[3] += b0.w;
+      x[4] += b1.x; x[5] += b1.y; x[6] += b1.z; x[7] += b1.w;
+    } else {
+      for (int j = 0; j < nvalid; ++j) x[j] += __ldg(p.bias + co + j);
     }
   }
+  const bool fast16 = p.out_dtype != kF32 && p.y_vec != 0 && nvalid == 8;
+  if (fast16) {
+    const bool out_bf16 = p.out_dtype == kBF16;
+    uint32_t w[4];
+    uint4 rv = make_uint4(0, 0, 0, 0);
+    const bool res_fast = p.res_mode != 0 && p.res_vec != 0 && in_bf16 == out_bf16;
+    if (p.res_mode != 0) {
+      if (res_fast && p.res_mode == 2) {
+        rv = *reinterpret_cast<const uint4*>(rrow + co * 2);
+      } else {
+        float r[8];
+        load8_as_float(rrow + co * 2, in_bf16, p.res_vec != 0, 8, r);
+        if (p.res_mode == 1) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) x[j] += r[j];
+        } else {
+          // after-activation add with mismatching dtypes: stash as packed output type
+          rv = make_uint4(pack2(r[0], r[1], out_bf16), pack2(r[2], r[3], out_bf16),
+                          pack2(r[4], r[5], out_bf16), pack2(r[6], r[7], out_bf16));
+        }
+      }
+    }
+    if (ACT == kTplGeneric) apply_act8(x, p.act, p.act_alpha, p.act_beta);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t h = pack2(x[2 * j], x[2 * j + 1], out_bf16);
+      if (ACT == kActSilu) h = out_bf16 ? silu_bf16x2(h) : silu_f16x2(h);
+      if (ACT == kActRelu) h = relu2(h, out_bf16);
+      w[j] = h;
+    }
+    if (p.res_mode == 2) {
+      w[0] = add2(w[0], rv.x, out_bf16); w[1] = add2(w[1], rv.y, out_bf16);
+      w[2] = add2(w[2], rv.z, out_bf16); w[3] = add2(w[3], rv.w, out_bf16);
+    }
+    *reinterpret_cast<uint4*>(yrow + static_cast<size_t>(co) * 2) = make_uint4(w[0], w[1], w[2], w[3]);
+    return;
+  }
+  // general path: fp32 output, channel tails, unaligned rows
+  float r[8];
+  if (p.res_mode != 0) load8_as_float(rrow + co * 2, in_bf16, p.res_vec != 0, nvalid, r);
+  if (p.res_mode == 1) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] += r[j];
+  }
+  if (ACT == kTplGeneric) apply_act8(x, p.act, p.act_alpha, p.act_beta);
+  if (ACT == kActSilu) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = silu_f32(x[j]);
+  }
+  if (ACT == kActRelu) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = fmaxf(x[j], 0.f);
+  }
+  if (p.res_mode == 2) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] += r[j];
+  }
+  store8_general(yrow + static_cast<size_t>(co) * out_es, p.out_dtype, p.y_vec != 0, nvalid, x);
 }
 
 template <int BN>
@@ -164,7 +303,7 @@ struct KernelCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;  // +1024: alignment slack
 };
 
-template <int BN>
+template <int BN, int ACT>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const ConvGemmParams p) {
@@ -194,7 +333,7 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);
+      mbar_init(tempty_bar(a), kEpiWarps);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -292,7 +431,13 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------ epilogue
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    // Two warps share each TMEM lane quarter and split the tile's columns.
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int kChunks = BN / 32;
+    constexpr int kChunksHalf0 = (kChunks + 1) / 2;
+    const int c_begin = half == 0 ? 0 : kChunksHalf0;
+    const int c_end = half == 0 ? kChunksHalf0 : kChunks;
     const bool in_bf16 = p.in_bf16 != 0;
     const int out_es = p.out_dtype == kF32 ? 4 : 2;
     int acc = 0;
@@ -309,57 +454,38 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int rh = row / p.tw, rw = row - rh * p.tw;
       const int oh = thi * p.th + rh, ow = twi * p.tw + rw;
       const bool valid = rh < p.th && oh < p.Ho && ow < p.Wo;
-      const size_t pix = (static_cast<size_t>(img) * p.Ho + oh) * p.Wo + ow;
-      uint8_t* yrow = reinterpret_cast<uint8_t*>(p.y) + pix * p.y_ld * out_es;
-      const uint8_t* rrow =
-          reinterpret_cast<const uint8_t*>(p.residual) + pix * p.res_ld * 2;
+      const size_t pix = static_cast<size_t>(oh) * p.Wo + ow;
+      uint8_t* yrow = reinterpret_cast<uint8_t*>(p.y) +
+                      (static_cast<size_t>(img) * p.y_n_stride + pix * p.y_ld) * out_es;
+      const uint8_t* rrow = reinterpret_cast<const uint8_t*>(p.residual) +
+                            (static_cast<size_t>(img) * p.res_n_stride + pix * p.res_ld) * 2;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = n_tile * BN + c * 32;
-        if (col0 >= p.Cout) break;
-        uint32_t v[32];
-        tmem_ld_32x32(t_row + c * 32, v);
-        tmem_ld_wait();
+      const int colbase = n_tile * BN;
+      uint32_t va[32], vb[32];
+      int c = c_begin;
+      bool have = c < c_end && colbase + c * 32 < p.Cout;
+      if (have) tmem_ld_32x32(t_row + c * 32, va);
+      while (have) {
+        tmem_ld_wait_dep(va);
+        bool next = (c + 1 < c_end) && (colbase + (c + 1) * 32 < p.Cout);
+        if (next) tmem_ld_32x32(t_row + (c + 1) * 32, vb);
         if (valid) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int co = col0 + g * 8;
-            const int nvalid = min(8, p.Cout - co);
-            if (nvalid > 0) {
-              float x[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(v[g * 8 + j]);
-              if (p.bias != nullptr) {
-                if (nvalid == 8) {
-                  const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + co));
-                  const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + co) + 1);
-                  x[0] += b0.x; x[1] += b0.y; x[2] += b0.z; x[3] += b0.w;
-                  x[4] += b1.x; x[5] += b1.y; x[6] += b1.z; x[7] += b1.w;
-                } else {
-#pragma unroll
-                  for (int j = 0; j < 8; ++j)
-                    if (j < nvalid) x[j] += __ldg(p.bias + co + j);
-                }
-              }
-              float r[8];
-              if (p.res_mode != 0) load8_as_float(rrow + co * 2, in_bf16, p.res_vec != 0, nvalid, r);
-              if (p.res_mode == 1) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) x[j] += r[j];
-              }
-              if (p.act != kActNone) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) x[j] = apply_act(x[j], p.act, p.act_alpha, p.act_beta);
-              }
-              if (p.res_mode == 2) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) x[j] += r[j];
-              }
-              store8(yrow + static_cast<size_t>(co) * out_es, p.out_dtype, p.y_vec != 0, nvalid, x);
-            }
-          }
+          for (int g = 0; g < 4; ++g)
+            epilogue8<ACT>(va + g * 8, p, colbase + c * 32 + g * 8, yrow, rrow, in_bf16, out_es);
         }
+        if (!next) break;
+        ++c;
+        tmem_ld_wait_dep(vb);
+        next = (c + 1 < c_end) && (colbase + (c + 1) * 32 < p.Cout);
+        if (next) tmem_ld_32x32(t_row + (c + 1) * 32, va);
+        if (valid) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            epilogue8<ACT>(vb + g * 8, p, colbase + c * 32 + g * 8, yrow, rrow, in_bf16, out_es);
+        }
+        ++c;
+        have = next;
       }
       tc_fence_before();
       __syncwarp();
@@ -390,20 +516,30 @@ struct ConvGemmOp : Op {
   int launch(cudaStream_t stream) override;
 };
 
-template <int BN>
-static int launch_bn(ConvGemmOp* op, cudaStream_t stream) {
+template <int BN, int ACT>
+static int launch_inst(ConvGemmOp* op, cudaStream_t stream) {
   using Cfg = KernelCfg<BN>;
   static bool attr_set[64] = {false};
   int dev = 0;
   FDB_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 64 && !attr_set[dev]) {
-    FDB_CUDA_OK(cudaFuncSetAttribute(conv_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    FDB_CUDA_OK(cudaFuncSetAttribute(conv_gemm_kernel<BN, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Cfg::kSmemBytes));
     attr_set[dev] = true;
   }
-  conv_gemm_kernel<BN><<<op->grid, kThreads, Cfg::kSmemBytes, stream>>>(op->tmA, op->tmB, op->prm);
+  conv_gemm_kernel<BN, ACT><<<op->grid, kThreads, Cfg::kSmemBytes, stream>>>(op->tmA, op->tmB, op->prm);
   FDB_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+template <int BN>
+static int launch_bn(ConvGemmOp* op, cudaStream_t stream) {
+  switch (op->prm.act) {
+    case kActNone: return launch_inst<BN, kActNone>(op, stream);
+    case kActRelu: return launch_inst<BN, kActRelu>(op, stream);
+    case kActSilu: return launch_inst<BN, kActSilu>(op, stream);
+    default: return launch_inst<BN, kTplGeneric>(op, stream);
+  }
 }
 
 int ConvGemmOp::launch(cudaStream_t stream) {
@@ -504,6 +640,8 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   p.out_dtype = d->out_dtype; p.in_bf16 = d->dtype == kBF16;
   p.KH = d->KH; p.KW = d->KW; p.stride = d->stride; p.pad_h = d->pad_h; p.pad_w = d->pad_w;
   p.act = d->act; p.act_alpha = d->act_alpha; p.act_beta = d->act_beta;
+  p.y_n_stride = d->y_n_stride > 0 ? d->y_n_stride : static_cast<long long>(d->Ho) * d->Wo * d->y_ld;
+  p.res_n_stride = d->res_n_stride > 0 ? d->res_n_stride : static_cast<long long>(d->Ho) * d->Wo * d->res_ld;
   p.a_bytes = static_cast<uint32_t>(tw * th * kBK * 2);
   p.idesc = make_idesc(d->dtype == kBF16 ? 1u : 0u, kBM, bn);
   const int out_es = d->out_dtype == kF32 ? 4 : 2;
@@ -522,7 +660,7 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   {
     cuuint64_t dims[4] = {(cuuint64_t)d->Cin, (cuuint64_t)d->W, (cuuint64_t)d->H, (cuuint64_t)d->N};
     cuuint64_t strides[3] = {(cuuint64_t)d->x_ld * 2, (cuuint64_t)d->W * d->x_ld * 2,
-                             (cuuint64_t)d->H * d->W * d->x_ld * 2};
+                             (cuuint64_t)(d->x_n_stride > 0 ? d->x_n_stride : (long long)d->H * d->W * d->x_ld) * 2};
     cuuint32_t box[4] = {(cuuint32_t)kBK, (cuuint32_t)(tw * d->stride), (cuuint32_t)(th * d->stride), 1};
     cuuint32_t estr[4] = {1, (cuuint32_t)d->stride, (cuuint32_t)d->stride, 1};
     CUresult r = enc(&op->tmA, tdt, 4, const_cast<void*>(d->x), dims, strides, box, estr,

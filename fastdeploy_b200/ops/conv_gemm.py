@@ -31,6 +31,7 @@ class _ConvGemmDesc(ctypes.Structure):
         ("res_ld", ctypes.c_int), ("res_mode", ctypes.c_int),
         ("act", ctypes.c_int), ("act_alpha", ctypes.c_float), ("act_beta", ctypes.c_float),
         ("tile_w", ctypes.c_int), ("tile_h", ctypes.c_int), ("block_n", ctypes.c_int), ("max_ctas", ctypes.c_int),
+        ("x_n_stride", ctypes.c_longlong), ("y_n_stride", ctypes.c_longlong), ("res_n_stride", ctypes.c_longlong),
     ]
 
 
@@ -69,7 +70,8 @@ class ConvGemm(NativeOp):
                  res_mode: int = 0, act: Optional[str] = None, act_alpha: float = 0.0, act_beta: float = 0.0,
                  x_ld: Optional[int] = None, y_ld: Optional[int] = None, res_ld: Optional[int] = None,
                  status: Optional[StatusWord] = None, tile: Tuple[int, int] = (0, 0), block_n: int = 0,
-                 max_ctas: int = 0, name: str = "conv_gemm"):
+                 max_ctas: int = 0, x_n_stride: int = 0, y_n_stride: int = 0, res_n_stride: int = 0,
+                 name: str = "conv_gemm"):
         n, h, w_, cin = in_shape
         d = _ConvGemmDesc()
         self.status = status or StatusWord(x.device)
@@ -87,6 +89,7 @@ class ConvGemm(NativeOp):
         d.res_mode = res_mode if residual is not None else 0
         d.act, d.act_alpha, d.act_beta = ACT[act], act_alpha, act_beta
         d.tile_w, d.tile_h, d.block_n, d.max_ctas = tile[0], tile[1], block_n, max_ctas
+        d.x_n_stride, d.y_n_stride, d.res_n_stride = x_n_stride, y_n_stride, res_n_stride
         if bias is not None:
             assert bias.dtype == torch.float32
         if residual is not None:

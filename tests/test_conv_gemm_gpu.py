@@ -111,3 +111,38 @@ def test_conv_residual_and_concat_slice(res_mode):
     ref = _ref_conv(x.contiguous(), w, b, 1, 1, "silu", res, res_mode)
     _check(ybuf[..., 128:], ref)
     assert float(ybuf[..., :128].abs().max()) == 0.0
+
+
+def test_conv_image_strides_and_fp32_out():
+    """Per-image strides: levels of a detection head land in one [N, anchors, C] buffer."""
+    from fastdeploy_b200.ops.conv_gemm import ConvGemm, pack_conv_weight
+    torch.manual_seed(5)
+    n, h, w_, cin, cout = 3, 10, 10, 64, 68
+    x = (torch.randn(n, h, w_, cin, device="cuda") * 0.5).half()
+    w = (torch.randn(cout, cin, 3, 3, device="cuda") * 0.04).half()
+    b = torch.randn(cout, device="cuda") * 0.1
+    total = 250
+    ybuf = torch.zeros(n, total, cout, device="cuda", dtype=torch.float32)
+    op = ConvGemm(x, pack_conv_weight(w, torch.float16), ybuf[:, 150:], in_shape=(n, h, w_, cin), out_hw=(h, w_),
+                  cout=cout, kernel=(3, 3), stride=1, pad=(1, 1), bias=b, act="sigmoid", y_n_stride=total * cout)
+    op.launch()
+    op.status.check()
+    ref = torch.sigmoid(_ref_conv(x, w, b, 1, 1, None)).reshape(n, h * w_, cout)
+    _check(ybuf[:, 150:], ref, tol=5e-3)
+    assert float(ybuf[:, :150].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("act", ["relu", "silu", "hard_swish", "sigmoid", "gelu", "relu6", "tanh", None])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_linear_activations(act, dtype):
+    from fastdeploy_b200.ops.conv_gemm import linear
+    torch.manual_seed(6)
+    x = (torch.randn(300, 128, device="cuda")).to(dtype)
+    w = (torch.randn(96, 128, device="cuda") * 0.1).to(dtype)
+    b = torch.randn(96, device="cuda")
+    y = linear(x, w, b, act=act)
+    z = x.float() @ w.float().t() + b
+    F = torch.nn.functional
+    ref = {None: lambda t: t, "relu": torch.relu, "silu": F.silu, "hard_swish": F.hardswish, "sigmoid": torch.sigmoid,
+           "gelu": F.gelu, "relu6": F.relu6, "tanh": torch.tanh}[act](z)
+    _check(y, ref, tol=2e-2 if dtype == torch.bfloat16 else 6e-3)
