@@ -1,0 +1,135 @@
+"""Python handles for the memory-bound NHWC kernels (csrc/kernels/nhwc_ops.cu).
+
+Every factory returns a :class:`NativeOp` bound to fixed tensors; channel strides
+(``*_ld``) let an op read or write a channel slice of a wider buffer, which is how
+concat and split disappear from the executed plan.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import _native
+from .base import ACT, DT_BF16, NativeOp, dtype_code
+
+K_GAP_PARTIAL, K_GAP_FINALIZE, K_SE_FC, K_SCALE_CHANNELS, K_MAXPOOL, K_UPSAMPLE, K_COPY, K_DFL, K_BINARY, \
+    K_AVGPOOL, K_CAST, K_UNARY = range(12)
+
+
+class _SimpleDesc(ctypes.Structure):
+    _fields_ = [("p", ctypes.c_void_p * 8), ("i", ctypes.c_longlong * 24), ("f", ctypes.c_float * 8)]
+
+
+def _lib():
+    lib = _native.kernels()
+    if not getattr(lib, "_simple_ready", False):
+        lib.fdb_simple_create.restype = ctypes.c_void_p
+        lib.fdb_simple_create.argtypes = [ctypes.c_int, ctypes.POINTER(_SimpleDesc)]
+        lib._simple_ready = True
+    return lib
+
+
+def make_simple(kind: int, ptrs: Sequence[Optional[torch.Tensor]], ints: Sequence[int],
+                floats: Sequence[float] = (), name: str = "simple") -> NativeOp:
+    d = _SimpleDesc()
+    for k, t in enumerate(ptrs):
+        d.p[k] = t.data_ptr() if t is not None else None
+    for k, v in enumerate(ints):
+        d.i[k] = int(v)
+    for k, v in enumerate(floats):
+        d.f[k] = float(v)
+    return NativeOp(_lib().fdb_simple_create(kind, ctypes.byref(d)), list(ptrs), name)
+
+
+def _bf(t: torch.Tensor) -> int:
+    return 1 if dtype_code(t.dtype) == DT_BF16 else 0
+
+
+def gap_splits(hw: int, n: int, c: int, sms: int = 148) -> int:
+    """Number of pixel splits so that a global average pool fills the GPU."""
+    blocks = n * ((c + 63) // 64)
+    return max(1, min((2 * sms + blocks - 1) // blocks, (hw + 255) // 256))
+
+
+def global_avgpool(x: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, *, n: int, hw: int, c: int,
+                   x_ld: Optional[int] = None, x_n_stride: int = 0, splits: int = 1,
+                   out_ld: Optional[int] = None) -> List[NativeOp]:
+    """``out[n,c] = mean_p x[n,p,c]``. ``scratch`` holds ``n*splits*c`` fp32 partial sums."""
+    assert scratch.dtype == torch.float32 and scratch.numel() >= n * splits * c
+    a = make_simple(K_GAP_PARTIAL, [x, scratch], [n, hw, c, x_ld or c, splits, _bf(x), x_n_stride], name="gap_partial")
+    b = make_simple(K_GAP_FINALIZE, [scratch, out], [n, c, splits, dtype_code(out.dtype), out_ld or c],
+                    [1.0 / hw], name="gap_finalize")
+    return [a, b]
+
+
+def se_fc(v: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, *, n: int, cin: int,
+          cout: int, act: Optional[str] = None, alpha: float = 0.0, beta: float = 0.0) -> NativeOp:
+    """``out[n,co] = act(bias[co] + sum_ci w[co,ci] v[n,ci])`` with fp32 ``v``/``out`` and 16-bit ``w``."""
+    assert v.dtype == torch.float32 and out.dtype == torch.float32
+    return make_simple(K_SE_FC, [v, w, bias, out], [n, cin, cout, ACT[act], _bf(w)], [alpha, beta], name="se_fc")
+
+
+def scale_channels(x: torch.Tensor, s: torch.Tensor, y: torch.Tensor, *, n: int, hw: int, c: int,
+                   x_ld: Optional[int] = None, y_ld: Optional[int] = None, residual: Optional[torch.Tensor] = None,
+                   r_ld: int = 0, x_n_stride: int = 0, y_n_stride: int = 0, r_n_stride: int = 0) -> NativeOp:
+    """``y[n,p,c] = x[n,p,c] * s[n,c] (+ residual[n,p,c])``."""
+    assert s.dtype == torch.float32
+    return make_simple(K_SCALE_CHANNELS, [x, s, y, residual],
+                       [n, hw, c, x_ld or c, y_ld or c, _bf(x), x_n_stride, y_n_stride, r_ld, r_n_stride],
+                       name="scale_channels")
+
+
+def pool2d(x: torch.Tensor, y: torch.Tensor, *, n: int, h: int, w: int, c: int, kernel: Tuple[int, int],
+           stride: Tuple[int, int], pad: Tuple[int, int], out_hw: Tuple[int, int], mode: str = "max",
+           x_ld: Optional[int] = None, y_ld: Optional[int] = None, x_n_stride: int = 0, y_n_stride: int = 0,
+           count_include_pad: bool = False) -> NativeOp:
+    kind = K_MAXPOOL if mode == "max" else K_AVGPOOL
+    return make_simple(kind, [x, y], [n, h, w, c, x_ld or c, out_hw[0], out_hw[1], y_ld or c, kernel[0], kernel[1],
+                                      stride[0], stride[1], pad[0], pad[1], _bf(x), x_n_stride, y_n_stride,
+                                      2 if count_include_pad else 1], name=f"{mode}pool")
+
+
+def upsample_nearest(x: torch.Tensor, y: torch.Tensor, *, n: int, h: int, w: int, c: int, factor: Tuple[int, int],
+                     x_ld: Optional[int] = None, y_ld: Optional[int] = None, x_n_stride: int = 0,
+                     y_n_stride: int = 0) -> NativeOp:
+    return make_simple(K_UPSAMPLE, [x, y], [n, h, w, c, x_ld or c, y_ld or c, factor[0], factor[1], x_n_stride,
+                                            y_n_stride], name="upsample_nearest")
+
+
+def copy_channels(x: torch.Tensor, y: torch.Tensor, *, n: int, h: int, w: int, c: int, x_ld: Optional[int] = None,
+                  y_ld: Optional[int] = None, x_n_stride: int = 0, y_n_stride: int = 0) -> NativeOp:
+    return make_simple(K_COPY, [x, y], [n, h, w, c, x_ld or c, y_ld or c, 1, 1, x_n_stride, y_n_stride],
+                       name="copy_channels")
+
+
+def dfl_decode(reg: torch.Tensor, boxes: torch.Tensor, scale_factor: Optional[torch.Tensor], *, n: int, anchors: int,
+               bins: int, levels: Sequence[Tuple[int, int, int]], offset: float = 0.5) -> NativeOp:
+    """``levels``: ``(first_anchor, grid_width, stride)`` per pyramid level, in anchor order."""
+    ints = [n, anchors, bins, dtype_code(reg.dtype), len(levels)]
+    for st, w, s in levels:
+        ints += [st, w, s]
+    assert boxes.dtype == torch.float32
+    return make_simple(K_DFL, [reg, boxes, scale_factor], ints, [offset], name="dfl_decode")
+
+
+_BIN = {"add": 0, "mul": 1, "sub": 2, "max": 3}
+
+
+def binary(a: torch.Tensor, b: torch.Tensor, y: torch.Tensor, *, rows: int, c: int, op: str = "add",
+           act: Optional[str] = None, a_ld: Optional[int] = None, b_ld: Optional[int] = None,
+           y_ld: Optional[int] = None, broadcast_b: bool = False, alpha: float = 0.0, beta: float = 0.0) -> NativeOp:
+    return make_simple(K_BINARY, [a, b, y], [rows, c, a_ld or c, b_ld or c, y_ld or c, _bf(a), _BIN[op], ACT[act],
+                                             1 if broadcast_b else 0], [alpha, beta], name=f"binary_{op}")
+
+
+def unary(x: torch.Tensor, y: torch.Tensor, *, rows: int, c: int, act: str, x_ld: Optional[int] = None,
+          y_ld: Optional[int] = None, alpha: float = 0.0, beta: float = 0.0) -> NativeOp:
+    return make_simple(K_UNARY, [x, y], [rows, c, x_ld or c, y_ld or c, _bf(x), ACT[act]], [alpha, beta],
+                       name=f"unary_{act}")
+
+
+def cast(x: torch.Tensor, y: torch.Tensor) -> NativeOp:
+    assert x.numel() == y.numel()
+    return make_simple(K_CAST, [x, y], [x.numel(), dtype_code(x.dtype), dtype_code(y.dtype)], name="cast")
