@@ -1,0 +1,669 @@
+"""Graph rewrites applied before lowering: constant folding, BatchNorm / bias folding,
+RepVGG branch folding, activation and residual fusion into convolutions and GEMMs,
+LayerNorm / GELU / attention recognition.
+
+They take over the jobs of the optimisers inside the reference's vendor engines and of
+the paddle2onnx graph passes (paddle2onnx/optimizer/fuse_paddle_conv_bias.h,
+fuse_constant_reshape.h, ...). Every pass keeps the graph executable by the reference
+interpreter, which is how the tests prove pass-on == pass-off.
+"""
+from __future__ import annotations
+
+import math
+from typing import Callable, Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import interp
+from .graph import Graph, Node
+from .shape_infer import ShapeInfo, infer_shapes
+
+ACT_OPS = {"Relu": "relu", "Silu": "silu", "Swish": "silu", "Sigmoid": "sigmoid", "HardSwish": "hard_swish",
+           "Tanh": "tanh", "Gelu": "gelu"}
+
+
+def _single_consumer(cons: Dict[str, List[Node]], graph: Graph, name: str) -> Optional[Node]:
+    c = cons.get(name, [])
+    if len(c) == 1 and name not in graph.output_names():
+        return c[0]
+    return None
+
+
+def _remove(graph: Graph, dead: Sequence[Node]) -> None:
+    ids = {id(n) for n in dead}
+    graph.nodes = [n for n in graph.nodes if id(n) not in ids]
+
+
+def _replace_uses(graph: Graph, old: str, new: str) -> None:
+    for n in graph.nodes:
+        n.inputs = [new if i == old else i for i in n.inputs]
+    for o in graph.outputs:
+        if o.name == old:
+            o.name = new
+
+
+def _act_of(node: Node, graph: Graph):
+    """(activation, alpha, beta) if ``node`` is a fusable unary activation."""
+    if node.op in ACT_OPS and not (node.op == "Gelu" and node.attr("approximate", "none") == "tanh"):
+        return ACT_OPS[node.op], 0.0, 0.0
+    if node.op == "LeakyRelu":
+        return "leaky_relu", float(node.attr("alpha", 0.01)), 0.0
+    if node.op == "HardSigmoid":
+        return "hard_sigmoid", float(node.attr("alpha", 0.2)), float(node.attr("beta", 0.5))
+    if node.op == "Clip":
+        lo = graph.initializers.get(node.inputs[1]) if len(node.inputs) > 1 and node.inputs[1] else node.attr("min")
+        hi = graph.initializers.get(node.inputs[2]) if len(node.inputs) > 2 and node.inputs[2] else node.attr("max")
+        if lo is not None and hi is not None and float(np.asarray(lo)) == 0.0 and float(np.asarray(hi)) == 6.0:
+            return "relu6", 0.0, 0.0
+    return None
+
+
+# --------------------------------------------------------------------------- constants
+def fold_constants(graph: Graph, info: Optional[ShapeInfo] = None) -> int:
+    """Evaluates nodes whose inputs are all constants; with ``info`` also replaces values
+    that shape inference proved constant (shape arithmetic)."""
+    changed = 0
+    keep: List[Node] = []
+    for node in graph.nodes:
+        if info is not None and all(o in info.values for o in node.outputs if o) and node.op not in ("Constant",):
+            small = all(info.values[o].size <= 4096 for o in node.outputs if o)
+            dyn_free = node.op in ("Shape", "Size") or all((i in graph.initializers or i == "") for i in node.inputs)
+            if small and dyn_free:
+                for o in node.outputs:
+                    if o:
+                        graph.initializers[o] = np.ascontiguousarray(info.values[o])
+                changed += 1
+                continue
+        if node.inputs and all((i in graph.initializers or i == "") for i in node.inputs) and node.op in interp._OPS \
+                and node.op not in ("MultiClassNMS",):
+            args = []
+            for i in node.inputs:
+                if i == "":
+                    args.append(None)
+                else:
+                    t = torch.from_numpy(np.ascontiguousarray(graph.initializers[i]))
+                    args.append(t.float() if t.dtype in (torch.float16, torch.float64) else t)
+            while args and args[-1] is None:
+                args.pop()
+            node.attrs.setdefault("_opset", graph.opset)
+            with torch.no_grad():
+                res = interp._OPS[node.op](node, *args)
+            res = res if isinstance(res, tuple) else (res,)
+            for o, r in zip(node.outputs, res):
+                if o:
+                    graph.initializers[o] = np.ascontiguousarray(r.numpy())
+            changed += 1
+            continue
+        keep.append(node)
+    graph.nodes = keep
+    return changed
+
+
+def eliminate_identity(graph: Graph) -> int:
+    changed = 0
+    for node in list(graph.nodes):
+        if node.op in ("Identity", "Dropout") and node.inputs[0] not in graph.initializers:
+            if node.outputs[0] in graph.output_names() and node.inputs[0] in graph.input_names():
+                continue
+            if node.outputs[0] in graph.output_names():
+                # keep the public output name: rename the producer's output instead
+                prod = graph.producers().get(node.inputs[0])
+                if prod is None or len(graph.consumers().get(node.inputs[0], [])) != 1:
+                    continue
+                prod.outputs = [node.outputs[0] if o == node.inputs[0] else o for o in prod.outputs]
+            else:
+                _replace_uses(graph, node.outputs[0], node.inputs[0])
+            _remove(graph, [node])
+            changed += 1
+    return changed
+
+
+# --------------------------------------------------------------------------- conv folding
+def fold_batchnorm(graph: Graph) -> int:
+    """Conv -> BatchNormalization  =>  Conv with scaled weights and folded bias."""
+    changed = 0
+    cons = graph.consumers()
+    for conv in list(graph.nodes):
+        if conv.op != "Conv" or conv.inputs[1] not in graph.initializers:
+            continue
+        bn = _single_consumer(cons, graph, conv.outputs[0])
+        if bn is None or bn.op != "BatchNormalization" or bn.inputs[0] != conv.outputs[0]:
+            continue
+        if not all(i in graph.initializers for i in bn.inputs[1:5]):
+            continue
+        w = graph.initializers[conv.inputs[1]].astype(np.float64)
+        b = graph.initializers[conv.inputs[2]].astype(np.float64) if len(conv.inputs) > 2 and conv.inputs[2] else 0.0
+        scale, bias, mean, var = (graph.initializers[i].astype(np.float64) for i in bn.inputs[1:5])
+        k = scale / np.sqrt(var + bn.attr("epsilon", 1e-5))
+        w2 = (w * k.reshape([-1] + [1] * (w.ndim - 1))).astype(np.float32)
+        b2 = ((b - mean) * k + bias).astype(np.float32)
+        conv.inputs = [conv.inputs[0], graph.const(w2, prefix="w_bnfold"), graph.const(b2, prefix="b_bnfold")]
+        conv.outputs = [bn.outputs[0]]
+        _remove(graph, [bn])
+        cons = graph.consumers()
+        changed += 1
+    return changed
+
+
+def fold_conv_bias_add(graph: Graph) -> int:
+    """Conv -> Add(per-channel constant)  =>  Conv with bias (Paddle exports bias as elementwise_add)."""
+    changed = 0
+    cons = graph.consumers()
+    for conv in list(graph.nodes):
+        if conv.op not in ("Conv", "ConvTranspose") or conv.inputs[1] not in graph.initializers:
+            continue
+        add = _single_consumer(cons, graph, conv.outputs[0])
+        if add is None or add.op != "Add":
+            continue
+        other = add.inputs[1] if add.inputs[0] == conv.outputs[0] else add.inputs[0]
+        if other not in graph.initializers:
+            continue
+        w = graph.initializers[conv.inputs[1]]
+        cout = w.shape[0] if conv.op == "Conv" else w.shape[1] * conv.attr("group", 1)
+        bv = graph.initializers[other]
+        if bv.size != cout or (bv.ndim > 1 and bv.shape[1 if bv.ndim == w.ndim else 0] != cout and bv.size != 1):
+            continue
+        bv = bv.reshape(-1).astype(np.float32)
+        if len(conv.inputs) > 2 and conv.inputs[2]:
+            bv = bv + graph.initializers[conv.inputs[2]].astype(np.float32)
+        conv.inputs = [conv.inputs[0], conv.inputs[1], graph.const(bv, prefix="b_fold")]
+        conv.outputs = [add.outputs[0]]
+        _remove(graph, [add])
+        cons = graph.consumers()
+        changed += 1
+    return changed
+
+
+def fold_repvgg(graph: Graph) -> int:
+    """Add(Conv3x3(x), Conv1x1(x) [, x via identity BN]) => one Conv3x3 (re-parameterisation)."""
+    changed = 0
+    prod = graph.producers()
+    cons = graph.consumers()
+    for add in list(graph.nodes):
+        if add.op != "Add":
+            continue
+        a, b = prod.get(add.inputs[0]), prod.get(add.inputs[1])
+        if a is None or b is None or a.op != "Conv" or b.op != "Conv" or a.inputs[0] != b.inputs[0]:
+            continue
+        if _single_consumer(cons, graph, a.outputs[0]) is not add or _single_consumer(cons, graph, b.outputs[0]) is not add:
+            continue
+        wa, wb = graph.initializers.get(a.inputs[1]), graph.initializers.get(b.inputs[1])
+        if wa is None or wb is None:
+            continue
+        if wa.shape[2:] == (1, 1) and wb.shape[2:] == (3, 3):
+            a, b, wa, wb = b, a, wb, wa
+        if wa.shape[2:] != (3, 3) or wb.shape[2:] != (1, 1) or wa.shape[:2] != wb.shape[:2]:
+            continue
+        if a.attr("strides", [1, 1]) != b.attr("strides", [1, 1]) or a.attr("group", 1) != b.attr("group", 1):
+            continue
+        if list(a.attr("pads", [0] * 4)) != [1, 1, 1, 1] or any(b.attr("pads", [0] * 4)):
+            continue
+        w = wa.astype(np.float32).copy()
+        w[:, :, 1, 1] += wb[:, :, 0, 0]
+        bias = np.zeros(w.shape[0], np.float32)
+        for cnode in (a, b):
+            if len(cnode.inputs) > 2 and cnode.inputs[2]:
+                bias = bias + graph.initializers[cnode.inputs[2]].astype(np.float32)
+        a.inputs = [a.inputs[0], graph.const(w, prefix="w_rep"), graph.const(bias, prefix="b_rep")]
+        a.outputs = [add.outputs[0]]
+        _remove(graph, [b, add])
+        prod, cons = graph.producers(), graph.consumers()
+        changed += 1
+    return changed
+
+
+# --------------------------------------------------------------------------- activation patterns
+def recognize_silu(graph: Graph) -> int:
+    """Mul(x, Sigmoid(x)) => Silu(x);  Mul(x, HardSigmoid(x; 1/6, 0.5)) => HardSwish(x)."""
+    changed = 0
+    prod = graph.producers()
+    cons = graph.consumers()
+    for mul in list(graph.nodes):
+        if mul.op != "Mul":
+            continue
+        for xi, si in ((0, 1), (1, 0)):
+            s = prod.get(mul.inputs[si])
+            if s is None or s.inputs[0] != mul.inputs[xi] or _single_consumer(cons, graph, s.outputs[0]) is not mul:
+                continue
+            if s.op == "Sigmoid":
+                new = "Silu"
+            elif s.op == "HardSigmoid" and abs(s.attr("alpha", 0.2) - 1 / 6) < 1e-6 and abs(s.attr("beta", 0.5) - 0.5) < 1e-6:
+                new = "HardSwish"
+            else:
+                continue
+            mul.op, mul.inputs, mul.attrs = new, [mul.inputs[xi]], {}
+            _remove(graph, [s])
+            prod, cons = graph.producers(), graph.consumers()
+            changed += 1
+            break
+    return changed
+
+
+def recognize_gelu(graph: Graph) -> int:
+    """x * 0.5 * (1 + erf(x / sqrt(2))) in any multiplication order => Gelu(x)."""
+    changed = 0
+    prod = graph.producers()
+    cons = graph.consumers()
+
+    def const_val(name):
+        v = graph.initializers.get(name)
+        return float(v.reshape(-1)[0]) if v is not None and v.size == 1 else None
+
+    for erf in [n for n in graph.nodes if n.op == "Erf"]:
+        div = prod.get(erf.inputs[0])
+        if div is None:
+            continue
+        if div.op == "Div" and const_val(div.inputs[1]) is not None and abs(const_val(div.inputs[1]) - math.sqrt(2)) < 1e-3:
+            x = div.inputs[0]
+        elif div.op == "Mul" and any(const_val(i) is not None and abs(const_val(i) - 1 / math.sqrt(2)) < 1e-3 for i in div.inputs):
+            x = div.inputs[0] if const_val(div.inputs[1]) is not None else div.inputs[1]
+        else:
+            continue
+        add = _single_consumer(cons, graph, erf.outputs[0])
+        if add is None or add.op != "Add" or not any(const_val(i) == 1.0 for i in add.inputs):
+            continue
+        # collect the multiplication chain that follows: needs x and 0.5
+        chain, cur, have_x, have_half = [], add, False, False
+        while True:
+            nxt = _single_consumer(cons, graph, cur.outputs[0])
+            if nxt is None or nxt.op != "Mul":
+                break
+            other = nxt.inputs[1] if nxt.inputs[0] == cur.outputs[0] else nxt.inputs[0]
+            if other == x:
+                have_x = True
+            elif const_val(other) == 0.5:
+                have_half = True
+            else:
+                p = prod.get(other)
+                if p is not None and p.op == "Mul" and x in p.inputs and any(const_val(i) == 0.5 for i in p.inputs) \
+                        and _single_consumer(cons, graph, p.outputs[0]) is nxt:
+                    have_x = have_half = True
+                    chain.append(p)
+                else:
+                    break
+            chain.append(nxt)
+            cur = nxt
+            if have_x and have_half:
+                break
+        if not (have_x and have_half):
+            continue
+        last = chain[-1]
+        graph.nodes[graph.nodes.index(last)] = Node("Gelu", [x], [last.outputs[0]], {"approximate": "none"}, last.name)
+        _remove(graph, [div, erf, add] + chain[:-1])
+        prod, cons = graph.producers(), graph.consumers()
+        changed += 1
+    return changed
+
+
+def recognize_layernorm(graph: Graph) -> int:
+    """ReduceMean / Sub / Pow|Mul / ReduceMean / Add eps / Sqrt / Div / Mul gamma / Add beta => LayerNormalization."""
+    changed = 0
+    prod = graph.producers()
+    cons = graph.consumers()
+    for sqrt in [n for n in graph.nodes if n.op == "Sqrt"]:
+        add_eps = prod.get(sqrt.inputs[0])
+        if add_eps is None or add_eps.op != "Add":
+            continue
+        eps_name = next((i for i in add_eps.inputs if i in graph.initializers and graph.initializers[i].size == 1), None)
+        var_name = next((i for i in add_eps.inputs if i != eps_name), None)
+        var = prod.get(var_name)
+        if eps_name is None or var is None or var.op != "ReduceMean":
+            continue
+        sq = prod.get(var.inputs[0])
+        if sq is None or sq.op not in ("Pow", "Mul"):
+            continue
+        sub = prod.get(sq.inputs[0])
+        if sub is None or sub.op != "Sub":
+            continue
+        mean = prod.get(sub.inputs[1])
+        if mean is None or mean.op != "ReduceMean" or mean.inputs[0] != sub.inputs[0]:
+            continue
+        axes = mean.attr("axes", [-1])
+        if list(axes) not in ([-1],) and not (len(axes) == 1):
+            continue
+        div = _single_consumer(cons, graph, sqrt.outputs[0])
+        if div is None or div.op != "Div" or div.inputs[0] != sub.outputs[0]:
+            continue
+        x = sub.inputs[0]
+        out, dead = div.outputs[0], [mean, sub, sq, var, add_eps, sqrt, div]
+        gamma = beta = ""
+        mul = _single_consumer(cons, graph, out)
+        if mul is not None and mul.op == "Mul":
+            g = next((i for i in mul.inputs if i in graph.initializers), None)
+            if g is not None:
+                gamma, out = g, mul.outputs[0]
+                dead.append(mul)
+                addb = _single_consumer(cons, graph, out)
+                if addb is not None and addb.op == "Add":
+                    bname = next((i for i in addb.inputs if i in graph.initializers), None)
+                    if bname is not None:
+                        beta, out = bname, addb.outputs[0]
+                        dead.append(addb)
+        eps = float(graph.initializers[eps_name].reshape(-1)[0])
+        idx = graph.nodes.index(dead[-1])
+        graph.nodes[idx] = Node("LayerNormalization", [x, gamma, beta], [out], {"axis": int(axes[0]), "epsilon": eps},
+                                graph.unique("n_LayerNorm"))
+        _remove(graph, dead[:-1])
+        prod, cons = graph.producers(), graph.consumers()
+        changed += 1
+    return changed
+
+
+# --------------------------------------------------------------------------- fusion into conv / gemm
+def fuse_conv_activation(graph: Graph) -> int:
+    """Conv (+Add residual) + activation (+Add residual) => FusedConv (domain fdb)."""
+    changed = 0
+    cons = graph.consumers()
+    for conv in list(graph.nodes):
+        if conv.op != "Conv" or conv.inputs[1] not in graph.initializers:
+            continue
+        if conv.attr("auto_pad", "NOTSET") not in ("NOTSET", "VALID") and False:
+            continue
+        out = conv.outputs[0]
+        attrs = dict(conv.attrs)
+        attrs.update(activation="none", act_alpha=0.0, act_beta=0.0, res_mode=0)
+        dead: List[Node] = []
+        residual = ""
+        nxt = _single_consumer(cons, graph, out)
+        # residual before activation (ResNet): Conv -> Add(res) -> Relu
+        if nxt is not None and nxt.op == "Add":
+            other = nxt.inputs[1] if nxt.inputs[0] == out else nxt.inputs[0]
+            after = _single_consumer(cons, graph, nxt.outputs[0])
+            if other not in graph.initializers and other != out and after is not None and _act_of(after, graph):
+                residual, attrs["res_mode"] = other, 1
+                dead.append(nxt)
+                out = nxt.outputs[0]
+                nxt = after
+        if nxt is not None:
+            act = _act_of(nxt, graph)
+            if act is not None:
+                attrs["activation"], attrs["act_alpha"], attrs["act_beta"] = act
+                dead.append(nxt)
+                out = nxt.outputs[0]
+                nxt = _single_consumer(cons, graph, out)
+        # residual after activation (CSPRes basic block): act(Conv) + x
+        if attrs["res_mode"] == 0 and nxt is not None and nxt.op == "Add":
+            other = nxt.inputs[1] if nxt.inputs[0] == out else nxt.inputs[0]
+            if other not in graph.initializers and other != out:
+                residual, attrs["res_mode"] = other, 2
+                dead.append(nxt)
+                out = nxt.outputs[0]
+        bias = conv.inputs[2] if len(conv.inputs) > 2 else ""
+        conv.op, conv.domain = "FusedConv", "fdb"
+        conv.inputs = [conv.inputs[0], conv.inputs[1], bias] + ([residual] if residual else [])
+        conv.outputs = [out]
+        conv.attrs = attrs
+        if dead:
+            # the fused node must come after the residual's producer
+            _remove(graph, dead)
+            if residual:
+                graph.nodes.remove(conv)
+                graph.nodes.append(conv)
+                graph.toposort()
+            cons = graph.consumers()
+        changed += 1
+    return changed
+
+
+def fuse_gemm(graph: Graph, info: Optional[ShapeInfo] = None) -> int:
+    """MatMul(x, W) | Gemm (+Add bias) (+activation) (+Add residual) => FusedGemm with W as [N, K]."""
+    changed = 0
+    cons = graph.consumers()
+    for mm in list(graph.nodes):
+        if mm.op == "MatMul":
+            wname = mm.inputs[1]
+            w = graph.initializers.get(wname)
+            if w is None or w.ndim != 2:
+                continue
+            w_nk = np.ascontiguousarray(w.T)
+            bias = ""
+        elif mm.op == "Gemm":
+            w = graph.initializers.get(mm.inputs[1])
+            if w is None or mm.attr("transA", 0) or mm.attr("alpha", 1.0) != 1.0 or mm.attr("beta", 1.0) != 1.0:
+                continue
+            w_nk = np.ascontiguousarray(w if mm.attr("transB", 0) else w.T)
+            bias = mm.inputs[2] if len(mm.inputs) > 2 else ""
+            if bias and (bias not in graph.initializers or graph.initializers[bias].size != w_nk.shape[0]):
+                continue
+        else:
+            continue
+        out = mm.outputs[0]
+        dead: List[Node] = []
+        attrs = dict(activation="none", act_alpha=0.0, act_beta=0.0, res_mode=0)
+        nxt = _single_consumer(cons, graph, out)
+        if not bias and nxt is not None and nxt.op == "Add":
+            other = nxt.inputs[1] if nxt.inputs[0] == out else nxt.inputs[0]
+            if other in graph.initializers and graph.initializers[other].size == w_nk.shape[0]:
+                bias = graph.const(graph.initializers[other].reshape(-1).astype(np.float32), prefix="b_gemm")
+                dead.append(nxt)
+                out = nxt.outputs[0]
+                nxt = _single_consumer(cons, graph, out)
+        elif bias:
+            bias = graph.const(graph.initializers[bias].reshape(-1).astype(np.float32), prefix="b_gemm")
+        if nxt is not None:
+            act = _act_of(nxt, graph)
+            if act is not None:
+                attrs["activation"], attrs["act_alpha"], attrs["act_beta"] = act
+                dead.append(nxt)
+                out = nxt.outputs[0]
+                nxt = _single_consumer(cons, graph, out)
+        residual = ""
+        if nxt is not None and nxt.op == "Add":
+            other = nxt.inputs[1] if nxt.inputs[0] == out else nxt.inputs[0]
+            same_shape = info is None or info.shapes.get(other) == info.shapes.get(out)
+            if other not in graph.initializers and other != out and same_shape:
+                residual, attrs["res_mode"] = other, 2
+                dead.append(nxt)
+                out = nxt.outputs[0]
+        mm.op, mm.domain = "FusedGemm", "fdb"
+        mm.inputs = [mm.inputs[0], graph.const(w_nk, prefix="w_nk"), bias] + ([residual] if residual else [])
+        mm.outputs = [out]
+        mm.attrs = attrs
+        _remove(graph, dead)
+        if residual:
+            graph.nodes.remove(mm)
+            graph.nodes.append(mm)
+            graph.toposort()
+        cons = graph.consumers()
+        changed += 1
+    return changed
+
+
+# --------------------------------------------------------------------------- transformer blocks
+def fuse_attention(graph: Graph, info: ShapeInfo) -> int:
+    """Recognises multi-head self-attention written with Reshape/Transpose/MatMul/Softmax:
+
+        q,k,v [B,S,H*D] -Reshape-> [B,S,H,D] -Transpose(0,2,1,3)-> [B,H,S,D]
+        softmax(q @ k^T * scale (+ mask)) @ v -Transpose(0,2,1,3)-> Reshape [B,S,H*D]
+
+    and replaces it by one ``Attention`` node (domain fdb). The scale may sit on q, on k or on the scores."""
+    changed = 0
+    prod = graph.producers()
+    cons = graph.consumers()
+
+    def scalar(name):
+        v = graph.initializers.get(name)
+        return float(v.reshape(-1)[0]) if v is not None and v.size == 1 else None
+
+    def peel_scale(name):
+        """value name -> (source name, multiplicative scale)"""
+        p = prod.get(name)
+        if p is not None and p.op in ("Mul", "Div"):
+            for a, b in ((0, 1), (1, 0)):
+                s = scalar(p.inputs[b])
+                if s is not None and (p.op == "Mul" or b == 1):
+                    return p.inputs[a], (s if p.op == "Mul" else 1.0 / s), [p]
+        return name, 1.0, []
+
+    def head_split(name):
+        """[B,H,S,D] value produced by Transpose(0,2,1,3)(Reshape(x)) -> (x, heads, dead nodes)"""
+        t = prod.get(name)
+        if t is None or t.op != "Transpose" or list(t.attr("perm", [])) != [0, 2, 1, 3]:
+            return None
+        r = prod.get(t.inputs[0])
+        if r is None or r.op != "Reshape":
+            return None
+        shp = info.shapes.get(r.outputs[0])
+        if shp is None or len(shp) != 4:
+            return None
+        return r.inputs[0], shp[2], [t, r]
+
+    for sm in [n for n in graph.nodes if n.op == "Softmax"]:
+        dead: List[Node] = [sm]
+        scale = 1.0
+        src = sm.inputs[0]
+        mask = ""
+        p = prod.get(src)
+        if p is not None and p.op == "Add":
+            a, b = p.inputs
+            pa, pb = prod.get(a), prod.get(b)
+            # the branch that leads to a MatMul is the scores; the other is the additive mask
+            def leads_to_mm(nm):
+                q = prod.get(nm)
+                while q is not None and q.op in ("Mul", "Div"):
+                    q = prod.get(q.inputs[0])
+                return q is not None and q.op == "MatMul"
+            if leads_to_mm(a):
+                src, mask = a, b
+            elif leads_to_mm(b):
+                src, mask = b, a
+            else:
+                continue
+            dead.append(p)
+        src, s1, d1 = peel_scale(src)
+        scale *= s1
+        dead += d1
+        qk = prod.get(src)
+        if qk is None or qk.op != "MatMul":
+            continue
+        dead.append(qk)
+        qn, s2, d2 = peel_scale(qk.inputs[0])
+        scale *= s2
+        dead += d2
+        kn = qk.inputs[1]
+        kt = prod.get(kn)
+        if kt is None or kt.op != "Transpose":
+            continue
+        perm = list(kt.attr("perm", []))
+        if perm == [0, 1, 3, 2]:
+            kn2, s3, d3 = peel_scale(kt.inputs[0])
+            ksplit = head_split(kn2)
+            dead += [kt] + d3
+            scale *= s3
+        elif perm == [0, 2, 3, 1]:      # Transpose straight from [B,S,H,D] to [B,H,D,S]
+            r = prod.get(kt.inputs[0])
+            if r is None or r.op != "Reshape":
+                continue
+            shp = info.shapes.get(r.outputs[0])
+            ksplit = (r.inputs[0], shp[2], [kt, r])
+        else:
+            continue
+        qsplit = head_split(qn)
+        pv = _single_consumer(cons, graph, sm.outputs[0])
+        if pv is None or pv.op != "MatMul" or pv.inputs[0] != sm.outputs[0]:
+            continue
+        vsplit = head_split(pv.inputs[1])
+        if qsplit is None or ksplit is None or vsplit is None:
+            continue
+        t_out = _single_consumer(cons, graph, pv.outputs[0])
+        if t_out is None or t_out.op != "Transpose" or list(t_out.attr("perm", [])) != [0, 2, 1, 3]:
+            continue
+        r_out = _single_consumer(cons, graph, t_out.outputs[0])
+        if r_out is None or r_out.op != "Reshape":
+            continue
+        heads = qsplit[1]
+        dead += [pv, t_out] + qsplit[2] + ksplit[2] + vsplit[2]
+        # every removed node must feed only this pattern
+        dead_ids = {id(n) for n in dead} | {id(r_out)}
+        ok = True
+        for n in dead:
+            for o in n.outputs:
+                if any(id(cn) not in dead_ids for cn in cons.get(o, [])) or o in graph.output_names():
+                    ok = False
+        if not ok:
+            continue
+        node = Node("Attention", [qsplit[0], ksplit[0], vsplit[0]] + ([mask] if mask else []), [r_out.outputs[0]],
+                    {"num_heads": int(heads), "scale": float(scale)}, graph.unique("n_Attention"), "fdb")
+        graph.nodes[graph.nodes.index(r_out)] = node
+        _remove(graph, dead)
+        graph.toposort()
+        prod, cons = graph.producers(), graph.consumers()
+        changed += 1
+    return changed
+
+
+def fuse_embed_layernorm(graph: Graph) -> int:
+    """LayerNormalization(Gather(T0, ids0) + Gather(T1, ids1) + ...) => EmbedLayerNorm (domain fdb)."""
+    changed = 0
+    prod = graph.producers()
+    cons = graph.consumers()
+    for ln in [n for n in graph.nodes if n.op == "LayerNormalization"]:
+        leaves, dead, stack = [], [], [ln.inputs[0]]
+        ok = True
+        while stack:
+            name = stack.pop()
+            p = prod.get(name)
+            if p is None:
+                ok = False
+                break
+            if p.op == "Add" and _single_consumer(cons, graph, p.outputs[0]) is not None:
+                dead.append(p)
+                stack += [p.inputs[1], p.inputs[0]]
+            elif p.op == "Gather" and p.inputs[0] in graph.initializers and p.attr("axis", 0) == 0 \
+                    and graph.initializers[p.inputs[0]].ndim == 2 and _single_consumer(cons, graph, p.outputs[0]) is not None:
+                dead.append(p)
+                leaves.append((p.inputs[1], p.inputs[0]))
+            else:
+                ok = False
+                break
+        if not ok or len(leaves) < 2 or not ln.inputs[1] or not ln.inputs[2]:
+            continue
+        ids = [l[0] for l in leaves]
+        tabs = [l[1] for l in leaves]
+        node = Node("EmbedLayerNorm", ids + tabs + [ln.inputs[1], ln.inputs[2]], [ln.outputs[0]],
+                    {"num_tables": len(leaves), "epsilon": float(ln.attr("epsilon", 1e-5))},
+                    graph.unique("n_EmbedLayerNorm"), "fdb")
+        graph.nodes[graph.nodes.index(ln)] = node
+        _remove(graph, dead)
+        graph.toposort()
+        prod, cons = graph.producers(), graph.consumers()
+        changed += 1
+    return changed
+
+
+# --------------------------------------------------------------------------- pipelines
+def optimize(graph: Graph, input_shapes: Optional[Dict[str, Sequence[int]]] = None,
+             input_values: Optional[Dict[str, np.ndarray]] = None, level: int = 2) -> Graph:
+    """Runs the standard pipeline on a copy of ``graph``.
+
+    level 0: nothing; 1: constant folding and BN / bias folding (numerically safe rewrites);
+    2: + operator fusion into FusedConv / FusedGemm / Attention / EmbedLayerNorm."""
+    g = graph.clone()
+    if level <= 0:
+        return g
+    g.toposort()
+    eliminate_identity(g)
+    info = None
+    if input_shapes is not None:
+        info = infer_shapes(g, input_shapes, input_values)
+    for _ in range(4):
+        if not fold_constants(g, info):
+            break
+    fold_conv_bias_add(g)
+    fold_batchnorm(g)
+    fold_conv_bias_add(g)
+    fold_repvgg(g)
+    recognize_silu(g)
+    recognize_gelu(g)
+    recognize_layernorm(g)
+    if level >= 2:
+        if info is not None:
+            info = infer_shapes(g, input_shapes, input_values)
+            fuse_attention(g, info)
+        fuse_embed_layernorm(g)
+        fuse_conv_activation(g)
+        fuse_gemm(g, info)
+    g.prune()
+    g.toposort()
+    return g
