@@ -343,7 +343,8 @@ __global__ void cast_kernel<__nv_bfloat16, float>(const __nv_bfloat16* __restric
 // per-image scale factor (h_ratio, w_ratio) so that boxes are in source-image pixels
 // (fastdeploy/vision/detection/ppdet/postprocessor.cc:171-180).
 // p0 reg, p1 boxes, p2 scale_factor fp32 [N][2] or null; i0 N, i1 A, i2 R+1 (bins), i3 reg dtype,
-// i4 num levels, i5.. per level: start, W, stride (3 ints each, up to 5 levels); f0 grid cell offset
+// i4 num levels, i5.. per level: start, W, stride (3 ints each, up to 5 levels), i20 elements between
+// anchors of reg (0 = 4*bins); f0 grid cell offset
 struct DflLevels {
   int n;
   int start[5], w[5], stride[5];
@@ -359,13 +360,13 @@ template <> __device__ __forceinline__ float ld_as_float<__nv_bfloat16>(const __
 template <typename T>
 __global__ void dfl_decode_kernel(const T* __restrict__ reg, float* __restrict__ boxes,
                                   const float* __restrict__ scale_factor, int N, int A, int bins, DflLevels lv,
-                                  float offset) {
+                                  float offset, int reg_ld) {
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;  // one thread per (n, a, side)
   if (idx >= N * A * 4) return;
   const int side = idx & 3;
   const int na = idx >> 2;
   const int n = na / A, a = na - n * A;
-  const T* p = reg + (static_cast<size_t>(na) * 4 + side) * bins;
+  const T* p = reg + static_cast<size_t>(na) * reg_ld + side * bins;
   float m = -INFINITY;
   for (int k = 0; k < bins; ++k) m = fmaxf(m, ld_as_float<T>(p + k));
   float den = 0.f, num = 0.f;
@@ -508,12 +509,13 @@ FDB_API void* fdb_simple_create(int kind, const SimpleDesc* dp) {
         lv.stride[k] = static_cast<int>(d.i[7 + 3 * k]);
       }
       const float off = d.f[0];
+      const int reg_ld = d.i[20] > 0 ? static_cast<int>(d.i[20]) : 4 * bins;
       op->fn = [=](cudaStream_t s) {
         const int total = N * A * 4;
         const int grid = (total + 255) / 256;
-        if (rdt == kF32) dfl_decode_kernel<float><<<grid, 256, 0, s>>>((const float*)d.p[0], (float*)d.p[1], (const float*)d.p[2], N, A, bins, lv, off);
-        else if (rdt == kBF16) dfl_decode_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)d.p[0], (float*)d.p[1], (const float*)d.p[2], N, A, bins, lv, off);
-        else dfl_decode_kernel<__half><<<grid, 256, 0, s>>>((const __half*)d.p[0], (float*)d.p[1], (const float*)d.p[2], N, A, bins, lv, off);
+        if (rdt == kF32) dfl_decode_kernel<float><<<grid, 256, 0, s>>>((const float*)d.p[0], (float*)d.p[1], (const float*)d.p[2], N, A, bins, lv, off, reg_ld);
+        else if (rdt == kBF16) dfl_decode_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)d.p[0], (float*)d.p[1], (const float*)d.p[2], N, A, bins, lv, off, reg_ld);
+        else dfl_decode_kernel<__half><<<grid, 256, 0, s>>>((const __half*)d.p[0], (float*)d.p[1], (const float*)d.p[2], N, A, bins, lv, off, reg_ld);
         FDB_LAUNCH_CHECK();
       };
       break;

@@ -455,16 +455,8 @@ def _fc(c, op):
 
 @mapper("softmax")
 def _softmax(c, op):
-    axis = int(op.attr("axis", -1))
-    x = op.input("X")
-    r = c.rank(x)
-    if axis in (-1, (r - 1) if r else -1):
-        c.emit("Softmax", [x], [op.output("Out")], axis=-1, _opset=13)
-    else:
-        perm = list(range(r)); perm[axis], perm[-1] = perm[-1], perm[axis]
-        t = c.g.op("Transpose", x, perm=perm)
-        t = c.g.op("Softmax", t, axis=-1, _opset=13)
-        c.emit("Transpose", [t], [op.output("Out")], perm=perm)
+    # the IR is opset 13: Softmax normalises along one arbitrary axis
+    c.emit("Softmax", [op.input("X")], [op.output("Out")], axis=int(op.attr("axis", -1)), _opset=13)
 
 
 @mapper("log_softmax")

@@ -732,6 +732,31 @@ def _mc_nms(node, boxes, scores):
             torch.from_numpy(num.astype(np.int32)))
 
 
+@op("PPYOLOEPost")
+def _ppyoloe_post(node, *args):
+    """DFL integral + distance->box + stride + scale-factor division + multiclass NMS; domain fdb.
+
+    inputs: cls_0..cls_{L-1} [b,C,H,W] (scores), reg_0..reg_{L-1} [b,4*bins,H,W] (logits), scale_factor [b,2]"""
+    nl = node.attr("num_levels")
+    cls, reg, sf = args[:nl], args[nl:2 * nl], args[2 * nl]
+    bins = node.attr("bins")
+    boxes, scores = [], []
+    for i in range(nl):
+        b, c, h, w = cls[i].shape
+        scores.append(cls[i].float().reshape(b, c, h * w))
+        r = reg[i].float().reshape(b, 4, bins, h * w).permute(0, 3, 1, 2)          # [b, l, 4, bins]
+        dist = (torch.softmax(r, -1) * torch.arange(bins, dtype=torch.float32, device=r.device)).sum(-1)
+        ys, xs = torch.meshgrid(torch.arange(h, device=r.device) + node.attr("offset", 0.5),
+                                torch.arange(w, device=r.device) + node.attr("offset", 0.5), indexing="ij")
+        pts = torch.stack([xs.reshape(-1), ys.reshape(-1)], -1).float()
+        bx = torch.cat([pts - dist[..., :2], pts + dist[..., 2:]], -1) * float(node.attr("strides")[i])
+        boxes.append(bx)
+    boxes = torch.cat(boxes, 1)
+    sf = sf.float()
+    boxes = boxes / torch.stack([sf[:, 1], sf[:, 0], sf[:, 1], sf[:, 0]], -1)[:, None, :]
+    return _mc_nms(node, boxes, torch.cat(scores, 2))
+
+
 @op("LSTM")
 def _lstm(node, x, w, r, b=None, seq_lens=None, h0=None, c0=None, *_):
     """Single-layer forward/bidirectional LSTM, ONNX gate order i,o,f,c."""

@@ -664,6 +664,106 @@ def optimize(graph: Graph, input_shapes: Optional[Dict[str, Sequence[int]]] = No
         fuse_embed_layernorm(g)
         fuse_conv_activation(g)
         fuse_gemm(g, info)
+        if info is not None and any(n.op == "MultiClassNMS" for n in g.nodes):
+            info = infer_shapes(g, input_shapes, input_values)
+            fuse_ppyoloe_head(g, info)
     g.prune()
     g.toposort()
     return g
+
+
+# --------------------------------------------------------------------------- PP-YOLOE head
+def fuse_ppyoloe_head(graph: Graph, info: ShapeInfo) -> int:
+    """Collapses the exported PP-YOLOE ET-head tail - per level Reshape/Transpose/Softmax/projection
+    conv (DFL integral), distance->box with constant anchor points and strides, division by the
+    scale factor, score concat and ``MultiClassNMS`` - into one ``PPYOLOEPost`` node (domain fdb)
+    that consumes the per-level class-score maps ``[b,C,H,W]`` and regression maps ``[b,4*bins,H,W]``."""
+    changed = 0
+    prod = graph.producers()
+
+    def const(name):
+        return graph.initializers.get(name)
+
+    for nms in [n for n in graph.nodes if n.op == "MultiClassNMS"]:
+        try:
+            boxes_name, scores_name = nms.inputs[:2]
+            sc = prod[scores_name]
+            assert sc.op == "Concat"
+            cls_src, grids = [], []
+            for nm in sc.inputs:
+                r = prod[nm]
+                assert r.op == "Reshape"
+                shp = info.shapes[r.inputs[0]]
+                assert len(shp) == 4 and info.shapes[nm] == [shp[0], shp[1], shp[2] * shp[3]]
+                cls_src.append(r.inputs[0])
+                grids.append((shp[2], shp[3]))
+            div = prod[boxes_name]
+            assert div.op == "Div"
+            # scale factor expression: Reshape(Concat(sx, sy, sx, sy)) with (sy, sx) = Split(scale_factor)
+            rs = prod[div.inputs[1]]
+            assert rs.op == "Reshape"
+            cc = prod[rs.inputs[0]]
+            assert cc.op == "Concat" and len(cc.inputs) == 4
+            sp = prod[cc.inputs[0]]
+            assert sp.op == "Split" and sp.inputs[0] in graph.input_names()
+            assert cc.inputs == [sp.outputs[1], sp.outputs[0], sp.outputs[1], sp.outputs[0]]
+            sf_input = sp.inputs[0]
+            mul = prod[div.inputs[0]]
+            assert mul.op == "Mul"
+            stride_c = const(mul.inputs[1]) if const(mul.inputs[1]) is not None else const(mul.inputs[0])
+            cat_name = mul.inputs[0] if const(mul.inputs[1]) is not None else mul.inputs[1]
+            cat = prod[cat_name]
+            assert cat.op == "Concat" and len(cat.inputs) == 2
+            sub, add = prod[cat.inputs[0]], prod[cat.inputs[1]]
+            assert sub.op == "Sub" and add.op == "Add"
+            anchor = const(sub.inputs[0])
+            assert anchor is not None
+            lt = sub.inputs[1]
+            rb = add.inputs[0] if const(add.inputs[1]) is not None else add.inputs[1]
+            spl = prod[lt]
+            assert spl.op == "Split" and spl.outputs == [lt, rb]
+            dcat = prod[spl.inputs[0]]
+            assert dcat.op == "Concat"
+            reg_src, bins = [], None
+            for nm in dcat.inputs:
+                sq = prod[nm]
+                assert sq.op == "Squeeze"
+                cv = prod[sq.inputs[0]]
+                assert cv.op in ("Conv", "FusedConv") and cv.attr("activation", "none") == "none"
+                w = const(cv.inputs[1])
+                assert w is not None and w.shape[0] == 1 and np.allclose(w.reshape(-1), np.arange(w.size))
+                bins = int(w.size)
+                sm = prod[cv.inputs[0]]
+                assert sm.op == "Softmax"
+                tr = prod[sm.inputs[0]]
+                assert tr.op == "Transpose" and list(tr.attr("perm")) == [0, 2, 3, 1]
+                rr = prod[tr.inputs[0]]
+                assert rr.op == "Reshape"
+                rshape = info.shapes[rr.inputs[0]]
+                assert len(rshape) == 4 and rshape[1] == 4 * bins
+                reg_src.append(rr.inputs[0])
+            assert len(reg_src) == len(cls_src)
+            # anchors / strides must be the canonical grid
+            strides, pos = [], 0
+            for (h, w) in grids:
+                l = h * w
+                ys, xs = np.meshgrid(np.arange(h, dtype=np.float32) + 0.5, np.arange(w, dtype=np.float32) + 0.5, indexing="ij")
+                pts = np.stack([xs.reshape(-1), ys.reshape(-1)], -1)
+                assert np.allclose(anchor[pos:pos + l], pts)
+                s = stride_c.reshape(-1)[pos:pos + l]
+                assert np.all(s == s[0])
+                strides.append(int(s[0]))
+                pos += l
+            assert pos == anchor.shape[0]
+        except (AssertionError, KeyError, IndexError):
+            continue
+        attrs = {k: v for k, v in nms.attrs.items() if not k.startswith("_")}
+        attrs.update(strides=strides, grid_h=[g[0] for g in grids], grid_w=[g[1] for g in grids], bins=bins,
+                     offset=0.5, num_levels=len(grids))
+        node = Node("PPYOLOEPost", cls_src + reg_src + [sf_input], list(nms.outputs), attrs,
+                    graph.unique("n_PPYOLOEPost"), "fdb")
+        graph.nodes[graph.nodes.index(nms)] = node
+        graph.prune()
+        prod = graph.producers()
+        changed += 1
+    return changed

@@ -80,10 +80,14 @@ def infer_shapes(graph: Graph, input_shapes: Dict[str, Sequence[int]],
                 res = torch.tensor(list(args[0].shape), dtype=torch.int64)
             elif node.op == "Size":
                 res = torch.tensor(args[0].numel(), dtype=torch.int64)
-            elif node.op == "MultiClassNMS":
+            elif node.op in ("MultiClassNMS", "PPYOLOEPost"):
                 n = args[0].shape[0]
                 k = node.attr("keep_top_k", 100)
-                k = k if k > 0 else args[0].shape[1]
+                if node.op == "PPYOLOEPost":
+                    m = sum(h * w for h, w in zip(node.attr("grid_h"), node.attr("grid_w")))
+                else:
+                    m = args[0].shape[1]
+                k = k if k > 0 else m
                 res = (torch.empty(n * k, 6, device="meta"), torch.empty(n * k, 1, dtype=torch.int64, device="meta"),
                        torch.empty(n, dtype=torch.int32, device="meta"))
             else:

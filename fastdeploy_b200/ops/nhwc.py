@@ -105,11 +105,12 @@ def copy_channels(x: torch.Tensor, y: torch.Tensor, *, n: int, h: int, w: int, c
 
 
 def dfl_decode(reg: torch.Tensor, boxes: torch.Tensor, scale_factor: Optional[torch.Tensor], *, n: int, anchors: int,
-               bins: int, levels: Sequence[Tuple[int, int, int]], offset: float = 0.5) -> NativeOp:
+               bins: int, levels: Sequence[Tuple[int, int, int]], offset: float = 0.5, reg_ld: int = 0) -> NativeOp:
     """``levels``: ``(first_anchor, grid_width, stride)`` per pyramid level, in anchor order."""
     ints = [n, anchors, bins, dtype_code(reg.dtype), len(levels)]
     for st, w, s in levels:
         ints += [st, w, s]
+    ints += [0] * (20 - len(ints)) + [reg_ld]
     assert boxes.dtype == torch.float32
     return make_simple(K_DFL, [reg, boxes, scale_factor], ints, [offset], name="dfl_decode")
 

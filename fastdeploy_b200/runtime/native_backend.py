@@ -1,0 +1,744 @@
+"""The single native backend: lowers an optimised IR graph to a static launch plan of
+sm_100a kernels for one concrete set of input shapes ("shape bucket"), optionally
+captured into a CUDA graph.
+
+It replaces the reference's ten vendor backends behind ``BaseBackend``
+(fastdeploy/runtime/backends/backend.h:51-97): where TensorRT rebuilds an engine when
+an unseen shape arrives (fastdeploy/runtime/backends/tensorrt/trt_backend.cc:327-339),
+this backend keeps one plan per shape bucket and builds a new one in milliseconds.
+
+Layout and precision: 4-D activations live as NHWC fp16/bf16 tensors (logically NCHW),
+channel counts are padded to multiples of 8, concat / split along channels are
+realised as channel-slice views so producers write straight into the concatenated
+buffer. Operators without a hand-written kernel run through the interpreter's torch
+implementation on the GPU in fp32 (shape plumbing and tiny tensors only).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import _native
+from ..ir import interp, passes
+from ..ir.graph import Graph, Node
+from ..ir.shape_infer import ShapeInfo, infer_shapes
+from ..ops import nhwc as K
+from ..ops.base import NativeOp, StatusWord, current_stream_ptr
+from ..ops.conv_gemm import ConvGemm, pack_conv_weight, pack_linear_weight
+from ..ops.nms import MulticlassNMS
+
+
+def _round8(c: int) -> int:
+    return (c + 7) // 8 * 8
+
+
+@dataclass
+class Val:
+    """A value on the device. ``nhwc``: ``t`` is ``[N,H,W,C]`` (maybe a channel slice of a
+    wider buffer, ``t.stride(2)`` = channel stride) holding the logical ``[N,C,H,W]`` tensor;
+    otherwise ``t`` is a torch tensor in the logical layout."""
+    t: torch.Tensor
+    nhwc: bool = False
+
+    @property
+    def logical_shape(self) -> List[int]:
+        if self.nhwc:
+            n, h, w, c = self.t.shape
+            return [n, c, h, w]
+        return list(self.t.shape)
+
+    def logical(self) -> torch.Tensor:
+        return self.t.permute(0, 3, 1, 2) if self.nhwc else self.t
+
+    @property
+    def ld(self) -> int:
+        return self.t.stride(2)
+
+    @property
+    def n_stride(self) -> int:
+        return self.t.stride(0)
+
+
+class Step:
+    """One plan entry: a native op or a python callable."""
+    __slots__ = ("fn", "native", "name", "node")
+
+    def __init__(self, fn: Callable[[], None], native: Optional[NativeOp], name: str, node: Optional[Node]):
+        self.fn, self.native, self.name, self.node = fn, native, name, node
+
+
+class Plan:
+    """Static launch list for one shape bucket."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.steps: List[Step] = []
+        self.inputs: Dict[str, Val] = {}
+        self.outputs: Dict[str, Val] = {}
+        self.status = StatusWord(device)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.native_plan = None
+        self._segments: List[Any] = []
+        self.native_kernel_launches = 0
+        self.extra: Dict[str, Any] = {}
+
+    # ------------------------------------------------------------------ building
+    def add_native(self, op: NativeOp, node: Optional[Node] = None, launches: int = 1) -> None:
+        self.steps.append(Step(op.launch, op, op.name, node))
+        self.native_kernel_launches += launches
+
+    def add_py(self, fn: Callable[[], None], name: str, node: Optional[Node] = None) -> None:
+        self.steps.append(Step(fn, None, name, node))
+
+    def finalize(self) -> None:
+        """Groups consecutive native ops into native sub-plans (one ctypes call each)."""
+        lib = _native.kernels()
+        self._segments = []
+        run: List[Step] = []
+
+        def flush():
+            if not run:
+                return
+            handle = ctypes.c_void_p(lib.fdb_plan_create())
+            for s in run:
+                lib.fdb_plan_add(handle, s.native.handle, 0)
+            self._segments.append(("native", handle, list(run)))
+            run.clear()
+        for s in self.steps:
+            if s.native is not None:
+                run.append(s)
+            else:
+                flush()
+                self._segments.append(("py", s.fn, s))
+        flush()
+
+    # ------------------------------------------------------------------ running
+    def run(self) -> None:
+        if self.graph is not None:
+            self.graph.replay()
+            return
+        self._run_eager()
+
+    def _run_eager(self) -> None:
+        lib = _native.kernels()
+        stream = ctypes.c_void_p(current_stream_ptr(self.device))
+        for kind, obj, _ in self._segments:
+            if kind == "native":
+                if lib.fdb_plan_run(obj, stream) != 0:
+                    raise RuntimeError(f"native plan failed: {_native.last_error()}")
+            else:
+                obj()
+
+    def capture(self, warmup: int = 2) -> None:
+        """Captures the whole plan into one CUDA graph (replay = one launch)."""
+        s = torch.cuda.Stream(self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            for _ in range(warmup):
+                self._run_eager()
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            self._run_eager()
+        self.graph = g
+
+    def __del__(self):
+        try:
+            lib = _native.kernels()
+            for kind, obj, _ in self._segments:
+                if kind == "native":
+                    lib.fdb_plan_destroy(obj)
+        except Exception:
+            pass
+
+
+class Lowering:
+    """Builds a :class:`Plan` from an optimised graph and concrete input shapes."""
+
+    def __init__(self, graph: Graph, input_shapes: Dict[str, Sequence[int]], device: torch.device,
+                 dtype: torch.dtype = torch.float16, input_values: Optional[Dict[str, np.ndarray]] = None):
+        self.g = graph
+        self.device = device
+        self.dtype = dtype
+        self.info: ShapeInfo = infer_shapes(graph, input_shapes, input_values)
+        self.plan = Plan(device)
+        self.vals: Dict[str, Val] = {}
+        self.consts: Dict[str, torch.Tensor] = {}
+        self.packed: Dict[Tuple[str, str], torch.Tensor] = {}
+        self.cons = graph.consumers()
+        self.prod = graph.producers()
+        self.preassigned: Dict[str, Val] = {}
+        self.input_shapes = {k: list(v) for k, v in input_shapes.items()}
+
+    # ------------------------------------------------------------------ helpers
+    def const_f32(self, name: str) -> torch.Tensor:
+        key = name
+        if key not in self.consts:
+            arr = self.g.initializers[name]
+            t = torch.from_numpy(np.ascontiguousarray(arr))
+            if t.dtype in (torch.float16, torch.float64):
+                t = t.float()
+            self.consts[key] = t.to(self.device)
+        return self.consts[key]
+
+    def new_nhwc(self, n: int, h: int, w: int, c: int, dtype: Optional[torch.dtype] = None) -> Val:
+        cp = _round8(c)
+        buf = torch.zeros(n, h, w, cp, dtype=dtype or self.dtype, device=self.device)
+        return Val(buf[..., :c], True)
+
+    def out_nhwc(self, name: str, dtype: Optional[torch.dtype] = None) -> Val:
+        """Destination of a 4-D op output: the pre-assigned concat slice or a fresh buffer."""
+        if name in self.preassigned:
+            return self.preassigned[name]
+        n, c, h, w = self.info.shapes[name]
+        return self.new_nhwc(n, h, w, c, dtype)
+
+    def as_nhwc(self, name: str) -> Val:
+        """Value as a 16-bit NHWC tensor with 8-aligned channel stride (converting if needed)."""
+        v = self.get(name)
+        if v.nhwc and v.t.dtype == self.dtype and v.t.stride(3) == 1 and v.ld % 8 == 0 \
+                and v.t.data_ptr() % 16 == 0:
+            return v
+        n, c, h, w = v.logical_shape
+        dst = self.new_nhwc(n, h, w, c)
+        src = v
+
+        def conv():
+            dst.t.copy_(src.logical().permute(0, 2, 3, 1))
+        self.plan.add_py(conv, f"to_nhwc({name})")
+        conv()
+        self.vals[name] = dst
+        return dst
+
+    def as_torch(self, name: str, fp32: bool = True) -> torch.Tensor:
+        """Logical-layout view for fallback ops (no copy; 16-bit floats are upcast lazily by the op)."""
+        if name in self.g.initializers:
+            return self.const_f32(name)
+        return self.get(name).logical()
+
+    def get(self, name: str) -> Val:
+        if name in self.vals:
+            return self.vals[name]
+        if name in self.g.initializers:
+            v = Val(self.const_f32(name), False)
+            self.vals[name] = v
+            return v
+        raise KeyError(f"value {name!r} not produced yet")
+
+    def is4d(self, name: str) -> bool:
+        return len(self.info.shapes.get(name, [])) == 4
+
+    # ------------------------------------------------------------------ driver
+    def build(self) -> Plan:
+        g = self.g
+        # graph inputs
+        for vi in g.inputs:
+            shape = self.input_shapes[vi.name]
+            tdt = interp.NP2TORCH[vi.dtype]
+            if len(shape) == 4 and tdt.is_floating_point:
+                n, c, h, w = shape
+                v = self.new_nhwc(n, h, w, c)
+            else:
+                if tdt.is_floating_point:
+                    tdt = torch.float32
+                v = Val(torch.zeros(shape, dtype=tdt, device=self.device), False)
+            self.vals[vi.name] = v
+            self.plan.inputs[vi.name] = v
+        self._plan_concats()
+        for node in g.nodes:
+            fn = getattr(self, "lower_" + node.op, None)
+            done = False
+            if fn is not None:
+                done = fn(node) is not False
+            if not done:
+                self.lower_fallback(node)
+        for vi in g.outputs:
+            self.plan.outputs[vi.name] = self.get(vi.name)
+        self.plan.finalize()
+        torch.cuda.synchronize(self.device)
+        self.plan.status.check("plan build")
+        return self.plan
+
+    def _plan_concats(self) -> None:
+        """Pre-assigns channel slices of concat outputs to their producers (concat fusion)."""
+        nhwc_producers = {"FusedConv", "MaxPool", "AveragePool", "Resize", "Mul", "Add", "Concat"}
+        for node in self.g.nodes:
+            if node.op != "Concat" or not self.is4d(node.outputs[0]):
+                continue
+            axis = node.attr("axis", 1)
+            if axis not in (1, -3):
+                continue
+            n, c, h, w = self.info.shapes[node.outputs[0]]
+            if node.outputs[0] in self.preassigned:
+                dst = self.preassigned[node.outputs[0]]
+            else:
+                dst = self.new_nhwc(n, h, w, c)
+                self.preassigned[node.outputs[0]] = dst
+            off = 0
+            for i in node.inputs:
+                ci = self.info.shapes[i][1]
+                p = self.prod.get(i)
+                aligned = off % 8 == 0
+                if (p is not None and p.op in nhwc_producers and i not in self.preassigned and aligned
+                        and i not in self.g.output_names()):
+                    self.preassigned[i] = Val(dst.t[..., off:off + ci], True)
+                off += ci
+
+    # ------------------------------------------------------------------ fallback
+    def lower_fallback(self, node: Node) -> None:
+        fn = interp._OPS.get(node.op)
+        if fn is None:
+            raise NotImplementedError(f"native backend: unsupported op {node.op}")
+        args_names = list(node.inputs)
+        ins = [None if nm == "" else self.as_torch(nm) for nm in args_names]
+        while ins and ins[-1] is None:
+            ins.pop()
+        value_pos = {}
+        from ..ir.shape_infer import VALUE_ARGS
+        for k in VALUE_ARGS.get(node.op, ()):
+            if k < len(node.inputs) and node.inputs[k] in self.info.values:
+                value_pos[k] = torch.from_numpy(np.ascontiguousarray(self.info.values[node.inputs[k]]))
+        node.attrs.setdefault("_opset", self.g.opset)
+
+        def compute():
+            a = []
+            for k, t in enumerate(ins):
+                if k in value_pos:
+                    a.append(value_pos[k])
+                elif t is not None and t.dtype in (torch.float16, torch.bfloat16):
+                    a.append(t.float())
+                else:
+                    a.append(t)
+            r = fn(node, *a)
+            return r if isinstance(r, tuple) else (r,)
+        with torch.no_grad():
+            first = compute()
+        outs = [torch.empty_like(r, memory_format=torch.contiguous_format).copy_(r) for r in first]
+
+        def step():
+            with torch.no_grad():
+                for o, r in zip(outs, compute()):
+                    o.copy_(r)
+        self.plan.add_py(step, f"torch:{node.op}", node)
+        for name, o in zip(node.outputs, outs):
+            if name:
+                self.vals[name] = Val(o, False)
+                if name in self.preassigned:       # a concat slice was promised: copy into it
+                    self._copy_into_slice(name)
+
+    def _copy_into_slice(self, name: str) -> None:
+        dst = self.preassigned[name]
+        src = self.vals[name]
+
+        def cp():
+            dst.t.copy_(src.logical().permute(0, 2, 3, 1))
+        self.plan.add_py(cp, f"to_slice({name})")
+        cp()
+        self.vals[name] = dst
+
+    # ------------------------------------------------------------------ conv
+    def lower_FusedConv(self, node: Node):
+        x_name, w_name = node.inputs[0], node.inputs[1]
+        w = self.g.initializers[w_name]
+        if w.ndim != 4 or node.attr("group", 1) != 1 or any(d != 1 for d in node.attr("dilations", [1, 1])):
+            return False
+        if not self.is4d(x_name):
+            return False
+        strides = node.attr("strides", [1, 1])
+        if strides[0] != strides[1]:
+            return False
+        cout, cin, kh, kw = w.shape
+        x = self.as_nhwc(x_name)
+        n, cx, h, wd = x.logical_shape
+        n_o, c_o, ho, wo = self.info.shapes[node.outputs[0]]
+        pads = interp._pads_2d(node, x.logical(), [kh, kw], strides, node.attr("dilations", [1, 1]))
+        pad_t, pad_l = pads[0], pads[1]
+        cin_phys = _round8(cin)
+        key = (w_name, f"conv{cin_phys}")
+        if key not in self.packed:
+            wt = torch.from_numpy(np.ascontiguousarray(w)).float()
+            if cin_phys != cin:
+                wt = torch.nn.functional.pad(wt, (0, 0, 0, 0, 0, cin_phys - cin))
+            self.packed[key] = pack_conv_weight(wt.to(self.device), self.dtype)
+        wp = self.packed[key]
+        bias = None
+        if len(node.inputs) > 2 and node.inputs[2]:
+            bias = self.const_f32(node.inputs[2]).float().contiguous()
+        # an ESE gate ([N,C,1,1] multiplied into a feature map) is produced in fp32
+        out_name = node.outputs[0]
+        gate = ho == 1 and wo == 1 and all(c.op == "Mul" for c in self.cons.get(out_name, [])) \
+            and len(self.cons.get(out_name, [])) > 0 and out_name not in self.preassigned
+        y = self.out_nhwc(out_name, torch.float32 if gate else None)
+        res = None
+        if len(node.inputs) > 3 and node.inputs[3]:
+            res = self.as_nhwc(node.inputs[3])
+        op = ConvGemm(x.t, wp, y.t, in_shape=(n, h, wd, cin_phys), out_hw=(ho, wo), cout=cout, kernel=(kh, kw),
+                      stride=strides[0], pad=(pad_t, pad_l), bias=bias,
+                      residual=res.t if res is not None else None, res_mode=node.attr("res_mode", 0),
+                      act=node.attr("activation", "none"), act_alpha=node.attr("act_alpha", 0.0),
+                      act_beta=node.attr("act_beta", 0.0), x_ld=x.ld, y_ld=y.ld,
+                      res_ld=res.ld if res is not None else None, status=self.plan.status,
+                      x_n_stride=x.n_stride, y_n_stride=y.n_stride,
+                      res_n_stride=res.n_stride if res is not None else 0, name=f"conv:{node.name}")
+        self.plan.add_native(op, node)
+        op.launch()
+        self.vals[out_name] = y
+
+    lower_Conv = lower_FusedConv
+
+    # ------------------------------------------------------------------ gemm
+    def lower_FusedGemm(self, node: Node):
+        x_name, w_name = node.inputs[0], node.inputs[1]
+        w = self.g.initializers[w_name]
+        nout, kdim = w.shape
+        xv = self.get(x_name)
+        shp = xv.logical_shape
+        if shp[-1] != kdim or kdim % 8 != 0:
+            return False
+        rows = int(np.prod(shp[:-1]))
+        x2 = self.rows_view(x_name, rows, kdim)
+        key = (w_name, "lin")
+        if key not in self.packed:
+            self.packed[key] = pack_linear_weight(torch.from_numpy(np.ascontiguousarray(w)).float().to(self.device),
+                                                  self.dtype)
+        bias = self.const_f32(node.inputs[2]).float().contiguous() if len(node.inputs) > 2 and node.inputs[2] else None
+        out_shape = self.info.shapes[node.outputs[0]]
+        is_output = node.outputs[0] in self.g.output_names()
+        y = torch.zeros(rows, _round8(nout), dtype=torch.float32 if is_output else self.dtype, device=self.device)
+        res = None
+        if len(node.inputs) > 3 and node.inputs[3]:
+            res = self.rows_view(node.inputs[3], rows, nout)
+        op = ConvGemm(x2, self.packed[key], y, in_shape=(1, 1, rows, kdim), out_hw=(1, rows), cout=nout, bias=bias,
+                      residual=res, res_mode=node.attr("res_mode", 0), act=node.attr("activation", "none"),
+                      act_alpha=node.attr("act_alpha", 0.0), act_beta=node.attr("act_beta", 0.0),
+                      x_ld=x2.stride(0), y_ld=y.stride(0), res_ld=res.stride(0) if res is not None else None,
+                      status=self.plan.status, name=f"gemm:{node.name}")
+        self.plan.add_native(op, node)
+        op.launch()
+        self.vals[node.outputs[0]] = Val(y[:, :nout].unflatten(0, out_shape[:-1]), False)
+
+    def rows_view(self, name: str, rows: int, cols: int) -> torch.Tensor:
+        """``[rows, cols]`` 16-bit view with unit inner stride and 8-aligned row stride."""
+        v = self.get(name)
+        t = v.t
+        if v.nhwc:
+            n, h, w, c = t.shape
+            if h == 1 and w == 1 and c == cols and t.dtype == self.dtype:
+                return t.reshape(n, c) if t.is_contiguous() else t[:, 0, 0, :]
+            t = v.logical()
+        if t.dtype == self.dtype and t.stride(-1) == 1:
+            try:
+                t2 = t.view(rows, cols)
+                if t2.stride(0) % 8 == 0 and t2.data_ptr() % 16 == 0:
+                    return t2
+            except RuntimeError:
+                pass
+        dst = torch.zeros(rows, cols, dtype=self.dtype, device=self.device)
+        src = t
+
+        def cp():
+            dst.copy_(src.reshape(rows, cols))
+        self.plan.add_py(cp, f"to_rows({name})")
+        cp()
+        return dst
+
+    # ------------------------------------------------------------------ pooling / resize / elementwise
+    def _lower_pool(self, node: Node, mode: str):
+        x_name = node.inputs[0]
+        if not self.is4d(x_name):
+            return False
+        k = node.attr("kernel_shape")
+        if len(k) != 2 or node.attr("ceil_mode", 0):
+            return False
+        x = self.as_nhwc(x_name)
+        n, c, h, w = x.logical_shape
+        strides = node.attr("strides", [1, 1])
+        pads = interp._pads_2d(node, x.logical(), k, strides)
+        _, _, ho, wo = self.info.shapes[node.outputs[0]]
+        y = self.out_nhwc(node.outputs[0])
+        op = K.pool2d(x.t, y.t, n=n, h=h, w=w, c=_round8(c) if x.ld >= _round8(c) and y.ld >= _round8(c) else c,
+                      kernel=(k[0], k[1]), stride=(strides[0], strides[1]), pad=(pads[0], pads[1]), out_hw=(ho, wo),
+                      mode=mode, x_ld=x.ld, y_ld=y.ld, x_n_stride=x.n_stride, y_n_stride=y.n_stride,
+                      count_include_pad=bool(node.attr("count_include_pad", 0)))
+        self.plan.add_native(op, node)
+        op.launch()
+        self.vals[node.outputs[0]] = y
+
+    def lower_MaxPool(self, node: Node):
+        if len(node.outputs) > 1 and node.outputs[1]:
+            return False
+        return self._lower_pool(node, "max")
+
+    def lower_AveragePool(self, node: Node):
+        return self._lower_pool(node, "avg")
+
+    def lower_GlobalAveragePool(self, node: Node):
+        x_name = node.inputs[0]
+        if not self.is4d(x_name):
+            return False
+        x = self.as_nhwc(x_name)
+        n, c, h, w = x.logical_shape
+        cp = _round8(c) if x.ld >= _round8(c) else c
+        y = self.out_nhwc(node.outputs[0])
+        splits = K.gap_splits(h * w, n, cp)
+        scratch = torch.empty(n * splits * cp, dtype=torch.float32, device=self.device)
+        for op in K.global_avgpool(x.t, y.t, scratch, n=n, hw=h * w, c=cp, x_ld=x.ld, x_n_stride=x.n_stride,
+                                   splits=splits, out_ld=y.t.stride(0)):
+            self.plan.add_native(op, node)
+            op.launch()
+        self.vals[node.outputs[0]] = y
+
+    def lower_Resize(self, node: Node):
+        x_name = node.inputs[0]
+        if not self.is4d(x_name) or node.attr("mode", "nearest") != "nearest":
+            return False
+        n, c, h, w = self.info.shapes[x_name]
+        _, _, ho, wo = self.info.shapes[node.outputs[0]]
+        if ho % h or wo % w:
+            return False
+        ctm = node.attr("coordinate_transformation_mode", "half_pixel")
+        if not (ctm == "asymmetric" or (ho // h in (1, 2) and wo // w in (1, 2))):
+            return False
+        x = self.as_nhwc(x_name)
+        y = self.out_nhwc(node.outputs[0])
+        cc = _round8(c) if x.ld >= _round8(c) and y.ld >= _round8(c) else c
+        op = K.upsample_nearest(x.t, y.t, n=n, h=h, w=w, c=cc, factor=(ho // h, wo // w), x_ld=x.ld, y_ld=y.ld,
+                                x_n_stride=x.n_stride, y_n_stride=y.n_stride)
+        self.plan.add_native(op, node)
+        op.launch()
+        self.vals[node.outputs[0]] = y
+
+    def lower_Concat(self, node: Node):
+        out = node.outputs[0]
+        if out not in self.preassigned or not self.is4d(out):
+            return False
+        dst = self.preassigned[out]
+        off = 0
+        for i in node.inputs:
+            ci = self.info.shapes[i][1]
+            v = self.get(i)
+            sl = dst.t[..., off:off + ci]
+            same = v.nhwc and v.t.data_ptr() == sl.data_ptr() and v.t.stride() == sl.stride()
+            if not same:
+                src = v
+
+                def cp(src=src, sl=sl):
+                    sl.copy_(src.logical().permute(0, 2, 3, 1))
+                self.plan.add_py(cp, f"concat_copy({i})", node)
+                cp()
+            off += ci
+        self.vals[out] = dst
+
+    def _lower_binary(self, node: Node, opname: str):
+        a_name, b_name = node.inputs
+        if not (self.is4d(a_name) and self.is4d(b_name)):
+            return False
+        if a_name in self.g.initializers or b_name in self.g.initializers:
+            return False
+        sa, sb = self.info.shapes[a_name], self.info.shapes[b_name]
+        if sa != sb:
+            # feature map times per-image channel gate [N,C,1,1]
+            if opname == "mul" and sb[2:] == [1, 1] and sa[:2] == sb[:2]:
+                return self._lower_scale(node, a_name, b_name)
+            if opname == "mul" and sa[2:] == [1, 1] and sa[:2] == sb[:2]:
+                return self._lower_scale(node, b_name, a_name)
+            return False
+        a, b = self.as_nhwc(a_name), self.as_nhwc(b_name)
+        n, c, h, w = a.logical_shape
+        if a.n_stride != h * w * a.ld or b.n_stride != h * w * b.ld:
+            return False
+        y = self.out_nhwc(node.outputs[0])
+        if y.n_stride != h * w * y.ld:
+            return False
+        op = K.binary(a.t, b.t, y.t, rows=n * h * w, c=_round8(c) if min(a.ld, b.ld, y.ld) >= _round8(c) else c,
+                      op=opname, a_ld=a.ld, b_ld=b.ld, y_ld=y.ld)
+        self.plan.add_native(op, node)
+        op.launch()
+        self.vals[node.outputs[0]] = y
+
+    def _lower_scale(self, node: Node, x_name: str, s_name: str):
+        x = self.as_nhwc(x_name)
+        s = self.get(s_name)
+        n, c, h, w = x.logical_shape
+        if not (s.nhwc and s.t.dtype == torch.float32 and s.t.stride(0) == _round8(c) and _round8(c) == c):
+            sv = torch.zeros(n, c, dtype=torch.float32, device=self.device)
+            src = s
+
+            def cp():
+                sv.copy_(src.logical().reshape(n, c))
+            self.plan.add_py(cp, f"gate_to_f32({s_name})", node)
+            cp()
+            s_t = sv
+        else:
+            s_t = s.t
+        y = self.out_nhwc(node.outputs[0])
+        op = K.scale_channels(x.t, s_t, y.t, n=n, hw=h * w, c=c, x_ld=x.ld, y_ld=y.ld, x_n_stride=x.n_stride,
+                              y_n_stride=y.n_stride) if c % 8 == 0 else None
+        if op is None:
+            return False
+        self.plan.add_native(op, node)
+        op.launch()
+        self.vals[node.outputs[0]] = y
+
+    def lower_Add(self, node: Node):
+        return self._lower_binary(node, "add")
+
+    def lower_Mul(self, node: Node):
+        return self._lower_binary(node, "mul")
+
+    def lower_Sub(self, node: Node):
+        return self._lower_binary(node, "sub")
+
+    def _lower_unary(self, node: Node, act: str, alpha: float = 0.0, beta: float = 0.0):
+        x_name = node.inputs[0]
+        if not self.is4d(x_name):
+            return False
+        x = self.as_nhwc(x_name)
+        n, c, h, w = x.logical_shape
+        y = self.out_nhwc(node.outputs[0])
+        if x.n_stride != h * w * x.ld or y.n_stride != h * w * y.ld:
+            return False
+        op = K.unary(x.t, y.t, rows=n * h * w, c=_round8(c) if min(x.ld, y.ld) >= _round8(c) else c, act=act,
+                     x_ld=x.ld, y_ld=y.ld, alpha=alpha, beta=beta)
+        self.plan.add_native(op, node)
+        op.launch()
+        self.vals[node.outputs[0]] = y
+
+    def lower_Relu(self, node): return self._lower_unary(node, "relu")
+    def lower_Silu(self, node): return self._lower_unary(node, "silu")
+    def lower_Sigmoid(self, node): return self._lower_unary(node, "sigmoid")
+    def lower_HardSwish(self, node): return self._lower_unary(node, "hard_swish")
+    def lower_Tanh(self, node): return self._lower_unary(node, "tanh")
+
+    def lower_HardSigmoid(self, node):
+        return self._lower_unary(node, "hard_sigmoid", node.attr("alpha", 0.2), node.attr("beta", 0.5))
+
+    def lower_LeakyRelu(self, node):
+        return self._lower_unary(node, "leaky_relu", node.attr("alpha", 0.01))
+
+    def lower_Flatten(self, node: Node):
+        v = self.get(node.inputs[0])
+        if v.nhwc and v.t.shape[1] == 1 and v.t.shape[2] == 1 and node.attr("axis", 1) == 1:
+            self.vals[node.outputs[0]] = Val(v.t[:, 0, 0, :], False)
+            return True
+        return False
+
+    # ------------------------------------------------------------------ detection post-processing
+    def lower_MultiClassNMS(self, node: Node):
+        if node.attr("nms_eta", 1.0) < 1.0 or not (0 <= node.attr("nms_top_k", 1000) <= MulticlassNMS.MAX_TOP_K):
+            return False
+        boxes = self.as_torch(node.inputs[0])
+        scores = self.as_torch(node.inputs[1])
+        n, m, _ = boxes.shape
+        bx = torch.zeros(n, m, 4, dtype=torch.float32, device=self.device)
+        src = boxes
+
+        def cp():
+            bx.copy_(src)
+        self.plan.add_py(cp, "nms_boxes_f32", node)
+        cp()
+        if not scores.is_contiguous():
+            sc = torch.zeros(scores.shape, dtype=scores.dtype, device=self.device)
+            ssrc = scores
+
+            def cp2():
+                sc.copy_(ssrc)
+            self.plan.add_py(cp2, "nms_scores", node)
+            cp2()
+            scores = sc
+        self._emit_nms(node, bx, scores, class_major=True)
+
+    def _emit_nms(self, node: Node, boxes: torch.Tensor, scores: torch.Tensor, class_major: bool) -> None:
+        nms = MulticlassNMS(boxes, scores, class_major=class_major,
+                            score_threshold=node.attr("score_threshold", 0.01),
+                            nms_threshold=node.attr("nms_threshold", 0.5), nms_top_k=node.attr("nms_top_k", 1000),
+                            keep_top_k=node.attr("keep_top_k", 100), normalized=bool(node.attr("normalized", 1)),
+                            background_label=node.attr("background_label", -1))
+        self.plan.add_native(nms.op, node, launches=2)
+        nms.launch()
+        self.plan.extra.setdefault("nms", []).append(nms)
+        n = boxes.shape[0]
+        cap = nms.out.shape[1]
+        # padded outputs; the runtime compacts them with the per-image counts after the D2H copy
+        self.vals[node.outputs[0]] = Val(nms.out.view(n * cap, 6), False)
+        if len(node.outputs) > 1 and node.outputs[1]:
+            self.vals[node.outputs[1]] = Val(nms.out_index.view(n * cap, 1), False)
+        if len(node.outputs) > 2 and node.outputs[2]:
+            self.vals[node.outputs[2]] = Val(nms.out_num, False)
+        self.plan.extra.setdefault("padded_nms_outputs", {})[node.outputs[0]] = (node.outputs[2] if len(node.outputs) > 2 else None, cap)
+        if len(node.outputs) > 1 and node.outputs[1]:
+            self.plan.extra["padded_nms_outputs"][node.outputs[1]] = (node.outputs[2] if len(node.outputs) > 2 else None, cap)
+
+    def plan_PPYOLOEPost(self, node: Node) -> None:
+        """Allocates the anchor-major score / regression buffers and hands their per-level row
+        ranges to the producing convolutions."""
+        nl = node.attr("num_levels")
+        gh, gw = node.attr("grid_h"), node.attr("grid_w")
+        a_total = sum(h * w for h, w in zip(gh, gw))
+        n, c = self.info.shapes[node.inputs[0]][:2]
+        rc = self.info.shapes[node.inputs[nl]][1]
+        scores = torch.zeros(n, a_total, _round8(c), dtype=torch.float32, device=self.device)
+        regs = torch.zeros(n, a_total, _round8(rc), dtype=self.dtype, device=self.device)
+        off = 0
+        for i in range(nl):
+            h, w = gh[i], gw[i]
+            for name, buf, ch in ((node.inputs[i], scores, c), (node.inputs[nl + i], regs, rc)):
+                p = self.prod.get(name)
+                if p is not None and p.op in ("FusedConv", "Conv") and len(self.cons.get(name, [])) == 1 \
+                        and name not in self.preassigned:
+                    view = buf[:, off:off + h * w, :ch].unflatten(1, (h, w))
+                    self.preassigned[name] = Val(view, True)
+            off += h * w
+        self.plan.extra[("ppyoloe_post", node.name)] = (scores, regs)
+
+    def lower_PPYOLOEPost(self, node: Node):
+        nl = node.attr("num_levels")
+        gh, gw = node.attr("grid_h"), node.attr("grid_w")
+        scores, regs = self.plan.extra[("ppyoloe_post", node.name)]
+        n, a_total = scores.shape[:2]
+        c = self.info.shapes[node.inputs[0]][1]
+        rc = self.info.shapes[node.inputs[nl]][1]
+        off = 0
+        levels = []
+        for i in range(nl):
+            h, w = gh[i], gw[i]
+            for name, buf, ch in ((node.inputs[i], scores, c), (node.inputs[nl + i], regs, rc)):
+                v = self.get(name)
+                view = buf[:, off:off + h * w, :ch].unflatten(1, (h, w))
+                if not (v.nhwc and v.t.data_ptr() == view.data_ptr()):
+                    src = v
+
+                    def cp(src=src, view=view):
+                        view.copy_(src.logical().permute(0, 2, 3, 1))
+                    self.plan.add_py(cp, "ppyoloe_gather", node)
+                    cp()
+            levels.append((off, w, node.attr("strides")[i]))
+            off += h * w
+        sf = self.get(node.inputs[2 * nl]).t
+        boxes = torch.zeros(n, a_total, 4, dtype=torch.float32, device=self.device)
+        op = K.dfl_decode(regs, boxes, sf, n=n, anchors=a_total, bins=node.attr("bins"), levels=levels,
+                          offset=node.attr("offset", 0.5), reg_ld=regs.shape[2])
+        self.plan.add_native(op, node)
+        op.launch()
+        self._emit_nms(node, boxes, scores[:, :, :c], class_major=False)
+
+
+def build_plan(graph: Graph, input_shapes: Dict[str, Sequence[int]], device, dtype=torch.float16,
+               input_values: Optional[Dict[str, np.ndarray]] = None, opt_level: int = 2) -> Plan:
+    """Optimises ``graph`` for the given shapes and lowers it to a plan on ``device``."""
+    device = torch.device(device)
+    with torch.cuda.device(device):
+        g = passes.optimize(graph, input_shapes, input_values, level=opt_level)
+        low = Lowering(g, input_shapes, device, dtype, input_values)
+        for node in g.nodes:
+            if node.op == "PPYOLOEPost":
+                low.plan_PPYOLOEPost(node)
+        plan = low.build()
+        plan.extra["graph"] = g
+    return plan

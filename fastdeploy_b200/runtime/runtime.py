@@ -1,0 +1,264 @@
+"""``Runtime``: the model-agnostic inference object
+(fastdeploy/runtime/runtime.h:37-127, python/fastdeploy/runtime.py:21-158).
+
+``Init`` = read (optionally decrypt) the model, import it into the IR, and - on GPU -
+lower it to a launch plan for every input-shape bucket it meets; ``Infer`` copies the
+inputs into the plan's static buffers, replays the plan (a CUDA graph when enabled)
+and returns the outputs. ``Clone`` shares the imported graph and, on the same device,
+the device-resident weights, as the reference's backends do
+(fastdeploy/runtime/runtime.cc:396-414).
+"""
+from __future__ import annotations
+
+import os
+import threading
+import time
+from typing import Any, Dict, List, Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from ..core.types import Backend, Device, FDDataType, ModelFormat, TensorInfo
+from ..importer.onnx_format import load_onnx
+from ..importer.paddle_import import load_paddle
+from ..ir.graph import Graph
+from ..ir.interp import Interpreter
+from ..utils import log
+from .option import RuntimeOption
+
+
+def _read(path: str) -> bytes:
+    with open(path, "rb") as f:
+        return f.read()
+
+
+def load_graph(option: RuntimeOption) -> Graph:
+    """Model file(s) or buffers -> IR, honouring ``model_format`` and the encryption key."""
+    fmt = option.model_format
+    if option.model_from_memory:
+        model, params = option.model_buffer, option.params_buffer or b""
+    else:
+        if not option.model_file:
+            raise ValueError("RuntimeOption has no model: call set_model_path or set_model_buffer")
+        model = _read(option.model_file)
+        params = _read(option.params_file) if option.params_file else b""
+    if option.encryption_key:
+        from ..encryption import decrypt
+        model = decrypt(model, option.encryption_key)
+        if params:
+            params = decrypt(params, option.encryption_key)
+    if fmt == ModelFormat.AUTOREC:
+        name = (option.model_file or "").lower()
+        fmt = ModelFormat.ONNX if name.endswith(".onnx") else ModelFormat.PADDLE
+    if fmt == ModelFormat.ONNX:
+        return load_onnx(model)
+    if fmt == ModelFormat.PADDLE:
+        return load_paddle(model, params)
+    raise ValueError(f"model format {fmt.name} is not supported by this runtime (ONNX and PADDLE are)")
+
+
+class Runtime:
+    def __init__(self, runtime_option: Optional[RuntimeOption] = None, _graph: Optional[Graph] = None):
+        self.option = runtime_option or RuntimeOption()
+        self.option.native_option.apply_env()
+        self.graph: Graph = _graph if _graph is not None else load_graph(self.option)
+        self._lock = threading.Lock()
+        self._plans: Dict[tuple, Any] = {}
+        self._interp: Optional[Interpreter] = None
+        self._bound_inputs: Dict[str, Any] = {}
+        self._bound_outputs: Dict[str, torch.Tensor] = {}
+        self._last_outputs: Dict[str, Any] = {}
+        self._profile_time = 0.0
+        self.gpu_launches = 0
+        self.on_gpu = self.option.device == Device.GPU
+        if self.on_gpu:
+            if not torch.cuda.is_available():
+                raise RuntimeError("RuntimeOption.use_gpu() was requested but no CUDA device is available")
+            from .. import _native
+            _native.kernels()           # fail loudly when the kernel library is missing
+            self.device = torch.device("cuda", self.option.device_id)
+            self.dtype = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp8": torch.float16}[
+                self.option.native_option.precision]
+            if self.option.trt_shapes:
+                shapes = {k: v["opt"] for k, v in self.option.trt_shapes.items()}
+                if all(vi.name in shapes for vi in self.graph.inputs):
+                    self._plan_for(shapes)
+        else:
+            self.device = torch.device("cpu")
+            if self.option.cpu_thread_num > 0:
+                torch.set_num_threads(self.option.cpu_thread_num)
+            self._interp = Interpreter(self.graph)
+
+    # ------------------------------------------------------------------ introspection
+    def num_inputs(self) -> int:
+        return len(self.graph.inputs)
+
+    def num_outputs(self) -> int:
+        return len(self.graph.outputs)
+
+    def get_input_info(self, index: int) -> TensorInfo:
+        vi = self.graph.inputs[index]
+        shape = [d if isinstance(d, int) else -1 for d in (vi.shape or [])]
+        return TensorInfo(vi.name, shape, FDDataType.from_numpy(vi.dtype))
+
+    def get_output_info(self, index: int) -> TensorInfo:
+        vi = self.graph.outputs[index]
+        shape = [d if isinstance(d, int) else -1 for d in (vi.shape or [])]
+        return TensorInfo(vi.name, shape, FDDataType.from_numpy(vi.dtype) if vi.dtype in ("float32", "int32", "int64", "float16", "uint8", "int8", "bool", "float64", "int16") else FDDataType.FP32)
+
+    def get_input_infos(self) -> List[TensorInfo]:
+        return [self.get_input_info(i) for i in range(self.num_inputs())]
+
+    def get_output_infos(self) -> List[TensorInfo]:
+        return [self.get_output_info(i) for i in range(self.num_outputs())]
+
+    # ------------------------------------------------------------------ plans
+    def _plan_for(self, shapes: Dict[str, Sequence[int]]):
+        key = tuple((k, tuple(int(d) for d in shapes[k])) for k in sorted(shapes))
+        plan = self._plans.get(key)
+        if plan is None:
+            from .native_backend import build_plan
+            t0 = time.time()
+            plan = build_plan(self.graph, {k: list(v) for k, v in shapes.items()}, self.device, self.dtype,
+                              opt_level=self.option.native_option.opt_level)
+            if self.option.native_option.use_cuda_graph:
+                try:
+                    plan.capture()
+                except Exception as e:   # capture is an optimisation; eager replay stays correct
+                    log.warning(f"CUDA graph capture failed ({e}); running the plan eagerly")
+                    plan.graph = None
+            if len(self._plans) >= self.option.native_option.max_plans:
+                self._plans.pop(next(iter(self._plans)))
+            self._plans[key] = plan
+            log.info(f"built plan for {dict(key)} in {time.time() - t0:.2f}s: {len(plan.steps)} steps, "
+                     f"{plan.native_kernel_launches} native kernel launches")
+        return plan
+
+    def plan_for_shapes(self, shapes: Dict[str, Sequence[int]]):
+        """Public access for model classes that write inputs straight into plan buffers."""
+        with torch.cuda.device(self.device):
+            return self._plan_for(shapes)
+
+    # ------------------------------------------------------------------ inference
+    def infer(self, data: Union[Dict[str, Any], Sequence[Any]]) -> List[np.ndarray]:
+        if not isinstance(data, dict):
+            names = [vi.name for vi in self.graph.inputs]
+            data = dict(zip(names, data))
+        outs = self._infer_dict(data)
+        return [self._to_numpy(outs[vi.name]) for vi in self.graph.outputs]
+
+    def forward(self, *inputs) -> List[np.ndarray]:
+        return self.infer(list(inputs))
+
+    @staticmethod
+    def _to_numpy(t) -> np.ndarray:
+        if isinstance(t, np.ndarray):
+            return t
+        if t.dtype in (torch.float16, torch.bfloat16):
+            t = t.float()
+        return t.detach().cpu().numpy()
+
+    def _infer_dict(self, data: Dict[str, Any]) -> Dict[str, Any]:
+        with self._lock:
+            if not self.on_gpu:
+                res = self._interp.run({k: (np.ascontiguousarray(v) if isinstance(v, np.ndarray) else v)
+                                        for k, v in data.items()})
+                return res
+            with torch.cuda.device(self.device):
+                shapes = {vi.name: list(data[vi.name].shape) for vi in self.graph.inputs}
+                plan = self._plan_for(shapes)
+                prof = self.option.profiling
+                ev = None
+                if prof["enable"] and prof["include_h2d_d2h"]:
+                    ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                    ev[0].record()
+                for vi in self.graph.inputs:
+                    self._copy_in(plan.inputs[vi.name], data[vi.name])
+                if prof["enable"] and not prof["include_h2d_d2h"]:
+                    for _ in range(prof["warmup"]):
+                        plan.run()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for _ in range(prof["repeat"]):
+                        plan.run()
+                    e1.record()
+                    torch.cuda.synchronize(self.device)
+                    self._profile_time = e0.elapsed_time(e1) / 1e3 / max(prof["repeat"], 1)
+                else:
+                    plan.run()
+                self.gpu_launches += plan.native_kernel_launches
+                outs = self._collect_outputs(plan)
+                if ev is not None:
+                    ev[1].record()
+                    torch.cuda.synchronize(self.device)
+                    self._profile_time = ev[0].elapsed_time(ev[1]) / 1e3
+                return outs
+
+    def _copy_in(self, dst, src) -> None:
+        if isinstance(src, np.ndarray):
+            src = torch.from_numpy(np.ascontiguousarray(src))
+        if src.device != dst.t.device:
+            src = src.to(dst.t.device, non_blocking=True)
+        if dst.nhwc:
+            dst.t.copy_(src.permute(0, 2, 3, 1))
+        else:
+            dst.t.copy_(src.reshape(dst.t.shape))
+
+    def _collect_outputs(self, plan) -> Dict[str, Any]:
+        padded = plan.extra.get("padded_nms_outputs", {})
+        outs: Dict[str, Any] = {}
+        host: Dict[str, np.ndarray] = {}
+        for vi in self.graph.outputs:
+            v = plan.outputs[vi.name]
+            t = v.logical()
+            if vi.name in padded:
+                host[vi.name] = self._to_numpy(t)
+            else:
+                outs[vi.name] = t
+        if host:
+            torch.cuda.synchronize(self.device)
+            plan.status.check("inference")
+            for name, arr in host.items():
+                num_name, cap = padded[name]
+                counts = self._to_numpy(plan.outputs[num_name].t) if num_name in plan.outputs else \
+                    self._to_numpy(plan.extra["nms"][0].out_num)
+                rows = arr.reshape(len(counts), cap, -1)
+                outs[name] = np.concatenate([rows[i, :counts[i]] for i in range(len(counts))], 0) \
+                    if len(counts) else rows.reshape(0, rows.shape[-1])
+        return outs
+
+    # ------------------------------------------------------------------ zero-copy API
+    def bind_input_tensor(self, name: str, tensor) -> None:
+        self._bound_inputs[name] = tensor
+
+    def bind_output_tensor(self, name: str, tensor) -> None:
+        self._bound_outputs[name] = tensor
+
+    def zero_copy_infer(self) -> None:
+        outs = self._infer_dict(self._bound_inputs)
+        self._last_outputs = outs
+        for name, dst in self._bound_outputs.items():
+            src = outs[name]
+            src = torch.from_numpy(src) if isinstance(src, np.ndarray) else src
+            dst.copy_(src.reshape(dst.shape))
+
+    def get_output_tensor(self, name: str):
+        return self._last_outputs.get(name)
+
+    def compile(self, warm_datas) -> bool:
+        """Pre-builds plans for the given sample inputs (the reference compiles TorchScript
+        through Poros here, fastdeploy/runtime/runtime.cc:430-449)."""
+        for sample in warm_datas:
+            self.infer(sample)
+        return True
+
+    def get_profile_time(self) -> float:
+        return self._profile_time
+
+    def clone(self, stream=None, device_id: int = -1) -> "Runtime":
+        opt = self.option.clone()
+        if device_id >= 0:
+            opt.device_id = device_id
+        if stream is not None:
+            opt.external_stream = stream
+        return Runtime(opt, _graph=self.graph)
