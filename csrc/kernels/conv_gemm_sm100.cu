@@ -215,9 +215,9 @@ constexpr int kTplGeneric = -1;
 // One group of 8 consecutive output channels of one output pixel.
 template <int ACT>
 __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParams& p, int co,
-                                          uint8_t* yrow, const uint8_t* rrow, bool in_bf16,
-                                          int out_es) {
-  const int nvalid = min(8, p.Cout - co);
+                                          int col_limit, uint8_t* yrow, const uint8_t* rrow,
+                                          bool in_bf16, int out_es) {
+  const int nvalid = min(8, col_limit - co);
   if (nvalid <= 0) return;
   float x[8];
 #pragma unroll
@@ -292,14 +292,20 @@ __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParam
   store8_general(yrow + static_cast<size_t>(co) * out_es, p.out_dtype, p.y_vec != 0, nvalid, x);
 }
 
+constexpr int kMaxSmem = 232448;  // 227 KB opt-in limit per CTA
+constexpr int kBarBytes = 256;
+
+constexpr int next_pow2_cols(int c) { return c <= 32 ? 32 : c <= 64 ? 64 : c <= 128 ? 128 : c <= 256 ? 256 : 512; }
+
 template <int BN>
 struct KernelCfg {
+  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N must be a multiple of 16 up to 256");
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
-  static constexpr int kTmemCols = BN * 2 < 32 ? 32 : BN * 2;
-  static constexpr int kBarBytes = 256;
+  static constexpr int kStagesFit = (kMaxSmem - kBarBytes - 1024) / kStageBytes;
+  static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
+  static constexpr int kTmemCols = next_pow2_cols(2 * BN);
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;  // +1024: alignment slack
 };
 
@@ -434,7 +440,7 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // Two warps share each TMEM lane quarter and split the tile's columns.
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
-    constexpr int kChunks = BN / 32;
+    constexpr int kChunks = (BN + 31) / 32;
     constexpr int kChunksHalf0 = (kChunks + 1) / 2;
     const int c_begin = half == 0 ? 0 : kChunksHalf0;
     const int c_end = half == 0 ? kChunksHalf0 : kChunks;
@@ -461,28 +467,29 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                             (static_cast<size_t>(img) * p.res_n_stride + pix * p.res_ld) * 2;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
       const int colbase = n_tile * BN;
+      const int col_limit = min(p.Cout, colbase + BN);
       uint32_t va[32], vb[32];
       int c = c_begin;
-      bool have = c < c_end && colbase + c * 32 < p.Cout;
+      bool have = c < c_end && colbase + c * 32 < col_limit;
       if (have) tmem_ld_32x32(t_row + c * 32, va);
       while (have) {
         tmem_ld_wait_dep(va);
-        bool next = (c + 1 < c_end) && (colbase + (c + 1) * 32 < p.Cout);
+        bool next = (c + 1 < c_end) && (colbase + (c + 1) * 32 < col_limit);
         if (next) tmem_ld_32x32(t_row + (c + 1) * 32, vb);
         if (valid) {
 #pragma unroll
           for (int g = 0; g < 4; ++g)
-            epilogue8<ACT>(va + g * 8, p, colbase + c * 32 + g * 8, yrow, rrow, in_bf16, out_es);
+            epilogue8<ACT>(va + g * 8, p, colbase + c * 32 + g * 8, col_limit, yrow, rrow, in_bf16, out_es);
         }
         if (!next) break;
         ++c;
         tmem_ld_wait_dep(vb);
-        next = (c + 1 < c_end) && (colbase + (c + 1) * 32 < p.Cout);
+        next = (c + 1 < c_end) && (colbase + (c + 1) * 32 < col_limit);
         if (next) tmem_ld_32x32(t_row + (c + 1) * 32, va);
         if (valid) {
 #pragma unroll
           for (int g = 0; g < 4; ++g)
-            epilogue8<ACT>(vb + g * 8, p, colbase + c * 32 + g * 8, yrow, rrow, in_bf16, out_es);
+            epilogue8<ACT>(vb + g * 8, p, colbase + c * 32 + g * 8, col_limit, yrow, rrow, in_bf16, out_es);
         }
         ++c;
         have = next;
@@ -545,8 +552,13 @@ static int launch_bn(ConvGemmOp* op, cudaStream_t stream) {
 int ConvGemmOp::launch(cudaStream_t stream) {
   switch (block_n) {
     case 32: return launch_bn<32>(this, stream);
+    case 48: return launch_bn<48>(this, stream);
     case 64: return launch_bn<64>(this, stream);
+    case 80: return launch_bn<80>(this, stream);
+    case 96: return launch_bn<96>(this, stream);
     case 128: return launch_bn<128>(this, stream);
+    case 160: return launch_bn<160>(this, stream);
+    case 192: return launch_bn<192>(this, stream);
     case 256: return launch_bn<256>(this, stream);
   }
   set_error("conv_gemm: bad block_n");
@@ -574,27 +586,27 @@ static void choose_tile(int Ho, int Wo, int stride, int* tw_out, int* th_out) {
   *th_out = bth;
 }
 
+static const int kBlockNs[9] = {256, 192, 160, 128, 96, 80, 64, 48, 32};
+
+static bool valid_block_n(int bn) {
+  for (int i = 0; i < 9; ++i)
+    if (kBlockNs[i] == bn) return true;
+  return false;
+}
+
+// Smallest padded width wins (fewest wasted MMA columns); among equals the widest tile,
+// because the activation tile is fetched once per column tile.
 static int choose_block_n(int Cout, long m_tiles, int sms) {
-  const int cands[4] = {256, 128, 64, 32};
-  int pick = 32;
-  for (int i = 0; i < 4; ++i) {
-    const int bn = cands[i];
-    const int nt = (Cout + bn - 1) / bn;
-    const double waste = static_cast<double>(nt) * bn / Cout;
-    if (waste > 1.2 && bn > 32) continue;
-    pick = bn;
-    // keep every SM busy when a smaller tile would
-    if (m_tiles * nt >= sms || bn == 32) break;
-    // otherwise try the next smaller candidate, but remember this one
-    bool smaller_helps = false;
-    for (int j = i + 1; j < 4; ++j) {
-      const int nt2 = (Cout + cands[j] - 1) / cands[j];
-      if (static_cast<double>(nt2) * cands[j] / Cout <= 1.2 && m_tiles * nt2 > m_tiles * nt) {
-        smaller_helps = true;
-        break;
-      }
+  (void)m_tiles; (void)sms;
+  int pick = 256;
+  long best = -1;
+  for (int i = 0; i < 9; ++i) {
+    const int bn = kBlockNs[i];
+    const long padded = static_cast<long>((Cout + bn - 1) / bn) * bn;
+    if (best < 0 || padded < best) {
+      best = padded;
+      pick = bn;
     }
-    if (!smaller_helps) break;
   }
   return pick;
 }
@@ -626,7 +638,7 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   const long m_tiles = static_cast<long>(p.tiles_w) * p.tiles_h * d->N;
   const int sms = sm_count();
   int bn = d->block_n > 0 ? d->block_n : choose_block_n(d->Cout, m_tiles, sms);
-  if (bn != 32 && bn != 64 && bn != 128 && bn != 256) { set_error("conv_gemm: block_n"); delete op; return nullptr; }
+  if (!valid_block_n(bn)) { set_error("conv_gemm: block_n must be one of 32,48,64,80,96,128,160,192,256"); delete op; return nullptr; }
   op->block_n = bn;
   p.n_tiles = (d->Cout + bn - 1) / bn;
   const long total = m_tiles * p.n_tiles;

@@ -44,7 +44,7 @@ def test_linear(m, k, n, dtype):
     _check(y, ref)
 
 
-@pytest.mark.parametrize("block_n", [32, 64, 128, 256])
+@pytest.mark.parametrize("block_n", [32, 48, 64, 80, 96, 128, 160, 192, 256])
 def test_linear_block_n(block_n):
     from fastdeploy_b200.ops.conv_gemm import linear
     torch.manual_seed(1)
