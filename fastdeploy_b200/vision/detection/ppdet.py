@@ -1,0 +1,390 @@
+"""PaddleDetection model family: ``PaddleDetPreprocessor``, ``PaddleDetPostprocessor``,
+``PPDetBase`` and its subclasses (PPYOLOE, PicoDet, YOLOv3, ...), following
+fastdeploy/vision/detection/ppdet/{preprocessor,postprocessor,base}.cc and model.h:24-492.
+
+On a GPU runtime the whole chain stays on the device: raw uint8 frames are copied once
+(async, from pinned memory when the caller provides it), one fused kernel does
+BGR->RGB + resize + normalise + layout + cast straight into the plan's input buffer, the
+plan runs the network, DFL decode and multiclass NMS, and only ``keep_top_k x 6`` floats
+per image come back. The CPU path restates the reference's OpenCV pipeline with cv2 /
+numpy and doubles as the oracle in the tests.
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+import yaml
+
+from ...core.types import ModelFormat
+from ...ops.nms import multiclass_nms_reference
+from ...runtime.model import FastDeployModel
+from ...runtime.option import RuntimeOption
+from ...utils import log
+from ..result import DetectionResult
+
+
+class NMSOption:
+    """Defaults of fastdeploy/vision/detection/ppdet/multiclass_nms.h:32-41."""
+
+    def __init__(self):
+        self.background_label = -1
+        self.keep_top_k = 100
+        self.nms_eta = 1.0
+        self.nms_threshold = 0.5
+        self.nms_top_k = 1000
+        self.normalized = True
+        self.score_threshold = 0.3
+
+
+class PaddleDetPreprocessor:
+    def __init__(self, config_file: str):
+        self.config_file = config_file
+        self.disable_normalize_ = False
+        self.disable_permute_ = False
+        self.use_cuda_ = False
+        self.gpu_id = -1
+        self._build()
+
+    # ------------------------------------------------------------------ config
+    def _build(self) -> None:
+        with open(self.config_file) as f:
+            cfg = yaml.safe_load(f)
+        if "arch" not in cfg:
+            raise ValueError("Please set model arch, support value : SOLOv2, YOLO, SSD, RetinaNet, RCNN, Face.")
+        self.arch = cfg["arch"]
+        self.ops: List[Dict[str, Any]] = []
+        self.has_permute = False
+        for op in cfg.get("Preprocess", []):
+            t = op["type"]
+            if t == "NormalizeImage":
+                if self.disable_normalize_:
+                    continue
+                mean, std = list(op["mean"]), list(op["std"])
+                if op.get("norm_type", "mean_std") != "mean_std":
+                    mean, std = [0.0] * 3, [1.0] * 3
+                self.ops.append({"type": "Normalize", "mean": mean, "std": std, "is_scale": op.get("is_scale", True)})
+            elif t == "Resize":
+                ts = op["target_size"]
+                assert len(ts) == 2, f"Require size of target_size be 2, but now it's {len(ts)}."
+                self.ops.append({"type": "Resize", "keep_ratio": bool(op["keep_ratio"]), "target_size": list(ts),
+                                 "interp": int(op["interp"])})
+            elif t == "Permute":
+                self.has_permute = True
+            elif t == "Pad":
+                self.ops.append({"type": "PadToSize", "size": list(op["size"]), "value": list(op["fill_value"])})
+            elif t == "PadStride":
+                self.ops.append({"type": "StridePad", "stride": int(op["stride"])})
+            else:
+                raise ValueError(f"Unexcepted preprocess operator: {t}.")
+        self.label_list = cfg.get("label_list", [])
+
+    def disable_normalize(self):
+        self.disable_normalize_ = True
+        self._build()
+
+    def disable_permute(self):
+        self.disable_permute_ = True
+
+    def use_cuda(self, enable_cv_cuda: bool = False, gpu_id: int = -1):
+        self.use_cuda_ = True
+        self.gpu_id = gpu_id
+
+    # ------------------------------------------------------------------ geometry shared by both paths
+    def plan_image(self, h: int, w: int) -> Dict[str, Any]:
+        """Resolves the op list for one source size: resized size, canvas size, scale factor."""
+        rh, rw = h, w
+        interp = 1
+        resized = False
+        pad_to = None
+        stride = 0
+        for op in self.ops:
+            if op["type"] == "Resize":
+                interp = op["interp"]
+                if not op["keep_ratio"]:
+                    rh, rw = op["target_size"][0], op["target_size"][1]
+                else:
+                    tmin, tmax = min(op["target_size"]), max(op["target_size"])
+                    scale = tmin / min(rh, rw)
+                    if tmax > 0 and round(scale * max(rh, rw)) > tmax:
+                        scale = tmax / max(rh, rw)
+                    rh, rw = int(round(rh * scale)), int(round(rw * scale))
+                resized = True
+            elif op["type"] == "PadToSize":
+                pad_to = (op["size"][0], op["size"][1], op["value"])
+            elif op["type"] == "StridePad":
+                stride = op["stride"]
+        ch, cw = rh, rw
+        if pad_to is not None:
+            ch, cw = max(ch, pad_to[0]), max(cw, pad_to[1])
+        if stride > 0:
+            ch, cw = math.ceil(ch / stride) * stride, math.ceil(cw / stride) * stride
+        sf = (rh / h, rw / w) if resized else (1.0, 1.0)
+        return {"rh": rh, "rw": rw, "ch": ch, "cw": cw, "interp": interp, "scale_factor": sf,
+                "pad_value": pad_to[2] if pad_to is not None else [0.0, 0.0, 0.0]}
+
+    def norm_coeffs(self) -> Tuple[List[float], List[float]]:
+        from ...ops.preproc import normalize_coeffs
+        for op in self.ops:
+            if op["type"] == "Normalize":
+                return normalize_coeffs(op["mean"], op["std"], op["is_scale"])
+        return [1.0] * 3, [0.0] * 3
+
+    # ------------------------------------------------------------------ CPU path
+    def run(self, images: Sequence[np.ndarray]) -> List[np.ndarray]:
+        """Returns ``[image NCHW fp32, scale_factor [N,2], im_shape [N,2]]``."""
+        import cv2
+        if len(images) == 0:
+            raise ValueError("The size of input images should be greater than 0.")
+        alpha, beta = self.norm_coeffs()
+        alpha, beta = np.asarray(alpha, np.float32), np.asarray(beta, np.float32)
+        plans = [self.plan_image(im.shape[0], im.shape[1]) for im in images]
+        max_h = max(p["ch"] for p in plans)
+        max_w = max(p["cw"] for p in plans)
+        n = len(images)
+        out = np.zeros((n, max_h, max_w, 3), np.float32)
+        sf = np.zeros((n, 2), np.float32)
+        im_shape = np.zeros((n, 2), np.float32)
+        for i, (im, p) in enumerate(zip(images, plans)):
+            x = im[..., ::-1]                                    # BGR2RGB
+            if (p["rh"], p["rw"]) != im.shape[:2]:
+                x = cv2.resize(np.ascontiguousarray(x), (p["rw"], p["rh"]), interpolation=p["interp"])
+            x = x.astype(np.float32) * alpha + beta
+            out[i, :p["rh"], :p["rw"]] = x
+            if p["ch"] > p["rh"] or p["cw"] > p["rw"]:
+                pv = np.asarray(p["pad_value"], np.float32)
+                out[i, p["rh"]:p["ch"], :p["cw"]] = pv
+                out[i, :p["rh"], p["rw"]:p["cw"]] = pv
+            sf[i] = p["scale_factor"]
+            im_shape[i] = (max_h, max_w)
+        if self.has_permute and not self.disable_permute_:
+            out = np.ascontiguousarray(out.transpose(0, 3, 1, 2))
+        return [out, sf, im_shape]
+
+
+class PaddleDetPostprocessor:
+    def __init__(self, arch: str = "YOLO"):
+        self.arch = arch
+        self.with_nms_ = True
+        self.nms_option = NMSOption()
+        self.decode_and_nms = None
+
+    def apply_nms(self):
+        """The exported model has no NMS: run it here (reference: ApplyNMS / ProcessWithoutNMS)."""
+        self.with_nms_ = False
+
+    ApplyNMS = apply_nms
+
+    def set_nms_option(self, option: NMSOption):
+        self.nms_option = option
+
+    def set_nms_rotated_option(self, option):
+        self.nms_rotated_option = option
+
+    def run(self, tensors: Sequence[np.ndarray]) -> List[DetectionResult]:
+        if self.with_nms_:
+            return self._with_nms(np.asarray(tensors[0]), np.asarray(tensors[1]))
+        return self._without_nms(np.asarray(tensors[0]), np.asarray(tensors[1]))
+
+    @staticmethod
+    def _rows_to_results(rows: np.ndarray, counts: np.ndarray) -> List[DetectionResult]:
+        results = []
+        pos = 0
+        for c in counts:
+            r = rows[pos:pos + int(c)]
+            pos += int(c)
+            res = DetectionResult()
+            if len(r):
+                res.label_ids = r[:, 0].astype(np.int32).tolist()
+                res.scores = r[:, 1].astype(np.float32).tolist()
+                res.boxes = r[:, 2:6].astype(np.float32).tolist()
+            results.append(res)
+        return results
+
+    def _with_nms(self, out: np.ndarray, num: np.ndarray) -> List[DetectionResult]:
+        return self._rows_to_results(out.reshape(-1, out.shape[-1]), num.reshape(-1))
+
+    def _without_nms(self, boxes: np.ndarray, scores: np.ndarray) -> List[DetectionResult]:
+        o = self.nms_option
+        out, _, num = multiclass_nms_reference(boxes, scores, o.score_threshold, o.nms_threshold, o.nms_top_k,
+                                               o.keep_top_k, o.normalized, o.background_label, o.nms_eta)
+        return self._rows_to_results(out, num)
+
+
+class _GpuSlot:
+    """Staging buffers of one in-flight batch."""
+
+    def __init__(self, device, raw_bytes: int, n: int, out_rows: int):
+        from ...ops.preproc import IMAGE_META
+        self.raw = torch.empty(raw_bytes, dtype=torch.uint8, device=device)
+        self.meta_host = torch.empty(n * IMAGE_META.itemsize, dtype=torch.uint8).pin_memory()
+        self.meta_dev = torch.empty(n * IMAGE_META.itemsize, dtype=torch.uint8, device=device)
+        self.sf_host = torch.empty(n, 2, dtype=torch.float32).pin_memory()
+        self.out_host = torch.empty(n, out_rows, 6, dtype=torch.float32).pin_memory()
+        self.num_host = torch.empty(n, dtype=torch.int32).pin_memory()
+        self.copied = torch.cuda.Event()
+        self.done = torch.cuda.Event()
+        self.pre = None
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+
+class PendingDetection:
+    """Handle of a batch submitted with :meth:`PPDetBase.predict_async`."""
+
+    def __init__(self, slot: _GpuSlot, n: int, status):
+        self.slot, self.n, self.status = slot, n, status
+
+    def result(self) -> List[DetectionResult]:
+        self.slot.done.synchronize()
+        self.status.check("detection")
+        num = self.slot.num_host[:self.n].numpy()
+        out = self.slot.out_host[:self.n].numpy()
+        rows = np.concatenate([out[i, :num[i]] for i in range(self.n)], 0) if self.n else np.zeros((0, 6), np.float32)
+        return PaddleDetPostprocessor._rows_to_results(rows, num)
+
+
+class PPDetBase(FastDeployModel):
+    def __init__(self, model_file: str, params_file: str, config_file: str,
+                 runtime_option: Optional[RuntimeOption] = None, model_format: ModelFormat = ModelFormat.PADDLE):
+        super().__init__(runtime_option)
+        self.runtime_option.set_model_path(model_file, params_file, model_format)
+        self.preprocessor = PaddleDetPreprocessor(config_file)
+        self.postprocessor = PaddleDetPostprocessor(self.preprocessor.arch)
+        self.init_runtime()
+        out_names = [vi.name for vi in self.runtime.graph.outputs]
+        self._nms_in_graph = any(n.op in ("MultiClassNMS", "PPYOLOEPost") for n in self.runtime.graph.nodes)
+        if not self._nms_in_graph:
+            self.postprocessor.apply_nms()
+        self._slots: Dict[Tuple, List[_GpuSlot]] = {}
+        self._slot_rr = 0
+        self._copy_stream = None
+        self.h2d_bytes_last = 0
+        self.d2h_bytes_last = 0
+
+    def get_preprocessor(self):
+        return self.preprocessor
+
+    def get_postprocessor(self):
+        return self.postprocessor
+
+    # ------------------------------------------------------------------ public API
+    def predict(self, im: np.ndarray) -> DetectionResult:
+        return self.batch_predict([im])[0]
+
+    def batch_predict(self, images: Sequence[Any]) -> List[DetectionResult]:
+        if self.runtime.on_gpu and self._nms_in_graph:
+            return self.predict_async(images).result()
+        tensors = self.preprocessor.run([np.asarray(im) for im in images])
+        feeds = self._name_inputs(tensors)
+        outs = self.infer(feeds)
+        names = [vi.name for vi in self.runtime.graph.outputs]
+        arrs = [self.runtime._to_numpy(outs[n]) for n in names]
+        return self.postprocessor.run(arrs)
+
+    def _name_inputs(self, tensors: List[np.ndarray]) -> Dict[str, np.ndarray]:
+        pool = {"image": tensors[0], "scale_factor": tensors[1], "im_shape": tensors[2]}
+        return {vi.name: pool[vi.name] for vi in self.runtime.graph.inputs}
+
+    # ------------------------------------------------------------------ device pipeline
+    def predict_async(self, images: Sequence[Any]) -> PendingDetection:
+        """Enqueues copy + pre-processing + network + NMS for one batch and returns at once.
+        Up to two batches are in flight: the next batch's host->device copy overlaps the
+        current batch's compute."""
+        from ...ops import preproc as P
+        rt = self.runtime
+        dev = rt.device
+        n = len(images)
+        geo = [self.preprocessor.plan_image(int(im.shape[0]), int(im.shape[1])) for im in images]
+        ch, cw = max(g["ch"] for g in geo), max(g["cw"] for g in geo)
+        shapes = {}
+        for vi in rt.graph.inputs:
+            shapes[vi.name] = [n, 3, ch, cw] if vi.name == "image" else [n, 2]
+        with torch.cuda.device(dev):
+            plan = rt.plan_for_shapes(shapes)
+            sizes = [int(im.shape[0]) * int(im.shape[1]) * 3 for im in images]
+            raw_bytes = sum((s + 255) // 256 * 256 for s in sizes)
+            nms = plan.extra["nms"][0]
+            key = (tuple(sorted((k, tuple(v)) for k, v in shapes.items())), raw_bytes)
+            if key not in self._slots:
+                self._slots[key] = [_GpuSlot(dev, raw_bytes, n, nms.out.shape[1]) for _ in range(2)]
+            if self._copy_stream is None:
+                self._copy_stream = torch.cuda.Stream(dev)
+            self._slot_rr ^= 1
+            slot = self._slots[key][self._slot_rr]
+            slot.done.synchronize()                 # the slot's previous batch has been read back
+            compute = torch.cuda.current_stream(dev)
+            # ---- host->device copies on the copy stream
+            meta = np.frombuffer(slot.meta_host.numpy(), dtype=P.IMAGE_META)
+            off = 0
+            h2d = 0
+            with torch.cuda.stream(self._copy_stream):
+                for i, (im, g) in enumerate(zip(images, geo)):
+                    t = im if isinstance(im, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(im))
+                    flat = t.reshape(-1)
+                    slot.raw[off:off + flat.numel()].copy_(flat, non_blocking=True)
+                    if flat.device.type == "cpu":
+                        h2d += flat.numel()
+                    P.fill_meta(meta, i, src_offset=off, src_hw=(int(im.shape[0]), int(im.shape[1])),
+                                src_stride=int(im.shape[1]) * 3, resized_hw=(g["rh"], g["rw"]))
+                    slot.sf_host[i, 0], slot.sf_host[i, 1] = g["scale_factor"]
+                    off += (flat.numel() + 255) // 256 * 256
+                slot.meta_dev.copy_(slot.meta_host, non_blocking=True)
+                h2d += slot.meta_host.numel()
+                slot.copied.record(self._copy_stream)
+            # ---- compute stream: pre-process, network, NMS, read-back
+            compute.wait_event(slot.copied)
+            if "scale_factor" in plan.inputs:
+                # the plan's input buffer is shared by both slots: write it in compute-stream order
+                plan.inputs["scale_factor"].t.copy_(slot.sf_host[:n], non_blocking=True)
+                h2d += n * 8
+            if slot.pre is None:
+                alpha, beta = self.preprocessor.norm_coeffs()
+                img_val = plan.inputs["image"]
+                base = img_val.t
+                c_phys = base.stride(2)
+                dst = torch.as_strided(base, (n, ch, cw, c_phys), base.stride())
+                slot.pre = P.Preprocess(slot.raw, slot.meta_dev, dst, n=n, out_hw=(ch, cw), layout="nhwc",
+                                        c_out=c_phys, interp=geo[0]["interp"], swap_rb=True, alpha=alpha, beta=beta,
+                                        pad_value=[0.0, 0.0, 0.0])
+            slot.pre.launch()
+            plan.run()
+            slot.out_host[:n].copy_(nms.out, non_blocking=True)
+            slot.num_host[:n].copy_(nms.out_num, non_blocking=True)
+            slot.done.record(compute)
+            rt.gpu_launches += plan.native_kernel_launches + 1
+            self.h2d_bytes_last = h2d
+            self.d2h_bytes_last = n * nms.out.shape[1] * 6 * 4 + n * 4
+        return PendingDetection(slot, n, plan.status)
+
+
+def _subclass(name: str, doc: str):
+    return type(name, (PPDetBase,), {"__doc__": doc})
+
+
+PPYOLOE = _subclass("PPYOLOE", "PP-YOLOE / PP-YOLOE+ (fastdeploy/vision/detection/ppdet/model.h:52-74).")
+PicoDet = _subclass("PicoDet", "PicoDet (model.h:24-50).")
+PPYOLO = _subclass("PPYOLO", "PP-YOLO / PP-YOLOv2 (model.h:76-98).")
+YOLOv3 = _subclass("YOLOv3", "YOLOv3 (model.h:100-122).")
+PaddleYOLOX = _subclass("PaddleYOLOX", "YOLOX exported by PaddleDetection (model.h:124-146).")
+FasterRCNN = _subclass("FasterRCNN", "Faster R-CNN (model.h:148-167).")
+MaskRCNN = _subclass("MaskRCNN", "Mask R-CNN (model.h:169-188).")
+SSD = _subclass("SSD", "SSD (model.h:190-210).")
+PaddleYOLOv5 = _subclass("PaddleYOLOv5", "YOLOv5 exported by PaddleDetection (model.h:212-230).")
+PaddleYOLOv6 = _subclass("PaddleYOLOv6", "YOLOv6 exported by PaddleDetection (model.h:232-250).")
+PaddleYOLOv7 = _subclass("PaddleYOLOv7", "YOLOv7 exported by PaddleDetection (model.h:252-270).")
+PaddleYOLOv8 = _subclass("PaddleYOLOv8", "YOLOv8 exported by PaddleDetection (model.h:272-292).")
+RTMDet = _subclass("RTMDet", "RTMDet (model.h:294-312).")
+CascadeRCNN = _subclass("CascadeRCNN", "Cascade R-CNN (model.h:314-332).")
+PSSDet = _subclass("PSSDet", "PSS-Det (model.h:334-352).")
+RetinaNet = _subclass("RetinaNet", "RetinaNet (model.h:354-372).")
+PPYOLOESOD = _subclass("PPYOLOESOD", "PP-YOLOE-SOD (model.h:374-392).")
+FCOS = _subclass("FCOS", "FCOS (model.h:394-412).")
+TTFNet = _subclass("TTFNet", "TTFNet (model.h:414-432).")
+TOOD = _subclass("TOOD", "TOOD (model.h:434-452).")
+GFL = _subclass("GFL", "GFL (model.h:454-472).")
+SOLOv2 = _subclass("SOLOv2", "SOLOv2 (model.h:24-50 family).")
+PaddleDetectionModel = _subclass("PaddleDetectionModel", "Any PaddleDetection export (model.h:474-492).")
+PPYOLOER = _subclass("PPYOLOER", "PP-YOLOE-R rotated detector.")
