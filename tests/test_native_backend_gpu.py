@@ -47,7 +47,7 @@ def test_ppyoloe_tiny_matches_interpreter(with_nms):
     from fastdeploy_b200.ir.interp import Interpreter
     from fastdeploy_b200.models.ppyoloe import build_ppyoloe
     from fastdeploy_b200.runtime.native_backend import build_plan
-    net = build_ppyoloe("tiny", image=128, num_classes=8, with_nms=with_nms, score_threshold=0.02)
+    net = build_ppyoloe("tiny", image=128, num_classes=8, with_nms=with_nms, score_threshold=0.005)
     m, p = net.serialize()
     g = load_paddle(m, p)
     rng = np.random.RandomState(1)

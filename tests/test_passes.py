@@ -1,0 +1,118 @@
+"""Graph passes keep the numerics: pass-on == pass-off through the reference interpreter (CPU)."""
+import numpy as np
+import pytest
+
+
+def _run(g, feeds):
+    from fastdeploy_b200.ir.interp import Interpreter
+    return {k: v.float().numpy() for k, v in Interpreter(g).run(feeds).items()}
+
+
+def test_resnet_fusion_equivalence():
+    from fastdeploy_b200.ir.passes import optimize
+    from fastdeploy_b200.models.resnet import build_resnet
+    g = build_resnet((1, 1, 1, 1), num_classes=10, width=16, image=64)
+    x = np.random.RandomState(0).rand(2, 3, 64, 64).astype(np.float32)
+    ref = _run(g, {"input": x})["output"]
+    g2 = optimize(g, {"input": [2, 3, 64, 64]}, level=2)
+    hist = g2.op_histogram()
+    assert "BatchNormalization" not in hist and "Relu" not in hist and "Add" not in hist
+    assert hist["FusedConv"] == 17 and hist["FusedGemm"] == 1
+    out = _run(g2, {"input": x})["output"]
+    assert np.abs(out - ref).max() < 1e-5
+    # residual add before the activation for the ResNet pattern
+    assert any(n.attr("res_mode") == 1 for n in g2.nodes if n.op == "FusedConv")
+
+
+@pytest.mark.parametrize("level", [1, 2])
+def test_ppyoloe_tiny_equivalence(level):
+    from fastdeploy_b200.importer.paddle_import import load_paddle
+    from fastdeploy_b200.ir.passes import optimize
+    from fastdeploy_b200.models.ppyoloe import build_ppyoloe
+    net = build_ppyoloe("tiny", image=96, num_classes=6, score_threshold=0.005)
+    g = load_paddle(*net.serialize())
+    x = np.random.RandomState(1).rand(2, 3, 96, 96).astype(np.float32)
+    sf = np.array([[1.0, 1.0], [0.5, 0.75]], np.float32)
+    ref = _run(g, {"image": x, "scale_factor": sf})
+    g2 = optimize(g, {"image": [2, 3, 96, 96], "scale_factor": [2, 2]}, level=level)
+    out = _run(g2, {"image": x, "scale_factor": sf})
+    if level == 2:
+        assert g2.op_histogram().get("PPYOLOEPost") == 1
+        assert "Softmax" not in g2.op_histogram() and "Silu" not in g2.op_histogram()
+    for k in ref:
+        assert out[k].shape == ref[k].shape and ref[k].size > 0
+        assert np.abs(out[k] - ref[k]).max() < 5e-4
+
+
+def test_repvgg_and_silu_patterns():
+    from fastdeploy_b200.ir.graph import Graph
+    from fastdeploy_b200.ir.passes import optimize
+    rng = np.random.RandomState(3)
+    g = Graph()
+    g.add_input("x", "float32", [1, 8, 10, 10])
+    w3 = g.add_initializer("w3", rng.randn(8, 8, 3, 3).astype(np.float32) * 0.1)
+    w1 = g.add_initializer("w1", rng.randn(8, 8, 1, 1).astype(np.float32) * 0.1)
+    b3 = g.add_initializer("b3", rng.randn(8).astype(np.float32))
+    a = g.op("Conv", "x", w3, b3, pads=[1, 1, 1, 1], strides=[1, 1], kernel_shape=[3, 3])
+    b = g.op("Conv", "x", w1, pads=[0, 0, 0, 0], strides=[1, 1], kernel_shape=[1, 1])
+    s = g.op("Add", a, b)
+    y = g.op("Mul", s, g.op("Sigmoid", s))
+    g.nodes[-1].outputs = ["y"]
+    g.add_output("y")
+    x = rng.randn(1, 8, 10, 10).astype(np.float32)
+    ref = _run(g, {"x": x})["y"]
+    g2 = optimize(g, {"x": [1, 8, 10, 10]}, level=2)
+    assert [n.op for n in g2.nodes] == ["FusedConv"] and g2.nodes[0].attr("activation") == "silu"
+    assert np.abs(_run(g2, {"x": x})["y"] - ref).max() < 1e-5
+
+
+def test_gelu_layernorm_attention_recognition():
+    import math
+    from fastdeploy_b200.ir.graph import Graph
+    from fastdeploy_b200.ir.passes import optimize
+    rng = np.random.RandomState(4)
+    B, S, H, D = 2, 6, 2, 4
+    g = Graph(opset=13)
+    g.add_input("x", "float32", [B, S, H * D])
+    g.add_input("mask", "float32", [B, 1, 1, S])
+
+    def lin(inp, name):
+        w = g.add_initializer(name + ".w", rng.randn(H * D, H * D).astype(np.float32) * 0.3)
+        b = g.add_initializer(name + ".b", rng.randn(H * D).astype(np.float32) * 0.1)
+        return g.op("Add", g.op("MatMul", inp, w), b)
+
+    def heads(t):
+        r = g.op("Reshape", t, g.const(np.array([0, 0, H, D], np.int64)))
+        return g.op("Transpose", r, perm=[0, 2, 1, 3])
+    q, k, v = lin("x", "q"), lin("x", "k"), lin("x", "v")
+    att = g.op("MatMul", heads(q), g.op("Transpose", heads(k), perm=[0, 1, 3, 2]))
+    att = g.op("Mul", att, g.const(np.float32(1 / math.sqrt(D))))
+    att = g.op("Softmax", g.op("Add", att, "mask"), axis=-1)
+    ctx = g.op("Transpose", g.op("MatMul", att, heads(v)), perm=[0, 2, 1, 3])
+    ctx = g.op("Reshape", ctx, g.const(np.array([0, 0, H * D], np.int64)))
+    h = g.op("Add", lin(ctx, "o"), "x")
+    # decomposed LayerNorm
+    mean = g.op("ReduceMean", h, axes=[-1], keepdims=1)
+    d = g.op("Sub", h, mean)
+    var = g.op("ReduceMean", g.op("Pow", d, g.const(np.float32(2.0))), axes=[-1], keepdims=1)
+    nrm = g.op("Div", d, g.op("Sqrt", g.op("Add", var, g.const(np.float32(1e-5)))))
+    gamma = g.add_initializer("gamma", rng.rand(H * D).astype(np.float32) + 0.5)
+    beta = g.add_initializer("beta", rng.randn(H * D).astype(np.float32))
+    ln = g.op("Add", g.op("Mul", nrm, gamma), beta)
+    # erf GELU
+    f = lin(ln, "ffn")
+    e = g.op("Erf", g.op("Div", f, g.const(np.float32(math.sqrt(2)))))
+    ge = g.op("Mul", g.op("Mul", f, g.op("Add", e, g.const(np.float32(1.0)))), g.const(np.float32(0.5)))
+    g.nodes[-1].outputs = ["y"]
+    g.add_output("y")
+    x = rng.randn(B, S, H * D).astype(np.float32)
+    mask = np.zeros((B, 1, 1, S), np.float32)
+    mask[1, ..., 4:] = -1e4
+    ref = _run(g, {"x": x, "mask": mask})["y"]
+    g2 = optimize(g, {"x": [B, S, H * D], "mask": [B, 1, 1, S]}, level=2)
+    hist = g2.op_histogram()
+    assert hist.get("Attention") == 1 and hist.get("LayerNormalization") == 1, hist
+    assert "Erf" not in hist and "Softmax" not in hist and "Transpose" not in hist
+    gem = [n for n in g2.nodes if n.op == "FusedGemm"]
+    assert len(gem) == 5 and any(n.attr("activation") == "gelu" for n in gem) and any(n.attr("res_mode") == 2 for n in gem)
+    assert np.abs(_run(g2, {"x": x, "mask": mask})["y"] - ref).max() < 1e-5
