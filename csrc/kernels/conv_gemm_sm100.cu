@@ -55,6 +55,14 @@ struct ConvGemmDesc {
   long long x_n_stride;  // elements between images (0 = H*W*x_ld)
   long long y_n_stride;  // elements between images (0 = Ho*Wo*y_ld)
   long long res_n_stride;
+  int halo_mode;         // 3x3 stride-1 halo kernel: -1 choose, 0 never, 1 force
+  // Batched "weights" (attention products): one [Cout][K] matrix per (image row h, image n),
+  // row stride w_ld, matrix strides w_h_stride / w_n_stride (elements). Needs tile_h = 1.
+  int w_batched;
+  int w_ld;
+  long long w_h_stride, w_n_stride;
+  // elements between image rows (0 = W * ld): lets heads of a [B, S, H*D] tensor act as image rows
+  long long x_h_stride, y_h_stride, res_h_stride;
 };
 
 struct ConvGemmParams {
@@ -72,6 +80,8 @@ struct ConvGemmParams {
   uint32_t idesc;
   int y_vec, res_vec;
   long long y_n_stride, res_n_stride;
+  long long y_h_stride, res_h_stride;
+  int b_batched;
 };
 
 // Generic activation (runtime code); the hot ones have dedicated template paths.
@@ -292,6 +302,80 @@ __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParam
   store8_general(yrow + static_cast<size_t>(co) * out_es, p.out_dtype, p.y_vec != 0, nvalid, x);
 }
 
+// Epilogue role shared by the convolution kernels: drains the double-buffered TMEM
+// accumulators tile by tile. `tfull0` / `tempty0` are the shared-memory addresses of
+// tmem_full[0] and tmem_empty[0]; index 1 of each follows 8 bytes later.
+template <int BN, int ACT>
+__device__ __forceinline__ void epilogue_loop(const ConvGemmParams& p, uint32_t tmem_base, uint32_t tfull0,
+                                              uint32_t tempty0, volatile int* abort_flag, int warp, int lane) {
+  auto tfull_bar = [&](int a) { return tfull0 + 8u * a; };
+  auto tempty_bar = [&](int a) { return tempty0 + 8u * a; };
+  // Two warps share each TMEM lane quarter and split the tile's columns.
+  const int q = warp & 3;
+  const int half = (warp - 2) >> 2;
+  constexpr int kChunks = (BN + 31) / 32;
+  constexpr int kChunksHalf0 = (kChunks + 1) / 2;
+  const int c_begin = half == 0 ? 0 : kChunksHalf0;
+  const int c_end = half == 0 ? kChunksHalf0 : kChunks;
+  const bool in_bf16 = p.in_bf16 != 0;
+  const int out_es = p.out_dtype == kF32 ? 4 : 2;
+  int acc = 0;
+  uint32_t acc_ph = 0;
+  for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+    const int n_tile = tile % p.n_tiles;
+    int m_tile = tile / p.n_tiles;
+    const int twi = m_tile % p.tiles_w; m_tile /= p.tiles_w;
+    const int thi = m_tile % p.tiles_h;
+    const int img = m_tile / p.tiles_h;
+    if (!mbar_wait(tfull_bar(acc), acc_ph, abort_flag, kStatusTimeoutEpilogue)) break;
+    tc_fence_after();
+    const int row = q * 32 + lane;
+    const int rh = row / p.tw, rw = row - rh * p.tw;
+    const int oh = thi * p.th + rh, ow = twi * p.tw + rw;
+    const bool valid = rh < p.th && oh < p.Ho && ow < p.Wo;
+    uint8_t* yrow = reinterpret_cast<uint8_t*>(p.y) +
+                    (static_cast<size_t>(img) * p.y_n_stride + static_cast<size_t>(oh) * p.y_h_stride +
+                     static_cast<size_t>(ow) * p.y_ld) * out_es;
+    const uint8_t* rrow = reinterpret_cast<const uint8_t*>(p.residual) +
+                          (static_cast<size_t>(img) * p.res_n_stride + static_cast<size_t>(oh) * p.res_h_stride +
+                           static_cast<size_t>(ow) * p.res_ld) * 2;
+    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+    const int colbase = n_tile * BN;
+    const int col_limit = min(p.Cout, colbase + BN);
+    uint32_t va[32], vb[32];
+    int c = c_begin;
+    bool have = c < c_end && colbase + c * 32 < col_limit;
+    if (have) tmem_ld_32x32(t_row + c * 32, va);
+    while (have) {
+      tmem_ld_wait_dep(va);
+      bool next = (c + 1 < c_end) && (colbase + (c + 1) * 32 < col_limit);
+      if (next) tmem_ld_32x32(t_row + (c + 1) * 32, vb);
+      if (valid) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          epilogue8<ACT>(va + g * 8, p, colbase + c * 32 + g * 8, col_limit, yrow, rrow, in_bf16, out_es);
+      }
+      if (!next) break;
+      ++c;
+      tmem_ld_wait_dep(vb);
+      next = (c + 1 < c_end) && (colbase + (c + 1) * 32 < col_limit);
+      if (next) tmem_ld_32x32(t_row + (c + 1) * 32, va);
+      if (valid) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          epilogue8<ACT>(vb + g * 8, p, colbase + c * 32 + g * 8, col_limit, yrow, rrow, in_bf16, out_es);
+      }
+      ++c;
+      have = next;
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(tempty_bar(acc));
+    acc ^= 1;
+    if (acc == 0) acc_ph ^= 1;
+  }
+}
+
 constexpr int kMaxSmem = 232448;  // 227 KB opt-in limit per CTA
 constexpr int kBarBytes = 256;
 
@@ -383,7 +467,10 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
               const uint32_t a_dst = tile0 + s * Cfg::kStageBytes;
               tma_load_4d(a_dst, &tmA, full_bar(s), kb * kBK, x0 + kw, y0 + kh, img);
-              tma_load_2d(a_dst + Cfg::kABytes, &tmB, full_bar(s), kcol, n_tile * BN);
+              if (p.b_batched)
+                tma_load_4d(a_dst + Cfg::kABytes, &tmB, full_bar(s), kcol, n_tile * BN, thi * p.th, img);
+              else
+                tma_load_2d(a_dst + Cfg::kABytes, &tmB, full_bar(s), kcol, n_tile * BN);
               if (++s == S) { s = 0; ph ^= 1; }
             }
           }
@@ -436,70 +523,7 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue
-    // Two warps share each TMEM lane quarter and split the tile's columns.
-    const int q = warp & 3;
-    const int half = (warp - 2) >> 2;
-    constexpr int kChunks = (BN + 31) / 32;
-    constexpr int kChunksHalf0 = (kChunks + 1) / 2;
-    const int c_begin = half == 0 ? 0 : kChunksHalf0;
-    const int c_end = half == 0 ? kChunksHalf0 : kChunks;
-    const bool in_bf16 = p.in_bf16 != 0;
-    const int out_es = p.out_dtype == kF32 ? 4 : 2;
-    int acc = 0;
-    uint32_t acc_ph = 0;
-    for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
-      const int n_tile = tile % p.n_tiles;
-      int m_tile = tile / p.n_tiles;
-      const int twi = m_tile % p.tiles_w; m_tile /= p.tiles_w;
-      const int thi = m_tile % p.tiles_h;
-      const int img = m_tile / p.tiles_h;
-      if (!mbar_wait(tfull_bar(acc), acc_ph, abort_flag, kStatusTimeoutEpilogue)) break;
-      tc_fence_after();
-      const int row = q * 32 + lane;
-      const int rh = row / p.tw, rw = row - rh * p.tw;
-      const int oh = thi * p.th + rh, ow = twi * p.tw + rw;
-      const bool valid = rh < p.th && oh < p.Ho && ow < p.Wo;
-      const size_t pix = static_cast<size_t>(oh) * p.Wo + ow;
-      uint8_t* yrow = reinterpret_cast<uint8_t*>(p.y) +
-                      (static_cast<size_t>(img) * p.y_n_stride + pix * p.y_ld) * out_es;
-      const uint8_t* rrow = reinterpret_cast<const uint8_t*>(p.residual) +
-                            (static_cast<size_t>(img) * p.res_n_stride + pix * p.res_ld) * 2;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      const int colbase = n_tile * BN;
-      const int col_limit = min(p.Cout, colbase + BN);
-      uint32_t va[32], vb[32];
-      int c = c_begin;
-      bool have = c < c_end && colbase + c * 32 < col_limit;
-      if (have) tmem_ld_32x32(t_row + c * 32, va);
-      while (have) {
-        tmem_ld_wait_dep(va);
-        bool next = (c + 1 < c_end) && (colbase + (c + 1) * 32 < col_limit);
-        if (next) tmem_ld_32x32(t_row + (c + 1) * 32, vb);
-        if (valid) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g)
-            epilogue8<ACT>(va + g * 8, p, colbase + c * 32 + g * 8, col_limit, yrow, rrow, in_bf16, out_es);
-        }
-        if (!next) break;
-        ++c;
-        tmem_ld_wait_dep(vb);
-        next = (c + 1 < c_end) && (colbase + (c + 1) * 32 < col_limit);
-        if (next) tmem_ld_32x32(t_row + (c + 1) * 32, va);
-        if (valid) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g)
-            epilogue8<ACT>(vb + g * 8, p, colbase + c * 32 + g * 8, col_limit, yrow, rrow, in_bf16, out_es);
-        }
-        ++c;
-        have = next;
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
-      acc ^= 1;
-      if (acc == 0) acc_ph ^= 1;
-    }
+    epilogue_loop<BN, ACT>(p, tmem_base, tfull_bar(0), tempty_bar(0), abort_flag, warp, lane);
   }
 
   // ------------------------------------------------------------ teardown
@@ -513,6 +537,158 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, *abort_flag);
 }
 
+
+// ------------------------------------------------------------------ 3x3 stride-1 "halo" variant
+// The generic kernel re-fetches the activation tile once per filter tap (9x for a 3x3
+// filter), which makes small-channel layers L2-bound. Here an output tile is 8 pixels wide and
+// 16 high; per 64-channel slab ONE (16+2) x (8+2) halo patch is loaded and all 9 taps read it
+// through shifted shared-memory descriptors: tap (kh, kw) starts (kh*10 + kw) pixel rows into
+// the patch and consecutive 8-row groups are 10 pixel rows (1280 bytes) apart, so the 8 pixels
+// of an output row stay one contiguous swizzled group. Weights stream through their own ring;
+// when the whole filter fits (`b_resident`) it is loaded once per CTA and kept.
+constexpr int kHaloTw = 8, kHaloTh = 16;
+constexpr int kHaloCols = kHaloTw + 2, kHaloRows = kHaloTh + 2;
+constexpr int kHaloABytes = ((kHaloCols * kHaloRows * 128) + 1023) / 1024 * 1024;   // 23552
+constexpr int kHaloMaxB = 18;   // weight stages (barrier slots)
+constexpr int kHaloBarBytes = 512;
+
+struct HaloParams {
+  int a_stages, b_stages, b_resident;
+};
+
+template <int BN, int ACT>
+__global__ void __launch_bounds__(kThreads, 1)
+conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const ConvGemmParams p, const HaloParams hp) {
+  constexpr int kBBytes = BN * kBK * 2;
+  constexpr int kTmemCols = next_pow2_cols(2 * BN);
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const int SA = hp.a_stages, SB = hp.b_stages;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SA * kHaloABytes + SB * kBBytes);
+  // bars: a_full[SA] a_empty[SA] b_full[SB] b_empty[SB] tfull[2] tempty[2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SA + 2 * SB + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t bar0 = smem_u32(bars);
+  auto a_full = [&](int s) { return bar0 + 8u * s; };
+  auto a_empty = [&](int s) { return bar0 + 8u * (SA + s); };
+  auto b_full = [&](int s) { return bar0 + 8u * (2 * SA + s); };
+  auto b_empty = [&](int s) { return bar0 + 8u * (2 * SA + SB + s); };
+  const uint32_t tfull0 = bar0 + 8u * (2 * SA + 2 * SB);
+  const uint32_t tempty0 = tfull0 + 16u;
+  const uint32_t a0 = smem_u32(smem);
+  const uint32_t b0 = a0 + SA * kHaloABytes;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < SA; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), 1); }
+    for (int s = 0; s < SB; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8u * a, 1); mbar_init(tempty0 + 8u * a, kEpiWarps); }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int slabs = p.kb_per_tap;
+  const uint32_t halo_bytes = kHaloCols * kHaloRows * 128;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int sa = 0, sb = 0;
+      uint32_t pa = 0, pb = 0;
+      bool ok = true, first = true;
+      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+        const int n_tile = tile % p.n_tiles;
+        int m_tile = tile / p.n_tiles;
+        const int twi = m_tile % p.tiles_w; m_tile /= p.tiles_w;
+        const int thi = m_tile % p.tiles_h;
+        const int img = m_tile / p.tiles_h;
+        for (int kb = 0; ok && kb < slabs; ++kb) {
+          if (!mbar_wait(a_empty(sa), pa ^ 1, abort_flag, kStatusTimeoutProducer)) { ok = false; break; }
+          mbar_arrive_expect_tx(a_full(sa), halo_bytes);
+          tma_load_4d(a0 + sa * kHaloABytes, &tmA, a_full(sa), kb * kBK, twi * kHaloTw - 1, thi * kHaloTh - 1, img);
+          if (++sa == SA) { sa = 0; pa ^= 1; }
+          if (hp.b_resident && !first) continue;
+          for (int tap = 0; tap < 9; ++tap) {
+            if (!hp.b_resident) {
+              if (!mbar_wait(b_empty(sb), pb ^ 1, abort_flag, kStatusTimeoutProducer)) { ok = false; break; }
+            }
+            mbar_arrive_expect_tx(b_full(sb), kBBytes);
+            tma_load_2d(b0 + sb * kBBytes, &tmB, b_full(sb), (tap * slabs + kb) * kBK, n_tile * BN);
+            if (++sb == SB) { sb = 0; pb ^= 1; }
+          }
+        }
+        first = false;
+      }
+      if (!ok) {
+        for (int i = 0; i < SA; ++i)
+          for (int it = 0; it < (1 << 14); ++it)
+            if (mbar_try_wait(a_full(i), 0) || mbar_try_wait(a_full(i), 1)) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int sa = 0, sb = 0, acc = 0;
+      uint32_t pa = 0, pb = 0, acc_ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+        if (!mbar_wait(tempty0 + 8u * acc, acc_ph ^ 1, abort_flag, kStatusTimeoutMma)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; ok && kb < slabs; ++kb) {
+          if (!mbar_wait(a_full(sa), pa, abort_flag, kStatusTimeoutMma)) { ok = false; break; }
+          const uint32_t a_base = a0 + sa * kHaloABytes;
+          for (int tap = 0; tap < 9; ++tap) {
+            if (hp.b_resident) sb = kb * 9 + tap;
+            if (!mbar_wait(b_full(sb), hp.b_resident ? 0u : pb, abort_flag, kStatusTimeoutMma)) { ok = false; break; }
+            tc_fence_after();
+            const int kh = tap / 3, kw = tap - kh * 3;
+            // shifted view of the halo patch: start (kh*10 + kw) pixel rows in, 8-row groups 10 rows apart
+            uint64_t adesc = make_kmajor_desc(a_base + (kh * kHaloCols + kw) * 128, 128);
+            adesc = (adesc & ~(0x3FFFull << 32)) | (static_cast<uint64_t>((kHaloCols * 128) >> 4) << 32);
+            const uint64_t bdesc = make_kmajor_desc(b0 + sb * kBBytes, 128);
+#pragma unroll
+            for (int kk = 0; kk < kBK / 16; ++kk)
+              umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, p.idesc, (kb | tap | kk) != 0 ? 1u : 0u);
+            if (!hp.b_resident) {
+              umma_commit(b_empty(sb));
+              if (++sb == SB) { sb = 0; pb ^= 1; }
+            }
+          }
+          if (!ok) break;
+          umma_commit(a_empty(sa));
+          if (++sa == SA) { sa = 0; pa ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(tfull0 + 8u * acc);
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1;
+      }
+    }
+  } else {
+    epilogue_loop<BN, ACT>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, *abort_flag);
+}
+
 // ------------------------------------------------------------------ host side
 struct ConvGemmOp : Op {
   alignas(64) CUtensorMap tmA;
@@ -520,6 +696,9 @@ struct ConvGemmOp : Op {
   ConvGemmParams prm;
   int block_n = 0;
   int grid = 0;
+  int halo = 0;          // 1: conv3x3_halo_kernel
+  HaloParams hp{};
+  int halo_smem = 0;
   int launch(cudaStream_t stream) override;
 };
 
@@ -539,8 +718,31 @@ static int launch_inst(ConvGemmOp* op, cudaStream_t stream) {
   return 0;
 }
 
+template <int BN, int ACT>
+static int launch_halo_inst(ConvGemmOp* op, cudaStream_t stream) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  FDB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    FDB_CUDA_OK(cudaFuncSetAttribute(conv3x3_halo_kernel<BN, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kMaxSmem));
+    attr_set[dev] = true;
+  }
+  conv3x3_halo_kernel<BN, ACT><<<op->grid, kThreads, op->halo_smem, stream>>>(op->tmA, op->tmB, op->prm, op->hp);
+  FDB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 template <int BN>
 static int launch_bn(ConvGemmOp* op, cudaStream_t stream) {
+  if (op->halo) {
+    switch (op->prm.act) {
+      case kActNone: return launch_halo_inst<BN, kActNone>(op, stream);
+      case kActRelu: return launch_halo_inst<BN, kActRelu>(op, stream);
+      case kActSilu: return launch_halo_inst<BN, kActSilu>(op, stream);
+      default: return launch_halo_inst<BN, kTplGeneric>(op, stream);
+    }
+  }
   switch (op->prm.act) {
     case kActNone: return launch_inst<BN, kActNone>(op, stream);
     case kActRelu: return launch_inst<BN, kActRelu>(op, stream);
@@ -629,8 +831,29 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   ConvGemmParams& p = op->prm;
   int tw = d->tile_w, th = d->tile_h;
   if (tw <= 0 || th <= 0) choose_tile(d->Ho, d->Wo, d->stride, &tw, &th);
+  if (d->w_batched) {
+    if (d->KH != 1 || d->KW != 1 || d->stride != 1 || d->w_ld % 8 != 0) {
+      set_error("conv_gemm: batched weights need a 1x1 stride-1 product and w_ld % 8 == 0"); delete op; return nullptr;
+    }
+    th = 1;
+    tw = std::min(d->Wo, kBM);
+  }
   if (tw * th > kBM || tw * d->stride > 256 || th * d->stride > 256) {
     set_error("conv_gemm: tile too large"); delete op; return nullptr;
+  }
+  // 3x3 / stride 1 / pad 1: prefer the halo kernel unless its fixed 8x16 tile wastes too many rows
+  const bool halo_ok = !d->w_batched && d->KH == 3 && d->KW == 3 && d->stride == 1 && d->pad_h == 1 && d->pad_w == 1;
+  if (d->halo_mode == 1 && !halo_ok) { set_error("conv_gemm: halo kernel needs 3x3, stride 1, pad 1"); delete op; return nullptr; }
+  if (halo_ok && d->halo_mode != 0) {
+    const double util_gen = static_cast<double>(d->Ho) * d->Wo /
+        (static_cast<double>((d->Wo + tw - 1) / tw) * ((d->Ho + th - 1) / th) * kBM);
+    const double util_halo = static_cast<double>(d->Ho) * d->Wo /
+        (static_cast<double>((d->Wo + kHaloTw - 1) / kHaloTw) * ((d->Ho + kHaloTh - 1) / kHaloTh) * kBM);
+    if (d->halo_mode == 1 || util_halo >= 0.75 * util_gen) {
+      op->halo = 1;
+      tw = kHaloTw;
+      th = kHaloTh;
+    }
   }
   p.tw = tw; p.th = th;
   p.tiles_w = (d->Wo + tw - 1) / tw;
@@ -652,6 +875,9 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   p.out_dtype = d->out_dtype; p.in_bf16 = d->dtype == kBF16;
   p.KH = d->KH; p.KW = d->KW; p.stride = d->stride; p.pad_h = d->pad_h; p.pad_w = d->pad_w;
   p.act = d->act; p.act_alpha = d->act_alpha; p.act_beta = d->act_beta;
+  p.b_batched = d->w_batched ? 1 : 0;
+  p.y_h_stride = d->y_h_stride > 0 ? d->y_h_stride : static_cast<long long>(d->Wo) * d->y_ld;
+  p.res_h_stride = d->res_h_stride > 0 ? d->res_h_stride : static_cast<long long>(d->Wo) * d->res_ld;
   p.y_n_stride = d->y_n_stride > 0 ? d->y_n_stride : static_cast<long long>(d->Ho) * d->Wo * d->y_ld;
   p.res_n_stride = d->res_n_stride > 0 ? d->res_n_stride : static_cast<long long>(d->Ho) * d->Wo * d->res_ld;
   p.a_bytes = static_cast<uint32_t>(tw * th * kBK * 2);
@@ -666,14 +892,45 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   }
   int grid = static_cast<int>(std::min<long>(total, d->max_ctas > 0 ? d->max_ctas : sms));
   op->grid = std::max(grid, 1);
+  if (op->halo) {
+    const int budget = kMaxSmem - 1024 - kHaloBarBytes;
+    const int b_bytes = bn * kBK * 2;
+    const int all_b = 9 * p.kb_per_tap;
+    HaloParams hp{};
+    hp.a_stages = p.kb_per_tap > 1 ? 3 : 2;
+    if (p.n_tiles == 1 && all_b <= kHaloMaxB && hp.a_stages * kHaloABytes + all_b * b_bytes <= budget) {
+      hp.b_resident = 1;
+      hp.b_stages = all_b;
+    } else {
+      hp.b_resident = 0;
+      hp.b_stages = std::min(kHaloMaxB, (budget - hp.a_stages * kHaloABytes) / b_bytes);
+    }
+    if (hp.b_stages < 3) {
+      if (d->halo_mode == 1) { set_error("conv_gemm: halo kernel does not fit shared memory"); delete op; return nullptr; }
+      op->halo = 0;   // fall back to the generic kernel with its own tile choice
+      choose_tile(d->Ho, d->Wo, d->stride, &tw, &th);
+      p.tw = tw; p.th = th;
+      p.tiles_w = (d->Wo + tw - 1) / tw;
+      p.tiles_h = (d->Ho + th - 1) / th;
+      const long mt = static_cast<long>(p.tiles_w) * p.tiles_h * d->N;
+      p.total_tiles = static_cast<int>(mt * p.n_tiles);
+      p.a_bytes = static_cast<uint32_t>(tw * th * kBK * 2);
+      op->grid = std::max(1, static_cast<int>(std::min<long>(p.total_tiles, d->max_ctas > 0 ? d->max_ctas : sms)));
+    } else {
+      op->hp = hp;
+      op->halo_smem = hp.a_stages * kHaloABytes + hp.b_stages * b_bytes + kHaloBarBytes + 1024;
+    }
+  }
 
   const CUtensorMapDataType tdt =
       d->dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   {
     cuuint64_t dims[4] = {(cuuint64_t)d->Cin, (cuuint64_t)d->W, (cuuint64_t)d->H, (cuuint64_t)d->N};
-    cuuint64_t strides[3] = {(cuuint64_t)d->x_ld * 2, (cuuint64_t)d->W * d->x_ld * 2,
+    cuuint64_t strides[3] = {(cuuint64_t)d->x_ld * 2,
+                             (cuuint64_t)(d->x_h_stride > 0 ? d->x_h_stride : (long long)d->W * d->x_ld) * 2,
                              (cuuint64_t)(d->x_n_stride > 0 ? d->x_n_stride : (long long)d->H * d->W * d->x_ld) * 2};
     cuuint32_t box[4] = {(cuuint32_t)kBK, (cuuint32_t)(tw * d->stride), (cuuint32_t)(th * d->stride), 1};
+    if (op->halo) { box[1] = kHaloCols; box[2] = kHaloRows; }
     cuuint32_t estr[4] = {1, (cuuint32_t)d->stride, (cuuint32_t)d->stride, 1};
     CUresult r = enc(&op->tmA, tdt, 4, const_cast<void*>(d->x), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -683,7 +940,19 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
       delete op; return nullptr;
     }
   }
-  {
+  if (d->w_batched) {
+    cuuint64_t dims[4] = {(cuuint64_t)d->Cin, (cuuint64_t)d->Cout, (cuuint64_t)d->H, (cuuint64_t)d->N};
+    cuuint64_t strides[3] = {(cuuint64_t)d->w_ld * 2, (cuuint64_t)d->w_h_stride * 2, (cuuint64_t)d->w_n_stride * 2};
+    cuuint32_t box[4] = {(cuuint32_t)kBK, (cuuint32_t)bn, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(&op->tmB, tdt, 4, const_cast<void*>(d->w), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_error("conv_gemm: encode batched weight tensor map failed, CUresult " + std::to_string((int)r));
+      delete op; return nullptr;
+    }
+  } else {
     const cuuint64_t ktot = (cuuint64_t)d->KH * d->KW * p.kb_per_tap * kBK;
     cuuint64_t dims[2] = {ktot, (cuuint64_t)d->Cout};
     cuuint64_t strides[1] = {ktot * 2};
@@ -705,4 +974,10 @@ FDB_API void fdb_conv_gemm_info(void* handle, int* out5) {
   auto* op = static_cast<ConvGemmOp*>(handle);
   out5[0] = op->prm.tw; out5[1] = op->prm.th; out5[2] = op->block_n; out5[3] = op->grid;
   out5[4] = op->prm.total_tiles;
+}
+
+// 0 generic kernel, 1 halo kernel with streamed weights, 2 halo kernel with resident weights
+FDB_API int fdb_conv_gemm_variant(void* handle) {
+  auto* op = static_cast<ConvGemmOp*>(handle);
+  return op->halo ? (op->hp.b_resident ? 2 : 1) : 0;
 }

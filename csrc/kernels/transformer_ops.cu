@@ -1,0 +1,293 @@
+// Row-wise kernels of the transformer path: LayerNorm, fused embedding-sum + LayerNorm,
+// masked scaled softmax over attention scores, per-head transpose of V.
+// The GEMMs around them (QKV / output projection / FFN and the two batched attention
+// products) run on the tcgen05 kernel in conv_gemm_sm100.cu.
+//
+// In the reference these are whatever Paddle Inference / TensorRT pick for ERNIE and ViT
+// (fastdeploy/runtime/backends/paddle/paddle_backend.cc:426 predictor_->Run()).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <functional>
+
+#include "fdb_common.h"
+
+namespace fdb {
+
+struct TfDesc {
+  void* p[10];
+  long long i[16];
+  float f[4];
+};
+
+struct TfOp : Op {
+  std::function<int(cudaStream_t)> fn;
+  int launch(cudaStream_t s) override { return fn(s); }
+};
+
+enum TfKind : int { kLayerNorm = 0, kEmbedLayerNorm = 1, kMaskedSoftmax = 2, kHeadTranspose = 3 };
+
+template <bool BF16>
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 t;
+    if (BF16) t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+    else t = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+    f[2 * j] = t.x;
+    f[2 * j + 1] = t.y;
+  }
+}
+template <bool BF16>
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (BF16) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+      w[j] = *reinterpret_cast<uint32_t*>(&h);
+    } else {
+      __half2 h = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+      w[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---- LayerNorm over the last dimension: one warp per row --------------------------------
+// p0 x, p1 y, p2 gamma fp32 (or null), p3 beta fp32 (or null); i0 rows, i1 C, i2 x_ld, i3 y_ld, i4 bf16; f0 eps
+template <bool BF16>
+__global__ void layernorm_kernel(const uint8_t* __restrict__ x, uint8_t* __restrict__ y, const float* __restrict__ gamma,
+                                 const float* __restrict__ beta, long long rows, int C, int x_ld, int y_ld, float eps) {
+  const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const uint8_t* xr = x + row * x_ld * 2;
+  float s = 0.f, ss = 0.f;
+  for (int c = lane * 8; c < C; c += 256) {
+    float f[8];
+    unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(xr + c * 2)), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += f[j];
+  }
+  const float mean = warp_sum(s) / C;
+  for (int c = lane * 8; c < C; c += 256) {
+    float f[8];
+    unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(xr + c * 2)), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { const float d = f[j] - mean; ss += d * d; }
+  }
+  const float rstd = rsqrtf(warp_sum(ss) / C + eps);
+  uint8_t* yr = y + row * y_ld * 2;
+  for (int c = lane * 8; c < C; c += 256) {
+    float f[8];
+    unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(xr + c * 2)), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float v = (f[j] - mean) * rstd;
+      if (gamma) v *= gamma[c + j];
+      if (beta) v += beta[c + j];
+      f[j] = v;
+    }
+    *reinterpret_cast<uint4*>(yr + c * 2) = pack8<BF16>(f);
+  }
+}
+
+// ---- sum of up to 4 embedding lookups + LayerNorm: one warp per token ---------------------
+// p0..p3 ids (int64 [rows]) (null = position index row % i3), p4..p7 tables (16-bit [V][C]), p8 y;
+// gamma/beta fp32 are passed in a second descriptor call? No: p9 points at a fp32 block [gamma(C) | beta(C)].
+// i0 rows, i1 C, i2 num tables, i3 seq_len (for implicit positions), i4 bf16, i5 y_ld; f0 eps
+template <bool BF16>
+__global__ void embed_layernorm_kernel(const long long* const* __restrict__ ids4, const uint8_t* const* __restrict__ tabs4,
+                                       uint8_t* __restrict__ y, const float* __restrict__ gb, long long rows, int C,
+                                       int ntab, int seq, int y_ld, float eps) {
+  const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  long long idx[4];
+  for (int t = 0; t < ntab; ++t) idx[t] = ids4[t] ? ids4[t][row] : (row % seq);
+  float s = 0.f, ss = 0.f;
+  // C <= 8 * 32 * 6 = 1536 keeps the row in registers
+  float v[6][8];
+  int nv = 0;
+  for (int c = lane * 8; c < C; c += 256, ++nv) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[nv][j] = 0.f;
+    for (int t = 0; t < ntab; ++t) {
+      float f[8];
+      unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(tabs4[t] + (idx[t] * C + c) * 2)), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[nv][j] += f[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += v[nv][j];
+  }
+  const float mean = warp_sum(s) / C;
+  for (int k = 0; k < nv; ++k)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { const float d = v[k][j] - mean; ss += d * d; }
+  const float rstd = rsqrtf(warp_sum(ss) / C + eps);
+  uint8_t* yr = y + row * y_ld * 2;
+  int k = 0;
+  for (int c = lane * 8; c < C; c += 256, ++k) {
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = (v[k][j] - mean) * rstd * gb[c + j] + gb[C + c + j];
+    *reinterpret_cast<uint4*>(yr + c * 2) = pack8<BF16>(f);
+  }
+}
+
+// ---- softmax(scale * s + mask) in place over attention scores: one warp per row ---------------
+// scores [B][H][S][ld] 16-bit, valid columns Sk, columns [Sk, ld) are written as zero (they pad the
+// K dimension of the following P.V product). mask fp32, element (b, s, k) at b*m_b + s*m_s + k (m_s may
+// be 0 for a key-padding mask [B][Sk]); null = no mask.
+// p0 scores, p1 mask; i0 B, i1 H, i2 S, i3 Sk, i4 ld, i5 bf16, i6 m_b, i7 m_s; f0 scale
+template <bool BF16>
+__global__ void masked_softmax_kernel(uint8_t* __restrict__ sc, const float* __restrict__ mask, long long rows, int H,
+                                      int S, int Sk, int ld, long long m_b, long long m_s, float scale) {
+  const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int s_idx = static_cast<int>(row % S);
+  const long long b = row / (static_cast<long long>(S) * H);
+  uint8_t* r = sc + row * ld * 2;
+  const float* mrow = mask ? mask + b * m_b + s_idx * m_s : nullptr;
+  // Sk <= 8 * 32 * 4 = 1024 keeps the row in registers
+  float v[4][8];
+  int nv = 0;
+  float mx = -INFINITY;
+  for (int c = lane * 8; c < ld; c += 256, ++nv) {
+    unpack8<BF16>(*reinterpret_cast<const uint4*>(r + c * 2), v[nv]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float t = (c + j < Sk) ? v[nv][j] * scale + (mrow ? mrow[c + j] : 0.f) : -INFINITY;
+      v[nv][j] = t;
+      mx = fmaxf(mx, t);
+    }
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int k = 0; k < nv; ++k)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float e = v[k][j] == -INFINITY ? 0.f : __expf(v[k][j] - mx);
+      v[k][j] = e;
+      sum += e;
+    }
+  const float inv = 1.f / warp_sum(sum);
+  int k = 0;
+  for (int c = lane * 8; c < ld; c += 256, ++k) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[k][j] *= inv;
+    *reinterpret_cast<uint4*>(r + c * 2) = pack8<BF16>(v[k]);
+  }
+}
+
+// ---- V [B][S][H*D] (row stride ld) -> V^T [B][H][D][Sp], zero padded to Sp ------------------------
+// p0 v, p1 vt; i0 B, i1 S, i2 H, i3 D, i4 v_ld, i5 Sp
+__global__ void head_transpose_kernel(const uint16_t* __restrict__ v, uint16_t* __restrict__ vt, int B, int S, int H,
+                                      int D, int v_ld, int Sp) {
+  __shared__ uint16_t tile[32][33];
+  const int bh = blockIdx.z, b = bh / H, h = bh - b * H;
+  const int s0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int s = s0 + i, d = d0 + threadIdx.x;
+    tile[i][threadIdx.x] = (s < S && d < D) ? v[(static_cast<size_t>(b) * S + s) * v_ld + h * D + d] : 0;
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int d = d0 + i, s = s0 + threadIdx.x;
+    if (d < D && s < Sp) vt[((static_cast<size_t>(b) * H + h) * D + d) * Sp + s] = tile[threadIdx.x][i];
+  }
+}
+
+#define FDB_TF_CHECK()                              \
+  do {                                              \
+    cudaError_t _e = cudaGetLastError();            \
+    if (_e != cudaSuccess) {                        \
+      set_error(cudaGetErrorString(_e));            \
+      return -1;                                    \
+    }                                               \
+    return 0;                                       \
+  } while (0)
+
+}  // namespace fdb
+
+using namespace fdb;
+
+FDB_API void* fdb_transformer_create(int kind, const TfDesc* dp) {
+  const TfDesc d = *dp;
+  auto* op = new TfOp();
+  switch (kind) {
+    case kLayerNorm: {
+      const long long rows = d.i[0];
+      const int C = d.i[1], x_ld = d.i[2], y_ld = d.i[3];
+      const bool bf = d.i[4] != 0;
+      const float eps = d.f[0];
+      if (C % 8 || x_ld % 8 || y_ld % 8) { set_error("layernorm: C/ld must be multiples of 8"); delete op; return nullptr; }
+      op->fn = [=](cudaStream_t s) {
+        const int grid = static_cast<int>((rows * 32 + 255) / 256);
+        if (bf) layernorm_kernel<true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps);
+        else layernorm_kernel<false><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps);
+        FDB_TF_CHECK();
+      };
+      break;
+    }
+    case kEmbedLayerNorm: {
+      // p0 = device array of 4 id pointers, p1 = device array of 4 table pointers, p2 = y, p3 = gamma|beta block
+      const long long rows = d.i[0];
+      const int C = d.i[1], ntab = d.i[2], seq = d.i[3], y_ld = d.i[5];
+      const bool bf = d.i[4] != 0;
+      const float eps = d.f[0];
+      if (C % 8 || C > 1536 || ntab < 1 || ntab > 4 || y_ld % 8) { set_error("embed_layernorm: C multiple of 8 and <= 1536, 1..4 tables"); delete op; return nullptr; }
+      op->fn = [=](cudaStream_t s) {
+        const int grid = static_cast<int>((rows * 32 + 255) / 256);
+        if (bf) embed_layernorm_kernel<true><<<grid, 256, 0, s>>>((const long long* const*)d.p[0], (const uint8_t* const*)d.p[1], (uint8_t*)d.p[2], (const float*)d.p[3], rows, C, ntab, seq, y_ld, eps);
+        else embed_layernorm_kernel<false><<<grid, 256, 0, s>>>((const long long* const*)d.p[0], (const uint8_t* const*)d.p[1], (uint8_t*)d.p[2], (const float*)d.p[3], rows, C, ntab, seq, y_ld, eps);
+        FDB_TF_CHECK();
+      };
+      break;
+    }
+    case kMaskedSoftmax: {
+      const int B = d.i[0], H = d.i[1], S = d.i[2], Sk = d.i[3], ld = d.i[4];
+      const bool bf = d.i[5] != 0;
+      const long long m_b = d.i[6], m_s = d.i[7];
+      const float scale = d.f[0];
+      if (ld % 8 || ld > 1024 || Sk > ld) { set_error("masked_softmax: ld multiple of 8, <= 1024, >= Sk"); delete op; return nullptr; }
+      const long long rows = static_cast<long long>(B) * H * S;
+      op->fn = [=](cudaStream_t s) {
+        const int grid = static_cast<int>((rows * 32 + 255) / 256);
+        if (bf) masked_softmax_kernel<true><<<grid, 256, 0, s>>>((uint8_t*)d.p[0], (const float*)d.p[1], rows, H, S, Sk, ld, m_b, m_s, scale);
+        else masked_softmax_kernel<false><<<grid, 256, 0, s>>>((uint8_t*)d.p[0], (const float*)d.p[1], rows, H, S, Sk, ld, m_b, m_s, scale);
+        FDB_TF_CHECK();
+      };
+      break;
+    }
+    case kHeadTranspose: {
+      const int B = d.i[0], S = d.i[1], H = d.i[2], D = d.i[3], v_ld = d.i[4], Sp = d.i[5];
+      op->fn = [=](cudaStream_t s) {
+        dim3 grid((Sp + 31) / 32, (D + 31) / 32, B * H), block(32, 8);
+        head_transpose_kernel<<<grid, block, 0, s>>>((const uint16_t*)d.p[0], (uint16_t*)d.p[1], B, S, H, D, v_ld, Sp);
+        FDB_TF_CHECK();
+      };
+      break;
+    }
+    default:
+      set_error("fdb_transformer_create: unknown kind");
+      delete op;
+      return nullptr;
+  }
+  return op;
+}

@@ -32,6 +32,10 @@ class _ConvGemmDesc(ctypes.Structure):
         ("act", ctypes.c_int), ("act_alpha", ctypes.c_float), ("act_beta", ctypes.c_float),
         ("tile_w", ctypes.c_int), ("tile_h", ctypes.c_int), ("block_n", ctypes.c_int), ("max_ctas", ctypes.c_int),
         ("x_n_stride", ctypes.c_longlong), ("y_n_stride", ctypes.c_longlong), ("res_n_stride", ctypes.c_longlong),
+        ("halo_mode", ctypes.c_int),
+        ("w_batched", ctypes.c_int), ("w_ld", ctypes.c_int), ("w_h_stride", ctypes.c_longlong),
+        ("w_n_stride", ctypes.c_longlong),
+        ("x_h_stride", ctypes.c_longlong), ("y_h_stride", ctypes.c_longlong), ("res_h_stride", ctypes.c_longlong),
     ]
 
 
@@ -41,6 +45,7 @@ def _lib():
         lib.fdb_conv_gemm_create.restype = ctypes.c_void_p
         lib.fdb_conv_gemm_create.argtypes = [ctypes.POINTER(_ConvGemmDesc)]
         lib.fdb_conv_gemm_info.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]
+        lib.fdb_conv_gemm_variant.argtypes = [ctypes.c_void_p]
         lib._conv_gemm_ready = True
     return lib
 
@@ -71,6 +76,8 @@ class ConvGemm(NativeOp):
                  x_ld: Optional[int] = None, y_ld: Optional[int] = None, res_ld: Optional[int] = None,
                  status: Optional[StatusWord] = None, tile: Tuple[int, int] = (0, 0), block_n: int = 0,
                  max_ctas: int = 0, x_n_stride: int = 0, y_n_stride: int = 0, res_n_stride: int = 0,
+                 halo_mode: int = -1, w_batched: bool = False, w_ld: int = 0, w_h_stride: int = 0,
+                 w_n_stride: int = 0, x_h_stride: int = 0, y_h_stride: int = 0, res_h_stride: int = 0,
                  name: str = "conv_gemm"):
         n, h, w_, cin = in_shape
         d = _ConvGemmDesc()
@@ -90,6 +97,9 @@ class ConvGemm(NativeOp):
         d.act, d.act_alpha, d.act_beta = ACT[act], act_alpha, act_beta
         d.tile_w, d.tile_h, d.block_n, d.max_ctas = tile[0], tile[1], block_n, max_ctas
         d.x_n_stride, d.y_n_stride, d.res_n_stride = x_n_stride, y_n_stride, res_n_stride
+        d.halo_mode = halo_mode
+        d.w_batched, d.w_ld, d.w_h_stride, d.w_n_stride = int(w_batched), w_ld, w_h_stride, w_n_stride
+        d.x_h_stride, d.y_h_stride, d.res_h_stride = x_h_stride, y_h_stride, res_h_stride
         if bias is not None:
             assert bias.dtype == torch.float32
         if residual is not None:
@@ -101,7 +111,8 @@ class ConvGemm(NativeOp):
     def info(self):
         out = (ctypes.c_int * 5)()
         _lib().fdb_conv_gemm_info(self.handle, out)
-        return dict(tile_w=out[0], tile_h=out[1], block_n=out[2], grid=out[3], tiles=out[4])
+        return dict(tile_w=out[0], tile_h=out[1], block_n=out[2], grid=out[3], tiles=out[4],
+                    variant=_lib().fdb_conv_gemm_variant(self.handle))
 
 
 def conv2d_nhwc(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, *, stride: int = 1,

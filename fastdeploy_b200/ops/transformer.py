@@ -1,0 +1,119 @@
+"""Transformer-path ops: LayerNorm, embedding-sum + LayerNorm, masked softmax, and multi-head
+attention composed from two batched tcgen05 GEMMs (csrc/kernels/transformer_ops.cu and
+conv_gemm_sm100.cu in batched-weight mode).
+
+Attention(q, k, v, mask) for ``[B, S, H*D]`` inputs runs as
+  scores[b,h] = q[b,:,h,:] @ k[b,:,h,:]^T      (batched GEMM, heads = image rows of a B x H x S "image")
+  p           = softmax(scale * scores + mask)  (in place, padded key columns zeroed)
+  vT          = per-head transpose of v
+  out[b,:,h,:] = p[b,h] @ vT[b,h]^T            (batched GEMM writing straight into [B, S, H*D])
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+
+from .. import _native
+from .base import DT_BF16, NativeOp, StatusWord, dtype_code
+from .conv_gemm import ConvGemm
+
+K_LAYERNORM, K_EMBED_LN, K_SOFTMAX, K_HEAD_TRANSPOSE = range(4)
+
+
+class _TfDesc(ctypes.Structure):
+    _fields_ = [("p", ctypes.c_void_p * 10), ("i", ctypes.c_longlong * 16), ("f", ctypes.c_float * 4)]
+
+
+def _lib():
+    lib = _native.kernels()
+    if not getattr(lib, "_tf_ready", False):
+        lib.fdb_transformer_create.restype = ctypes.c_void_p
+        lib.fdb_transformer_create.argtypes = [ctypes.c_int, ctypes.POINTER(_TfDesc)]
+        lib._tf_ready = True
+    return lib
+
+
+def _make(kind, ptrs, ints, floats=(), name="tf", keep=None) -> NativeOp:
+    d = _TfDesc()
+    for k, t in enumerate(ptrs):
+        d.p[k] = (t.data_ptr() if isinstance(t, torch.Tensor) else t) if t is not None else None
+    for k, v in enumerate(ints):
+        d.i[k] = int(v)
+    for k, v in enumerate(floats):
+        d.f[k] = float(v)
+    return NativeOp(_lib().fdb_transformer_create(kind, ctypes.byref(d)), list(ptrs) + list(keep or []), name)
+
+
+def _bf(t) -> int:
+    return 1 if dtype_code(t.dtype) == DT_BF16 else 0
+
+
+def layernorm(x: torch.Tensor, y: torch.Tensor, gamma: Optional[torch.Tensor], beta: Optional[torch.Tensor], *,
+              rows: int, c: int, eps: float = 1e-5, x_ld: Optional[int] = None, y_ld: Optional[int] = None) -> NativeOp:
+    return _make(K_LAYERNORM, [x, y, gamma, beta], [rows, c, x_ld or c, y_ld or c, _bf(x)], [eps], "layernorm")
+
+
+def embed_layernorm(ids: List[Optional[torch.Tensor]], tables: List[torch.Tensor], y: torch.Tensor,
+                    gamma: torch.Tensor, beta: torch.Tensor, *, rows: int, c: int, seq: int, eps: float = 1e-5,
+                    y_ld: Optional[int] = None) -> NativeOp:
+    """``ids[k]`` int64 ``[rows]`` (``None`` = position index ``row % seq``), ``tables[k]`` 16-bit ``[V, c]``."""
+    dev = y.device
+    idp = torch.tensor([(t.data_ptr() if t is not None else 0) for t in ids] + [0] * (4 - len(ids)),
+                       dtype=torch.int64, device=dev)
+    tbp = torch.tensor([t.data_ptr() for t in tables] + [0] * (4 - len(tables)), dtype=torch.int64, device=dev)
+    gb = torch.cat([gamma.float().reshape(-1), beta.float().reshape(-1)]).contiguous().to(dev)
+    return _make(K_EMBED_LN, [idp, tbp, y, gb], [rows, c, len(tables), seq, _bf(y), y_ld or c], [eps],
+                 "embed_layernorm", keep=list(ids) + list(tables))
+
+
+def masked_softmax(scores: torch.Tensor, mask: Optional[torch.Tensor], *, b: int, h: int, s: int, sk: int, ld: int,
+                   scale: float, mask_b_stride: int = 0, mask_s_stride: int = 0) -> NativeOp:
+    return _make(K_SOFTMAX, [scores, mask], [b, h, s, sk, ld, _bf(scores), mask_b_stride, mask_s_stride], [scale],
+                 "masked_softmax")
+
+
+def head_transpose(v: torch.Tensor, vt: torch.Tensor, *, b: int, s: int, h: int, d: int, v_ld: int, sp: int) -> NativeOp:
+    return _make(K_HEAD_TRANSPOSE, [v, vt], [b, s, h, d, v_ld, sp], name="head_transpose")
+
+
+class Attention:
+    """Planned multi-head attention over fixed buffers. ``q``/``k``/``v`` are ``[B, S, H*D]`` views
+    (row strides may differ, e.g. slices of a fused QKV buffer); ``out`` is ``[B, S, H*D]``."""
+
+    def __init__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, *, heads: int,
+                 scale: float, mask: Optional[torch.Tensor] = None, status: Optional[StatusWord] = None):
+        b, s, hd = q.shape
+        sk = k.shape[1]
+        d = hd // heads
+        assert d % 8 == 0, "head dim must be a multiple of 8"
+        dev, dt = q.device, q.dtype
+        skp = (sk + 7) // 8 * 8
+        self.scores = torch.zeros(b, heads, s, skp, dtype=dt, device=dev)
+        self.vt = torch.zeros(b, heads, d, skp, dtype=dt, device=dev)
+        self.status = status or StatusWord(dev)
+        q_ld, k_ld, v_ld, o_ld = q.stride(1), k.stride(1), v.stride(1), out.stride(1)
+        # scores: "image" = B x (H rows) x (S pixels) x D channels; weights = K of the same (b, h)
+        qk = ConvGemm(q, k, self.scores, in_shape=(b, heads, s, d), out_hw=(heads, s), cout=sk, x_ld=q_ld,
+                      x_n_stride=q.stride(0), x_h_stride=d, y_ld=skp, status=self.status, w_batched=True,
+                      w_ld=k_ld, w_h_stride=d, w_n_stride=k.stride(0), name="attn_qk")
+        m_b = m_s = 0
+        if mask is not None:
+            assert mask.dtype == torch.float32
+            mm = mask.reshape(b, -1, sk) if mask.numel() != b * sk else mask.reshape(b, 1, sk)
+            m_b = mm.stride(0)
+            m_s = mm.stride(1) if mm.shape[1] > 1 else 0
+        sm = masked_softmax(self.scores, mask, b=b, h=heads, s=s, sk=sk, ld=skp, scale=scale, mask_b_stride=m_b,
+                            mask_s_stride=m_s)
+        tr = head_transpose(v, self.vt, b=b, s=sk, h=heads, d=d, v_ld=v_ld, sp=skp)
+        pv = ConvGemm(self.scores, self.vt, out, in_shape=(b, heads, s, skp), out_hw=(heads, s), cout=d,
+                      x_ld=skp, y_ld=o_ld, y_n_stride=out.stride(0), y_h_stride=d, status=self.status,
+                      w_batched=True, w_ld=skp,
+                      w_h_stride=d * skp, w_n_stride=heads * d * skp, name="attn_pv")
+        self.ops = [qk, sm, tr, pv]
+        self.keep = [q, k, v, out, mask]
+
+    def launch(self, stream=None) -> None:
+        for op in self.ops:
+            op.launch(stream)

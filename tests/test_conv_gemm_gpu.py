@@ -146,3 +146,31 @@ def test_linear_activations(act, dtype):
     ref = {None: lambda t: t, "relu": torch.relu, "silu": F.silu, "hard_swish": F.hardswish, "sigmoid": torch.sigmoid,
            "gelu": F.gelu, "relu6": F.relu6, "tanh": torch.tanh}[act](z)
     _check(y, ref, tol=2e-2 if dtype == torch.bfloat16 else 6e-3)
+
+
+@pytest.mark.parametrize("cfg", [
+    # n, h, w, cin, cout, act, expected variant (1 streamed weights, 2 resident weights)
+    (2, 16, 16, 64, 64, "silu", 2),
+    (2, 32, 24, 48, 48, "silu", 2),
+    (1, 33, 21, 32, 40, None, 2),          # ragged edges in both directions
+    (2, 16, 16, 96, 96, "relu", 1),        # two channel slabs -> streamed weights
+    (2, 24, 16, 192, 192, "silu", 1),
+    (1, 16, 16, 128, 320, None, 1),        # two column tiles
+    (3, 40, 40, 8, 32, "silu", 2),         # stem-like: 8 physical input channels
+])
+def test_conv3x3_halo_kernel(cfg):
+    from fastdeploy_b200.ops.conv_gemm import ConvGemm, pack_conv_weight
+    n, h, w_, cin, cout, act, variant = cfg
+    torch.manual_seed(7)
+    x = (torch.randn(n, h, w_, cin, device="cuda") * 0.5).half()
+    w = (torch.randn(cout, cin, 3, 3, device="cuda") * (1.0 / (cin * 9) ** 0.5)).half()
+    b = torch.randn(cout, device="cuda") * 0.1
+    res = (torch.randn(n, h, w_, cout, device="cuda") * 0.5).half()
+    y = torch.zeros(n, h, w_, cout, device="cuda", dtype=torch.float16)
+    op = ConvGemm(x, pack_conv_weight(w, torch.float16), y, in_shape=(n, h, w_, cin), out_hw=(h, w_), cout=cout,
+                  kernel=(3, 3), stride=1, pad=(1, 1), bias=b, residual=res, res_mode=2, act=act, halo_mode=1)
+    assert op.info()["variant"] == variant
+    for _ in range(2):                      # the persistent pipeline must also be right on reuse
+        op.launch()
+    op.status.check()
+    _check(y, _ref_conv(x, w, b, 1, 1, act, res, 2))
