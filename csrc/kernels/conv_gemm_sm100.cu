@@ -63,6 +63,7 @@ struct ConvGemmDesc {
   long long w_h_stride, w_n_stride;
   // elements between image rows (0 = W * ld): lets heads of a [B, S, H*D] tensor act as image rows
   long long x_h_stride, y_h_stride, res_h_stride;
+  int y_tma_mode;        // -1/1: TMA tensor stores for 16-bit outputs when possible, 0: direct stores
 };
 
 struct ConvGemmParams {
@@ -82,6 +83,7 @@ struct ConvGemmParams {
   long long y_n_stride, res_n_stride;
   long long y_h_stride, res_h_stride;
   int b_batched;
+  int y_tma;   // 16-bit output leaves through shared-memory staging + TMA tensor stores
 };
 
 // Generic activation (runtime code); the hot ones have dedicated template paths.
@@ -226,7 +228,7 @@ constexpr int kTplGeneric = -1;
 template <int ACT>
 __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParams& p, int co,
                                           int col_limit, uint8_t* yrow, const uint8_t* rrow,
-                                          bool in_bf16, int out_es) {
+                                          bool in_bf16, int out_es, uint32_t stage_addr = 0) {
   const int nvalid = min(8, col_limit - co);
   if (nvalid <= 0) return;
   float x[8];
@@ -242,18 +244,19 @@ __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParam
       for (int j = 0; j < nvalid; ++j) x[j] += __ldg(p.bias + co + j);
     }
   }
-  const bool fast16 = p.out_dtype != kF32 && p.y_vec != 0 && nvalid == 8;
+  // staged rows go out through a TMA store that clips channel tails, so tails may take this path too
+  const bool fast16 = p.out_dtype != kF32 && (stage_addr != 0 || (p.y_vec != 0 && nvalid == 8));
   if (fast16) {
     const bool out_bf16 = p.out_dtype == kBF16;
     uint32_t w[4];
     uint4 rv = make_uint4(0, 0, 0, 0);
-    const bool res_fast = p.res_mode != 0 && p.res_vec != 0 && in_bf16 == out_bf16;
+    const bool res_fast = p.res_mode != 0 && p.res_vec != 0 && in_bf16 == out_bf16 && nvalid == 8;
     if (p.res_mode != 0) {
       if (res_fast && p.res_mode == 2) {
         rv = *reinterpret_cast<const uint4*>(rrow + co * 2);
       } else {
         float r[8];
-        load8_as_float(rrow + co * 2, in_bf16, p.res_vec != 0, 8, r);
+        load8_as_float(rrow + co * 2, in_bf16, p.res_vec != 0, nvalid, r);
         if (p.res_mode == 1) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) x[j] += r[j];
@@ -276,7 +279,13 @@ __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParam
       w[0] = add2(w[0], rv.x, out_bf16); w[1] = add2(w[1], rv.y, out_bf16);
       w[2] = add2(w[2], rv.z, out_bf16); w[3] = add2(w[3], rv.w, out_bf16);
     }
-    *reinterpret_cast<uint4*>(yrow + static_cast<size_t>(co) * 2) = make_uint4(w[0], w[1], w[2], w[3]);
+    if (stage_addr != 0) {
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_addr), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                   "r"(w[3])
+                   : "memory");
+    } else {
+      *reinterpret_cast<uint4*>(yrow + static_cast<size_t>(co) * 2) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
     return;
   }
   // general path: fp32 output, channel tails, unaligned rows
@@ -305,6 +314,90 @@ __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParam
 // Epilogue role shared by the convolution kernels: drains the double-buffered TMEM
 // accumulators tile by tile. `tfull0` / `tempty0` are the shared-memory addresses of
 // tmem_full[0] and tmem_empty[0]; index 1 of each follows 8 bytes later.
+constexpr int kStageTileBytes = kBM * 128;      // one 128-row x 64-channel (16-bit) output block
+constexpr int kStagingBytes = 2 * kStageTileBytes;
+
+// Output path for 16-bit results: the eight epilogue warps assemble a 128 x 64-channel block in
+// shared memory (128-byte swizzled rows) and one thread hands it to a TMA tensor store, which writes
+// whole lines and clips ragged tile edges and channel tails. Two blocks are in flight.
+template <int BN, int ACT>
+__device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const CUtensorMap* tmY, uint32_t stage0,
+                                                  uint32_t tmem_base, uint32_t tfull0, uint32_t tempty0,
+                                                  volatile int* abort_flag, int warp, int lane) {
+  const int q = warp & 3;
+  const int half = (warp - 2) >> 2;
+  const bool issuer = warp == 2 && lane == 0;
+  const bool in_bf16 = p.in_bf16 != 0;
+  int acc = 0;
+  uint32_t acc_ph = 0;
+  uint32_t blk_count = 0;
+  for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+    const int n_tile = tile % p.n_tiles;
+    int m_tile = tile / p.n_tiles;
+    const int twi = m_tile % p.tiles_w; m_tile /= p.tiles_w;
+    const int thi = m_tile % p.tiles_h;
+    const int img = m_tile / p.tiles_h;
+    mbar_wait(tfull0 + 8u * acc, acc_ph, abort_flag, kStatusTimeoutEpilogue);
+    // The warps meet at named barriers below, so they must all leave together: one thread samples
+    // the abort flag and everybody acts on that sample.
+    volatile int* abort_sample = abort_flag + 1;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (issuer) *abort_sample = *abort_flag;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (*abort_sample != 0) break;
+    tc_fence_after();
+    const int row = q * 32 + lane;
+    const int rh = row / p.tw, rw = row - rh * p.tw;
+    const int oh = thi * p.th + rh, ow = twi * p.tw + rw;
+    const bool valid = rh < p.th && oh < p.Ho && ow < p.Wo;
+    const uint8_t* rrow = reinterpret_cast<const uint8_t*>(p.residual) +
+                          (static_cast<size_t>(img) * p.res_n_stride + static_cast<size_t>(oh) * p.res_h_stride +
+                           static_cast<size_t>(ow) * p.res_ld) * 2;
+    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+    const int colbase = n_tile * BN;
+    const int col_limit = min(p.Cout, colbase + BN);
+    const int nblk = (col_limit - colbase + 63) / 64;
+    for (int blk = 0; blk < nblk; ++blk, ++blk_count) {
+      const uint32_t buf = stage0 + (blk_count & 1u) * kStageTileBytes;
+      if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      const int c = blk * 2 + half;                 // this warp's 32-column TMEM chunk
+      if (colbase + c * 32 < col_limit) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_row + c * 32, v);
+        tmem_ld_wait_dep(v);
+        if (valid) {
+          const uint32_t srow = buf + row * 128;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint32_t chunk = static_cast<uint32_t>(half * 4 + g);
+            epilogue8<ACT>(v + g * 8, p, colbase + c * 32 + g * 8, col_limit, nullptr, rrow, in_bf16, 2,
+                           srow + ((chunk ^ (row & 7)) << 4));
+          }
+        }
+      }
+      if (blk == nblk - 1) {        // last TMEM read of this accumulator
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty0 + 8u * acc);
+      }
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (issuer) {
+        asm volatile(
+            "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                reinterpret_cast<uint64_t>(tmY)),
+            "r"(buf), "r"(colbase + blk * 64), "r"(twi * p.tw), "r"(thi * p.th), "r"(img)
+            : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
+    }
+    acc ^= 1;
+    if (acc == 0) acc_ph ^= 1;
+  }
+  if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
 template <int BN, int ACT>
 __device__ __forceinline__ void epilogue_loop(const ConvGemmParams& p, uint32_t tmem_base, uint32_t tfull0,
                                               uint32_t tempty0, volatile int* abort_flag, int warp, int lane) {
@@ -387,22 +480,22 @@ struct KernelCfg {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStagesFit = (kMaxSmem - kBarBytes - 1024) / kStageBytes;
+  static constexpr int kStagesFit = (kMaxSmem - kBarBytes - 1024 - kStagingBytes) / kStageBytes;
   static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
   static constexpr int kTmemCols = next_pow2_cols(2 * BN);
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;  // +1024: alignment slack
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarBytes + 1024;  // +1024: alignment slack
 };
 
 template <int BN, int ACT>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const ConvGemmParams p) {
+                 const __grid_constant__ CUtensorMap tmY, const ConvGemmParams p) {
   using Cfg = KernelCfg<BN>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes + kStagingBytes);
   // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -522,6 +615,9 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (acc == 0) acc_ph ^= 1;
       }
     }
+  } else if (p.y_tma) {
+    epilogue_loop_tma<BN, ACT>(p, &tmY, tile0 + S * Cfg::kStageBytes, tmem_base, tfull_bar(0), tempty_bar(0),
+                               abort_flag, warp, lane);
   } else {
     epilogue_loop<BN, ACT>(p, tmem_base, tfull_bar(0), tempty_bar(0), abort_flag, warp, lane);
   }
@@ -550,6 +646,7 @@ constexpr int kHaloTw = 8, kHaloTh = 16;
 constexpr int kHaloCols = kHaloTw + 2, kHaloRows = kHaloTh + 2;
 constexpr int kHaloABytes = ((kHaloCols * kHaloRows * 128) + 1023) / 1024 * 1024;   // 23552
 constexpr int kHaloMaxB = 18;   // weight stages (barrier slots)
+constexpr int kHaloMaxA = 8;    // activation patch stages
 constexpr int kHaloBarBytes = 512;
 
 struct HaloParams {
@@ -559,14 +656,14 @@ struct HaloParams {
 template <int BN, int ACT>
 __global__ void __launch_bounds__(kThreads, 1)
 conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const ConvGemmParams p, const HaloParams hp) {
+                    const __grid_constant__ CUtensorMap tmY, const ConvGemmParams p, const HaloParams hp) {
   constexpr int kBBytes = BN * kBK * 2;
   constexpr int kTmemCols = next_pow2_cols(2 * BN);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   const int SA = hp.a_stages, SB = hp.b_stages;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SA * kHaloABytes + SB * kBBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SA * kHaloABytes + SB * kBBytes + kStagingBytes);
   // bars: a_full[SA] a_empty[SA] b_full[SB] b_empty[SB] tfull[2] tempty[2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SA + 2 * SB + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -675,6 +772,8 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (acc == 0) acc_ph ^= 1;
       }
     }
+  } else if (p.y_tma) {
+    epilogue_loop_tma<BN, ACT>(p, &tmY, b0 + SB * kBBytes, tmem_base, tfull0, tempty0, abort_flag, warp, lane);
   } else {
     epilogue_loop<BN, ACT>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane);
   }
@@ -693,6 +792,7 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 struct ConvGemmOp : Op {
   alignas(64) CUtensorMap tmA;
   alignas(64) CUtensorMap tmB;
+  alignas(64) CUtensorMap tmY;
   ConvGemmParams prm;
   int block_n = 0;
   int grid = 0;
@@ -713,7 +813,7 @@ static int launch_inst(ConvGemmOp* op, cudaStream_t stream) {
                                      Cfg::kSmemBytes));
     attr_set[dev] = true;
   }
-  conv_gemm_kernel<BN, ACT><<<op->grid, kThreads, Cfg::kSmemBytes, stream>>>(op->tmA, op->tmB, op->prm);
+  conv_gemm_kernel<BN, ACT><<<op->grid, kThreads, Cfg::kSmemBytes, stream>>>(op->tmA, op->tmB, op->tmY, op->prm);
   FDB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -728,7 +828,7 @@ static int launch_halo_inst(ConvGemmOp* op, cudaStream_t stream) {
                                      kMaxSmem));
     attr_set[dev] = true;
   }
-  conv3x3_halo_kernel<BN, ACT><<<op->grid, kThreads, op->halo_smem, stream>>>(op->tmA, op->tmB, op->prm, op->hp);
+  conv3x3_halo_kernel<BN, ACT><<<op->grid, kThreads, op->halo_smem, stream>>>(op->tmA, op->tmB, op->tmY, op->prm, op->hp);
   FDB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -893,17 +993,21 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   int grid = static_cast<int>(std::min<long>(total, d->max_ctas > 0 ? d->max_ctas : sms));
   op->grid = std::max(grid, 1);
   if (op->halo) {
-    const int budget = kMaxSmem - 1024 - kHaloBarBytes;
+    const int budget = kMaxSmem - 1024 - kHaloBarBytes - kStagingBytes;
     const int b_bytes = bn * kBK * 2;
     const int all_b = 9 * p.kb_per_tap;
     HaloParams hp{};
-    hp.a_stages = p.kb_per_tap > 1 ? 3 : 2;
-    if (p.n_tiles == 1 && all_b <= kHaloMaxB && hp.a_stages * kHaloABytes + all_b * b_bytes <= budget) {
+    // Activation patches come from DRAM, weights from L2: bytes in flight matter for the patches,
+    // so they get the deeper ring.
+    if (p.n_tiles == 1 && all_b <= kHaloMaxB && 3 * kHaloABytes + all_b * b_bytes <= budget) {
       hp.b_resident = 1;
       hp.b_stages = all_b;
+      hp.a_stages = std::min(kHaloMaxA, (budget - all_b * b_bytes) / kHaloABytes);
     } else {
       hp.b_resident = 0;
-      hp.b_stages = std::min(kHaloMaxB, (budget - hp.a_stages * kHaloABytes) / b_bytes);
+      hp.b_stages = std::max(3, std::min(kHaloMaxB, (budget / 2) / b_bytes));
+      hp.a_stages = std::min(kHaloMaxA, (budget - hp.b_stages * b_bytes) / kHaloABytes);
+      if (hp.a_stages < 2) { hp.a_stages = 2; hp.b_stages = (budget - 2 * kHaloABytes) / b_bytes; }
     }
     if (hp.b_stages < 3) {
       if (d->halo_mode == 1) { set_error("conv_gemm: halo kernel does not fit shared memory"); delete op; return nullptr; }
@@ -918,7 +1022,7 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
       op->grid = std::max(1, static_cast<int>(std::min<long>(p.total_tiles, d->max_ctas > 0 ? d->max_ctas : sms)));
     } else {
       op->hp = hp;
-      op->halo_smem = hp.a_stages * kHaloABytes + hp.b_stages * b_bytes + kHaloBarBytes + 1024;
+      op->halo_smem = hp.a_stages * kHaloABytes + hp.b_stages * b_bytes + kStagingBytes + kHaloBarBytes + 1024;
     }
   }
 
@@ -965,6 +1069,26 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
       set_error("conv_gemm: encode weight tensor map failed, CUresult " + std::to_string((int)r));
       delete op; return nullptr;
     }
+  }
+  // 16-bit outputs leave through TMA tensor stores when the layout allows it
+  p.y_tma = 0;
+  {
+    const bool out16 = d->out_dtype == kF16 || d->out_dtype == kBF16;
+    const bool aligned = reinterpret_cast<uintptr_t>(d->y) % 16 == 0 && (d->y_ld * 2) % 16 == 0 &&
+                         (p.y_h_stride * 2) % 16 == 0 && (p.y_n_stride * 2) % 16 == 0;
+    const bool cols_ok = p.n_tiles == 1 || bn % 64 == 0;
+    if (out16 && aligned && cols_ok && d->y_tma_mode != 0) {
+      const CUtensorMapDataType ydt =
+          d->out_dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+      cuuint64_t dims[4] = {(cuuint64_t)d->Cout, (cuuint64_t)d->Wo, (cuuint64_t)d->Ho, (cuuint64_t)d->N};
+      cuuint64_t strides[3] = {(cuuint64_t)d->y_ld * 2, (cuuint64_t)p.y_h_stride * 2, (cuuint64_t)p.y_n_stride * 2};
+      cuuint32_t box[4] = {64, (cuuint32_t)p.tw, (cuuint32_t)p.th, 1};
+      cuuint32_t estr[4] = {1, 1, 1, 1};
+      CUresult r = enc(&op->tmY, ydt, 4, d->y, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r == CUDA_SUCCESS) p.y_tma = 1;
+    }
+    if (!p.y_tma) op->tmY = op->tmA;   // a valid map is still passed; the kernel does not touch it
   }
   return op;
 }

@@ -298,9 +298,9 @@ class ProgramBuilder:
         return name
 
     def op(self, type_: str, inputs: Dict[str, Sequence[str]], out_keys: Sequence[str] = ("Out",),
-           out_shape: Sequence[int] = (), out_dtype: str = "float32", **attrs) -> str:
+           out_shape: Sequence[int] = (), var_dtype: str = "float32", **attrs) -> str:
         """Adds an op with fresh output variables; returns the first output name."""
-        outs = {k: [self.tmp(type_, out_dtype, out_shape)] for k in out_keys}
+        outs = {k: [self.tmp(type_, var_dtype, out_shape)] for k in out_keys}
         self.prog.add_op(type_, inputs, outs, **attrs)
         return outs[out_keys[0]][0]
 

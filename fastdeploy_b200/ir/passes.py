@@ -75,8 +75,11 @@ def fold_constants(graph: Graph, info: Optional[ShapeInfo] = None) -> int:
                         graph.initializers[o] = np.ascontiguousarray(info.values[o])
                 changed += 1
                 continue
+        big_gather = node.op == "Gather" and node.inputs[0] in graph.initializers and \
+            graph.initializers[node.inputs[0]].ndim == 2 and node.inputs[1] in graph.initializers and \
+            graph.initializers[node.inputs[1]].size * graph.initializers[node.inputs[0]].shape[1] > 1024
         if node.inputs and all((i in graph.initializers or i == "") for i in node.inputs) and node.op in interp._OPS \
-                and node.op not in ("MultiClassNMS",):
+                and node.op not in ("MultiClassNMS",) and not big_gather:
             args = []
             for i in node.inputs:
                 if i == "":

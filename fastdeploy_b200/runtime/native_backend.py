@@ -742,3 +742,134 @@ def build_plan(graph: Graph, input_shapes: Dict[str, Sequence[int]], device, dty
         plan = low.build()
         plan.extra["graph"] = g
     return plan
+
+
+# ---------------------------------------------------------------------- transformer lowering
+def _rows_of(shape: Sequence[int]) -> int:
+    return int(np.prod(shape[:-1])) if len(shape) > 1 else 1
+
+
+def _lower_LayerNormalization(self: Lowering, node: Node):
+    from ..ops import transformer as T
+    x_name = node.inputs[0]
+    shp = self.info.shapes[x_name]
+    axis = node.attr("axis", -1)
+    if axis not in (-1, len(shp) - 1) or shp[-1] % 8 != 0:
+        return False
+    c, rows = shp[-1], _rows_of(shp)
+    x2 = self.rows_view(x_name, rows, c)
+    gamma = self.const_f32(node.inputs[1]).float().contiguous() if len(node.inputs) > 1 and node.inputs[1] else None
+    beta = self.const_f32(node.inputs[2]).float().contiguous() if len(node.inputs) > 2 and node.inputs[2] else None
+    y = torch.zeros(rows, c, dtype=self.dtype, device=self.device)
+    op = T.layernorm(x2, y, gamma, beta, rows=rows, c=c, eps=node.attr("epsilon", 1e-5), x_ld=x2.stride(0), y_ld=c)
+    self.plan.add_native(op, node)
+    op.launch()
+    self.vals[node.outputs[0]] = Val(y.unflatten(0, shp[:-1]), False)
+
+
+def _lower_EmbedLayerNorm(self: Lowering, node: Node):
+    from ..ops import transformer as T
+    k = node.attr("num_tables")
+    ids_names, tab_names = node.inputs[:k], node.inputs[k:2 * k]
+    gamma, beta = self.const_f32(node.inputs[2 * k]), self.const_f32(node.inputs[2 * k + 1])
+    out_shape = self.info.shapes[node.outputs[0]]
+    c, rows = out_shape[-1], _rows_of(out_shape)
+    if c % 8 != 0 or c > 1536 or k > 4:
+        return False
+    seq = out_shape[-2]
+    ids: List[Optional[torch.Tensor]] = []
+    for nm in ids_names:
+        if nm in self.g.initializers:
+            arr = self.g.initializers[nm].reshape(-1)
+            # constant position ids 0..S-1 (broadcast over the batch) become the implicit index
+            if arr.size == seq and np.array_equal(arr, np.arange(seq)):
+                ids.append(None)
+                continue
+            full = np.broadcast_to(self.g.initializers[nm], out_shape[:-1]).reshape(-1)
+            ids.append(torch.from_numpy(np.ascontiguousarray(full)).long().to(self.device))
+            continue
+        v = self.get(nm).t
+        if v.dtype != torch.int64 or not v.is_contiguous() or v.numel() != rows:
+            buf = torch.zeros(rows, dtype=torch.int64, device=self.device)
+            src = v
+            shape_b = out_shape[:-1]
+
+            def cp(src=src, buf=buf, shape_b=shape_b):
+                buf.copy_(src.expand(shape_b).reshape(-1))
+            self.plan.add_py(cp, f"ids_i64({nm})", node)
+            cp()
+            v = buf
+        ids.append(v.reshape(-1))
+    tabs = []
+    for nm in tab_names:
+        key = (nm, "emb")
+        if key not in self.packed:
+            self.packed[key] = self.const_f32(nm).to(self.dtype).contiguous()
+        tabs.append(self.packed[key])
+    y = torch.zeros(rows, c, dtype=self.dtype, device=self.device)
+    op = T.embed_layernorm(ids, tabs, y, gamma, beta, rows=rows, c=c, seq=seq, eps=node.attr("epsilon", 1e-5))
+    self.plan.add_native(op, node)
+    op.launch()
+    self.vals[node.outputs[0]] = Val(y.unflatten(0, out_shape[:-1]), False)
+
+
+def _lower_Attention(self: Lowering, node: Node):
+    from ..ops.transformer import Attention
+    shp = self.info.shapes[node.inputs[0]]
+    if len(shp) != 3:
+        return False
+    b, s, hd = shp
+    heads = node.attr("num_heads")
+    d = hd // heads
+    if d % 8 != 0 or s > 1024:
+        return False
+
+    def view3(name):
+        v = self.get(name).t
+        if v.dtype == self.dtype and v.dim() == 3 and v.stride(2) == 1 and v.stride(1) % 8 == 0 \
+                and v.data_ptr() % 16 == 0:
+            return v
+        return self.rows_view(name, b * s, hd).unflatten(0, (b, s))
+    q, k, v = view3(node.inputs[0]), view3(node.inputs[1]), view3(node.inputs[2])
+    mask = None
+    if len(node.inputs) > 3 and node.inputs[3]:
+        mshape = self.info.shapes[node.inputs[3]]
+        if int(np.prod(mshape)) not in (b * s, b * s * s):
+            return False
+        mv = self.as_torch(node.inputs[3])
+        mask = torch.zeros(mshape, dtype=torch.float32, device=self.device)
+        src = mv
+
+        def cpm(src=src, mask=mask):
+            mask.copy_(src)
+        self.plan.add_py(cpm, "attn_mask_f32", node)
+        cpm()
+    out = torch.zeros(b, s, hd, dtype=self.dtype, device=self.device)
+    att = Attention(q, k, v, out, heads=heads, scale=node.attr("scale", 1.0 / math.sqrt(d)), mask=mask,
+                    status=self.plan.status)
+    for op in att.ops:
+        self.plan.add_native(op, node)
+        op.launch()
+    self.plan.extra.setdefault("attention", []).append(att)
+    self.vals[node.outputs[0]] = Val(out, False)
+
+
+def _lower_Gelu(self: Lowering, node: Node):
+    if node.attr("approximate", "none") == "tanh":
+        return False
+    shp = self.info.shapes[node.inputs[0]]
+    if shp[-1] % 8 != 0:
+        return False
+    rows, c = _rows_of(shp), shp[-1]
+    x2 = self.rows_view(node.inputs[0], rows, c)
+    y = torch.zeros(rows, c, dtype=self.dtype, device=self.device)
+    op = K.unary(x2, y, rows=rows, c=c, act="gelu", x_ld=x2.stride(0), y_ld=c)
+    self.plan.add_native(op, node)
+    op.launch()
+    self.vals[node.outputs[0]] = Val(y.unflatten(0, shp[:-1]), False)
+
+
+Lowering.lower_LayerNormalization = _lower_LayerNormalization
+Lowering.lower_EmbedLayerNorm = _lower_EmbedLayerNorm
+Lowering.lower_Attention = _lower_Attention
+Lowering.lower_Gelu = _lower_Gelu

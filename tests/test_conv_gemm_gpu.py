@@ -174,3 +174,28 @@ def test_conv3x3_halo_kernel(cfg):
         op.launch()
     op.status.check()
     _check(y, _ref_conv(x, w, b, 1, 1, act, res, 2))
+
+
+@pytest.mark.parametrize("y_tma_mode", [0, 1])
+@pytest.mark.parametrize("cfg", [(2, 20, 20, 64, 192, 3), (1, 33, 47, 32, 40, 3), (2, 16, 16, 128, 320, 1),
+                                 (2, 24, 24, 64, 68, 3), (1, 40, 40, 96, 96, 3)])
+def test_conv_output_paths_agree(cfg, y_tma_mode):
+    """Direct 16-byte stores and staged TMA tensor stores (ragged tiles, channel tails, concat slices)."""
+    from fastdeploy_b200.ops.conv_gemm import ConvGemm, pack_conv_weight
+    n, h, w_, cin, cout, k = cfg
+    torch.manual_seed(8)
+    x = (torch.randn(n, h, w_, cin, device="cuda") * 0.5).half()
+    w = (torch.randn(cout, cin, k, k, device="cuda") * (1.0 / (cin * k * k) ** 0.5)).half()
+    b = torch.randn(cout, device="cuda") * 0.1
+    total = (cout + 7) // 8 * 8 + 64
+    ybuf = torch.zeros(n, h, w_, total, device="cuda", dtype=torch.float16)
+    res = (torch.randn(n, h, w_, cout, device="cuda") * 0.5).half()
+    op = ConvGemm(x, pack_conv_weight(w, torch.float16), ybuf[..., 64:64 + cout], in_shape=(n, h, w_, cin),
+                  out_hw=(h, w_), cout=cout, kernel=(k, k), stride=1, pad=(k // 2, k // 2), bias=b, residual=res,
+                  res_mode=2, act="silu", y_ld=total, y_tma_mode=y_tma_mode)
+    for _ in range(3):
+        op.launch()
+    op.status.check()
+    _check(ybuf[..., 64:64 + cout], _ref_conv(x, w, b, 1, k // 2, "silu", res, 2))
+    assert float(ybuf[..., :64].abs().max()) == 0.0
+    assert float(ybuf[..., 64 + cout:].abs().max()) == 0.0

@@ -80,3 +80,32 @@ def test_ppyoloe_tiny_matches_interpreter(with_nms):
             k = min(len(got), len(want), 10)
             # the strongest detections agree
             assert np.allclose(np.sort(got[:, 1])[::-1][:k], np.sort(want[:, 1])[::-1][:k], atol=2e-2)
+
+
+@pytest.mark.parametrize("task", ["seq_cls", "uie"])
+def test_ernie_tiny_matches_interpreter(task):
+    from fastdeploy_b200.importer.paddle_import import load_paddle
+    from fastdeploy_b200.ir.interp import Interpreter
+    from fastdeploy_b200.models.ernie import build_ernie
+    from fastdeploy_b200.runtime.native_backend import build_plan
+    g = load_paddle(*build_ernie("tiny", task).serialize())
+    B, S = 3, 24
+    rng = np.random.RandomState(0)
+    ids = rng.randint(1, 1000, (B, S)).astype(np.int64)
+    ids[1, 15:] = 0
+    feeds = {"input_ids": ids, "token_type_ids": rng.randint(0, 2, (B, S)).astype(np.int64)}
+    if task == "uie":
+        feeds["pos_ids"] = np.tile(np.arange(S), (B, 1)).astype(np.int64)
+        feeds["att_mask"] = (ids != 0).astype(np.int64)
+    ref = Interpreter(g).run(feeds)
+    plan = build_plan(g, {k: list(v.shape) for k, v in feeds.items()}, "cuda:0", dtype=torch.bfloat16)
+    _feed(plan, feeds)
+    plan.run()
+    torch.cuda.synchronize()
+    plan.status.check()
+    for k, r in ref.items():
+        out = plan.outputs[k].logical().float().cpu()
+        assert out.shape == r.shape
+        assert (out - r).abs().max().item() < 3e-2
+    names = [s.name for s in plan.steps]
+    assert any(n.startswith("attn_qk") for n in names) and any(n == "layernorm" for n in names)
