@@ -64,6 +64,7 @@ struct ConvGemmDesc {
   // elements between image rows (0 = W * ld): lets heads of a [B, S, H*D] tensor act as image rows
   long long x_h_stride, y_h_stride, res_h_stride;
   int y_tma_mode;        // -1/1: TMA tensor stores for 16-bit outputs when possible, 0: direct stores
+  long long* trace;      // optional device buffer of 48*8 int64 for the timeline probe (null = off)
 };
 
 struct ConvGemmParams {
@@ -84,7 +85,16 @@ struct ConvGemmParams {
   long long y_h_stride, res_h_stride;
   int b_batched;
   int y_tma;   // 16-bit output leaves through shared-memory staging + TMA tensor stores
+  long long* trace;  // optional: CTA 0 records clock64() at pipeline events of its first tiles
 };
+
+// Timeline probe for tuning: slot layout [tile][8]: 0 producer issue, 1 MMA got accumulator,
+// 2 MMA first operands ready, 3 MMA committed, 4 epilogue saw accumulator, 5 epilogue TMEM read done,
+// 6 epilogue released accumulator, 7 epilogue store issued.
+constexpr int kTraceTiles = 48;
+__device__ __forceinline__ void trace_mark(const ConvGemmParams& p, int local_tile, int slot) {
+  if (p.trace != nullptr && blockIdx.x == 0 && local_tile < kTraceTiles) p.trace[local_tile * 8 + slot] = clock64();
+}
 
 // Generic activation (runtime code); the hot ones have dedicated template paths.
 __device__ __forceinline__ void apply_act8(float (&x)[8], int act, float alpha, float beta) {
@@ -346,6 +356,7 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
     asm volatile("bar.sync 1, 256;" ::: "memory");
     if (*abort_sample != 0) break;
     tc_fence_after();
+    if (issuer) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 4);
     const int row = q * 32 + lane;
     const int rh = row / p.tw, rw = row - rh * p.tw;
     const int oh = thi * p.th + rh, ow = twi * p.tw + rw;
@@ -377,9 +388,11 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
         }
       }
       if (blk == nblk - 1) {        // last TMEM read of this accumulator
+        if (issuer) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 5);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty0 + 8u * acc);
+        if (issuer) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 6);
       }
       fence_proxy_async_smem();
       asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -390,6 +403,7 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
             "r"(buf), "r"(colbase + blk * 64), "r"(twi * p.tw), "r"(thi * p.th), "r"(img)
             : "memory");
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        if (blk == nblk - 1) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 7);
       }
     }
     acc ^= 1;
@@ -713,6 +727,7 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int kb = 0; ok && kb < slabs; ++kb) {
           if (!mbar_wait(a_empty(sa), pa ^ 1, abort_flag, kStatusTimeoutProducer)) { ok = false; break; }
           mbar_arrive_expect_tx(a_full(sa), halo_bytes);
+          if (kb == 0) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 0);
           tma_load_4d(a0 + sa * kHaloABytes, &tmA, a_full(sa), kb * kBK, twi * kHaloTw - 1, thi * kHaloTh - 1, img);
           if (++sa == SA) { sa = 0; pa ^= 1; }
           if (hp.b_resident && !first) continue;
@@ -741,9 +756,11 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
         if (!mbar_wait(tempty0 + 8u * acc, acc_ph ^ 1, abort_flag, kStatusTimeoutMma)) break;
         tc_fence_after();
+        trace_mark(p, (tile - blockIdx.x) / gridDim.x, 1);
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; ok && kb < slabs; ++kb) {
           if (!mbar_wait(a_full(sa), pa, abort_flag, kStatusTimeoutMma)) { ok = false; break; }
+          if (kb == 0) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 2);
           const uint32_t a_base = a0 + sa * kHaloABytes;
           for (int tap = 0; tap < 9; ++tap) {
             if (hp.b_resident) sb = kb * 9 + tap;
@@ -768,6 +785,7 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         if (!ok) break;
         umma_commit(tfull0 + 8u * acc);
+        trace_mark(p, (tile - blockIdx.x) / gridDim.x, 3);
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1;
       }
@@ -976,6 +994,7 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   p.KH = d->KH; p.KW = d->KW; p.stride = d->stride; p.pad_h = d->pad_h; p.pad_w = d->pad_w;
   p.act = d->act; p.act_alpha = d->act_alpha; p.act_beta = d->act_beta;
   p.b_batched = d->w_batched ? 1 : 0;
+  p.trace = d->trace;
   p.y_h_stride = d->y_h_stride > 0 ? d->y_h_stride : static_cast<long long>(d->Wo) * d->y_ld;
   p.res_h_stride = d->res_h_stride > 0 ? d->res_h_stride : static_cast<long long>(d->Wo) * d->res_ld;
   p.y_n_stride = d->y_n_stride > 0 ? d->y_n_stride : static_cast<long long>(d->Ho) * d->Wo * d->y_ld;

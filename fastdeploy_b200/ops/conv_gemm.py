@@ -37,6 +37,7 @@ class _ConvGemmDesc(ctypes.Structure):
         ("w_n_stride", ctypes.c_longlong),
         ("x_h_stride", ctypes.c_longlong), ("y_h_stride", ctypes.c_longlong), ("res_h_stride", ctypes.c_longlong),
         ("y_tma_mode", ctypes.c_int),
+        ("trace", ctypes.c_void_p),
     ]
 
 
@@ -79,7 +80,7 @@ class ConvGemm(NativeOp):
                  max_ctas: int = 0, x_n_stride: int = 0, y_n_stride: int = 0, res_n_stride: int = 0,
                  halo_mode: int = -1, w_batched: bool = False, w_ld: int = 0, w_h_stride: int = 0,
                  w_n_stride: int = 0, x_h_stride: int = 0, y_h_stride: int = 0, res_h_stride: int = 0,
-                 y_tma_mode: int = -1, name: str = "conv_gemm"):
+                 y_tma_mode: int = -1, trace: Optional[torch.Tensor] = None, name: str = "conv_gemm"):
         n, h, w_, cin = in_shape
         d = _ConvGemmDesc()
         self.status = status or StatusWord(x.device)
@@ -102,6 +103,8 @@ class ConvGemm(NativeOp):
         d.w_batched, d.w_ld, d.w_h_stride, d.w_n_stride = int(w_batched), w_ld, w_h_stride, w_n_stride
         d.x_h_stride, d.y_h_stride, d.res_h_stride = x_h_stride, y_h_stride, res_h_stride
         d.y_tma_mode = y_tma_mode
+        d.trace = trace.data_ptr() if trace is not None else None
+        self.trace = trace
         if bias is not None:
             assert bias.dtype == torch.float32
         if residual is not None:

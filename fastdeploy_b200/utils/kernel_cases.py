@@ -1,0 +1,84 @@
+"""Single-kernel cases for timing and for profiler captures.
+
+    python -m fastdeploy_b200.utils.kernel_cases conv --n 16 --hw 160 --cin 48 --cout 48 --k 3
+    python -m fastdeploy_b200.utils.kernel_cases gemm --m 8192 --k 4096 --n 4096
+
+Each run launches the kernel ``--iters`` times after ``--warmup`` launches, times it with CUDA events
+and prints one JSON line (time, TFLOP/s, bytes moved, fraction of the measured peaks when
+``MEASURED_PEAKS.json`` sits in the working directory).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+
+def main(argv=None) -> int:
+    import torch
+    from ..ops.conv_gemm import ConvGemm, pack_conv_weight, pack_linear_weight
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kind", choices=["conv", "gemm"])
+    ap.add_argument("--n", type=int, default=16)
+    ap.add_argument("--hw", type=int, default=160)
+    ap.add_argument("--cin", type=int, default=48)
+    ap.add_argument("--cout", type=int, default=48)
+    ap.add_argument("--k", type=int, default=3)
+    ap.add_argument("--stride", type=int, default=1)
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--act", default="silu")
+    ap.add_argument("--dtype", default="fp16")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--halo", type=int, default=-1)
+    ap.add_argument("--block-n", type=int, default=0)
+    ap.add_argument("--y-tma", type=int, default=-1)
+    a = ap.parse_args(argv)
+    dt = torch.float16 if a.dtype == "fp16" else torch.bfloat16
+    dev = "cuda"
+    if a.kind == "conv":
+        n, h, cin, cout, k, s = a.n, a.hw, a.cin, a.cout, a.k, a.stride
+        p = k // 2
+        ho = (h + 2 * p - k) // s + 1
+        x = (torch.randn(n, h, h, cin, device=dev) * 0.5).to(dt)
+        w = (torch.randn(cout, cin, k, k, device=dev) * 0.05).to(dt)
+        b = torch.randn(cout, device=dev)
+        y = torch.empty(n, ho, ho, cout, device=dev, dtype=dt)
+        op = ConvGemm(x, pack_conv_weight(w, dt), y, in_shape=(n, h, h, cin), out_hw=(ho, ho), cout=cout,
+                      kernel=(k, k), stride=s, pad=(p, p), bias=b, act=a.act if a.act != "none" else None,
+                      halo_mode=a.halo, block_n=a.block_n, y_tma_mode=a.y_tma)
+        flops = 2.0 * n * ho * ho * cout * cin * k * k
+        nbytes = x.numel() * 2 + y.numel() * 2 + w.numel() * 2
+    else:
+        m, kk, nn = a.m, a.k if a.k > 8 else 4096, a.n if a.n > 16 else 4096
+        x = (torch.randn(m, kk, device=dev) * 0.5).to(dt)
+        w = (torch.randn(nn, kk, device=dev) * 0.05).to(dt)
+        y = torch.empty(m, nn, device=dev, dtype=dt)
+        op = ConvGemm(x, pack_linear_weight(w, dt), y, in_shape=(1, 1, m, kk), out_hw=(1, m), cout=nn,
+                      block_n=a.block_n, y_tma_mode=a.y_tma)
+        flops = 2.0 * m * kk * nn
+        nbytes = (x.numel() + y.numel() + w.numel()) * 2
+    for _ in range(a.warmup):
+        op.launch()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.iters):
+        op.launch()
+    e1.record()
+    torch.cuda.synchronize()
+    op.status.check()
+    ms = e0.elapsed_time(e1) / a.iters
+    out = {"case": vars(a), "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
+           "gbytes_per_s": round(nbytes / ms / 1e6, 1), "info": op.info()}
+    if os.path.exists("MEASURED_PEAKS.json"):
+        pk = json.load(open("MEASURED_PEAKS.json"))
+        out["frac_of_measured_bf16_peak"] = round(out["tflops"] / pk["bf16_tflops"], 3)
+        out["frac_of_measured_hbm"] = round(out["gbytes_per_s"] / pk["hbm_gbs"], 3)
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -198,4 +198,5 @@ def test_conv_output_paths_agree(cfg, y_tma_mode):
     op.status.check()
     _check(ybuf[..., 64:64 + cout], _ref_conv(x, w, b, 1, k // 2, "silu", res, 2))
     assert float(ybuf[..., :64].abs().max()) == 0.0
-    assert float(ybuf[..., 64 + cout:].abs().max()) == 0.0
+    if ybuf.shape[-1] > 64 + cout:
+        assert float(ybuf[..., 64 + cout:].abs().max()) == 0.0
