@@ -596,35 +596,38 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the loops (so addresses and descriptors stay warp-uniform); one elected
+    // lane issues the MMAs and the commits.
+    {
       int s = 0;
       uint32_t ph = 0;
       int acc = 0;
       uint32_t acc_ph = 0;
       bool ok = true;
+      const uint64_t desc_hi = make_kmajor_desc(0, 128);
       for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-        if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, kStatusTimeoutMma)) break;
+        if (!mbar_wait_warp(tempty_bar(acc), acc_ph ^ 1, abort_flag, kStatusTimeoutMma)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int k = 0; k < p.k_iters; ++k) {
-          if (!mbar_wait(full_bar(s), ph, abort_flag, kStatusTimeoutMma)) {
+          if (!mbar_wait_warp(full_bar(s), ph, abort_flag, kStatusTimeoutMma)) {
             ok = false;
             break;
           }
           tc_fence_after();
           const uint32_t a_addr = tile0 + s * Cfg::kStageBytes;
-          const uint64_t adesc = make_kmajor_desc(a_addr, 128);
-          const uint64_t bdesc = make_kmajor_desc(a_addr + Cfg::kABytes, 128);
-#pragma unroll
-          for (int kk = 0; kk < kBK / 16; ++kk) {
-            // +32 bytes per 16-element K step inside the 128-byte swizzle atom
-            umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, p.idesc, (k | kk) != 0 ? 1u : 0u);
+          const uint64_t adesc = desc_hi | ((a_addr & 0x3FFFF) >> 4);
+          const uint64_t bdesc = desc_hi | (((a_addr + Cfg::kABytes) & 0x3FFFF) >> 4);
+          if (elect_one()) {
+            umma_f16_kblock(d_tmem, adesc, bdesc, p.idesc, k != 0 ? 1u : 0u);
+            umma_commit(empty_bar(s));
           }
-          umma_commit(empty_bar(s));
+          __syncwarp();
           if (++s == S) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
-        umma_commit(tfull_bar(acc));
+        if (elect_one()) umma_commit(tfull_bar(acc));
+        __syncwarp();
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1;
       }
@@ -677,7 +680,7 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   const int SA = hp.a_stages, SB = hp.b_stages;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SA * kHaloABytes + SB * kBBytes + kStagingBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SA * kHaloABytes + SB * 3 * kBBytes + kStagingBytes);
   // bars: a_full[SA] a_empty[SA] b_full[SB] b_empty[SB] tfull[2] tempty[2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SA + 2 * SB + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -731,12 +734,16 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tma_load_4d(a0 + sa * kHaloABytes, &tmA, a_full(sa), kb * kBK, twi * kHaloTw - 1, thi * kHaloTh - 1, img);
           if (++sa == SA) { sa = 0; pa ^= 1; }
           if (hp.b_resident && !first) continue;
-          for (int tap = 0; tap < 9; ++tap) {
+          // weights travel one filter row (3 taps) per stage
+          for (int kh = 0; kh < 3; ++kh) {
             if (!hp.b_resident) {
               if (!mbar_wait(b_empty(sb), pb ^ 1, abort_flag, kStatusTimeoutProducer)) { ok = false; break; }
             }
-            mbar_arrive_expect_tx(b_full(sb), kBBytes);
-            tma_load_2d(b0 + sb * kBBytes, &tmB, b_full(sb), (tap * slabs + kb) * kBK, n_tile * BN);
+            mbar_arrive_expect_tx(b_full(sb), 3 * kBBytes);
+#pragma unroll
+            for (int kw = 0; kw < 3; ++kw)
+              tma_load_2d(b0 + sb * (3 * kBBytes) + kw * kBBytes, &tmB, b_full(sb),
+                          ((kh * 3 + kw) * slabs + kb) * kBK, n_tile * BN);
             if (++sb == SB) { sb = 0; pb ^= 1; }
           }
         }
@@ -749,49 +756,62 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
       int sa = 0, sb = 0, acc = 0;
       uint32_t pa = 0, pb = 0, acc_ph = 0;
-      bool ok = true;
+      bool ok = true, weights_ready = false;
+      const uint64_t bdesc_hi = make_kmajor_desc(0, 128);
+      // shifted views of the halo patch: 8-row groups are 10 pixel rows (1280 bytes) apart
+      const uint64_t adesc_hi = (bdesc_hi & ~(0x3FFFull << 32)) | (static_cast<uint64_t>((kHaloCols * 128) >> 4) << 32);
       for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-        if (!mbar_wait(tempty0 + 8u * acc, acc_ph ^ 1, abort_flag, kStatusTimeoutMma)) break;
+        if (!mbar_wait_warp(tempty0 + 8u * acc, acc_ph ^ 1, abort_flag, kStatusTimeoutMma)) break;
         tc_fence_after();
-        trace_mark(p, (tile - blockIdx.x) / gridDim.x, 1);
+        if (lane == 0) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 1);
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; ok && kb < slabs; ++kb) {
-          if (!mbar_wait(a_full(sa), pa, abort_flag, kStatusTimeoutMma)) { ok = false; break; }
-          if (kb == 0) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 2);
+          if (!mbar_wait_warp(a_full(sa), pa, abort_flag, kStatusTimeoutMma)) { ok = false; break; }
+          tc_fence_after();
+          if (kb == 0 && lane == 0) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 2);
           const uint32_t a_base = a0 + sa * kHaloABytes;
-          for (int tap = 0; tap < 9; ++tap) {
-            if (hp.b_resident) sb = kb * 9 + tap;
-            if (!mbar_wait(b_full(sb), hp.b_resident ? 0u : pb, abort_flag, kStatusTimeoutMma)) { ok = false; break; }
-            tc_fence_after();
-            const int kh = tap / 3, kw = tap - kh * 3;
-            // shifted view of the halo patch: start (kh*10 + kw) pixel rows in, 8-row groups 10 rows apart
-            uint64_t adesc = make_kmajor_desc(a_base + (kh * kHaloCols + kw) * 128, 128);
-            adesc = (adesc & ~(0x3FFFull << 32)) | (static_cast<uint64_t>((kHaloCols * 128) >> 4) << 32);
-            const uint64_t bdesc = make_kmajor_desc(b0 + sb * kBBytes, 128);
-#pragma unroll
-            for (int kk = 0; kk < kBK / 16; ++kk)
-              umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, p.idesc, (kb | tap | kk) != 0 ? 1u : 0u);
+#pragma unroll 1
+          for (int kh = 0; kh < 3; ++kh) {
+            if (hp.b_resident) sb = kb * 3 + kh;
+            if (!(hp.b_resident && weights_ready)) {
+              if (!mbar_wait_warp(b_full(sb), hp.b_resident ? 0u : pb, abort_flag, kStatusTimeoutMma)) { ok = false; break; }
+              tc_fence_after();
+            }
+            // tap (kh, kw) starts (kh*10 + kw) pixel rows into the patch
+            const uint32_t a_row = a_base + kh * kHaloCols * 128;
+            const uint32_t b_row = b0 + sb * (3 * kBBytes);
+            const uint64_t ad0 = adesc_hi | ((a_row & 0x3FFFF) >> 4);
+            const uint64_t bd0 = bdesc_hi | ((b_row & 0x3FFFF) >> 4);
+            if (elect_one()) {
+              umma_f16_kblock(d_tmem, ad0, bd0, p.idesc, (kb | kh) != 0 ? 1u : 0u);
+              umma_f16_kblock(d_tmem, ad0 + (128 >> 4), bd0 + (kBBytes >> 4), p.idesc, 1u);
+              umma_f16_kblock(d_tmem, ad0 + (256 >> 4), bd0 + (2 * kBBytes >> 4), p.idesc, 1u);
+              if (!hp.b_resident) umma_commit(b_empty(sb));
+            }
+            __syncwarp();
             if (!hp.b_resident) {
-              umma_commit(b_empty(sb));
               if (++sb == SB) { sb = 0; pb ^= 1; }
             }
           }
           if (!ok) break;
-          umma_commit(a_empty(sa));
+          if (elect_one()) umma_commit(a_empty(sa));
+          __syncwarp();
           if (++sa == SA) { sa = 0; pa ^= 1; }
         }
         if (!ok) break;
-        umma_commit(tfull0 + 8u * acc);
-        trace_mark(p, (tile - blockIdx.x) / gridDim.x, 3);
+        if (elect_one()) umma_commit(tfull0 + 8u * acc);
+        __syncwarp();
+        weights_ready = true;
+        if (lane == 0) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 3);
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1;
       }
     }
   } else if (p.y_tma) {
-    epilogue_loop_tma<BN, ACT>(p, &tmY, b0 + SB * kBBytes, tmem_base, tfull0, tempty0, abort_flag, warp, lane);
+    epilogue_loop_tma<BN, ACT>(p, &tmY, b0 + SB * 3 * kBBytes, tmem_base, tfull0, tempty0, abort_flag, warp, lane);
   } else {
     epilogue_loop<BN, ACT>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane);
   }
@@ -1013,8 +1033,8 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   op->grid = std::max(grid, 1);
   if (op->halo) {
     const int budget = kMaxSmem - 1024 - kHaloBarBytes - kStagingBytes;
-    const int b_bytes = bn * kBK * 2;
-    const int all_b = 9 * p.kb_per_tap;
+    const int b_bytes = 3 * bn * kBK * 2;          // one filter row (3 taps) per weight stage
+    const int all_b = 3 * p.kb_per_tap;
     HaloParams hp{};
     // Activation patches come from DRAM, weights from L2: bytes in flight matter for the patches,
     // so they get the deeper ring.
@@ -1024,11 +1044,11 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
       hp.a_stages = std::min(kHaloMaxA, (budget - all_b * b_bytes) / kHaloABytes);
     } else {
       hp.b_resident = 0;
-      hp.b_stages = std::max(3, std::min(kHaloMaxB, (budget / 2) / b_bytes));
+      hp.b_stages = std::max(2, std::min(kHaloMaxB, (budget / 2) / b_bytes));
       hp.a_stages = std::min(kHaloMaxA, (budget - hp.b_stages * b_bytes) / kHaloABytes);
       if (hp.a_stages < 2) { hp.a_stages = 2; hp.b_stages = (budget - 2 * kHaloABytes) / b_bytes; }
     }
-    if (hp.b_stages < 3) {
+    if (hp.b_stages < 2) {
       if (d->halo_mode == 1) { set_error("conv_gemm: halo kernel does not fit shared memory"); delete op; return nullptr; }
       op->halo = 0;   // fall back to the generic kernel with its own tile choice
       choose_tile(d->Ho, d->Wo, d->stride, &tw, &th);

@@ -86,6 +86,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Same wait executed by a fully converged warp; the verdict is made warp-uniform so that the
+// lanes never part ways before a later elect.sync / __syncwarp.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               int code) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, code);
+  return __all_sync(0xffffffffu, ok) != 0;
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
@@ -142,6 +150,46 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// One elected lane of a fully converged warp (the same lane every time while all 32 are active).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, P;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// The four K=16 steps of one 64-element K block in a single instruction group: the descriptors of
+// steps 1..3 are the first one advanced by 32 bytes each (+2 in the 16-byte address field). Keeping
+// this in one asm block keeps the issuing thread's instruction count per MMA small, which is what
+// bounds the rate for narrow tiles.
+__device__ __forceinline__ void umma_f16_kblock(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                                uint32_t idesc, uint32_t accumulate_first) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p0, p1;\n"
+      ".reg .b64 a1, a2, a3, b1, b2, b3;\n"
+      "setp.ne.b32 p0, %4, 0;\n"
+      "setp.eq.u32 p1, %3, %3;\n"
+      "add.s64 a1, %1, 2;\n"
+      "add.s64 b1, %2, 2;\n"
+      "add.s64 a2, %1, 4;\n"
+      "add.s64 b2, %2, 4;\n"
+      "add.s64 a3, %1, 6;\n"
+      "add.s64 b3, %2, 6;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, p1;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, p1;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, p1;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate_first)
+      : "memory");
+}
+
 // kind::f8f6f4: e4m3 / e5m2 inputs, fp32 accumulate, K = 32 per instruction.
 __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
                                         uint32_t idesc, uint32_t accumulate) {

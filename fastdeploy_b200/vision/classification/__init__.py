@@ -1,0 +1,156 @@
+"""``fastdeploy.vision.classification``: PaddleClas models (any PaddleClas export incl. ViT), torchvision-style
+ResNet, YOLOv5Cls, PP-ShiTuV2 recogniser (fastdeploy/vision/classification/**)."""
+from __future__ import annotations
+
+from typing import Any, Dict, List, Optional, Sequence
+
+import numpy as np
+import yaml
+
+from ...core.types import ModelFormat
+from ...runtime.model import FastDeployModel
+from ...runtime.option import RuntimeOption
+from ..common.processors import (BGR2RGB, Cast, CenterCrop, HWC2CHW, Normalize, ProcessorManager, Resize,
+                                 ResizeByShort, fuse_transforms)
+from ..result import ClassifyResult
+from ..utils import l2_normalize, topk_indices
+
+
+class PaddleClasPreprocessor(ProcessorManager):
+    """``inference_cls.yaml`` ``PreProcess.transform_ops``: ResizeImage{resize_short|size}, CropImage{size},
+    NormalizeImage{mean,std,scale}, ToCHWImage (fastdeploy/vision/classification/ppcls/preprocessor.cc:40-95)."""
+
+    def __init__(self, config_file: str):
+        super().__init__()
+        with open(config_file) as f:
+            cfg = yaml.safe_load(f)
+        ops = cfg["PreProcess"]["transform_ops"]
+        procs = [BGR2RGB()]
+        self.disable_normalize_ = False
+        self.disable_permute_ = False
+        for op in ops:
+            (name, args), = op.items()
+            args = args or {}
+            if name == "ResizeImage":
+                if "resize_short" in args:
+                    procs.append(ResizeByShort(int(args["resize_short"]), 1, False))
+                else:
+                    size = args["size"]
+                    size = [size, size] if isinstance(size, int) else size
+                    procs.append(Resize(int(size[0]), int(size[1])))
+            elif name == "CropImage":
+                size = args["size"]
+                size = [size, size] if isinstance(size, int) else size
+                procs.append(CenterCrop(int(size[0]), int(size[1])))
+            elif name == "NormalizeImage":
+                procs.append(Normalize(list(args["mean"]), list(args["std"]), True))
+            elif name == "ToCHWImage":
+                procs.append(HWC2CHW())
+            else:
+                raise ValueError(f"Unexcepted preprocess operator: {name}.")
+        self.processors = fuse_transforms(procs)
+
+    def run(self, images):
+        return super().run([np.asarray(im) for im in images])
+
+
+class PaddleClasPostprocessor:
+    """Top-k WITHOUT softmax (fastdeploy/vision/classification/ppcls/postprocessor.cc:27-49)."""
+
+    def __init__(self, topk: int = 1):
+        self.topk = topk
+
+    def run(self, tensors: Sequence[np.ndarray]) -> List[ClassifyResult]:
+        scores = np.asarray(tensors[0], np.float32)
+        scores = scores.reshape(scores.shape[0], -1)
+        out = []
+        for row in scores:
+            idx = topk_indices(row, self.topk)
+            out.append(ClassifyResult(label_ids=idx, scores=[float(row[i]) for i in idx]))
+        return out
+
+
+class _ClsBase(FastDeployModel):
+    def _finish_init(self):
+        self.init_runtime()
+
+    def predict(self, im: np.ndarray, topk: int = 1) -> ClassifyResult:
+        self.postprocessor.topk = topk
+        return self.batch_predict([im])[0]
+
+    def batch_predict(self, images: Sequence[np.ndarray]) -> List[ClassifyResult]:
+        if self.runtime.on_gpu:
+            self.preprocessor.use_cuda(gpu_id=self.runtime_option.device_id)
+        x = self.preprocessor.run(images)[0]
+        name = self.runtime.graph.inputs[0].name
+        outs = self.infer({name: x})
+        first = self.runtime.graph.outputs[0].name
+        return self.postprocessor.run([self.runtime._to_numpy(outs[first])])
+
+    def get_preprocessor(self): return self.preprocessor
+    def get_postprocessor(self): return self.postprocessor
+
+
+class PaddleClasModel(_ClsBase):
+    def __init__(self, model_file: str, params_file: str, config_file: str,
+                 runtime_option: Optional[RuntimeOption] = None, model_format: ModelFormat = ModelFormat.PADDLE):
+        super().__init__(runtime_option)
+        self.runtime_option.set_model_path(model_file, params_file, model_format)
+        self.preprocessor = PaddleClasPreprocessor(config_file)
+        self.postprocessor = PaddleClasPostprocessor()
+        self._finish_init()
+
+
+class ResNet(_ClsBase):
+    """torchvision-style ONNX ResNet: resize -> BGR2RGB -> ImageNet mean/std -> CHW, softmax then top-k
+    (fastdeploy/vision/classification/contrib/resnet.cc)."""
+
+    def __init__(self, model_file: str, params_file: str = "", runtime_option: Optional[RuntimeOption] = None,
+                 model_format: ModelFormat = ModelFormat.ONNX):
+        super().__init__(runtime_option)
+        self.runtime_option.set_model_path(model_file, params_file, model_format)
+        self.size = [224, 224]
+        self.mean_vals = [0.485, 0.456, 0.406]
+        self.std_vals = [0.229, 0.224, 0.225]
+        self.preprocessor = ProcessorManager()
+        self._rebuild()
+        self.postprocessor = _SoftmaxTopK()
+        self._finish_init()
+
+    def _rebuild(self):
+        self.preprocessor.processors = fuse_transforms([
+            Resize(self.size[0], self.size[1]), BGR2RGB(), Normalize(self.mean_vals, self.std_vals), HWC2CHW()])
+
+
+class _SoftmaxTopK(PaddleClasPostprocessor):
+    def run(self, tensors):
+        x = np.asarray(tensors[0], np.float32)
+        x = x.reshape(x.shape[0], -1)
+        e = np.exp(x - x.max(1, keepdims=True))
+        return super().run([e / e.sum(1, keepdims=True)])
+
+
+class YOLOv5Cls(ResNet):
+    """YOLOv5 classification head: centre-crop resize to 224, ImageNet normalisation, softmax + top-k
+    (fastdeploy/vision/classification/contrib/yolov5cls)."""
+
+
+class PPShiTuV2Recognizer(_ClsBase):
+    """Feature extractor of PP-ShiTuV2: PaddleClas pre-processing, L2-normalised embedding in ``feature``."""
+
+    def __init__(self, model_file: str, params_file: str, config_file: str,
+                 runtime_option: Optional[RuntimeOption] = None, model_format: ModelFormat = ModelFormat.PADDLE):
+        super().__init__(runtime_option)
+        self.runtime_option.set_model_path(model_file, params_file, model_format)
+        self.preprocessor = PaddleClasPreprocessor(config_file)
+        self.feature_norm = True
+        self.postprocessor = self
+        self.topk = 1
+        self._finish_init()
+
+    def run(self, tensors):
+        feats = np.asarray(tensors[0], np.float32)
+        return [ClassifyResult(feature=l2_normalize(f) if self.feature_norm else f.tolist()) for f in feats]
+
+
+from ..detection.ppdet import PicoDet as PPShiTuV2Detector   # noqa: E402  (alias, as in the reference)

@@ -1,0 +1,130 @@
+"""Vision utilities (fastdeploy/vision/utils/utils.h:31-118): top-k, hard NMS, result sorting, L2 normalise,
+cosine similarity, five-point face alignment, crop-by-box, result -> JSON."""
+from __future__ import annotations
+
+import json
+from typing import Any, List, Sequence
+
+import numpy as np
+
+from .result import DetectionResult, FaceDetectionResult
+
+
+def topk_indices(scores: np.ndarray, k: int) -> List[int]:
+    """Repeated max scan like the reference (ties resolve to the lowest index)."""
+    s = np.asarray(scores, dtype=np.float64).copy()
+    k = min(k, s.size)
+    out = []
+    for _ in range(k):
+        i = int(np.argmax(s))
+        out.append(i)
+        s[i] = -np.inf
+    return out
+
+
+TopKIndices = topk_indices
+
+
+def _iou_one_to_many(b, boxes):
+    x1, y1 = np.maximum(b[0], boxes[:, 0]), np.maximum(b[1], boxes[:, 1])
+    x2, y2 = np.minimum(b[2], boxes[:, 2]), np.minimum(b[3], boxes[:, 3])
+    inter = np.maximum(x2 - x1, 0) * np.maximum(y2 - y1, 0)
+    a = (b[2] - b[0]) * (b[3] - b[1])
+    areas = (boxes[:, 2] - boxes[:, 0]) * (boxes[:, 3] - boxes[:, 1])
+    return inter / np.maximum(a + areas - inter, 1e-12)
+
+
+def nms(result, iou_threshold: float = 0.5) -> None:
+    """In-place hard NMS on a DetectionResult / FaceDetectionResult sorted by score
+    (fastdeploy/vision/utils/nms.cc:24-145)."""
+    if not result.boxes:
+        return
+    order = np.argsort(-np.asarray(result.scores), kind="stable")
+    boxes = np.asarray(result.boxes, np.float32)[order]
+    keep = []
+    suppressed = np.zeros(len(order), bool)
+    for i in range(len(order)):
+        if suppressed[i]:
+            continue
+        keep.append(i)
+        if i + 1 < len(order):
+            iou = _iou_one_to_many(boxes[i], boxes[i + 1:])
+            suppressed[i + 1:] |= iou > iou_threshold
+    idx = order[keep]
+    result.boxes = [result.boxes[i] for i in idx]
+    result.scores = [result.scores[i] for i in idx]
+    if isinstance(result, DetectionResult):
+        result.label_ids = [result.label_ids[i] for i in idx]
+    if isinstance(result, FaceDetectionResult) and result.landmarks_per_face > 0:
+        k = result.landmarks_per_face
+        result.landmarks = [result.landmarks[i * k + j] for i in idx for j in range(k)]
+
+
+NMS = nms
+
+
+def sort_detection_result(result: DetectionResult) -> None:
+    order = np.argsort(-np.asarray(result.scores), kind="stable")
+    result.boxes = [result.boxes[i] for i in order]
+    result.scores = [result.scores[i] for i in order]
+    result.label_ids = [result.label_ids[i] for i in order]
+
+
+def l2_normalize(values: Sequence[float]) -> List[float]:
+    v = np.asarray(values, np.float32)
+    n = float(np.sqrt((v * v).sum()))
+    return (v / max(n, 1e-12)).tolist()
+
+
+L2Normalize = l2_normalize
+
+
+def cosine_similarity(a: Sequence[float], b: Sequence[float], normalized: bool = True) -> float:
+    a, b = np.asarray(a, np.float32), np.asarray(b, np.float32)
+    if normalized:
+        a, b = np.asarray(l2_normalize(a)), np.asarray(l2_normalize(b))
+    return float((a * b).sum())
+
+
+CosineSimilarity = cosine_similarity
+
+ARCFACE_TEMPLATE = np.array([[38.2946, 51.6963], [73.5318, 51.5014], [56.0252, 71.7366], [41.5493, 92.3655],
+                             [70.7299, 92.2041]], np.float32)
+
+
+def align_face_with_five_points(image: np.ndarray, result: FaceDetectionResult, output_size=(112, 112)) -> List[np.ndarray]:
+    """Similarity transform of each face to the 112x112 five-point template."""
+    import cv2
+    out = []
+    if result.landmarks_per_face != 5:
+        return out
+    dst = ARCFACE_TEMPLATE * (np.asarray(output_size, np.float32) / 112.0)
+    for i in range(len(result.boxes)):
+        src = np.asarray(result.landmarks[i * 5:(i + 1) * 5], np.float32)
+        m, _ = cv2.estimateAffinePartial2D(src, dst, method=cv2.LMEDS)
+        out.append(cv2.warpAffine(image, m, tuple(output_size)))
+    return out
+
+
+def crop_image_by_box(image: np.ndarray, box: Sequence[float]) -> np.ndarray:
+    h, w = image.shape[:2]
+    x1, y1 = max(int(box[0]), 0), max(int(box[1]), 0)
+    x2, y2 = min(int(box[2]), w), min(int(box[3]), h)
+    return image[y1:y2, x1:x2].copy()
+
+
+def fd_result_to_json(result: Any) -> str:
+    """Result object -> JSON string (python/fastdeploy/vision/utils.py:137-172)."""
+    def conv(o):
+        if isinstance(o, (np.floating, np.integer)):
+            return o.item()
+        if isinstance(o, np.ndarray):
+            return o.tolist()
+        if hasattr(o, "__dict__"):
+            return {k: conv(v) for k, v in o.__dict__.items()}
+        if isinstance(o, (list, tuple)):
+            return [conv(v) for v in o]
+        return o
+    d = conv(result)
+    d["type"] = type(result).__name__
+    return json.dumps(d)
