@@ -154,3 +154,54 @@ class PaddleNet:
 
     def serialize(self) -> Tuple[bytes, bytes]:
         return self.b.serialize()
+
+
+# ---------------------------------------------------------------------- extra layers (OCR / mobile nets)
+def _pn_dwconv_bn_act(self, x, k, stride, act, name):
+    return self.conv_bn_act(x, x.c, k, stride, act, groups=x.c, name=name)
+
+
+def _pn_se(self, x, reduction=4, name="se", gate="hard_sigmoid"):
+    mid = max(8, x.c // reduction)
+    s = self.global_avgpool(x)
+    s = self.act(self.conv(s, mid, 1, 1, bias=True, name=name + ".conv1"), "relu")
+    s = self.act(self.conv(s, x.c, 1, 1, bias=True, name=name + ".conv2"), gate)
+    return self.mul(x, s)
+
+
+def _pn_deconv2x(self, x, cout, name, bias=True):
+    w = self.weight(name + ".w", (x.c, cout, 2, 2))
+    shape = [x.shape[0], cout, x.shape[2] * 2, x.shape[3] * 2]
+    y = self.b.op("conv2d_transpose", {"Input": [x.name], "Filter": [w]}, ("Output",), shape, strides=[2, 2],
+                  paddings=[0, 0], dilations=[1, 1], groups=1, padding_algorithm="EXPLICIT", data_format="NCHW",
+                  output_padding=[], output_size=[])
+    if bias:
+        bname = self.const_param(name + ".b", (0.1 * self.rng.standard_normal(cout)).astype("float32"))
+        y = self.b.op("elementwise_add", {"X": [y], "Y": [bname]}, ("Out",), shape, axis=1)
+    return Tensor(y, shape)
+
+
+def _pn_linear(self, x, cout, name, act=None):
+    cin = x.shape[-1]
+    w = self.weight(name + ".w", (cin, cout), scale=(1.0 / cin) ** 0.5)
+    bname = self.const_param(name + ".b", (0.02 * self.rng.standard_normal(cout)).astype("float32"))
+    shape = list(x.shape[:-1]) + [cout]
+    y = self.b.op("matmul_v2", {"X": [x.name], "Y": [w]}, ("Out",), shape, trans_x=False, trans_y=False)
+    y = self.b.op("elementwise_add", {"X": [y], "Y": [bname]}, ("Out",), shape, axis=-1)
+    return self.act(Tensor(y, shape), act)
+
+
+def _pn_layer_norm(self, x, name):
+    c = x.shape[-1]
+    g = self.const_param(name + ".w", (1.0 + 0.05 * self.rng.standard_normal(c)).astype("float32"))
+    bt = self.const_param(name + ".b", (0.02 * self.rng.standard_normal(c)).astype("float32"))
+    y = self.b.op("layer_norm", {"X": [x.name], "Scale": [g], "Bias": [bt]}, ("Y", "Mean", "Variance"), x.shape,
+                  begin_norm_axis=len(x.shape) - 1, epsilon=1e-6)
+    return Tensor(y, x.shape)
+
+
+PaddleNet.dwconv_bn_act = _pn_dwconv_bn_act
+PaddleNet.se = _pn_se
+PaddleNet.deconv2x = _pn_deconv2x
+PaddleNet.linear = _pn_linear
+PaddleNet.layer_norm = _pn_layer_norm
