@@ -341,20 +341,15 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
   int acc = 0;
   uint32_t acc_ph = 0;
   uint32_t blk_count = 0;
-  for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+  volatile int* abort_sample = abort_flag + 1;
+  bool aborted = false;
+  for (int tile = blockIdx.x; tile < p.total_tiles && !aborted; tile += gridDim.x) {
     const int n_tile = tile % p.n_tiles;
     int m_tile = tile / p.n_tiles;
     const int twi = m_tile % p.tiles_w; m_tile /= p.tiles_w;
     const int thi = m_tile % p.tiles_h;
     const int img = m_tile / p.tiles_h;
     mbar_wait(tfull0 + 8u * acc, acc_ph, abort_flag, kStatusTimeoutEpilogue);
-    // The warps meet at named barriers below, so they must all leave together: one thread samples
-    // the abort flag and everybody acts on that sample.
-    volatile int* abort_sample = abort_flag + 1;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    if (issuer) *abort_sample = *abort_flag;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    if (*abort_sample != 0) break;
     tc_fence_after();
     if (issuer) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 4);
     const int row = q * 32 + lane;
@@ -370,12 +365,19 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
     const int nblk = (col_limit - colbase + 63) / 64;
     for (int blk = 0; blk < nblk; ++blk, ++blk_count) {
       const uint32_t buf = stage0 + (blk_count & 1u) * kStageTileBytes;
-      if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-      asm volatile("bar.sync 1, 256;" ::: "memory");
       const int c = blk * 2 + half;                 // this warp's 32-column TMEM chunk
-      if (colbase + c * 32 < col_limit) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_row + c * 32, v);
+      const bool have_cols = colbase + c * 32 < col_limit;
+      uint32_t v[32];
+      if (have_cols) tmem_ld_32x32(t_row + c * 32, v);      // in flight across the barrier below
+      // The warps meet at named barriers, so they must all leave together: one thread samples the
+      // abort flag before the barrier and everybody acts on that sample after it.
+      if (issuer) {
+        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        *abort_sample = *abort_flag;
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (*abort_sample != 0) { aborted = true; break; }
+      if (have_cols) {
         tmem_ld_wait_dep(v);
         if (valid) {
           const uint32_t srow = buf + row * 128;

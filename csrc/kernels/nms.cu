@@ -136,9 +136,17 @@ __global__ void __launch_bounds__(kNmsThreads) nms_class_kernel(const NmsDesc d)
       __syncthreads();
       const uint32_t prefix = sel_prefix;
       const uint32_t mask_hi = shift == 24 ? 0u : (0xFFFFFFFFu << (shift + 8));
-      for (int m = tid; m < d.M; m += kNmsThreads) {
-        const uint32_t k = keys[m];
-        if (k != 0u && (k & mask_hi) == (prefix & mask_hi)) atomicAdd(&hist[(k >> shift) & 0xFF], 1);
+      // Score maps of a freshly initialised or confident head put most keys into one bin, so the
+      // histogram is warp-aggregated: lanes with equal bins elect one lane that adds their count.
+      for (int base_m = 0; base_m < d.M; base_m += kNmsThreads) {
+        const int m = base_m + tid;
+        int bin = -1;
+        if (m < d.M) {
+          const uint32_t k = keys[m];
+          if (k != 0u && (k & mask_hi) == (prefix & mask_hi)) bin = static_cast<int>((k >> shift) & 0xFF);
+        }
+        const unsigned peers = __match_any_sync(0xffffffffu, bin);
+        if (bin >= 0 && (tid & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], __popc(peers));
       }
       __syncthreads();
       if (tid == 0) {
