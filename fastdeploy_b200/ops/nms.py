@@ -22,7 +22,7 @@ class _NmsDesc(ctypes.Structure):
         ("cls_count", ctypes.c_void_p), ("cls_score", ctypes.c_void_p), ("cls_index", ctypes.c_void_p),
         ("max_keep", ctypes.c_int),
         ("out", ctypes.c_void_p), ("out_index", ctypes.c_void_p), ("out_num", ctypes.c_void_p),
-        ("out_cap", ctypes.c_int),
+        ("out_cap", ctypes.c_int), ("scores_t", ctypes.c_void_p),
     ]
 
 
@@ -79,6 +79,11 @@ class MulticlassNMS:
         d.cls_count, d.cls_score, d.cls_index = self.cls_count.data_ptr(), self.cls_score.data_ptr(), self.cls_index.data_ptr()
         d.max_keep = max_keep
         d.out, d.out_index, d.out_num, d.out_cap = self.out.data_ptr(), self.out_index.data_ptr(), self.out_num.data_ptr(), cap
+        # anchor-major scores are transposed once so that each class reads contiguous memory
+        self.scores_t = None
+        if not class_major and s_c == 1 and c > 1:
+            self.scores_t = torch.empty(n, c, m, dtype=scores.dtype, device=dev)
+            d.scores_t = self.scores_t.data_ptr()
         self.op = NativeOp(_lib().fdb_nms_create(ctypes.byref(d)), [boxes, scores, self], "multiclass_nms")
         self.op.keep = [boxes, scores]  # avoid a reference cycle through self
 

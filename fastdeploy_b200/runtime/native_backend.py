@@ -660,7 +660,7 @@ class Lowering:
                             nms_threshold=node.attr("nms_threshold", 0.5), nms_top_k=node.attr("nms_top_k", 1000),
                             keep_top_k=node.attr("keep_top_k", 100), normalized=bool(node.attr("normalized", 1)),
                             background_label=node.attr("background_label", -1))
-        self.plan.add_native(nms.op, node, launches=2)
+        self.plan.add_native(nms.op, node, launches=3 if nms.scores_t is not None else 2)
         nms.launch()
         self.plan.extra.setdefault("nms", []).append(nms)
         n = boxes.shape[0]
