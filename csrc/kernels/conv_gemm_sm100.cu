@@ -76,6 +76,7 @@ struct ConvGemmParams {
   int KH, KW, stride, pad_h, pad_w;
   int tw, th, tiles_w, tiles_h, n_tiles, total_tiles;
   int kb_per_tap, k_iters;
+  int last_ksteps;   // K = 16 steps that carry data in the last 64-wide slab of each tap (1..4)
   int act;
   float act_alpha, act_beta;
   uint32_t a_bytes;
@@ -88,12 +89,14 @@ struct ConvGemmParams {
   long long* trace;  // optional: CTA 0 records clock64() at pipeline events of its first tiles
 };
 
-// Timeline probe for tuning: slot layout [tile][8]: 0 producer issue, 1 MMA got accumulator,
+// Timeline probe for tuning (32 tiles of CTA 0): slot layout [tile][12]: 0 producer issue, 1 MMA got accumulator,
 // 2 MMA first operands ready, 3 MMA committed, 4 epilogue saw accumulator, 5 epilogue TMEM read done,
-// 6 epilogue released accumulator, 7 epilogue store issued.
-constexpr int kTraceTiles = 48;
+// 6 epilogue released accumulator, 7 epilogue store issued, 8 epilogue warps met, 9 TMEM data
+// arrived, 10 staging complete.
+constexpr int kTraceTiles = 32;
+constexpr int kTraceSlots = 12;
 __device__ __forceinline__ void trace_mark(const ConvGemmParams& p, int local_tile, int slot) {
-  if (p.trace != nullptr && blockIdx.x == 0 && local_tile < kTraceTiles) p.trace[local_tile * 8 + slot] = clock64();
+  if (p.trace != nullptr && blockIdx.x == 0 && local_tile < kTraceTiles) p.trace[local_tile * kTraceSlots + slot] = clock64();
 }
 
 // Generic activation (runtime code); the hot ones have dedicated template paths.
@@ -238,20 +241,30 @@ constexpr int kTplGeneric = -1;
 template <int ACT>
 __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParams& p, int co,
                                           int col_limit, uint8_t* yrow, const uint8_t* rrow,
-                                          bool in_bf16, int out_es, uint32_t stage_addr = 0) {
+                                          bool in_bf16, int out_es, uint32_t stage_addr = 0,
+                                          const float* bias_s = nullptr, bool has_pre = false,
+                                          uint4 res_pre = make_uint4(0, 0, 0, 0)) {
   const int nvalid = min(8, col_limit - co);
   if (nvalid <= 0) return;
   float x[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(v[j]);
-  if (p.bias != nullptr) {
+  if (bias_s != nullptr) {   // shared-memory copy (zeros where there is no bias), padded to the tile width
+    const float4 b0 = *reinterpret_cast<const float4*>(bias_s);
+    const float4 b1 = *reinterpret_cast<const float4*>(bias_s + 4);
+    x[0] += b0.x; x[1] += b0.y; x[2] += b0.z; x[3] += b0.w;
+    x[4] += b1.x; x[5] += b1.y; x[6] += b1.z; x[7] += b1.w;
+  } else if (p.bias != nullptr) {
     if (nvalid == 8) {
       const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + co));
       const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + co) + 1);
       x[0] += b0.x; x[1] += b0.y; x[2] += b0.z; x[3] += b0.w;
       x[4] += b1.x; x[5] += b1.y; x[6] += b1.z; x[7] += b1.w;
     } else {
-      for (int j = 0; j < nvalid; ++j) x[j] += __ldg(p.bias + co + j);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (j < nvalid) x[j] += __ldg(p.bias + co + j);
+      }
     }
   }
   // staged rows go out through a TMA store that clips channel tails, so tails may take this path too
@@ -263,7 +276,7 @@ __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParam
     const bool res_fast = p.res_mode != 0 && p.res_vec != 0 && in_bf16 == out_bf16 && nvalid == 8;
     if (p.res_mode != 0) {
       if (res_fast && p.res_mode == 2) {
-        rv = *reinterpret_cast<const uint4*>(rrow + co * 2);
+        rv = has_pre ? res_pre : *reinterpret_cast<const uint4*>(rrow + co * 2);
       } else {
         float r[8];
         load8_as_float(rrow + co * 2, in_bf16, p.res_vec != 0, nvalid, r);
@@ -290,9 +303,10 @@ __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParam
       w[2] = add2(w[2], rv.z, out_bf16); w[3] = add2(w[3], rv.w, out_bf16);
     }
     if (stage_addr != 0) {
+      // no memory clobber: the next group's loads may move above this store; volatile keeps it
+      // ordered against the barriers
       asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_addr), "r"(w[0]), "r"(w[1]), "r"(w[2]),
-                   "r"(w[3])
-                   : "memory");
+                   "r"(w[3]));
     } else {
       *reinterpret_cast<uint4*>(yrow + static_cast<size_t>(co) * 2) = make_uint4(w[0], w[1], w[2], w[3]);
     }
@@ -318,7 +332,12 @@ __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParam
 #pragma unroll
     for (int j = 0; j < 8; ++j) x[j] += r[j];
   }
-  store8_general(yrow + static_cast<size_t>(co) * out_es, p.out_dtype, p.y_vec != 0, nvalid, x);
+  // The out-of-line store takes an address, which would pin its argument in local memory for the
+  // whole function, fast paths included: hand it a copy so that x itself stays in registers.
+  float xs[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) xs[j] = x[j];
+  store8_general(yrow + static_cast<size_t>(co) * out_es, p.out_dtype, p.y_vec != 0, nvalid, xs);
 }
 
 // Epilogue role shared by the convolution kernels: drains the double-buffered TMEM
@@ -333,27 +352,31 @@ constexpr int kStagingBytes = 2 * kStageTileBytes;
 template <int BN, int ACT>
 __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const CUtensorMap* tmY, uint32_t stage0,
                                                   uint32_t tmem_base, uint32_t tfull0, uint32_t tempty0,
-                                                  volatile int* abort_flag, int warp, int lane) {
+                                                  volatile int* abort_flag, float* s_bias, int warp, int lane) {
   const int q = warp & 3;
   const int half = (warp - 2) >> 2;
   const bool issuer = warp == 2 && lane == 0;
   const bool in_bf16 = p.in_bf16 != 0;
+  const int et = static_cast<int>(threadIdx.x) - 64;   // index among the 256 epilogue threads
+  const int row = q * 32 + lane;
+  const int rh = row / p.tw, rw = row - rh * p.tw;
+  // after-activation residual rows can be fetched while the accumulator is still being produced
+  const bool res_pre = p.res_mode == 2 && p.res_vec != 0 && in_bf16 == (p.out_dtype == kBF16);
   int acc = 0;
   uint32_t acc_ph = 0;
   uint32_t blk_count = 0;
   volatile int* abort_sample = abort_flag + 1;
   bool aborted = false;
-  for (int tile = blockIdx.x; tile < p.total_tiles && !aborted; tile += gridDim.x) {
+  // Bias lives in shared memory: the whole vector once when one column tile covers Cout, else the
+  // tile's slice, double-buffered by tile parity. The barrier that opens a tile publishes it.
+  if (p.n_tiles == 1 && et < BN) s_bias[et] = (p.bias != nullptr && et < p.Cout) ? __ldg(p.bias + et) : 0.f;
+  int it = 0;
+  for (int tile = blockIdx.x; tile < p.total_tiles && !aborted; tile += gridDim.x, ++it) {
     const int n_tile = tile % p.n_tiles;
     int m_tile = tile / p.n_tiles;
     const int twi = m_tile % p.tiles_w; m_tile /= p.tiles_w;
     const int thi = m_tile % p.tiles_h;
     const int img = m_tile / p.tiles_h;
-    mbar_wait(tfull0 + 8u * acc, acc_ph, abort_flag, kStatusTimeoutEpilogue);
-    tc_fence_after();
-    if (issuer) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 4);
-    const int row = q * 32 + lane;
-    const int rh = row / p.tw, rw = row - rh * p.tw;
     const int oh = thi * p.th + rh, ow = twi * p.tw + rw;
     const bool valid = rh < p.th && oh < p.Ho && ow < p.Wo;
     const uint8_t* rrow = reinterpret_cast<const uint8_t*>(p.residual) +
@@ -363,49 +386,76 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
     const int colbase = n_tile * BN;
     const int col_limit = min(p.Cout, colbase + BN);
     const int nblk = (col_limit - colbase + 63) / 64;
+    const float* bias_s = s_bias;
+    if (p.n_tiles > 1) {
+      float* dst = s_bias + (it & 1) * 256;
+      if (et < BN) dst[et] = (p.bias != nullptr && colbase + et < p.Cout) ? __ldg(p.bias + colbase + et) : 0.f;
+      bias_s = dst;
+    }
     for (int blk = 0; blk < nblk; ++blk, ++blk_count) {
       const uint32_t buf = stage0 + (blk_count & 1u) * kStageTileBytes;
       const int c = blk * 2 + half;                 // this warp's 32-column TMEM chunk
-      const bool have_cols = colbase + c * 32 < col_limit;
-      uint32_t v[32];
-      if (have_cols) tmem_ld_32x32(t_row + c * 32, v);      // in flight across the barrier below
-      // The warps meet at named barriers, so they must all leave together: one thread samples the
-      // abort flag before the barrier and everybody acts on that sample after it.
-      if (issuer) {
-        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-        *abort_sample = *abort_flag;
+      const int co0 = colbase + c * 32;
+      const bool have_cols = co0 < col_limit;
+      uint4 rpre[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+      if (res_pre && valid && have_cols) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          if (co0 + g * 8 + 8 <= col_limit) rpre[g] = *reinterpret_cast<const uint4*>(rrow + (co0 + g * 8) * 2);
+        }
+      }
+      // One warp waits for the accumulator; the others sleep at the named barrier, which wakes them
+      // faster than eight separate polls would. The same thread makes sure that the staging buffer
+      // of two blocks ago has been read out and samples the abort flag for everybody, because warps
+      // that meet at barriers must all leave together.
+      if (warp == 2) {
+        if (blk == 0) {
+          mbar_wait(tfull0 + 8u * acc, acc_ph, abort_flag, kStatusTimeoutEpilogue);
+          if (issuer) trace_mark(p, it, 4);
+        }
+        if (lane == 0) {
+          asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          *abort_sample = *abort_flag;
+        }
       }
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (*abort_sample != 0) { aborted = true; break; }
+      if (blk == 0) tc_fence_after();
+      if (issuer && blk == nblk - 1) trace_mark(p, it, 8);
       if (have_cols) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_row + c * 32, v);
         tmem_ld_wait_dep(v);
+        if (issuer && blk == nblk - 1) trace_mark(p, it, 9);
         if (valid) {
           const uint32_t srow = buf + row * 128;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             const uint32_t chunk = static_cast<uint32_t>(half * 4 + g);
-            epilogue8<ACT>(v + g * 8, p, colbase + c * 32 + g * 8, col_limit, nullptr, rrow, in_bf16, 2,
-                           srow + ((chunk ^ (row & 7)) << 4));
+            const bool pre = res_pre && co0 + g * 8 + 8 <= col_limit;
+            epilogue8<ACT>(v + g * 8, p, co0 + g * 8, col_limit, nullptr, rrow, in_bf16, 2,
+                           srow + ((chunk ^ (row & 7)) << 4), bias_s + (c * 32 + g * 8), pre, rpre[g]);
           }
         }
       }
       if (blk == nblk - 1) {        // last TMEM read of this accumulator
-        if (issuer) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 5);
+        if (issuer) trace_mark(p, it, 5);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty0 + 8u * acc);
-        if (issuer) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 6);
+        if (issuer) trace_mark(p, it, 6);
       }
       fence_proxy_async_smem();
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (issuer) {
+        if (blk == nblk - 1) trace_mark(p, it, 10);
         asm volatile(
             "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
                 reinterpret_cast<uint64_t>(tmY)),
             "r"(buf), "r"(colbase + blk * 64), "r"(twi * p.tw), "r"(thi * p.th), "r"(img)
             : "memory");
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        if (blk == nblk - 1) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 7);
+        if (blk == nblk - 1) trace_mark(p, it, 7);
       }
     }
     acc ^= 1;
@@ -485,7 +535,8 @@ __device__ __forceinline__ void epilogue_loop(const ConvGemmParams& p, uint32_t 
   }
 }
 
-constexpr int kMaxSmem = 232448;  // 227 KB opt-in limit per CTA
+constexpr int kMaxSmem = 232448 - 3072;  // 227 KB opt-in limit per CTA less the static shared memory
+constexpr int kBiasFloats = 512;      // shared-memory bias: two tile slices of up to 256 columns
 constexpr int kBarBytes = 256;
 
 constexpr int next_pow2_cols(int c) { return c <= 32 ? 32 : c <= 64 ? 64 : c <= 128 ? 128 : c <= 256 ? 256 : 512; }
@@ -509,6 +560,7 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   using Cfg = KernelCfg<BN>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(16) float s_bias[kBiasFloats];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes + kStagingBytes);
@@ -563,6 +615,7 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int img = m_tile / p.tiles_h;
         const int x0 = twi * p.tw * p.stride - p.pad_w;
         const int y0 = thi * p.th * p.stride - p.pad_h;
+        trace_mark(p, (tile - blockIdx.x) / gridDim.x, 0);
         int kcol = 0;
         for (int kh = 0; ok && kh < p.KH; ++kh) {
           for (int kw = 0; ok && kw < p.KW; ++kw) {
@@ -598,45 +651,51 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    // The whole warp walks the loops (so addresses and descriptors stay warp-uniform); one elected
-    // lane issues the MMAs and the commits.
-    {
+    // One elected thread runs the whole loop. tcgen05.mma issue is nearly synchronous for narrow
+    // tiles (the thread cannot run far ahead of the tensor pipe), so every vote, fence or poll
+    // between two MMAs adds its full latency to the tile: the loop holds nothing but the waits that
+    // are needed. No tcgen05 fence follows them: operands arrive through the async proxy (TMA
+    // complete_tx), and an accumulator is only handed back after the epilogue's tcgen05.wait::ld,
+    // so its reads have finished before the arrive that this thread observes.
+    if (elect_one()) {
       int s = 0;
       uint32_t ph = 0;
       int acc = 0;
       uint32_t acc_ph = 0;
       bool ok = true;
       const uint64_t desc_hi = make_kmajor_desc(0, 128);
-      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-        if (!mbar_wait_warp(tempty_bar(acc), acc_ph ^ 1, abort_flag, kStatusTimeoutMma)) break;
-        tc_fence_after();
+      int it = 0;
+      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++it) {
+        if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, kStatusTimeoutMma)) break;
+        trace_mark(p, it, 1);
         const uint32_t d_tmem = tmem_base + acc * BN;
+        int kb = 0;
         for (int k = 0; k < p.k_iters; ++k) {
-          if (!mbar_wait_warp(full_bar(s), ph, abort_flag, kStatusTimeoutMma)) {
+          const uint32_t ksteps = kb == p.kb_per_tap - 1 ? static_cast<uint32_t>(p.last_ksteps) : 4u;
+          if (++kb == p.kb_per_tap) kb = 0;
+          if (!mbar_wait(full_bar(s), ph, abort_flag, kStatusTimeoutMma)) {
             ok = false;
             break;
           }
-          tc_fence_after();
+          if (k == 0) trace_mark(p, it, 2);
           const uint32_t a_addr = tile0 + s * Cfg::kStageBytes;
           const uint64_t adesc = desc_hi | ((a_addr & 0x3FFFF) >> 4);
           const uint64_t bdesc = desc_hi | (((a_addr + Cfg::kABytes) & 0x3FFFF) >> 4);
-          if (elect_one()) {
-            umma_f16_kblock(d_tmem, adesc, bdesc, p.idesc, k != 0 ? 1u : 0u);
-            umma_commit(empty_bar(s));
-          }
-          __syncwarp();
+          umma_f16_ksteps(d_tmem, adesc, bdesc, p.idesc, k != 0 ? 1u : 0u, ksteps);
+          umma_commit(empty_bar(s));
           if (++s == S) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
-        if (elect_one()) umma_commit(tfull_bar(acc));
-        __syncwarp();
+        umma_commit(tfull_bar(acc));
+        trace_mark(p, it, 3);
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1;
       }
     }
+    __syncwarp();
   } else if (p.y_tma) {
     epilogue_loop_tma<BN, ACT>(p, &tmY, tile0 + S * Cfg::kStageBytes, tmem_base, tfull_bar(0), tempty_bar(0),
-                               abort_flag, warp, lane);
+                               abort_flag, s_bias, warp, lane);
   } else {
     epilogue_loop<BN, ACT>(p, tmem_base, tfull_bar(0), tempty_bar(0), abort_flag, warp, lane);
   }
@@ -679,6 +738,7 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   constexpr int kBBytes = BN * kBK * 2;
   constexpr int kTmemCols = next_pow2_cols(2 * BN);
   extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(16) float s_bias[kBiasFloats];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   const int SA = hp.a_stages, SB = hp.b_stages;
@@ -758,62 +818,60 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
   } else if (warp == 1) {
-    {
+    // One elected thread issues everything; see the note in conv_gemm_kernel on why the loop holds
+    // no votes and no tcgen05 fences.
+    if (elect_one()) {
       int sa = 0, sb = 0, acc = 0;
       uint32_t pa = 0, pb = 0, acc_ph = 0;
       bool ok = true, weights_ready = false;
       const uint64_t bdesc_hi = make_kmajor_desc(0, 128);
       // shifted views of the halo patch: 8-row groups are 10 pixel rows (1280 bytes) apart
       const uint64_t adesc_hi = (bdesc_hi & ~(0x3FFFull << 32)) | (static_cast<uint64_t>((kHaloCols * 128) >> 4) << 32);
-      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-        if (!mbar_wait_warp(tempty0 + 8u * acc, acc_ph ^ 1, abort_flag, kStatusTimeoutMma)) break;
-        tc_fence_after();
-        if (lane == 0) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 1);
+      int it = 0;
+      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++it) {
+        if (!mbar_wait(tempty0 + 8u * acc, acc_ph ^ 1, abort_flag, kStatusTimeoutMma)) break;
+        trace_mark(p, it, 1);
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; ok && kb < slabs; ++kb) {
-          if (!mbar_wait_warp(a_full(sa), pa, abort_flag, kStatusTimeoutMma)) { ok = false; break; }
-          tc_fence_after();
-          if (kb == 0 && lane == 0) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 2);
+          if (!mbar_wait(a_full(sa), pa, abort_flag, kStatusTimeoutMma)) { ok = false; break; }
+          if (kb == 0) trace_mark(p, it, 2);
           const uint32_t a_base = a0 + sa * kHaloABytes;
+          const uint32_t ksteps = kb == slabs - 1 ? static_cast<uint32_t>(p.last_ksteps) : 4u;
 #pragma unroll 1
           for (int kh = 0; kh < 3; ++kh) {
             if (hp.b_resident) sb = kb * 3 + kh;
             if (!(hp.b_resident && weights_ready)) {
-              if (!mbar_wait_warp(b_full(sb), hp.b_resident ? 0u : pb, abort_flag, kStatusTimeoutMma)) { ok = false; break; }
-              tc_fence_after();
+              if (!mbar_wait(b_full(sb), hp.b_resident ? 0u : pb, abort_flag, kStatusTimeoutMma)) { ok = false; break; }
             }
             // tap (kh, kw) starts (kh*10 + kw) pixel rows into the patch
             const uint32_t a_row = a_base + kh * kHaloCols * 128;
             const uint32_t b_row = b0 + sb * (3 * kBBytes);
             const uint64_t ad0 = adesc_hi | ((a_row & 0x3FFFF) >> 4);
             const uint64_t bd0 = bdesc_hi | ((b_row & 0x3FFFF) >> 4);
-            if (elect_one()) {
-              umma_f16_kblock(d_tmem, ad0, bd0, p.idesc, (kb | kh) != 0 ? 1u : 0u);
-              umma_f16_kblock(d_tmem, ad0 + (128 >> 4), bd0 + (kBBytes >> 4), p.idesc, 1u);
-              umma_f16_kblock(d_tmem, ad0 + (256 >> 4), bd0 + (2 * kBBytes >> 4), p.idesc, 1u);
-              if (!hp.b_resident) umma_commit(b_empty(sb));
-            }
-            __syncwarp();
+            umma_f16_ksteps(d_tmem, ad0, bd0, p.idesc, (kb | kh) != 0 ? 1u : 0u, ksteps);
+            umma_f16_ksteps(d_tmem, ad0 + (128 >> 4), bd0 + (kBBytes >> 4), p.idesc, 1u, ksteps);
+            umma_f16_ksteps(d_tmem, ad0 + (256 >> 4), bd0 + (2 * kBBytes >> 4), p.idesc, 1u, ksteps);
             if (!hp.b_resident) {
+              umma_commit(b_empty(sb));
               if (++sb == SB) { sb = 0; pb ^= 1; }
             }
           }
           if (!ok) break;
-          if (elect_one()) umma_commit(a_empty(sa));
-          __syncwarp();
+          umma_commit(a_empty(sa));
           if (++sa == SA) { sa = 0; pa ^= 1; }
         }
         if (!ok) break;
-        if (elect_one()) umma_commit(tfull0 + 8u * acc);
-        __syncwarp();
+        umma_commit(tfull0 + 8u * acc);
         weights_ready = true;
-        if (lane == 0) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 3);
+        trace_mark(p, it, 3);
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1;
       }
     }
+    __syncwarp();
   } else if (p.y_tma) {
-    epilogue_loop_tma<BN, ACT>(p, &tmY, b0 + SB * 3 * kBBytes, tmem_base, tfull0, tempty0, abort_flag, warp, lane);
+    epilogue_loop_tma<BN, ACT>(p, &tmY, b0 + SB * 3 * kBBytes, tmem_base, tfull0, tempty0, abort_flag, s_bias, warp,
+                               lane);
   } else {
     epilogue_loop<BN, ACT>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane);
   }
@@ -1009,6 +1067,7 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   p.total_tiles = static_cast<int>(total);
   p.kb_per_tap = (d->Cin + kBK - 1) / kBK;
   p.k_iters = d->KH * d->KW * p.kb_per_tap;
+  p.last_ksteps = (d->Cin - (p.kb_per_tap - 1) * kBK + 15) / 16;
   p.bias = d->bias; p.residual = d->residual; p.y = d->y; p.status = d->status;
   p.Ho = d->Ho; p.Wo = d->Wo; p.Cout = d->Cout; p.y_ld = d->y_ld;
   p.res_ld = d->res_ld; p.res_mode = d->residual ? d->res_mode : 0;

@@ -190,6 +190,34 @@ __device__ __forceinline__ void umma_f16_kblock(uint32_t tmem_d, uint64_t adesc,
       : "memory");
 }
 
+// The same K block with only the first `nsteps` (1..4) K = 16 steps issued: the tail slab of a
+// reduction whose length is not a multiple of 64 skips the steps that would multiply zero padding.
+__device__ __forceinline__ void umma_f16_ksteps(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t accumulate_first, uint32_t nsteps) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p0, p1, q1, q2, q3;\n"
+      ".reg .b64 a1, a2, a3, b1, b2, b3;\n"
+      "setp.ne.b32 p0, %4, 0;\n"
+      "setp.eq.u32 p1, %3, %3;\n"
+      "setp.gt.u32 q1, %5, 1;\n"
+      "setp.gt.u32 q2, %5, 2;\n"
+      "setp.gt.u32 q3, %5, 3;\n"
+      "add.s64 a1, %1, 2;\n"
+      "add.s64 b1, %2, 2;\n"
+      "add.s64 a2, %1, 4;\n"
+      "add.s64 b2, %2, 4;\n"
+      "add.s64 a3, %1, 6;\n"
+      "add.s64 b3, %2, 6;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p0;\n"
+      "@q1 tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, p1;\n"
+      "@q2 tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, p1;\n"
+      "@q3 tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, p1;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate_first), "r"(nsteps)
+      : "memory");
+}
+
 // kind::f8f6f4: e4m3 / e5m2 inputs, fp32 accumulate, K = 32 per instruction.
 __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
                                         uint32_t idesc, uint32_t accumulate) {
