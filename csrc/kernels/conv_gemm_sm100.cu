@@ -75,6 +75,7 @@ struct ConvGemmParams {
   int Ho, Wo, Cout, y_ld, res_ld, res_mode, out_dtype, in_bf16;
   int KH, KW, stride, pad_h, pad_w;
   int tw, th, tiles_w, tiles_h, n_tiles, total_tiles;
+  unsigned long long mul_n, mul_w, mul_h;   // ceil(2^40 / divisor) for n_tiles, tiles_w, tiles_h
   int kb_per_tap, k_iters;
   int last_ksteps;   // K = 16 steps that carry data in the last 64-wide slab of each tap (1..4)
   int act;
@@ -88,6 +89,27 @@ struct ConvGemmParams {
   int y_tma;   // 16-bit output leaves through shared-memory staging + TMA tensor stores
   long long* trace;  // optional: CTA 0 records clock64() at pipeline events of its first tiles
 };
+
+// Tile index -> (column tile, tile column, tile row, image). Integer division by the three runtime
+// divisors is replaced by a multiply with ceil(2^40 / d) and a shift, exact while index * d < 2^40
+// (the host refuses larger problems): every role decodes once per tile, and the hardware division
+// sequence is long enough to show in the per-tile cost of small layers.
+struct TileCoord { int n_tile, twi, thi, img; };
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, unsigned long long mul) {
+  return static_cast<uint32_t>((static_cast<unsigned long long>(n) * mul) >> 40);
+}
+__device__ __forceinline__ TileCoord decode_tile(const ConvGemmParams& p, int tile) {
+  const uint32_t t = static_cast<uint32_t>(tile);
+  const uint32_t m = fast_div(t, p.mul_n);
+  const uint32_t r = fast_div(m, p.mul_w);
+  const uint32_t img = fast_div(r, p.mul_h);
+  TileCoord c;
+  c.n_tile = static_cast<int>(t - m * static_cast<uint32_t>(p.n_tiles));
+  c.twi = static_cast<int>(m - r * static_cast<uint32_t>(p.tiles_w));
+  c.thi = static_cast<int>(r - img * static_cast<uint32_t>(p.tiles_h));
+  c.img = static_cast<int>(img);
+  return c;
+}
 
 // Timeline probe for tuning (32 tiles of CTA 0): slot layout [tile][12]: 0 producer issue, 1 MMA got accumulator,
 // 2 MMA first operands ready, 3 MMA committed, 4 epilogue saw accumulator, 5 epilogue TMEM read done,
@@ -340,6 +362,41 @@ __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParam
   store8_general(yrow + static_cast<size_t>(co) * out_es, p.out_dtype, p.y_vec != 0, nvalid, xs);
 }
 
+// Straight-line epilogue of one 32-column chunk into the staging row: bias from shared memory,
+// activation, optional after-activation residual already in registers, four 16-byte stores. All
+// data-type and residual decisions are template parameters: with two or three warps per scheduler
+// nothing hides branch latency, and a dozen uniform branches per 8 columns used to cost more than
+// the arithmetic. Columns past Cout carry padding that the TMA store clips.
+template <int ACT, bool BF16, bool RES>
+__device__ __forceinline__ void staged_chunk(const uint32_t (&v)[32], const float* bias_s, const uint4 (&rpre)[4],
+                                             uint32_t srow, uint32_t chunk0, uint32_t row7, const ConvGemmParams& p) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const float4 b0 = *reinterpret_cast<const float4*>(bias_s + g * 8);
+    const float4 b1 = *reinterpret_cast<const float4*>(bias_s + g * 8 + 4);
+    float x[8];
+    x[0] = __uint_as_float(v[g * 8 + 0]) + b0.x; x[1] = __uint_as_float(v[g * 8 + 1]) + b0.y;
+    x[2] = __uint_as_float(v[g * 8 + 2]) + b0.z; x[3] = __uint_as_float(v[g * 8 + 3]) + b0.w;
+    x[4] = __uint_as_float(v[g * 8 + 4]) + b1.x; x[5] = __uint_as_float(v[g * 8 + 5]) + b1.y;
+    x[6] = __uint_as_float(v[g * 8 + 6]) + b1.z; x[7] = __uint_as_float(v[g * 8 + 7]) + b1.w;
+    if (ACT == kTplGeneric) apply_act8(x, p.act, p.act_alpha, p.act_beta);
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t h = pack2(x[2 * j], x[2 * j + 1], BF16);
+      if (ACT == kActSilu) h = BF16 ? silu_bf16x2(h) : silu_f16x2(h);
+      if (ACT == kActRelu) h = relu2(h, BF16);
+      w[j] = h;
+    }
+    if (RES) {
+      w[0] = add2(w[0], rpre[g].x, BF16); w[1] = add2(w[1], rpre[g].y, BF16);
+      w[2] = add2(w[2], rpre[g].z, BF16); w[3] = add2(w[3], rpre[g].w, BF16);
+    }
+    const uint32_t addr = srow + (((chunk0 + g) ^ row7) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]));
+  }
+}
+
 // Epilogue role shared by the convolution kernels: drains the double-buffered TMEM
 // accumulators tile by tile. `tfull0` / `tempty0` are the shared-memory addresses of
 // tmem_full[0] and tmem_empty[0]; index 1 of each follows 8 bytes later.
@@ -361,7 +418,9 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
   const int row = q * 32 + lane;
   const int rh = row / p.tw, rw = row - rh * p.tw;
   // after-activation residual rows can be fetched while the accumulator is still being produced
-  const bool res_pre = p.res_mode == 2 && p.res_vec != 0 && in_bf16 == (p.out_dtype == kBF16);
+  const bool out_bf16 = p.out_dtype == kBF16;
+  const bool res_pre = p.res_mode == 2 && p.res_vec != 0 && in_bf16 == out_bf16;
+  const bool simple = p.res_mode == 0 || res_pre;   // everything else takes the general per-group path
   int acc = 0;
   uint32_t acc_ph = 0;
   uint32_t blk_count = 0;
@@ -372,11 +431,8 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
   if (p.n_tiles == 1 && et < BN) s_bias[et] = (p.bias != nullptr && et < p.Cout) ? __ldg(p.bias + et) : 0.f;
   int it = 0;
   for (int tile = blockIdx.x; tile < p.total_tiles && !aborted; tile += gridDim.x, ++it) {
-    const int n_tile = tile % p.n_tiles;
-    int m_tile = tile / p.n_tiles;
-    const int twi = m_tile % p.tiles_w; m_tile /= p.tiles_w;
-    const int thi = m_tile % p.tiles_h;
-    const int img = m_tile / p.tiles_h;
+    const TileCoord tc = decode_tile(p, tile);
+    const int n_tile = tc.n_tile, twi = tc.twi, thi = tc.thi, img = tc.img;
     const int oh = thi * p.th + rh, ow = twi * p.tw + rw;
     const bool valid = rh < p.th && oh < p.Ho && ow < p.Wo;
     const uint8_t* rrow = reinterpret_cast<const uint8_t*>(p.residual) +
@@ -401,7 +457,9 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
       if (res_pre && valid && have_cols) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          if (co0 + g * 8 + 8 <= col_limit) rpre[g] = *reinterpret_cast<const uint4*>(rrow + (co0 + g * 8) * 2);
+          // a ragged last group still reads 16 bytes: the row pitch is a multiple of 8 elements and
+          // columns past Cout are clipped by the store
+          if (co0 + g * 8 < col_limit) rpre[g] = *reinterpret_cast<const uint4*>(rrow + (co0 + g * 8) * 2);
         }
       }
       // One warp waits for the accumulator; the others sleep at the named barrier, which wakes them
@@ -429,12 +487,22 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
         if (issuer && blk == nblk - 1) trace_mark(p, it, 9);
         if (valid) {
           const uint32_t srow = buf + row * 128;
+          const uint32_t chunk0 = static_cast<uint32_t>(half * 4), row7 = static_cast<uint32_t>(row & 7);
+          const float* bs = bias_s + c * 32;
+          if (simple) {
+            if (out_bf16) {
+              if (res_pre) staged_chunk<ACT, true, true>(v, bs, rpre, srow, chunk0, row7, p);
+              else staged_chunk<ACT, true, false>(v, bs, rpre, srow, chunk0, row7, p);
+            } else {
+              if (res_pre) staged_chunk<ACT, false, true>(v, bs, rpre, srow, chunk0, row7, p);
+              else staged_chunk<ACT, false, false>(v, bs, rpre, srow, chunk0, row7, p);
+            }
+          } else {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const uint32_t chunk = static_cast<uint32_t>(half * 4 + g);
-            const bool pre = res_pre && co0 + g * 8 + 8 <= col_limit;
-            epilogue8<ACT>(v + g * 8, p, co0 + g * 8, col_limit, nullptr, rrow, in_bf16, 2,
-                           srow + ((chunk ^ (row & 7)) << 4), bias_s + (c * 32 + g * 8), pre, rpre[g]);
+            for (int g = 0; g < 4; ++g) {
+              epilogue8<ACT>(v + g * 8, p, co0 + g * 8, col_limit, nullptr, rrow, in_bf16, 2,
+                             srow + (((chunk0 + g) ^ row7) << 4), bs + g * 8, false);
+            }
           }
         }
       }
@@ -481,11 +549,8 @@ __device__ __forceinline__ void epilogue_loop(const ConvGemmParams& p, uint32_t 
   int acc = 0;
   uint32_t acc_ph = 0;
   for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
-    const int n_tile = tile % p.n_tiles;
-    int m_tile = tile / p.n_tiles;
-    const int twi = m_tile % p.tiles_w; m_tile /= p.tiles_w;
-    const int thi = m_tile % p.tiles_h;
-    const int img = m_tile / p.tiles_h;
+    const TileCoord tc = decode_tile(p, tile);
+    const int n_tile = tc.n_tile, twi = tc.twi, thi = tc.thi, img = tc.img;
     if (!mbar_wait(tfull_bar(acc), acc_ph, abort_flag, kStatusTimeoutEpilogue)) break;
     tc_fence_after();
     const int row = q * 32 + lane;
@@ -608,11 +673,8 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t armed = 0, armed_parity = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-        const int n_tile = tile % p.n_tiles;
-        int m_tile = tile / p.n_tiles;
-        const int twi = m_tile % p.tiles_w; m_tile /= p.tiles_w;
-        const int thi = m_tile % p.tiles_h;
-        const int img = m_tile / p.tiles_h;
+        const TileCoord tc = decode_tile(p, tile);
+        const int n_tile = tc.n_tile, twi = tc.twi, thi = tc.thi, img = tc.img;
         const int x0 = twi * p.tw * p.stride - p.pad_w;
         const int y0 = thi * p.th * p.stride - p.pad_h;
         trace_mark(p, (tile - blockIdx.x) / gridDim.x, 0);
@@ -784,11 +846,8 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t pa = 0, pb = 0;
       bool ok = true, first = true;
       for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-        const int n_tile = tile % p.n_tiles;
-        int m_tile = tile / p.n_tiles;
-        const int twi = m_tile % p.tiles_w; m_tile /= p.tiles_w;
-        const int thi = m_tile % p.tiles_h;
-        const int img = m_tile / p.tiles_h;
+        const TileCoord tc = decode_tile(p, tile);
+        const int n_tile = tc.n_tile, twi = tc.twi, thi = tc.thi, img = tc.img;
         for (int kb = 0; ok && kb < slabs; ++kb) {
           if (!mbar_wait(a_empty(sa), pa ^ 1, abort_flag, kStatusTimeoutProducer)) { ok = false; break; }
           mbar_arrive_expect_tx(a_full(sa), halo_bytes);
@@ -1189,6 +1248,16 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
       if (r == CUDA_SUCCESS) p.y_tma = 1;
     }
     if (!p.y_tma) op->tmY = op->tmA;   // a valid map is still passed; the kernel does not touch it
+  }
+  {
+    const unsigned long long one = 1ull << 40;
+    const long long dmax = std::max(p.n_tiles, std::max(p.tiles_w, p.tiles_h));
+    if (static_cast<long long>(p.total_tiles) * dmax >= static_cast<long long>(one)) {
+      set_error("conv_gemm: too many tiles for the tile decoder"); delete op; return nullptr;
+    }
+    p.mul_n = (one + p.n_tiles - 1) / p.n_tiles;
+    p.mul_w = (one + p.tiles_w - 1) / p.tiles_w;
+    p.mul_h = (one + p.tiles_h - 1) / p.tiles_h;
   }
   return op;
 }
