@@ -403,34 +403,48 @@ __device__ __forceinline__ void staged_chunk(const uint32_t (&v)[32], const floa
 constexpr int kStageTileBytes = kBM * 128;      // one 128-row x 64-channel (16-bit) output block
 constexpr int kStagingBytes = 2 * kStageTileBytes;
 
-// Output path for 16-bit results: the eight epilogue warps assemble a 128 x 64-channel block in
-// shared memory (128-byte swizzled rows) and one thread hands it to a TMA tensor store, which writes
-// whole lines and clips ragged tile edges and channel tails. Two blocks are in flight.
+// Output path for 16-bit results. The eight epilogue warps form two teams of four; team t owns
+// accumulator t, i.e. every second tile of the CTA, so two tiles drain at the same time and the
+// per-tile latency chain (wait, TMEM load, activation, staging, store issue) is paid at half rate.
+// Within a team each thread owns one accumulator row: it walks the tile's columns in 64-channel
+// blocks, assembles each block in the team's staging buffer (128-byte swizzled rows) and the team
+// leader hands it to a TMA tensor store, which writes whole lines and clips ragged tile edges and
+// channel tails. Named barrier 1 + t (128 threads) keeps the team in step.
+constexpr int kTeamWarps = 4;
 template <int BN, int ACT>
 __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const CUtensorMap* tmY, uint32_t stage0,
                                                   uint32_t tmem_base, uint32_t tfull0, uint32_t tempty0,
                                                   volatile int* abort_flag, float* s_bias, int warp, int lane) {
-  const int q = warp & 3;
-  const int half = (warp - 2) >> 2;
-  const bool issuer = warp == 2 && lane == 0;
+  const int q = warp & 3;                       // TMEM lane quarter this warp may read
+  const int team = (warp - 2) >> 2;
+  const bool leader_warp = ((warp - 2) & 3) == 0;
+  const bool issuer = leader_warp && lane == 0;
   const bool in_bf16 = p.in_bf16 != 0;
   const int et = static_cast<int>(threadIdx.x) - 64;   // index among the 256 epilogue threads
+  const int tt = et - team * 128;                      // index within the team
   const int row = q * 32 + lane;
   const int rh = row / p.tw, rw = row - rh * p.tw;
-  // after-activation residual rows can be fetched while the accumulator is still being produced
   const bool out_bf16 = p.out_dtype == kBF16;
+  // after-activation residual rows can be fetched while the accumulator is still being produced
   const bool res_pre = p.res_mode == 2 && p.res_vec != 0 && in_bf16 == out_bf16;
   const bool simple = p.res_mode == 0 || res_pre;   // everything else takes the general per-group path
-  int acc = 0;
+  const uint32_t buf = stage0 + team * kStageTileBytes;
+  const uint32_t tfull = tfull0 + 8u * team, tempty = tempty0 + 8u * team;
+  const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + team * BN;
+  volatile int* abort_sample = abort_flag + 1 + team;
   uint32_t acc_ph = 0;
-  uint32_t blk_count = 0;
-  volatile int* abort_sample = abort_flag + 1;
   bool aborted = false;
   // Bias lives in shared memory: the whole vector once when one column tile covers Cout, else the
-  // tile's slice, double-buffered by tile parity. The barrier that opens a tile publishes it.
-  if (p.n_tiles == 1 && et < BN) s_bias[et] = (p.bias != nullptr && et < p.Cout) ? __ldg(p.bias + et) : 0.f;
-  int it = 0;
-  for (int tile = blockIdx.x; tile < p.total_tiles && !aborted; tile += gridDim.x, ++it) {
+  // team's slice for its current tile. A barrier publishes it before it is read.
+  if (p.n_tiles == 1) {
+    if (et < BN) s_bias[et] = (p.bias != nullptr && et < p.Cout) ? __ldg(p.bias + et) : 0.f;
+    asm volatile("bar.sync 3, 256;" ::: "memory");
+  }
+  const float* bias_s = p.n_tiles == 1 ? s_bias : s_bias + team * 256;
+  for (int it = team; !aborted; it += 2) {
+    const long long tile_ll = static_cast<long long>(blockIdx.x) + static_cast<long long>(it) * gridDim.x;
+    if (tile_ll >= p.total_tiles) break;
+    const int tile = static_cast<int>(tile_ll);
     const TileCoord tc = decode_tile(p, tile);
     const int n_tile = tc.n_tile, twi = tc.twi, thi = tc.thi, img = tc.img;
     const int oh = thi * p.th + rh, ow = twi * p.tw + rw;
@@ -438,70 +452,72 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
     const uint8_t* rrow = reinterpret_cast<const uint8_t*>(p.residual) +
                           (static_cast<size_t>(img) * p.res_n_stride + static_cast<size_t>(oh) * p.res_h_stride +
                            static_cast<size_t>(ow) * p.res_ld) * 2;
-    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
     const int colbase = n_tile * BN;
     const int col_limit = min(p.Cout, colbase + BN);
     const int nblk = (col_limit - colbase + 63) / 64;
-    const float* bias_s = s_bias;
     if (p.n_tiles > 1) {
-      float* dst = s_bias + (it & 1) * 256;
-      if (et < BN) dst[et] = (p.bias != nullptr && colbase + et < p.Cout) ? __ldg(p.bias + colbase + et) : 0.f;
-      bias_s = dst;
+      float* dst = s_bias + team * 256;
+      for (int i = tt; i < BN; i += 128) dst[i] = (p.bias != nullptr && colbase + i < p.Cout) ? __ldg(p.bias + colbase + i) : 0.f;
     }
-    for (int blk = 0; blk < nblk; ++blk, ++blk_count) {
-      const uint32_t buf = stage0 + (blk_count & 1u) * kStageTileBytes;
-      const int c = blk * 2 + half;                 // this warp's 32-column TMEM chunk
-      const int co0 = colbase + c * 32;
-      const bool have_cols = co0 < col_limit;
-      uint4 rpre[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-      if (res_pre && valid && have_cols) {
+    for (int blk = 0; blk < nblk; ++blk) {
+      const int co0 = colbase + blk * 64;
+      uint4 rpre[8];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
+      for (int g = 0; g < 8; ++g) rpre[g] = make_uint4(0, 0, 0, 0);
+      if (res_pre && valid) {
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
           // a ragged last group still reads 16 bytes: the row pitch is a multiple of 8 elements and
           // columns past Cout are clipped by the store
           if (co0 + g * 8 < col_limit) rpre[g] = *reinterpret_cast<const uint4*>(rrow + (co0 + g * 8) * 2);
         }
       }
-      // One warp waits for the accumulator; the others sleep at the named barrier, which wakes them
-      // faster than eight separate polls would. The same thread makes sure that the staging buffer
-      // of two blocks ago has been read out and samples the abort flag for everybody, because warps
-      // that meet at barriers must all leave together.
-      if (warp == 2) {
+      // The leader warp waits for the accumulator; the other warps sleep at the named barrier, which
+      // wakes them faster than separate polls would. The same thread makes sure that the previous
+      // block has been read out of the staging buffer and samples the abort flag for the team,
+      // because warps that meet at barriers must all leave together.
+      if (leader_warp) {
         if (blk == 0) {
-          mbar_wait(tfull0 + 8u * acc, acc_ph, abort_flag, kStatusTimeoutEpilogue);
+          mbar_wait(tfull, acc_ph, abort_flag, kStatusTimeoutEpilogue);
           if (issuer) trace_mark(p, it, 4);
         }
         if (lane == 0) {
-          asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           *abort_sample = *abort_flag;
         }
       }
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + team) : "memory");
       if (*abort_sample != 0) { aborted = true; break; }
       if (blk == 0) tc_fence_after();
       if (issuer && blk == nblk - 1) trace_mark(p, it, 8);
-      if (have_cols) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_row + c * 32, v);
-        tmem_ld_wait_dep(v);
-        if (issuer && blk == nblk - 1) trace_mark(p, it, 9);
-        if (valid) {
-          const uint32_t srow = buf + row * 128;
-          const uint32_t chunk0 = static_cast<uint32_t>(half * 4), row7 = static_cast<uint32_t>(row & 7);
-          const float* bs = bias_s + c * 32;
-          if (simple) {
-            if (out_bf16) {
-              if (res_pre) staged_chunk<ACT, true, true>(v, bs, rpre, srow, chunk0, row7, p);
-              else staged_chunk<ACT, true, false>(v, bs, rpre, srow, chunk0, row7, p);
-            } else {
-              if (res_pre) staged_chunk<ACT, false, true>(v, bs, rpre, srow, chunk0, row7, p);
-              else staged_chunk<ACT, false, false>(v, bs, rpre, srow, chunk0, row7, p);
-            }
-          } else {
+      const uint32_t srow = buf + row * 128;
+      const uint32_t row7 = static_cast<uint32_t>(row & 7);
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              epilogue8<ACT>(v + g * 8, p, co0 + g * 8, col_limit, nullptr, rrow, in_bf16, 2,
-                             srow + (((chunk0 + g) ^ row7) << 4), bs + g * 8, false);
+      for (int h = 0; h < 2; ++h) {
+        const int c = blk * 2 + h;                 // 32-column TMEM chunk
+        if (co0 + h * 32 < col_limit) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_row + c * 32, v);
+          tmem_ld_wait_dep(v);
+          if (issuer && blk == nblk - 1 && h == 0) trace_mark(p, it, 9);
+          if (valid) {
+            const uint32_t chunk0 = static_cast<uint32_t>(h * 4);
+            const float* bs = bias_s + c * 32;
+            const uint4(&rp)[4] = *reinterpret_cast<const uint4(*)[4]>(&rpre[h * 4]);
+            if (simple) {
+              if (out_bf16) {
+                if (res_pre) staged_chunk<ACT, true, true>(v, bs, rp, srow, chunk0, row7, p);
+                else staged_chunk<ACT, true, false>(v, bs, rp, srow, chunk0, row7, p);
+              } else {
+                if (res_pre) staged_chunk<ACT, false, true>(v, bs, rp, srow, chunk0, row7, p);
+                else staged_chunk<ACT, false, false>(v, bs, rp, srow, chunk0, row7, p);
+              }
+            } else {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                epilogue8<ACT>(v + g * 8, p, co0 + h * 32 + g * 8, col_limit, nullptr, rrow, in_bf16, 2,
+                               srow + (((chunk0 + g) ^ row7) << 4), bs + g * 8, false);
+              }
             }
           }
         }
@@ -510,24 +526,23 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
         if (issuer) trace_mark(p, it, 5);
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(tempty0 + 8u * acc);
+        if (lane == 0) mbar_arrive(tempty);
         if (issuer) trace_mark(p, it, 6);
       }
       fence_proxy_async_smem();
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + team) : "memory");
       if (issuer) {
         if (blk == nblk - 1) trace_mark(p, it, 10);
         asm volatile(
             "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
                 reinterpret_cast<uint64_t>(tmY)),
-            "r"(buf), "r"(colbase + blk * 64), "r"(twi * p.tw), "r"(thi * p.th), "r"(img)
+            "r"(buf), "r"(co0), "r"(twi * p.tw), "r"(thi * p.th), "r"(img)
             : "memory");
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         if (blk == nblk - 1) trace_mark(p, it, 7);
       }
     }
-    acc ^= 1;
-    if (acc == 0) acc_ph ^= 1;
+    acc_ph ^= 1;
   }
   if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
@@ -649,7 +664,7 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), kEpiWarps);
+      mbar_init(tempty_bar(a), p.y_tma ? kTeamWarps : kEpiWarps);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -823,7 +838,7 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (threadIdx.x == 0) {
     for (int s = 0; s < SA; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), 1); }
     for (int s = 0; s < SB; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8u * a, 1); mbar_init(tempty0 + 8u * a, kEpiWarps); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8u * a, 1); mbar_init(tempty0 + 8u * a, p.y_tma ? kTeamWarps : kEpiWarps); }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&tmA);
