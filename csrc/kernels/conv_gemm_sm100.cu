@@ -911,6 +911,21 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if (kb == 0) trace_mark(p, it, 2);
           const uint32_t a_base = a0 + sa * kHaloABytes;
           const uint32_t ksteps = kb == slabs - 1 ? static_cast<uint32_t>(p.last_ksteps) : 4u;
+          if (hp.b_resident && weights_ready) {
+            // Steady state with all weights resident: nine taps, straight-line. Nothing but the
+            // descriptor additions sits between the MMAs, because whatever does is paid in full.
+            const uint64_t ad = adesc_hi | ((a_base & 0x3FFFF) >> 4);
+            const uint64_t bd = bdesc_hi | (((b0 + kb * 9 * kBBytes) & 0x3FFFF) >> 4);
+#pragma unroll
+            for (int t = 0; t < 9; ++t) {
+              const int kh = t / 3, kw = t - 3 * kh;
+              umma_f16_ksteps(d_tmem, ad + (((kh * kHaloCols + kw) * 128) >> 4), bd + ((t * kBBytes) >> 4), p.idesc,
+                              (kb | t) != 0 ? 1u : 0u, ksteps);
+            }
+            umma_commit(a_empty(sa));
+            if (++sa == SA) { sa = 0; pa ^= 1; }
+            continue;
+          }
 #pragma unroll 1
           for (int kh = 0; kh < 3; ++kh) {
             if (hp.b_resident) sb = kb * 3 + kh;

@@ -28,6 +28,7 @@ from ..ir import interp, passes
 from ..ir.graph import Graph, Node
 from ..ir.shape_infer import ShapeInfo, infer_shapes
 from ..ops import nhwc as K
+from ..ops import stem_conv
 from ..ops.base import NativeOp, StatusWord, current_stream_ptr
 from ..ops.conv_gemm import ConvGemm, pack_conv_weight, pack_linear_weight
 from ..ops.nms import MulticlassNMS
@@ -359,6 +360,19 @@ class Lowering:
         n_o, c_o, ho, wo = self.info.shapes[node.outputs[0]]
         pads = interp._pads_2d(node, x.logical(), [kh, kw], strides, node.attr("dilations", [1, 1]))
         pad_t, pad_l = pads[0], pads[1]
+        if stem_conv.eligible(cout, cin, kh, kw, strides[0], pads, node.attr("activation", "none"), self.dtype) \
+                and not (len(node.inputs) > 3 and node.inputs[3]) and x.ld == 8 \
+                and node.outputs[0] not in self.preassigned:
+            y = self.out_nhwc(node.outputs[0], None)
+            bias_np = np.asarray(self.g.initializers[node.inputs[2]], dtype=np.float32) \
+                if len(node.inputs) > 2 and node.inputs[2] else None
+            op = stem_conv.StemConv(x.t, np.asarray(w), y.t, n=n, h=h, w=wd, bias=bias_np,
+                                    act=node.attr("activation", "none"), x_ld=x.ld, y_ld=y.ld,
+                                    x_n_stride=x.n_stride, y_n_stride=y.n_stride, name=f"stem_conv:{node.name}")
+            self.plan.add_native(op, node)
+            op.launch()
+            self.vals[node.outputs[0]] = y
+            return None
         cin_phys = _round8(cin)
         key = (w_name, f"conv{cin_phys}")
         if key not in self.packed:
@@ -378,6 +392,17 @@ class Lowering:
         res = None
         if len(node.inputs) > 3 and node.inputs[3]:
             res = self.as_nhwc(node.inputs[3])
+        if h == 1 and wd == 1 and kh == 1 and kw == 1 and res is None and n > 1:
+            # a 1x1 map per image (squeeze-excite gates): the images become the rows of one GEMM
+            # tile instead of one nearly empty 128-row tile each
+            op = ConvGemm(x.t, wp, y.t, in_shape=(1, 1, n, cin_phys), out_hw=(1, n), cout=cout, bias=bias,
+                          act=node.attr("activation", "none"), act_alpha=node.attr("act_alpha", 0.0),
+                          act_beta=node.attr("act_beta", 0.0), x_ld=x.n_stride, y_ld=y.n_stride,
+                          status=self.plan.status, name=f"conv:{node.name}")
+            self.plan.add_native(op, node)
+            op.launch()
+            self.vals[out_name] = y
+            return None
         op = ConvGemm(x.t, wp, y.t, in_shape=(n, h, wd, cin_phys), out_hw=(ho, wo), cout=cout, kernel=(kh, kw),
                       stride=strides[0], pad=(pad_t, pad_l), bias=bias,
                       residual=res.t if res is not None else None, res_mode=node.attr("res_mode", 0),

@@ -200,3 +200,31 @@ def test_conv_output_paths_agree(cfg, y_tma_mode):
     assert float(ybuf[..., :64].abs().max()) == 0.0
     if ybuf.shape[-1] > 64 + cout:
         assert float(ybuf[..., 64 + cout:].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("act", [None, "relu", "silu"])
+@pytest.mark.parametrize("hw", [(64, 96), (37, 51)])
+def test_stem_conv_matches_fp32_reference(dtype, act, hw):
+    from fastdeploy_b200.ops.stem_conv import StemConv
+    torch.manual_seed(3)
+    n, (h, w) = 3, hw
+    x = torch.zeros(n, h, w, 8, device="cuda", dtype=dtype)
+    x[..., :3] = torch.randn(n, h, w, 3, device="cuda").to(dtype)
+    x[..., 3:] = 7.0        # padding channels must not leak into the result
+    wt = torch.randn(32, 3, 3, 3) * 0.2
+    b = torch.randn(32)
+    ho, wo = (h - 1) // 2 + 1, (w - 1) // 2 + 1
+    y = torch.empty(n, ho, wo, 32, device="cuda", dtype=dtype)
+    op = StemConv(x, wt.numpy(), y, n=n, h=h, w=w, bias=b.numpy(), act=act)
+    op.launch()
+    torch.cuda.synchronize()
+    ref = torch.nn.functional.conv2d(x[..., :3].float().permute(0, 3, 1, 2), wt.cuda(), b.cuda(), stride=2, padding=1)
+    if act == "relu":
+        ref = torch.relu(ref)
+    elif act == "silu":
+        ref = torch.nn.functional.silu(ref)
+    ref = ref.permute(0, 2, 3, 1)
+    tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
+    err = (y.float() - ref).abs().max().item()
+    assert err <= tol * max(1.0, ref.abs().max().item()), err
