@@ -84,7 +84,20 @@ class StatusWord:
         return self.t.data_ptr()
 
     def check(self, what: str = "kernel") -> None:
+        """Blocking read of the device word (waits for everything queued on the current stream)."""
         v = int(self.t.item())
+        if v != 0:
+            self.t.zero_()
+            raise RuntimeError(f"{what}: device status {v} ({self.MESSAGES.get(v, 'unknown')})")
+
+    def snapshot_async(self, host: torch.Tensor) -> None:
+        """Queues a copy of the word into pinned ``host`` (int32[1]) on the current stream. A pipelined
+        caller reads it with :meth:`check_snapshot` once its own completion event has fired, so that
+        checking one batch never waits for the batches queued behind it."""
+        host.copy_(self.t, non_blocking=True)
+
+    def check_snapshot(self, host: torch.Tensor, what: str = "kernel") -> None:
+        v = int(host[0])
         if v != 0:
             self.t.zero_()
             raise RuntimeError(f"{what}: device status {v} ({self.MESSAGES.get(v, 'unknown')})")

@@ -224,6 +224,7 @@ class _GpuSlot:
         self.sf_host = torch.empty(n, 2, dtype=torch.float32).pin_memory()
         self.out_host = torch.empty(n, out_rows, 6, dtype=torch.float32).pin_memory()
         self.num_host = torch.empty(n, dtype=torch.int32).pin_memory()
+        self.status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self.copied = torch.cuda.Event()
         self.done = torch.cuda.Event()
         self.pre = None
@@ -239,7 +240,7 @@ class PendingDetection:
 
     def result(self) -> List[DetectionResult]:
         self.slot.done.synchronize()
-        self.status.check("detection")
+        self.status.check_snapshot(self.slot.status_host, "detection")
         num = self.slot.num_host[:self.n].numpy()
         out = self.slot.out_host[:self.n].numpy()
         rows = np.concatenate([out[i, :num[i]] for i in range(self.n)], 0) if self.n else np.zeros((0, 6), np.float32)
@@ -353,10 +354,11 @@ class PPDetBase(FastDeployModel):
             plan.run()
             slot.out_host[:n].copy_(nms.out, non_blocking=True)
             slot.num_host[:n].copy_(nms.out_num, non_blocking=True)
+            plan.status.snapshot_async(slot.status_host)
             slot.done.record(compute)
             rt.gpu_launches += plan.native_kernel_launches + 1
             self.h2d_bytes_last = h2d
-            self.d2h_bytes_last = n * nms.out.shape[1] * 6 * 4 + n * 4
+            self.d2h_bytes_last = n * nms.out.shape[1] * 6 * 4 + n * 4 + 4
         return PendingDetection(slot, n, plan.status)
 
 
