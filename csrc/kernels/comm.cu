@@ -1,0 +1,241 @@
+// Peer-memory communication layer for one process per GPU.
+//
+// * symmetric heap: every rank allocates the same-sized device buffer here and publishes its CUDA
+//   IPC handle; peers open it and get a plain device pointer that their kernels load from and store
+//   to over NVLink (no library kernel ever receives such a pointer);
+// * signals: 32-bit counters inside the heap, bumped with system-scope atomics after the data they
+//   cover, waited for with a clock budget; a wait that runs out records kStatusTimeoutPeer in the
+//   status word and the kernel returns, so the context stays usable;
+// * collectives written directly on top: barrier, all-gather (pull), reduce-scatter and all-reduce
+//   (pull + sum), and the slot reduction that finishes the fused GEMM -> reduce-scatter.
+//
+// The reference has no communication layer at all (it scales by independent instances,
+// serving/src/fastdeploy_runtime.cc); this file has no counterpart there.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "fdb_common.h"
+
+namespace fdb {
+
+constexpr int kMaxPeers = 8;
+constexpr long long kPeerWaitClocks = 2000000000LL;   // about one second at 1.9 GHz
+constexpr int kStatusTimeoutPeerCode = 4;
+
+struct PeerPtrs {
+  void* p[kMaxPeers];
+};
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add(unsigned* p, unsigned v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Spins until *flag >= target or the budget runs out (then the status word gets the peer code).
+__device__ __forceinline__ bool wait_ge(const unsigned* flag, unsigned target, int* status) {
+  const long long t0 = clock64();
+  for (unsigned it = 0;; ++it) {
+    if (static_cast<int>(ld_acquire_sys(flag) - target) >= 0) return true;
+    if ((it & 63u) == 63u) {
+      if (clock64() - t0 > kPeerWaitClocks) {
+        if (status != nullptr) atomicExch(status, kStatusTimeoutPeerCode);
+        return false;
+      }
+      __nanosleep(200);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ barrier
+// flags[r] on every rank counts arrivals of rank r. Each rank bumps its slot on all peers, then waits
+// until all slots of its own array reach the epoch.
+__global__ void comm_barrier_kernel(PeerPtrs flags, int world, int rank, unsigned epoch, int* status) {
+  const int t = threadIdx.x;
+  if (t < world) {
+    __threadfence_system();
+    red_release_sys_add(static_cast<unsigned*>(flags.p[t]) + rank, 1u);
+    wait_ge(static_cast<const unsigned*>(flags.p[rank]) + t, epoch, status);
+  }
+}
+
+// ------------------------------------------------------------------ pull collectives (16-bit or fp32 payloads)
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// out[r * count + i] = src_r[i] for every rank r (16-byte vectors; count * sizeof(T) % 16 == 0)
+__global__ void allgather_pull_kernel(PeerPtrs src, uint4* out, long long vecs_per_rank, int world, int rank) {
+  const long long total = vecs_per_rank * world;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    // start with the next rank so that the ranks do not all read the same peer at once
+    const int step = static_cast<int>(i / vecs_per_rank);
+    const int r = (rank + 1 + step) % world;
+    const long long k = i - step * vecs_per_rank;
+    out[r * vecs_per_rank + k] = static_cast<const uint4*>(src.p[r])[k];
+  }
+}
+
+// out[i] = sum_r src_r[offset + i], i < count: reduce-scatter with offset = rank * count, all-reduce with
+// offset = 0 and count = everything. Eight 16-bit (or four fp32) elements per thread step.
+template <typename T>
+__global__ void reduce_pull_kernel(PeerPtrs src, T* out, long long offset, long long count, int world, int rank) {
+  constexpr int kVec = 16 / sizeof(T);
+  const long long vecs = count / kVec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < vecs;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[kVec];
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) acc[j] = 0.f;
+    for (int s = 0; s < world; ++s) {
+      const int r = (rank + s) % world;
+      const uint4 v = reinterpret_cast<const uint4*>(static_cast<const T*>(src.p[r]) + offset)[i];
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) acc[j] += to_f<T>(e[j]);
+    }
+    uint4 o;
+    T* e = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) e[j] = from_f<T>(acc[j]);
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
+// ------------------------------------------------------------------ slot reduction of the fused GEMM -> reduce-scatter
+// slots: [world][rows][ld] partial results written by the ranks' GEMM epilogues into this rank's heap;
+// counters[b] counts the stores that have landed for 128-row block b. One CTA per (row block, column
+// chunk) waits for its block, then sums the world slots in fp32, adds the bias and writes the output.
+template <typename T>
+__global__ void __launch_bounds__(256) slot_reduce_kernel(const T* slots, const unsigned* counters, unsigned target,
+                                                          T* out, const float* bias, int rows, int cols, int ld,
+                                                          int out_ld, int world, int* status) {
+  __shared__ int ok;
+  const int blk = blockIdx.x;
+  if (threadIdx.x == 0) ok = wait_ge(counters + blk, target, status) ? 1 : 0;
+  __syncthreads();
+  if (!ok) return;
+  constexpr int kVec = 16 / sizeof(T);
+  const int row0 = blk * 128;
+  const int nrow = min(128, rows - row0);
+  const int vec_cols = cols / kVec;
+  const int chunk = blockIdx.y, chunks = gridDim.y;
+  for (int idx = threadIdx.x + chunk * blockDim.x; idx < nrow * vec_cols; idx += blockDim.x * chunks) {
+    const int r = idx / vec_cols, c = (idx - r * vec_cols) * kVec;
+    float acc[kVec];
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) acc[j] = bias != nullptr ? bias[c + j] : 0.f;
+    for (int s = 0; s < world; ++s) {
+      const uint4 v = *reinterpret_cast<const uint4*>(slots + (static_cast<size_t>(s) * rows + row0 + r) * ld + c);
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) acc[j] += to_f<T>(e[j]);
+    }
+    uint4 o;
+    T* e = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) e[j] = from_f<T>(acc[j]);
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(row0 + r) * out_ld + c) = o;
+  }
+}
+
+}  // namespace fdb
+
+using namespace fdb;
+
+// ------------------------------------------------------------------ heap + IPC
+FDB_API void* fdb_comm_alloc(long long bytes) {
+  void* p = nullptr;
+  if (cudaMalloc(&p, static_cast<size_t>(bytes)) != cudaSuccess) { set_error("comm: cudaMalloc failed"); return nullptr; }
+  cudaMemset(p, 0, static_cast<size_t>(bytes));
+  return p;
+}
+FDB_API int fdb_comm_free(void* p) { return cudaFree(p) == cudaSuccess ? 0 : -1; }
+FDB_API int fdb_comm_ipc_handle(void* p, void* out64) {
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) { set_error("comm: cudaIpcGetMemHandle failed"); return -1; }
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(out64, &h, 64);
+  return 0;
+}
+FDB_API void* fdb_comm_ipc_open(const void* handle64) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) { set_error(cudaGetErrorString(e)); return nullptr; }
+  return p;
+}
+FDB_API int fdb_comm_ipc_close(void* p) { return cudaIpcCloseMemHandle(p) == cudaSuccess ? 0 : -1; }
+
+static int check_launch(const char* what) {
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_error(cudaGetErrorString(e)); return -1; }
+  (void)what;
+  return 0;
+}
+
+FDB_API int fdb_comm_barrier(void* const* flag_ptrs, int world, int rank, unsigned epoch, int* status, void* stream) {
+  if (world < 1 || world > kMaxPeers) { set_error("comm: 1..8 ranks"); return -1; }
+  PeerPtrs f{};
+  for (int i = 0; i < world; ++i) f.p[i] = flag_ptrs[i];
+  comm_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, world, rank, epoch, status);
+  return check_launch("barrier");
+}
+
+FDB_API int fdb_comm_allgather(void* const* src_ptrs, void* out, long long bytes_per_rank, int world, int rank,
+                               void* stream) {
+  if (world < 1 || world > kMaxPeers || bytes_per_rank % 16 != 0) { set_error("comm: all-gather needs 16-byte multiples"); return -1; }
+  PeerPtrs s{};
+  for (int i = 0; i < world; ++i) s.p[i] = src_ptrs[i];
+  const long long vecs = bytes_per_rank / 16;
+  const int grid = static_cast<int>(std::min<long long>((vecs * world + 255) / 256, 4 * sm_count()));
+  allgather_pull_kernel<<<std::max(grid, 1), 256, 0, static_cast<cudaStream_t>(stream)>>>(s, static_cast<uint4*>(out), vecs,
+                                                                                       world, rank);
+  return check_launch("allgather");
+}
+
+// dtype: kF16 | kBF16 | kF32; out[i] = sum over ranks of src_r[offset + i]
+FDB_API int fdb_comm_reduce(void* const* src_ptrs, void* out, long long offset, long long count, int dtype, int world,
+                            int rank, void* stream) {
+  const int es = dtype == kF32 ? 4 : 2;
+  if (world < 1 || world > kMaxPeers || (count * es) % 16 != 0 || (offset * es) % 16 != 0) {
+    set_error("comm: reduce needs 16-byte multiples"); return -1;
+  }
+  PeerPtrs s{};
+  for (int i = 0; i < world; ++i) s.p[i] = src_ptrs[i];
+  const long long vecs = count * es / 16;
+  const int grid = std::max(1, static_cast<int>(std::min<long long>((vecs + 255) / 256, 4 * sm_count())));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == kF32) reduce_pull_kernel<float><<<grid, 256, 0, st>>>(s, static_cast<float*>(out), offset, count, world, rank);
+  else if (dtype == kBF16) reduce_pull_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(s, static_cast<__nv_bfloat16*>(out), offset, count, world, rank);
+  else reduce_pull_kernel<__half><<<grid, 256, 0, st>>>(s, static_cast<__half*>(out), offset, count, world, rank);
+  return check_launch("reduce");
+}
+
+FDB_API int fdb_comm_slot_reduce(const void* slots, const unsigned* counters, unsigned target, void* out,
+                                 const float* bias, int rows, int cols, int ld, int out_ld, int world, int dtype,
+                                 int* status, void* stream) {
+  if (cols % 8 != 0 || ld % 8 != 0 || out_ld % 8 != 0) { set_error("comm: slot reduce needs 8-element multiples"); return -1; }
+  const dim3 grid((rows + 127) / 128, std::max(1, std::min(8, cols / 256)));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == kBF16)
+    slot_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(slots), counters, target,
+                                                           static_cast<__nv_bfloat16*>(out), bias, rows, cols, ld, out_ld, world, status);
+  else if (dtype == kF16)
+    slot_reduce_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(slots), counters, target,
+                                                    static_cast<__half*>(out), bias, rows, cols, ld, out_ld, world, status);
+  else { set_error("comm: slot reduce takes fp16 or bf16"); return -1; }
+  return check_launch("slot_reduce");
+}

@@ -64,7 +64,22 @@ struct ConvGemmDesc {
   // elements between image rows (0 = W * ld): lets heads of a [B, S, H*D] tensor act as image rows
   long long x_h_stride, y_h_stride, res_h_stride;
   int y_tma_mode;        // -1/1: TMA tensor stores for 16-bit outputs when possible, 0: direct stores
-  long long* trace;      // optional device buffer of 48*8 int64 for the timeline probe (null = off)
+  long long* trace;      // optional device buffer of 32*12 int64 for the timeline probe (null = off)
+  // Tensor parallelism over peer memory (plain GEMMs only: 1x1, one image row of W = M rows).
+  //   peer_mode 1, all-gather -> GEMM: the M rows of A live in peer_world equal shards of peer_rows
+  //     rows; shard r is read straight from peer_ptrs[r] (this rank's own shard included) by TMA.
+  //   peer_mode 2, GEMM -> reduce-scatter: the 128-row output block whose rows belong to rank o is
+  //     stored by TMA into slot peer_rank of o's slot buffer peer_ptrs[o] ([world][peer_rows][y_ld])
+  //     and o's counter for that block (peer_counters[o][block]) is bumped once per store.
+  int peer_mode, peer_rows, peer_rank, peer_world;
+  void* peer_ptrs[8];
+  unsigned int* peer_counters[8];
+};
+
+// Device-resident table of the peers' tensor maps and counters (host-written before any launch).
+struct PeerTable {
+  alignas(64) CUtensorMap maps[8];
+  unsigned int* counters[8];
 };
 
 struct ConvGemmParams {
@@ -87,6 +102,8 @@ struct ConvGemmParams {
   long long y_h_stride, res_h_stride;
   int b_batched;
   int y_tma;   // 16-bit output leaves through shared-memory staging + TMA tensor stores
+  const PeerTable* peer;   // null unless peer_mode != 0
+  int peer_mode, peer_rows, peer_rank;
   long long* trace;  // optional: CTA 0 records clock64() at pipeline events of its first tiles
 };
 
@@ -533,12 +550,31 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
       asm volatile("bar.sync %0, 128;" ::"r"(1 + team) : "memory");
       if (issuer) {
         if (blk == nblk - 1) trace_mark(p, it, 10);
-        asm volatile(
-            "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
-                reinterpret_cast<uint64_t>(tmY)),
-            "r"(buf), "r"(co0), "r"(twi * p.tw), "r"(thi * p.th), "r"(img)
-            : "memory");
-        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        if (p.peer_mode == 2) {
+          // reduce-scatter: the block goes to the rank that owns these rows, into this rank's slot
+          const int row = twi * p.tw;
+          const int owner = row / p.peer_rows;
+          const int local = row - owner * p.peer_rows;
+          asm volatile(
+              "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                  reinterpret_cast<uint64_t>(&p.peer->maps[owner])),
+              "r"(buf), "r"(co0), "r"(p.peer_rank * p.peer_rows + local), "r"(0), "r"(0)
+              : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          // the signal may only follow the data: wait for the store to complete, then release
+          asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+          asm volatile("fence.proxy.async;" ::: "memory");
+          __threadfence_system();
+          asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.peer->counters[owner] + local / kBM), "r"(1u)
+                       : "memory");
+        } else {
+          asm volatile(
+              "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                  reinterpret_cast<uint64_t>(tmY)),
+              "r"(buf), "r"(co0), "r"(twi * p.tw), "r"(thi * p.th), "r"(img)
+              : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
         if (blk == nblk - 1) trace_mark(p, it, 7);
       }
     }
@@ -705,7 +741,12 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               armed |= 1u << s;
               armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
               const uint32_t a_dst = tile0 + s * Cfg::kStageBytes;
-              tma_load_4d(a_dst, &tmA, full_bar(s), kb * kBK, x0 + kw, y0 + kh, img);
+              if (p.peer_mode == 1) {
+                const int owner = (twi * p.tw) / p.peer_rows;
+                tma_load_4d(a_dst, &p.peer->maps[owner], full_bar(s), kb * kBK, twi * p.tw - owner * p.peer_rows, 0, 0);
+              } else {
+                tma_load_4d(a_dst, &tmA, full_bar(s), kb * kBK, x0 + kw, y0 + kh, img);
+              }
               if (p.b_batched)
                 tma_load_4d(a_dst + Cfg::kABytes, &tmB, full_bar(s), kcol, n_tile * BN, thi * p.th, img);
               else
@@ -986,7 +1027,11 @@ struct ConvGemmOp : Op {
   int halo = 0;          // 1: conv3x3_halo_kernel
   HaloParams hp{};
   int halo_smem = 0;
+  PeerTable* peer_dev = nullptr;
   int launch(cudaStream_t stream) override;
+  ~ConvGemmOp() override {
+    if (peer_dev != nullptr) cudaFree(peer_dev);
+  }
 };
 
 template <int BN, int ACT>
@@ -1279,6 +1324,59 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
     }
     if (!p.y_tma) op->tmY = op->tmA;   // a valid map is still passed; the kernel does not touch it
   }
+  p.peer = nullptr;
+  p.peer_mode = 0; p.peer_rows = 0; p.peer_rank = 0;
+  if (d->peer_mode != 0) {
+    const bool gemm_shape = d->KH == 1 && d->KW == 1 && d->stride == 1 && d->H == 1 && d->N == 1 && d->Ho == 1 &&
+                            d->pad_h == 0 && d->pad_w == 0 && !op->halo && !d->w_batched && p.tw == kBM && p.th == 1;
+    if (!gemm_shape || d->peer_world < 1 || d->peer_world > 8 || d->peer_rows % kBM != 0 ||
+        d->W != d->peer_rows * d->peer_world || d->peer_rank < 0 || d->peer_rank >= d->peer_world ||
+        (d->peer_mode != 1 && d->peer_mode != 2)) {
+      set_error("conv_gemm: peer modes take a plain GEMM whose M is world * peer_rows, peer_rows a multiple of 128");
+      delete op; return nullptr;
+    }
+    if (d->peer_mode == 2 && !p.y_tma) {
+      set_error("conv_gemm: reduce-scatter mode needs the TMA store path (16-bit output, aligned rows)");
+      delete op; return nullptr;
+    }
+    PeerTable host{};
+    for (int r = 0; r < d->peer_world; ++r) {
+      if (d->peer_ptrs[r] == nullptr || (d->peer_mode == 2 && d->peer_counters[r] == nullptr)) {
+        set_error("conv_gemm: missing peer pointer"); delete op; return nullptr;
+      }
+      CUresult res;
+      if (d->peer_mode == 1) {
+        cuuint64_t dims[4] = {(cuuint64_t)d->Cin, (cuuint64_t)d->peer_rows, 1, 1};
+        cuuint64_t strides[3] = {(cuuint64_t)d->x_ld * 2, (cuuint64_t)d->peer_rows * d->x_ld * 2,
+                                 (cuuint64_t)d->peer_rows * d->x_ld * 2};
+        cuuint32_t box[4] = {(cuuint32_t)kBK, (cuuint32_t)p.tw, 1, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        res = enc(&host.maps[r], tdt, 4, d->peer_ptrs[r], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      } else {
+        const CUtensorMapDataType ydt =
+            d->out_dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        const cuuint64_t rows = (cuuint64_t)d->peer_rows * d->peer_world;
+        cuuint64_t dims[4] = {(cuuint64_t)d->Cout, rows, 1, 1};
+        cuuint64_t strides[3] = {(cuuint64_t)d->y_ld * 2, rows * d->y_ld * 2, rows * d->y_ld * 2};
+        cuuint32_t box[4] = {64, (cuuint32_t)p.tw, 1, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        res = enc(&host.maps[r], ydt, 4, d->peer_ptrs[r], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        host.counters[r] = d->peer_counters[r];
+      }
+      if (res != CUDA_SUCCESS) {
+        set_error("conv_gemm: encode peer tensor map failed, CUresult " + std::to_string((int)res));
+        delete op; return nullptr;
+      }
+    }
+    if (cudaMalloc(reinterpret_cast<void**>(&op->peer_dev), sizeof(PeerTable)) != cudaSuccess ||
+        cudaMemcpy(op->peer_dev, &host, sizeof(PeerTable), cudaMemcpyHostToDevice) != cudaSuccess) {
+      set_error("conv_gemm: peer table allocation failed"); delete op; return nullptr;
+    }
+    p.peer = op->peer_dev;
+    p.peer_mode = d->peer_mode; p.peer_rows = d->peer_rows; p.peer_rank = d->peer_rank;
+  }
   {
     const unsigned long long one = 1ull << 40;
     const long long dmax = std::max(p.n_tiles, std::max(p.tiles_w, p.tiles_h));
@@ -1291,6 +1389,9 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   }
   return op;
 }
+
+// Size of the descriptor as this library was compiled: the Python mirror checks it at load time.
+FDB_API int fdb_conv_gemm_desc_size() { return static_cast<int>(sizeof(ConvGemmDesc)); }
 
 // Introspection for tests and the autotuner: tile_w, tile_h, block_n, grid, total tiles.
 FDB_API void fdb_conv_gemm_info(void* handle, int* out5) {

@@ -9,7 +9,7 @@ TensorRT / Paddle Inference / ONNX Runtime
 from __future__ import annotations
 
 import ctypes
-from typing import Optional, Tuple
+from typing import Sequence, Optional, Tuple
 
 import torch
 
@@ -38,6 +38,9 @@ class _ConvGemmDesc(ctypes.Structure):
         ("x_h_stride", ctypes.c_longlong), ("y_h_stride", ctypes.c_longlong), ("res_h_stride", ctypes.c_longlong),
         ("y_tma_mode", ctypes.c_int),
         ("trace", ctypes.c_void_p),
+        ("peer_mode", ctypes.c_int), ("peer_rows", ctypes.c_int), ("peer_rank", ctypes.c_int),
+        ("peer_world", ctypes.c_int),
+        ("peer_ptrs", ctypes.c_void_p * 8), ("peer_counters", ctypes.c_void_p * 8),
     ]
 
 
@@ -48,6 +51,9 @@ def _lib():
         lib.fdb_conv_gemm_create.argtypes = [ctypes.POINTER(_ConvGemmDesc)]
         lib.fdb_conv_gemm_info.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]
         lib.fdb_conv_gemm_variant.argtypes = [ctypes.c_void_p]
+        if lib.fdb_conv_gemm_desc_size() != ctypes.sizeof(_ConvGemmDesc):
+            raise RuntimeError("libfdb200_kernels.so is out of date: ConvGemmDesc layout differs; rebuild with "
+                               "`python -m fastdeploy_b200._native.build`")
         lib._conv_gemm_ready = True
     return lib
 
@@ -80,7 +86,9 @@ class ConvGemm(NativeOp):
                  max_ctas: int = 0, x_n_stride: int = 0, y_n_stride: int = 0, res_n_stride: int = 0,
                  halo_mode: int = -1, w_batched: bool = False, w_ld: int = 0, w_h_stride: int = 0,
                  w_n_stride: int = 0, x_h_stride: int = 0, y_h_stride: int = 0, res_h_stride: int = 0,
-                 y_tma_mode: int = -1, trace: Optional[torch.Tensor] = None, name: str = "conv_gemm"):
+                 y_tma_mode: int = -1, trace: Optional[torch.Tensor] = None, name: str = "conv_gemm",
+                 peer_mode: int = 0, peer_rows: int = 0, peer_rank: int = 0, peer_world: int = 0,
+                 peer_ptrs: Optional[Sequence[int]] = None, peer_counters: Optional[Sequence[int]] = None):
         n, h, w_, cin = in_shape
         d = _ConvGemmDesc()
         self.status = status or StatusWord(x.device)
@@ -105,6 +113,11 @@ class ConvGemm(NativeOp):
         d.y_tma_mode = y_tma_mode
         d.trace = trace.data_ptr() if trace is not None else None
         self.trace = trace
+        d.peer_mode, d.peer_rows, d.peer_rank, d.peer_world = peer_mode, peer_rows, peer_rank, peer_world
+        for i, ptr in enumerate(peer_ptrs or []):
+            d.peer_ptrs[i] = ptr
+        for i, ptr in enumerate(peer_counters or []):
+            d.peer_counters[i] = ptr
         if bias is not None:
             assert bias.dtype == torch.float32
         if residual is not None:
