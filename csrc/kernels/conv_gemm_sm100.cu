@@ -74,6 +74,11 @@ struct ConvGemmDesc {
   int peer_mode, peer_rows, peer_rank, peer_world;
   void* peer_ptrs[8];
   unsigned int* peer_counters[8];
+  // peer_mode 1 only: x is this rank's gathered buffer [M][x_ld] (same heap offset on every rank, rank r's
+  // shard valid at rows r * peer_rows of its own buffer, peer_ptrs[r] = base of rank r's buffer);
+  // peer_ready = M / 128 flags in local memory; peer_copiers = CTAs set aside to pull the remote shards.
+  unsigned int* peer_ready;
+  int peer_copiers;
 };
 
 // Device-resident table of the peers' tensor maps and counters (host-written before any launch).
@@ -104,6 +109,13 @@ struct ConvGemmParams {
   int y_tma;   // 16-bit output leaves through shared-memory staging + TMA tensor stores
   const PeerTable* peer;   // null unless peer_mode != 0
   int peer_mode, peer_rows, peer_rank;
+  int gemm_ctas;           // CTAs that run the GEMM roles; the rest of the grid (peer_mode 1) are copiers
+  int peer_world, peer_rot;       // all-gather mode: ranks, and the tile-row rotation that puts local rows first
+  unsigned peer_epoch;            // value the ready flags take in this launch
+  unsigned* ready;                // [tiles_w] flags of the gathered buffer, written by the copier CTAs
+  uint8_t* gather_dst;            // this rank's gathered A buffer ([M][x_ld] 16-bit)
+  const uint8_t* peer_src[8];     // every rank's gathered buffer (rank r's shard is valid in its own)
+  long long gather_row_bytes;     // bytes per row of A
   long long* trace;  // optional: CTA 0 records clock64() at pipeline events of its first tiles
 };
 
@@ -458,12 +470,30 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
     asm volatile("bar.sync 3, 256;" ::: "memory");
   }
   const float* bias_s = p.n_tiles == 1 ? s_bias : s_bias + team * 256;
+  unsigned int* pending_counter = nullptr;   // issuer only: stores of the previous tile not yet signalled
+  unsigned pending_stores = 0;
+  auto flush_signal = [&]() {
+    if (pending_counter != nullptr) {
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      asm volatile("fence.proxy.async;" ::: "memory");
+      __threadfence_system();
+      asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(pending_counter), "r"(pending_stores) : "memory");
+      pending_counter = nullptr;
+      pending_stores = 0;
+    }
+  };
   for (int it = team; !aborted; it += 2) {
-    const long long tile_ll = static_cast<long long>(blockIdx.x) + static_cast<long long>(it) * gridDim.x;
+    const long long tile_ll = static_cast<long long>(blockIdx.x) + static_cast<long long>(it) * p.gemm_ctas;
     if (tile_ll >= p.total_tiles) break;
+    if (issuer) flush_signal();
     const int tile = static_cast<int>(tile_ll);
     const TileCoord tc = decode_tile(p, tile);
-    const int n_tile = tc.n_tile, twi = tc.twi, thi = tc.thi, img = tc.img;
+    const int n_tile = tc.n_tile, thi = tc.thi, img = tc.img;
+    int twi = tc.twi;
+    if (p.peer_mode == 1) {   // same rotation as the producer: local rows first
+      twi += p.peer_rot;
+      if (twi >= p.tiles_w) twi -= p.tiles_w;
+    }
     const int oh = thi * p.th + rh, ow = twi * p.tw + rw;
     const bool valid = rh < p.th && oh < p.Ho && ow < p.Wo;
     const uint8_t* rrow = reinterpret_cast<const uint8_t*>(p.residual) +
@@ -561,12 +591,11 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
               "r"(buf), "r"(co0), "r"(p.peer_rank * p.peer_rows + local), "r"(0), "r"(0)
               : "memory");
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          // the signal may only follow the data: wait for the store to complete, then release
-          asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-          asm volatile("fence.proxy.async;" ::: "memory");
-          __threadfence_system();
-          asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.peer->counters[owner] + local / kBM), "r"(1u)
-                       : "memory");
+          // The signal may only follow the data, and waiting for a remote store to complete takes
+          // microseconds: the wait is deferred to the start of this team's next tile (or the end of
+          // the kernel), where it overlaps the tensor-core work of the tiles in between.
+          pending_counter = p.peer->counters[owner] + local / kBM;
+          ++pending_stores;
         } else {
           asm volatile(
               "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
@@ -580,7 +609,10 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
     }
     acc_ph ^= 1;
   }
-  if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  if (issuer) {
+    flush_signal();
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
 }
 
 template <int BN, int ACT>
@@ -599,9 +631,14 @@ __device__ __forceinline__ void epilogue_loop(const ConvGemmParams& p, uint32_t 
   const int out_es = p.out_dtype == kF32 ? 4 : 2;
   int acc = 0;
   uint32_t acc_ph = 0;
-  for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+  for (int tile = blockIdx.x; tile < p.total_tiles; tile += p.gemm_ctas) {
     const TileCoord tc = decode_tile(p, tile);
-    const int n_tile = tc.n_tile, twi = tc.twi, thi = tc.thi, img = tc.img;
+    const int n_tile = tc.n_tile, thi = tc.thi, img = tc.img;
+    int twi = tc.twi;
+    if (p.peer_mode == 1) {   // same rotation as the producer: local rows first
+      twi += p.peer_rot;
+      if (twi >= p.tiles_w) twi -= p.tiles_w;
+    }
     if (!mbar_wait(tfull_bar(acc), acc_ph, abort_flag, kStatusTimeoutEpilogue)) break;
     tc_fence_after();
     const int row = q * 32 + lane;
@@ -716,19 +753,63 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (blockIdx.x >= p.gemm_ctas) {
+    // ------------------------------------------------------------ copier CTA (all-gather -> GEMM)
+    // Pulls the remote shards of A over NVLink into this rank's gathered buffer, one 128-row block
+    // at a time in the order the GEMM CTAs will want them, and publishes a flag per block. Each
+    // remote row crosses NVLink exactly once however many column tiles later read it from HBM / L2.
+    const int copiers = static_cast<int>(gridDim.x) - p.gemm_ctas;
+    const int c = static_cast<int>(blockIdx.x) - p.gemm_ctas;
+    const int per_shard = p.peer_rows / p.tw;
+    const long long blk_vecs = static_cast<long long>(p.tw) * p.gather_row_bytes / 16;
+    for (int j = per_shard + c; j < p.tiles_w; j += copiers) {      // rotated order, remote blocks only
+      int b = j + p.peer_rot;
+      if (b >= p.tiles_w) b -= p.tiles_w;
+      const int owner = b / per_shard;
+      const long long off = static_cast<long long>(b) * p.tw * p.gather_row_bytes;
+      const uint4* from = reinterpret_cast<const uint4*>(p.peer_src[owner] + off);
+      uint4* to = reinterpret_cast<uint4*>(p.gather_dst + off);
+      long long i = threadIdx.x;
+      for (; i + 3 * kThreads < blk_vecs; i += 4 * kThreads) {      // four loads in flight per thread
+        const uint4 v0 = from[i], v1 = from[i + kThreads], v2 = from[i + 2 * kThreads], v3 = from[i + 3 * kThreads];
+        to[i] = v0; to[i + kThreads] = v1; to[i + 2 * kThreads] = v2; to[i + 3 * kThreads] = v3;
+      }
+      for (; i < blk_vecs; i += kThreads) to[i] = from[i];
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) st_release_gpu(p.ready + b, p.peer_epoch);
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int s = 0;
       uint32_t ph = 0;
       uint32_t armed = 0, armed_parity = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += p.gemm_ctas) {
         const TileCoord tc = decode_tile(p, tile);
-        const int n_tile = tc.n_tile, twi = tc.twi, thi = tc.thi, img = tc.img;
+        const int n_tile = tc.n_tile, thi = tc.thi, img = tc.img;
+        int twi = tc.twi;
+        if (p.peer_mode == 1) {
+          // local rows first, then the shards in the order the copier CTAs bring them in
+          twi += p.peer_rot;
+          if (twi >= p.tiles_w) twi -= p.tiles_w;
+          const int owner = (twi * p.tw) / p.peer_rows;
+          if (owner != p.peer_rank) {
+            const long long t0 = clock64();
+            while (static_cast<int>(ld_acquire_gpu(p.ready + twi) - p.peer_epoch) < 0) {
+              if (*abort_flag || clock64() - t0 > kWaitClockLimit) {
+                *abort_flag = kStatusTimeoutPeer;
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+          }
+        }
         const int x0 = twi * p.tw * p.stride - p.pad_w;
         const int y0 = thi * p.th * p.stride - p.pad_h;
-        trace_mark(p, (tile - blockIdx.x) / gridDim.x, 0);
+        trace_mark(p, (tile - blockIdx.x) / p.gemm_ctas, 0);
         int kcol = 0;
         for (int kh = 0; ok && kh < p.KH; ++kh) {
           for (int kw = 0; ok && kw < p.KW; ++kw) {
@@ -741,12 +822,7 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               armed |= 1u << s;
               armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
               const uint32_t a_dst = tile0 + s * Cfg::kStageBytes;
-              if (p.peer_mode == 1) {
-                const int owner = (twi * p.tw) / p.peer_rows;
-                tma_load_4d(a_dst, &p.peer->maps[owner], full_bar(s), kb * kBK, twi * p.tw - owner * p.peer_rows, 0, 0);
-              } else {
-                tma_load_4d(a_dst, &tmA, full_bar(s), kb * kBK, x0 + kw, y0 + kh, img);
-              }
+              tma_load_4d(a_dst, &tmA, full_bar(s), kb * kBK, x0 + kw, y0 + kh, img);
               if (p.b_batched)
                 tma_load_4d(a_dst + Cfg::kABytes, &tmB, full_bar(s), kcol, n_tile * BN, thi * p.th, img);
               else
@@ -783,7 +859,7 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       const uint64_t desc_hi = make_kmajor_desc(0, 128);
       int it = 0;
-      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++it) {
+      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += p.gemm_ctas, ++it) {
         if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, kStatusTimeoutMma)) break;
         trace_mark(p, it, 1);
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -1045,6 +1121,7 @@ static int launch_inst(ConvGemmOp* op, cudaStream_t stream) {
                                      Cfg::kSmemBytes));
     attr_set[dev] = true;
   }
+  if (op->prm.peer_mode == 1) ++op->prm.peer_epoch;   // the ready flags of this launch
   conv_gemm_kernel<BN, ACT><<<op->grid, kThreads, Cfg::kSmemBytes, stream>>>(op->tmA, op->tmB, op->tmY, op->prm);
   FDB_CUDA_OK(cudaGetLastError());
   return 0;
@@ -1326,6 +1403,8 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   }
   p.peer = nullptr;
   p.peer_mode = 0; p.peer_rows = 0; p.peer_rank = 0;
+  p.peer_world = 1; p.peer_rot = 0; p.peer_epoch = 0; p.ready = nullptr; p.gather_dst = nullptr; p.gather_row_bytes = 0;
+  for (int r = 0; r < 8; ++r) p.peer_src[r] = nullptr;
   if (d->peer_mode != 0) {
     const bool gemm_shape = d->KH == 1 && d->KW == 1 && d->stride == 1 && d->H == 1 && d->N == 1 && d->Ho == 1 &&
                             d->pad_h == 0 && d->pad_w == 0 && !op->halo && !d->w_batched && p.tw == kBM && p.th == 1;
@@ -1344,15 +1423,9 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
       if (d->peer_ptrs[r] == nullptr || (d->peer_mode == 2 && d->peer_counters[r] == nullptr)) {
         set_error("conv_gemm: missing peer pointer"); delete op; return nullptr;
       }
-      CUresult res;
+      CUresult res = CUDA_SUCCESS;
       if (d->peer_mode == 1) {
-        cuuint64_t dims[4] = {(cuuint64_t)d->Cin, (cuuint64_t)d->peer_rows, 1, 1};
-        cuuint64_t strides[3] = {(cuuint64_t)d->x_ld * 2, (cuuint64_t)d->peer_rows * d->x_ld * 2,
-                                 (cuuint64_t)d->peer_rows * d->x_ld * 2};
-        cuuint32_t box[4] = {(cuuint32_t)kBK, (cuuint32_t)p.tw, 1, 1};
-        cuuint32_t estr[4] = {1, 1, 1, 1};
-        res = enc(&host.maps[r], tdt, 4, d->peer_ptrs[r], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        p.peer_src[r] = static_cast<const uint8_t*>(d->peer_ptrs[r]);
       } else {
         const CUtensorMapDataType ydt =
             d->out_dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -1376,7 +1449,24 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
     }
     p.peer = op->peer_dev;
     p.peer_mode = d->peer_mode; p.peer_rows = d->peer_rows; p.peer_rank = d->peer_rank;
+    p.peer_world = d->peer_world;
+    if (d->peer_mode == 1) {
+      if (d->peer_ready == nullptr || (static_cast<long long>(d->x_ld) * 2) % 16 != 0) {
+        set_error("conv_gemm: all-gather mode needs ready flags and 16-byte rows"); delete op; return nullptr;
+      }
+      const int remote_blocks = p.tiles_w - d->peer_rows / p.tw;
+      int copiers = d->peer_copiers > 0 ? d->peer_copiers : 20;
+      copiers = std::min(copiers, std::min(remote_blocks, op->grid / 2));
+      op->grid = std::max(op->grid, copiers + 1);
+      p.gemm_ctas = op->grid - std::max(copiers, 0);
+      p.peer_rot = d->peer_rank * (d->peer_rows / p.tw);
+      p.peer_epoch = 0;
+      p.ready = d->peer_ready;
+      p.gather_dst = static_cast<uint8_t*>(const_cast<void*>(d->x));
+      p.gather_row_bytes = static_cast<long long>(d->x_ld) * 2;
+    }
   }
+  if (p.peer_mode != 1) p.gemm_ctas = op->grid;
   {
     const unsigned long long one = 1ull << 40;
     const long long dmax = std::max(p.n_tiles, std::max(p.tiles_w, p.tiles_h));

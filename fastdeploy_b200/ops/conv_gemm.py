@@ -41,6 +41,7 @@ class _ConvGemmDesc(ctypes.Structure):
         ("peer_mode", ctypes.c_int), ("peer_rows", ctypes.c_int), ("peer_rank", ctypes.c_int),
         ("peer_world", ctypes.c_int),
         ("peer_ptrs", ctypes.c_void_p * 8), ("peer_counters", ctypes.c_void_p * 8),
+        ("peer_ready", ctypes.c_void_p), ("peer_copiers", ctypes.c_int),
     ]
 
 
@@ -88,7 +89,8 @@ class ConvGemm(NativeOp):
                  w_n_stride: int = 0, x_h_stride: int = 0, y_h_stride: int = 0, res_h_stride: int = 0,
                  y_tma_mode: int = -1, trace: Optional[torch.Tensor] = None, name: str = "conv_gemm",
                  peer_mode: int = 0, peer_rows: int = 0, peer_rank: int = 0, peer_world: int = 0,
-                 peer_ptrs: Optional[Sequence[int]] = None, peer_counters: Optional[Sequence[int]] = None):
+                 peer_ptrs: Optional[Sequence[int]] = None, peer_counters: Optional[Sequence[int]] = None,
+                 peer_ready: Optional[torch.Tensor] = None, peer_copiers: int = 0):
         n, h, w_, cin = in_shape
         d = _ConvGemmDesc()
         self.status = status or StatusWord(x.device)
@@ -118,6 +120,9 @@ class ConvGemm(NativeOp):
             d.peer_ptrs[i] = ptr
         for i, ptr in enumerate(peer_counters or []):
             d.peer_counters[i] = ptr
+        d.peer_ready = peer_ready.data_ptr() if peer_ready is not None else None
+        d.peer_copiers = peer_copiers
+        self.peer_ready = peer_ready
         if bias is not None:
             assert bias.dtype == torch.float32
         if residual is not None:

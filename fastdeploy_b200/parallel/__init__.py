@@ -1,4 +1,4 @@
 """Multi-GPU layer: peer-memory communicator, fused GEMM + collective kernels, tensor-parallel
 layers and the data-parallel serving scheduler."""
 from .comm import Communicator, HeapBlock, HeapLayout, shard_rows  # noqa: F401
-from .tp import ColumnParallelLinear, RowParallelLinear  # noqa: F401
+from .tp import ColumnParallelLinear, RowParallelLinear, TensorParallelMLP  # noqa: F401

@@ -44,4 +44,4 @@ def test_tp_worker_two_ranks():
     line = [l for l in p.stdout.splitlines() if l.startswith("TPRESULT ")][-1]
     r = json.loads(line[len("TPRESULT "):])
     assert r["allreduce_err"] < 0.1 and r["reducescatter_err"] < 0.1 and r["allgather_err"] == 0.0
-    assert r["col_err"] < 2e-2 and r["row_err"] < 2e-2, r
+    assert r["col_err"] < 2e-2 and r["row_err"] < 2e-2 and r["mlp_err"] < 2e-2, r

@@ -34,7 +34,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    from fastdeploy_b200.parallel import ColumnParallelLinear, Communicator, RowParallelLinear
+    from fastdeploy_b200.parallel import ColumnParallelLinear, Communicator, RowParallelLinear, TensorParallelMLP
     comm = Communicator(heap_bytes=1 << 30)
     out = {"world": world}
     dt = torch.bfloat16
@@ -54,7 +54,8 @@ def main():
     out["allgather_err"] = float((ag.float() - torch.cat(ref_ag).float()).abs().max())
 
     # ---- all-gather -> GEMM (column parallel): M x K times (N / world) x K
-    M, K, N = world * 1024, 1280, 5120
+    mpr = int(os.environ.get("TP_M_PER_RANK", "1024"))
+    M, K, N = world * mpr, 1280, 5120
     gw = torch.Generator(device="cpu").manual_seed(7)
     w_full = torch.randn(N, K, generator=gw) * 0.03
     b_full = torch.randn(N, generator=gw)
@@ -87,6 +88,7 @@ def main():
     w2 = torch.randn(N2, K2, generator=gw) * 0.03
     b2 = torch.randn(N2, generator=gw)
     row = RowParallelLinear(comm, M, kl, N2, w2[:, rank * kl:(rank + 1) * kl], b2, dtype=dt)
+    assert kl == nl
     gx = torch.Generator(device="cpu").manual_seed(11)
     x2_full = (torch.randn(M, K2, generator=gx) * 0.5).to(dt)
     row.input_tensor().copy_(x2_full[:, rank * kl:(rank + 1) * kl].to(dev))
@@ -105,6 +107,24 @@ def main():
         return rs_out
     out["row_fused_ms"] = timed(row.forward)
     out["row_nccl_torch_ms"] = timed(row_baseline)
+    # ---- whole feed-forward block (ViT-H sizes: hidden 1280, ffn 5120), row shards in and out
+    mlp = TensorParallelMLP(comm, M, K, N, w_full, b_full, w2, b2, dtype=dt)
+    mlp.input_tensor().copy_(x_shard)
+    ym = mlp.forward()
+    torch.cuda.synchronize()
+    h_ref = torch.nn.functional.gelu(x_full @ w_full.to(dev).to(dt).float().T + b_full.to(dev)).to(dt).float()
+    ref_m = h_ref @ w2.to(dev).to(dt).float().T + b2.to(dev)
+    out["mlp_err"] = float((ym.float() - ref_m[rank * rows:(rank + 1) * rows]).abs().max() / ref_m.abs().max())
+    w1l, b1l = wl, bl
+
+    def mlp_baseline():
+        dist.all_gather(xs, x_shard)
+        h = torch.nn.functional.gelu(torch.nn.functional.linear(torch.cat(xs), w1l, b1l))
+        part = torch.nn.functional.linear(h, w2l)
+        dist.reduce_scatter_tensor(rs_out, part)
+        return rs_out
+    out["mlp_fused_ms"] = timed(mlp.forward)
+    out["mlp_nccl_torch_ms"] = timed(mlp_baseline)
     comm.check("tp worker")
     # roofline of the fused kernels: max(FLOPs / measured GEMM peak, NVLink bytes / 770 GB/s)
     flops = 2.0 * M * K * nl
