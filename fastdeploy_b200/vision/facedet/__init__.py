@@ -1,0 +1,287 @@
+"""Face detectors (fastdeploy/vision/facedet/): SCRFD, RetinaFace, YOLOv5Face, YOLOv7Face, UltraFace,
+BlazeFace, CenterFace. Each class restates its reference decoder - anchor / stride grids, optional 5
+landmarks - and finishes with the shared hard NMS on ``FaceDetectionResult``
+(fastdeploy/vision/utils/nms.cc:87-145)."""
+from __future__ import annotations
+
+import math
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from ...core.types import ModelFormat
+from ...runtime.model import FastDeployModel
+from ...runtime.option import RuntimeOption
+from .. import utils as vutils
+from ..detection.contrib import _resize_bilinear, letterbox
+from ..result import FaceDetectionResult
+
+
+def _finish(boxes, scores, lms, k, nms_iou, info=None, clip_hw=None) -> FaceDetectionResult:
+    r = FaceDetectionResult()
+    r.landmarks_per_face = k
+    if len(scores) == 0:
+        return r
+    boxes = np.asarray(boxes, np.float32).reshape(-1, 4).copy()
+    lms = np.asarray(lms, np.float32).reshape(len(scores), k, 2).copy() if k else None
+    if info is not None:
+        boxes[:, [0, 2]] = (boxes[:, [0, 2]] - info["pad_w"]) / info["scale"]
+        boxes[:, [1, 3]] = (boxes[:, [1, 3]] - info["pad_h"]) / info["scale"]
+        if k:
+            lms[..., 0] = (lms[..., 0] - info["pad_w"]) / info["scale"]
+            lms[..., 1] = (lms[..., 1] - info["pad_h"]) / info["scale"]
+        clip_hw = info["in_hw"]
+    if clip_hw is not None:
+        h, w = clip_hw
+        boxes[:, [0, 2]] = np.clip(boxes[:, [0, 2]], 0, w - 1.0)
+        boxes[:, [1, 3]] = np.clip(boxes[:, [1, 3]], 0, h - 1.0)
+        if k:
+            lms[..., 0] = np.clip(lms[..., 0], 0, w - 1.0)
+            lms[..., 1] = np.clip(lms[..., 1], 0, h - 1.0)
+    r.boxes = boxes.tolist()
+    r.scores = [float(s) for s in scores]
+    if k:
+        r.landmarks = lms.reshape(-1, 2).tolist()
+    vutils.nms(r, nms_iou)
+    return r
+
+
+class _FaceDetBase(FastDeployModel):
+    SIZE = (640, 640)
+
+    def __init__(self, model_file: str, params_file: str = "", runtime_option: Optional[RuntimeOption] = None,
+                 model_format: int = ModelFormat.ONNX):
+        super().__init__(runtime_option)
+        self.runtime_option.set_model_path(model_file, params_file, model_format)
+        self.size = list(self.SIZE)
+        self.conf_threshold = 0.25
+        self.nms_iou_threshold = 0.4
+        self._configure()
+        self.init_runtime()
+
+    def _configure(self):
+        pass
+
+    def _infer(self, x: np.ndarray) -> List[np.ndarray]:
+        return [np.asarray(o, np.float32) for o in self.runtime.infer({self.runtime.get_input_info(0).name: x})]
+
+    def predict(self, im: np.ndarray, conf_threshold: Optional[float] = None, nms_iou_threshold: Optional[float] = None):
+        if conf_threshold is not None:
+            self.conf_threshold = conf_threshold
+        if nms_iou_threshold is not None:
+            self.nms_iou_threshold = nms_iou_threshold
+        x, info = self.preprocess(im)
+        return self.postprocess(self._infer(x), info)
+
+    def batch_predict(self, images: Sequence[np.ndarray]):
+        return [self.predict(im) for im in images]
+
+
+class SCRFD(_FaceDetBase):
+    """SCRFD (facedet/contrib/scrfd.cc:178-330): strides 8/16/32, 2 anchors per cell, outputs per
+    stride: score [n,1], bbox distances [n,4] (x stride), optional kps [n,10] (x stride)."""
+
+    def _configure(self):
+        self.strides = [8, 16, 32]
+        self.num_anchors = 2
+        self.use_kps = True
+        self.landmarks_per_face = 5
+        self.mean, self.scale = 127.5, 1.0 / 128.0
+
+    def preprocess(self, im):
+        canvas, info = letterbox(im, self.size, (0, 0, 0))
+        x = (canvas[..., ::-1].astype(np.float32) - self.mean) * self.scale
+        return np.ascontiguousarray(x.transpose(2, 0, 1))[None], info
+
+    def postprocess(self, outs, info):
+        n_s = len(self.strides)
+        boxes, scores, lms = [], [], []
+        h, w = info["out_hw"]
+        for i, s in enumerate(self.strides):
+            sc = outs[i].reshape(-1)
+            bb = outs[i + n_s].reshape(-1, 4) * s
+            fh, fw = h // s, w // s
+            gy, gx = np.meshgrid(np.arange(fh), np.arange(fw), indexing="ij")
+            c = np.stack([gx.ravel(), gy.ravel()], 1).astype(np.float32) * s
+            c = np.repeat(c, self.num_anchors, axis=0)
+            m = sc > self.conf_threshold
+            if not m.any():
+                continue
+            cm, bm = c[m], bb[m]
+            boxes.append(np.stack([cm[:, 0] - bm[:, 0], cm[:, 1] - bm[:, 1], cm[:, 0] + bm[:, 2], cm[:, 1] + bm[:, 3]], 1))
+            scores.append(sc[m])
+            if self.use_kps and len(outs) >= 3 * n_s:
+                kp = outs[i + 2 * n_s].reshape(-1, 5, 2)[m] * s
+                lms.append(kp + cm[:, None, :])
+        if not scores:
+            return _finish([], [], [], 0, self.nms_iou_threshold)
+        k = 5 if lms else 0
+        return _finish(np.concatenate(boxes), np.concatenate(scores), np.concatenate(lms) if lms else [], k,
+                       self.nms_iou_threshold, info)
+
+
+class RetinaFace(_FaceDetBase):
+    """RetinaFace (facedet/contrib/retinaface.cc:100-270): prior boxes with min sizes {16,32},{64,128},
+    {256,512} on strides 8/16/32, variances (0.1, 0.2), outputs loc [n,4], conf [n,2], landms [n,10]."""
+
+    def _configure(self):
+        self.variance = [0.1, 0.2]
+        self.strides = [8, 16, 32]
+        self.min_sizes = [[16, 32], [64, 128], [256, 512]]
+        self.landmarks_per_face = 5
+
+    def priors(self, h, w):
+        out = []
+        for s, sizes in zip(self.strides, self.min_sizes):
+            fh, fw = math.ceil(h / s), math.ceil(w / s)
+            for i in range(fh):
+                for j in range(fw):
+                    for ms in sizes:
+                        out.append([(j + 0.5) * s / w, (i + 0.5) * s / h, ms / w, ms / h])
+        return np.asarray(out, np.float32)
+
+    def preprocess(self, im):
+        h, w = im.shape[:2]
+        x = _resize_bilinear(im, self.size[0], self.size[1]).astype(np.float32) - np.asarray([104.0, 117.0, 123.0], np.float32)
+        info = {"scale_w": self.size[0] / w, "scale_h": self.size[1] / h, "in_hw": (h, w)}
+        return np.ascontiguousarray(x.transpose(2, 0, 1))[None], info
+
+    def postprocess(self, outs, info):
+        loc, conf, landm = outs[0].reshape(-1, 4), outs[1].reshape(-1, 2), outs[2].reshape(-1, 10)
+        H, W = self.size[1], self.size[0]
+        pr = self.priors(H, W)
+        sc = conf[:, 1]
+        m = sc > self.conf_threshold
+        pr, loc, landm, sc = pr[m], loc[m], landm[m], sc[m]
+        cx = pr[:, 0] + loc[:, 0] * self.variance[0] * pr[:, 2]
+        cy = pr[:, 1] + loc[:, 1] * self.variance[0] * pr[:, 3]
+        bw = pr[:, 2] * np.exp(loc[:, 2] * self.variance[1])
+        bh = pr[:, 3] * np.exp(loc[:, 3] * self.variance[1])
+        boxes = np.stack([(cx - bw / 2) * W, (cy - bh / 2) * H, (cx + bw / 2) * W, (cy + bh / 2) * H], 1)
+        lm = landm.reshape(-1, 5, 2) * self.variance[0] * pr[:, None, 2:4] + pr[:, None, 0:2]
+        lm = lm * np.asarray([W, H], np.float32)
+        boxes[:, [0, 2]] /= info["scale_w"]
+        boxes[:, [1, 3]] /= info["scale_h"]
+        lm[..., 0] /= info["scale_w"]
+        lm[..., 1] /= info["scale_h"]
+        return _finish(boxes, sc, lm, 5, self.nms_iou_threshold, None, info["in_hw"])
+
+
+class YOLOv5Face(_FaceDetBase):
+    """YOLOv5-Face (facedet/contrib/yolov5face.cc:150-260): rows ``[cx, cy, w, h, obj, 5 x (lx, ly), cls]``."""
+
+    def _configure(self):
+        self.landmarks_per_face = 5
+
+    def preprocess(self, im):
+        canvas, info = letterbox(im, self.size, (114, 114, 114))
+        x = canvas[..., ::-1].astype(np.float32) / 255.0
+        return np.ascontiguousarray(x.transpose(2, 0, 1))[None], info
+
+    def postprocess(self, outs, info):
+        rows = outs[0].reshape(-1, outs[0].shape[-1])
+        conf = rows[:, 4] * rows[:, 15]
+        m = conf > self.conf_threshold
+        rows, conf = rows[m], conf[m]
+        boxes = np.stack([rows[:, 0] - rows[:, 2] / 2, rows[:, 1] - rows[:, 3] / 2, rows[:, 0] + rows[:, 2] / 2,
+                          rows[:, 1] + rows[:, 3] / 2], 1)
+        return _finish(boxes, conf, rows[:, 5:15].reshape(-1, 5, 2), 5, self.nms_iou_threshold, info)
+
+
+class YOLOv7Face(YOLOv5Face):
+    """YOLOv7-Face (facedet/contrib/yolov7face/): rows ``[cx, cy, w, h, obj, cls, 5 x (lx, ly, conf)]``."""
+
+    def postprocess(self, outs, info):
+        rows = outs[0].reshape(-1, outs[0].shape[-1])
+        conf = rows[:, 4] * rows[:, 5]
+        m = conf > self.conf_threshold
+        rows, conf = rows[m], conf[m]
+        boxes = np.stack([rows[:, 0] - rows[:, 2] / 2, rows[:, 1] - rows[:, 3] / 2, rows[:, 0] + rows[:, 2] / 2,
+                          rows[:, 1] + rows[:, 3] / 2], 1)
+        lm = rows[:, 6:21].reshape(-1, 5, 3)[..., :2]
+        return _finish(boxes, conf, lm, 5, self.nms_iou_threshold, info)
+
+
+class UltraFace(_FaceDetBase):
+    """UltraFace (facedet/contrib/ultraface.cc:120-200): outputs scores [n,2] and boxes [n,4] already
+    decoded and normalised to [0,1]; input 320x240, (x - 127) / 128."""
+    SIZE = (320, 240)
+
+    def _configure(self):
+        self.conf_threshold = 0.7
+        self.nms_iou_threshold = 0.3
+
+    def preprocess(self, im):
+        h, w = im.shape[:2]
+        x = (_resize_bilinear(im, self.size[0], self.size[1])[..., ::-1].astype(np.float32) - 127.0) / 128.0
+        return np.ascontiguousarray(x.transpose(2, 0, 1))[None], {"in_hw": (h, w)}
+
+    def postprocess(self, outs, info):
+        sc, bb = outs[0].reshape(-1, 2)[:, 1], outs[1].reshape(-1, 4)
+        m = sc > self.conf_threshold
+        h, w = info["in_hw"]
+        boxes = bb[m] * np.asarray([w, h, w, h], np.float32)
+        return _finish(boxes, sc[m], [], 0, self.nms_iou_threshold, None, (h, w))
+
+
+class BlazeFace(_FaceDetBase):
+    """BlazeFace exported by PaddleDetection (facedet/ppdet/blazeface/): the graph ends in NMS-ready
+    rows ``[label, score, x1, y1, x2, y2]`` and a per-image count; only the score filter remains."""
+    SIZE = (640, 640)
+
+    def _configure(self):
+        self.conf_threshold = 0.5
+
+    def preprocess(self, im):
+        h, w = im.shape[:2]
+        x = _resize_bilinear(im, self.size[0], self.size[1]).astype(np.float32)
+        x = (x[..., ::-1] / 255.0 - np.asarray([0.485, 0.456, 0.406], np.float32)) / np.asarray([0.229, 0.224, 0.225], np.float32)
+        return np.ascontiguousarray(x.transpose(2, 0, 1))[None], {"in_hw": (h, w), "sx": w / self.size[0], "sy": h / self.size[1]}
+
+    def predict(self, im, conf_threshold=None, nms_iou_threshold=None):
+        if conf_threshold is not None:
+            self.conf_threshold = conf_threshold
+        x, info = self.preprocess(im)
+        feeds = {}
+        for i in range(self.runtime.num_inputs()):
+            name = self.runtime.get_input_info(i).name
+            if name == "image" or i == 0 and self.runtime.num_inputs() == 1:
+                feeds[name] = x
+            elif name == "scale_factor":
+                feeds[name] = np.asarray([[1.0 / info["sy"], 1.0 / info["sx"]]], np.float32)
+            elif name == "im_shape":
+                feeds[name] = np.asarray([[self.size[1], self.size[0]]], np.float32)
+        rows = np.asarray(self.runtime.infer(feeds)[0], np.float32).reshape(-1, 6)
+        rows = rows[rows[:, 1] > self.conf_threshold]
+        r = FaceDetectionResult()
+        r.boxes, r.scores = rows[:, 2:6].tolist(), rows[:, 1].tolist()
+        return r
+
+
+class CenterFace(_FaceDetBase):
+    """CenterFace (facedet/contrib/centerface/): heat-map [1,1,h/4,w/4], scale [1,2,..], offset [1,2,..],
+    landmarks [1,10,..]; peaks above the threshold decode to boxes of size exp(scale) * 4."""
+
+    def _configure(self):
+        self.conf_threshold = 0.5
+        self.nms_iou_threshold = 0.3
+        self.landmarks_per_face = 5
+
+    def preprocess(self, im):
+        canvas, info = letterbox(im, self.size, (0, 0, 0))
+        x = canvas[..., ::-1].astype(np.float32)
+        return np.ascontiguousarray(x.transpose(2, 0, 1))[None], info
+
+    def postprocess(self, outs, info):
+        heat, scale, offset, lms = outs[0][0, 0], outs[1][0], outs[2][0], outs[3][0]
+        ys, xs = np.nonzero(heat > self.conf_threshold)
+        boxes, scores, pts = [], [], []
+        for y, x in zip(ys, xs):
+            s0, s1 = math.exp(scale[0, y, x]) * 4, math.exp(scale[1, y, x]) * 4
+            o0, o1 = offset[0, y, x], offset[1, y, x]
+            x1 = max(0.0, (x + o1 + 0.5) * 4 - s1 / 2)
+            y1 = max(0.0, (y + o0 + 0.5) * 4 - s0 / 2)
+            boxes.append([x1, y1, x1 + s1, y1 + s0])
+            scores.append(heat[y, x])
+            pts.append([[lms[2 * j + 1, y, x] * s1 + x1, lms[2 * j, y, x] * s0 + y1] for j in range(5)])
+        return _finish(boxes, scores, pts, 5, self.nms_iou_threshold, info)
