@@ -3,3 +3,6 @@ from .ppdet import (FCOS, GFL, PPYOLO, PPYOLOE, PPYOLOER, PPYOLOESOD, RTMDet, SO
                     FasterRCNN, MaskRCNN, NMSOption, PaddleDetectionModel, PaddleDetPostprocessor,
                     PaddleDetPreprocessor, PaddleYOLOv5, PaddleYOLOv6, PaddleYOLOv7, PaddleYOLOv8, PaddleYOLOX,
                     PicoDet, PPDetBase, PSSDet, RetinaNet, TTFNet, YOLOv3)
+from .contrib import (RKYOLOV5, RKYOLOV7, RKYOLOX, YOLOR, YOLOX, FastestDet, NanoDetPlus, ScaledYOLOv4,  # noqa: E402
+                      YOLOPostprocessor, YOLOPreprocessor, YOLOv5, YOLOv5Lite, YOLOv5Seg, YOLOv6, YOLOv7,
+                      YOLOv7End2EndORT, YOLOv7End2EndTRT, YOLOv8, letterbox)

@@ -1,0 +1,103 @@
+"""Decoders of the model families on hand-made network outputs (no runtime involved)."""
+import numpy as np
+import pytest
+
+from fastdeploy_b200.vision.detection import contrib as C
+from fastdeploy_b200.vision import facedet, keypointdetection as K, perception as P, tracking as T, utils as U
+
+
+def test_letterbox_geometry_and_inverse():
+    img = np.zeros((480, 640, 3), np.uint8)
+    canvas, info = C.letterbox(img, (640, 640))
+    assert canvas.shape == (640, 640, 3) and info["pad_h"] == 80 and info["pad_w"] == 0 and info["scale"] == 1.0
+    assert (canvas[:80] == 114).all() and (canvas[80:560] == 0).all()
+    canvas, info = C.letterbox(np.zeros((100, 50, 3), np.uint8), (64, 64), scale_up=False)
+    assert info["scale"] == 0.64 and canvas.shape == (64, 64, 3)
+
+
+def test_yolov5_decode_class_aware_nms():
+    _, infos = C.YOLOPreprocessor().run([np.zeros((480, 640, 3), np.uint8)])
+    out = np.zeros((1, 10, 85), np.float32)
+    out[0, 0, :5] = [320, 320, 100, 80, 0.9]; out[0, 0, 5 + 3] = 0.8
+    out[0, 1, :5] = [322, 321, 100, 80, 0.8]; out[0, 1, 5 + 3] = 0.9     # same class, suppressed
+    out[0, 2, :5] = [322, 321, 100, 80, 0.8]; out[0, 2, 5 + 7] = 0.9     # other class, kept
+    r = C.YOLOPostprocessor("v5").run([out], infos)[0]
+    assert sorted(r.label_ids) == [3, 7] and len(r.boxes) == 2
+    b = r.boxes[r.label_ids.index(3)]
+    assert np.allclose(b, [270, 200, 370, 280])          # letterbox padding of 80 rows removed
+
+
+def test_yolov8_and_yolox_layouts():
+    _, infos = C.YOLOPreprocessor().run([np.zeros((640, 640, 3), np.uint8)])
+    out8 = np.zeros((1, 84, 5), np.float32)
+    out8[0, :4, 0] = [100, 100, 40, 40]; out8[0, 4 + 2, 0] = 0.7
+    r = C.YOLOPostprocessor("v8").run([out8], infos)[0]
+    assert r.label_ids == [2] and np.allclose(r.boxes[0], [80, 80, 120, 120])
+    pp = C.YOLOPostprocessor("x")
+    n = sum((640 // s) ** 2 for s in pp.strides)
+    outx = np.zeros((1, n, 85), np.float32)
+    outx[0, 81, :5] = [0.5, 0.5, np.log(4.0), np.log(2.0), 0.9]; outx[0, 81, 5] = 0.9    # cell (1, 1) of stride 8
+    r = pp.run([outx], infos)[0]
+    assert np.allclose(r.boxes[0], [(1.5 * 8) - 16, (1.5 * 8) - 8, (1.5 * 8) + 16, (1.5 * 8) + 8].copy() if False else
+                       [max(0, 12 - 16), 12 - 8, 12 + 16, 12 + 8])
+
+
+def test_scrfd_decode_with_landmarks():
+    m = facedet.SCRFD.__new__(facedet.SCRFD)
+    m.size = [64, 64]; m.conf_threshold = 0.5; m.nms_iou_threshold = 0.4
+    facedet.SCRFD._configure(m)
+    info = {"scale": 1.0, "pad_w": 0, "pad_h": 0, "in_hw": (64, 64), "out_hw": (64, 64)}
+    outs = []
+    for s in m.strides:
+        n = (64 // s) ** 2 * 2
+        outs.append(np.zeros((n, 1), np.float32))
+    for s in m.strides:
+        outs.append(np.zeros(((64 // s) ** 2 * 2, 4), np.float32))
+    for s in m.strides:
+        outs.append(np.zeros(((64 // s) ** 2 * 2, 10), np.float32))
+    outs[0][2 * (8 * 2 + 3), 0] = 0.9                      # stride 8, cell (y=2, x=3), anchor 0
+    outs[3][2 * (8 * 2 + 3)] = [1, 1, 2, 2]
+    outs[6][2 * (8 * 2 + 3)] = [0.5] * 10
+    r = m.postprocess(outs, info)
+    assert len(r.boxes) == 1 and np.allclose(r.boxes[0], [24 - 8, 16 - 8, 24 + 16, 16 + 16])
+    assert r.landmarks_per_face == 5 and np.allclose(r.landmarks[0], [28, 20])
+
+
+def test_dark_and_plain_heatmap_decoding_agree_on_symmetric_peak():
+    heat = np.zeros((1, 32, 24), np.float32)
+    yy, xx = np.mgrid[0:32, 0:24]
+    heat[0] = np.exp(-((xx - 10) ** 2 + (yy - 12) ** 2) / 4.0)
+    p1, s1 = K.decode_heatmaps(heat, (50, 60), (48, 64), use_dark=True)
+    p2, s2 = K.decode_heatmaps(heat, (50, 60), (48, 64), use_dark=False)
+    assert np.allclose(p1, p2, atol=0.6) and abs(s1[0] - 1) < 1e-6
+    m, mi = K.get_affine((100, 80), (60, 80), (192, 256)), K.get_affine((100, 80), (60, 80), (192, 256), inv=True)
+    assert np.allclose(mi @ np.r_[m @ [100, 80, 1], 1], [100, 80], atol=1e-3)
+
+
+def test_trackers_keep_identities():
+    rng = np.random.default_rng(0)
+    f = rng.standard_normal((2, 16))
+    jt, oc = T.JDETracker(), T.OCSortTracker(det_thresh=0.3)
+    ids_j, ids_o = [], []
+    for fr in range(10):
+        b = np.array([[100 + 5 * fr, 100, 150 + 5 * fr, 200], [300, 50 + 3 * fr, 380, 190 + 3 * fr]], float)
+        if fr == 4:            # one missed detection in the middle
+            b = b[:1]
+            tr = jt.update(b, np.array([0.9]), f[:1])
+            o = oc.update(b, np.array([0.9]))
+        else:
+            tr = jt.update(b, np.array([0.9, 0.8]), f + 0.01 * rng.standard_normal((2, 16)))
+            o = oc.update(b, np.array([0.9, 0.8]))
+        ids_j.append(sorted(t.id for t in tr)); ids_o.append(sorted(int(i) for i in o[:, 4]))
+    assert ids_j[-1] == ids_j[0] and len(ids_j[0]) == 2
+    assert ids_o[-1] == ids_o[0] and len(ids_o[0]) == 2
+
+
+def test_voxelize_and_bev_nms():
+    pts = np.array([[0.1, 0.1, 0, 1], [0.2, 0.2, 0, 1], [0.3, 0.3, 0, 1], [5.1, 5.1, 0, 1], [99, 0, 0, 1]], np.float32)
+    v, c, n = P.hard_voxelize(pts, [1, 1, 8], [0, 0, -4, 10, 10, 4], max_points=2, max_voxels=10)
+    assert v.shape == (2, 2, 4) and n.tolist() == [2, 1] and c.tolist() == [[0, 0, 0], [0, 5, 5]]
+    assert abs(P.rotated_iou_bev((0, 0, 2, 4, 0), (1, 0, 2, 4, 0)) - 1 / 3) < 1e-6
+    assert abs(P.rotated_iou_bev((0, 0, 2, 2, 0), (0, 0, 2, 2, np.pi / 4)) - 0.70710678) < 1e-4
+    boxes = np.array([[0, 0, 2, 4, 0], [0.2, 0, 2, 4, 0], [10, 10, 2, 4, 1.0]], np.float32)
+    assert P.nms_bev(boxes, np.array([0.9, 0.8, 0.7]), 0.5) == [0, 2]
