@@ -1,0 +1,120 @@
+"""Scheduler / batcher with fake devices, config.pbtxt parsing, SimpleServer routes (in-process client)."""
+import os
+import threading
+import time
+
+import numpy as np
+import pytest
+
+from fastdeploy_b200.serving import Scheduler, parse_pbtxt, load_model_config
+
+
+class FakeModel:
+    def __init__(self, index, fail_after=None, delay=0.002):
+        self.index, self.calls, self.fail_after, self.delay = index, 0, fail_after, delay
+
+    def run(self, xs):
+        self.calls += 1
+        if self.fail_after is not None and self.calls > self.fail_after:
+            raise RuntimeError(f"device {self.index} lost")
+        time.sleep(self.delay)
+        return [(self.index, x * 2) for x in xs]
+
+
+def test_batches_and_balances_over_workers():
+    models = {}
+
+    def factory(i):
+        models[i] = FakeModel(i)
+        return models[i]
+    s = Scheduler(factory, lambda m, xs: m.run(xs), num_workers=4, max_batch_size=8, max_queue_delay_us=2000)
+    out = s.map(list(range(200)))
+    assert [v for _, v in out] == [2 * i for i in range(200)]
+    st = s.stats()["workers"]
+    assert all(w["requests"] > 0 for w in st) and sum(w["requests"] for w in st) == 200
+    assert max(w["avg_batch_size"] for w in st) > 1.5
+    s.close()
+
+
+def test_failed_worker_leaves_rotation_and_requests_survive():
+    def factory(i):
+        if i == 3:
+            raise RuntimeError("no such device")          # never joins
+        return FakeModel(i, fail_after=2 if i == 1 else None)
+    s = Scheduler(factory, lambda m, xs: m.run(xs), num_workers=4, max_batch_size=4, max_queue_delay_us=200, max_failures=2)
+    assert len(s.alive_workers()) == 3
+    ok = failed = 0
+    for i in range(120):
+        try:
+            s.infer(i, timeout=5)
+            ok += 1
+        except RuntimeError:
+            failed += 1
+    assert failed >= 2 and ok >= 100
+    assert not s.workers[1].alive and len(s.alive_workers()) == 2
+    assert s.infer(7, timeout=5)[1] == 14                 # still serving
+    s.close()
+
+
+def test_all_workers_dead_is_an_error_not_a_hang():
+    with pytest.raises(RuntimeError, match="no worker could be started"):
+        Scheduler(lambda i: (_ for _ in ()).throw(RuntimeError("gone")), lambda m, xs: xs, num_workers=2)
+
+
+PBTXT = '''
+name: "ppyoloe"   # comment
+backend: "fastdeploy"
+max_batch_size: 16
+input [
+  { name: "image", data_type: TYPE_FP32, dims: [ 3, -1, -1 ] },
+  { name: "scale_factor", data_type: TYPE_FP32, dims: [ 2 ] }
+]
+output [ { name: "multiclass_nms3_0.tmp_0", data_type: TYPE_FP32, dims: [ -1, 6 ] } ]
+instance_group [ { count: 2, kind: KIND_GPU, gpus: [0, 1] } ]
+dynamic_batching { preferred_batch_size: [ 4, 8 ], max_queue_delay_microseconds: 300 }
+optimization { execution_accelerators { gpu_execution_accelerator : [ {
+  name: "tensorrt"
+  parameters { key: "precision" value: "trt_fp16" }
+  parameters { key: "max_shape" value: "image:16 3 640 640" }
+} ] } }
+parameters { key: "note" value: { string_value: "hello" } }
+'''
+
+
+def test_config_pbtxt(tmp_path):
+    cfg = parse_pbtxt(PBTXT)
+    assert cfg["name"] == "ppyoloe" and cfg["max_batch_size"] == 16 and cfg["input"][0]["dims"] == [3, -1, -1]
+    d = tmp_path / "ppyoloe"
+    (d / "1").mkdir(parents=True)
+    (d / "config.pbtxt").write_text(PBTXT)
+    (d / "1" / "model.onnx").write_bytes(b"")
+    mc = load_model_config(str(d))
+    assert mc.instances() == [("gpu", 0), ("gpu", 0), ("gpu", 1), ("gpu", 1)]
+    assert mc.dynamic_batching and mc.max_queue_delay_us == 300 and mc.preferred_batch_size == [4, 8]
+    assert mc.parameters["note"] == "hello" and mc.versions() == [1]
+    assert mc.gpu_accelerators[0]["name"] == "tensorrt"
+    opt = mc.runtime_option("cpu", -1)
+    assert opt.model_file.endswith("model.onnx")
+
+
+def test_simple_server_routes():
+    fastapi = pytest.importorskip("fastapi")
+    from fastapi.testclient import TestClient
+    from fastdeploy_b200.serving import BaseModelHandler, SimpleServer
+
+    class EchoHandler(BaseModelHandler):
+        @classmethod
+        def process(cls, predictor, data, parameters):
+            return {"sum": predictor(data["values"]), "scale": parameters.get("scale", 1)}
+
+    app = SimpleServer()
+    app.register("add", EchoHandler, [sum, sum])
+    try:
+        c = TestClient(app)
+    except RuntimeError as e:          # httpx is not installed in every image
+        pytest.skip(str(e))
+    r = c.post("/add", json={"data": {"values": [1, 2, 3]}, "parameters": {"scale": 2}})
+    assert r.status_code == 200 and r.json() == {"result": {"sum": 6, "scale": 2}}
+    assert c.post("/add", json={"data": {"values": ["x", 1]}}).status_code == 400
+    assert c.post("/add", json={"nope": 1}).status_code == 422
+    assert c.get("/health").json()["models"] == ["add"]
