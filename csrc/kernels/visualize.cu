@@ -22,8 +22,10 @@ namespace fdb {
 __global__ void draw_boxes_kernel(uint8_t* img, int H, int W, const float* boxes, const uint8_t* colors, int n, int thick) {
   const int b = blockIdx.y;
   if (b >= n) return;
-  const int x1 = max(0, __float2int_rn(boxes[4 * b])), y1 = max(0, __float2int_rn(boxes[4 * b + 1]));
-  const int x2 = min(W - 1, __float2int_rn(boxes[4 * b + 2])), y2 = min(H - 1, __float2int_rn(boxes[4 * b + 3]));
+  // edges that fall outside the frame are not drawn (the box is clipped, not clamped), but coordinates
+  // are limited to one frame size around it so that absurd boxes cannot make the loops long
+  const int x1 = max(-W, __float2int_rn(boxes[4 * b])), y1 = max(-H, __float2int_rn(boxes[4 * b + 1]));
+  const int x2 = min(2 * W, __float2int_rn(boxes[4 * b + 2])), y2 = min(2 * H, __float2int_rn(boxes[4 * b + 3]));
   if (x2 < x1 || y2 < y1) return;
   const int bw = x2 - x1 + 1, bh = y2 - y1 + 1;
   const int t = min(thick, min(bw, bh));
@@ -37,6 +39,7 @@ __global__ void draw_boxes_kernel(uint8_t* img, int H, int W, const float* boxes
     else if (i < 2 * band_h) { const int j = i - band_h; y = y2 - j / bw; x = x1 + j % bw; }
     else if (i < 2 * band_h + band_v) { const int j = i - 2 * band_h; y = y1 + t + j / t; x = x1 + j % t; }
     else { const int j = i - 2 * band_h - band_v; y = y1 + t + j / t; x = x2 - j % t; }
+    if (x < 0 || y < 0 || x >= W || y >= H) continue;
     uint8_t* p = img + (static_cast<size_t>(y) * W + x) * 3;
     p[0] = c0; p[1] = c1; p[2] = c2;
   }

@@ -24,7 +24,7 @@ def test_boxes_match_host_rectangles():
     import cv2
     for b, l in zip(d.boxes, d.label_ids):
         c = tuple(int(v) for v in V.get_color_map()[l % 256])
-        x1, y1, x2, y2 = max(0, int(b[0])), max(0, int(b[1])), min(130, int(b[2])), min(96, int(b[3]))
+        x1, y1, x2, y2 = int(b[0]), int(b[1]), int(b[2]), int(b[3])
         for t in range(2):      # thickness 2 grows inwards on the device path
             cv2.rectangle(ref, (x1 + t, y1 + t), (x2 - t, y2 - t), c, 1)
     assert (out == ref).all()
