@@ -11,6 +11,8 @@ from .runtime.runtime import Runtime
 from .runtime.model import FastDeployModel
 from .utils.log import set_logger
 from . import vision
+from . import download as _download_module  # noqa: F401
+from .download import download, download_and_decompress, download_model  # noqa: F401
 
 
 def is_built_with_gpu() -> bool:
@@ -36,3 +38,11 @@ def is_built_with_openvino() -> bool:
 
 def get_default_cuda_directory() -> str:
     return "/usr/local/cuda"
+
+
+def __getattr__(name):
+    # heavier sub-packages load on first use
+    import importlib
+    if name in ("text", "pipeline", "serving", "encryption", "parallel", "streamer", "tools", "function", "utils"):
+        return importlib.import_module("." + name, __name__)
+    raise AttributeError(name)

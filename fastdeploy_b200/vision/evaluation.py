@@ -1,0 +1,118 @@
+"""Evaluation toolkit (python/fastdeploy/vision/evaluation/{classify,detection,segmentation}.py):
+top-k accuracy, COCO-style box mAP (101-point interpolated AP over IoU 0.50:0.95, no pycocotools
+dependency) and mIoU / pixel accuracy. Each ``eval_*`` takes a model object and an iterable of samples,
+so it runs on synthetic data as well as on a dataset directory."""
+from __future__ import annotations
+
+import time
+from typing import Any, Dict, Iterable, List, Sequence, Tuple
+
+import numpy as np
+
+
+def topk_accuracy(scores: np.ndarray, labels: Sequence[int], k: int = 1) -> float:
+    order = np.argsort(-np.asarray(scores), axis=1, kind="stable")[:, :k]
+    labels = np.asarray(labels).reshape(-1, 1)
+    return float((order == labels).any(1).mean())
+
+
+def eval_classify(model, samples: Iterable[Tuple[np.ndarray, int]], topk: int = 5) -> Dict[str, float]:
+    hit1 = hitk = n = 0
+    t0 = time.perf_counter()
+    for im, label in samples:
+        r = model.predict(im, topk) if "topk" in model.predict.__code__.co_varnames else model.predict(im)
+        ids = list(r.label_ids)
+        hit1 += int(ids[:1] == [label])
+        hitk += int(label in ids[:topk])
+        n += 1
+    return {"topk1": hit1 / max(n, 1), f"topk{topk}": hitk / max(n, 1), "samples": n, "seconds": time.perf_counter() - t0}
+
+
+def _iou(b, boxes):
+    x1 = np.maximum(b[0], boxes[:, 0]); y1 = np.maximum(b[1], boxes[:, 1])
+    x2 = np.minimum(b[2], boxes[:, 2]); y2 = np.minimum(b[3], boxes[:, 3])
+    inter = np.maximum(x2 - x1, 0) * np.maximum(y2 - y1, 0)
+    return inter / np.maximum((b[2] - b[0]) * (b[3] - b[1]) + (boxes[:, 2] - boxes[:, 0]) * (boxes[:, 3] - boxes[:, 1]) - inter, 1e-12)
+
+
+def average_precision(dets: List[Tuple[int, float, Sequence[float]]], gts: Dict[int, np.ndarray], iou_thr: float) -> float:
+    """``dets`` = (image id, score, box) of one class; ``gts[image id]`` = boxes ``[n, 4]`` of that class."""
+    npos = sum(len(v) for v in gts.values())
+    if npos == 0:
+        return float("nan")
+    used = {k: np.zeros(len(v), bool) for k, v in gts.items()}
+    dets = sorted(dets, key=lambda d: -d[1])
+    tp = np.zeros(len(dets)); fp = np.zeros(len(dets))
+    for i, (img, _, box) in enumerate(dets):
+        g = gts.get(img)
+        if g is None or len(g) == 0:
+            fp[i] = 1
+            continue
+        ious = _iou(np.asarray(box, float), g)
+        ious[used[img]] = -1
+        j = int(ious.argmax())
+        if ious[j] >= iou_thr:
+            tp[i] = 1
+            used[img][j] = True
+        else:
+            fp[i] = 1
+    ctp, cfp = np.cumsum(tp), np.cumsum(fp)
+    rec = ctp / npos
+    prec = ctp / np.maximum(ctp + cfp, 1e-12)
+    for i in range(len(prec) - 2, -1, -1):
+        prec[i] = max(prec[i], prec[i + 1])
+    pts = np.linspace(0, 1, 101)
+    idx = np.searchsorted(rec, pts, side="left")
+    return float(np.mean([prec[i] if i < len(prec) else 0.0 for i in idx]))
+
+
+def coco_map(predictions: List[Dict[str, Any]], ground_truth: List[Dict[str, Any]]) -> Dict[str, float]:
+    """Both lists are per image: ``{"boxes": [n,4], "labels": [n], "scores": [n]}`` (scores only in predictions)."""
+    classes = sorted({int(l) for g in ground_truth for l in g["labels"]})
+    thrs = np.arange(0.5, 0.96, 0.05)
+    per_thr = []
+    for t in thrs:
+        aps = []
+        for c in classes:
+            dets = [(i, float(s), b) for i, p in enumerate(predictions) for b, l, s in zip(p["boxes"], p["labels"], p["scores"]) if int(l) == c]
+            gts = {i: np.asarray([b for b, l in zip(g["boxes"], g["labels"]) if int(l) == c], float).reshape(-1, 4)
+                   for i, g in enumerate(ground_truth)}
+            ap = average_precision(dets, gts, float(t))
+            if ap == ap:
+                aps.append(ap)
+        per_thr.append(np.mean(aps) if aps else 0.0)
+    return {"bbox_mAP": float(np.mean(per_thr)), "bbox_mAP50": float(per_thr[0]), "bbox_mAP75": float(per_thr[5])}
+
+
+def eval_detection(model, samples: Iterable[Tuple[np.ndarray, Dict[str, Any]]]) -> Dict[str, float]:
+    preds, gts = [], []
+    for im, gt in samples:
+        r = model.predict(im)
+        preds.append({"boxes": r.boxes, "labels": r.label_ids, "scores": r.scores})
+        gts.append(gt)
+    return coco_map(preds, gts)
+
+
+def segmentation_metrics(pred: np.ndarray, label: np.ndarray, num_classes: int, ignore_index: int = 255) -> Dict[str, float]:
+    m = label != ignore_index
+    p, l = pred[m].astype(np.int64), label[m].astype(np.int64)
+    conf = np.bincount(l * num_classes + p, minlength=num_classes ** 2).reshape(num_classes, num_classes)
+    inter = np.diag(conf).astype(float)
+    union = conf.sum(0) + conf.sum(1) - inter
+    present = union > 0
+    return {"miou": float((inter[present] / union[present]).mean()) if present.any() else 0.0,
+            "acc": float(inter.sum() / max(conf.sum(), 1))}
+
+
+def eval_segmentation(model, samples: Iterable[Tuple[np.ndarray, np.ndarray]], num_classes: int) -> Dict[str, float]:
+    conf = np.zeros((num_classes, num_classes), np.int64)
+    for im, label in samples:
+        r = model.predict(im)
+        pred = np.asarray(r.label_map, np.int64).reshape(r.shape[:2])
+        m = label != 255
+        conf += np.bincount(label[m].astype(np.int64) * num_classes + pred[m], minlength=num_classes ** 2).reshape(num_classes, num_classes)
+    inter = np.diag(conf).astype(float)
+    union = conf.sum(0) + conf.sum(1) - inter
+    present = union > 0
+    return {"miou": float((inter[present] / union[present]).mean()) if present.any() else 0.0,
+            "acc": float(inter.sum() / max(conf.sum(), 1))}
