@@ -1,0 +1,393 @@
+// C API over an embedded interpreter (see fd_c_api.h). Every entry point takes the GIL, forwards to the
+// Python package and converts results into malloc'ed C arrays. Errors never cross the boundary as
+// exceptions: calls return NULL / false and FD_C_GetLastError() holds the text.
+#include "fd_c_api.h"
+
+#include <Python.h>
+
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+namespace {
+
+thread_local std::string g_err;
+std::once_flag g_init;
+PyObject* g_pkg = nullptr;      // fastdeploy_b200
+PyObject* g_np = nullptr;       // numpy
+bool g_owns_interpreter = false;
+
+void set_err(const std::string& s) { g_err = s; }
+
+void fetch_py_error(const char* what) {
+  PyObject *t = nullptr, *v = nullptr, *tb = nullptr;
+  PyErr_Fetch(&t, &v, &tb);
+  PyErr_NormalizeException(&t, &v, &tb);
+  std::string msg = what;
+  if (v != nullptr) {
+    PyObject* s = PyObject_Str(v);
+    if (s != nullptr) {
+      const char* c = PyUnicode_AsUTF8(s);
+      if (c != nullptr) msg += std::string(": ") + c;
+      Py_DECREF(s);
+    }
+  }
+  Py_XDECREF(t); Py_XDECREF(v); Py_XDECREF(tb);
+  set_err(msg);
+}
+
+void ensure_python() {
+  std::call_once(g_init, [] {
+    if (!Py_IsInitialized()) {
+      Py_InitializeEx(0);
+      g_owns_interpreter = true;
+      PyEval_SaveThread();      // release the GIL acquired by initialisation; every call re-takes it
+    }
+    PyGILState_STATE st = PyGILState_Ensure();
+    g_pkg = PyImport_ImportModule("fastdeploy_b200");
+    if (g_pkg == nullptr) fetch_py_error("import fastdeploy_b200");
+    g_np = PyImport_ImportModule("numpy");
+    if (g_np == nullptr) fetch_py_error("import numpy");
+    PyGILState_Release(st);
+  });
+}
+
+struct Gil {
+  PyGILState_STATE st;
+  Gil() { ensure_python(); st = PyGILState_Ensure(); }
+  ~Gil() { PyGILState_Release(st); }
+};
+
+PyObject* call_method(PyObject* obj, const char* name, const char* fmt = nullptr, ...) {
+  PyObject* m = PyObject_GetAttrString(obj, name);
+  if (m == nullptr) { fetch_py_error(name); return nullptr; }
+  PyObject* args = nullptr;
+  if (fmt != nullptr) {
+    va_list va;
+    va_start(va, fmt);
+    args = Py_VaBuildValue(fmt, va);
+    va_end(va);
+    if (args != nullptr && !PyTuple_Check(args)) {
+      PyObject* t = PyTuple_Pack(1, args);
+      Py_DECREF(args);
+      args = t;
+    }
+  } else {
+    args = PyTuple_New(0);
+  }
+  PyObject* r = args != nullptr ? PyObject_CallObject(m, args) : nullptr;
+  Py_XDECREF(args);
+  Py_DECREF(m);
+  if (r == nullptr) fetch_py_error(name);
+  return r;
+}
+
+// numpy array viewing (copying) a C buffer
+PyObject* np_from_buffer(const void* data, size_t nbytes, const char* dtype, const int64_t* shape, size_t ndim) {
+  PyObject* bytes = PyBytes_FromStringAndSize(static_cast<const char*>(data), static_cast<Py_ssize_t>(nbytes));
+  PyObject* arr = PyObject_CallMethod(g_np, "frombuffer", "Os", bytes, dtype);
+  Py_DECREF(bytes);
+  if (arr == nullptr) { fetch_py_error("numpy.frombuffer"); return nullptr; }
+  PyObject* shp = PyTuple_New(static_cast<Py_ssize_t>(ndim));
+  for (size_t i = 0; i < ndim; ++i) PyTuple_SET_ITEM(shp, i, PyLong_FromLongLong(shape[i]));
+  PyObject* out = PyObject_CallMethod(arr, "reshape", "O", shp);
+  Py_DECREF(shp);
+  Py_DECREF(arr);
+  if (out == nullptr) fetch_py_error("reshape");
+  return out;
+}
+
+PyObject* mat_to_numpy(const FD_C_Mat& m) {
+  const int64_t shape[3] = {m.height, m.width, m.channels};
+  return np_from_buffer(m.data, static_cast<size_t>(m.height) * m.width * m.channels, "uint8", shape, 3);
+}
+
+bool floats_from_seq(PyObject* seq, FD_C_OneDimArrayFloat* out) {
+  PyObject* fast = PySequence_Fast(seq, "sequence expected");
+  if (fast == nullptr) { fetch_py_error("result"); return false; }
+  const Py_ssize_t n = PySequence_Fast_GET_SIZE(fast);
+  out->size = static_cast<size_t>(n);
+  out->data = static_cast<float*>(std::malloc(sizeof(float) * (n > 0 ? n : 1)));
+  for (Py_ssize_t i = 0; i < n; ++i) out->data[i] = static_cast<float>(PyFloat_AsDouble(PySequence_Fast_GET_ITEM(fast, i)));
+  Py_DECREF(fast);
+  return true;
+}
+bool ints_from_seq(PyObject* seq, FD_C_OneDimArrayInt32* out) {
+  PyObject* fast = PySequence_Fast(seq, "sequence expected");
+  if (fast == nullptr) { fetch_py_error("result"); return false; }
+  const Py_ssize_t n = PySequence_Fast_GET_SIZE(fast);
+  out->size = static_cast<size_t>(n);
+  out->data = static_cast<int32_t*>(std::malloc(sizeof(int32_t) * (n > 0 ? n : 1)));
+  for (Py_ssize_t i = 0; i < n; ++i) out->data[i] = static_cast<int32_t>(PyLong_AsLong(PySequence_Fast_GET_ITEM(fast, i)));
+  Py_DECREF(fast);
+  return true;
+}
+
+PyObject* get_class(const char* dotted) {      // e.g. "vision.detection.PPYOLOE"
+  PyObject* cur = g_pkg;
+  Py_XINCREF(cur);
+  std::string path = dotted;
+  size_t pos = 0;
+  while (cur != nullptr && pos <= path.size()) {
+    const size_t dot = path.find('.', pos);
+    const std::string part = path.substr(pos, dot == std::string::npos ? std::string::npos : dot - pos);
+    PyObject* nxt = PyObject_GetAttrString(cur, part.c_str());
+    Py_DECREF(cur);
+    cur = nxt;
+    if (dot == std::string::npos) break;
+    pos = dot + 1;
+  }
+  if (cur == nullptr) fetch_py_error(dotted);
+  return cur;
+}
+
+}  // namespace
+
+struct FD_C_RuntimeOptionWrapper { PyObject* obj; };
+struct FD_C_RuntimeWrapper { PyObject* obj; };
+struct FD_C_ModelWrapper { PyObject* obj; };
+
+extern "C" {
+
+const char* FD_C_GetLastError(void) { return g_err.c_str(); }
+
+FD_C_RuntimeOptionWrapper* FD_C_CreateRuntimeOptionWrapper(void) {
+  Gil g;
+  if (g_pkg == nullptr) return nullptr;
+  PyObject* o = PyObject_CallMethod(g_pkg, "RuntimeOption", nullptr);
+  if (o == nullptr) { fetch_py_error("RuntimeOption"); return nullptr; }
+  return new FD_C_RuntimeOptionWrapper{o};
+}
+void FD_C_DestroyRuntimeOptionWrapper(FD_C_RuntimeOptionWrapper* w) {
+  if (w == nullptr) return;
+  Gil g;
+  Py_XDECREF(w->obj);
+  delete w;
+}
+#define FD_OPT_CALL0(cname, pyname)                                    \
+  void cname(FD_C_RuntimeOptionWrapper* w) {                           \
+    Gil g;                                                             \
+    PyObject* r = call_method(w->obj, pyname);                         \
+    Py_XDECREF(r);                                                     \
+  }
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperUseCpu, "use_cpu")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperUsePaddleBackend, "use_paddle_backend")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperUsePaddleInferBackend, "use_paddle_infer_backend")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperUseOrtBackend, "use_ort_backend")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperUseTrtBackend, "use_trt_backend")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperUseOpenVINOBackend, "use_openvino_backend")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperEnableTrtFP16, "enable_trt_fp16")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperDisableTrtFP16, "disable_trt_fp16")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperEnablePinnedMemory, "enable_pinned_memory")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperDisablePinnedMemory, "disable_pinned_memory")
+
+void FD_C_RuntimeOptionWrapperSetModelPath(FD_C_RuntimeOptionWrapper* w, const char* model_path, const char* params_path,
+                                           FD_C_ModelFormat format) {
+  Gil g;
+  PyObject* r = call_method(w->obj, "set_model_path", "(ssi)", model_path, params_path ? params_path : "", static_cast<int>(format));
+  Py_XDECREF(r);
+}
+void FD_C_RuntimeOptionWrapperUseGpu(FD_C_RuntimeOptionWrapper* w, int gpu_id) {
+  Gil g;
+  PyObject* r = call_method(w->obj, "use_gpu", "(i)", gpu_id);
+  Py_XDECREF(r);
+}
+void FD_C_RuntimeOptionWrapperSetCpuThreadNum(FD_C_RuntimeOptionWrapper* w, int n) {
+  Gil g;
+  PyObject* r = call_method(w->obj, "set_cpu_thread_num", "(i)", n);
+  Py_XDECREF(r);
+}
+void FD_C_RuntimeOptionWrapperSetTrtCacheFile(FD_C_RuntimeOptionWrapper* w, const char* path) {
+  Gil g;
+  PyObject* r = call_method(w->obj, "set_trt_cache_file", "(s)", path);
+  Py_XDECREF(r);
+}
+void FD_C_RuntimeOptionWrapperSetEncryptionKey(FD_C_RuntimeOptionWrapper* w, const char* key) {
+  Gil g;
+  PyObject* r = call_method(w->obj, "set_encryption_key", "(s)", key);
+  Py_XDECREF(r);
+}
+
+// ---------------------------------------------------------------- runtime
+FD_C_RuntimeWrapper* FD_C_CreateRuntimeWrapper(FD_C_RuntimeOptionWrapper* option) {
+  Gil g;
+  if (g_pkg == nullptr || option == nullptr) return nullptr;
+  PyObject* o = PyObject_CallMethod(g_pkg, "Runtime", "O", option->obj);
+  if (o == nullptr) { fetch_py_error("Runtime"); return nullptr; }
+  return new FD_C_RuntimeWrapper{o};
+}
+void FD_C_DestroyRuntimeWrapper(FD_C_RuntimeWrapper* w) {
+  if (w == nullptr) return;
+  Gil g;
+  Py_XDECREF(w->obj);
+  delete w;
+}
+static int int_call(PyObject* o, const char* name) {
+  PyObject* r = call_method(o, name);
+  if (r == nullptr) return -1;
+  const int v = static_cast<int>(PyLong_AsLong(r));
+  Py_DECREF(r);
+  return v;
+}
+int FD_C_RuntimeWrapperNumInputs(FD_C_RuntimeWrapper* w) { Gil g; return int_call(w->obj, "num_inputs"); }
+int FD_C_RuntimeWrapperNumOutputs(FD_C_RuntimeWrapper* w) { Gil g; return int_call(w->obj, "num_outputs"); }
+
+FD_C_Bool FD_C_RuntimeWrapperInfer(FD_C_RuntimeWrapper* w, const FD_C_Tensor* inputs, int n_inputs, FD_C_Tensor* outputs,
+                                   int max_outputs, int* n_outputs) {
+  Gil g;
+  static const char* kDtypes[] = {"float32", "int64", "int32", "uint8"};
+  PyObject* feeds = PyDict_New();
+  for (int i = 0; i < n_inputs; ++i) {
+    const FD_C_Tensor& t = inputs[i];
+    if (t.dtype < 0 || t.dtype > 3) { set_err("unsupported tensor dtype"); Py_DECREF(feeds); return 0; }
+    PyObject* arr = np_from_buffer(t.data, t.nbytes, kDtypes[t.dtype], t.shape.data, t.shape.size);
+    if (arr == nullptr) { Py_DECREF(feeds); return 0; }
+    PyDict_SetItemString(feeds, t.name, arr);
+    Py_DECREF(arr);
+  }
+  PyObject* outs = call_method(w->obj, "infer", "(O)", feeds);
+  Py_DECREF(feeds);
+  if (outs == nullptr) return 0;
+  const Py_ssize_t n = PySequence_Size(outs);
+  *n_outputs = static_cast<int>(n);
+  for (Py_ssize_t i = 0; i < n && i < max_outputs; ++i) {
+    PyObject* o = PySequence_GetItem(outs, i);
+    PyObject* c = PyObject_CallMethod(g_np, "ascontiguousarray", "Os", o, "float32");
+    Py_DECREF(o);
+    if (c == nullptr) { fetch_py_error("ascontiguousarray"); Py_DECREF(outs); return 0; }
+    PyObject* shp = PyObject_GetAttrString(c, "shape");
+    const Py_ssize_t nd = PyTuple_Size(shp);
+    FD_C_Tensor& t = outputs[i];
+    t.name = nullptr;
+    t.dtype = 0;
+    t.shape.size = static_cast<size_t>(nd);
+    t.shape.data = static_cast<int64_t*>(std::malloc(sizeof(int64_t) * (nd > 0 ? nd : 1)));
+    for (Py_ssize_t k = 0; k < nd; ++k) t.shape.data[k] = PyLong_AsLongLong(PyTuple_GET_ITEM(shp, k));
+    Py_DECREF(shp);
+    PyObject* b = PyObject_CallMethod(c, "tobytes", nullptr);
+    Py_DECREF(c);
+    char* buf = nullptr;
+    Py_ssize_t len = 0;
+    PyBytes_AsStringAndSize(b, &buf, &len);
+    t.nbytes = static_cast<size_t>(len);
+    t.data = std::malloc(len > 0 ? len : 1);
+    std::memcpy(t.data, buf, len);
+    Py_DECREF(b);
+  }
+  Py_DECREF(outs);
+  return 1;
+}
+void FD_C_DestroyTensors(FD_C_Tensor* tensors, int n) {
+  for (int i = 0; i < n; ++i) {
+    std::free(tensors[i].data);
+    std::free(tensors[i].shape.data);
+    tensors[i].data = nullptr;
+    tensors[i].shape.data = nullptr;
+  }
+}
+
+// ---------------------------------------------------------------- models
+static FD_C_ModelWrapper* create_model(const char* dotted, const char* model_file, const char* params_file, const char* config_file,
+                                       FD_C_RuntimeOptionWrapper* option, FD_C_ModelFormat format) {
+  Gil g;
+  if (g_pkg == nullptr) return nullptr;
+  PyObject* cls = get_class(dotted);
+  if (cls == nullptr) return nullptr;
+  PyObject* kwargs = PyDict_New();
+  if (option != nullptr) PyDict_SetItemString(kwargs, "runtime_option", option->obj);
+  PyObject* fmt = PyLong_FromLong(static_cast<long>(format));
+  PyDict_SetItemString(kwargs, "model_format", fmt);
+  Py_DECREF(fmt);
+  PyObject* args = config_file != nullptr && config_file[0] != 0
+                       ? Py_BuildValue("(sss)", model_file, params_file ? params_file : "", config_file)
+                       : Py_BuildValue("(ss)", model_file, params_file ? params_file : "");
+  PyObject* o = PyObject_Call(cls, args, kwargs);
+  Py_DECREF(args); Py_DECREF(kwargs); Py_DECREF(cls);
+  if (o == nullptr) { fetch_py_error(dotted); return nullptr; }
+  return new FD_C_ModelWrapper{o};
+}
+void FD_C_DestroyModelWrapper(FD_C_ModelWrapper* w) {
+  if (w == nullptr) return;
+  Gil g;
+  Py_XDECREF(w->obj);
+  delete w;
+}
+static FD_C_Bool predict_detection(FD_C_ModelWrapper* w, FD_C_Mat img, FD_C_DetectionResult* out) {
+  Gil g;
+  PyObject* arr = mat_to_numpy(img);
+  if (arr == nullptr) return 0;
+  PyObject* r = call_method(w->obj, "predict", "(O)", arr);
+  Py_DECREF(arr);
+  if (r == nullptr) return 0;
+  PyObject *boxes = PyObject_GetAttrString(r, "boxes"), *scores = PyObject_GetAttrString(r, "scores"),
+           *labels = PyObject_GetAttrString(r, "label_ids");
+  bool ok = boxes && scores && labels && floats_from_seq(scores, &out->scores) && ints_from_seq(labels, &out->label_ids);
+  if (ok) {
+    const Py_ssize_t n = PySequence_Size(boxes);
+    out->boxes.size = static_cast<size_t>(n);
+    out->boxes.data = static_cast<FD_C_OneDimArrayFloat*>(std::calloc(n > 0 ? n : 1, sizeof(FD_C_OneDimArrayFloat)));
+    for (Py_ssize_t i = 0; i < n && ok; ++i) {
+      PyObject* b = PySequence_GetItem(boxes, i);
+      ok = floats_from_seq(b, &out->boxes.data[i]);
+      Py_DECREF(b);
+    }
+  } else if (PyErr_Occurred()) {
+    fetch_py_error("DetectionResult");
+  }
+  Py_XDECREF(boxes); Py_XDECREF(scores); Py_XDECREF(labels); Py_DECREF(r);
+  return ok ? 1 : 0;
+}
+
+FD_C_PPYOLOEWrapper* FD_C_CreatePPYOLOEWrapper(const char* m, const char* p, const char* c, FD_C_RuntimeOptionWrapper* o,
+                                               FD_C_ModelFormat f) {
+  return create_model("vision.detection.PPYOLOE", m, p, c, o, f);
+}
+void FD_C_DestroyPPYOLOEWrapper(FD_C_PPYOLOEWrapper* w) { FD_C_DestroyModelWrapper(w); }
+FD_C_Bool FD_C_PPYOLOEWrapperPredict(FD_C_PPYOLOEWrapper* w, FD_C_Mat img, FD_C_DetectionResult* r) { return predict_detection(w, img, r); }
+FD_C_Bool FD_C_PPYOLOEWrapperInitialized(FD_C_PPYOLOEWrapper* w) {
+  Gil g;
+  PyObject* r = call_method(w->obj, "initialized");
+  const FD_C_Bool v = r != nullptr && PyObject_IsTrue(r) ? 1 : 0;
+  Py_XDECREF(r);
+  return v;
+}
+FD_C_ModelWrapper* FD_C_CreateDetectionModelWrapper(const char* class_name, const char* m, const char* p, const char* c,
+                                                    FD_C_RuntimeOptionWrapper* o, FD_C_ModelFormat f) {
+  return create_model((std::string("vision.detection.") + class_name).c_str(), m, p, c, o, f);
+}
+FD_C_Bool FD_C_DetectionModelWrapperPredict(FD_C_ModelWrapper* w, FD_C_Mat img, FD_C_DetectionResult* r) {
+  return predict_detection(w, img, r);
+}
+
+FD_C_PaddleClasModelWrapper* FD_C_CreatePaddleClasModelWrapper(const char* m, const char* p, const char* c,
+                                                               FD_C_RuntimeOptionWrapper* o, FD_C_ModelFormat f) {
+  return create_model("vision.classification.PaddleClasModel", m, p, c, o, f);
+}
+void FD_C_DestroyPaddleClasModelWrapper(FD_C_PaddleClasModelWrapper* w) { FD_C_DestroyModelWrapper(w); }
+FD_C_Bool FD_C_PaddleClasModelWrapperPredict(FD_C_PaddleClasModelWrapper* w, FD_C_Mat img, FD_C_ClassifyResult* out) {
+  Gil g;
+  PyObject* arr = mat_to_numpy(img);
+  if (arr == nullptr) return 0;
+  PyObject* r = call_method(w->obj, "predict", "(O)", arr);
+  Py_DECREF(arr);
+  if (r == nullptr) return 0;
+  PyObject *ids = PyObject_GetAttrString(r, "label_ids"), *scores = PyObject_GetAttrString(r, "scores");
+  const bool ok = ids && scores && ints_from_seq(ids, &out->label_ids) && floats_from_seq(scores, &out->scores);
+  Py_XDECREF(ids); Py_XDECREF(scores); Py_DECREF(r);
+  return ok ? 1 : 0;
+}
+
+void FD_C_DestroyClassifyResult(FD_C_ClassifyResult* r) {
+  if (r == nullptr) return;
+  std::free(r->label_ids.data); std::free(r->scores.data);
+  r->label_ids.data = nullptr; r->scores.data = nullptr;
+}
+void FD_C_DestroyDetectionResult(FD_C_DetectionResult* r) {
+  if (r == nullptr) return;
+  for (size_t i = 0; i < r->boxes.size; ++i) std::free(r->boxes.data[i].data);
+  std::free(r->boxes.data); std::free(r->scores.data); std::free(r->label_ids.data);
+  r->boxes.data = nullptr; r->scores.data = nullptr; r->label_ids.data = nullptr;
+}
+
+}  // extern "C"

@@ -1,0 +1,118 @@
+/* C API of the deployment library: opaque wrappers with FD_C_Create / Destroy / Predict entry points,
+ * named after the reference's c_api/fastdeploy_capi (core/fd_type.h, runtime/runtime_option.h,
+ * vision/result.h, vision/detection/ppdet/model.h, vision/classification/ppcls/model.h). The
+ * implementation drives the Python package through an embedded interpreter, so one shared library
+ * serves C, C# (P/Invoke) and Java (JNI) callers; images are plain interleaved BGR buffers. */
+#ifndef FASTDEPLOY_B200_C_API_H_
+#define FASTDEPLOY_B200_C_API_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FD_C_EXPORT __attribute__((visibility("default")))
+
+typedef int8_t FD_C_Bool;
+
+typedef enum { FD_C_ModelFormat_AUTOREC = 0, FD_C_ModelFormat_PADDLE = 1, FD_C_ModelFormat_ONNX = 2 } FD_C_ModelFormat;
+
+typedef struct FD_C_OneDimArrayInt32 { size_t size; int32_t* data; } FD_C_OneDimArrayInt32;
+typedef struct FD_C_OneDimArrayInt64 { size_t size; int64_t* data; } FD_C_OneDimArrayInt64;
+typedef struct FD_C_OneDimArrayFloat { size_t size; float* data; } FD_C_OneDimArrayFloat;
+typedef struct FD_C_TwoDimArrayFloat { size_t size; FD_C_OneDimArrayFloat* data; } FD_C_TwoDimArrayFloat;
+
+/* interleaved uint8 image, BGR channel order (what cv::Mat holds in the reference) */
+typedef struct FD_C_Mat { uint8_t* data; int height; int width; int channels; } FD_C_Mat;
+
+typedef struct FD_C_ClassifyResult {
+  FD_C_OneDimArrayInt32 label_ids;
+  FD_C_OneDimArrayFloat scores;
+} FD_C_ClassifyResult;
+
+typedef struct FD_C_DetectionResult {
+  FD_C_TwoDimArrayFloat boxes;        /* n x 4 */
+  FD_C_OneDimArrayFloat scores;
+  FD_C_OneDimArrayInt32 label_ids;
+} FD_C_DetectionResult;
+
+typedef struct FD_C_Tensor {
+  const char* name;
+  int dtype;                          /* 0 float32, 1 int64, 2 int32, 3 uint8 */
+  FD_C_OneDimArrayInt64 shape;
+  void* data;
+  size_t nbytes;
+} FD_C_Tensor;
+
+typedef struct FD_C_RuntimeOptionWrapper FD_C_RuntimeOptionWrapper;
+typedef struct FD_C_RuntimeWrapper FD_C_RuntimeWrapper;
+typedef struct FD_C_ModelWrapper FD_C_ModelWrapper;
+typedef FD_C_ModelWrapper FD_C_PPYOLOEWrapper;
+typedef FD_C_ModelWrapper FD_C_PaddleClasModelWrapper;
+
+/* last error text of the calling thread ("" when none) */
+FD_C_EXPORT const char* FD_C_GetLastError(void);
+
+/* ---- RuntimeOption */
+FD_C_EXPORT FD_C_RuntimeOptionWrapper* FD_C_CreateRuntimeOptionWrapper(void);
+FD_C_EXPORT void FD_C_DestroyRuntimeOptionWrapper(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetModelPath(FD_C_RuntimeOptionWrapper* w, const char* model_path,
+                                                       const char* params_path, FD_C_ModelFormat format);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperUseCpu(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperUseGpu(FD_C_RuntimeOptionWrapper* w, int gpu_id);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetCpuThreadNum(FD_C_RuntimeOptionWrapper* w, int thread_num);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperUsePaddleBackend(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperUsePaddleInferBackend(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperUseOrtBackend(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperUseTrtBackend(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperUseOpenVINOBackend(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperEnableTrtFP16(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperDisableTrtFP16(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetTrtCacheFile(FD_C_RuntimeOptionWrapper* w, const char* path);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperEnablePinnedMemory(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperDisablePinnedMemory(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetEncryptionKey(FD_C_RuntimeOptionWrapper* w, const char* key);
+
+/* ---- Runtime (generic tensors in, tensors out) */
+FD_C_EXPORT FD_C_RuntimeWrapper* FD_C_CreateRuntimeWrapper(FD_C_RuntimeOptionWrapper* option);
+FD_C_EXPORT void FD_C_DestroyRuntimeWrapper(FD_C_RuntimeWrapper* w);
+FD_C_EXPORT int FD_C_RuntimeWrapperNumInputs(FD_C_RuntimeWrapper* w);
+FD_C_EXPORT int FD_C_RuntimeWrapperNumOutputs(FD_C_RuntimeWrapper* w);
+/* outputs[i].data / shape.data are allocated by the library: release with FD_C_DestroyTensors */
+FD_C_EXPORT FD_C_Bool FD_C_RuntimeWrapperInfer(FD_C_RuntimeWrapper* w, const FD_C_Tensor* inputs, int n_inputs,
+                                               FD_C_Tensor* outputs, int max_outputs, int* n_outputs);
+FD_C_EXPORT void FD_C_DestroyTensors(FD_C_Tensor* tensors, int n);
+
+/* ---- vision models */
+FD_C_EXPORT FD_C_PPYOLOEWrapper* FD_C_CreatePPYOLOEWrapper(const char* model_file, const char* params_file,
+                                                           const char* config_file, FD_C_RuntimeOptionWrapper* option,
+                                                           FD_C_ModelFormat format);
+FD_C_EXPORT void FD_C_DestroyPPYOLOEWrapper(FD_C_PPYOLOEWrapper* w);
+FD_C_EXPORT FD_C_Bool FD_C_PPYOLOEWrapperPredict(FD_C_PPYOLOEWrapper* w, FD_C_Mat img, FD_C_DetectionResult* result);
+FD_C_EXPORT FD_C_Bool FD_C_PPYOLOEWrapperInitialized(FD_C_PPYOLOEWrapper* w);
+
+FD_C_EXPORT FD_C_PaddleClasModelWrapper* FD_C_CreatePaddleClasModelWrapper(const char* model_file, const char* params_file,
+                                                                           const char* config_file,
+                                                                           FD_C_RuntimeOptionWrapper* option,
+                                                                           FD_C_ModelFormat format);
+FD_C_EXPORT void FD_C_DestroyPaddleClasModelWrapper(FD_C_PaddleClasModelWrapper* w);
+FD_C_EXPORT FD_C_Bool FD_C_PaddleClasModelWrapperPredict(FD_C_PaddleClasModelWrapper* w, FD_C_Mat img,
+                                                         FD_C_ClassifyResult* result);
+
+/* any detection class of the Python package by name ("PicoDet", "YOLOv5", ...) */
+FD_C_EXPORT FD_C_ModelWrapper* FD_C_CreateDetectionModelWrapper(const char* class_name, const char* model_file,
+                                                                const char* params_file, const char* config_file,
+                                                                FD_C_RuntimeOptionWrapper* option, FD_C_ModelFormat format);
+FD_C_EXPORT FD_C_Bool FD_C_DetectionModelWrapperPredict(FD_C_ModelWrapper* w, FD_C_Mat img, FD_C_DetectionResult* result);
+FD_C_EXPORT void FD_C_DestroyModelWrapper(FD_C_ModelWrapper* w);
+
+/* ---- results */
+FD_C_EXPORT void FD_C_DestroyClassifyResult(FD_C_ClassifyResult* r);
+FD_C_EXPORT void FD_C_DestroyDetectionResult(FD_C_DetectionResult* r);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

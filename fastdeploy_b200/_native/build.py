@@ -89,10 +89,10 @@ def build_kernels(verbose: bool = False, force: bool = False) -> str:
 
 def build_cpu(verbose: bool = False, force: bool = False) -> str:
     os.makedirs(OBJ_DIR, exist_ok=True)
-    srcs = sorted(glob.glob(os.path.join(CSRC, "cpu", "*.cc")) + glob.glob(os.path.join(CSRC, "capi", "*.cc")))
+    srcs = sorted(glob.glob(os.path.join(CSRC, "cpu", "*.cc")))
     if not srcs:
         return ""
-    hdrs = glob.glob(os.path.join(CSRC, "cpu", "*.h")) + glob.glob(os.path.join(CSRC, "capi", "*.h"))
+    hdrs = glob.glob(os.path.join(CSRC, "cpu", "*.h"))
     cxx = shutil.which("g++") or "g++"
     jobs = []
     objs = []
@@ -119,9 +119,39 @@ def build_cpu(verbose: bool = False, force: bool = False) -> str:
     return CPU_LIB
 
 
+CAPI_LIB = os.path.join(HERE, "libfastdeploy_capi.so")
+
+
+def build_capi(verbose: bool = False, force: bool = False) -> str:
+    """C API shared library (embeds the interpreter: links libpython of the running Python)."""
+    import sysconfig
+    srcs = sorted(glob.glob(os.path.join(CSRC, "capi", "*.cc")))
+    if not srcs:
+        return ""
+    hdrs = glob.glob(os.path.join(CSRC, "capi", "*.h"))
+    if not force and os.path.exists(CAPI_LIB) and not any(_newer(s, CAPI_LIB, hdrs) for s in srcs):
+        return CAPI_LIB
+    inc = sysconfig.get_paths()["include"]
+    if not os.path.exists(os.path.join(inc, "Python.h")):
+        return ""            # no interpreter headers on this machine: the C API is optional
+    libdir = sysconfig.get_config_var("LIBDIR") or ""
+    ver = sysconfig.get_config_var("LDVERSION") or sysconfig.get_python_version()
+    cxx = shutil.which("g++") or "g++"
+    cmd = [cxx] + CXX_FLAGS + ["-shared", "-I", inc, "-I", os.path.join(CSRC, "capi")] + srcs + \
+          ["-o", CAPI_LIB, "-L", libdir, f"-lpython{ver}", f"-Wl,-rpath,{libdir}"]
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    rc, out = _compile(cmd, os.path.join(OBJ_DIR, "link_capi.log"))
+    if verbose or rc != 0:
+        print(out)
+    if rc != 0:
+        raise RuntimeError("building libfastdeploy_capi.so failed")
+    return CAPI_LIB
+
+
 def build_all(verbose: bool = False, force: bool = False) -> None:
     build_kernels(verbose=verbose, force=force)
     build_cpu(verbose=verbose, force=force)
+    build_capi(verbose=verbose, force=force)
 
 
 if __name__ == "__main__":

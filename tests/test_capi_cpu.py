@@ -1,0 +1,44 @@
+"""Builds a C program against the C API header and library and runs it as a child process."""
+import os
+import shutil
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB = os.path.join(ROOT, "fastdeploy_b200", "_native", "libfastdeploy_capi.so")
+
+
+@pytest.mark.skipif(shutil.which("gcc") is None, reason="no C compiler")
+def test_c_program_runs_a_model(tmp_path):
+    if not os.path.exists(LIB):
+        from fastdeploy_b200._native import build
+        if not build.build_capi():
+            pytest.skip("interpreter headers not available")
+    import fastdeploy_b200 as fd
+    from fastdeploy_b200.core.types import ModelFormat
+    from fastdeploy_b200.models.resnet import resnet18_like_onnx
+    model = str(tmp_path / "m.onnx")
+    resnet18_like_onnx(model, seed=0)
+    opt = fd.RuntimeOption(); opt.use_cpu(); opt.set_model_path(model, "", ModelFormat.ONNX)
+    rt = fd.Runtime(opt)
+    info = rt.get_input_info(0)
+    shape = [d if isinstance(d, int) and d > 0 else 1 for d in info.shape]
+    n, c, hw = shape[0], shape[1], shape[2]
+    count = n * c * hw * hw
+    x = ((np.arange(count, dtype=np.uint64) * np.uint64(2654435761)) % np.uint64(1000)).astype(np.float32) / np.float32(1000.0) - np.float32(0.5)
+    ref = float(np.asarray(rt.infer({info.name: x.reshape(n, c, hw, hw)})[0], np.float64).sum())
+    exe = str(tmp_path / "capi_smoke")
+    subprocess.run(["gcc", os.path.join(ROOT, "tests", "capi_smoke.c"), "-I", os.path.join(ROOT, "csrc", "capi"), "-o", exe,
+                    "-L", os.path.dirname(LIB), "-lfastdeploy_capi", f"-Wl,-rpath,{os.path.dirname(LIB)}"], check=True)
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.pathsep.join(p for p in sys.path if p), PYTHONHOME="")
+    env.pop("PYTHONHOME")
+    p = subprocess.run([exe, model, info.name, str(n), str(c), str(hw)], capture_output=True, text=True, env=env, timeout=300)
+    assert p.returncode == 0, p.stdout + p.stderr
+    lines = p.stdout.strip().splitlines()
+    assert lines[0].startswith("inputs=1 outputs=1")
+    chk = float(lines[1].split("checksum=")[1])
+    assert abs(chk - ref) <= 1e-3 * max(1.0, abs(ref)), (chk, ref)
+    assert lines[2] == "bad=null err=set"
