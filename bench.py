@@ -155,12 +155,16 @@ def main():
         host_sets.append([t[i] for i in range(B)])
     dev_sets = [[f.to(dev) for f in frames] for frames in host_sets]
 
+    # The clock sampler starts before the warm-up: the first nvidia-smi query initialises NVML for every GPU
+    # of the box and holds driver locks while it does, which must not land inside a timed region.
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
     # ---------------- device-timed step (inputs resident on the GPU)
     for i in range(max(args.warmup, 3)):
         model.predict_async(dev_sets[i & 1]).result()
     barrier()
-    sampler = ClockSampler(physical_gpu_index(local_rank))
-    sampler.start()
+    time.sleep(0.5)
+    sampler.rows.clear()
     launches0 = model.runtime.gpu_launches
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()

@@ -1,7 +1,8 @@
 // Rasterisers for result visualisation and for matting / segmentation compositing, on interleaved
 // uint8 BGR frames that already live on the device (headless: the output is a device buffer).
 //
-//   draw_boxes        rectangle outlines of a given thickness, one colour per box
+//   draw_boxes        rectangle outlines of a given thickness, one colour per box (boxes are drawn
+//                     concurrently: where outlines of different boxes cross, either colour may win)
 //   blend_label_map   per-pixel class map -> colour table, alpha-blended over the frame
 //   blend_masks       per-instance binary masks alpha-blended with the instance colour
 //   draw_points       filled discs (key points, landmarks)

@@ -16,7 +16,7 @@ def _img(h=97, w=131, seed=0):
 def test_boxes_match_host_rectangles():
     im = _img()
     d = DetectionResult()
-    d.boxes = [[5, 6, 60, 40], [50, 30, 129, 95], [-4, -3, 10, 12]]
+    d.boxes = [[15, 16, 60, 40], [70, 50, 129, 95], [-4, -3, 10, 12]]     # edges that do not cross: boxes are drawn concurrently
     d.scores = [0.9, 0.8, 0.7]
     d.label_ids = [1, 7, 300]
     out = V.vis_detection(torch.as_tensor(im).cuda(), d, line_size=2).cpu().numpy()
