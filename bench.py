@@ -32,7 +32,10 @@ REF_UNAVAILABLE = ("refused by a safety check: building the reference (python se
 
 
 class ClockSampler:
-    """Polls nvidia-smi for SM clocks and throttle reasons while the timed region runs."""
+    """Samples SM clocks and throttle reasons every 200 ms while the timed regions run. NVML is called in
+    process (three light queries per sample); spawning ``nvidia-smi -lms`` instead was seen to stall the
+    GPUs of a multi-GPU box for tens of milliseconds per poll, which lands inside short timed regions.
+    Falls back to ``nvidia-smi`` when the NVML binding is missing."""
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -40,11 +43,24 @@ class ClockSampler:
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
-        self.rows = []
+        self.rows = []          # (sm_mhz, max_mhz, set of reason names)
         self.proc = None
         self.thread = None
+        self._stop = threading.Event()
+        self._nvml = None
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+            self._max = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self._nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
                                           "-lms", "200", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
@@ -52,35 +68,55 @@ class ClockSampler:
         except OSError:
             self.proc = None
             return
-        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread = threading.Thread(target=self._read_smi, daemon=True)
         self.thread.start()
 
-    def _read(self):
+    def ready(self) -> bool:
+        return bool(self.rows) or (self._nvml is None and self.proc is None)
+
+    def _poll_nvml(self):
+        n = self._nvml
+        names = (("hw_slowdown", getattr(n, "nvmlClocksEventReasonHwSlowdown", 0x8)),
+                 ("hw_thermal_slowdown", getattr(n, "nvmlClocksEventReasonHwThermalSlowdown", 0x40)),
+                 ("sw_thermal_slowdown", getattr(n, "nvmlClocksEventReasonSwThermalSlowdown", 0x20)),
+                 ("sw_power_cap", getattr(n, "nvmlClocksEventReasonSwPowerCap", 0x4)))
+        get_reasons = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(n, "nvmlDeviceGetCurrentClocksThrottleReasons", None)
+        while not self._stop.is_set():
+            try:
+                sm = float(n.nvmlDeviceGetClockInfo(self._handle, n.NVML_CLOCK_SM))
+                mask = int(get_reasons(self._handle)) if get_reasons else 0
+                self.rows.append((sm, self._max, {k for k, bit in names if mask & bit}))
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def _read_smi(self):
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) >= 8:
-                self.rows.append(parts)
+                try:
+                    reasons = {k for k, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                                  "sw_power_cap"), parts[4:8]) if v.lower().startswith("active")}
+                    self.rows.append((float(parts[1]), float(parts[2]), reasons))
+                except ValueError:
+                    continue
 
     def stop(self):
+        self._stop.set()
         if self.proc is not None:
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
             except Exception:
                 self.proc.kill()
-        sm, mx, reasons = [], 0.0, set()
-        for r in self.rows:
-            try:
-                sm.append(float(r[1]))
-                mx = max(mx, float(r[2]))
-            except ValueError:
-                continue
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        sm.sort()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        sm = sorted(r[0] for r in self.rows)
+        mx = max((r[1] for r in self.rows), default=0.0)
+        reasons = set().union(*(r[2] for r in self.rows)) if self.rows else set()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "source": "nvml" if self._nvml is not None else "nvidia-smi"}
 
 
 def physical_gpu_index(local_rank: int) -> int:
@@ -102,6 +138,8 @@ def main():
     ap.add_argument("--batch", type=int, default=32, help="images per GPU per step")
     ap.add_argument("--variant", default="l")
     ap.add_argument("--model-dir", default="")
+    ap.add_argument("--latency-iters", type=int, default=50)
+    ap.add_argument("--skip-latency", action="store_true")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -172,7 +210,7 @@ def main():
         return dets
 
     t_wait = time.time()
-    while not sampler.rows and sampler.proc is not None and time.time() - t_wait < 10.0:
+    while not sampler.ready() and time.time() - t_wait < 10.0:
         time.sleep(0.05)                          # NVML is initialised once the first sample is in
     run_steps(dev_sets, max(args.warmup, 3))      # warm-up in the same pipelined pattern as the timed loop
     barrier()                                     # no idle gap from here on: an idle GPU drops its clocks
@@ -196,8 +234,17 @@ def main():
     e3.record()
     barrier()
     ms_e2e = e2.elapsed_time(e3)
-    clocks = sampler.stop()
     h2d, d2h = model.h2d_bytes_last, model.d2h_bytes_last
+    # ---------------- batch-1 latency through the public API (one pinned 1080p frame in, detections out)
+    lat = []
+    if not args.skip_latency:
+        for i in range(3):
+            model.predict(host_sets[0][i])
+        for i in range(args.latency_iters):
+            t0 = time.perf_counter()
+            model.predict(host_sets[i & 1][i % B])
+            lat.append((time.perf_counter() - t0) * 1e3)
+    clocks = sampler.stop()
 
     if world > 1:
         t = torch.tensor([ms_dev, ms_e2e], device=dev, dtype=torch.float64)
@@ -220,6 +267,8 @@ def main():
             "e2e": {"value": round(e2e, 1), "unit": "images/s", "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h), "ms_per_step": round(ms_e2e / args.steps, 3),
                     "detections_read": int(n_det)},
+            "latency": ({"p50_batch1_ms": round(float(np.percentile(lat, 50)), 3), "p99_batch1_ms": round(float(np.percentile(lat, 99)), 3),
+                         "iters": len(lat), "what": "rank 0, PPYOLOE.predict on one pinned 1080x1920 frame, wall clock"} if lat else None),
             "gpu_launches": int(launches), "clocks": clocks, "impl": "ours",
         }
         print(json.dumps(out))
