@@ -2,3 +2,4 @@
 layers and the data-parallel serving scheduler."""
 from .comm import Communicator, HeapBlock, HeapLayout, shard_rows  # noqa: F401
 from .tp import ColumnParallelLinear, RowParallelLinear, TensorParallelMLP  # noqa: F401
+from .health import RankHealth, RankLostError  # noqa: F401
