@@ -43,6 +43,7 @@ enum SimpleKind : int {
   kAvgPool = 9,
   kCast = 10,
   kUnary = 11,
+  kDepthwiseConv = 12,
 };
 
 // ---- 16-bit pack helpers -----------------------------------------------------------
@@ -408,6 +409,55 @@ static inline int grid_for(long long total, int block) {
 
 using namespace fdb;
 
+// ---- depthwise convolution -----------------------------------------------------------
+// p0 x (16-bit NHWC), p1 w fp32 [KH*KW][C], p2 bias fp32 [C] or null, p3 y (16-bit NHWC);
+// i0 N, i1 H, i2 W, i3 C, i4 x_ld, i5 Ho, i6 Wo, i7 y_ld, i8 KH, i9 KW, i10 stride_h, i11 stride_w,
+// i12 pad_top, i13 pad_left, i14 bf16, i15 x_n_stride, i16 y_n_stride, i17 act; f0 alpha, f1 beta.
+// One thread = one output pixel x 8 channels: KH*KW 16-byte input loads, weights through L1, fp32
+// accumulation, bias + activation fused. Memory bound by construction (one MAC per loaded value).
+template <bool BF16>
+__global__ void depthwise_conv_kernel(const uint8_t* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                                      uint8_t* __restrict__ y, long long total, int H, int W, int C8, int x_ld, int Ho, int Wo,
+                                      int y_ld, int KH, int KW, int sh, int sw, int pt, int pl, long long xns, long long yns,
+                                      int act, float alpha, float beta) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int cg = static_cast<int>(i % C8);
+    long long r = i / C8;
+    const int ow = static_cast<int>(r % Wo); r /= Wo;
+    const int oh = static_cast<int>(r % Ho);
+    const int n = static_cast<int>(r / Ho);
+    const int c0 = cg * 8, C = C8 * 8;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = bias != nullptr ? bias[c0 + j] : 0.f;
+    const uint8_t* xn = x + static_cast<size_t>(n) * xns * 2;
+    for (int kh = 0; kh < KH; ++kh) {
+      const int ih = oh * sh - pt + kh;
+      if (ih < 0 || ih >= H) continue;
+      for (int kw = 0; kw < KW; ++kw) {
+        const int iw = ow * sw - pl + kw;
+        if (iw < 0 || iw >= W) continue;
+        const uint4 v = *reinterpret_cast<const uint4*>(xn + ((static_cast<size_t>(ih) * W + iw) * x_ld + c0) * 2);
+        float f[8];
+        unpack8<BF16>(v, f);
+        const float4 w0 = *reinterpret_cast<const float4*>(w + static_cast<size_t>(kh * KW + kw) * C + c0);
+        const float4 w1 = *reinterpret_cast<const float4*>(w + static_cast<size_t>(kh * KW + kw) * C + c0 + 4);
+        acc[0] = fmaf(f[0], w0.x, acc[0]); acc[1] = fmaf(f[1], w0.y, acc[1]);
+        acc[2] = fmaf(f[2], w0.z, acc[2]); acc[3] = fmaf(f[3], w0.w, acc[3]);
+        acc[4] = fmaf(f[4], w1.x, acc[4]); acc[5] = fmaf(f[5], w1.y, acc[5]);
+        acc[6] = fmaf(f[6], w1.z, acc[6]); acc[7] = fmaf(f[7], w1.w, acc[7]);
+      }
+    }
+    if (act != kActNone) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = act_f32(acc[j], act, alpha, beta);
+    }
+    *reinterpret_cast<uint4*>(y + (static_cast<size_t>(n) * yns + (static_cast<size_t>(oh) * Wo + ow) * y_ld + c0) * 2) =
+        pack8<BF16>(acc);
+  }
+}
+
 FDB_API void* fdb_simple_create(int kind, const SimpleDesc* dp) {
   const SimpleDesc d = *dp;
   auto* op = new LambdaOp();
@@ -532,6 +582,28 @@ FDB_API void* fdb_simple_create(int kind, const SimpleDesc* dp) {
         const int grid = grid_for(total, 256);
         if (bf) binary_kernel<true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (const uint8_t*)d.p[1], (uint8_t*)d.p[2], total, C / 8, a_ld, b_ld, y_ld, bop, act, b_mode, al, be);
         else binary_kernel<false><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (const uint8_t*)d.p[1], (uint8_t*)d.p[2], total, C / 8, a_ld, b_ld, y_ld, bop, act, b_mode, al, be);
+        FDB_LAUNCH_CHECK();
+      };
+      break;
+    }
+    case kDepthwiseConv: {
+      const int N = d.i[0], H = d.i[1], W = d.i[2], C = d.i[3], x_ld = d.i[4], Ho = d.i[5], Wo = d.i[6], y_ld = d.i[7];
+      const int KH = d.i[8], KW = d.i[9], sh = d.i[10], sw = d.i[11], pt = d.i[12], pl = d.i[13];
+      const bool bf = d.i[14] != 0;
+      const long long xns = d.i[15] > 0 ? d.i[15] : static_cast<long long>(H) * W * x_ld;
+      const long long yns = d.i[16] > 0 ? d.i[16] : static_cast<long long>(Ho) * Wo * y_ld;
+      const int act = d.i[17];
+      const float al = d.f[0], be = d.f[1];
+      if (C % 8 || x_ld % 8 || y_ld % 8) { set_error("depthwise_conv: C/ld must be multiples of 8"); delete op; return nullptr; }
+      const long long total = static_cast<long long>(N) * Ho * Wo * (C / 8);
+      op->fn = [=](cudaStream_t s) {
+        const int grid = grid_for(total, 256);
+        if (bf) depthwise_conv_kernel<true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (const float*)d.p[1], (const float*)d.p[2],
+                                                                 (uint8_t*)d.p[3], total, H, W, C / 8, x_ld, Ho, Wo, y_ld, KH, KW, sh,
+                                                                 sw, pt, pl, xns, yns, act, al, be);
+        else depthwise_conv_kernel<false><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (const float*)d.p[1], (const float*)d.p[2],
+                                                                (uint8_t*)d.p[3], total, H, W, C / 8, x_ld, Ho, Wo, y_ld, KH, KW, sh,
+                                                                sw, pt, pl, xns, yns, act, al, be);
         FDB_LAUNCH_CHECK();
       };
       break;

@@ -134,3 +134,18 @@ def unary(x: torch.Tensor, y: torch.Tensor, *, rows: int, c: int, act: str, x_ld
 def cast(x: torch.Tensor, y: torch.Tensor) -> NativeOp:
     assert x.numel() == y.numel()
     return make_simple(K_CAST, [x, y], [x.numel(), dtype_code(x.dtype), dtype_code(y.dtype)], name="cast")
+
+
+K_DEPTHWISE = 12
+
+
+def depthwise_conv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], y: torch.Tensor, *, n: int, h: int,
+                   w_in: int, c: int, kernel: Tuple[int, int], stride: Tuple[int, int], pad: Tuple[int, int],
+                   out_hw: Tuple[int, int], act: Optional[str] = None, act_alpha: float = 0.0, act_beta: float = 0.0,
+                   x_ld: Optional[int] = None, y_ld: Optional[int] = None, x_n_stride: int = 0, y_n_stride: int = 0) -> NativeOp:
+    """Depthwise convolution on NHWC 16-bit tensors; ``w`` is fp32 ``[KH*KW, C]`` (C padded to 8)."""
+    from .base import ACT
+    assert w.dtype == torch.float32 and w.shape == (kernel[0] * kernel[1], c)
+    return make_simple(K_DEPTHWISE, [x, w, bias, y],
+                       [n, h, w_in, c, x_ld or c, out_hw[0], out_hw[1], y_ld or c, kernel[0], kernel[1], stride[0], stride[1],
+                        pad[0], pad[1], _bf(x), x_n_stride, y_n_stride, ACT[act]], [act_alpha, act_beta], name="depthwise_conv")

@@ -347,10 +347,13 @@ class Lowering:
     def lower_FusedConv(self, node: Node):
         x_name, w_name = node.inputs[0], node.inputs[1]
         w = self.g.initializers[w_name]
-        if w.ndim != 4 or node.attr("group", 1) != 1 or any(d != 1 for d in node.attr("dilations", [1, 1])):
+        if w.ndim != 4 or any(d != 1 for d in node.attr("dilations", [1, 1])):
             return False
         if not self.is4d(x_name):
             return False
+        group = node.attr("group", 1)
+        if group != 1:
+            return self._lower_depthwise(node, w, group)
         strides = node.attr("strides", [1, 1])
         if strides[0] != strides[1]:
             return False
@@ -416,6 +419,41 @@ class Lowering:
         self.vals[out_name] = y
 
     lower_Conv = lower_FusedConv
+
+    def _lower_depthwise(self, node: Node, w: np.ndarray, group: int):
+        """Depthwise convolution (one filter per channel): CUDA-core kernel, bias and activation fused."""
+        cout, cpg, kh, kw = w.shape
+        x = self.as_nhwc(node.inputs[0])
+        n, cx, h, wd = x.logical_shape
+        if cpg != 1 or group != cx or cout != cx or (len(node.inputs) > 3 and node.inputs[3]):
+            return False
+        strides = node.attr("strides", [1, 1])
+        pads = interp._pads_2d(node, x.logical(), [kh, kw], strides, node.attr("dilations", [1, 1]))
+        n_o, c_o, ho, wo = self.info.shapes[node.outputs[0]]
+        cp = _round8(cx)
+        key = (node.inputs[1], "dw")
+        if key not in self.packed:
+            wk = np.zeros((kh * kw, cp), np.float32)
+            wk[:, :cx] = np.asarray(w, np.float32).reshape(cx, kh * kw).T
+            self.packed[key] = torch.from_numpy(wk).to(self.device)
+        bias = None
+        if len(node.inputs) > 2 and node.inputs[2]:
+            b = np.zeros(cp, np.float32)
+            b[:cx] = np.asarray(self.g.initializers[node.inputs[2]], np.float32).reshape(-1)
+            bias = torch.from_numpy(b).to(self.device)
+        y = self.out_nhwc(node.outputs[0], None)
+        if x.ld < cp or y.ld < cp:
+            return False
+        op = K.depthwise_conv(x.t, self.packed[key], bias, y.t, n=n, h=h, w_in=wd, c=cp, kernel=(kh, kw),
+                              stride=(strides[0], strides[1]), pad=(pads[0], pads[1]), out_hw=(ho, wo),
+                              act=node.attr("activation", "none"), act_alpha=node.attr("act_alpha", 0.0),
+                              act_beta=node.attr("act_beta", 0.0), x_ld=x.ld, y_ld=y.ld, x_n_stride=x.n_stride,
+                              y_n_stride=y.n_stride)
+        op.keep.append(bias)
+        self.plan.add_native(op, node)
+        op.launch()
+        self.vals[node.outputs[0]] = y
+        return None
 
     # ------------------------------------------------------------------ gemm
     def lower_FusedGemm(self, node: Node):

@@ -201,3 +201,32 @@ def test_multiclass_nms_keep_all_and_background():
     assert num == int(ref_num[0])
     assert np.array_equal(nms.out_index[0, :num].cpu().numpy(), ref_idx)
     assert np.allclose(nms.out[0, :num].cpu().numpy(), ref_out, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("k,stride,act", [(3, 1, "relu"), (3, 2, "hard_swish"), (5, 1, None), (5, 2, "hard_sigmoid")])
+def test_depthwise_conv_matches_fp32_reference(dtype, k, stride, act):
+    from fastdeploy_b200.ops import nhwc as K
+    torch.manual_seed(0)
+    n, h, w, c = 2, 23, 31, 24
+    x = torch.randn(n, h, w, c, device="cuda").to(dtype)
+    wt = torch.randn(c, 1, k, k, device="cuda") * 0.3
+    b = torch.randn(c, device="cuda")
+    pad = k // 2
+    ho, wo = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+    y = torch.empty(n, ho, wo, c, device="cuda", dtype=dtype)
+    wk = wt.reshape(c, k * k).t().contiguous()
+    op = K.depthwise_conv(x, wk, b, y, n=n, h=h, w_in=w, c=c, kernel=(k, k), stride=(stride, stride), pad=(pad, pad),
+                          out_hw=(ho, wo), act=act, act_alpha=0.2, act_beta=0.5)
+    op.launch()
+    torch.cuda.synchronize()
+    ref = torch.nn.functional.conv2d(x.float().permute(0, 3, 1, 2), wt, b, stride=stride, padding=pad, groups=c)
+    if act == "relu":
+        ref = torch.relu(ref)
+    elif act == "hard_swish":
+        ref = torch.nn.functional.hardswish(ref)
+    elif act == "hard_sigmoid":
+        ref = torch.clamp(0.2 * ref + 0.5, 0, 1)
+    ref = ref.permute(0, 2, 3, 1)
+    tol = 3e-2 if dtype == torch.bfloat16 else 5e-3
+    assert (y.float() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())

@@ -1,0 +1,38 @@
+"""PP-OCRv3 stage networks on the GPU back end against the CPU interpreter."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("stage,shape", [("det", [1, 3, 160, 224]), ("cls", [4, 3, 48, 192]), ("rec", [2, 3, 48, 160])])
+def test_stage_matches_cpu(stage, shape, tmp_path):
+    import fastdeploy_b200 as fd
+    from fastdeploy_b200.models import ppocr
+    net = {"det": ppocr.build_det, "cls": ppocr.build_cls, "rec": ppocr.build_rec}[stage]()
+    m, p = net.serialize()
+    mf, pf = str(tmp_path / "m.pdmodel"), str(tmp_path / "m.pdiparams")
+    open(mf, "wb").write(m)
+    open(pf, "wb").write(p)
+    x = np.random.default_rng(0).standard_normal(shape).astype(np.float32)
+    outs = {}
+    for dev in ("cpu", "gpu"):
+        opt = fd.RuntimeOption()
+        opt.set_model_path(mf, pf)
+        if dev == "gpu":
+            opt.use_gpu(0)
+            opt.enable_trt_fp16()
+        else:
+            opt.use_cpu()
+        rt = fd.Runtime(opt)
+        outs[dev] = np.asarray(rt.infer({rt.get_input_info(0).name: x})[0], np.float32)
+        if dev == "gpu":
+            plan = rt.plan_for_shapes({rt.get_input_info(0).name: shape})
+            native = plan.native_kernel_launches
+            torch_steps = sum(1 for s in plan.steps if s.name.startswith("torch"))
+            assert native > 5 * max(torch_steps, 1), (native, torch_steps)
+    a, b = outs["cpu"], outs["gpu"]
+    assert a.shape == b.shape
+    denom = max(float(np.abs(a).max()), 1e-3)
+    assert float(np.abs(a - b).max()) / denom < 6e-2
