@@ -399,3 +399,7 @@ class PPOCRv4(PPOCRv3):
 
 
 PPOCRSystemv2, PPOCRSystemv3, PPOCRSystemv4 = PPOCRv2, PPOCRv3, PPOCRv4
+
+
+from .structure import (PPStructureV2Table, StructureV2Layout, StructureV2LayoutPostprocessor, StructureV2Table,  # noqa: E402,F401
+                        StructureV2TablePostprocessor, StructureV2TablePreprocessor, build_html)

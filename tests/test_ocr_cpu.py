@@ -70,3 +70,45 @@ def test_ppocr_pipeline_cpu(tmp_path):
     assert len(res.boxes) >= 1
     assert len(res.text) == len(res.boxes) == len(res.rec_scores) == len(res.cls_labels)
     assert "det boxes" in str(res)
+
+
+def test_table_structure_decode_and_html(tmp_path):
+    import numpy as np
+    from fastdeploy_b200.vision.ocr import StructureV2TablePostprocessor, build_html
+    p = tmp_path / "dict.txt"
+    p.write_text("\n".join(["<thead>", "<tr>", "<td>", "</td>", "</tr>", "</thead>", "<td></td>", "beg", "end"]) + "\n")
+    pp = StructureV2TablePostprocessor(str(p))
+    assert pp.dict_character[0] == "sos" and pp.dict_character[-1] == "eos" and "<td>" not in pp.dict_character
+    V, T = len(pp.dict_character), 8
+    probs = np.zeros((1, T, V), np.float32)
+    for i, t in enumerate(["beg", "<tr>", "<td></td>", "<td></td>", "</tr>", "eos", "<tr>"]):
+        probs[0, i, pp.dict_character.index(t)] = 1
+    boxes = np.zeros((1, T, 4), np.float32)
+    boxes[0, 2] = [0.1, 0.1, 0.4, 0.3]
+    boxes[0, 3] = [0.5, 0.1, 0.9, 0.3]
+    b, t = pp.run(boxes, probs, [(1000, 500, 488, 244)])
+    assert t[0] == ["<html>", "<body>", "<table>", "<tr>", "<td></td>", "<td></td>", "</tr>", "</table>", "</body>", "</html>"]
+    assert b[0][0] == [100, 50, 400, 50, 400, 150, 100, 150]
+    html = build_html(t[0], b[0], [[520, 60, 800, 60, 800, 140, 520, 140], [120, 55, 300, 55, 300, 145, 120, 145]], ["B", "A"])
+    assert html == "<html><body><table><tr><td>A</td><td>B</td></tr></table></body></html>"
+
+
+def test_layout_gfl_decode():
+    import numpy as np
+    from fastdeploy_b200.vision.ocr import StructureV2LayoutPostprocessor
+    pp = StructureV2LayoutPostprocessor()
+    in_w, in_h = 64, 64
+    outs = []
+    for s in pp.fpn_stride:
+        a = int(np.ceil(in_w / s)) * int(np.ceil(in_h / s))
+        outs.append(np.zeros((1, a, pp.num_class), np.float32))
+    for s in pp.fpn_stride:
+        a = int(np.ceil(in_w / s)) * int(np.ceil(in_h / s))
+        outs.append(np.zeros((1, a, 4 * pp.reg_max), np.float32))
+    outs[0][0, 8 * 3 + 4, 2] = 0.9                       # stride 8, cell (y=3, x=4)
+    reg = np.full((4, pp.reg_max), -20.0, np.float32)
+    reg[:, 2] = 20.0                                     # every distance = 2 strides
+    outs[4][0, 8 * 3 + 4] = reg.reshape(-1)
+    r = pp.run(outs, (128, 128, in_w, in_h))
+    assert r.label_ids == [2] and abs(r.scores[0] - 0.9) < 1e-6
+    assert np.allclose(r.boxes[0], [(36 - 16) * 2, (28 - 16) * 2, (36 + 16) * 2, (28 + 16) * 2], atol=1e-3)
