@@ -27,3 +27,20 @@ def test_ernie_tiny_fusion_equivalence(task):
     out = Interpreter(g2).run(feeds)
     for k in ref:
         assert float((ref[k] - out[k]).abs().max()) < 1e-5
+
+
+def test_vit_tiny_fusion_equivalence():
+    from fastdeploy_b200.importer.paddle_import import load_paddle
+    from fastdeploy_b200.ir.interp import Interpreter
+    from fastdeploy_b200.ir.passes import optimize
+    from fastdeploy_b200.models.vit import build_vit
+    g = load_paddle(*build_vit("tiny", image=32, num_classes=10).serialize())
+    x = np.random.RandomState(0).randn(2, 3, 32, 32).astype(np.float32)
+    ref = Interpreter(g).run({"x": x})
+    g2 = optimize(g, {"x": [2, 3, 32, 32]}, level=2)
+    hist = g2.op_histogram()
+    assert hist.get("Attention") == 2 and hist.get("FusedGemm", 0) >= 9 and hist.get("LayerNormalization", 0) >= 5, hist
+    out = Interpreter(g2).run({"x": x})
+    for k in ref:
+        assert float((ref[k] - out[k]).abs().max()) < 1e-5
+        assert abs(float(out[k].sum()) - 2.0) < 1e-4        # two softmax rows
