@@ -79,6 +79,10 @@ struct ConvGemmDesc {
   // peer_ready = M / 128 flags in local memory; peer_copiers = CTAs set aside to pull the remote shards.
   unsigned int* peer_ready;
   int peer_copiers;
+  // fp8 operands (dtype = kF8E4M3, generic kernel only): fp32 scales applied to the fp32 accumulator in
+  // the epilogue, scale_a per output row (pixel / token), scale_b per output channel; either may be null.
+  const float* scale_a;
+  const float* scale_b;
 };
 
 // Device-resident table of the peers' tensor maps and counters (host-written before any launch).
@@ -109,6 +113,10 @@ struct ConvGemmParams {
   int y_tma;   // 16-bit output leaves through shared-memory staging + TMA tensor stores
   const PeerTable* peer;   // null unless peer_mode != 0
   int peer_mode, peer_rows, peer_rank;
+  int kblk;                // K elements per pipeline stage: 64 (16-bit operands) or 128 (fp8), always 128 bytes
+  int fp8;                 // operands are e4m3
+  const float* scale_a;    // fp8: per-row and per-column dequantisation scales (null = 1)
+  const float* scale_b;
   int gemm_ctas;           // CTAs that run the GEMM roles; the rest of the grid (peer_mode 1) are copiers
   int peer_world, peer_rot;       // all-gather mode: ranks, and the tile-row rotation that puts local rows first
   unsigned peer_epoch;            // value the ready flags take in this launch
@@ -294,12 +302,19 @@ __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParam
                                           int col_limit, uint8_t* yrow, const uint8_t* rrow,
                                           bool in_bf16, int out_es, uint32_t stage_addr = 0,
                                           const float* bias_s = nullptr, bool has_pre = false,
-                                          uint4 res_pre = make_uint4(0, 0, 0, 0)) {
+                                          uint4 res_pre = make_uint4(0, 0, 0, 0), float row_scale = 1.f) {
   const int nvalid = min(8, col_limit - co);
   if (nvalid <= 0) return;
   float x[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) x[j] = __uint_as_float(v[j]);
+  if (p.fp8) {   // dequantise: accumulator * scale of the row * scale of the column
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sb = (p.scale_b != nullptr && j < nvalid) ? __ldg(p.scale_b + co + j) : 1.f;
+      x[j] *= row_scale * sb;
+    }
+  }
   if (bias_s != nullptr) {   // shared-memory copy (zeros where there is no bias), padded to the tile width
     const float4 b0 = *reinterpret_cast<const float4*>(bias_s);
     const float4 b1 = *reinterpret_cast<const float4*>(bias_s + 4);
@@ -456,7 +471,7 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
   const bool out_bf16 = p.out_dtype == kBF16;
   // after-activation residual rows can be fetched while the accumulator is still being produced
   const bool res_pre = p.res_mode == 2 && p.res_vec != 0 && in_bf16 == out_bf16;
-  const bool simple = p.res_mode == 0 || res_pre;   // everything else takes the general per-group path
+  const bool simple = (p.res_mode == 0 || res_pre) && !p.fp8;   // everything else takes the general per-group path
   const uint32_t buf = stage0 + team * kStageTileBytes;
   const uint32_t tfull = tfull0 + 8u * team, tempty = tempty0 + 8u * team;
   const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + team * BN;
@@ -502,6 +517,8 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
     const int colbase = n_tile * BN;
     const int col_limit = min(p.Cout, colbase + BN);
     const int nblk = (col_limit - colbase + 63) / 64;
+    const float row_scale = (p.fp8 && p.scale_a != nullptr && valid)
+                                ? __ldg(p.scale_a + (static_cast<long long>(img) * p.Ho + oh) * p.Wo + ow) : 1.f;
     if (p.n_tiles > 1) {
       float* dst = s_bias + team * 256;
       for (int i = tt; i < BN; i += 128) dst[i] = (p.bias != nullptr && colbase + i < p.Cout) ? __ldg(p.bias + colbase + i) : 0.f;
@@ -563,7 +580,7 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
 #pragma unroll
               for (int g = 0; g < 4; ++g) {
                 epilogue8<ACT>(v + g * 8, p, co0 + h * 32 + g * 8, col_limit, nullptr, rrow, in_bf16, 2,
-                               srow + (((chunk0 + g) ^ row7) << 4), bs + g * 8, false);
+                               srow + (((chunk0 + g) ^ row7) << 4), bs + g * 8, false, make_uint4(0, 0, 0, 0), row_scale);
               }
             }
           }
@@ -654,6 +671,8 @@ __device__ __forceinline__ void epilogue_loop(const ConvGemmParams& p, uint32_t 
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
     const int colbase = n_tile * BN;
     const int col_limit = min(p.Cout, colbase + BN);
+    const float row_scale = (p.fp8 && p.scale_a != nullptr && valid)
+                                ? __ldg(p.scale_a + (static_cast<long long>(img) * p.Ho + oh) * p.Wo + ow) : 1.f;
     uint32_t va[32], vb[32];
     int c = c_begin;
     bool have = c < c_end && colbase + c * 32 < col_limit;
@@ -665,7 +684,8 @@ __device__ __forceinline__ void epilogue_loop(const ConvGemmParams& p, uint32_t 
       if (valid) {
 #pragma unroll
         for (int g = 0; g < 4; ++g)
-          epilogue8<ACT>(va + g * 8, p, colbase + c * 32 + g * 8, col_limit, yrow, rrow, in_bf16, out_es);
+          epilogue8<ACT>(va + g * 8, p, colbase + c * 32 + g * 8, col_limit, yrow, rrow, in_bf16, out_es, 0, nullptr, false,
+                         make_uint4(0, 0, 0, 0), row_scale);
       }
       if (!next) break;
       ++c;
@@ -675,7 +695,8 @@ __device__ __forceinline__ void epilogue_loop(const ConvGemmParams& p, uint32_t 
       if (valid) {
 #pragma unroll
         for (int g = 0; g < 4; ++g)
-          epilogue8<ACT>(vb + g * 8, p, colbase + c * 32 + g * 8, col_limit, yrow, rrow, in_bf16, out_es);
+          epilogue8<ACT>(vb + g * 8, p, colbase + c * 32 + g * 8, col_limit, yrow, rrow, in_bf16, out_es, 0, nullptr, false,
+                         make_uint4(0, 0, 0, 0), row_scale);
       }
       ++c;
       have = next;
@@ -813,7 +834,7 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int kcol = 0;
         for (int kh = 0; ok && kh < p.KH; ++kh) {
           for (int kw = 0; ok && kw < p.KW; ++kw) {
-            for (int kb = 0; kb < p.kb_per_tap; ++kb, kcol += kBK) {
+            for (int kb = 0; kb < p.kb_per_tap; ++kb, kcol += p.kblk) {
               if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, kStatusTimeoutProducer)) {
                 ok = false;
                 break;
@@ -822,7 +843,7 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               armed |= 1u << s;
               armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
               const uint32_t a_dst = tile0 + s * Cfg::kStageBytes;
-              tma_load_4d(a_dst, &tmA, full_bar(s), kb * kBK, x0 + kw, y0 + kh, img);
+              tma_load_4d(a_dst, &tmA, full_bar(s), kb * p.kblk, x0 + kw, y0 + kh, img);
               if (p.b_batched)
                 tma_load_4d(a_dst + Cfg::kABytes, &tmB, full_bar(s), kcol, n_tile * BN, thi * p.th, img);
               else
@@ -875,7 +896,8 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t a_addr = tile0 + s * Cfg::kStageBytes;
           const uint64_t adesc = desc_hi | ((a_addr & 0x3FFFF) >> 4);
           const uint64_t bdesc = desc_hi | (((a_addr + Cfg::kABytes) & 0x3FFFF) >> 4);
-          umma_f16_ksteps(d_tmem, adesc, bdesc, p.idesc, k != 0 ? 1u : 0u, ksteps);
+          if (p.fp8) umma_f8_ksteps(d_tmem, adesc, bdesc, p.idesc, k != 0 ? 1u : 0u, ksteps);
+          else umma_f16_ksteps(d_tmem, adesc, bdesc, p.idesc, k != 0 ? 1u : 0u, ksteps);
           umma_commit(empty_bar(s));
           if (++s == S) { s = 0; ph ^= 1; }
         }
@@ -1227,8 +1249,15 @@ static int choose_block_n(int Cout, long m_tiles, int sms) {
 using namespace fdb;
 
 FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
-  if (d->dtype != kF16 && d->dtype != kBF16) { set_error("conv_gemm: dtype must be fp16/bf16"); return nullptr; }
+  const bool fp8 = d->dtype == kF8E4M3;
+  if (d->dtype != kF16 && d->dtype != kBF16 && !fp8) { set_error("conv_gemm: dtype must be fp16, bf16 or fp8 e4m3"); return nullptr; }
+  if (fp8 && (d->residual != nullptr || d->w_batched || d->peer_mode != 0 || d->halo_mode == 1)) {
+    set_error("conv_gemm: fp8 operands take the plain kernel without residual, batched weights or peer modes"); return nullptr;
+  }
+  const int es = fp8 ? 1 : 2;                 // operand element size
+  const int kblk = fp8 ? 2 * kBK : kBK;       // K elements per 128-byte stage row
   if (d->Cin % 8 != 0 || d->x_ld % 8 != 0) { set_error("conv_gemm: Cin and x_ld must be multiples of 8"); return nullptr; }
+  if (fp8 && (d->Cin % 16 != 0 || d->x_ld % 16 != 0)) { set_error("conv_gemm: fp8 rows must be multiples of 16 elements"); return nullptr; }
   if ((reinterpret_cast<uintptr_t>(d->x) & 15) || (reinterpret_cast<uintptr_t>(d->w) & 15)) {
     set_error("conv_gemm: x and w must be 16-byte aligned"); return nullptr;
   }
@@ -1253,7 +1282,7 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   // 3x3 / stride 1 / pad 1: prefer the halo kernel unless its fixed 8x16 tile wastes too many rows
   const bool halo_ok = !d->w_batched && d->KH == 3 && d->KW == 3 && d->stride == 1 && d->pad_h == 1 && d->pad_w == 1;
   if (d->halo_mode == 1 && !halo_ok) { set_error("conv_gemm: halo kernel needs 3x3, stride 1, pad 1"); delete op; return nullptr; }
-  if (halo_ok && d->halo_mode != 0) {
+  if (halo_ok && d->halo_mode != 0 && !fp8) {
     const double util_gen = static_cast<double>(d->Ho) * d->Wo /
         (static_cast<double>((d->Wo + tw - 1) / tw) * ((d->Ho + th - 1) / th) * kBM);
     const double util_halo = static_cast<double>(d->Ho) * d->Wo /
@@ -1276,9 +1305,10 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   const long total = m_tiles * p.n_tiles;
   if (total > 0x7fffffffL) { set_error("conv_gemm: too many tiles"); delete op; return nullptr; }
   p.total_tiles = static_cast<int>(total);
-  p.kb_per_tap = (d->Cin + kBK - 1) / kBK;
+  p.kb_per_tap = (d->Cin + kblk - 1) / kblk;
   p.k_iters = d->KH * d->KW * p.kb_per_tap;
-  p.last_ksteps = (d->Cin - (p.kb_per_tap - 1) * kBK + 15) / 16;
+  p.last_ksteps = (d->Cin - (p.kb_per_tap - 1) * kblk + kblk / 4 - 1) / (kblk / 4);
+  p.kblk = kblk; p.fp8 = fp8 ? 1 : 0; p.scale_a = d->scale_a; p.scale_b = d->scale_b;
   p.bias = d->bias; p.residual = d->residual; p.y = d->y; p.status = d->status;
   p.Ho = d->Ho; p.Wo = d->Wo; p.Cout = d->Cout; p.y_ld = d->y_ld;
   p.res_ld = d->res_ld; p.res_mode = d->residual ? d->res_mode : 0;
@@ -1292,7 +1322,7 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   p.y_n_stride = d->y_n_stride > 0 ? d->y_n_stride : static_cast<long long>(d->Ho) * d->Wo * d->y_ld;
   p.res_n_stride = d->res_n_stride > 0 ? d->res_n_stride : static_cast<long long>(d->Ho) * d->Wo * d->res_ld;
   p.a_bytes = static_cast<uint32_t>(tw * th * kBK * 2);
-  p.idesc = make_idesc(d->dtype == kBF16 ? 1u : 0u, kBM, bn);
+  p.idesc = make_idesc(d->dtype == kBF16 ? 1u : 0u, kBM, bn);   // format 0 = F16 (kind::f16) or E4M3 (kind::f8f6f4)
   const int out_es = d->out_dtype == kF32 ? 4 : 2;
   p.y_vec = (reinterpret_cast<uintptr_t>(d->y) % 16 == 0) && ((d->y_ld * out_es) % 16 == 0) &&
             (d->bias == nullptr || reinterpret_cast<uintptr_t>(d->bias) % 16 == 0);
@@ -1337,14 +1367,14 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
     }
   }
 
-  const CUtensorMapDataType tdt =
-      d->dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUtensorMapDataType tdt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+      : d->dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   {
     cuuint64_t dims[4] = {(cuuint64_t)d->Cin, (cuuint64_t)d->W, (cuuint64_t)d->H, (cuuint64_t)d->N};
-    cuuint64_t strides[3] = {(cuuint64_t)d->x_ld * 2,
-                             (cuuint64_t)(d->x_h_stride > 0 ? d->x_h_stride : (long long)d->W * d->x_ld) * 2,
-                             (cuuint64_t)(d->x_n_stride > 0 ? d->x_n_stride : (long long)d->H * d->W * d->x_ld) * 2};
-    cuuint32_t box[4] = {(cuuint32_t)kBK, (cuuint32_t)(tw * d->stride), (cuuint32_t)(th * d->stride), 1};
+    cuuint64_t strides[3] = {(cuuint64_t)d->x_ld * es,
+                             (cuuint64_t)(d->x_h_stride > 0 ? d->x_h_stride : (long long)d->W * d->x_ld) * es,
+                             (cuuint64_t)(d->x_n_stride > 0 ? d->x_n_stride : (long long)d->H * d->W * d->x_ld) * es};
+    cuuint32_t box[4] = {(cuuint32_t)kblk, (cuuint32_t)(tw * d->stride), (cuuint32_t)(th * d->stride), 1};
     if (op->halo) { box[1] = kHaloCols; box[2] = kHaloRows; }
     cuuint32_t estr[4] = {1, (cuuint32_t)d->stride, (cuuint32_t)d->stride, 1};
     CUresult r = enc(&op->tmA, tdt, 4, const_cast<void*>(d->x), dims, strides, box, estr,
@@ -1368,10 +1398,10 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
       delete op; return nullptr;
     }
   } else {
-    const cuuint64_t ktot = (cuuint64_t)d->KH * d->KW * p.kb_per_tap * kBK;
+    const cuuint64_t ktot = (cuuint64_t)d->KH * d->KW * p.kb_per_tap * kblk;
     cuuint64_t dims[2] = {ktot, (cuuint64_t)d->Cout};
-    cuuint64_t strides[1] = {ktot * 2};
-    cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)bn};
+    cuuint64_t strides[1] = {ktot * es};
+    cuuint32_t box[2] = {(cuuint32_t)kblk, (cuuint32_t)bn};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(&op->tmB, tdt, 2, const_cast<void*>(d->w), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,

@@ -239,6 +239,34 @@ __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// One K block of e4m3 operands: up to four K = 32 steps (32 bytes each, so the descriptors advance
+// exactly like the 16-bit form), the first `nsteps` issued.
+__device__ __forceinline__ void umma_f8_ksteps(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate_first, uint32_t nsteps) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p0, p1, q1, q2, q3;\n"
+      ".reg .b64 a1, a2, a3, b1, b2, b3;\n"
+      "setp.ne.b32 p0, %4, 0;\n"
+      "setp.eq.u32 p1, %3, %3;\n"
+      "setp.gt.u32 q1, %5, 1;\n"
+      "setp.gt.u32 q2, %5, 2;\n"
+      "setp.gt.u32 q3, %5, 3;\n"
+      "add.s64 a1, %1, 2;\n"
+      "add.s64 b1, %2, 2;\n"
+      "add.s64 a2, %1, 4;\n"
+      "add.s64 b2, %2, 4;\n"
+      "add.s64 a3, %1, 6;\n"
+      "add.s64 b3, %2, 6;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p0;\n"
+      "@q1 tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a1, b1, %3, p1;\n"
+      "@q2 tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a2, b2, %3, p1;\n"
+      "@q3 tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a3, b3, %3, p1;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate_first), "r"(nsteps)
+      : "memory");
+}
+
 // Arrive on an mbarrier once every tcgen05.mma issued so far by this thread retired.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(

@@ -42,6 +42,7 @@ class _ConvGemmDesc(ctypes.Structure):
         ("peer_world", ctypes.c_int),
         ("peer_ptrs", ctypes.c_void_p * 8), ("peer_counters", ctypes.c_void_p * 8),
         ("peer_ready", ctypes.c_void_p), ("peer_copiers", ctypes.c_int),
+        ("scale_a", ctypes.c_void_p), ("scale_b", ctypes.c_void_p),
     ]
 
 
@@ -90,7 +91,8 @@ class ConvGemm(NativeOp):
                  y_tma_mode: int = -1, trace: Optional[torch.Tensor] = None, name: str = "conv_gemm",
                  peer_mode: int = 0, peer_rows: int = 0, peer_rank: int = 0, peer_world: int = 0,
                  peer_ptrs: Optional[Sequence[int]] = None, peer_counters: Optional[Sequence[int]] = None,
-                 peer_ready: Optional[torch.Tensor] = None, peer_copiers: int = 0):
+                 peer_ready: Optional[torch.Tensor] = None, peer_copiers: int = 0,
+                 scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None):
         n, h, w_, cin = in_shape
         d = _ConvGemmDesc()
         self.status = status or StatusWord(x.device)
@@ -123,6 +125,9 @@ class ConvGemm(NativeOp):
         d.peer_ready = peer_ready.data_ptr() if peer_ready is not None else None
         d.peer_copiers = peer_copiers
         self.peer_ready = peer_ready
+        d.scale_a = scale_a.data_ptr() if scale_a is not None else None
+        d.scale_b = scale_b.data_ptr() if scale_b is not None else None
+        self.scales = (scale_a, scale_b)
         if bias is not None:
             assert bias.dtype == torch.float32
         if residual is not None:
@@ -170,3 +175,47 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     op.launch()
     op.status.check("linear")
     return y
+
+
+# ------------------------------------------------------------------ fp8 (e4m3) operands
+FP8_MAX = 448.0
+K_BLOCK_FP8 = 128
+
+
+def quantize_rows_e4m3(x: torch.Tensor):
+    """Per-row symmetric quantisation to e4m3: returns ``(q [rows, K] float8_e4m3fn, scale [rows] fp32)`` with
+    ``x ~= q * scale[:, None]``; the scale maps the row's absolute maximum onto 448."""
+    xf = x.float()
+    amax = xf.abs().amax(dim=1).clamp_min(1e-12)
+    scale = amax / FP8_MAX
+    q = (xf / scale[:, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q, scale.contiguous()
+
+
+def pack_linear_weight_fp8(w: torch.Tensor):
+    """``[N, K]`` weight -> (e4m3 ``[N, K padded to 128]``, per-output-channel scale ``[N]``)."""
+    q, scale = quantize_rows_e4m3(w)
+    n, k = q.shape
+    kp = (k + K_BLOCK_FP8 - 1) // K_BLOCK_FP8 * K_BLOCK_FP8
+    out = torch.zeros(n, kp, dtype=torch.float8_e4m3fn, device=w.device)
+    out[:, :k] = q
+    return out, scale
+
+
+def linear_fp8(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: Optional[str] = None,
+               out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``act(x @ w.T + bias)`` with both operands quantised to e4m3 on the fly (per token / per output channel
+    scales) and multiplied by tcgen05 ``kind::f8f6f4`` MMAs with fp32 accumulation. This is per-channel-scaled fp8;
+    the MX block-scaled form (one ue8m0 scale per 32 elements, scales in tensor memory) is not implemented."""
+    m, k = x.shape
+    n = w.shape[0]
+    assert k % 16 == 0 and w.shape[1] == k
+    xq, sa = quantize_rows_e4m3(x)
+    wq, sb = pack_linear_weight_fp8(w)
+    y = torch.empty(m, (n + 7) // 8 * 8, dtype=out_dtype, device=x.device)
+    b = bias.float().contiguous() if bias is not None else None
+    op = ConvGemm(xq, wq, y, in_shape=(1, 1, m, k), out_hw=(1, m), cout=n, bias=b, act=act, x_ld=k, y_ld=y.stride(0),
+                  scale_a=sa, scale_b=sb, name="linear_fp8")
+    op.launch()
+    op.status.check("linear_fp8")
+    return y[:, :n]

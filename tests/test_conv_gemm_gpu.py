@@ -228,3 +228,25 @@ def test_stem_conv_matches_fp32_reference(dtype, act, hw):
     tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
     err = (y.float() - ref).abs().max().item()
     assert err <= tol * max(1.0, ref.abs().max().item()), err
+
+
+@pytest.mark.parametrize("m,k,n", [(256, 256, 128), (1000, 1280, 320), (4096, 5120, 1280)])
+@pytest.mark.parametrize("act", [None, "gelu"])
+def test_fp8_linear_matches_quantised_reference(m, k, n, act):
+    """fp8 GEMM against an fp32 product of the same quantised operands (exact up to accumulation order), and
+    against the unquantised product within e4m3's precision."""
+    from fastdeploy_b200.ops.conv_gemm import linear_fp8, quantize_rows_e4m3
+    torch.manual_seed(0)
+    x = torch.randn(m, k, device="cuda") * 0.7
+    w = torch.randn(n, k, device="cuda") * 0.05
+    b = torch.randn(n, device="cuda")
+    y = linear_fp8(x, w, b, act=act).float()
+    xq, sa = quantize_rows_e4m3(x)
+    wq, sb = quantize_rows_e4m3(w)
+    ref_q = (xq.float() @ wq.float().T) * sa[:, None] * sb[None, :] + b
+    ref = x @ w.T + b
+    if act == "gelu":
+        ref_q, ref = torch.nn.functional.gelu(ref_q), torch.nn.functional.gelu(ref)
+    scale = ref.abs().max().item()
+    assert (y - ref_q).abs().max().item() <= 1.5e-2 * scale        # bf16 output rounding
+    assert (y - ref).abs().max().item() <= 8e-2 * scale            # e4m3 quantisation error
