@@ -120,7 +120,8 @@ __global__ void reduce_pull_kernel(PeerPtrs src, T* out, long long offset, long 
 template <typename T>
 __global__ void __launch_bounds__(256) slot_reduce_kernel(const T* slots, const unsigned* counters, unsigned target,
                                                           T* out, const float* bias, int rows, int cols, int ld,
-                                                          int out_ld, int world, int* status) {
+                                                          int out_ld, int world, int* status,
+                                                          const T* residual, int res_ld) {
   __shared__ int ok;
   const int blk = blockIdx.x;
   if (threadIdx.x == 0) ok = wait_ge(counters + blk, target, status) ? 1 : 0;
@@ -136,6 +137,12 @@ __global__ void __launch_bounds__(256) slot_reduce_kernel(const T* slots, const 
     float acc[kVec];
 #pragma unroll
     for (int j = 0; j < kVec; ++j) acc[j] = bias != nullptr ? bias[c + j] : 0.f;
+    if (residual != nullptr) {   // may alias out: each element is read and written by the same thread
+      const uint4 v = *reinterpret_cast<const uint4*>(residual + static_cast<size_t>(row0 + r) * res_ld + c);
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) acc[j] += to_f<T>(e[j]);
+    }
     for (int s = 0; s < world; ++s) {
       const uint4 v = *reinterpret_cast<const uint4*>(slots + (static_cast<size_t>(s) * rows + row0 + r) * ld + c);
       const T* e = reinterpret_cast<const T*>(&v);
@@ -224,18 +231,28 @@ FDB_API int fdb_comm_reduce(void* const* src_ptrs, void* out, long long offset, 
   return check_launch("reduce");
 }
 
-FDB_API int fdb_comm_slot_reduce(const void* slots, const unsigned* counters, unsigned target, void* out,
-                                 const float* bias, int rows, int cols, int ld, int out_ld, int world, int dtype,
-                                 int* status, void* stream) {
-  if (cols % 8 != 0 || ld % 8 != 0 || out_ld % 8 != 0) { set_error("comm: slot reduce needs 8-element multiples"); return -1; }
+// out = sum over slots + bias + residual (bias and residual optional; residual may be the same buffer as out).
+FDB_API int fdb_comm_slot_reduce_res(const void* slots, const unsigned* counters, unsigned target, void* out,
+                                     const float* bias, const void* residual, int res_ld, int rows, int cols, int ld,
+                                     int out_ld, int world, int dtype, int* status, void* stream) {
+  if (cols % 8 != 0 || ld % 8 != 0 || out_ld % 8 != 0 || (residual != nullptr && res_ld % 8 != 0)) { set_error("comm: slot reduce needs 8-element multiples"); return -1; }
   const dim3 grid((rows + 127) / 128, std::max(1, std::min(8, cols / 256)));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == kBF16)
     slot_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(slots), counters, target,
-                                                           static_cast<__nv_bfloat16*>(out), bias, rows, cols, ld, out_ld, world, status);
+                                                           static_cast<__nv_bfloat16*>(out), bias, rows, cols, ld, out_ld, world, status,
+                                                           static_cast<const __nv_bfloat16*>(residual), res_ld);
   else if (dtype == kF16)
     slot_reduce_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(slots), counters, target,
-                                                    static_cast<__half*>(out), bias, rows, cols, ld, out_ld, world, status);
+                                                    static_cast<__half*>(out), bias, rows, cols, ld, out_ld, world, status,
+                                                    static_cast<const __half*>(residual), res_ld);
   else { set_error("comm: slot reduce takes fp16 or bf16"); return -1; }
   return check_launch("slot_reduce");
+}
+
+FDB_API int fdb_comm_slot_reduce(const void* slots, const unsigned* counters, unsigned target, void* out,
+                                 const float* bias, int rows, int cols, int ld, int out_ld, int world, int dtype,
+                                 int* status, void* stream) {
+  return fdb_comm_slot_reduce_res(slots, counters, target, out, bias, nullptr, 0, rows, cols, ld, out_ld, world, dtype,
+                                  status, stream);
 }

@@ -1,0 +1,38 @@
+"""Tensor-parallel ViT against the fp32 PyTorch forward of the same weights: one rank on one GPU, and two
+ranks (child processes under torchrun) where two GPUs are present."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ARGS = ["-m", "fastdeploy_b200.parallel.bench_vit", "--size", "test", "--batch", "8", "--image", "28", "--classes", "16",
+        "--steps", "0", "--check"]
+
+
+def _result(p):
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    line = [l for l in p.stdout.splitlines() if l.startswith("TPVIT ")][-1]
+    return json.loads(line[len("TPVIT "):])
+
+
+def test_vit_one_rank_matches_fp32_reference():
+    p = subprocess.run([sys.executable] + ARGS, capture_output=True, text=True, timeout=600, cwd=ROOT)
+    r = _result(p)
+    assert r["max_abs_err"] < 0.03 * r["ref_max_prob"], r
+    assert r["top1_agree"] >= 0.75, r
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_vit_two_ranks_match_fp32_reference():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29543"] + ARGS
+    r = _result(subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT))
+    assert r["world"] == 2
+    assert r["max_abs_err"] < 0.03 * r["ref_max_prob"], r
+    assert r["top1_agree"] >= 0.75, r
