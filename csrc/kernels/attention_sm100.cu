@@ -1,0 +1,356 @@
+// Fused multi-head attention for short sequences (keys <= 512, head dim <= 128) on tcgen05 / TMEM.
+//
+// One CTA per (batch, head). K [Sk x D] and V^T [D x Sk] of that head are brought into shared memory
+// once by TMA and stay there; the CTA then walks the query tiles of 128 rows:
+//
+//   S = Q K^T            tcgen05.mma, fp32 accumulator in tensor memory (one row per TMEM lane)
+//   p = exp(scale * S + mask - rowmax)   each of the 128 threads owns one row: no shuffles, the whole
+//                        row of scores is in TMEM, so the softmax is exact in one go (no running rescale)
+//   O = P V              P is written as bf16 / fp16 into a 128B-swizzled K-major tile in shared memory,
+//                        at most 256 keys at a time, and multiplied by the resident V^T; O's accumulator
+//                        reuses the TMEM columns of S, which are dead by then
+//   out = O / rowsum     straight from TMEM to the [B, S, H * D] output
+//
+// The score matrix never exists in global memory. The reference gets attention from its vendor
+// back ends (fastdeploy/runtime/backends/tensorrt/trt_backend.cc:347); there is no source to mirror.
+//
+// Every wait is bounded and reports through the status word; on a timeout the CTA frees its TMEM
+// and returns.
+#include "fdb_common.h"
+#include "sm100_ptx.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <functional>
+
+namespace fdb {
+
+struct AttnDesc {
+  const void* q; const void* k; const void* vt; void* out; const float* mask; int* status;
+  int dtype;                 // kF16 or kBF16
+  int B, H, S, Sk, D;
+  int q_ld, k_ld, o_ld;      // row pitches in elements; rows of one batch item are S (Sk) consecutive rows
+  int skp;                   // row pitch of vt [B][H][D][skp]
+  long long m_b, m_s;        // mask element (b, s, k) at b * m_b + s * m_s + k; mask may be null
+  float scale;
+};
+
+struct AttnParams {
+  const float* mask; uint8_t* out; int* status;
+  int H, S, Sk, D, o_ld;
+  int sk_pad;                // keys rounded up: multiple of 16 (<= 256) or of 32 (> 256)
+  int d_chunks;              // ceil(D / 64)
+  int k_chunks;              // ceil(sk_pad / 64)
+  int k_box, k_loads;        // rows per K TMA box and boxes per D chunk
+  int q_tiles;
+  int tmem_cols;
+  long long m_b, m_s;
+  float scale;
+  uint32_t smem_k, smem_vt, smem_q, smem_p;   // byte offsets from the 1024-aligned base
+};
+
+constexpr int kAttnThreads = 128;
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if (BF16) { __nv_bfloat162 h = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&h); }
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_vt, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[4];      // 0 K/V landed, 1 Q landed, 2 S ready, 3 PV group done
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sK = base + p.smem_k, sVT = base + p.smem_vt, sQ = base + p.smem_q, sP = base + p.smem_p;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int b = blockIdx.x / p.H, h = blockIdx.x - b * p.H;
+  const uint32_t bar_kv = smem_u32(&bars[0]), bar_q = smem_u32(&bars[1]), bar_s = smem_u32(&bars[2]),
+                 bar_o = smem_u32(&bars[3]);
+
+  if (tid == 0) {
+    abort_word = 0;
+    mbar_init(bar_kv, 1); mbar_init(bar_q, 1); mbar_init(bar_s, 1); mbar_init(bar_o, 1);
+    fence_mbar_init();
+    prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_vt);
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_slot), static_cast<uint32_t>(p.tmem_cols));
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+
+  const uint32_t q_chunk_bytes = 128u * 128u;                         // 128 rows x 128 B
+  const uint32_t k_chunk_bytes = static_cast<uint32_t>(p.sk_pad) * 128u;
+  const uint32_t vt_chunk_bytes = static_cast<uint32_t>((p.D + 7) / 8 * 8) * 128u;
+  const int col0 = h * p.D;
+
+  if (tid == 0) {
+    // K: d_chunks x k_loads boxes of [k_box rows x 64 cols]; V^T: k_chunks boxes of [D rows x 64 cols]
+    const uint32_t bytes = static_cast<uint32_t>(p.d_chunks) * k_chunk_bytes +
+                           static_cast<uint32_t>(p.k_chunks) * static_cast<uint32_t>(p.D) * 128u;
+    mbar_arrive_expect_tx(bar_kv, bytes);
+    for (int c = 0; c < p.d_chunks; ++c)
+      for (int l = 0; l < p.k_loads; ++l)
+        tma_load_2d(sK + c * k_chunk_bytes + static_cast<uint32_t>(l * p.k_box) * 128u, &tm_k, bar_kv, col0 + c * 64,
+                    b * p.Sk + l * p.k_box);
+    for (int j = 0; j < p.k_chunks; ++j)
+      tma_load_2d(sVT + j * vt_chunk_bytes, &tm_vt, bar_kv, j * 64, (b * p.H + h) * p.D);
+    mbar_arrive_expect_tx(bar_q, static_cast<uint32_t>(p.d_chunks) * q_chunk_bytes);
+    for (int c = 0; c < p.d_chunks; ++c) tma_load_2d(sQ + c * q_chunk_bytes, &tm_q, bar_q, col0 + c * 64, b * p.S);
+  }
+
+  const uint32_t fmt = BF16 ? 1u : 0u;
+  const int n_first = p.sk_pad > 256 ? 256 : p.sk_pad;
+  const int n_second = p.sk_pad - n_first;
+  const int d_steps_last = ((p.D - (p.d_chunks - 1) * 64) + 15) / 16;
+  const float sl2 = p.scale * 1.4426950408889634f;
+  uint32_t o_phase = 0;
+  bool ok = mbar_wait(bar_kv, 0, abort_flag, kStatusTimeoutProducer);
+
+  for (int qt = 0; ok && qt < p.q_tiles; ++qt) {
+    ok = mbar_wait(bar_q, qt & 1, abort_flag, kStatusTimeoutProducer);
+    if (!ok) break;
+    // ---------------------------------------------------------------- S = Q K^T
+    if (tid == 0) {
+      tc_fence_after();
+      for (int part = 0; part < (n_second > 0 ? 2 : 1); ++part) {
+        const int n = part == 0 ? n_first : n_second;
+        const uint32_t idesc = make_idesc(fmt, 128, static_cast<uint32_t>(n));
+        for (int c = 0; c < p.d_chunks; ++c) {
+          const uint64_t ad = make_kmajor_desc(sQ + c * q_chunk_bytes, 128);
+          const uint64_t bd = make_kmajor_desc(sK + c * k_chunk_bytes + static_cast<uint32_t>(part * 256) * 128u, 128);
+          umma_f16_ksteps(tmem + static_cast<uint32_t>(part * 256), ad, bd, idesc, c != 0 ? 1u : 0u,
+                          c + 1 == p.d_chunks ? static_cast<uint32_t>(d_steps_last) : 4u);
+        }
+      }
+      umma_commit(bar_s);
+    }
+    ok = mbar_wait(bar_s, qt & 1, abort_flag, kStatusTimeoutMma);
+    if (!ok) break;
+    tc_fence_after();
+    const int row = qt * 128 + tid;
+    const float* mrow = p.mask != nullptr ? p.mask + b * p.m_b + static_cast<long long>(row < p.S ? row : 0) * p.m_s : nullptr;
+    // ---------------------------------------------------------------- pass 1: row maximum (in log2 units)
+    float mx = -INFINITY;
+    for (int c0 = 0; c0 < p.sk_pad; c0 += 32) {
+      uint32_t v[32];
+      tmem_ld_32x32(lane_base + static_cast<uint32_t>(c0), v);
+      tmem_ld_wait_dep(v);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int col = c0 + j;
+        if (col < p.Sk) {
+          float s = __uint_as_float(v[j]) * sl2;
+          if (mrow != nullptr) s = fmaf(__ldg(mrow + col), 1.4426950408889634f, s);
+          mx = fmaxf(mx, s);
+        }
+      }
+    }
+    if (mx == -INFINITY) mx = 0.f;
+    // ---------------------------------------------------------------- pass 2: P and O = P V, 4 key chunks at a time
+    float sum = 0.f;
+    const int groups = (p.k_chunks + 3) / 4;
+    const uint32_t prow = sP + static_cast<uint32_t>(tid) * 128u;
+    const uint32_t r7 = static_cast<uint32_t>(tid & 7);
+    for (int g = 0; ok && g < groups; ++g) {
+      const int ch0 = g * 4, ch1 = min(p.k_chunks, ch0 + 4);
+      for (int ch = ch0; ch < ch1; ++ch) {
+        for (int half = 0; half < 2; ++half) {
+          const int c0 = ch * 64 + half * 32;
+          uint32_t w[16];
+          if (c0 < p.sk_pad) {
+            uint32_t v[32];
+            tmem_ld_32x32(lane_base + static_cast<uint32_t>(c0), v);
+            tmem_ld_wait_dep(v);
+            float e[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = c0 + j;
+              float s = __uint_as_float(v[j]) * sl2;
+              if (mrow != nullptr && col < p.Sk) s = fmaf(__ldg(mrow + col), 1.4426950408889634f, s);
+              e[j] = col < p.Sk ? exp2f(s - mx) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              w[j] = pack2<BF16>(e[2 * j], e[2 * j + 1]);
+              // the sum is taken over the rounded values that the tensor cores will multiply
+              float2 r;
+              if (BF16) r = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+              else r = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+              sum += r.x + r.y;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) w[j] = 0u;
+          }
+          const uint32_t cbase = prow + static_cast<uint32_t>(ch - ch0) * q_chunk_bytes;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const uint32_t unit = static_cast<uint32_t>(half * 4 + u);
+            const uint32_t addr = cbase + ((unit ^ r7) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * u]), "r"(w[4 * u + 1]),
+                         "r"(w[4 * u + 2]), "r"(w[4 * u + 3]) : "memory");
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0) {
+        tc_fence_after();
+        const uint32_t idesc = make_idesc(fmt, 128, static_cast<uint32_t>((p.D + 15) / 16 * 16));
+        for (int ch = ch0; ch < ch1; ++ch) {
+          const int keys = min(64, p.sk_pad - ch * 64);
+          const uint64_t ad = make_kmajor_desc(sP + static_cast<uint32_t>(ch - ch0) * q_chunk_bytes, 128);
+          const uint64_t bd = make_kmajor_desc(sVT + static_cast<uint32_t>(ch) * vt_chunk_bytes, 128);
+          umma_f16_ksteps(tmem, ad, bd, idesc, ch != 0 ? 1u : 0u, static_cast<uint32_t>((keys + 15) / 16));
+        }
+        umma_commit(bar_o);
+        // Q is free since S was committed, and every thread is past its wait on this tile's Q barrier
+        // (they all met at the barrier above): fetch the next tile's Q behind the rest of this one.
+        if (g == 0 && qt + 1 < p.q_tiles) {
+          mbar_arrive_expect_tx(bar_q, static_cast<uint32_t>(p.d_chunks) * q_chunk_bytes);
+          for (int c = 0; c < p.d_chunks; ++c)
+            tma_load_2d(sQ + c * q_chunk_bytes, &tm_q, bar_q, col0 + c * 64, b * p.S + (qt + 1) * 128);
+        }
+      }
+      ok = mbar_wait(bar_o, o_phase, abort_flag, kStatusTimeoutMma);
+      o_phase ^= 1u;
+      tc_fence_after();
+    }
+    if (!ok) break;
+    // ---------------------------------------------------------------- out = O / sum
+    const float inv = sum > 0.f ? 1.f / sum : 0.f;
+    uint8_t* orow = p.out + ((static_cast<long long>(b) * p.S + row) * p.o_ld + col0) * 2;
+    for (int c0 = 0; c0 < p.D; c0 += 32) {
+      uint32_t v[32];
+      tmem_ld_32x32(lane_base + static_cast<uint32_t>(c0), v);
+      tmem_ld_wait_dep(v);
+      if (row < p.S) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (c0 + u * 8 < p.D) {
+            uint4 o;
+            o.x = pack2<BF16>(__uint_as_float(v[8 * u]) * inv, __uint_as_float(v[8 * u + 1]) * inv);
+            o.y = pack2<BF16>(__uint_as_float(v[8 * u + 2]) * inv, __uint_as_float(v[8 * u + 3]) * inv);
+            o.z = pack2<BF16>(__uint_as_float(v[8 * u + 4]) * inv, __uint_as_float(v[8 * u + 5]) * inv);
+            o.w = pack2<BF16>(__uint_as_float(v[8 * u + 6]) * inv, __uint_as_float(v[8 * u + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + (c0 + u * 8) * 2) = o;
+          }
+        }
+      }
+    }
+    // the next tile's S overwrites the TMEM columns that were just read
+    tc_fence_before();
+    __syncthreads();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && abort_word != 0 && p.status != nullptr) atomicCAS(p.status, 0, abort_word);
+  if (warp == 0) tmem_dealloc(tmem, static_cast<uint32_t>(p.tmem_cols));
+}
+
+}  // namespace fdb
+
+using namespace fdb;
+
+namespace {
+
+struct AttnOp : Op {
+  CUtensorMap tq, tk, tvt;
+  AttnParams prm;
+  int grid = 0, smem = 0;
+  bool bf16 = true;
+  int launch(cudaStream_t s) override {
+    if (bf16) attention_kernel<true><<<grid, kAttnThreads, smem, s>>>(tq, tk, tvt, prm);
+    else attention_kernel<false><<<grid, kAttnThreads, smem, s>>>(tq, tk, tvt, prm);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_error(std::string("attention: ") + cudaGetErrorString(e)); return -1; }
+    return 0;
+  }
+};
+
+bool encode_2d(CUtensorMap* m, CUtensorMapDataType dt, const void* base, unsigned long long inner,
+               unsigned long long rows, unsigned long long row_bytes, unsigned box_rows) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (enc == nullptr) return false;
+  cuuint64_t dims[2] = {inner, rows};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+FDB_API int fdb_attention_desc_size() { return static_cast<int>(sizeof(AttnDesc)); }
+
+// Plans one fused attention launch over fixed buffers. q [B*S rows, q_ld], k [B*Sk rows, k_ld] (head h in
+// columns h*D .. h*D+D-1), vt [B][H][D][skp] (V transposed per head, zero beyond Sk), out [B*S rows, o_ld].
+FDB_API void* fdb_attention_create(const AttnDesc* d) {
+  if (d->dtype != kF16 && d->dtype != kBF16) { set_error("attention: dtype must be fp16 or bf16"); return nullptr; }
+  if (d->D % 16 != 0 || d->D < 16 || d->D > 128 || d->Sk < 1 || d->Sk > 512 || d->S < 1 || d->B < 1 || d->H < 1) {
+    set_error("attention: needs head dim in 16..128 (multiple of 16) and 1..512 keys"); return nullptr;
+  }
+  auto al16 = [](const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; };
+  if (!al16(d->q) || !al16(d->k) || !al16(d->vt) || !al16(d->out) || d->q_ld % 8 || d->k_ld % 8 || d->o_ld % 8 ||
+      d->skp % 8 || d->skp < d->Sk) {
+    set_error("attention: pointers must be 16-byte aligned and row pitches multiples of 8 elements"); return nullptr;
+  }
+  auto* op = new AttnOp();
+  AttnParams& p = op->prm;
+  p.mask = d->mask; p.out = static_cast<uint8_t*>(d->out); p.status = d->status;
+  p.H = d->H; p.S = d->S; p.Sk = d->Sk; p.D = d->D; p.o_ld = d->o_ld;
+  p.sk_pad = d->Sk <= 256 ? (d->Sk + 15) / 16 * 16 : (d->Sk + 31) / 32 * 32;
+  p.d_chunks = (d->D + 63) / 64;
+  p.k_chunks = (p.sk_pad + 63) / 64;
+  p.k_loads = p.sk_pad > 256 ? 2 : 1;
+  p.k_box = p.sk_pad / p.k_loads;
+  p.q_tiles = (d->S + 127) / 128;
+  int cols = 32;
+  while (cols < std::max((p.sk_pad + 31) / 32 * 32, (d->D + 31) / 32 * 32)) cols *= 2;
+  p.tmem_cols = cols;
+  p.m_b = d->m_b; p.m_s = d->m_s; p.scale = d->scale;
+  const uint32_t k_bytes = static_cast<uint32_t>(p.d_chunks) * p.sk_pad * 128u;
+  const uint32_t vt_bytes = static_cast<uint32_t>(p.k_chunks) * d->D * 128u;
+  const uint32_t q_bytes = static_cast<uint32_t>(p.d_chunks) * 16384u;
+  const uint32_t p_bytes = static_cast<uint32_t>(std::min(p.k_chunks, 4)) * 16384u;
+  p.smem_k = 0; p.smem_vt = k_bytes; p.smem_q = k_bytes + vt_bytes; p.smem_p = k_bytes + vt_bytes + q_bytes;
+  op->smem = static_cast<int>(k_bytes + vt_bytes + q_bytes + p_bytes + 1024u);
+  if (op->smem > 227 * 1024) {
+    set_error("attention: K, V and the probability tile do not fit in shared memory (" + std::to_string(op->smem) + " bytes)");
+    delete op; return nullptr;
+  }
+  op->bf16 = d->dtype == kBF16;
+  op->grid = d->B * d->H;
+  const CUtensorMapDataType dt = op->bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const unsigned long long width = static_cast<unsigned long long>(d->H) * d->D;
+  if (!encode_2d(&op->tq, dt, d->q, width, static_cast<unsigned long long>(d->B) * d->S, d->q_ld * 2ull, 128) ||
+      !encode_2d(&op->tk, dt, d->k, width, static_cast<unsigned long long>(d->B) * d->Sk, d->k_ld * 2ull, p.k_box) ||
+      !encode_2d(&op->tvt, dt, d->vt, d->skp, static_cast<unsigned long long>(d->B) * d->H * d->D, d->skp * 2ull, d->D)) {
+    set_error("attention: tensor map encoding failed"); delete op; return nullptr;
+  }
+  const void* fn = op->bf16 ? reinterpret_cast<const void*>(&attention_kernel<true>)
+                            : reinterpret_cast<const void*>(&attention_kernel<false>);
+  if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, op->smem) != cudaSuccess) {
+    cudaGetLastError();
+    set_error("attention: cannot raise the dynamic shared memory limit"); delete op; return nullptr;
+  }
+  return op;
+}

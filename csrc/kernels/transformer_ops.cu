@@ -105,6 +105,66 @@ __global__ void layernorm_kernel(const uint8_t* __restrict__ x, uint8_t* __restr
   }
 }
 
+// ---- LayerNorm with the row held in registers (C <= 2048): every load of the row is in flight before the
+// first use, the row is read from memory once, and the statistics take two register passes.
+template <bool BF16>
+__global__ void __launch_bounds__(256) layernorm_reg_kernel(const uint8_t* __restrict__ x, uint8_t* __restrict__ y,
+                                                            const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                            long long rows, int C, int x_ld, int y_ld, float eps) {
+  const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const uint8_t* xr = x + row * x_ld * 2;
+  uint4 raw[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int c = lane * 8 + k * 256;
+    raw[k] = c < C ? __ldg(reinterpret_cast<const uint4*>(xr + c * 2)) : make_uint4(0, 0, 0, 0);
+  }
+  float v[8][8];
+  float s = 0.f, ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    unpack8<BF16>(raw[k], v[k]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += v[k][j];
+  }
+  const float mean = warp_sum(s) / C;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    if (lane * 8 + k * 256 < C) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { const float d = v[k][j] - mean; ss += d * d; }
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(ss) / C + eps);
+  uint8_t* yr = y + row * y_ld * 2;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int c = lane * 8 + k * 256;
+    if (c < C) {
+      float g[8], b[8];
+      if (gamma) {
+        const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + c)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + c + 4));
+        g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+      }
+      if (beta) {
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta + c)), b1 = __ldg(reinterpret_cast<const float4*>(beta + c + 4));
+        b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+      }
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float t = (v[k][j] - mean) * rstd;
+        if (gamma) t *= g[j];
+        if (beta) t += b[j];
+        f[j] = t;
+      }
+      *reinterpret_cast<uint4*>(yr + c * 2) = pack8<BF16>(f);
+    }
+  }
+}
+
 // ---- sum of up to 4 embedding lookups + LayerNorm: one warp per token ---------------------
 // p0..p3 ids (int64 [rows]) (null = position index row % i3), p4..p7 tables (16-bit [V][C]), p8 y;
 // gamma/beta fp32 are passed in a second descriptor call? No: p9 points at a fp32 block [gamma(C) | beta(C)].
@@ -239,7 +299,10 @@ FDB_API void* fdb_transformer_create(int kind, const TfDesc* dp) {
       if (C % 8 || x_ld % 8 || y_ld % 8) { set_error("layernorm: C/ld must be multiples of 8"); delete op; return nullptr; }
       op->fn = [=](cudaStream_t s) {
         const int grid = static_cast<int>((rows * 32 + 255) / 256);
-        if (bf) layernorm_kernel<true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps);
+        const bool regs = C <= 2048 && (reinterpret_cast<uintptr_t>(d.p[2]) % 16 == 0) && (reinterpret_cast<uintptr_t>(d.p[3]) % 16 == 0);
+        if (regs && bf) layernorm_reg_kernel<true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps);
+        else if (regs) layernorm_reg_kernel<false><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps);
+        else if (bf) layernorm_kernel<true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps);
         else layernorm_kernel<false><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps);
         FDB_TF_CHECK();
       };

@@ -78,22 +78,82 @@ def head_transpose(v: torch.Tensor, vt: torch.Tensor, *, b: int, s: int, h: int,
     return _make(K_HEAD_TRANSPOSE, [v, vt], [b, s, h, d, v_ld, sp], name="head_transpose")
 
 
+class _AttnDesc(ctypes.Structure):
+    _fields_ = [("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("vt", ctypes.c_void_p), ("out", ctypes.c_void_p),
+                ("mask", ctypes.c_void_p), ("status", ctypes.c_void_p), ("dtype", ctypes.c_int),
+                ("B", ctypes.c_int), ("H", ctypes.c_int), ("S", ctypes.c_int), ("Sk", ctypes.c_int), ("D", ctypes.c_int),
+                ("q_ld", ctypes.c_int), ("k_ld", ctypes.c_int), ("o_ld", ctypes.c_int), ("skp", ctypes.c_int),
+                ("m_b", ctypes.c_longlong), ("m_s", ctypes.c_longlong), ("scale", ctypes.c_float)]
+
+
+def fused_attention_fits(s: int, sk: int, d: int) -> bool:
+    """Whether the single-kernel attention can hold this head's K, V and probability tile on chip."""
+    if d % 16 or d < 16 or d > 128 or sk > 512 or sk < 1:
+        return False
+    sk_pad = (sk + 15) // 16 * 16 if sk <= 256 else (sk + 31) // 32 * 32
+    dch, kch = (d + 63) // 64, (sk_pad + 63) // 64
+    return dch * sk_pad * 128 + kch * d * 128 + dch * 16384 + min(kch, 4) * 16384 + 1024 <= 227 * 1024
+
+
+def fused_attention_op(q, k, vt, out, mask, *, b, heads, s, sk, d, skp, scale, m_b, m_s, status) -> NativeOp:
+    """One launch of csrc/kernels/attention_sm100.cu: scores and probabilities stay in tensor / shared memory."""
+    lib = _native.kernels()
+    if not getattr(lib, "_attn_ready", False):
+        lib.fdb_attention_create.restype = ctypes.c_void_p
+        lib.fdb_attention_create.argtypes = [ctypes.POINTER(_AttnDesc)]
+        if lib.fdb_attention_desc_size() != ctypes.sizeof(_AttnDesc):
+            raise RuntimeError("libfdb200_kernels.so is out of date: AttnDesc layout differs")
+        lib._attn_ready = True
+    dd = _AttnDesc()
+    dd.q, dd.k, dd.vt, dd.out = q.data_ptr(), k.data_ptr(), vt.data_ptr(), out.data_ptr()
+    dd.mask = mask.data_ptr() if mask is not None else None
+    dd.status = status.ptr
+    dd.dtype = dtype_code(q.dtype)
+    dd.B, dd.H, dd.S, dd.Sk, dd.D = b, heads, s, sk, d
+    dd.q_ld, dd.k_ld, dd.o_ld, dd.skp = q.stride(1), k.stride(1), out.stride(1), skp
+    dd.m_b, dd.m_s, dd.scale = m_b, m_s, scale
+    return NativeOp(lib.fdb_attention_create(ctypes.byref(dd)), [q, k, vt, out, mask, status], "attention")
+
+
 class Attention:
     """Planned multi-head attention over fixed buffers. ``q``/``k``/``v`` are ``[B, S, H*D]`` views
     (row strides may differ, e.g. slices of a fused QKV buffer); ``out`` is ``[B, S, H*D]``."""
 
     def __init__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, *, heads: int,
-                 scale: float, mask: Optional[torch.Tensor] = None, status: Optional[StatusWord] = None):
+                 scale: float, mask: Optional[torch.Tensor] = None, status: Optional[StatusWord] = None,
+                 fused: Optional[bool] = None):
         b, s, hd = q.shape
         sk = k.shape[1]
         d = hd // heads
         assert d % 8 == 0, "head dim must be a multiple of 8"
         dev, dt = q.device, q.dtype
         skp = (sk + 7) // 8 * 8
-        self.scores = torch.zeros(b, heads, s, skp, dtype=dt, device=dev)
         self.vt = torch.zeros(b, heads, d, skp, dtype=dt, device=dev)
         self.status = status or StatusWord(dev)
         q_ld, k_ld, v_ld, o_ld = q.stride(1), k.stride(1), v.stride(1), out.stride(1)
+        rows_consecutive = (q.stride(0) == s * q_ld and k.stride(0) == sk * k_ld and v.stride(0) == sk * v_ld
+                            and out.stride(0) == s * o_ld)
+        can_fuse = fused_attention_fits(s, sk, d) and rows_consecutive
+        if fused is None:
+            fused = can_fuse
+        if fused and not can_fuse:
+            raise ValueError("fused attention needs <= 512 keys, a head dim that is a multiple of 16 (<= 128) and "
+                             "batch items stored as consecutive rows")
+        self.fused = fused
+        if fused:
+            m_b = m_s = 0
+            if mask is not None:
+                assert mask.dtype == torch.float32
+                mm = mask.reshape(b, -1, sk) if mask.numel() != b * sk else mask.reshape(b, 1, sk)
+                m_b = mm.stride(0)
+                m_s = mm.stride(1) if mm.shape[1] > 1 else 0
+            tr = head_transpose(v, self.vt, b=b, s=sk, h=heads, d=d, v_ld=v_ld, sp=skp)
+            at = fused_attention_op(q, k, self.vt, out, mask, b=b, heads=heads, s=s, sk=sk, d=d, skp=skp, scale=scale,
+                                    m_b=m_b, m_s=m_s, status=self.status)
+            self.ops = [tr, at]
+            self.keep = [q, k, v, out, mask]
+            return
+        self.scores = torch.zeros(b, heads, s, skp, dtype=dt, device=dev)
         # scores: "image" = B x (H rows) x (S pixels) x D channels; weights = K of the same (b, h)
         qk = ConvGemm(q, k, self.scores, in_shape=(b, heads, s, d), out_hw=(heads, s), cout=sk, x_ld=q_ld,
                       x_n_stride=q.stride(0), x_h_stride=d, y_ld=skp, status=self.status, w_batched=True,

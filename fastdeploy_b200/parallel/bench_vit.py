@@ -153,8 +153,8 @@ def main(argv=None):
             lay = model.layers[0]
             parts = {"ln": lay["ln1"].launch, "qkv": lay["qkv"].launch, "fc1": lay["fc1"].launch,
                      "proj": lay["proj"].launch, "fc2": lay["fc2"].launch, "barrier": comm.barrier,
-                     "attn_qk": model.attn.ops[0].launch, "attn_softmax": model.attn.ops[1].launch,
-                     "attn_vt": model.attn.ops[2].launch, "attn_pv": model.attn.ops[3].launch}
+                     "reduce": lambda: (model.counters[0].fill_(1 << 30), model._reduce_into_residual(0, lay["proj"], lay["proj_b"]))}
+            parts.update({"attn_" + op.name: op.launch for op in model.attn.ops})
             out["breakdown_ms"] = {k: round(_timed(f, a.steps, a.warmup, 1), 4) for k, f in parts.items()}
             model.counters[0].zero_(); model.counters[1].zero_(); model.targets = [0, 0]
         if not a.no_baseline:

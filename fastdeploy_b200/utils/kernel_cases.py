@@ -2,6 +2,7 @@
 
     python -m fastdeploy_b200.utils.kernel_cases conv --n 16 --hw 160 --cin 48 --cout 48 --k 3
     python -m fastdeploy_b200.utils.kernel_cases gemm --m 8192 --k 4096 --n 4096
+    python -m fastdeploy_b200.utils.kernel_cases attention --b 64 --heads 16 --s 257 --d 80 --dtype bf16
 
 Each run launches the kernel ``--iters`` times after ``--warmup`` launches, times it with CUDA events
 and prints one JSON line (time, TFLOP/s, bytes moved, fraction of the measured peaks when
@@ -19,7 +20,7 @@ def main(argv=None) -> int:
     import torch
     from ..ops.conv_gemm import ConvGemm, pack_conv_weight, pack_linear_weight
     ap = argparse.ArgumentParser()
-    ap.add_argument("kind", choices=["conv", "gemm"])
+    ap.add_argument("kind", choices=["conv", "gemm", "attention"])
     ap.add_argument("--n", type=int, default=16)
     ap.add_argument("--hw", type=int, default=160)
     ap.add_argument("--cin", type=int, default=48)
@@ -34,6 +35,10 @@ def main(argv=None) -> int:
     ap.add_argument("--halo", type=int, default=-1)
     ap.add_argument("--block-n", type=int, default=0)
     ap.add_argument("--y-tma", type=int, default=-1)
+    ap.add_argument("--b", type=int, default=64)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--s", type=int, default=257)
+    ap.add_argument("--d", type=int, default=80)
     a = ap.parse_args(argv)
     dt = torch.float16 if a.dtype == "fp16" else torch.bfloat16
     dev = "cuda"
@@ -50,6 +55,19 @@ def main(argv=None) -> int:
                       halo_mode=a.halo, block_n=a.block_n, y_tma_mode=a.y_tma)
         flops = 2.0 * n * ho * ho * cout * cin * k * k
         nbytes = x.numel() * 2 + y.numel() * 2 + w.numel() * 2
+    elif a.kind == "attention":
+        from ..ops.transformer import Attention
+        b, h, s, d = a.b, a.heads, a.s, a.d
+        qkv = (torch.randn(b, s, 3 * h * d, device=dev) * 0.5).to(dt)
+        o = torch.zeros(b, s, h * d, device=dev, dtype=dt)
+        att = Attention(qkv[..., :h * d], qkv[..., h * d:2 * h * d], qkv[..., 2 * h * d:], o, heads=h, scale=d ** -0.5,
+                        fused=True)
+        att.ops[0].launch()          # V^T once; the timed launch is the fused kernel alone
+        op = att.ops[1]
+        op.status = att.status
+        op.info = lambda: {"kernel": "attention_sm100"}
+        flops = 4.0 * b * h * s * s * d
+        nbytes = (qkv.numel() + o.numel()) * 2
     else:
         m, kk, nn = a.m, a.k if a.k > 8 else 4096, a.n if a.n > 16 else 4096
         x = (torch.randn(m, kk, device=dev) * 0.5).to(dt)

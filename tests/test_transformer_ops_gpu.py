@@ -1,4 +1,4 @@
-"""LayerNorm, embedding + LayerNorm, masked softmax and composed attention vs PyTorch fp32."""
+"""LayerNorm, embedding + LayerNorm, masked softmax, composed and fused attention vs PyTorch fp32."""
 import math
 
 import pytest
@@ -43,7 +43,8 @@ def test_embed_layernorm():
 @pytest.mark.parametrize("cfg", [(2, 4, 128, 64, True), (3, 2, 50, 64, True), (2, 16, 257, 80, False),
                                  (1, 12, 512, 64, True)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-def test_attention(cfg, dtype):
+@pytest.mark.parametrize("fused", [True, False])
+def test_attention(cfg, dtype, fused):
     from fastdeploy_b200.ops.transformer import Attention
     b, h, s, d, use_mask = cfg
     torch.manual_seed(2)
@@ -56,7 +57,8 @@ def test_attention(cfg, dtype):
         for i in range(b):
             mask[i, ..., lens[i]:] = -1e4
     out = torch.zeros(b, s, h * d, device="cuda", dtype=dtype)
-    att = Attention(q, k, v, out, heads=h, scale=1 / math.sqrt(d), mask=mask)
+    att = Attention(q, k, v, out, heads=h, scale=1 / math.sqrt(d), mask=mask, fused=fused)
+    assert att.fused == fused
     att.launch()
     att.status.check()
 
