@@ -59,6 +59,12 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <bool BF16>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -143,66 +149,115 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     tc_fence_after();
     const int row = qt * 128 + tid;
     const float* mrow = p.mask != nullptr ? p.mask + b * p.m_b + static_cast<long long>(row < p.S ? row : 0) * p.m_s : nullptr;
-    // ---------------------------------------------------------------- pass 1: row maximum (in log2 units)
-    float mx = -INFINITY;
-    for (int c0 = 0; c0 < p.sk_pad; c0 += 32) {
-      uint32_t v[32];
-      tmem_ld_32x32(lane_base + static_cast<uint32_t>(c0), v);
-      tmem_ld_wait_dep(v);
+    // Warps whose 32 rows all lie beyond the last query take part in the barriers only.
+    const bool warp_active = qt * 128 + warp * 32 < p.S;
+    const bool masked = mrow != nullptr;
+    const int nblk = (p.sk_pad + 31) / 32;
+    constexpr float kLog2e = 1.4426950408889634f;
+    uint32_t va[32], vb[32];
+    // ---------------------------------------------------------------- pass 1: row maximum
+    // Without a mask the maximum is taken over the raw scores and scaled once (scale > 0); with a mask
+    // it is taken over scale * s + mask in log2 units. Four partial maxima keep the chain short, and the
+    // next 32 columns are already on their way out of tensor memory while these are compared.
+    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    auto max_block = [&](const uint32_t (&v)[32], int c0) {
+      if (!masked && c0 + 32 <= p.Sk) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int col = c0 + j;
-        if (col < p.Sk) {
-          float s = __uint_as_float(v[j]) * sl2;
-          if (mrow != nullptr) s = fmaf(__ldg(mrow + col), 1.4426950408889634f, s);
-          mx = fmaxf(mx, s);
+        for (int j = 0; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[j]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int col = c0 + j;
+          if (col < p.Sk) {
+            float sv = __uint_as_float(v[j]);
+            if (masked) sv = fmaf(sv, sl2, __ldg(mrow + col) * kLog2e);
+            m4[j & 3] = fmaxf(m4[j & 3], sv);
+          }
         }
       }
+    };
+    float mx = 0.f;
+    if (warp_active) {
+      tmem_ld_32x32(lane_base, va);
+      for (int blk = 0; blk < nblk; blk += 2) {
+        tmem_ld_wait_dep(va);
+        if (blk + 1 < nblk) tmem_ld_32x32(lane_base + static_cast<uint32_t>((blk + 1) * 32), vb);
+        max_block(va, blk * 32);
+        if (blk + 1 < nblk) {
+          tmem_ld_wait_dep(vb);
+          if (blk + 2 < nblk) tmem_ld_32x32(lane_base + static_cast<uint32_t>((blk + 2) * 32), va);
+          max_block(vb, (blk + 1) * 32);
+        }
+      }
+      mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      if (!masked) mx *= sl2;
+      if (mx == -INFINITY) mx = 0.f;
     }
-    if (mx == -INFINITY) mx = 0.f;
     // ---------------------------------------------------------------- pass 2: P and O = P V, 4 key chunks at a time
-    float sum = 0.f;
+    float s4[4] = {0.f, 0.f, 0.f, 0.f};
     const int groups = (p.k_chunks + 3) / 4;
     const uint32_t prow = sP + static_cast<uint32_t>(tid) * 128u;
     const uint32_t r7 = static_cast<uint32_t>(tid & 7);
+    const float neg_mx = -mx;
+    // 32 probabilities -> 16 packed words -> four 16-byte stores into the swizzled row of chunk `lc`
+    auto prob_block = [&](const uint32_t (&v)[32], int c0, int lc, int half) {
+      uint32_t w[16];
+      if (!masked && c0 + 32 <= p.Sk) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float e0 = ex2_approx(fmaf(__uint_as_float(v[2 * j]), sl2, neg_mx));
+          const float e1 = ex2_approx(fmaf(__uint_as_float(v[2 * j + 1]), sl2, neg_mx));
+          s4[j & 3] += e0 + e1;
+          w[j] = pack2<BF16>(e0, e1);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float e[2];
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            const int col = c0 + 2 * j + t;
+            float off = neg_mx;
+            if (masked && col < p.Sk) off = fmaf(__ldg(mrow + col), kLog2e, neg_mx);
+            e[t] = col < p.Sk ? ex2_approx(fmaf(__uint_as_float(v[2 * j + t]), sl2, off)) : 0.f;
+          }
+          s4[j & 3] += e[0] + e[1];
+          w[j] = pack2<BF16>(e[0], e[1]);
+        }
+      }
+      const uint32_t cbase = prow + static_cast<uint32_t>(lc) * q_chunk_bytes;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t addr = cbase + ((static_cast<uint32_t>(half * 4 + u) ^ r7) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * u]), "r"(w[4 * u + 1]),
+                     "r"(w[4 * u + 2]), "r"(w[4 * u + 3]) : "memory");
+      }
+    };
     for (int g = 0; ok && g < groups; ++g) {
       const int ch0 = g * 4, ch1 = min(p.k_chunks, ch0 + 4);
-      for (int ch = ch0; ch < ch1; ++ch) {
-        for (int half = 0; half < 2; ++half) {
-          const int c0 = ch * 64 + half * 32;
-          uint32_t w[16];
-          if (c0 < p.sk_pad) {
-            uint32_t v[32];
-            tmem_ld_32x32(lane_base + static_cast<uint32_t>(c0), v);
-            tmem_ld_wait_dep(v);
-            float e[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int col = c0 + j;
-              float s = __uint_as_float(v[j]) * sl2;
-              if (mrow != nullptr && col < p.Sk) s = fmaf(__ldg(mrow + col), 1.4426950408889634f, s);
-              e[j] = col < p.Sk ? exp2f(s - mx) : 0.f;
-            }
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              w[j] = pack2<BF16>(e[2 * j], e[2 * j + 1]);
-              // the sum is taken over the rounded values that the tensor cores will multiply
-              float2 r;
-              if (BF16) r = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
-              else r = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-              sum += r.x + r.y;
-            }
+      if (warp_active) {
+        const int b0 = ch0 * 2, b1 = ch1 * 2;           // 32-column blocks of this group; blocks >= nblk are padding
+        if (b0 < nblk) tmem_ld_32x32(lane_base + static_cast<uint32_t>(b0 * 32), va);
+        for (int blk = b0; blk < b1; blk += 2) {
+          if (blk < nblk) {
+            tmem_ld_wait_dep(va);
+            if (blk + 1 < nblk) tmem_ld_32x32(lane_base + static_cast<uint32_t>((blk + 1) * 32), vb);
+            prob_block(va, blk * 32, (blk >> 1) - ch0, 0);
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) w[j] = 0u;
+            for (int u = 0; u < 4; ++u)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(
+                  prow + static_cast<uint32_t>((blk >> 1) - ch0) * q_chunk_bytes + ((static_cast<uint32_t>(u) ^ r7) << 4)), "r"(0u) : "memory");
           }
-          const uint32_t cbase = prow + static_cast<uint32_t>(ch - ch0) * q_chunk_bytes;
+          if (blk + 1 < nblk) {
+            tmem_ld_wait_dep(vb);
+            if (blk + 2 < b1 && blk + 2 < nblk) tmem_ld_32x32(lane_base + static_cast<uint32_t>((blk + 2) * 32), va);
+            prob_block(vb, (blk + 1) * 32, (blk >> 1) - ch0, 1);
+          } else {
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const uint32_t unit = static_cast<uint32_t>(half * 4 + u);
-            const uint32_t addr = cbase + ((unit ^ r7) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * u]), "r"(w[4 * u + 1]),
-                         "r"(w[4 * u + 2]), "r"(w[4 * u + 3]) : "memory");
+            for (int u = 0; u < 4; ++u)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(
+                  prow + static_cast<uint32_t>((blk >> 1) - ch0) * q_chunk_bytes + ((static_cast<uint32_t>(4 + u) ^ r7) << 4)), "r"(0u) : "memory");
           }
         }
       }
@@ -233,9 +288,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
     if (!ok) break;
     // ---------------------------------------------------------------- out = O / sum
+    const float sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
     const float inv = sum > 0.f ? 1.f / sum : 0.f;
     uint8_t* orow = p.out + ((static_cast<long long>(b) * p.S + row) * p.o_ld + col0) * 2;
-    for (int c0 = 0; c0 < p.D; c0 += 32) {
+    for (int c0 = 0; warp_active && c0 < p.D; c0 += 32) {
       uint32_t v[32];
       tmem_ld_32x32(lane_base + static_cast<uint32_t>(c0), v);
       tmem_ld_wait_dep(v);
@@ -305,6 +361,7 @@ FDB_API int fdb_attention_desc_size() { return static_cast<int>(sizeof(AttnDesc)
 // columns h*D .. h*D+D-1), vt [B][H][D][skp] (V transposed per head, zero beyond Sk), out [B*S rows, o_ld].
 FDB_API void* fdb_attention_create(const AttnDesc* d) {
   if (d->dtype != kF16 && d->dtype != kBF16) { set_error("attention: dtype must be fp16 or bf16"); return nullptr; }
+  if (!(d->scale > 0.f)) { set_error("attention: the score scale must be positive"); return nullptr; }
   if (d->D % 16 != 0 || d->D < 16 || d->D > 128 || d->Sk < 1 || d->Sk > 512 || d->S < 1 || d->B < 1 || d->H < 1) {
     set_error("attention: needs head dim in 16..128 (multiple of 16) and 1..512 keys"); return nullptr;
   }

@@ -61,7 +61,17 @@ class PaddleClasPostprocessor:
         self.topk = topk
 
     def run(self, tensors: Sequence[np.ndarray]) -> List[ClassifyResult]:
-        scores = np.asarray(tensors[0], np.float32)
+        t = tensors[0]
+        if hasattr(t, "is_cuda") and t.is_cuda and 1 <= self.topk <= 16:
+            # logits are still on the device: reduce them there and copy back k numbers per image
+            from ...ops.postproc import row_topk
+            val, idx = row_topk(t.reshape(t.shape[0], -1).contiguous(), self.topk)
+            val, idx = val.cpu().numpy(), idx.cpu().numpy()
+            return [ClassifyResult(label_ids=[int(i) for i in idx[r]], scores=[float(v) for v in val[r]])
+                    for r in range(idx.shape[0])]
+        if hasattr(t, "detach"):
+            t = t.detach().float().cpu().numpy()
+        scores = np.asarray(t, np.float32)
         scores = scores.reshape(scores.shape[0], -1)
         out = []
         for row in scores:
@@ -85,7 +95,7 @@ class _ClsBase(FastDeployModel):
         name = self.runtime.graph.inputs[0].name
         outs = self.infer({name: x})
         first = self.runtime.graph.outputs[0].name
-        return self.postprocessor.run([self.runtime._to_numpy(outs[first])])
+        return self.postprocessor.run([outs[first]])
 
     def get_preprocessor(self): return self.preprocessor
     def get_postprocessor(self): return self.postprocessor

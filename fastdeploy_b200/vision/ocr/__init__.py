@@ -321,7 +321,13 @@ class RecognizerPostprocessor:
                 self.label_list += [l.rstrip("\n").rstrip("\r") for l in f]
         self.label_list.append(" ")
 
-    def run(self, probs: np.ndarray):
+    def run(self, probs):
+        if hasattr(probs, "is_cuda") and probs.is_cuda:
+            # per-step arg-max and CTC collapse on the device; only the kept ids and scores come back
+            from ...ops.postproc import ctc_greedy_decode_device, ctc_texts
+            return ctc_texts(*ctc_greedy_decode_device(probs.contiguous()), self.label_list)
+        if hasattr(probs, "detach"):
+            probs = probs.detach().float().cpu().numpy()
         return ctc_greedy_decode(probs, self.label_list)
 
 
@@ -337,7 +343,9 @@ class Recognizer(_OcrStage):
         return t[0], s[0]
 
     def batch_predict(self, images):
-        return self.postprocessor.run(self._run_net(self.preprocessor.run(images)))
+        x = self.preprocessor.run(images)
+        outs = self.infer({self.runtime.graph.inputs[0].name: x})
+        return self.postprocessor.run(outs[self.runtime.graph.outputs[0].name])
 
 
 # ---------------------------------------------------------------------------------- pipelines
