@@ -4,8 +4,9 @@
 // once by TMA and stay there; the CTA then walks the query tiles of 128 rows:
 //
 //   S = Q K^T            tcgen05.mma, fp32 accumulator in tensor memory (one row per TMEM lane)
-//   p = exp(scale * S + mask - rowmax)   each of the 128 threads owns one row: no shuffles, the whole
-//                        row of scores is in TMEM, so the softmax is exact in one go (no running rescale)
+//   p = exp(scale * S + mask - rowmax)   two threads own each row (they split its 32-column blocks and
+//                        exchange one maximum and one sum through shared memory); the whole row of
+//                        scores is in TMEM, so the softmax is exact in one go (no running rescale)
 //   O = P V              P is written as bf16 / fp16 into a 128B-swizzled K-major tile in shared memory,
 //                        at most 256 keys at a time, and multiplied by the resident V^T; O's accumulator
 //                        reuses the TMEM columns of S, which are dead by then
@@ -50,7 +51,7 @@ struct AttnParams {
   uint32_t smem_k, smem_vt, smem_q, smem_p;   // byte offsets from the 1024-aligned base
 };
 
-constexpr int kAttnThreads = 128;
+constexpr int kAttnThreads = 256;   // two warps per TMEM lane quarter: they split the score columns
 
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
@@ -73,11 +74,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   __shared__ __align__(8) uint64_t bars[4];      // 0 K/V landed, 1 Q landed, 2 S ready, 3 PV group done
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_word;
+  __shared__ float red_max[2][128], red_sum[2][128];
   volatile int* abort_flag = &abort_word;
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sK = base + p.smem_k, sVT = base + p.smem_vt, sQ = base + p.smem_q, sP = base + p.smem_p;
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int r = tid & 127;          // row of the query tile this thread owns (lane of tensor memory)
+  const int half = warp >> 2;       // which half of the 32-column blocks (and of the output columns) it handles
   const int b = blockIdx.x / p.H, h = blockIdx.x - b * p.H;
   const uint32_t bar_kv = smem_u32(&bars[0]), bar_q = smem_u32(&bars[1]), bar_s = smem_u32(&bars[2]),
                  bar_o = smem_u32(&bars[3]);
@@ -96,7 +100,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+  const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
 
   const uint32_t q_chunk_bytes = 128u * 128u;                         // 128 rows x 128 B
   const uint32_t k_chunk_bytes = static_cast<uint32_t>(p.sk_pad) * 128u;
@@ -147,10 +151,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     ok = mbar_wait(bar_s, qt & 1, abort_flag, kStatusTimeoutMma);
     if (!ok) break;
     tc_fence_after();
-    const int row = qt * 128 + tid;
+    const int row = qt * 128 + r;
     const float* mrow = p.mask != nullptr ? p.mask + b * p.m_b + static_cast<long long>(row < p.S ? row : 0) * p.m_s : nullptr;
     // Warps whose 32 rows all lie beyond the last query take part in the barriers only.
-    const bool warp_active = qt * 128 + warp * 32 < p.S;
+    const bool warp_active = qt * 128 + (warp & 3) * 32 < p.S;
     const bool masked = mrow != nullptr;
     const int nblk = (p.sk_pad + 31) / 32;
     constexpr float kLog2e = 1.4426950408889634f;
@@ -178,26 +182,32 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     };
     float mx = 0.f;
     if (warp_active) {
-      tmem_ld_32x32(lane_base, va);
-      for (int blk = 0; blk < nblk; blk += 2) {
+      int blk = half;
+      if (blk < nblk) tmem_ld_32x32(lane_base + static_cast<uint32_t>(blk * 32), va);
+      for (; blk < nblk; blk += 4) {
         tmem_ld_wait_dep(va);
-        if (blk + 1 < nblk) tmem_ld_32x32(lane_base + static_cast<uint32_t>((blk + 1) * 32), vb);
+        if (blk + 2 < nblk) tmem_ld_32x32(lane_base + static_cast<uint32_t>((blk + 2) * 32), vb);
         max_block(va, blk * 32);
-        if (blk + 1 < nblk) {
+        if (blk + 2 < nblk) {
           tmem_ld_wait_dep(vb);
-          if (blk + 2 < nblk) tmem_ld_32x32(lane_base + static_cast<uint32_t>((blk + 2) * 32), va);
-          max_block(vb, (blk + 1) * 32);
+          if (blk + 4 < nblk) tmem_ld_32x32(lane_base + static_cast<uint32_t>((blk + 4) * 32), va);
+          max_block(vb, (blk + 2) * 32);
         }
       }
-      mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-      if (!masked) mx *= sl2;
+      float part = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      if (!masked) part *= sl2;
+      red_max[half][r] = part;
+    }
+    __syncthreads();                 // the two warps of a row exchange their partial maxima
+    if (warp_active) {
+      mx = fmaxf(red_max[0][r], red_max[1][r]);
       if (mx == -INFINITY) mx = 0.f;
     }
     // ---------------------------------------------------------------- pass 2: P and O = P V, 4 key chunks at a time
     float s4[4] = {0.f, 0.f, 0.f, 0.f};
     const int groups = (p.k_chunks + 3) / 4;
-    const uint32_t prow = sP + static_cast<uint32_t>(tid) * 128u;
-    const uint32_t r7 = static_cast<uint32_t>(tid & 7);
+    const uint32_t prow = sP + static_cast<uint32_t>(r) * 128u;
+    const uint32_t r7 = static_cast<uint32_t>(r & 7);
     const float neg_mx = -mx;
     // 32 probabilities -> 16 packed words -> four 16-byte stores into the swizzled row of chunk `lc`
     auto prob_block = [&](const uint32_t (&v)[32], int c0, int lc, int half) {
@@ -236,30 +246,36 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     for (int g = 0; ok && g < groups; ++g) {
       const int ch0 = g * 4, ch1 = min(p.k_chunks, ch0 + 4);
       if (warp_active) {
-        const int b0 = ch0 * 2, b1 = ch1 * 2;           // 32-column blocks of this group; blocks >= nblk are padding
-        if (b0 < nblk) tmem_ld_32x32(lane_base + static_cast<uint32_t>(b0 * 32), va);
-        for (int blk = b0; blk < b1; blk += 2) {
+        // 32-column blocks b0 .. b1-1 of this group; this warp takes every other one (blk & 1 == half), so
+        // it always writes the same half of a 64-key chunk; blocks >= nblk are padding and written as zero
+        const int b0 = ch0 * 2, b1 = ch1 * 2;
+        auto zero_block = [&](int lc) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(
+                prow + static_cast<uint32_t>(lc) * q_chunk_bytes + ((static_cast<uint32_t>(half * 4 + u) ^ r7) << 4)), "r"(0u) : "memory");
+        };
+        int blk = b0 + half;
+        if (blk < nblk) tmem_ld_32x32(lane_base + static_cast<uint32_t>(blk * 32), va);
+        for (; blk < b1; blk += 4) {
           if (blk < nblk) {
             tmem_ld_wait_dep(va);
-            if (blk + 1 < nblk) tmem_ld_32x32(lane_base + static_cast<uint32_t>((blk + 1) * 32), vb);
-            prob_block(va, blk * 32, (blk >> 1) - ch0, 0);
+            if (blk + 2 < b1 && blk + 2 < nblk) tmem_ld_32x32(lane_base + static_cast<uint32_t>((blk + 2) * 32), vb);
+            prob_block(va, blk * 32, (blk >> 1) - ch0, half);
           } else {
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(
-                  prow + static_cast<uint32_t>((blk >> 1) - ch0) * q_chunk_bytes + ((static_cast<uint32_t>(u) ^ r7) << 4)), "r"(0u) : "memory");
+            zero_block((blk >> 1) - ch0);
           }
-          if (blk + 1 < nblk) {
-            tmem_ld_wait_dep(vb);
-            if (blk + 2 < b1 && blk + 2 < nblk) tmem_ld_32x32(lane_base + static_cast<uint32_t>((blk + 2) * 32), va);
-            prob_block(vb, (blk + 1) * 32, (blk >> 1) - ch0, 1);
-          } else {
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(
-                  prow + static_cast<uint32_t>((blk >> 1) - ch0) * q_chunk_bytes + ((static_cast<uint32_t>(4 + u) ^ r7) << 4)), "r"(0u) : "memory");
+          if (blk + 2 < b1) {
+            if (blk + 2 < nblk) {
+              tmem_ld_wait_dep(vb);
+              if (blk + 4 < b1 && blk + 4 < nblk) tmem_ld_32x32(lane_base + static_cast<uint32_t>((blk + 4) * 32), va);
+              prob_block(vb, (blk + 2) * 32, ((blk + 2) >> 1) - ch0, half);
+            } else {
+              zero_block(((blk + 2) >> 1) - ch0);
+            }
           }
         }
+        if (g + 1 == groups) red_sum[half][r] = (s4[0] + s4[1]) + (s4[2] + s4[3]);
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -288,10 +304,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
     if (!ok) break;
     // ---------------------------------------------------------------- out = O / sum
-    const float sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+    const float sum = warp_active ? red_sum[0][r] + red_sum[1][r] : 0.f;
     const float inv = sum > 0.f ? 1.f / sum : 0.f;
     uint8_t* orow = p.out + ((static_cast<long long>(b) * p.S + row) * p.o_ld + col0) * 2;
-    for (int c0 = 0; warp_active && c0 < p.D; c0 += 32) {
+    for (int c0 = half * 32; warp_active && c0 < p.D; c0 += 64) {
       uint32_t v[32];
       tmem_ld_32x32(lane_base + static_cast<uint32_t>(c0), v);
       tmem_ld_wait_dep(v);
@@ -390,7 +406,7 @@ FDB_API void* fdb_attention_create(const AttnDesc* d) {
   const uint32_t p_bytes = static_cast<uint32_t>(std::min(p.k_chunks, 4)) * 16384u;
   p.smem_k = 0; p.smem_vt = k_bytes; p.smem_q = k_bytes + vt_bytes; p.smem_p = k_bytes + vt_bytes + q_bytes;
   op->smem = static_cast<int>(k_bytes + vt_bytes + q_bytes + p_bytes + 1024u);
-  if (op->smem > 227 * 1024) {
+  if (op->smem + 4096 > 227 * 1024) {      // 4 KB: the kernel's static shared memory (barriers, row exchange)
     set_error("attention: K, V and the probability tile do not fit in shared memory (" + std::to_string(op->smem) + " bytes)");
     delete op; return nullptr;
   }

@@ -273,6 +273,37 @@ __global__ void head_transpose_kernel(const uint16_t* __restrict__ v, uint16_t* 
   }
 }
 
+// Same transpose with 16-byte accesses on both sides: one CTA per (b, h, 64 keys). Needs D, v_ld and Sp to be
+// multiples of 8 and 16-byte aligned bases.
+__global__ void __launch_bounds__(256) head_transpose_vec_kernel(const uint16_t* __restrict__ v, uint16_t* __restrict__ vt,
+                                                                 int B, int S, int H, int D, int v_ld, int Sp) {
+  extern __shared__ uint16_t tp_tile[];          // [64][D + 2]
+  const int pitch = D + 2;
+  const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
+  const int s0 = blockIdx.x * 64;
+  const int dv = D / 8;
+  for (int i = threadIdx.x; i < 64 * dv; i += blockDim.x) {
+    const int r = i / dv, c = (i - r * dv) * 8;
+    const int sidx = s0 + r;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (sidx < S) val = __ldg(reinterpret_cast<const uint4*>(v + (static_cast<size_t>(b) * S + sidx) * v_ld + h * D + c));
+    uint32_t* dst = reinterpret_cast<uint32_t*>(tp_tile + r * pitch + c);     // pitch and c are even: 4-byte aligned
+    dst[0] = val.x; dst[1] = val.y; dst[2] = val.z; dst[3] = val.w;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < D * 8; i += blockDim.x) {
+    const int sv = (i & 7) * 8, d = i >> 3;     // eight consecutive threads write one 128-byte row segment
+    if (s0 + sv >= Sp) continue;
+    uint16_t e[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) e[j] = tp_tile[(sv + j) * pitch + d];
+    uint4 o;
+    o.x = e[0] | (static_cast<uint32_t>(e[1]) << 16); o.y = e[2] | (static_cast<uint32_t>(e[3]) << 16);
+    o.z = e[4] | (static_cast<uint32_t>(e[5]) << 16); o.w = e[6] | (static_cast<uint32_t>(e[7]) << 16);
+    *reinterpret_cast<uint4*>(vt + ((static_cast<size_t>(b) * H + h) * D + d) * Sp + s0 + sv) = o;
+  }
+}
+
 #define FDB_TF_CHECK()                              \
   do {                                              \
     cudaError_t _e = cudaGetLastError();            \
@@ -341,6 +372,13 @@ FDB_API void* fdb_transformer_create(int kind, const TfDesc* dp) {
     case kHeadTranspose: {
       const int B = d.i[0], S = d.i[1], H = d.i[2], D = d.i[3], v_ld = d.i[4], Sp = d.i[5];
       op->fn = [=](cudaStream_t s) {
+        const bool vec = D % 8 == 0 && v_ld % 8 == 0 && Sp % 8 == 0 && B * H <= 65535 &&
+                         reinterpret_cast<uintptr_t>(d.p[0]) % 16 == 0 && reinterpret_cast<uintptr_t>(d.p[1]) % 16 == 0;
+        if (vec) {
+          head_transpose_vec_kernel<<<dim3((Sp + 63) / 64, B * H), 256, 64 * (D + 2) * 2, s>>>(
+              (const uint16_t*)d.p[0], (uint16_t*)d.p[1], B, S, H, D, v_ld, Sp);
+          FDB_TF_CHECK();
+        }
         dim3 grid((Sp + 31) / 32, (D + 31) / 32, B * H), block(32, 8);
         head_transpose_kernel<<<grid, block, 0, s>>>((const uint16_t*)d.p[0], (uint16_t*)d.p[1], B, S, H, D, v_ld, Sp);
         FDB_TF_CHECK();

@@ -92,7 +92,7 @@ def fused_attention_fits(s: int, sk: int, d: int) -> bool:
         return False
     sk_pad = (sk + 15) // 16 * 16 if sk <= 256 else (sk + 31) // 32 * 32
     dch, kch = (d + 63) // 64, (sk_pad + 63) // 64
-    return dch * sk_pad * 128 + kch * d * 128 + dch * 16384 + min(kch, 4) * 16384 + 1024 <= 227 * 1024
+    return dch * sk_pad * 128 + kch * d * 128 + dch * 16384 + min(kch, 4) * 16384 + 1024 + 4096 <= 227 * 1024
 
 
 def fused_attention_op(q, k, vt, out, mask, *, b, heads, s, sk, d, skp, scale, m_b, m_s, status) -> NativeOp:
