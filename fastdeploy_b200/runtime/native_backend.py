@@ -28,6 +28,7 @@ from ..ir import interp, passes
 from ..ir.graph import Graph, Node
 from ..ir.shape_infer import ShapeInfo, infer_shapes
 from ..ops import nhwc as K
+from ..utils import log
 from ..ops import stem_conv
 from ..ops.base import NativeOp, StatusWord, current_stream_ptr
 from ..ops.conv_gemm import ConvGemm, pack_conv_weight, pack_linear_weight
@@ -792,12 +793,61 @@ class Lowering:
         self._emit_nms(node, boxes, scores[:, :, :c], class_major=False)
 
 
+def graph_fingerprint(graph: Graph, input_shapes: Dict[str, Sequence[int]], dtype, opt_level: int) -> str:
+    """Cache key of an optimised graph: structure, attributes, shapes, and for every weight its shape,
+    dtype and a sample of its bytes (hashing 600 MB of weights on every start would cost more than the passes)."""
+    import hashlib
+    h = hashlib.sha256()
+    h.update(repr((sorted((k, tuple(v)) for k, v in input_shapes.items()), str(dtype), opt_level)).encode())
+    for n in graph.nodes:
+        h.update(repr((n.op, n.inputs, n.outputs, sorted((k, repr(v)[:200]) for k, v in n.attrs.items()))).encode())
+    for name in sorted(graph.initializers):
+        a = np.ascontiguousarray(graph.initializers[name])
+        raw = a.view(np.uint8).reshape(-1)
+        h.update(repr((name, a.shape, str(a.dtype))).encode())
+        h.update(raw[:256].tobytes())
+        h.update(raw[-256:].tobytes())
+        if raw.size > 4096:
+            h.update(raw[::max(1, raw.size // 1024)].tobytes())
+    return h.hexdigest()[:32]
+
+
+def optimize_cached(graph: Graph, input_shapes, input_values, opt_level: int, dtype, cache_dir: str) -> Graph:
+    """``passes.optimize`` behind an on-disk cache (the counterpart of the reference's serialized TensorRT engine,
+    fastdeploy/runtime/backends/tensorrt/trt_backend.cc:240-300 ``serialize_file``): the optimised graph, fused
+    ops included, is stored in this package's ONNX writer format under ``cache_dir`` and reloaded on the next
+    start instead of re-running constant folding, BN / RepVGG folding and the pattern matchers."""
+    if not cache_dir or input_values:
+        return passes.optimize(graph, input_shapes, input_values, level=opt_level)
+    import os
+    from ..importer.onnx_format import load_onnx, save_onnx
+    path = os.path.join(cache_dir, graph_fingerprint(graph, input_shapes, dtype, opt_level) + ".fdbgraph")
+    if os.path.exists(path):
+        try:
+            with open(path, "rb") as f:
+                g = load_onnx(f.read())
+            log.info(f"optimised graph loaded from {path}")
+            return g
+        except Exception as e:      # a damaged cache entry is rebuilt, never fatal
+            log.warning(f"ignoring unreadable plan cache entry {path}: {e}")
+    g = passes.optimize(graph, input_shapes, input_values, level=opt_level)
+    try:
+        os.makedirs(cache_dir, exist_ok=True)
+        tmp = path + f".tmp{os.getpid()}"
+        with open(tmp, "wb") as f:
+            f.write(save_onnx(g))
+        os.replace(tmp, path)
+    except OSError as e:
+        log.warning(f"could not write plan cache entry {path}: {e}")
+    return g
+
+
 def build_plan(graph: Graph, input_shapes: Dict[str, Sequence[int]], device, dtype=torch.float16,
-               input_values: Optional[Dict[str, np.ndarray]] = None, opt_level: int = 2) -> Plan:
+               input_values: Optional[Dict[str, np.ndarray]] = None, opt_level: int = 2, cache_dir: str = "") -> Plan:
     """Optimises ``graph`` for the given shapes and lowers it to a plan on ``device``."""
     device = torch.device(device)
     with torch.cuda.device(device):
-        g = passes.optimize(graph, input_shapes, input_values, level=opt_level)
+        g = optimize_cached(graph, input_shapes, input_values, opt_level, dtype, cache_dir)
         low = Lowering(g, input_shapes, device, dtype, input_values)
         for node in g.nodes:
             if node.op == "PPYOLOEPost":

@@ -120,7 +120,8 @@ class Runtime:
             from .native_backend import build_plan
             t0 = time.time()
             plan = build_plan(self.graph, {k: list(v) for k, v in shapes.items()}, self.device, self.dtype,
-                              opt_level=self.option.native_option.opt_level)
+                              opt_level=self.option.native_option.opt_level,
+                              cache_dir=self.option.native_option.plan_cache_dir)
             if self.option.native_option.use_cuda_graph:
                 try:
                     plan.capture()

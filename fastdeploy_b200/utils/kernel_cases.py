@@ -73,7 +73,9 @@ def main(argv=None) -> int:
         x = (torch.randn(m, kk, device=dev) * 0.5).to(dt)
         w = (torch.randn(nn, kk, device=dev) * 0.05).to(dt)
         y = torch.empty(m, nn, device=dev, dtype=dt)
+        gemm_act = a.act if a.act not in ("none", "silu") or "--act" in (argv or sys.argv) else None
         op = ConvGemm(x, pack_linear_weight(w, dt), y, in_shape=(1, 1, m, kk), out_hw=(1, m), cout=nn,
+                      bias=torch.randn(nn, device=dev) if gemm_act else None, act=gemm_act if gemm_act != "none" else None,
                       block_n=a.block_n, y_tma_mode=a.y_tma)
         flops = 2.0 * m * kk * nn
         nbytes = (x.numel() + y.numel() + w.numel()) * 2

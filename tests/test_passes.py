@@ -116,3 +116,35 @@ def test_gelu_layernorm_attention_recognition():
     gem = [n for n in g2.nodes if n.op == "FusedGemm"]
     assert len(gem) == 5 and any(n.attr("activation") == "gelu" for n in gem) and any(n.attr("res_mode") == 2 for n in gem)
     assert np.abs(_run(g2, {"x": x, "mask": mask})["y"] - ref).max() < 1e-5
+
+
+def test_optimised_graph_disk_cache_round_trip(tmp_path):
+    """The on-disk plan cache stores the optimised graph (fused ops included) and a second start loads it
+    instead of running the passes; both graphs compute the same outputs."""
+    import os
+    import numpy as np
+    import torch
+    from fastdeploy_b200.importer.paddle_import import load_paddle
+    from fastdeploy_b200.ir import passes
+    from fastdeploy_b200.ir.interp import Interpreter
+    from fastdeploy_b200.models.ernie import build_ernie
+    from fastdeploy_b200.runtime import native_backend as nb
+    g = load_paddle(*build_ernie("tiny").serialize())
+    shapes = {"input_ids": [2, 16], "token_type_ids": [2, 16]}
+    g1 = nb.optimize_cached(g, shapes, None, 2, torch.float16, str(tmp_path))
+    files = os.listdir(tmp_path)
+    assert len(files) == 1 and files[0].endswith(".fdbgraph")
+    calls = []
+    orig = passes.optimize
+    passes.optimize = lambda *a, **k: calls.append(1) or orig(*a, **k)
+    try:
+        g2 = nb.optimize_cached(load_paddle(*build_ernie("tiny").serialize()), shapes, None, 2, torch.float16, str(tmp_path))
+    finally:
+        passes.optimize = orig
+    assert not calls, "second start must come from the cache"
+    assert nb.graph_fingerprint(g, shapes, torch.float16, 2) != nb.graph_fingerprint(g, shapes, torch.bfloat16, 2)
+    feeds = {"input_ids": np.random.default_rng(0).integers(1, 1000, (2, 16)).astype(np.int64),
+             "token_type_ids": np.zeros((2, 16), np.int64)}
+    a, b = Interpreter(g1).run(feeds), Interpreter(g2).run(feeds)
+    for k in a:
+        assert np.array_equal(np.asarray(a[k]), np.asarray(b[k]))
