@@ -372,6 +372,10 @@ __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParam
       }
     }
     if (ACT == kTplGeneric) apply_act8(x, p.act, p.act_alpha, p.act_beta);
+    if (ACT == kActGelu) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = gelu_erf_fast(x[j]);
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       uint32_t h = pack2(x[2 * j], x[2 * j + 1], out_bf16);
@@ -401,6 +405,10 @@ __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParam
     for (int j = 0; j < 8; ++j) x[j] += r[j];
   }
   if (ACT == kTplGeneric) apply_act8(x, p.act, p.act_alpha, p.act_beta);
+  if (ACT == kActGelu) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = gelu_erf_fast(x[j]);
+  }
   if (ACT == kActSilu) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) x[j] = silu_f32(x[j]);
@@ -439,6 +447,10 @@ __device__ __forceinline__ void staged_chunk(const uint32_t (&v)[32], const floa
     x[4] = __uint_as_float(v[g * 8 + 4]) + b1.x; x[5] = __uint_as_float(v[g * 8 + 5]) + b1.y;
     x[6] = __uint_as_float(v[g * 8 + 6]) + b1.z; x[7] = __uint_as_float(v[g * 8 + 7]) + b1.w;
     if (ACT == kTplGeneric) apply_act8(x, p.act, p.act_alpha, p.act_beta);
+    if (ACT == kActGelu) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = gelu_erf_fast(x[j]);
+    }
     uint32_t w[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -1193,6 +1205,7 @@ static int launch_bn(ConvGemmOp* op, cudaStream_t stream) {
     case kActNone: return launch_inst<BN, kActNone>(op, stream);
     case kActRelu: return launch_inst<BN, kActRelu>(op, stream);
     case kActSilu: return launch_inst<BN, kActSilu>(op, stream);
+    case kActGelu: return launch_inst<BN, kActGelu>(op, stream);
     default: return launch_inst<BN, kTplGeneric>(op, stream);
   }
 }
