@@ -157,6 +157,83 @@ __global__ void __launch_bounds__(256) slot_reduce_kernel(const T* slots, const 
   }
 }
 
+
+// Slot reduction fused with the residual addition and the LayerNorm that follows it in a pre-norm transformer
+// block: x = x + bias + sum of the world partial blocks (written back in place), y = LayerNorm(x) * gamma + beta.
+// One warp per row keeps the whole row (cols <= 2048) in registers, so x is read once and the normalised row
+// leaves in the same pass. Two CTAs share each 128-row block (64 rows each) and both wait for its counter.
+template <typename T>
+__global__ void __launch_bounds__(256) slot_reduce_ln_kernel(const T* slots, const unsigned* counters, unsigned target,
+                                                             T* x, const float* bias, int rows, int cols, int world,
+                                                             int* status, const float* gamma, const float* beta,
+                                                             float eps, T* y, int y_ld) {
+  __shared__ int ok;
+  const int blk = blockIdx.x >> 1;
+  if (threadIdx.x == 0) ok = wait_ge(counters + blk, target, status) ? 1 : 0;
+  __syncthreads();
+  if (!ok) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row_lo = blk * 128 + (blockIdx.x & 1) * 64;
+  const int row_hi = min(rows, row_lo + 64);
+  for (int row = row_lo + warp; row < row_hi; row += 8) {
+    float v[8][8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int c = lane * 8 + k * 256;
+      if (c < cols) {
+        const uint4 xv = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * cols + c);
+        const T* xe = reinterpret_cast<const T*>(&xv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[k][j] = to_f<T>(xe[j]) + (bias != nullptr ? bias[c + j] : 0.f);
+        for (int s = 0; s < world; ++s) {
+          const uint4 sv = *reinterpret_cast<const uint4*>(slots + (static_cast<size_t>(s) * rows + row) * cols + c);
+          const T* se = reinterpret_cast<const T*>(&sv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[k][j] += to_f<T>(se[j]);
+        }
+        uint4 o;
+        T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { oe[j] = from_f<T>(v[k][j]); v[k][j] = to_f<T>(oe[j]); }   // normalise what was stored
+        *reinterpret_cast<uint4*>(x + static_cast<size_t>(row) * cols + c) = o;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[k][j] = 0.f;
+      }
+    }
+    float s1 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s1 += v[k][j];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+    const float mean = s1 / cols;
+    float s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (lane * 8 + k * 256 < cols) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { const float d = v[k][j] - mean; s2 += d * d; }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    const float rstd = rsqrtf(s2 / cols + eps);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int c = lane * 8 + k * 256;
+      if (c < cols) {
+        uint4 o;
+        T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) oe[j] = from_f<T>((v[k][j] - mean) * rstd * gamma[c + j] + beta[c + j]);
+        *reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * y_ld + c) = o;
+      }
+    }
+  }
+}
+
 }  // namespace fdb
 
 using namespace fdb;
@@ -255,4 +332,23 @@ FDB_API int fdb_comm_slot_reduce(const void* slots, const unsigned* counters, un
                                  int* status, void* stream) {
   return fdb_comm_slot_reduce_res(slots, counters, target, out, bias, nullptr, 0, rows, cols, ld, out_ld, world, dtype,
                                   status, stream);
+}
+
+// x [rows, cols] += bias + sum of slots [world, rows, cols]; y [rows, y_ld] = LayerNorm(x) * gamma + beta.
+FDB_API int fdb_comm_slot_reduce_ln(const void* slots, const unsigned* counters, unsigned target, void* x,
+                                    const float* bias, int rows, int cols, int world, int dtype, int* status,
+                                    const float* gamma, const float* beta, float eps, void* y, int y_ld, void* stream) {
+  if (cols % 8 != 0 || cols > 2048 || y_ld % 8 != 0 || gamma == nullptr || beta == nullptr) {
+    set_error("comm: fused slot reduce + LayerNorm needs cols a multiple of 8 up to 2048, gamma and beta"); return -1;
+  }
+  const int grid = 2 * ((rows + 127) / 128);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == kBF16)
+    slot_reduce_ln_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(slots), counters, target,
+        static_cast<__nv_bfloat16*>(x), bias, rows, cols, world, status, gamma, beta, eps, static_cast<__nv_bfloat16*>(y), y_ld);
+  else if (dtype == kF16)
+    slot_reduce_ln_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(slots), counters, target,
+        static_cast<__half*>(x), bias, rows, cols, world, status, gamma, beta, eps, static_cast<__half*>(y), y_ld);
+  else { set_error("comm: slot reduce takes fp16 or bf16"); return -1; }
+  return check_launch("slot_reduce_ln");
 }

@@ -153,7 +153,7 @@ def main(argv=None):
             lay = model.layers[0]
             parts = {"ln": lay["ln1"].launch, "qkv": lay["qkv"].launch, "fc1": lay["fc1"].launch,
                      "proj": lay["proj"].launch, "fc2": lay["fc2"].launch, "barrier": comm.barrier,
-                     "reduce": lambda: (model.counters[0].fill_(1 << 30), model._reduce_into_residual(0, lay["proj"], lay["proj_b"]))}
+                     "reduce": lambda: (model.counters[0].fill_(1 << 30), model._reduce_into_residual(0, lay["proj"], lay["proj_b"], lay["ln2_gb"] + (model.shard[1],)))}
             parts.update({"attn_" + op.name: op.launch for op in model.attn.ops})
             out["breakdown_ms"] = {k: round(_timed(f, a.steps, a.warmup, 1), 4) for k, f in parts.items()}
             model.counters[0].zero_(); model.counters[1].zero_(); model.targets = [0, 0]

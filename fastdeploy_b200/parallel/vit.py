@@ -6,10 +6,11 @@ only ever touch a rank's own rows. Each encoder block is four tensor-core launch
 collectives inside:
 
   LayerNorm -> [all-gather -> QKV GEMM]     column parallel, this rank's heads only
-  attention over the local heads            batched tcgen05 GEMMs + masked softmax
-  [proj GEMM -> reduce-scatter] + residual  row parallel, partial sums land in the owner's slots
-  LayerNorm -> [all-gather -> fc1 GEMM + GELU]
-  [fc2 GEMM -> reduce-scatter] + residual
+  attention over the local heads            one fused tcgen05 kernel (scores stay in tensor memory)
+  [proj GEMM -> reduce-scatter] + residual + LayerNorm   row parallel, partial sums land in the owner's
+                                            slots; one kernel sums them, adds the residual and normalises
+  [all-gather -> fc1 GEMM + GELU]
+  [fc2 GEMM -> reduce-scatter] + residual + the next block's LayerNorm
 
 Buffers are shared by all layers. The two all-gather inputs alternate between two heap buffers, so
 the one device barrier in front of each all-gather GEMM is also what keeps a fast rank from
@@ -170,6 +171,8 @@ class TensorParallelViT:
             w_qkv = torch.cat([dv(lw["q_w"][sl]), dv(lw["k_w"][sl]), dv(lw["v_w"][sl])])
             b_qkv = torch.cat([dv(lw["q_b"][sl]), dv(lw["k_b"][sl]), dv(lw["v_b"][sl])]).float().contiguous()
             lay = {}
+            lay["ln1_gb"] = (dv(lw["ln1_g"]).float().contiguous(), dv(lw["ln1_b"]).float().contiguous())
+            lay["ln2_gb"] = (dv(lw["ln2_g"]).float().contiguous(), dv(lw["ln2_b"]).float().contiguous())
             lay["ln1"] = layernorm(self.xres, self.shard[0], dv(lw["ln1_g"]).float(), dv(lw["ln1_b"]).float(), rows=rows,
                                    c=H, eps=eps)
             lay["ln2"] = layernorm(self.xres, self.shard[1], dv(lw["ln2_g"]).float(), dv(lw["ln2_b"]).float(), rows=rows,
@@ -189,8 +192,9 @@ class TensorParallelViT:
 
         # ---- head: final LayerNorm on the local rows, class rows summed over the ranks, replicated linear
         self.final = torch.zeros(rows, H, dtype=dtype, device=dev)
-        self.ln_f = layernorm(self.xres, self.final, dv(weights["norm_g"]).float(), dv(weights["norm_b"]).float(),
-                              rows=rows, c=H, eps=eps)
+        self.ln_f_gb = (dv(weights["norm_g"]).float().contiguous(), dv(weights["norm_b"]).float().contiguous())
+        self.ln_f = layernorm(self.xres, self.final, self.ln_f_gb[0], self.ln_f_gb[1], rows=rows, c=H, eps=eps)
+        self.fuse_ln = H <= 2048
         cls_rows = torch.arange(batch, device=dev) * T
         mine = (cls_rows >= self.row0) & (cls_rows < self.row0 + rows)
         self.cls_img = torch.nonzero(mine).flatten()
@@ -220,16 +224,25 @@ class TensorParallelViT:
         op.stores_per_block = sum((min(self.H, (t + 1) * bn) - t * bn + 63) // 64 for t in range(n_tiles))
         return op
 
-    def _reduce_into_residual(self, which: int, op, bias: torch.Tensor) -> None:
+    def _reduce_into_residual(self, which: int, op, bias: torch.Tensor, ln=None) -> None:
         """Waits (bounded, per 128-row block) for every rank's partial block, then
-        ``xres = xres + bias + sum of the partials``."""
+        ``xres = xres + bias + sum of the partials``; with ``ln = (gamma, beta, out)`` the same kernel also writes
+        ``out = LayerNorm(xres)``, i.e. the input of the next all-gather GEMM."""
         c = self.comm
         self.targets[which] += c.world * op.stores_per_block
-        rc = _lib().fdb_comm_slot_reduce_res(
-            ctypes.c_void_p(self.slots[which].data_ptr()), ctypes.c_void_p(self.counters[which].data_ptr()),
-            self.targets[which], ctypes.c_void_p(self.xres.data_ptr()), ctypes.c_void_p(bias.data_ptr()),
-            ctypes.c_void_p(self.xres.data_ptr()), self.H, self.rows, self.H, self.H, self.H, c.world,
-            dtype_code(self.dtype), c.status.ptr, ctypes.c_void_p(current_stream_ptr()))
+        P = ctypes.c_void_p
+        if ln is not None:
+            gamma, beta, out = ln
+            rc = _lib().fdb_comm_slot_reduce_ln(
+                P(self.slots[which].data_ptr()), P(self.counters[which].data_ptr()), self.targets[which],
+                P(self.xres.data_ptr()), P(bias.data_ptr()), self.rows, self.H, c.world, dtype_code(self.dtype),
+                c.status.ptr, P(gamma.data_ptr()), P(beta.data_ptr()), self.eps, P(out.data_ptr()), out.stride(0),
+                P(current_stream_ptr()))
+        else:
+            rc = _lib().fdb_comm_slot_reduce_res(
+                P(self.slots[which].data_ptr()), P(self.counters[which].data_ptr()), self.targets[which],
+                P(self.xres.data_ptr()), P(bias.data_ptr()), P(self.xres.data_ptr()), self.H, self.rows, self.H, self.H,
+                self.H, c.world, dtype_code(self.dtype), c.status.ptr, P(current_stream_ptr()))
         if rc != 0:
             raise RuntimeError("tp vit: " + _native.last_error())
 
@@ -253,22 +266,34 @@ class TensorParallelViT:
         self.xres[:cnt].copy_(flat[lo:lo + cnt])
 
     def encoder(self) -> None:
+        """All encoder blocks and the final LayerNorm: ``xres`` -> ``final``. Every LayerNorm except the first
+        rides on the slot reduction in front of it (``fuse_ln``)."""
         c = self.comm
-        for lay in self.layers:
-            lay["ln1"].launch()
+        n = len(self.layers)
+        for l, lay in enumerate(self.layers):
+            if l == 0 or not self.fuse_ln:
+                lay["ln1"].launch()
             c.barrier()
             lay["qkv"].launch()
             self.attn.launch()
             lay["proj"].launch()
-            self._reduce_into_residual(0, lay["proj"], lay["proj_b"])
-            lay["ln2"].launch()
+            if self.fuse_ln:
+                self._reduce_into_residual(0, lay["proj"], lay["proj_b"], lay["ln2_gb"] + (self.shard[1],))
+            else:
+                self._reduce_into_residual(0, lay["proj"], lay["proj_b"])
+                lay["ln2"].launch()
             c.barrier()
             lay["fc1"].launch()
             lay["fc2"].launch()
-            self._reduce_into_residual(1, lay["fc2"], lay["fc2_b"])
+            if self.fuse_ln:
+                nxt = self.layers[l + 1]["ln1_gb"] + (self.shard[0],) if l + 1 < n else self.ln_f_gb + (self.final,)
+                self._reduce_into_residual(1, lay["fc2"], lay["fc2_b"], nxt)
+            else:
+                self._reduce_into_residual(1, lay["fc2"], lay["fc2_b"])
+        if not self.fuse_ln:
+            self.ln_f.launch()
 
     def head(self) -> torch.Tensor:
-        self.ln_f.launch()
         self.cls_feat.zero_()
         if self.cls_img.numel():
             self.cls_feat[self.cls_img] = self.final[self.cls_local].float()
@@ -283,9 +308,10 @@ class TensorParallelViT:
 
     @property
     def launches_per_forward(self) -> int:
-        """Native kernel launches per forward: per layer 2 LayerNorms, 2 barriers, 4 GEMMs, 4 attention
-        launches and 2 slot reductions, plus the patch GEMM and the final LayerNorm."""
-        return len(self.layers) * 14 + 2
+        """Native kernel launches per forward: per layer 2 barriers, 4 GEMMs, 2 attention launches and 2 slot
+        reductions (with the LayerNorms inside), plus the patch GEMM and the first LayerNorm."""
+        per_layer = 2 + 4 + len(self.attn.ops) + 2 + (0 if self.fuse_ln else 2)
+        return len(self.layers) * per_layer + 2
 
     def flops(self) -> float:
         H, F, T, B, L = self.H, self.cfg["mlp"], self.T, self.B, len(self.layers)
