@@ -162,34 +162,45 @@ __global__ void __launch_bounds__(256) slot_reduce_kernel(const T* slots, const 
 // block: x = x + bias + sum of the world partial blocks (written back in place), y = LayerNorm(x) * gamma + beta.
 // One warp per row keeps the whole row (cols <= 2048) in registers, so x is read once and the normalised row
 // leaves in the same pass. Two CTAs share each 128-row block (64 rows each) and both wait for its counter.
-template <typename T>
+__device__ __forceinline__ void ld8f(const float* p, float (&f)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p + 4));
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+template <typename T, int WORLD>
 __global__ void __launch_bounds__(256) slot_reduce_ln_kernel(const T* slots, const unsigned* counters, unsigned target,
-                                                             T* x, const float* bias, int rows, int cols, int world,
+                                                             T* x, const float* bias, int rows, int cols,
                                                              int* status, const float* gamma, const float* beta,
                                                              float eps, T* y, int y_ld) {
   __shared__ int ok;
-  const int blk = blockIdx.x >> 1;
+  const int blk = blockIdx.x >> 2;                 // four CTAs share a 128-row block, 32 rows each
   if (threadIdx.x == 0) ok = wait_ge(counters + blk, target, status) ? 1 : 0;
   __syncthreads();
   if (!ok) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int row_lo = blk * 128 + (blockIdx.x & 1) * 64;
-  const int row_hi = min(rows, row_lo + 64);
+  const int row_lo = blk * 128 + (blockIdx.x & 3) * 32;
+  const int row_hi = min(rows, row_lo + 32);
   for (int row = row_lo + warp; row < row_hi; row += 8) {
     float v[8][8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       const int c = lane * 8 + k * 256;
       if (c < cols) {
-        const uint4 xv = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * cols + c);
-        const T* xe = reinterpret_cast<const T*>(&xv);
+        // every load of this chunk is issued before the first use
+        uint4 raw[WORLD + 1];
+        raw[0] = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * cols + c);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[k][j] = to_f<T>(xe[j]) + (bias != nullptr ? bias[c + j] : 0.f);
-        for (int s = 0; s < world; ++s) {
-          const uint4 sv = *reinterpret_cast<const uint4*>(slots + (static_cast<size_t>(s) * rows + row) * cols + c);
-          const T* se = reinterpret_cast<const T*>(&sv);
+        for (int s = 0; s < WORLD; ++s)
+          raw[s + 1] = *reinterpret_cast<const uint4*>(slots + (static_cast<size_t>(s) * rows + row) * cols + c);
+        float bv[8];
+        if (bias != nullptr) ld8f(bias + c, bv);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) v[k][j] += to_f<T>(se[j]);
+        for (int j = 0; j < 8; ++j) v[k][j] = bias != nullptr ? bv[j] : 0.f;
+#pragma unroll
+        for (int s = 0; s <= WORLD; ++s) {
+          const T* e = reinterpret_cast<const T*>(&raw[s]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[k][j] += to_f<T>(e[j]);
         }
         uint4 o;
         T* oe = reinterpret_cast<T*>(&o);
@@ -224,10 +235,13 @@ __global__ void __launch_bounds__(256) slot_reduce_ln_kernel(const T* slots, con
     for (int k = 0; k < 8; ++k) {
       const int c = lane * 8 + k * 256;
       if (c < cols) {
+        float g[8], bt[8];
+        ld8f(gamma + c, g);
+        ld8f(beta + c, bt);
         uint4 o;
         T* oe = reinterpret_cast<T*>(&o);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) oe[j] = from_f<T>((v[k][j] - mean) * rstd * gamma[c + j] + beta[c + j]);
+        for (int j = 0; j < 8; ++j) oe[j] = from_f<T>((v[k][j] - mean) * rstd * g[j] + bt[j]);
         *reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * y_ld + c) = o;
       }
     }
@@ -341,14 +355,25 @@ FDB_API int fdb_comm_slot_reduce_ln(const void* slots, const unsigned* counters,
   if (cols % 8 != 0 || cols > 2048 || y_ld % 8 != 0 || gamma == nullptr || beta == nullptr) {
     set_error("comm: fused slot reduce + LayerNorm needs cols a multiple of 8 up to 2048, gamma and beta"); return -1;
   }
-  const int grid = 2 * ((rows + 127) / 128);
+  auto al16 = [](const void* q) { return reinterpret_cast<uintptr_t>(q) % 16 == 0; };
+  if (!al16(gamma) || !al16(beta) || (bias != nullptr && !al16(bias))) { set_error("comm: bias, gamma and beta must be 16-byte aligned"); return -1; }
+  const int grid = 4 * ((rows + 127) / 128);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == kBF16)
-    slot_reduce_ln_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(slots), counters, target,
-        static_cast<__nv_bfloat16*>(x), bias, rows, cols, world, status, gamma, beta, eps, static_cast<__nv_bfloat16*>(y), y_ld);
-  else if (dtype == kF16)
-    slot_reduce_ln_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(slots), counters, target,
-        static_cast<__half*>(x), bias, rows, cols, world, status, gamma, beta, eps, static_cast<__half*>(y), y_ld);
+#define FDB_SRLN(T, W)                                                                                              \
+  slot_reduce_ln_kernel<T, W><<<grid, 256, 0, st>>>(static_cast<const T*>(slots), counters, target, static_cast<T*>(x), \
+                                                    bias, rows, cols, status, gamma, beta, eps, static_cast<T*>(y), y_ld)
+#define FDB_SRLN_W(T)                                              \
+  switch (world) {                                                 \
+    case 1: FDB_SRLN(T, 1); break;                                 \
+    case 2: FDB_SRLN(T, 2); break;                                 \
+    case 4: FDB_SRLN(T, 4); break;                                 \
+    case 8: FDB_SRLN(T, 8); break;                                 \
+    default: set_error("comm: fused slot reduce + LayerNorm takes 1, 2, 4 or 8 ranks"); return -1; \
+  }
+  if (dtype == kBF16) { FDB_SRLN_W(__nv_bfloat16) }
+  else if (dtype == kF16) { FDB_SRLN_W(__half) }
   else { set_error("comm: slot reduce takes fp16 or bf16"); return -1; }
+#undef FDB_SRLN_W
+#undef FDB_SRLN
   return check_launch("slot_reduce_ln");
 }

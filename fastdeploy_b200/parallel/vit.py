@@ -194,7 +194,7 @@ class TensorParallelViT:
         self.final = torch.zeros(rows, H, dtype=dtype, device=dev)
         self.ln_f_gb = (dv(weights["norm_g"]).float().contiguous(), dv(weights["norm_b"]).float().contiguous())
         self.ln_f = layernorm(self.xres, self.final, self.ln_f_gb[0], self.ln_f_gb[1], rows=rows, c=H, eps=eps)
-        self.fuse_ln = H <= 2048
+        self.fuse_ln = H <= 2048 and ws in (1, 2, 4, 8)
         cls_rows = torch.arange(batch, device=dev) * T
         mine = (cls_rows >= self.row0) & (cls_rows < self.row0 + rows)
         self.cls_img = torch.nonzero(mine).flatten()
