@@ -8,14 +8,14 @@ import torch.distributed as dist
 from fastdeploy_b200.parallel.health import RankHealth, RankLostError
 
 
-def _rank(rank, world, port, behaviour, q):
+def _rank(rank, world, port, behaviour, q, join_s):
     store = dist.TCPStore("127.0.0.1", port, world_size=None, is_master=(rank == 0), wait_for_workers=False)
     try:
         if behaviour == "never_joins":
-            time.sleep(2.5)
+            time.sleep(join_s + 1.5)
             return
         h = RankHealth(store, rank, world, timeout_s=0.6)
-        h.wait_for_all(timeout_s=2)
+        h.wait_for_all(timeout_s=join_s)      # generous: process start-up (imports) varies a lot under load
         for step in range(40):
             if behaviour == "dies" and step == 5:
                 q.put((rank, "died"))
@@ -36,22 +36,22 @@ def _rank(rank, world, port, behaviour, q):
             time.sleep(1.0)                   # keep the store up until the others have reported
 
 
-def _run(behaviours, port):
+def _run(behaviours, port, join_s=20.0):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     world = len(behaviours)
-    procs = [ctx.Process(target=_rank, args=(r, world, port, b, q)) for r, b in enumerate(behaviours)]
+    procs = [ctx.Process(target=_rank, args=(r, world, port, b, q, join_s)) for r, b in enumerate(behaviours)]
     for p in procs:
         p.start()
     out = []
-    deadline = time.time() + 12
+    deadline = time.time() + join_s + (40 if join_s > 5 else 8)
     while len(out) < sum(b != "never_joins" for b in behaviours) and time.time() < deadline:
         try:
             out.append(q.get(timeout=0.5))
         except Exception:
             pass
     for p in procs:
-        p.join(timeout=10)
+        p.join(timeout=join_s + 10)
     return out
 
 
@@ -72,7 +72,7 @@ def test_orderly_leave_is_not_a_failure():
 
 
 def test_rank_that_never_joins_fails_the_rendezvous():
-    out = _run(["ok", "never_joins"], 29613)
+    out = _run(["ok", "never_joins"], 29613, join_s=3.0)
     assert out == [] or all(o[1] != "done" for o in out)
 
 
