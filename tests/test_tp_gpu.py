@@ -45,3 +45,34 @@ def test_tp_worker_two_ranks():
     r = json.loads(line[len("TPRESULT "):])
     assert r["allreduce_err"] < 0.1 and r["reducescatter_err"] < 0.1 and r["allgather_err"] == 0.0
     assert r["col_err"] < 2e-2 and r["row_err"] < 2e-2 and r["mlp_err"] < 2e-2, r
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+def test_slot_reduce_with_residual_and_layernorm_matches_fp32(world):
+    """The kernel behind every row-parallel GEMM of the tensor-parallel ViT, fed by hand on one GPU: partial blocks
+    of `world` ranks already sit in the slots and the arrival counters already hold the target."""
+    import ctypes
+    from fastdeploy_b200.ops.base import StatusWord, current_stream_ptr, dtype_code
+    from fastdeploy_b200.parallel.comm import _lib
+    torch.manual_seed(0)
+    rows, cols = 300, 1280
+    dev = "cuda"
+    slots = (torch.randn(world, rows, cols, device=dev) * 0.3).bfloat16()
+    x = torch.randn(rows, cols, device=dev).bfloat16()
+    bias = torch.randn(cols, device=dev)
+    gamma, beta = torch.rand(cols, device=dev) + 0.5, torch.randn(cols, device=dev)
+    y = torch.zeros(rows, cols, device=dev, dtype=torch.bfloat16)
+    counters = torch.full(((rows + 127) // 128,), 7, dtype=torch.int32, device=dev)
+    x_ref = (x.float() + bias + slots.float().sum(0)).bfloat16()
+    y_ref = torch.nn.functional.layer_norm(x_ref.float(), (cols,), gamma, beta, 1e-6)
+    st = StatusWord(torch.device(dev))
+    P = ctypes.c_void_p
+    rc = _lib().fdb_comm_slot_reduce_ln(P(slots.data_ptr()), P(counters.data_ptr()), 7, P(x.data_ptr()), P(bias.data_ptr()),
+                                        rows, cols, world, dtype_code(torch.bfloat16), st.ptr, P(gamma.data_ptr()),
+                                        P(beta.data_ptr()), 1e-6, P(y.data_ptr()), cols, P(current_stream_ptr()))
+    assert rc == 0
+    torch.cuda.synchronize()
+    st.check("slot_reduce_ln")
+    assert (x.float() - x_ref.float()).abs().max().item() <= 0.0625       # one bf16 step at these magnitudes
+    assert (y.float() - y_ref).abs().max().item() < 0.1                   # bf16 output, values up to about 10
+    assert (y.float() - y_ref).abs().mean().item() < 5e-3
