@@ -1,285 +1,66 @@
-"""Headline benchmark: end-to-end images/s of PP-YOLOE+-L (fp16, 640x640 from 1080x1920 uint8
-frames, batch 32 per GPU, multiclass NMS score 0.01 / IoU 0.6 / keep_top_k 100), data-parallel over N GPUs.
+"""Benchmarks of the BASELINE configurations. The headline (no ``--config``) is end-to-end images/s of
+PP-YOLOE+-L (fp16, 640x640 from 1080x1920 uint8 frames, batch 32 per GPU, multiclass NMS score 0.01 / IoU 0.6 /
+keep_top_k 100), data-parallel over N GPUs:
 
     python bench.py --gpus 1 --steps 20 --warmup 5
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         bench.py --gpus N --steps K --warmup W
+    python bench.py --config ernie | ocr | vit_tp  ...        (same flags, same JSON schema)
 
-``value``   : device-timed (CUDA events, max over ranks) images/s of the on-device step: raw uint8 frames
-              already on the GPU -> fused pre-processing -> network -> DFL decode -> NMS.
-``e2e``     : the same metric through the public API (``fd.vision.detection.PPYOLOE.predict_async``), each
-              step copying its frames from pinned host memory and reading its detections back.
-Synthetic data, random-initialised weights (no network access here).
+``value``   : device-timed (CUDA events, max over ranks) rate of the on-device step, inputs resident on the GPU.
+``e2e``     : the same metric through the public API, each step copying its inputs from pinned host memory and
+              reading its results back.
+Every number is the median of ``--repeats`` timed blocks of exactly ``--steps`` steps. Synthetic data,
+random-initialised weights (there is no network access here).
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
-import subprocess
 import sys
-import tempfile
-import threading
-import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-PUBLISHED_IMG_S = 64.9     # best published end-to-end PP-YOLOE-L number of the reference: 15.42 ms on a T4
-REF_UNAVAILABLE = ("refused by a safety check: building the reference (python setup.py build, which downloads "
-                   "ONNX Runtime / Paddle Inference / OpenCV from bj.bcebos.com) was denied; pip install of "
-                   "/root/reference fails before that (no setup.py at the root, python/ needs the CMake build)")
+REF_UNAVAILABLE = ("refused by a safety check: building the reference (its python setup.py build, which downloads "
+                   "ONNX Runtime / Paddle Inference / OpenCV binaries from bj.bcebos.com) was denied; a plain pip "
+                   "install of the reference tree fails before that (no setup.py at its root, python/ needs the "
+                   "CMake build first)")
+
+CONFIGS = ("ppyoloe", "ernie", "ocr", "vit_tp")
 
 
-class ClockSampler:
-    """Samples SM clocks and throttle reasons every 200 ms while the timed regions run. NVML is called in
-    process (three light queries per sample); spawning ``nvidia-smi -lms`` instead was seen to stall the
-    GPUs of a multi-GPU box for tens of milliseconds per poll, which lands inside short timed regions.
-    Falls back to ``nvidia-smi`` when the NVML binding is missing."""
-
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, gpu_index: int):
-        self.gpu_index = gpu_index
-        self.rows = []          # (sm_mhz, max_mhz, set of reason names)
-        self.proc = None
-        self.thread = None
-        self._stop = threading.Event()
-        self._nvml = None
-
-    def start(self):
-        try:
-            import pynvml
-            pynvml.nvmlInit()
-            self._nvml = pynvml
-            self._handle = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
-            self._max = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
-            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
-            self.thread.start()
-            return
-        except Exception:
-            self._nvml = None
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
-            return
-        self.thread = threading.Thread(target=self._read_smi, daemon=True)
-        self.thread.start()
-
-    def ready(self) -> bool:
-        return bool(self.rows) or (self._nvml is None and self.proc is None)
-
-    def _poll_nvml(self):
-        n = self._nvml
-        names = (("hw_slowdown", getattr(n, "nvmlClocksEventReasonHwSlowdown", 0x8)),
-                 ("hw_thermal_slowdown", getattr(n, "nvmlClocksEventReasonHwThermalSlowdown", 0x40)),
-                 ("sw_thermal_slowdown", getattr(n, "nvmlClocksEventReasonSwThermalSlowdown", 0x20)),
-                 ("sw_power_cap", getattr(n, "nvmlClocksEventReasonSwPowerCap", 0x4)))
-        get_reasons = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
-            getattr(n, "nvmlDeviceGetCurrentClocksThrottleReasons", None)
-        while not self._stop.is_set():
-            try:
-                sm = float(n.nvmlDeviceGetClockInfo(self._handle, n.NVML_CLOCK_SM))
-                mask = int(get_reasons(self._handle)) if get_reasons else 0
-                self.rows.append((sm, self._max, {k for k, bit in names if mask & bit}))
-            except Exception:
-                pass
-            self._stop.wait(0.2)
-
-    def _read_smi(self):
-        for line in self.proc.stdout:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) >= 8:
-                try:
-                    reasons = {k for k, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
-                                                  "sw_power_cap"), parts[4:8]) if v.lower().startswith("active")}
-                    self.rows.append((float(parts[1]), float(parts[2]), reasons))
-                except ValueError:
-                    continue
-
-    def stop(self):
-        self._stop.set()
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=2)
-            except Exception:
-                self.proc.kill()
-        if self.thread is not None:
-            self.thread.join(timeout=2)
-        sm = sorted(r[0] for r in self.rows)
-        mx = max((r[1] for r in self.rows), default=0.0)
-        reasons = set().union(*(r[2] for r in self.rows)) if self.rows else set()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
-                "samples": len(sm), "source": "nvml" if self._nvml is not None else "nvidia-smi"}
-
-
-def physical_gpu_index(local_rank: int) -> int:
-    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
-    if vis:
-        try:
-            return int(vis.split(",")[local_rank])
-        except (ValueError, IndexError):
-            pass
-    return local_rank
-
-
-def main():
+def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--repeats", type=int, default=5, help="timed blocks of --steps steps; the median is reported")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=32, help="images per GPU per step")
+    ap.add_argument("--config", default="ppyoloe", choices=CONFIGS)
+    ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (0 = the configuration's own)")
     ap.add_argument("--variant", default="l")
     ap.add_argument("--model-dir", default="")
     ap.add_argument("--latency-iters", type=int, default=50)
     ap.add_argument("--skip-latency", action="store_true")
+    ap.add_argument("--scheduler-mode", action="store_true",
+                    help="also drive all N GPUs from ONE process through serving.Scheduler (extra key)")
+    ap.add_argument("--dtype", default="", help="vit_tp: bf16 | fp8")
     args = ap.parse_args()
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REF_UNAVAILABLE}))
         return 0
 
-    import numpy as np
-    import torch
-    import torch.distributed as dist
-
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
-
-    import fastdeploy_b200 as fd
-    from fastdeploy_b200.models.ppyoloe import write_ppyoloe
-    fd.set_logger(False, True)
-
-    model_dir = args.model_dir or os.path.join(tempfile.gettempdir(), f"fdb200_ppyoloe_{args.variant}_640")
-    if rank == 0 and not os.path.exists(os.path.join(model_dir, "model.pdiparams")):
-        write_ppyoloe(model_dir, args.variant, image=640, num_classes=80, seed=0, score_threshold=0.01,
-                      nms_threshold=0.6, nms_top_k=1000, keep_top_k=100)
-    barrier()
-
-    opt = fd.RuntimeOption()
-    opt.use_gpu(local_rank)
-    opt.enable_trt_fp16()
-    model = fd.vision.detection.PPYOLOE(os.path.join(model_dir, "model.pdmodel"),
-                                        os.path.join(model_dir, "model.pdiparams"),
-                                        os.path.join(model_dir, "infer_cfg.yml"), runtime_option=opt)
-    B = args.batch
-    H, W = 1080, 1920
-    rng = np.random.default_rng(1234 + rank)
-    # two alternating sets of pinned host frames, uniform in [0, 255]
-    host_sets = []
-    for s in range(2):
-        t = torch.from_numpy(rng.integers(0, 256, (B, H, W, 3), dtype=np.uint8)).pin_memory()
-        host_sets.append([t[i] for i in range(B)])
-    dev_sets = [[f.to(dev) for f in frames] for frames in host_sets]
-
-    # The clock sampler starts before the warm-up: the first nvidia-smi query initialises NVML for every GPU
-    # of the box and holds driver locks while it does, which must not land inside a timed region.
-    sampler = ClockSampler(physical_gpu_index(local_rank))
-    sampler.start()
-    # ---------------- device-timed step (inputs resident on the GPU)
-    def run_steps(sets, n):
-        """n pipelined steps (the next batch is queued before the previous one is read back)."""
-        pend, dets = None, 0
-        for i in range(n):
-            nxt = model.predict_async(sets[i & 1])
-            if pend is not None:
-                dets += sum(len(r.boxes) for r in pend.result())
-            pend = nxt
-        dets += sum(len(r.boxes) for r in pend.result())
-        return dets
-
-    t_wait = time.time()
-    while not sampler.ready() and time.time() - t_wait < 10.0:
-        time.sleep(0.05)                          # NVML is initialised once the first sample is in
-    run_steps(dev_sets, max(args.warmup, 3))      # warm-up in the same pipelined pattern as the timed loop
-    # A full collection over the model's object graph takes tens of milliseconds on the host, long enough
-    # to drain the two-batch pipeline: collect now and freeze the survivors, as a long-running server does
-    # after start-up, so that collections during the timed regions only see the per-step results.
-    import gc
-    gc.collect()
-    gc.freeze()
-    barrier()                                     # no idle gap from here on: an idle GPU drops its clocks
-    sampler.rows.clear()
-    launches0 = model.runtime.gpu_launches
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    run_steps(dev_sets, args.steps)
-    e1.record()
-    barrier()
-    ms_dev = e0.elapsed_time(e1)
-    launches = model.runtime.gpu_launches - launches0
-
-    # ---------------- end to end through the public API (pinned host frames in, detections out)
-    run_steps(host_sets, max(args.warmup, 3))
-    barrier()
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record()
-    n_det = run_steps(host_sets, args.steps)
-    e3.record()
-    barrier()
-    ms_e2e = e2.elapsed_time(e3)
-    h2d, d2h = model.h2d_bytes_last, model.d2h_bytes_last
-    # ---------------- batch-1 latency through the public API (one pinned 1080p frame in, detections out)
-    lat = []
-    if not args.skip_latency:
-        for i in range(3):
-            model.predict(host_sets[0][i])
-        for i in range(args.latency_iters):
-            t0 = time.perf_counter()
-            model.predict(host_sets[i & 1][i % B])
-            lat.append((time.perf_counter() - t0) * 1e3)
-    clocks = sampler.stop()
-
-    if world > 1:
-        t = torch.tensor([ms_dev, ms_e2e], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_dev, ms_e2e = float(t[0]), float(t[1])
-    if rank == 0:
-        total_imgs = B * world * args.steps
-        value = total_imgs / (ms_dev / 1e3)
-        e2e = total_imgs / (ms_e2e / 1e3)
-        out = {
-            "metric": "end-to-end images/sec PP-YOLOE+-L (device-timed)", "value": round(value, 1), "unit": "images/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": round(ms_dev / args.steps, 3), "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": round(value / PUBLISHED_IMG_S, 2), "dtype": "fp16", "data": "synthetic",
-            "config": {"model": f"PP-YOLOE+-{args.variant.upper()} 640x640 from 1080x1920 uint8, NMS 0.01/0.6/100, "
-                                "random-init weights", "global_batch": B * world, "seq_len": None,
-                       "parallelism": f"dp{world}",
-                       "l2_policy": "inputs larger than L2: 199 MB of raw frames per step, two alternating sets",
-                       "baseline_ref": "reference's best published end-to-end PP-YOLOE-L: 15.42 ms on one T4 (TensorRT INT8)"},
-            "e2e": {"value": round(e2e, 1), "unit": "images/s", "h2d_bytes_per_step": int(h2d),
-                    "d2h_bytes_per_step": int(d2h), "ms_per_step": round(ms_e2e / args.steps, 3),
-                    "detections_read": int(n_det)},
-            "latency": ({"p50_batch1_ms": round(float(np.percentile(lat, 50)), 3), "p99_batch1_ms": round(float(np.percentile(lat, 99)), 3),
-                         "iters": len(lat), "what": "rank 0, PPYOLOE.predict on one pinned 1080x1920 frame, wall clock"} if lat else None),
-            "gpu_launches": int(launches), "clocks": clocks, "impl": "ours",
-        }
+    import importlib
+    from fastdeploy_b200.benchmarks.common import Context
+    ctx = Context(args.gpus)
+    mod = importlib.import_module(f"fastdeploy_b200.benchmarks.{args.config}")
+    out = mod.run(ctx, args)
+    if ctx.rank == 0:
         print(json.dumps(out))
-    if world > 1:
-        dist.destroy_process_group()
+    ctx.finish()
     return 0
 
 

@@ -22,6 +22,9 @@ constexpr int kMaxPeers = 8;
 constexpr long long kPeerWaitClocks = 2000000000LL;   // about one second at 1.9 GHz
 constexpr int kStatusTimeoutPeerCode = 4;
 
+// Device barriers and the fused peer-mode GEMMs take their epoch as a launch parameter that the host
+// increments per launch, so these launches must not be captured into a CUDA graph (a replay would wait
+// for an epoch that has already passed): the Python layer launches them eagerly.
 struct PeerPtrs {
   void* p[kMaxPeers];
 };
@@ -36,11 +39,14 @@ __device__ __forceinline__ void red_release_sys_add(unsigned* p, unsigned v) {
 }
 
 // Spins until *flag >= target or the budget runs out (then the status word gets the peer code).
+// A status word that already holds an error ends the wait at once: after one lost peer every later wait
+// of the queued forward would otherwise spin for its whole budget on data that will never come.
 __device__ __forceinline__ bool wait_ge(const unsigned* flag, unsigned target, int* status) {
   const long long t0 = clock64();
   for (unsigned it = 0;; ++it) {
     if (static_cast<int>(ld_acquire_sys(flag) - target) >= 0) return true;
     if ((it & 63u) == 63u) {
+      if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return false;
       if (clock64() - t0 > kPeerWaitClocks) {
         if (status != nullptr) atomicExch(status, kStatusTimeoutPeerCode);
         return false;

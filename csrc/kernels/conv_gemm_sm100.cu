@@ -823,6 +823,9 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         to[i] = v0; to[i + kThreads] = v1; to[i + 2 * kThreads] = v2; to[i + 3 * kThreads] = v3;
       }
       for (; i < blk_vecs; i += kThreads) to[i] = from[i];
+      // The rows were written through the generic proxy and will be read by TMA (async proxy) in
+      // another CTA: each writer orders its stores before async-proxy accesses, then the flag is released.
+      asm volatile("fence.proxy.async;" ::: "memory");
       __threadfence();
       __syncthreads();
       if (threadIdx.x == 0) st_release_gpu(p.ready + b, p.peer_epoch);
@@ -846,13 +849,17 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (owner != p.peer_rank) {
             const long long t0 = clock64();
             while (static_cast<int>(ld_acquire_gpu(p.ready + twi) - p.peer_epoch) < 0) {
-              if (*abort_flag || clock64() - t0 > kWaitClockLimit) {
+              // an error already recorded by an earlier kernel of this forward ends the wait at once
+              const bool dead = p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0;
+              if (*abort_flag || dead || clock64() - t0 > kWaitClockLimit) {
                 *abort_flag = kStatusTimeoutPeer;
                 ok = false;
                 break;
               }
             }
             if (!ok) break;
+            // acquire (generic proxy) -> TMA reads of the gathered rows (async proxy)
+            asm volatile("fence.proxy.async;" ::: "memory");
           }
         }
         const int x0 = twi * p.tw * p.stride - p.pad_w;

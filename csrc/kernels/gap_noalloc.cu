@@ -103,6 +103,12 @@ int fdb_global_avgpool_noalloc(const void* x, void* out, int n, int hw, int c, i
   if (x == nullptr || out == nullptr || n <= 0 || hw <= 0 || c <= 0 || splits <= 0 || c % 8 != 0 || x_ld % 8 != 0 ||
       x_ld < c || out_ld < c || out_dtype < 0 || out_dtype > 2 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
     return FDB_GAP_NOALLOC_BAD_ARGUMENT;
+  // Every image starts at x + i * x_n_stride and is read with 16-byte loads: the image stride must keep
+  // that alignment, and a non-zero stride may not be shorter than one image (overlapping images are
+  // legal reads but never what a caller means).
+  if (x_n_stride < 0 || x_n_stride % 8 != 0 ||
+      (x_n_stride > 0 && x_n_stride < static_cast<long long>(hw - 1) * x_ld + c))
+    return FDB_GAP_NOALLOC_BAD_ARGUMENT;
   const long long need = static_cast<long long>(n) * splits * c;
   if (need > FDB_GAP_NOALLOC_MAX_SCRATCH_FLOATS) return FDB_GAP_NOALLOC_TOO_LARGE;
   if (splits > 65535 || n > 65535) return FDB_GAP_NOALLOC_BAD_ARGUMENT;
@@ -112,21 +118,25 @@ int fdb_global_avgpool_noalloc(const void* x, void* out, int n, int hw, int c, i
   const long long xns = x_n_stride > 0 ? x_n_stride : static_cast<long long>(hw) * x_ld;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   dim3 grid((c + 63) / 64, n, splits);
+  // Launch errors are read with cudaPeekAtLastError straight after each launch, so that this call
+  // reports its own launches only and leaves an earlier, unrelated error where its owner will find it.
+  if (cudaPeekAtLastError() != cudaSuccess) return FDB_GAP_NOALLOC_CUDA_ERROR;
   if (is_bf16)
     gap_partial_noalloc<true><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(x), scratch, hw, c, x_ld, splits, xns);
   else
     gap_partial_noalloc<false><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(x), scratch, hw, c, x_ld, splits, xns);
   gap_finalize_noalloc<<<(n * c + 255) / 256, 256, 0, s>>>(scratch, out, n, c, splits, out_dtype, out_ld, 1.0f / hw);
-  return cudaGetLastError() == cudaSuccess ? FDB_GAP_NOALLOC_OK : FDB_GAP_NOALLOC_CUDA_ERROR;
+  return cudaPeekAtLastError() == cudaSuccess ? FDB_GAP_NOALLOC_OK : FDB_GAP_NOALLOC_CUDA_ERROR;
 }
 
 extern "C" __attribute__((visibility("default")))
 const char* fdb_global_avgpool_noalloc_strerror(int code) {
   switch (code) {
     case FDB_GAP_NOALLOC_OK: return "ok";
-    case FDB_GAP_NOALLOC_BAD_ARGUMENT: return "bad argument: null pointer, non-positive size, or c / x_ld not a multiple of 8";
+    case FDB_GAP_NOALLOC_BAD_ARGUMENT: return "bad argument: null pointer, x not 16-byte aligned, non-positive size, c / x_ld / x_n_stride not a "
+                                              "multiple of 8, x_ld or out_ld below c, x_n_stride shorter than one image, or out_dtype outside 0..2";
     case FDB_GAP_NOALLOC_TOO_LARGE: return "n * splits * c exceeds the built-in scratch of 1048576 floats";
-    case FDB_GAP_NOALLOC_CUDA_ERROR: return "CUDA error while resolving the scratch address or launching";
+    case FDB_GAP_NOALLOC_CUDA_ERROR: return "CUDA error: pending before the call, while resolving the scratch address, or at launch";
     default: return "unknown code";
   }
 }

@@ -25,6 +25,12 @@
  *     it; this operation overwrites every element it later reads, so nothing has to be cleared
  *     between calls. Two calls whose kernels can overlap on the GPU (different streams without
  *     an ordering between them) race on the array: serialise them.
+ *   - x must be 16-byte aligned, and c, x_ld and x_n_stride multiples of 8 elements (the kernel reads
+ *     16 bytes at a time from every pixel of every image); x_ld and out_ld must be at least c; a non-zero
+ *     x_n_stride must span one whole image ((hw - 1) * x_ld + c elements). Anything else is rejected
+ *     with FDB_GAP_NOALLOC_BAD_ARGUMENT before a kernel is launched.
+ *   - If the CUDA runtime already holds an error from earlier work when the call comes in, the call
+ *     launches nothing and returns FDB_GAP_NOALLOC_CUDA_ERROR; it never clears that error.
  *   - No cudaMalloc, cudaFree or other allocating routine is called, on any path.
  */
 #ifndef FDB_GAP_NOALLOC_H_
@@ -38,17 +44,19 @@ extern "C" {
 
 enum {
   FDB_GAP_NOALLOC_OK = 0,
-  FDB_GAP_NOALLOC_BAD_ARGUMENT = 1, /* null pointer, non-positive size, c or x_ld not a multiple of 8 */
+  FDB_GAP_NOALLOC_BAD_ARGUMENT = 1, /* null / misaligned pointer, non-positive size, c, x_ld or x_n_stride not a
+                                       multiple of 8, strides too short, out_dtype outside 0..2 */
   FDB_GAP_NOALLOC_TOO_LARGE = 2,    /* n * splits * c exceeds the built-in scratch */
   FDB_GAP_NOALLOC_CUDA_ERROR = 3    /* device query, symbol lookup or launch failed */
 };
 
 /* out[i][ch] = mean over p of x[i][p][ch] for an NHWC tensor of 16-bit floats.
  *   x          device pointer, fp16 (is_bf16 = 0) or bf16 (is_bf16 = 1), 16-byte aligned
- *   out        device pointer, [n][out_ld] of out_dtype (0 fp16, 1 bf16, 2 fp32)
+ *   out        device pointer, [n][out_ld] of out_dtype (0 fp16, 1 bf16, 2 fp32), out_ld >= c
  *   n, hw, c   images, pixels per image, channels (c a multiple of 8)
  *   x_ld       elements between consecutive pixels (>= c, multiple of 8)
- *   x_n_stride elements between consecutive images (0 means hw * x_ld)
+ *   x_n_stride elements between consecutive images (0 means hw * x_ld; otherwise a multiple of 8 that
+ *              spans at least one image)
  *   splits     pixel ranges summed by separate thread blocks (>= 1)
  *   stream     cudaStream_t
  * Returns one of the codes above. */

@@ -46,6 +46,10 @@ struct NmsDesc {
   // optional scratch [N][C][M] in the score dtype: anchor-major scores are transposed into it
   // first so that every class reads its M scores contiguously
   void* scores_t;
+  // optional pre-pass scratch: lead[N][C][kLead] scores of each class's leading kept boxes and tau[N], the
+  // per-image score below which no box can reach the final keep_top_k rows (null = no pre-pass)
+  float* lead;
+  float* tau;
 };
 
 // Optional phase timing of the class kernel (compile with -DFDB_NMS_PROFILE): thread 0 of every
@@ -87,7 +91,7 @@ __device__ __forceinline__ float score_to_float(__nv_bfloat16 v) { return __bflo
 // Fills keys[m] with the bit pattern of score m when it passes the threshold, else 0. Eight loads
 // are in flight per thread before any is consumed. Returns this thread's count of passing scores.
 template <typename T>
-__device__ __forceinline__ int load_keys(const NmsDesc& d, uint32_t* keys, long long base) {
+__device__ __forceinline__ int load_keys(const NmsDesc& d, uint32_t* keys, long long base, float floor_score) {
   const T* src = reinterpret_cast<const T*>(d.scores) + base;
   int local = 0;
   for (int m0 = threadIdx.x; m0 < d.M; m0 += 8 * kNmsThreads) {
@@ -102,7 +106,7 @@ __device__ __forceinline__ int load_keys(const NmsDesc& d, uint32_t* keys, long 
       const int m = m0 + u * kNmsThreads;
       if (m < d.M) {
         const float s = score_to_float(v[u]);
-        const uint32_t k = (s > d.score_threshold && s > 0.f) ? __float_as_uint(s) : 0u;
+        const uint32_t k = (s > d.score_threshold && s > 0.f && s >= floor_score) ? __float_as_uint(s) : 0u;
         keys[m] = k;
         local += k != 0u;
       }
@@ -200,10 +204,11 @@ __global__ void __launch_bounds__(kNmsThreads) nms_class_kernel(const NmsDesc d)
   NMS_PHASE_BEGIN;
   // 1. keys: positive scores compare like their bit patterns
   int local = 0;
+  const float floor_score = d.tau != nullptr ? d.tau[n] : 0.f;
   switch (d.score_dtype) {
-    case kF32: local = load_keys<float>(d, keys, base); break;
-    case kBF16: local = load_keys<__nv_bfloat16>(d, keys, base); break;
-    default: local = load_keys<__half>(d, keys, base); break;
+    case kF32: local = load_keys<float>(d, keys, base, floor_score); break;
+    case kBF16: local = load_keys<__nv_bfloat16>(d, keys, base, floor_score); break;
+    default: local = load_keys<__half>(d, keys, base, floor_score); break;
   }
   int total_pos;
   block_excl_scan(local, warp_tmp, &total_pos);
@@ -382,6 +387,145 @@ __global__ void __launch_bounds__(kNmsThreads) nms_class_kernel(const NmsDesc d)
   if (tid == 0) *count_out = nkept;
 }
 
+// ------------------------------------------------------------------ pre-pass: a floor for the scores that can matter
+// The result keeps at most keep_top_k rows per image, the best-scoring kept boxes over all classes. The
+// kLead best candidates of a class, swept among themselves in score order, get exactly the verdict the
+// full sweep gives them (a box is only ever suppressed by better-scoring boxes of its class). So these
+// kept "leaders" are a subset of all kept boxes, and once an image has keep_top_k of them, the
+// keep_top_k-th best leader score tau is a floor: a box scoring below tau is outranked by keep_top_k kept
+// boxes and cannot reach the output, nor can it suppress a box scoring tau or more. The class kernel then
+// drops everything below tau when it loads the scores, which is exact for every input and turns the dense
+// score maps of an untrained or badly calibrated head (thousands of candidates per class, all swept for
+// nothing) into a few candidates per class.
+constexpr int kLead = 4;
+constexpr int kTauMax = 4096;   // classes * kLead entries sorted per image
+
+__device__ __forceinline__ void lead_insert(unsigned long long (&top)[kLead], unsigned long long v) {
+#pragma unroll
+  for (int i = 0; i < kLead; ++i) {
+    if (v > top[i]) { const unsigned long long t = top[i]; top[i] = v; v = t; }
+  }
+}
+// top kLead of the union of two descending lists, descending
+__device__ __forceinline__ void lead_merge(unsigned long long (&a)[kLead], const unsigned long long (&b)[kLead]) {
+  unsigned long long m[kLead];
+#pragma unroll
+  for (int i = 0; i < kLead; ++i) m[i] = a[i] > b[kLead - 1 - i] ? a[i] : b[kLead - 1 - i];   // bitonic, holds the top kLead
+  // bitonic merge network for 4 elements, descending
+  if (m[0] < m[2]) { const unsigned long long t = m[0]; m[0] = m[2]; m[2] = t; }
+  if (m[1] < m[3]) { const unsigned long long t = m[1]; m[1] = m[3]; m[3] = t; }
+  if (m[0] < m[1]) { const unsigned long long t = m[0]; m[0] = m[1]; m[1] = t; }
+  if (m[2] < m[3]) { const unsigned long long t = m[2]; m[2] = m[3]; m[3] = t; }
+#pragma unroll
+  for (int i = 0; i < kLead; ++i) a[i] = m[i];
+}
+static_assert(kLead == 4, "lead_merge is written for four entries");
+
+template <typename T>
+__device__ __forceinline__ void lead_scan(const NmsDesc& d, long long base, unsigned long long (&top)[kLead]) {
+  const T* src = reinterpret_cast<const T*>(d.scores) + base;
+  for (int m0 = threadIdx.x; m0 < d.M; m0 += 4 * kNmsThreads) {
+    T v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = src[static_cast<long long>(min(m0 + u * kNmsThreads, d.M - 1)) * d.s_m];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int m = m0 + u * kNmsThreads;
+      const float sc = score_to_float(v[u]);
+      if (m < d.M && sc > d.score_threshold && sc > 0.f)
+        lead_insert(top, (static_cast<unsigned long long>(__float_as_uint(sc)) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(m)));
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kNmsThreads) nms_lead_kernel(const NmsDesc d) {
+  const int c = blockIdx.x, n = blockIdx.y;
+  float* out = d.lead + (static_cast<size_t>(n) * d.C + c) * kLead;
+  if (c == d.background_label) {
+    if (threadIdx.x < kLead) out[threadIdx.x] = 0.f;
+    return;
+  }
+  const long long base = static_cast<long long>(n) * d.s_n + static_cast<long long>(c) * d.s_c;
+  unsigned long long top[kLead] = {0ull, 0ull, 0ull, 0ull};
+  switch (d.score_dtype) {
+    case kF32: lead_scan<float>(d, base, top); break;
+    case kBF16: lead_scan<__nv_bfloat16>(d, base, top); break;
+    default: lead_scan<__half>(d, base, top); break;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    unsigned long long other[kLead];
+#pragma unroll
+    for (int i = 0; i < kLead; ++i) other[i] = __shfl_xor_sync(0xffffffffu, top[i], o);
+    lead_merge(top, other);
+  }
+  __shared__ unsigned long long wtop[kNmsThreads / 32][kLead];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < kLead; ++i) wtop[warp][i] = top[i];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < kNmsThreads / 32; ++w) {
+      unsigned long long other[kLead];
+#pragma unroll
+      for (int i = 0; i < kLead; ++i) other[i] = wtop[w][i];
+      lead_merge(top, other);
+    }
+    // greedy sweep of the leaders among themselves
+    const float4* boxes = reinterpret_cast<const float4*>(d.boxes) + static_cast<size_t>(n) * d.M;
+    const bool normalized = d.normalized != 0;
+    float4 kb[kLead];
+    float ka[kLead];
+    int nk = 0;
+    const int considered = min(kLead, d.nms_top_k < 0 ? kLead : d.nms_top_k);   // candidates past nms_top_k are never swept
+    const int limit = min(considered, d.max_keep);
+#pragma unroll
+    for (int i = 0; i < kLead; ++i) {
+      float sc = 0.f;
+      if (top[i] != 0ull && i < considered && nk < limit) {
+        const uint32_t m = 0xFFFFFFFFu - static_cast<uint32_t>(top[i] & 0xFFFFFFFFull);
+        const float4 b = boxes[m];
+        const float ar = box_area(b, normalized);
+        bool hit = false;
+        for (int k = 0; k < nk; ++k) hit |= overlaps(b, ar, kb[k], ka[k], normalized, d.nms_threshold);
+        if (!hit) {
+          kb[nk] = b; ka[nk] = ar; ++nk;
+          sc = __uint_as_float(static_cast<uint32_t>(top[i] >> 32));
+        }
+      }
+      out[i] = sc;
+    }
+  }
+}
+
+// tau[n] = keep_top_k-th best leader score of image n, or 0 when the image has fewer leaders.
+__global__ void __launch_bounds__(1024) nms_tau_kernel(const NmsDesc d) {
+  __shared__ uint32_t keys[kTauMax];
+  const int n = blockIdx.x, tid = threadIdx.x;
+  const int E = d.C * kLead;
+  int sort_n = 32;
+  while (sort_n < E) sort_n <<= 1;
+  const float* lead = d.lead + static_cast<size_t>(n) * E;
+  for (int i = tid; i < sort_n; i += 1024) keys[i] = i < E ? __float_as_uint(lead[i]) : 0u;
+  __syncthreads();
+  for (int k = 2; k <= sort_n; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int i = tid; i < sort_n; i += 1024) {
+        const int ixj = i ^ j;
+        if (ixj > i) {
+          const uint32_t a = keys[i], b = keys[ixj];
+          const bool desc = (i & k) == 0;
+          if (desc ? (a < b) : (a > b)) { keys[i] = b; keys[ixj] = a; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  if (tid == 0) d.tau[n] = d.keep_top_k <= sort_n ? __uint_as_float(keys[d.keep_top_k - 1]) : 0.f;
+}
+
 // Anchor-major scores [N][M][C] (unit class stride) -> class-major [N][C][M], 32 x 32 tiles.
 template <typename T>
 __global__ void __launch_bounds__(256) nms_transpose_kernel(const T* __restrict__ in, T* __restrict__ out, long long s_n,
@@ -511,8 +655,16 @@ struct NmsOp : Op {
       NmsDesc t = d;
       t.scores = d.scores_t;
       t.s_n = static_cast<long long>(d.C) * d.M; t.s_c = d.M; t.s_m = 1;
+      if (d.tau != nullptr) {
+        nms_lead_kernel<<<grid, kNmsThreads, 0, s>>>(t);
+        nms_tau_kernel<<<d.N, 1024, 0, s>>>(t);
+      }
       nms_class_kernel<<<grid, kNmsThreads, smem1, s>>>(t);
     } else {
+      if (d.tau != nullptr) {
+        nms_lead_kernel<<<grid, kNmsThreads, 0, s>>>(d);
+        nms_tau_kernel<<<d.N, 1024, 0, s>>>(d);
+      }
       nms_class_kernel<<<grid, kNmsThreads, smem1, s>>>(d);
     }
     nms_merge_kernel<<<d.N, 1024, smem2, s>>>(d);
@@ -535,6 +687,9 @@ FDB_API int fdb_nms_phase_read(unsigned long long* host8, int reset) {
 #endif
 
 // Scratch requirement in bytes for the per-class lists: counts, scores, indices.
+// Leaders kept per class by the score-floor pre-pass (size of the `lead` scratch: N * C * this many floats).
+FDB_API int fdb_nms_lead_per_class() { return kLead; }
+
 FDB_API long long fdb_nms_scratch_bytes(int N, int C, int max_keep) {
   return static_cast<long long>(N) * C * (4 + 8ll * max_keep);
 }
@@ -551,6 +706,10 @@ FDB_API void* fdb_nms_create(const NmsDesc* dp) {
   if (d.max_keep < 1 || d.max_keep > kNmsMaxTopK) { set_error("nms: max_keep must be in [1, 1024]"); return nullptr; }
   if (d.keep_top_k > -1 && static_cast<long long>(d.C) * d.max_keep > kMergeMax && d.keep_top_k < d.C * d.max_keep) {
     set_error("nms: classes * max_keep exceeds the merge capacity (8192)"); return nullptr;
+  }
+  if ((d.lead == nullptr) != (d.tau == nullptr)) { set_error("nms: lead and tau scratch come together"); return nullptr; }
+  if (d.tau != nullptr && (d.keep_top_k < 1 || d.C * kLead > kTauMax || d.C * kLead < d.keep_top_k)) {
+    set_error("nms: the score-floor pre-pass needs keep_top_k <= 4 * classes <= 4096"); return nullptr;
   }
   auto* op = new NmsOp();
   op->d = d;

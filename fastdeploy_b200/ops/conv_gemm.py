@@ -135,6 +135,12 @@ class ConvGemm(NativeOp):
         assert w_packed.dtype == x.dtype
         handle = _lib().fdb_conv_gemm_create(ctypes.byref(d))
         super().__init__(handle, [x, w_packed, y, bias, residual, self.status], name)
+        es_in, es_out = x.element_size(), y.element_size()
+        # shape record for profilers: algorithmic FLOPs and bytes of this launch
+        self.meta = dict(in_shape=(n, h, w_, cin), cin_logical=cin, out_hw=tuple(out_hw), cout=cout,
+                         kernel=tuple(kernel), stride=stride,
+                         bytes=n * h * w_ * cin * es_in + n * out_hw[0] * out_hw[1] * cout * es_out
+                         + w_packed.numel() * es_in + (n * out_hw[0] * out_hw[1] * cout * es_in if residual is not None else 0))
 
     def info(self):
         out = (ctypes.c_int * 5)()

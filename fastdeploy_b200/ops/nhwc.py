@@ -149,3 +149,62 @@ def depthwise_conv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor
     return make_simple(K_DEPTHWISE, [x, w, bias, y],
                        [n, h, w_in, c, x_ld or c, out_hw[0], out_hw[1], y_ld or c, kernel[0], kernel[1], stride[0], stride[1],
                         pad[0], pad[1], _bf(x), x_n_stride, y_n_stride, ACT[act]], [act_alpha, act_beta], name="depthwise_conv")
+
+
+# ---------------------------------------------------------------------- fused small ops (csrc/kernels/fused_small_ops.cu)
+def _fused_lib():
+    lib = _native.kernels()
+    if not getattr(lib, "_fused_ready", False):
+        lib.fdb_fused_create.restype = ctypes.c_void_p
+        lib.fdb_fused_create.argtypes = [ctypes.c_int, ctypes.POINTER(_SimpleDesc)]
+        lib._fused_ready = True
+    return lib
+
+
+def _make_fused(kind: int, ptrs, ints, floats=(), name="fused") -> NativeOp:
+    d = _SimpleDesc()
+    for k, t in enumerate(ptrs):
+        d.p[k] = t.data_ptr() if t is not None else None
+    for k, v in enumerate(ints):
+        d.i[k] = int(v)
+    for k, v in enumerate(floats):
+        d.f[k] = float(v)
+    return NativeOp(_fused_lib().fdb_fused_create(kind, ctypes.byref(d)), list(ptrs), name)
+
+
+def gap_splits_v2(hw: int, n: int, c: int, sms: int = 148) -> int:
+    """Pixel splits of the bandwidth-bound partial-sum kernel: about eight blocks per SM, at least 128 pixels each."""
+    blocks = n * ((c + 63) // 64)
+    return max(1, min((8 * sms + blocks - 1) // blocks, (hw + 127) // 128))
+
+
+def gap_partial(x: torch.Tensor, part: torch.Tensor, *, n: int, hw: int, c: int, x_ld: Optional[int] = None,
+                x_n_stride: int = 0, splits: int = 1) -> NativeOp:
+    """``part[n, s, c] = sum of x[n, p, c] over the pixels of split s`` (fp32 ``part`` of ``n * splits * c``)."""
+    assert part.dtype == torch.float32 and part.numel() >= n * splits * c
+    return _make_fused(0, [x, part], [n, hw, c, x_ld or c, splits, _bf(x), x_n_stride], name="gap_partial")
+
+
+def ese_gate(part: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, *, n: int, cin: int,
+             cout: int, splits: int, hw: int, act: Optional[str] = None, alpha: float = 0.0, beta: float = 0.0,
+             out_ld: Optional[int] = None) -> NativeOp:
+    """``out[n, co] = act(bias[co] + sum_ci w[co, ci] * mean[n, ci])`` where the mean over ``hw`` pixels is finished
+    from the per-split partial sums: global-average-pool finalise + the 1x1 "excite" convolution + its activation."""
+    assert part.dtype == torch.float32 and out.dtype == torch.float32 and w.dim() == 2 and w.stride(1) == 1
+    return _make_fused(1, [part, w, bias, out], [n, cin, cout, splits, w.stride(0), out_ld or cout, ACT[act], _bf(w)],
+                       [1.0 / hw, alpha, beta], name="ese_gate")
+
+
+def spp_maxpool(x: torch.Tensor, outs: Sequence[torch.Tensor], kernels: Sequence[int], *, n: int, h: int, w: int, c: int,
+                x_ld: Optional[int] = None, x_n_stride: int = 0, y_lds: Optional[Sequence[int]] = None,
+                y_n_strides: Optional[Sequence[int]] = None) -> NativeOp:
+    """Stride-1, same-size max pools with odd, increasing ``kernels`` (e.g. 5, 9, 13) of one NHWC input, each written
+    to its own destination; the input is read once."""
+    ints = [n, h, w, c, x_ld or c, x_n_stride, _bf(x), len(kernels)]
+    for k in range(len(kernels)):
+        ints += [kernels[k], (y_lds[k] if y_lds else c), (y_n_strides[k] if y_n_strides else 0)]
+    return _make_fused(2, [x] + list(outs), ints, name="spp_maxpool")
+
+
+def spp_fits(h: int, w: int, nk: int) -> bool:
+    return h * w * 16 * (1 + nk) <= 96 * 1024

@@ -23,6 +23,7 @@ class _NmsDesc(ctypes.Structure):
         ("max_keep", ctypes.c_int),
         ("out", ctypes.c_void_p), ("out_index", ctypes.c_void_p), ("out_num", ctypes.c_void_p),
         ("out_cap", ctypes.c_int), ("scores_t", ctypes.c_void_p),
+        ("lead", ctypes.c_void_p), ("tau", ctypes.c_void_p),
     ]
 
 
@@ -48,7 +49,7 @@ class MulticlassNMS:
 
     def __init__(self, boxes: torch.Tensor, scores: torch.Tensor, *, class_major: bool, score_threshold: float,
                  nms_threshold: float, nms_top_k: int = 1000, keep_top_k: int = 100, normalized: bool = True,
-                 background_label: int = -1):
+                 background_label: int = -1, prepass: bool = True):
         n, m, four = boxes.shape
         assert four == 4 and boxes.dtype == torch.float32 and boxes.is_contiguous()
         if class_major:
@@ -84,6 +85,14 @@ class MulticlassNMS:
         if not class_major and s_c == 1 and c > 1:
             self.scores_t = torch.empty(n, c, m, dtype=scores.dtype, device=dev)
             d.scores_t = self.scores_t.data_ptr()
+        # score-floor pre-pass (exact): worthwhile when the classes together can supply keep_top_k leading boxes
+        self.lead = self.tau = None
+        lead_n = _lib().fdb_nms_lead_per_class()
+        if prepass and keep_top_k > 0 and 2 * keep_top_k <= c * lead_n <= 4096:
+            self.lead = torch.zeros(n, c, lead_n, dtype=torch.float32, device=dev)
+            self.tau = torch.zeros(n, dtype=torch.float32, device=dev)
+            d.lead, d.tau = self.lead.data_ptr(), self.tau.data_ptr()
+        self.launches = 2 + (1 if self.scores_t is not None else 0) + (2 if self.tau is not None else 0)
         self.op = NativeOp(_lib().fdb_nms_create(ctypes.byref(d)), [boxes, scores, self], "multiclass_nms")
         self.op.keep = [boxes, scores]  # avoid a reference cycle through self
 

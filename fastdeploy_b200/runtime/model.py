@@ -54,6 +54,8 @@ class FastDeployModel:
     def infer(self, feeds: Dict[str, Any]) -> Dict[str, Any]:
         t0 = time.perf_counter() if self._record_time else 0.0
         outs = self.runtime._infer_dict(feeds)
+        if self.runtime.on_gpu:
+            self.runtime._check_status()      # a kernel that gave up on a bounded wait raises here, not later
         if self._record_time:
             if self.runtime.on_gpu:
                 import torch

@@ -176,6 +176,7 @@ class Lowering:
         self.cons = graph.consumers()
         self.prod = graph.producers()
         self.preassigned: Dict[str, Val] = {}
+        self.fused_away: set = set()        # ids of nodes that an earlier node's lowering has already covered
         self.input_shapes = {k: list(v) for k, v in input_shapes.items()}
 
     # ------------------------------------------------------------------ helpers
@@ -254,6 +255,8 @@ class Lowering:
             self.plan.inputs[vi.name] = v
         self._plan_concats()
         for node in g.nodes:
+            if id(node) in self.fused_away:
+                continue
             fn = getattr(self, "lower_" + node.op, None)
             done = False
             if fn is not None:
@@ -537,7 +540,49 @@ class Lowering:
     def lower_MaxPool(self, node: Node):
         if len(node.outputs) > 1 and node.outputs[1]:
             return False
+        if self._lower_spp(node):
+            return None
         return self._lower_pool(node, "max")
+
+    def _same_size_pool(self, node: Node):
+        """Kernel size of a stride-1 max pool that keeps the spatial size (odd k, pad k // 2), else 0."""
+        k = node.attr("kernel_shape")
+        if node.op != "MaxPool" or len(k) != 2 or k[0] != k[1] or k[0] % 2 == 0 or node.attr("ceil_mode", 0):
+            return 0
+        if list(node.attr("strides", [1, 1])) != [1, 1] or (len(node.outputs) > 1 and node.outputs[1]):
+            return 0
+        if any(d != 1 for d in node.attr("dilations", [1, 1])):
+            return 0
+        pads = node.attr("pads", [0, 0, 0, 0])
+        if node.attr("auto_pad", "NOTSET") not in ("NOTSET", "") or list(pads) != [k[0] // 2] * 4:
+            return 0
+        return k[0]
+
+    def _lower_spp(self, node: Node) -> bool:
+        """Spatial pyramid pooling: the stride-1 max pools that share this node's input become one launch."""
+        x_name = node.inputs[0]
+        if not self.is4d(x_name) or not self._same_size_pool(node):
+            return False
+        group = [c for c in self.cons.get(x_name, []) if self._same_size_pool(c) and id(c) not in self.fused_away]
+        group.sort(key=self._same_size_pool)
+        sizes = [self._same_size_pool(c) for c in group]
+        n, c, h, w = self.info.shapes[x_name]
+        if len(group) < 2 or len(group) > 3 or len(set(sizes)) != len(sizes) or not K.spp_fits(h, w, len(group)):
+            return False
+        x = self.as_nhwc(x_name)
+        cp = _round8(c)
+        outs = [self.out_nhwc(g.outputs[0]) for g in group]
+        if x.ld < cp or any(o.ld < cp for o in outs):
+            return False
+        op = K.spp_maxpool(x.t, [o.t for o in outs], sizes, n=n, h=h, w=w, c=cp, x_ld=x.ld, x_n_stride=x.n_stride,
+                           y_lds=[o.ld for o in outs], y_n_strides=[o.n_stride for o in outs])
+        self.plan.add_native(op, node)
+        op.launch()
+        for g, o in zip(group, outs):
+            self.vals[g.outputs[0]] = o
+            if g is not node:
+                self.fused_away.add(id(g))
+        return True
 
     def lower_AveragePool(self, node: Node):
         return self._lower_pool(node, "avg")
@@ -549,14 +594,62 @@ class Lowering:
         x = self.as_nhwc(x_name)
         n, c, h, w = x.logical_shape
         cp = _round8(c) if x.ld >= _round8(c) else c
-        y = self.out_nhwc(node.outputs[0])
-        splits = K.gap_splits(h * w, n, cp)
+        splits = K.gap_splits_v2(h * w, n, cp)
         scratch = torch.empty(n * splits * cp, dtype=torch.float32, device=self.device)
-        for op in K.global_avgpool(x.t, y.t, scratch, n=n, hw=h * w, c=cp, x_ld=x.ld, x_n_stride=x.n_stride,
-                                   splits=splits, out_ld=y.t.stride(0)):
-            self.plan.add_native(op, node)
+        part = K.gap_partial(x.t, scratch, n=n, hw=h * w, c=cp, x_ld=x.ld, x_n_stride=x.n_stride, splits=splits)
+        self.plan.add_native(part, node)
+        part.launch()
+        gate = self._ese_consumer(node, c, cp)
+        if gate is not None:
+            # squeeze-excite: the pooled vector only feeds a 1x1 convolution whose result scales a feature map;
+            # one kernel finishes the mean, applies the 1x1 weights, the bias and the activation
+            conv, wt, bias, cout = gate
+            y = self.new_nhwc(n, 1, 1, cout, torch.float32)
+            op = K.ese_gate(scratch, wt, bias, y.t, n=n, cin=cp, cout=cout, splits=splits, hw=h * w,
+                            act=conv.attr("activation", "none"), alpha=conv.attr("act_alpha", 0.0),
+                            beta=conv.attr("act_beta", 0.0), out_ld=y.t.stride(0))
+            op.keep += [wt, bias]
+            self.plan.add_native(op, conv)
             op.launch()
+            self.fused_away.add(id(conv))
+            self.vals[conv.outputs[0]] = y
+            return None
+        y = self.out_nhwc(node.outputs[0])
+        fin = K.make_simple(K.K_GAP_FINALIZE, [scratch, y.t], [n, cp, splits, K.dtype_code(y.t.dtype), y.t.stride(0)],
+                            [1.0 / (h * w)], name="gap_finalize")
+        self.plan.add_native(fin, node)
+        fin.launch()
         self.vals[node.outputs[0]] = y
+
+    def _ese_consumer(self, node: Node, c: int, cp: int):
+        """The 1x1 convolution that turns this pooled vector into a channel gate, if that is all it feeds."""
+        out = node.outputs[0]
+        cons = self.cons.get(out, [])
+        if len(cons) != 1 or out in self.g.output_names() or out in self.preassigned:
+            return None
+        conv = cons[0]
+        if conv.op not in ("FusedConv", "Conv") or conv.inputs[0] != out or conv.attr("group", 1) != 1:
+            return None
+        if len(conv.inputs) > 3 and conv.inputs[3]:
+            return None
+        w = self.g.initializers.get(conv.inputs[1])
+        if w is None or w.ndim != 4 or w.shape[2:] != (1, 1) or w.shape[1] != c:
+            return None
+        gate_out = conv.outputs[0]
+        users = self.cons.get(gate_out, [])
+        if not users or any(u.op != "Mul" for u in users) or gate_out in self.preassigned \
+                or gate_out in self.g.output_names() or conv.attr("activation", "none") == "gelu":
+            return None
+        cout = w.shape[0]
+        if cout % 8 != 0:
+            return None
+        key = (conv.inputs[1], f"gate{cp}")
+        if key not in self.packed:
+            wt = torch.zeros(cout, cp, dtype=self.dtype, device=self.device)
+            wt[:, :c] = torch.from_numpy(np.ascontiguousarray(w.reshape(cout, c))).to(self.device).to(self.dtype)
+            self.packed[key] = wt
+        bias = self.const_f32(conv.inputs[2]).float().contiguous() if len(conv.inputs) > 2 and conv.inputs[2] else None
+        return conv, self.packed[key], bias, cout
 
     def lower_Resize(self, node: Node):
         x_name = node.inputs[0]
@@ -724,7 +817,7 @@ class Lowering:
                             nms_threshold=node.attr("nms_threshold", 0.5), nms_top_k=node.attr("nms_top_k", 1000),
                             keep_top_k=node.attr("keep_top_k", 100), normalized=bool(node.attr("normalized", 1)),
                             background_label=node.attr("background_label", -1))
-        self.plan.add_native(nms.op, node, launches=3 if nms.scores_t is not None else 2)
+        self.plan.add_native(nms.op, node, launches=nms.launches)
         nms.launch()
         self.plan.extra.setdefault("nms", []).append(nms)
         n = boxes.shape[0]
@@ -747,7 +840,10 @@ class Lowering:
         a_total = sum(h * w for h, w in zip(gh, gw))
         n, c = self.info.shapes[node.inputs[0]][:2]
         rc = self.info.shapes[node.inputs[nl]][1]
-        scores = torch.zeros(n, a_total, _round8(c), dtype=torch.float32, device=self.device)
+        # class scores stay in the network's 16-bit type when that is fp16 (11 significant bits, what an fp16 engine
+        # yields); bf16 would leave 8 bits, too coarse to rank detections, so bf16 plans keep fp32 scores
+        score_dt = torch.float16 if self.dtype == torch.float16 else torch.float32
+        scores = torch.zeros(n, a_total, _round8(c), dtype=score_dt, device=self.device)
         regs = torch.zeros(n, a_total, _round8(rc), dtype=self.dtype, device=self.device)
         off = 0
         for i in range(nl):

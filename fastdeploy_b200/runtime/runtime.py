@@ -69,6 +69,9 @@ class Runtime:
         self._bound_outputs: Dict[str, torch.Tensor] = {}
         self._last_outputs: Dict[str, Any] = {}
         self._profile_time = 0.0
+        self._last_plan = None
+        self._status_host = None
+        self._status_event = None
         self.gpu_launches = 0
         self.on_gpu = self.option.device == Device.GPU
         if self.on_gpu:
@@ -146,7 +149,9 @@ class Runtime:
             names = [vi.name for vi in self.graph.inputs]
             data = dict(zip(names, data))
         outs = self._infer_dict(data)
-        return [self._to_numpy(outs[vi.name]) for vi in self.graph.outputs]
+        res = [self._to_numpy(outs[vi.name]) for vi in self.graph.outputs]
+        self._check_status()
+        return res
 
     def forward(self, *inputs) -> List[np.ndarray]:
         return self.infer(list(inputs))
@@ -168,6 +173,7 @@ class Runtime:
             with torch.cuda.device(self.device):
                 shapes = {vi.name: list(data[vi.name].shape) for vi in self.graph.inputs}
                 plan = self._plan_for(shapes)
+                self._last_plan = plan
                 prof = self.option.profiling
                 ev = None
                 if prof["enable"] and prof["include_h2d_d2h"]:
@@ -189,11 +195,25 @@ class Runtime:
                     plan.run()
                 self.gpu_launches += plan.native_kernel_launches
                 outs = self._collect_outputs(plan)
+                if self._status_host is None:
+                    self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+                    self._status_event = torch.cuda.Event()
+                plan.status.snapshot_async(self._status_host)
+                self._status_event.record(torch.cuda.current_stream(self.device))
                 if ev is not None:
                     ev[1].record()
                     torch.cuda.synchronize(self.device)
                     self._profile_time = ev[0].elapsed_time(ev[1]) / 1e3
                 return outs
+
+    def _check_status(self) -> None:
+        """Reads the device status word of the plan that just ran. Kernels report a bounded wait that ran out
+        (or a rejected shape) through this word instead of trapping, so every inference must look at it: the
+        device->host copies of the outputs have already synchronised the stream, the extra 4-byte read is free."""
+        plan = self._last_plan
+        if plan is not None and self._status_event is not None:
+            self._status_event.synchronize()
+            plan.status.check_snapshot(self._status_host, "inference")
 
     def _copy_in(self, dst, src) -> None:
         if isinstance(src, np.ndarray):
@@ -242,6 +262,8 @@ class Runtime:
             src = outs[name]
             src = torch.from_numpy(src) if isinstance(src, np.ndarray) else src
             dst.copy_(src.reshape(dst.shape))
+        if self.on_gpu:
+            self._check_status()
 
     def get_output_tensor(self, name: str):
         return self._last_outputs.get(name)

@@ -50,8 +50,10 @@ class Worker:
     """One device: pulls batches from its queue and runs ``batch_fn(model, [payload, ...]) -> [result, ...]``."""
 
     def __init__(self, index: int, model_factory: Callable[[int], Any], batch_fn: Callable[[Any, List[Any]], Sequence[Any]],
-                 max_batch_size: int, max_queue_delay_us: int, max_failures: int = 3):
+                 max_batch_size: int, max_queue_delay_us: int, max_failures: int = 3,
+                 on_death: Optional[Callable[["Worker"], None]] = None):
         self.index = index
+        self.on_death = on_death
         self.q: "queue.Queue[Optional[_Item]]" = queue.Queue()
         self.max_batch_size, self.delay_s = max_batch_size, max_queue_delay_us / 1e6
         self.batch_fn, self.max_failures = batch_fn, max_failures
@@ -111,6 +113,9 @@ class Worker:
                 self._consecutive_failures += 1
                 if self._consecutive_failures >= self.max_failures:
                     self.alive, self.error = False, e
+                    # whatever is still queued here must not wait for a later submit(): hand it back now
+                    if self.on_death is not None:
+                        self.on_death(self)
                     return
             finally:
                 self.stats.compute_s += time.perf_counter() - t0
@@ -127,12 +132,13 @@ class Worker:
 class Scheduler:
     def __init__(self, model_factory: Callable[[int], Any], batch_fn: Callable[[Any, List[Any]], Sequence[Any]],
                  num_workers: int = 1, max_batch_size: int = 8, max_queue_delay_us: int = 500, max_failures: int = 3):
-        self.workers = [Worker(i, model_factory, batch_fn, max_batch_size, max_queue_delay_us, max_failures)
-                        for i in range(num_workers)]
+        self._lock = threading.RLock()
+        self.workers: List[Worker] = []
+        self.workers = [Worker(i, model_factory, batch_fn, max_batch_size, max_queue_delay_us, max_failures,
+                               on_death=self._worker_died) for i in range(num_workers)]
         if not any(w.alive for w in self.workers):
             errs = "; ".join(f"worker {w.index}: {w.error!r}" for w in self.workers)
             raise RuntimeError("no worker could be started: " + errs)
-        self._lock = threading.Lock()
         self._closed = False
         self._rr = 0
 
@@ -153,6 +159,13 @@ class Scheduler:
             w = min(alive, key=lambda x: (x.pending(), (x.index - self._rr) % n))
             w.q.put(_Item(payload, fut))
         return fut
+
+    def _worker_died(self, worker: Worker) -> None:
+        """Called on the dying worker's own thread: its queued items move to the living workers (or fail when
+        none is left) right away. submit() may have picked this worker a moment before it died; such an item
+        lands in the dead queue afterwards and is caught by the reap at the next submit() or at close()."""
+        with self._lock:
+            self._reap()
 
     def _reap(self) -> None:
         """Moves the queued items of dead workers to the living ones."""
@@ -186,3 +199,12 @@ class Scheduler:
             self._closed = True
         for w in self.workers:
             w.stop()
+        with self._lock:
+            for w in self.workers:          # nothing may stay pending after close()
+                while True:
+                    try:
+                        it = w.q.get_nowait()
+                    except queue.Empty:
+                        break
+                    if it is not None and not it.future.done():
+                        it.future.set_exception(RuntimeError("scheduler is closed"))

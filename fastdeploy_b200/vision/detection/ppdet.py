@@ -261,6 +261,7 @@ class PPDetBase(FastDeployModel):
             self.postprocessor.apply_nms()
         self._slots: Dict[Tuple, List[_GpuSlot]] = {}
         self._slot_rr = 0
+        self.slots_in_flight = 3        # batches whose copies / compute / read-back may overlap
         self._copy_stream = None
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
@@ -297,6 +298,8 @@ class PPDetBase(FastDeployModel):
         from ...ops import preproc as P
         rt = self.runtime
         dev = rt.device
+        if not isinstance(images, (list, tuple)) and getattr(images, "ndim", 0) == 4:
+            images = [images[i] for i in range(images.shape[0])]      # one [N,H,W,3] batch buffer
         n = len(images)
         geo = [self.preprocessor.plan_image(int(im.shape[0]), int(im.shape[1])) for im in images]
         ch, cw = max(g["ch"] for g in geo), max(g["cw"] for g in geo)
@@ -310,10 +313,10 @@ class PPDetBase(FastDeployModel):
             nms = plan.extra["nms"][0]
             key = (tuple(sorted((k, tuple(v)) for k, v in shapes.items())), raw_bytes)
             if key not in self._slots:
-                self._slots[key] = [_GpuSlot(dev, raw_bytes, n, nms.out.shape[1]) for _ in range(2)]
+                self._slots[key] = [_GpuSlot(dev, raw_bytes, n, nms.out.shape[1]) for _ in range(self.slots_in_flight)]
             if self._copy_stream is None:
                 self._copy_stream = torch.cuda.Stream(dev)
-            self._slot_rr ^= 1
+            self._slot_rr = (self._slot_rr + 1) % len(self._slots[key])
             slot = self._slots[key][self._slot_rr]
             slot.done.synchronize()                 # the slot's previous batch has been read back
             compute = torch.cuda.current_stream(dev)
@@ -322,16 +325,34 @@ class PPDetBase(FastDeployModel):
             off = 0
             h2d = 0
             with torch.cuda.stream(self._copy_stream):
-                for i, (im, g) in enumerate(zip(images, geo)):
-                    t = im if isinstance(im, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(im))
+                tens = [im if isinstance(im, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(im))
+                        for im in images]
+                # Frames that sit back to back in one host (or device) buffer - a batch staged in one pinned
+                # allocation - travel as ONE copy: a copy per frame costs a launch each and keeps the link
+                # from streaming.
+                packed = n > 0 and all(t.is_contiguous() and t.dtype == torch.uint8 for t in tens) and all(
+                    tens[i + 1].data_ptr() == tens[i].data_ptr() + tens[i].numel() and
+                    tens[i + 1].device == tens[0].device for i in range(n - 1))
+                if packed:
+                    total = sum(t.numel() for t in tens)
+                    try:
+                        whole = torch.as_strided(tens[0].reshape(-1), (total,), (1,)) if n > 1 else tens[0].reshape(-1)
+                    except RuntimeError:      # the frames are separate storages that merely happen to be adjacent
+                        packed = False
+                if packed:
+                    slot.raw[:total].copy_(whole, non_blocking=True)
+                    if whole.device.type == "cpu":
+                        h2d += total
+                for i, (t, g) in enumerate(zip(tens, geo)):
                     flat = t.reshape(-1)
-                    slot.raw[off:off + flat.numel()].copy_(flat, non_blocking=True)
-                    if flat.device.type == "cpu":
-                        h2d += flat.numel()
-                    P.fill_meta(meta, i, src_offset=off, src_hw=(int(im.shape[0]), int(im.shape[1])),
-                                src_stride=int(im.shape[1]) * 3, resized_hw=(g["rh"], g["rw"]))
+                    if not packed:
+                        slot.raw[off:off + flat.numel()].copy_(flat, non_blocking=True)
+                        if flat.device.type == "cpu":
+                            h2d += flat.numel()
+                    P.fill_meta(meta, i, src_offset=off, src_hw=(int(t.shape[0]), int(t.shape[1])),
+                                src_stride=int(t.shape[1]) * 3, resized_hw=(g["rh"], g["rw"]))
                     slot.sf_host[i, 0], slot.sf_host[i, 1] = g["scale_factor"]
-                    off += (flat.numel() + 255) // 256 * 256
+                    off += flat.numel() if packed else (flat.numel() + 255) // 256 * 256
                 slot.meta_dev.copy_(slot.meta_host, non_blocking=True)
                 h2d += slot.meta_host.numel()
                 slot.copied.record(self._copy_stream)

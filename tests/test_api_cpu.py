@@ -75,3 +75,45 @@ def test_nms_reference_ties_and_topk():
     assert out[:, 1].tolist() == pytest.approx([0.9, 0.7, 0.95])
     assert out[:, 0].tolist() == [0, 0, 1]
     assert idx.tolist() == [0, 2, 4]
+
+
+def test_nonzero_device_status_raises_on_every_inference_path():
+    """A kernel that gives up on a bounded wait writes a code to the plan's status word instead of trapping;
+    ``Runtime.infer`` and ``FastDeployModel.infer`` must turn that into an exception for every model kind,
+    not only for graphs with padded NMS outputs. Driven with a fake plan: no GPU involved."""
+    import torch
+    from fastdeploy_b200.ops.base import StatusWord
+    from fastdeploy_b200.runtime.runtime import Runtime
+    from fastdeploy_b200.runtime.model import FastDeployModel
+
+    class FakeEvent:
+        def synchronize(self):
+            pass
+
+    class FakePlan:
+        def __init__(self):
+            self.status = StatusWord.__new__(StatusWord)
+            self.status.t = torch.zeros(1, dtype=torch.int32)
+
+    rt = Runtime.__new__(Runtime)
+    rt.on_gpu = True
+    rt._last_plan = FakePlan()
+    rt._status_event = FakeEvent()
+    rt._status_host = torch.zeros(1, dtype=torch.int32)
+    rt._check_status()                                  # zero word: fine
+    rt._status_host[0] = 4
+    with pytest.raises(RuntimeError, match="peer signal wait timed out"):
+        rt._check_status()
+
+    class Graph:
+        inputs, outputs = [], []
+    rt.graph = Graph()
+    rt._infer_dict = lambda data: {}
+    rt._status_host[0] = 2
+    with pytest.raises(RuntimeError, match="device status 2"):
+        rt.infer({})
+    m = FastDeployModel.__new__(FastDeployModel)
+    m.runtime, m._record_time = rt, False
+    rt._status_host[0] = 3
+    with pytest.raises(RuntimeError, match="epilogue wait timed out"):
+        m.infer({})

@@ -56,6 +56,35 @@ def test_failed_worker_leaves_rotation_and_requests_survive():
     s.close()
 
 
+def test_dying_worker_hands_its_queue_over_without_a_later_submit():
+    """Worker 0 dies with several requests still queued and nobody calls submit() afterwards: the queued
+    requests must still complete (on worker 1), because the dying worker drains its own queue."""
+    gate = threading.Event()
+
+    class Slow(FakeModel):
+        def run(self, xs):
+            if self.index == 0:
+                gate.wait(5)
+                raise RuntimeError("device 0 lost")
+            return super().run(xs)
+    s = Scheduler(lambda i: Slow(i), lambda m, xs: m.run(xs), num_workers=2, max_batch_size=1,
+                  max_queue_delay_us=0, max_failures=1)
+    futs = [s.submit(i) for i in range(8)]           # alternate between the two workers; worker 0 is stuck
+    time.sleep(0.05)
+    assert s.workers[0].pending() >= 2
+    gate.set()                                       # worker 0 fails its first request and dies
+    done = failed = 0
+    for f in futs:
+        try:
+            f.result(timeout=5)                      # would block for ever if the queue were left behind
+            done += 1
+        except RuntimeError:
+            failed += 1
+    assert failed == 1 and done == 7
+    assert not s.workers[0].alive
+    s.close()
+
+
 def test_all_workers_dead_is_an_error_not_a_hang():
     with pytest.raises(RuntimeError, match="no worker could be started"):
         Scheduler(lambda i: (_ for _ in ()).throw(RuntimeError("gone")), lambda m, xs: xs, num_workers=2)

@@ -73,3 +73,31 @@ def test_noalloc_rejects_oversize_and_bad_arguments():
     assert rc == 1                                   # channels not a multiple of 8
     rc = lib.fdb_global_avgpool_noalloc(None, out.data_ptr(), 1, 16, 8, 8, 0, 1, 0, 2, 8, stream)
     assert rc == 1
+    # host-side rejections, nothing is launched: an image stride that would misalign every image after the
+    # first, one shorter than an image, a row pitch below the channel count, an output type that does not exist
+    big = torch.zeros(4 * 16 * 16 + 64, device="cuda", dtype=torch.float16)
+    for args in ((2, 16, 8, 16, 16 * 16 + 4, 1, 0, 2, 8), (2, 16, 8, 16, 16 * 8, 1, 0, 2, 8),
+                 (2, 16, 8, 16, -256, 1, 0, 2, 8), (1, 16, 16, 8, 0, 1, 0, 2, 16), (1, 16, 8, 8, 0, 1, 0, 3, 8),
+                 (1, 16, 8, 8, 0, 1, 0, 2, 4)):
+        rc = lib.fdb_global_avgpool_noalloc(big.data_ptr(), out.data_ptr(), *args, stream)
+        assert rc == 1, args
+    assert b"x_n_stride" in lib.fdb_global_avgpool_noalloc_strerror(1)
+    rc = lib.fdb_global_avgpool_noalloc(big.data_ptr() + 2, out.data_ptr(), 1, 16, 8, 8, 0, 1, 0, 2, 8, stream)
+    assert rc == 1                                   # x not 16-byte aligned
+    torch.cuda.synchronize()
+
+
+def test_noalloc_with_padded_image_stride():
+    """Images that sit further apart than hw * x_ld (a batch carved out of a larger buffer)."""
+    lib = _lib()
+    torch.manual_seed(1)
+    n, hw, c, ld, splits = 3, 5 * 7, 32, 40, 3
+    stride = hw * ld + 64
+    buf = torch.randn(n * stride, device="cuda").to(torch.float16)
+    x = torch.as_strided(buf, (n, hw, c), (stride, ld, 1))
+    got = torch.zeros(n, c, device="cuda")
+    rc = lib.fdb_global_avgpool_noalloc(x.data_ptr(), got.data_ptr(), n, hw, c, ld, stride, splits, 0, 2, c,
+                                        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0, lib.fdb_global_avgpool_noalloc_strerror(rc)
+    torch.cuda.synchronize()
+    assert (got - x.float().mean(1)).abs().max().item() <= 2e-3
