@@ -44,8 +44,8 @@ def main() -> int:
     ap.add_argument("--model-dir", default="")
     ap.add_argument("--latency-iters", type=int, default=50)
     ap.add_argument("--skip-latency", action="store_true")
-    ap.add_argument("--scheduler-mode", action="store_true",
-                    help="also drive all N GPUs from ONE process through serving.Scheduler (extra key)")
+    ap.add_argument("--no-scheduler-mode", action="store_true",
+                    help="ppyoloe: skip the extra run that drives all N GPUs from ONE process through serving.Scheduler")
     ap.add_argument("--dtype", default="", help="vit_tp: bf16 | fp8")
     args = ap.parse_args()
 

@@ -64,7 +64,7 @@ struct ConvGemmDesc {
   // elements between image rows (0 = W * ld): lets heads of a [B, S, H*D] tensor act as image rows
   long long x_h_stride, y_h_stride, res_h_stride;
   int y_tma_mode;        // -1/1: TMA tensor stores for 16-bit outputs when possible, 0: direct stores
-  long long* trace;      // optional device buffer of 32*12 int64 for the timeline probe (null = off)
+  long long* trace;      // optional device buffer of 2*32*12 int64 for the timeline probe (null = off)
   // Tensor parallelism over peer memory (plain GEMMs only: 1x1, one image row of W = M rows).
   //   peer_mode 1, all-gather -> GEMM: the M rows of A live in peer_world equal shards of peer_rows
   //     rows; shard r is read straight from peer_ptrs[r] (this rank's own shard included) by TMA.
@@ -83,6 +83,9 @@ struct ConvGemmDesc {
   // the epilogue, scale_a per output row (pixel / token), scale_b per output channel; either may be null.
   const float* scale_a;
   const float* scale_b;
+  // CTA pairs (cta_group::2): -1 choose, 0 never, 1 force. A pair computes two 128-row tiles of the same
+  // column tile with one M = 256 MMA; each CTA stages half of the weight tile.
+  int pair_mode;
 };
 
 // Device-resident table of the peers' tensor maps and counters (host-written before any launch).
@@ -125,6 +128,8 @@ struct ConvGemmParams {
   const uint8_t* peer_src[8];     // every rank's gathered buffer (rank r's shard is valid in its own)
   long long gather_row_bytes;     // bytes per row of A
   long long* trace;  // optional: CTA 0 records clock64() at pipeline events of its first tiles
+  int pair;          // launched as clusters of two CTAs that share every MMA
+  int n_images;      // N: tiles decoded to an image index past it are padding of an odd tile count (pairs)
 };
 
 // Tile index -> (column tile, tile column, tile row, image). Integer division by the three runtime
@@ -148,6 +153,20 @@ __device__ __forceinline__ TileCoord decode_tile(const ConvGemmParams& p, int ti
   return c;
 }
 
+// Work item -> tile index. Without pairs they are the same. A CTA pair takes item v as the two
+// consecutive pixel tiles 2m, 2m + 1 of column tile v % n_tiles (m = v / n_tiles), one per CTA; with an
+// odd number of pixel tiles the last item's second tile decodes to an image index past the batch: its
+// loads read zero fill and its stores are skipped.
+__device__ __forceinline__ int work_first(const ConvGemmParams& p) {
+  return p.pair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+}
+__device__ __forceinline__ int work_tile(const ConvGemmParams& p, int v, uint32_t rank) {
+  if (!p.pair) return v;
+  const uint32_t m = fast_div(static_cast<uint32_t>(v), p.mul_n);
+  const uint32_t nt = static_cast<uint32_t>(v) - m * static_cast<uint32_t>(p.n_tiles);
+  return static_cast<int>((2u * m + rank) * static_cast<uint32_t>(p.n_tiles) + nt);
+}
+
 // Timeline probe for tuning (32 tiles of CTA 0): slot layout [tile][12]: 0 producer issue, 1 MMA got accumulator,
 // 2 MMA first operands ready, 3 MMA committed, 4 epilogue saw accumulator, 5 epilogue TMEM read done,
 // 6 epilogue released accumulator, 7 epilogue store issued, 8 epilogue warps met, 9 TMEM data
@@ -155,7 +174,9 @@ __device__ __forceinline__ TileCoord decode_tile(const ConvGemmParams& p, int ti
 constexpr int kTraceTiles = 32;
 constexpr int kTraceSlots = 12;
 __device__ __forceinline__ void trace_mark(const ConvGemmParams& p, int local_tile, int slot) {
-  if (p.trace != nullptr && blockIdx.x == 0 && local_tile < kTraceTiles) p.trace[local_tile * kTraceSlots + slot] = clock64();
+  // CTAs 0 and 1 (the two halves of the first pair) each fill their own kTraceTiles x kTraceSlots block
+  if (p.trace != nullptr && blockIdx.x < 2 && local_tile < kTraceTiles)
+    p.trace[(blockIdx.x * kTraceTiles + local_tile) * kTraceSlots + slot] = clock64();
 }
 
 // erf-form GELU, 0.5 x (1 + erf(x / sqrt 2)), with erf from the five-term rational-exponential fit
@@ -436,7 +457,7 @@ __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParam
 // the arithmetic. Columns past Cout carry padding that the TMA store clips.
 template <int ACT, bool BF16, bool RES>
 __device__ __forceinline__ void staged_chunk(const uint32_t (&v)[32], const float* bias_s, const uint4 (&rpre)[4],
-                                             uint32_t srow, uint32_t chunk0, uint32_t row7, const ConvGemmParams& p) {
+                                             uint32_t srow, uint32_t row_sw, const ConvGemmParams& p) {
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     const float4 b0 = *reinterpret_cast<const float4*>(bias_s + g * 8);
@@ -463,7 +484,7 @@ __device__ __forceinline__ void staged_chunk(const uint32_t (&v)[32], const floa
       w[0] = add2(w[0], rpre[g].x, BF16); w[1] = add2(w[1], rpre[g].y, BF16);
       w[2] = add2(w[2], rpre[g].z, BF16); w[3] = add2(w[3], rpre[g].w, BF16);
     }
-    const uint32_t addr = srow + (((chunk0 + g) ^ row7) << 4);
+    const uint32_t addr = srow + ((static_cast<uint32_t>(g) ^ row_sw) << 4);   // 64-byte rows, 64-byte swizzle
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]));
   }
 }
@@ -471,47 +492,44 @@ __device__ __forceinline__ void staged_chunk(const uint32_t (&v)[32], const floa
 // Epilogue role shared by the convolution kernels: drains the double-buffered TMEM
 // accumulators tile by tile. `tfull0` / `tempty0` are the shared-memory addresses of
 // tmem_full[0] and tmem_empty[0]; index 1 of each follows 8 bytes later.
-constexpr int kStageTileBytes = kBM * 128;      // one 128-row x 64-channel (16-bit) output block
-constexpr int kStagingBytes = 2 * kStageTileBytes;
+constexpr int kChunkCols = 32;                        // output columns per staged chunk (one tcgen05.ld)
+constexpr int kChunkBytes = kBM * kChunkCols * 2;     // 128 rows x 32 channels (16-bit) = 8 KB
+constexpr int kStagingBytes = 4 * kChunkBytes;        // two chunk buffers for each half of the epilogue warps
 
-// Output path for 16-bit results. The eight epilogue warps form two teams of four; team t owns
-// accumulator t, i.e. every second tile of the CTA, so two tiles drain at the same time and the
-// per-tile latency chain (wait, TMEM load, activation, staging, store issue) is paid at half rate.
-// Within a team each thread owns one accumulator row: it walks the tile's columns in 64-channel
-// blocks, assembles each block in the team's staging buffer (128-byte swizzled rows) and the team
-// leader hands it to a TMA tensor store, which writes whole lines and clips ragged tile edges and
-// channel tails. Named barrier 1 + t (128 threads) keeps the team in step.
-constexpr int kTeamWarps = 4;
+// Output path for 16-bit results. All eight epilogue warps drain ONE tile together, so an accumulator
+// goes back to the MMA issuer after half the time two independent four-warp teams would hold it (the
+// accumulator cycle - MMA, then drain - is what bounds narrow layers). Warps w and w + 4 read the same
+// TMEM lane quarter and take alternate 32-column chunks; each thread owns one accumulator row. A chunk
+// is assembled in one of the half's two staging buffers (64-byte rows, 64-byte swizzle) and handed to a
+// TMA tensor store by the half's leader, which writes whole lines and clips ragged tile edges and channel
+// tails; with two buffers the next chunk is staged while the previous store still reads shared memory.
+// Named barrier 1 + half (128 threads) keeps a half in step.
 template <int BN, int ACT>
 __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const CUtensorMap* tmY, uint32_t stage0,
                                                   uint32_t tmem_base, uint32_t tfull0, uint32_t tempty0,
                                                   volatile int* abort_flag, float* s_bias, int warp, int lane) {
   const int q = warp & 3;                       // TMEM lane quarter this warp may read
-  const int team = (warp - 2) >> 2;
+  const int half = (warp - 2) >> 2;
   const bool leader_warp = ((warp - 2) & 3) == 0;
   const bool issuer = leader_warp && lane == 0;
   const bool in_bf16 = p.in_bf16 != 0;
-  const int et = static_cast<int>(threadIdx.x) - 64;   // index among the 256 epilogue threads
-  const int tt = et - team * 128;                      // index within the team
+  const int tt = static_cast<int>(threadIdx.x) - 64 - half * 128;   // index within the half
   const int row = q * 32 + lane;
   const int rh = row / p.tw, rw = row - rh * p.tw;
   const bool out_bf16 = p.out_dtype == kBF16;
   // after-activation residual rows can be fetched while the accumulator is still being produced
   const bool res_pre = p.res_mode == 2 && p.res_vec != 0 && in_bf16 == out_bf16;
   const bool simple = (p.res_mode == 0 || res_pre) && !p.fp8;   // everything else takes the general per-group path
-  const uint32_t buf = stage0 + team * kStageTileBytes;
-  const uint32_t tfull = tfull0 + 8u * team, tempty = tempty0 + 8u * team;
-  const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + team * BN;
-  volatile int* abort_sample = abort_flag + 1 + team;
-  uint32_t acc_ph = 0;
+  const uint32_t buf0 = stage0 + half * (2 * kChunkBytes);
+  const uint32_t row_sw = static_cast<uint32_t>((row >> 1) & 3);
+  volatile int* abort_sample = abort_flag + 1 + half;
   bool aborted = false;
-  // Bias lives in shared memory: the whole vector once when one column tile covers Cout, else the
-  // team's slice for its current tile. A barrier publishes it before it is read.
+  uint32_t par = 0;                             // staging buffer of this half's next chunk
+  float* bias_s = s_bias + half * 256;          // each half keeps the bias slice of the current column tile
   if (p.n_tiles == 1) {
-    if (et < BN) s_bias[et] = (p.bias != nullptr && et < p.Cout) ? __ldg(p.bias + et) : 0.f;
-    asm volatile("bar.sync 3, 256;" ::: "memory");
+    for (int i = tt; i < BN; i += 128) bias_s[i] = (p.bias != nullptr && i < p.Cout) ? __ldg(p.bias + i) : 0.f;
+    asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
   }
-  const float* bias_s = p.n_tiles == 1 ? s_bias : s_bias + team * 256;
   unsigned int* pending_counter = nullptr;   // issuer only: stores of the previous tile not yet signalled
   unsigned pending_stores = 0;
   auto flush_signal = [&]() {
@@ -524,11 +542,16 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
       pending_stores = 0;
     }
   };
-  for (int it = team; !aborted; it += 2) {
-    const long long tile_ll = static_cast<long long>(blockIdx.x) + static_cast<long long>(it) * p.gemm_ctas;
+  const uint32_t pair_rank = p.pair ? cluster_ctarank() : 0u;
+  for (int it = 0; !aborted; ++it) {
+    const long long tile_ll = static_cast<long long>(work_first(p)) + static_cast<long long>(it) * p.gemm_ctas;
     if (tile_ll >= p.total_tiles) break;
     if (issuer) flush_signal();
-    const int tile = static_cast<int>(tile_ll);
+    const int acc = it & 1;
+    const uint32_t acc_ph = static_cast<uint32_t>(it >> 1) & 1u;
+    const uint32_t tfull = tfull0 + 8u * acc, tempty = tempty0 + 8u * acc;
+    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+    const int tile = work_tile(p, static_cast<int>(tile_ll), pair_rank);
     const TileCoord tc = decode_tile(p, tile);
     const int n_tile = tc.n_tile, thi = tc.thi, img = tc.img;
     int twi = tc.twi;
@@ -537,98 +560,94 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
       if (twi >= p.tiles_w) twi -= p.tiles_w;
     }
     const int oh = thi * p.th + rh, ow = twi * p.tw + rw;
-    const bool valid = rh < p.th && oh < p.Ho && ow < p.Wo;
+    const bool real_tile = img < p.n_images;
+    const bool valid = rh < p.th && oh < p.Ho && ow < p.Wo && real_tile;
     const uint8_t* rrow = reinterpret_cast<const uint8_t*>(p.residual) +
                           (static_cast<size_t>(img) * p.res_n_stride + static_cast<size_t>(oh) * p.res_h_stride +
                            static_cast<size_t>(ow) * p.res_ld) * 2;
     const int colbase = n_tile * BN;
     const int col_limit = min(p.Cout, colbase + BN);
-    const int nblk = (col_limit - colbase + 63) / 64;
+    const int nchunks = (col_limit - colbase + kChunkCols - 1) / kChunkCols;
     const float row_scale = (p.fp8 && p.scale_a != nullptr && valid)
                                 ? __ldg(p.scale_a + (static_cast<long long>(img) * p.Ho + oh) * p.Wo + ow) : 1.f;
     if (p.n_tiles > 1) {
-      float* dst = s_bias + team * 256;
-      for (int i = tt; i < BN; i += 128) dst[i] = (p.bias != nullptr && colbase + i < p.Cout) ? __ldg(p.bias + colbase + i) : 0.f;
+      // the previous tile's chunks of this half were all staged before its last barrier, so the slice is free
+      for (int i = tt; i < BN; i += 128) bias_s[i] = (p.bias != nullptr && colbase + i < p.Cout) ? __ldg(p.bias + colbase + i) : 0.f;
     }
-    for (int blk = 0; blk < nblk; ++blk) {
-      const int co0 = colbase + blk * 64;
-      uint4 rpre[8];
+    // The leader warp waits for the accumulator; the other warps sleep at the named barrier, which wakes
+    // them faster than separate polls would. Every half waits here, also one without a chunk in this tile:
+    // it may only hand the accumulator back once the tile exists, or its arrivals would run ahead into the
+    // accumulator's next phase.
+    if (leader_warp) {
+      mbar_wait(tfull, acc_ph, abort_flag, kStatusTimeoutEpilogue);
+      if (issuer) trace_mark(p, it, 4);
+      if (lane == 0) *abort_sample = *abort_flag;
+    }
+    asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+    if (*abort_sample != 0) { aborted = true; break; }
+    tc_fence_after();
+    for (int c = half; c < nchunks; c += 2) {
+      const int co0 = colbase + c * kChunkCols;
+      uint4 rpre[4];
 #pragma unroll
-      for (int g = 0; g < 8; ++g) rpre[g] = make_uint4(0, 0, 0, 0);
+      for (int g = 0; g < 4; ++g) rpre[g] = make_uint4(0, 0, 0, 0);
       if (res_pre && valid) {
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
+        for (int g = 0; g < 4; ++g) {
           // a ragged last group still reads 16 bytes: the row pitch is a multiple of 8 elements and
           // columns past Cout are clipped by the store
           if (co0 + g * 8 < col_limit) rpre[g] = *reinterpret_cast<const uint4*>(rrow + (co0 + g * 8) * 2);
         }
       }
-      // The leader warp waits for the accumulator; the other warps sleep at the named barrier, which
-      // wakes them faster than separate polls would. The same thread makes sure that the previous
-      // block has been read out of the staging buffer and samples the abort flag for the team,
-      // because warps that meet at barriers must all leave together.
-      if (leader_warp) {
-        if (blk == 0) {
-          mbar_wait(tfull, acc_ph, abort_flag, kStatusTimeoutEpilogue);
-          if (issuer) trace_mark(p, it, 4);
-        }
+      uint32_t v[32];
+      tmem_ld_32x32(t_row + c * kChunkCols, v);
+      tmem_ld_wait_dep(v);
+      if (issuer && c + 2 >= nchunks) trace_mark(p, it, 9);
+      const bool last = c + 2 >= nchunks;
+      if (last) {        // this half's last TMEM read of the accumulator
+        tc_fence_before();
+        __syncwarp();
         if (lane == 0) {
-          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-          *abort_sample = *abort_flag;
+          if (pair_rank != 0) mbar_arrive_remote(tempty, 0);   // the MMA issuer lives in the even CTA
+          else mbar_arrive(tempty);
         }
+        if (issuer) trace_mark(p, it, 6);
       }
-      asm volatile("bar.sync %0, 128;" ::"r"(1 + team) : "memory");
-      if (*abort_sample != 0) { aborted = true; break; }
-      if (blk == 0) tc_fence_after();
-      if (issuer && blk == nblk - 1) trace_mark(p, it, 8);
-      const uint32_t srow = buf + row * 128;
-      const uint32_t row7 = static_cast<uint32_t>(row & 7);
+      // buffer `par` is free: the store that last read it was waited for before the previous chunk's barrier
+      const uint32_t buf = buf0 + par * kChunkBytes;
+      const uint32_t srow = buf + row * 64;
+      if (valid) {
+        const float* bs = bias_s + c * kChunkCols;
+        if (simple) {
+          if (out_bf16) {
+            if (res_pre) staged_chunk<ACT, true, true>(v, bs, rpre, srow, row_sw, p);
+            else staged_chunk<ACT, true, false>(v, bs, rpre, srow, row_sw, p);
+          } else {
+            if (res_pre) staged_chunk<ACT, false, true>(v, bs, rpre, srow, row_sw, p);
+            else staged_chunk<ACT, false, false>(v, bs, rpre, srow, row_sw, p);
+          }
+        } else {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int c = blk * 2 + h;                 // 32-column TMEM chunk
-        if (co0 + h * 32 < col_limit) {
-          uint32_t v[32];
-          tmem_ld_32x32(t_row + c * 32, v);
-          tmem_ld_wait_dep(v);
-          if (issuer && blk == nblk - 1 && h == 0) trace_mark(p, it, 9);
-          if (valid) {
-            const uint32_t chunk0 = static_cast<uint32_t>(h * 4);
-            const float* bs = bias_s + c * 32;
-            const uint4(&rp)[4] = *reinterpret_cast<const uint4(*)[4]>(&rpre[h * 4]);
-            if (simple) {
-              if (out_bf16) {
-                if (res_pre) staged_chunk<ACT, true, true>(v, bs, rp, srow, chunk0, row7, p);
-                else staged_chunk<ACT, true, false>(v, bs, rp, srow, chunk0, row7, p);
-              } else {
-                if (res_pre) staged_chunk<ACT, false, true>(v, bs, rp, srow, chunk0, row7, p);
-                else staged_chunk<ACT, false, false>(v, bs, rp, srow, chunk0, row7, p);
-              }
-            } else {
-#pragma unroll
-              for (int g = 0; g < 4; ++g) {
-                epilogue8<ACT>(v + g * 8, p, co0 + h * 32 + g * 8, col_limit, nullptr, rrow, in_bf16, 2,
-                               srow + (((chunk0 + g) ^ row7) << 4), bs + g * 8, false, make_uint4(0, 0, 0, 0), row_scale);
-              }
-            }
+          for (int g = 0; g < 4; ++g) {
+            epilogue8<ACT>(v + g * 8, p, co0 + g * 8, col_limit, nullptr, rrow, in_bf16, 2,
+                           srow + ((static_cast<uint32_t>(g) ^ row_sw) << 4), bs + g * 8, false, make_uint4(0, 0, 0, 0), row_scale);
           }
         }
       }
-      if (blk == nblk - 1) {        // last TMEM read of this accumulator
-        if (issuer) trace_mark(p, it, 5);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tempty);
-        if (issuer) trace_mark(p, it, 6);
-      }
+      if (issuer && last) trace_mark(p, it, 5);
       fence_proxy_async_smem();
-      asm volatile("bar.sync %0, 128;" ::"r"(1 + team) : "memory");
-      if (issuer) {
-        if (blk == nblk - 1) trace_mark(p, it, 10);
+      // One barrier per chunk: behind it the chunk is complete in shared memory, and - because the issuer
+      // first waits for every earlier store to have read its buffer - the other buffer is free for the
+      // next chunk.
+      if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+      if (issuer && real_tile) {
+        if (last) trace_mark(p, it, 10);
         if (p.peer_mode == 2) {
-          // reduce-scatter: the block goes to the rank that owns these rows, into this rank's slot
-          const int row = twi * p.tw;
-          const int owner = row / p.peer_rows;
-          const int local = row - owner * p.peer_rows;
+          // reduce-scatter: the chunk goes to the rank that owns these rows, into this rank's slot
+          const int grow = twi * p.tw;
+          const int owner = grow / p.peer_rows;
+          const int local = grow - owner * p.peer_rows;
           asm volatile(
               "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
                   reinterpret_cast<uint64_t>(&p.peer->maps[owner])),
@@ -636,8 +655,8 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
               : "memory");
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           // The signal may only follow the data, and waiting for a remote store to complete takes
-          // microseconds: the wait is deferred to the start of this team's next tile (or the end of
-          // the kernel), where it overlaps the tensor-core work of the tiles in between.
+          // microseconds: the wait is deferred to the start of the next tile (or the end of the kernel),
+          // where it overlaps the tensor-core work of the tiles in between.
           pending_counter = p.peer->counters[owner] + local / kBM;
           ++pending_stores;
         } else {
@@ -648,10 +667,18 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
               : "memory");
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
-        if (blk == nblk - 1) trace_mark(p, it, 7);
+        if (last) trace_mark(p, it, 7);
+      }
+      par ^= 1;
+    }
+    if (half >= nchunks) {   // nothing to drain in this tile: hand the accumulator back at once
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (pair_rank != 0) mbar_arrive_remote(tempty, 0);
+        else mbar_arrive(tempty);
       }
     }
-    acc_ph ^= 1;
   }
   if (issuer) {
     flush_signal();
@@ -675,7 +702,9 @@ __device__ __forceinline__ void epilogue_loop(const ConvGemmParams& p, uint32_t 
   const int out_es = p.out_dtype == kF32 ? 4 : 2;
   int acc = 0;
   uint32_t acc_ph = 0;
-  for (int tile = blockIdx.x; tile < p.total_tiles; tile += p.gemm_ctas) {
+  const uint32_t pair_rank = p.pair ? cluster_ctarank() : 0u;
+  for (int v = work_first(p); v < p.total_tiles; v += p.gemm_ctas) {
+    const int tile = work_tile(p, v, pair_rank);
     const TileCoord tc = decode_tile(p, tile);
     const int n_tile = tc.n_tile, thi = tc.thi, img = tc.img;
     int twi = tc.twi;
@@ -688,7 +717,7 @@ __device__ __forceinline__ void epilogue_loop(const ConvGemmParams& p, uint32_t 
     const int row = q * 32 + lane;
     const int rh = row / p.tw, rw = row - rh * p.tw;
     const int oh = thi * p.th + rh, ow = twi * p.tw + rw;
-    const bool valid = rh < p.th && oh < p.Ho && ow < p.Wo;
+    const bool valid = rh < p.th && oh < p.Ho && ow < p.Wo && img < p.n_images;
     uint8_t* yrow = reinterpret_cast<uint8_t*>(p.y) +
                     (static_cast<size_t>(img) * p.y_n_stride + static_cast<size_t>(oh) * p.y_h_stride +
                      static_cast<size_t>(ow) * p.y_ld) * out_es;
@@ -730,7 +759,10 @@ __device__ __forceinline__ void epilogue_loop(const ConvGemmParams& p, uint32_t 
     }
     tc_fence_before();
     __syncwarp();
-    if (lane == 0) mbar_arrive(tempty_bar(acc));
+    if (lane == 0) {
+      if (pair_rank != 0) mbar_arrive_remote(tempty_bar(acc), 0);
+      else mbar_arrive(tempty_bar(acc));
+    }
     acc ^= 1;
     if (acc == 0) acc_ph ^= 1;
   }
@@ -742,11 +774,12 @@ constexpr int kBarBytes = 256;
 
 constexpr int next_pow2_cols(int c) { return c <= 32 ? 32 : c <= 64 ? 64 : c <= 128 ? 128 : c <= 256 ? 256 : 512; }
 
-template <int BN>
+template <int BN, bool PAIR = false>
 struct KernelCfg {
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N must be a multiple of 16 up to 256");
   static constexpr int kABytes = kBM * kBK * 2;
-  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kBRows = PAIR ? BN / 2 : BN;      // weight rows staged by this CTA
+  static constexpr int kBBytes = kBRows * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStagesFit = (kMaxSmem - kBarBytes - 1024 - kStagingBytes) / kStageBytes;
   static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
@@ -754,11 +787,12 @@ struct KernelCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarBytes + 1024;  // +1024: alignment slack
 };
 
-template <int BN, int ACT>
+template <int BN, int ACT, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmY, const ConvGemmParams p) {
-  using Cfg = KernelCfg<BN>;
+  using Cfg = KernelCfg<BN, PAIR>;
+  const uint32_t pair_rank = PAIR ? cluster_ctarank() : 0u;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(16) float s_bias[kBiasFloats];
@@ -785,7 +819,8 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), p.y_tma ? kTeamWarps : kEpiWarps);
+      // a pair's accumulator is handed back by the epilogue warps of both CTAs
+      mbar_init(tempty_bar(a), kEpiWarps * (PAIR ? 2 : 1));
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -793,15 +828,16 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     prefetch_tensormap(&tmB);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
-    tmem_relinquish();
+    if (PAIR) { tmem_alloc_pair(smem_u32(tmem_slot), Cfg::kTmemCols); tmem_relinquish_pair(); }
+    else { tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols); tmem_relinquish(); }
   }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer's barriers exist before anything signals them
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (blockIdx.x >= p.gemm_ctas) {
+  if (!PAIR && blockIdx.x >= p.gemm_ctas) {
     // ------------------------------------------------------------ copier CTA (all-gather -> GEMM)
     // Pulls the remote shards of A over NVLink into this rank's gathered buffer, one 128-row block
     // at a time in the order the GEMM CTAs will want them, and publishes a flag per block. Each
@@ -837,11 +873,13 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t ph = 0;
       uint32_t armed = 0, armed_parity = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += p.gemm_ctas) {
+      int item = 0;
+      for (int v = work_first(p); ok && v < p.total_tiles; v += p.gemm_ctas, ++item) {
+        const int tile = work_tile(p, v, pair_rank);
         const TileCoord tc = decode_tile(p, tile);
         const int n_tile = tc.n_tile, thi = tc.thi, img = tc.img;
         int twi = tc.twi;
-        if (p.peer_mode == 1) {
+        if (!PAIR && p.peer_mode == 1) {
           // local rows first, then the shards in the order the copier CTAs bring them in
           twi += p.peer_rot;
           if (twi >= p.tiles_w) twi -= p.tiles_w;
@@ -864,7 +902,7 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         const int x0 = twi * p.tw * p.stride - p.pad_w;
         const int y0 = thi * p.th * p.stride - p.pad_h;
-        trace_mark(p, (tile - blockIdx.x) / p.gemm_ctas, 0);
+        trace_mark(p, item, 0);
         int kcol = 0;
         for (int kh = 0; ok && kh < p.KH; ++kh) {
           for (int kw = 0; ok && kw < p.KW; ++kw) {
@@ -873,15 +911,27 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 ok = false;
                 break;
               }
-              mbar_arrive_expect_tx(full_bar(s), p.a_bytes + Cfg::kBBytes);
-              armed |= 1u << s;
-              armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
               const uint32_t a_dst = tile0 + s * Cfg::kStageBytes;
-              tma_load_4d(a_dst, &tmA, full_bar(s), kb * p.kblk, x0 + kw, y0 + kh, img);
-              if (p.b_batched)
-                tma_load_4d(a_dst + Cfg::kABytes, &tmB, full_bar(s), kcol, n_tile * BN, thi * p.th, img);
-              else
-                tma_load_2d(a_dst + Cfg::kABytes, &tmB, full_bar(s), kcol, n_tile * BN);
+              if (PAIR) {
+                // Both CTAs' bytes complete on the even CTA's barrier, which alone is armed (for both).
+                if (pair_rank == 0) {
+                  mbar_arrive_expect_tx(full_bar(s), 2u * (p.a_bytes + Cfg::kBBytes));
+                  armed |= 1u << s;
+                  armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
+                }
+                tma_load_4d_pair(a_dst, &tmA, full_bar(s), kb * p.kblk, x0 + kw, y0 + kh, img);
+                tma_load_2d_pair(a_dst + Cfg::kABytes, &tmB, full_bar(s), kcol,
+                                 n_tile * BN + static_cast<int>(pair_rank) * Cfg::kBRows);
+              } else {
+                mbar_arrive_expect_tx(full_bar(s), p.a_bytes + Cfg::kBBytes);
+                armed |= 1u << s;
+                armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
+                tma_load_4d(a_dst, &tmA, full_bar(s), kb * p.kblk, x0 + kw, y0 + kh, img);
+                if (p.b_batched)   // 1: one matrix per (image row, image); 2: one matrix per image
+                  tma_load_4d(a_dst + Cfg::kABytes, &tmB, full_bar(s), kcol, n_tile * BN, p.b_batched == 2 ? 0 : thi * p.th, img);
+                else
+                  tma_load_2d(a_dst + Cfg::kABytes, &tmB, full_bar(s), kcol, n_tile * BN);
+              }
               if (++s == S) { s = 0; ph ^= 1; }
             }
           }
@@ -906,7 +956,7 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // are needed. No tcgen05 fence follows them: operands arrive through the async proxy (TMA
     // complete_tx), and an accumulator is only handed back after the epilogue's tcgen05.wait::ld,
     // so its reads have finished before the arrive that this thread observes.
-    if (elect_one()) {
+    if (pair_rank == 0 && elect_one()) {   // in a pair only the even CTA issues; its MMAs drive both tensor cores
       int s = 0;
       uint32_t ph = 0;
       int acc = 0;
@@ -914,7 +964,7 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       const uint64_t desc_hi = make_kmajor_desc(0, 128);
       int it = 0;
-      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += p.gemm_ctas, ++it) {
+      for (int v = work_first(p); ok && v < p.total_tiles; v += p.gemm_ctas, ++it) {
         if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, kStatusTimeoutMma)) break;
         trace_mark(p, it, 1);
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -930,13 +980,19 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t a_addr = tile0 + s * Cfg::kStageBytes;
           const uint64_t adesc = desc_hi | ((a_addr & 0x3FFFF) >> 4);
           const uint64_t bdesc = desc_hi | (((a_addr + Cfg::kABytes) & 0x3FFFF) >> 4);
-          if (p.fp8) umma_f8_ksteps(d_tmem, adesc, bdesc, p.idesc, k != 0 ? 1u : 0u, ksteps);
-          else umma_f16_ksteps(d_tmem, adesc, bdesc, p.idesc, k != 0 ? 1u : 0u, ksteps);
-          umma_commit(empty_bar(s));
+          if (PAIR) {
+            umma_f16_ksteps_pair(d_tmem, adesc, bdesc, p.idesc, k != 0 ? 1u : 0u, ksteps);
+            umma_commit_pair(empty_bar(s));      // frees the stage in both CTAs
+          } else {
+            if (p.fp8) umma_f8_ksteps(d_tmem, adesc, bdesc, p.idesc, k != 0 ? 1u : 0u, ksteps);
+            else umma_f16_ksteps(d_tmem, adesc, bdesc, p.idesc, k != 0 ? 1u : 0u, ksteps);
+            umma_commit(empty_bar(s));
+          }
           if (++s == S) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
-        umma_commit(tfull_bar(acc));
+        if (PAIR) umma_commit_pair(tfull_bar(acc));
+        else umma_commit(tfull_bar(acc));
         trace_mark(p, it, 3);
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1;
@@ -952,11 +1008,15 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   // ------------------------------------------------------------ teardown
   tc_fence_before();
-  __syncthreads();
+  // A pair leaves together: the even CTA's MMAs read the odd CTA's shared memory and signal its barriers
+  // until the last tile has been drained on both sides.
+  if (PAIR) cluster_sync_all();
+  else __syncthreads();
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    if (PAIR) tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    else tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
   if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, *abort_flag);
 }
@@ -981,12 +1041,14 @@ struct HaloParams {
   int a_stages, b_stages, b_resident;
 };
 
-template <int BN, int ACT>
+template <int BN, int ACT, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmY, const ConvGemmParams p, const HaloParams hp) {
-  constexpr int kBBytes = BN * kBK * 2;
+  constexpr int kBRows = PAIR ? BN / 2 : BN;      // weight rows staged by this CTA (a pair splits the column tile)
+  constexpr int kBBytes = kBRows * kBK * 2;
   constexpr int kTmemCols = next_pow2_cols(2 * BN);
+  const uint32_t pair_rank = PAIR ? cluster_ctarank() : 0u;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(16) float s_bias[kBiasFloats];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -1011,18 +1073,22 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (threadIdx.x == 0) {
     for (int s = 0; s < SA; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), 1); }
     for (int s = 0; s < SB; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8u * a, 1); mbar_init(tempty0 + 8u * a, p.y_tma ? kTeamWarps : kEpiWarps); }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull0 + 8u * a, 1);
+      mbar_init(tempty0 + 8u * a, kEpiWarps * (PAIR ? 2 : 1));
+    }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-    tmem_relinquish();
+    if (PAIR) { tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols); tmem_relinquish_pair(); }
+    else { tmem_alloc(smem_u32(tmem_slot), kTmemCols); tmem_relinquish(); }
   }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all();
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int slabs = p.kb_per_tap;
@@ -1033,14 +1099,19 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int sa = 0, sb = 0;
       uint32_t pa = 0, pb = 0;
       bool ok = true, first = true;
-      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+      int item = 0;
+      for (int v = work_first(p); ok && v < p.total_tiles; v += p.gemm_ctas, ++item) {
+        const int tile = work_tile(p, v, pair_rank);
         const TileCoord tc = decode_tile(p, tile);
         const int n_tile = tc.n_tile, twi = tc.twi, thi = tc.thi, img = tc.img;
         for (int kb = 0; ok && kb < slabs; ++kb) {
           if (!mbar_wait(a_empty(sa), pa ^ 1, abort_flag, kStatusTimeoutProducer)) { ok = false; break; }
-          mbar_arrive_expect_tx(a_full(sa), halo_bytes);
-          if (kb == 0) trace_mark(p, (tile - blockIdx.x) / gridDim.x, 0);
-          tma_load_4d(a0 + sa * kHaloABytes, &tmA, a_full(sa), kb * kBK, twi * kHaloTw - 1, thi * kHaloTh - 1, img);
+          // in a pair both CTAs' bytes complete on the even CTA's barriers, which it arms for both
+          if (!PAIR) mbar_arrive_expect_tx(a_full(sa), halo_bytes);
+          else if (pair_rank == 0) mbar_arrive_expect_tx(a_full(sa), 2u * halo_bytes);
+          if (kb == 0) trace_mark(p, item, 0);
+          if (PAIR) tma_load_4d_pair(a0 + sa * kHaloABytes, &tmA, a_full(sa), kb * kBK, twi * kHaloTw - 1, thi * kHaloTh - 1, img);
+          else tma_load_4d(a0 + sa * kHaloABytes, &tmA, a_full(sa), kb * kBK, twi * kHaloTw - 1, thi * kHaloTh - 1, img);
           if (++sa == SA) { sa = 0; pa ^= 1; }
           if (hp.b_resident && !first) continue;
           // weights travel one filter row (3 taps) per stage
@@ -1048,11 +1119,17 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (!hp.b_resident) {
               if (!mbar_wait(b_empty(sb), pb ^ 1, abort_flag, kStatusTimeoutProducer)) { ok = false; break; }
             }
-            mbar_arrive_expect_tx(b_full(sb), 3 * kBBytes);
+            if (!PAIR) mbar_arrive_expect_tx(b_full(sb), 3 * kBBytes);
+            else if (pair_rank == 0) mbar_arrive_expect_tx(b_full(sb), 2u * 3u * kBBytes);
 #pragma unroll
-            for (int kw = 0; kw < 3; ++kw)
-              tma_load_2d(b0 + sb * (3 * kBBytes) + kw * kBBytes, &tmB, b_full(sb),
-                          ((kh * 3 + kw) * slabs + kb) * kBK, n_tile * BN);
+            for (int kw = 0; kw < 3; ++kw) {
+              if (PAIR)
+                tma_load_2d_pair(b0 + sb * (3 * kBBytes) + kw * kBBytes, &tmB, b_full(sb),
+                                 ((kh * 3 + kw) * slabs + kb) * kBK, n_tile * BN + static_cast<int>(pair_rank) * kBRows);
+              else
+                tma_load_2d(b0 + sb * (3 * kBBytes) + kw * kBBytes, &tmB, b_full(sb),
+                            ((kh * 3 + kw) * slabs + kb) * kBK, n_tile * BN);
+            }
             if (++sb == SB) { sb = 0; pb ^= 1; }
           }
         }
@@ -1067,15 +1144,23 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (warp == 1) {
     // One elected thread issues everything; see the note in conv_gemm_kernel on why the loop holds
     // no votes and no tcgen05 fences.
-    if (elect_one()) {
+    if (pair_rank == 0 && elect_one()) {
       int sa = 0, sb = 0, acc = 0;
       uint32_t pa = 0, pb = 0, acc_ph = 0;
       bool ok = true, weights_ready = false;
       const uint64_t bdesc_hi = make_kmajor_desc(0, 128);
       // shifted views of the halo patch: 8-row groups are 10 pixel rows (1280 bytes) apart
       const uint64_t adesc_hi = (bdesc_hi & ~(0x3FFFull << 32)) | (static_cast<uint64_t>((kHaloCols * 128) >> 4) << 32);
+      auto mma = [&](uint32_t d, uint64_t ad, uint64_t bd, uint32_t accum, uint32_t nsteps) {
+        if (PAIR) umma_f16_ksteps_pair(d, ad, bd, p.idesc, accum, nsteps);
+        else umma_f16_ksteps(d, ad, bd, p.idesc, accum, nsteps);
+      };
+      auto commit = [&](uint32_t bar) {
+        if (PAIR) umma_commit_pair(bar);
+        else umma_commit(bar);
+      };
       int it = 0;
-      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++it) {
+      for (int v = work_first(p); ok && v < p.total_tiles; v += p.gemm_ctas, ++it) {
         if (!mbar_wait(tempty0 + 8u * acc, acc_ph ^ 1, abort_flag, kStatusTimeoutMma)) break;
         trace_mark(p, it, 1);
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -1092,10 +1177,10 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
             for (int t = 0; t < 9; ++t) {
               const int kh = t / 3, kw = t - 3 * kh;
-              umma_f16_ksteps(d_tmem, ad + (((kh * kHaloCols + kw) * 128) >> 4), bd + ((t * kBBytes) >> 4), p.idesc,
-                              (kb | t) != 0 ? 1u : 0u, ksteps);
+              mma(d_tmem, ad + (((kh * kHaloCols + kw) * 128) >> 4), bd + ((t * kBBytes) >> 4), (kb | t) != 0 ? 1u : 0u,
+                  ksteps);
             }
-            umma_commit(a_empty(sa));
+            commit(a_empty(sa));
             if (++sa == SA) { sa = 0; pa ^= 1; }
             continue;
           }
@@ -1110,20 +1195,20 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint32_t b_row = b0 + sb * (3 * kBBytes);
             const uint64_t ad0 = adesc_hi | ((a_row & 0x3FFFF) >> 4);
             const uint64_t bd0 = bdesc_hi | ((b_row & 0x3FFFF) >> 4);
-            umma_f16_ksteps(d_tmem, ad0, bd0, p.idesc, (kb | kh) != 0 ? 1u : 0u, ksteps);
-            umma_f16_ksteps(d_tmem, ad0 + (128 >> 4), bd0 + (kBBytes >> 4), p.idesc, 1u, ksteps);
-            umma_f16_ksteps(d_tmem, ad0 + (256 >> 4), bd0 + (2 * kBBytes >> 4), p.idesc, 1u, ksteps);
+            mma(d_tmem, ad0, bd0, (kb | kh) != 0 ? 1u : 0u, ksteps);
+            mma(d_tmem, ad0 + (128 >> 4), bd0 + (kBBytes >> 4), 1u, ksteps);
+            mma(d_tmem, ad0 + (256 >> 4), bd0 + (2 * kBBytes >> 4), 1u, ksteps);
             if (!hp.b_resident) {
-              umma_commit(b_empty(sb));
+              commit(b_empty(sb));
               if (++sb == SB) { sb = 0; pb ^= 1; }
             }
           }
           if (!ok) break;
-          umma_commit(a_empty(sa));
+          commit(a_empty(sa));
           if (++sa == SA) { sa = 0; pa ^= 1; }
         }
         if (!ok) break;
-        umma_commit(tfull0 + 8u * acc);
+        commit(tfull0 + 8u * acc);
         weights_ready = true;
         trace_mark(p, it, 3);
         acc ^= 1;
@@ -1139,11 +1224,13 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all();    // see conv_gemm_kernel: a pair leaves together
+  else __syncthreads();
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, *abort_flag);
 }
@@ -1156,6 +1243,7 @@ struct ConvGemmOp : Op {
   ConvGemmParams prm;
   int block_n = 0;
   int grid = 0;
+  int pair = 0;          // 1: clusters of two CTAs sharing every MMA (cta_group::2)
   int halo = 0;          // 1: conv3x3_halo_kernel
   HaloParams hp{};
   int halo_smem = 0;
@@ -1173,13 +1261,41 @@ static int launch_inst(ConvGemmOp* op, cudaStream_t stream) {
   int dev = 0;
   FDB_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 64 && !attr_set[dev]) {
-    FDB_CUDA_OK(cudaFuncSetAttribute(conv_gemm_kernel<BN, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    FDB_CUDA_OK(cudaFuncSetAttribute(conv_gemm_kernel<BN, ACT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Cfg::kSmemBytes));
     attr_set[dev] = true;
   }
   if (op->prm.peer_mode == 1) ++op->prm.peer_epoch;   // the ready flags of this launch
-  conv_gemm_kernel<BN, ACT><<<op->grid, kThreads, Cfg::kSmemBytes, stream>>>(op->tmA, op->tmB, op->tmY, op->prm);
+  conv_gemm_kernel<BN, ACT, false><<<op->grid, kThreads, Cfg::kSmemBytes, stream>>>(op->tmA, op->tmB, op->tmY, op->prm);
   FDB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// CTA-pair form: the grid is launched as clusters of two CTAs.
+template <int BN, int ACT>
+static int launch_pair_inst(ConvGemmOp* op, cudaStream_t stream) {
+  using Cfg = KernelCfg<BN, true>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  FDB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    FDB_CUDA_OK(cudaFuncSetAttribute(conv_gemm_kernel<BN, ACT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg::kSmemBytes));
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(op->grid, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  FDB_CUDA_OK(cudaLaunchKernelEx(&cfg, conv_gemm_kernel<BN, ACT, true>, op->tmA, op->tmB, op->tmY, op->prm));
   return 0;
 }
 
@@ -1189,23 +1305,76 @@ static int launch_halo_inst(ConvGemmOp* op, cudaStream_t stream) {
   int dev = 0;
   FDB_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 64 && !attr_set[dev]) {
-    FDB_CUDA_OK(cudaFuncSetAttribute(conv3x3_halo_kernel<BN, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    FDB_CUDA_OK(cudaFuncSetAttribute(conv3x3_halo_kernel<BN, ACT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      kMaxSmem));
     attr_set[dev] = true;
   }
-  conv3x3_halo_kernel<BN, ACT><<<op->grid, kThreads, op->halo_smem, stream>>>(op->tmA, op->tmB, op->tmY, op->prm, op->hp);
+  conv3x3_halo_kernel<BN, ACT, false><<<op->grid, kThreads, op->halo_smem, stream>>>(op->tmA, op->tmB, op->tmY, op->prm, op->hp);
   FDB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+template <int BN, int ACT>
+static int launch_halo_pair_inst(ConvGemmOp* op, cudaStream_t stream) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  FDB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    FDB_CUDA_OK(cudaFuncSetAttribute(conv3x3_halo_kernel<BN, ACT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kMaxSmem));
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(op->grid, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = op->halo_smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  FDB_CUDA_OK(cudaLaunchKernelEx(&cfg, conv3x3_halo_kernel<BN, ACT, true>, op->tmA, op->tmB, op->tmY, op->prm, op->hp));
   return 0;
 }
 
 template <int BN>
 static int launch_bn(ConvGemmOp* op, cudaStream_t stream) {
+  if (op->halo && op->pair) {
+    if constexpr (BN >= 64) {
+      switch (op->prm.act) {
+        case kActNone: return launch_halo_pair_inst<BN, kActNone>(op, stream);
+        case kActRelu: return launch_halo_pair_inst<BN, kActRelu>(op, stream);
+        case kActSilu: return launch_halo_pair_inst<BN, kActSilu>(op, stream);
+        default: return launch_halo_pair_inst<BN, kTplGeneric>(op, stream);
+      }
+    } else {
+      set_error("conv_gemm: CTA pairs need block_n >= 64");
+      return -1;
+    }
+  }
   if (op->halo) {
     switch (op->prm.act) {
       case kActNone: return launch_halo_inst<BN, kActNone>(op, stream);
       case kActRelu: return launch_halo_inst<BN, kActRelu>(op, stream);
       case kActSilu: return launch_halo_inst<BN, kActSilu>(op, stream);
       default: return launch_halo_inst<BN, kTplGeneric>(op, stream);
+    }
+  }
+  if (op->pair) {
+    if constexpr (BN >= 64) {      // pairs are only planned for wide column tiles
+      switch (op->prm.act) {
+        case kActNone: return launch_pair_inst<BN, kActNone>(op, stream);
+        case kActRelu: return launch_pair_inst<BN, kActRelu>(op, stream);
+        case kActSilu: return launch_pair_inst<BN, kActSilu>(op, stream);
+        case kActGelu: return launch_pair_inst<BN, kActGelu>(op, stream);
+        default: return launch_pair_inst<BN, kTplGeneric>(op, stream);
+      }
+    } else {
+      set_error("conv_gemm: CTA pairs need block_n >= 64");
+      return -1;
     }
   }
   switch (op->prm.act) {
@@ -1305,11 +1474,16 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   int tw = d->tile_w, th = d->tile_h;
   if (tw <= 0 || th <= 0) choose_tile(d->Ho, d->Wo, d->stride, &tw, &th);
   if (d->w_batched) {
-    if (d->KH != 1 || d->KW != 1 || d->stride != 1 || d->w_ld % 8 != 0) {
+    if (d->KH != 1 || d->KW != 1 || d->stride != 1 || d->w_ld % 8 != 0 || (d->w_batched != 1 && d->w_batched != 2)) {
       set_error("conv_gemm: batched weights need a 1x1 stride-1 product and w_ld % 8 == 0"); delete op; return nullptr;
     }
-    th = 1;
-    tw = std::min(d->Wo, kBM);
+    if (d->w_batched == 2 && (d->w_n_stride % 8 != 0 || d->w_n_stride < static_cast<long long>(d->Cout) * d->w_ld)) {
+      set_error("conv_gemm: per-image weights need w_n_stride % 8 == 0 covering Cout rows"); delete op; return nullptr;
+    }
+    if (d->w_batched == 1) {   // one matrix per image row: a tile may not span rows
+      th = 1;
+      tw = std::min(d->Wo, kBM);
+    }
   }
   if (tw * th > kBM || tw * d->stride > 256 || th * d->stride > 256) {
     set_error("conv_gemm: tile too large"); delete op; return nullptr;
@@ -1350,7 +1524,7 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   p.out_dtype = d->out_dtype; p.in_bf16 = d->dtype == kBF16;
   p.KH = d->KH; p.KW = d->KW; p.stride = d->stride; p.pad_h = d->pad_h; p.pad_w = d->pad_w;
   p.act = d->act; p.act_alpha = d->act_alpha; p.act_beta = d->act_beta;
-  p.b_batched = d->w_batched ? 1 : 0;
+  p.b_batched = d->w_batched;
   p.trace = d->trace;
   p.y_h_stride = d->y_h_stride > 0 ? d->y_h_stride : static_cast<long long>(d->Wo) * d->y_ld;
   p.res_h_stride = d->res_h_stride > 0 ? d->res_h_stride : static_cast<long long>(d->Wo) * d->res_ld;
@@ -1368,9 +1542,19 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   }
   int grid = static_cast<int>(std::min<long>(total, d->max_ctas > 0 ? d->max_ctas : sms));
   op->grid = std::max(grid, 1);
+  p.pair = 0;
+  p.n_images = d->N;
   if (op->halo) {
     const int budget = kMaxSmem - 1024 - kHaloBarBytes - kStagingBytes;
-    const int b_bytes = 3 * bn * kBK * 2;          // one filter row (3 taps) per weight stage
+    // CTA pairs: each CTA stages half of the filter, so twice the channels stay resident and streamed
+    // weights cost half the L2 traffic per SM
+    const long items_pair = ((m_tiles + 1) / 2) * p.n_tiles;
+    const bool pair_can = d->pair_mode != 0 && bn >= 64 && m_tiles >= 2 && d->peer_mode == 0 && d->max_ctas != 1;
+    if (d->pair_mode == 1 && !pair_can) {
+      set_error("conv_gemm: CTA pairs need block_n >= 64, no peer mode and 2+ tiles"); delete op; return nullptr;
+    }
+    const bool use_pair = pair_can && (d->pair_mode == 1 || (bn >= 96 && items_pair >= sms / 2));
+    const int b_bytes = 3 * (use_pair ? bn / 2 : bn) * kBK * 2;   // one filter row (3 taps) per weight stage
     const int all_b = 3 * p.kb_per_tap;
     HaloParams hp{};
     // Activation patches come from DRAM, weights from L2: bytes in flight matter for the patches,
@@ -1381,13 +1565,21 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
       hp.a_stages = std::min(kHaloMaxA, (budget - all_b * b_bytes) / kHaloABytes);
     } else {
       hp.b_resident = 0;
-      hp.b_stages = std::max(2, std::min(kHaloMaxB, (budget / 2) / b_bytes));
+      // three patch stages first, the rest of the budget to the weight ring (at least two stages)
+      hp.b_stages = std::max(2, std::min(kHaloMaxB, (budget - 3 * kHaloABytes) / b_bytes));
       hp.a_stages = std::min(kHaloMaxA, (budget - hp.b_stages * b_bytes) / kHaloABytes);
       if (hp.a_stages < 2) { hp.a_stages = 2; hp.b_stages = (budget - 2 * kHaloABytes) / b_bytes; }
+    }
+    if (use_pair && hp.b_stages >= 2) {
+      op->pair = p.pair = 1;
+      p.total_tiles = static_cast<int>(items_pair);
+      const int max_pairs = std::max(1, (d->max_ctas > 0 ? d->max_ctas : sms) / 2);
+      op->grid = 2 * static_cast<int>(std::min<long>(items_pair, max_pairs));
     }
     if (hp.b_stages < 2) {
       if (d->halo_mode == 1) { set_error("conv_gemm: halo kernel does not fit shared memory"); delete op; return nullptr; }
       op->halo = 0;   // fall back to the generic kernel with its own tile choice
+      op->pair = p.pair = 0;
       choose_tile(d->Ho, d->Wo, d->stride, &tw, &th);
       p.tw = tw; p.th = th;
       p.tiles_w = (d->Wo + tw - 1) / tw;
@@ -1399,6 +1591,25 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
     } else {
       op->hp = hp;
       op->halo_smem = hp.a_stages * kHaloABytes + hp.b_stages * b_bytes + kStagingBytes + kHaloBarBytes + 1024;
+    }
+  }
+
+  // ---- CTA pairs: two pixel tiles of one column tile per MMA, half of the weight tile staged per CTA
+  if (!op->halo && d->pair_mode != 0) {
+    const long mt = static_cast<long>(p.tiles_w) * p.tiles_h * d->N;
+    const bool can = !fp8 && !d->w_batched && d->peer_mode == 0 && bn >= 64 && mt >= 2 && d->max_ctas != 1;
+    if (d->pair_mode == 1 && !can) {
+      set_error("conv_gemm: CTA pairs need 16-bit operands, shared weights, block_n >= 64, no peer mode, 2+ tiles");
+      delete op; return nullptr;
+    }
+    // worthwhile when the weight tile is a large share of the operand traffic and there is work for every pair
+    const long items = ((mt + 1) / 2) * p.n_tiles;
+    if (can && (d->pair_mode == 1 || (bn >= 128 && items >= sms / 2))) {
+      op->pair = p.pair = 1;
+      p.total_tiles = static_cast<int>(items);
+      const int max_pairs = std::max(1, (d->max_ctas > 0 ? d->max_ctas : sms) / 2);
+      const int pairs = static_cast<int>(std::min<long>(items, max_pairs));
+      op->grid = 2 * pairs;
     }
   }
 
@@ -1421,8 +1632,10 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
     }
   }
   if (d->w_batched) {
-    cuuint64_t dims[4] = {(cuuint64_t)d->Cin, (cuuint64_t)d->Cout, (cuuint64_t)d->H, (cuuint64_t)d->N};
-    cuuint64_t strides[3] = {(cuuint64_t)d->w_ld * 2, (cuuint64_t)d->w_h_stride * 2, (cuuint64_t)d->w_n_stride * 2};
+    const bool per_image = d->w_batched == 2;
+    cuuint64_t dims[4] = {(cuuint64_t)d->Cin, (cuuint64_t)d->Cout, (cuuint64_t)(per_image ? 1 : d->H), (cuuint64_t)d->N};
+    cuuint64_t strides[3] = {(cuuint64_t)d->w_ld * 2, (cuuint64_t)(per_image ? d->w_n_stride : d->w_h_stride) * 2,
+                             (cuuint64_t)d->w_n_stride * 2};
     cuuint32_t box[4] = {(cuuint32_t)kBK, (cuuint32_t)bn, 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = enc(&op->tmB, tdt, 4, const_cast<void*>(d->w), dims, strides, box, estr,
@@ -1436,7 +1649,7 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
     const cuuint64_t ktot = (cuuint64_t)d->KH * d->KW * p.kb_per_tap * kblk;
     cuuint64_t dims[2] = {ktot, (cuuint64_t)d->Cout};
     cuuint64_t strides[1] = {ktot * es};
-    cuuint32_t box[2] = {(cuuint32_t)kblk, (cuuint32_t)bn};
+    cuuint32_t box[2] = {(cuuint32_t)kblk, (cuuint32_t)(op->pair ? bn / 2 : bn)};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(&op->tmB, tdt, 2, const_cast<void*>(d->w), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -1452,16 +1665,16 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
     const bool out16 = d->out_dtype == kF16 || d->out_dtype == kBF16;
     const bool aligned = reinterpret_cast<uintptr_t>(d->y) % 16 == 0 && (d->y_ld * 2) % 16 == 0 &&
                          (p.y_h_stride * 2) % 16 == 0 && (p.y_n_stride * 2) % 16 == 0;
-    const bool cols_ok = p.n_tiles == 1 || bn % 64 == 0;
+    const bool cols_ok = p.n_tiles == 1 || bn % kChunkCols == 0;
     if (out16 && aligned && cols_ok && d->y_tma_mode != 0) {
       const CUtensorMapDataType ydt =
           d->out_dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
       cuuint64_t dims[4] = {(cuuint64_t)d->Cout, (cuuint64_t)d->Wo, (cuuint64_t)d->Ho, (cuuint64_t)d->N};
       cuuint64_t strides[3] = {(cuuint64_t)d->y_ld * 2, (cuuint64_t)p.y_h_stride * 2, (cuuint64_t)p.y_n_stride * 2};
-      cuuint32_t box[4] = {64, (cuuint32_t)p.tw, (cuuint32_t)p.th, 1};
+      cuuint32_t box[4] = {kChunkCols, (cuuint32_t)p.tw, (cuuint32_t)p.th, 1};
       cuuint32_t estr[4] = {1, 1, 1, 1};
       CUresult r = enc(&op->tmY, ydt, 4, d->y, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                       CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       if (r == CUDA_SUCCESS) p.y_tma = 1;
     }
     if (!p.y_tma) op->tmY = op->tmA;   // a valid map is still passed; the kernel does not touch it
@@ -1497,10 +1710,10 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
         const cuuint64_t rows = (cuuint64_t)d->peer_rows * d->peer_world;
         cuuint64_t dims[4] = {(cuuint64_t)d->Cout, rows, 1, 1};
         cuuint64_t strides[3] = {(cuuint64_t)d->y_ld * 2, rows * d->y_ld * 2, rows * d->y_ld * 2};
-        cuuint32_t box[4] = {64, (cuuint32_t)p.tw, 1, 1};
+        cuuint32_t box[4] = {kChunkCols, (cuuint32_t)p.tw, 1, 1};
         cuuint32_t estr[4] = {1, 1, 1, 1};
         res = enc(&host.maps[r], ydt, 4, d->peer_ptrs[r], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         host.counters[r] = d->peer_counters[r];
       }
       if (res != CUDA_SUCCESS) {
@@ -1531,11 +1744,12 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
       p.gather_row_bytes = static_cast<long long>(d->x_ld) * 2;
     }
   }
-  if (p.peer_mode != 1) p.gemm_ctas = op->grid;
+  if (p.peer_mode != 1) p.gemm_ctas = op->pair ? op->grid / 2 : op->grid;
+  if (op->pair) p.idesc = make_idesc(d->dtype == kBF16 ? 1u : 0u, 2 * kBM, bn);   // M = 256 over the two CTAs
   {
     const unsigned long long one = 1ull << 40;
     const long long dmax = std::max(p.n_tiles, std::max(p.tiles_w, p.tiles_h));
-    if (static_cast<long long>(p.total_tiles) * dmax >= static_cast<long long>(one)) {
+    if ((static_cast<long long>(p.total_tiles) * (op->pair ? 2 : 1) + p.n_tiles) * dmax >= static_cast<long long>(one)) {
       set_error("conv_gemm: too many tiles for the tile decoder"); delete op; return nullptr;
     }
     p.mul_n = (one + p.n_tiles - 1) / p.n_tiles;
@@ -1555,8 +1769,10 @@ FDB_API void fdb_conv_gemm_info(void* handle, int* out5) {
   out5[4] = op->prm.total_tiles;
 }
 
-// 0 generic kernel, 1 halo kernel with streamed weights, 2 halo kernel with resident weights
+// 0 generic kernel, 1 halo kernel with streamed weights, 2 halo kernel with resident weights,
+// 3 generic kernel on CTA pairs, 4 / 5 halo kernel on CTA pairs with streamed / resident weights
 FDB_API int fdb_conv_gemm_variant(void* handle) {
   auto* op = static_cast<ConvGemmOp*>(handle);
-  return op->halo ? (op->hp.b_resident ? 2 : 1) : 0;
+  if (op->halo) return op->pair ? (op->hp.b_resident ? 5 : 4) : (op->hp.b_resident ? 2 : 1);
+  return op->pair ? 3 : 0;
 }

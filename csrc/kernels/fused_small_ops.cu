@@ -16,6 +16,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
 #include <functional>
 
 #include "fdb_common.h"
@@ -239,6 +240,41 @@ __global__ void __launch_bounds__(256) spp_maxpool_kernel(const SppParams p) {
   }
 }
 
+// ---- per-image weights: Wn[n][co][k] = W[co][k] * (gate[n][k] (+ 1)) ------------------------------
+// Folds a channel gate (squeeze-excite) that multiplies the INPUT of a 1x1 convolution into that
+// convolution's weights: conv(x * g) = conv_{W diag(g)}(x). The scaled feature map is then never
+// written or read. 16-byte vectors of 8 input channels; columns past Cin are copied (zero padding).
+template <bool BF16>
+__global__ void __launch_bounds__(256) scale_weights_kernel(const uint8_t* __restrict__ W, const float* __restrict__ gate,
+                                                            uint8_t* __restrict__ out, long long total, int Cout, int K8,
+                                                            int Cin, int gate_ld, float plus) {
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int kg = static_cast<int>(idx % K8);
+    const long long t = idx / K8;
+    const int co = static_cast<int>(t % Cout);
+    const int n = static_cast<int>(t / Cout);
+    const uint4 u = __ldg(reinterpret_cast<const uint4*>(W + (static_cast<size_t>(co) * K8 + kg) * 16));
+    float f[8];
+    unpack8f<BF16>(u, f);
+    const int k0 = kg * 8;
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float g0 = k0 + 2 * j < Cin ? gate[static_cast<size_t>(n) * gate_ld + k0 + 2 * j] + plus : 1.f;
+      const float g1 = k0 + 2 * j + 1 < Cin ? gate[static_cast<size_t>(n) * gate_ld + k0 + 2 * j + 1] + plus : 1.f;
+      if (BF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * j] * g0, f[2 * j + 1] * g1);
+        w[j] = *reinterpret_cast<uint32_t*>(&h);
+      } else {
+        __half2 h = __floats2half2_rn(f[2 * j] * g0, f[2 * j + 1] * g1);
+        w[j] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+    *reinterpret_cast<uint4*>(out + ((static_cast<size_t>(n) * Cout + co) * K8 + kg) * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 }  // namespace fdb
 
 using namespace fdb;
@@ -333,6 +369,24 @@ FDB_API void* fdb_fused_create(int kind, const FusedDesc* dp) {
         dim3 grid((p.C8 + p.cg_per_block - 1) / p.cg_per_block, N);
         if (bf) spp_maxpool_kernel<true><<<grid, 256, smem, s>>>(p);
         else spp_maxpool_kernel<false><<<grid, 256, smem, s>>>(p);
+        FDB_FUSED_CHECK();
+      };
+      break;
+    }
+    case 3: {
+      // scale_weights: p0 W 16-bit [Cout][K], p1 gate fp32 [N][gate_ld], p2 out 16-bit [N][Cout][K];
+      // i0 N, i1 Cout, i2 K (multiple of 8), i3 Cin (<= K), i4 gate_ld, i5 bf16; f0 added to the gate
+      const int N = d.i[0], Cout = d.i[1], Kp = d.i[2], Cin = d.i[3], gld = d.i[4];
+      const bool bf = d.i[5] != 0;
+      const float plus = d.f[0];
+      if (Kp % 8 || Cin > Kp || (reinterpret_cast<uintptr_t>(d.p[0]) & 15) || (reinterpret_cast<uintptr_t>(d.p[2]) & 15)) {
+        set_error("scale_weights: K must be a multiple of 8 covering Cin, pointers 16-byte aligned"); delete op; return nullptr;
+      }
+      const long long total = static_cast<long long>(N) * Cout * (Kp / 8);
+      op->fn = [=](cudaStream_t s) {
+        const int grid = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));
+        if (bf) scale_weights_kernel<true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (const float*)d.p[1], (uint8_t*)d.p[2], total, Cout, Kp / 8, Cin, gld, plus);
+        else scale_weights_kernel<false><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (const float*)d.p[1], (uint8_t*)d.p[2], total, Cout, Kp / 8, Cin, gld, plus);
         FDB_FUSED_CHECK();
       };
       break;

@@ -305,6 +305,95 @@ __device__ __forceinline__ void tmem_ld_wait_dep(uint32_t (&v)[32]) {
                : "memory");
 }
 
+// ---------------------------------------------------------------- CTA pairs (cta_group::2)
+// Two CTAs of a cluster (ranks 2k and 2k+1) act as one MMA unit: each stages its own 128 rows of A and
+// half of the B tile, the even CTA issues tcgen05.mma.cta_group::2 (M = 256), and each CTA's tensor
+// memory receives the accumulator of its own 128 rows. Every B byte then feeds twice the rows, which
+// halves the weight traffic per SM. Loads use the cta_group::2 form WITHOUT any cluster broadcast: each
+// CTA fetches its own bytes from global memory; only the completion signal goes to the even CTA's
+// mbarrier (same shared-memory offset, CTA-rank bit cleared).
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on the mbarrier at the same shared-memory offset in CTA `rank` of the cluster. Relaxed: the
+// arrival hands back tensor memory whose reads this thread has already waited for (tcgen05.wait::ld); no
+// data written through the generic proxy travels with it, and a release here would first drain the
+// thread's earlier shared-memory stores, which was measured at over a microsecond per tile.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar, uint32_t rank) {
+  asm volatile(
+      "{\n"
+      ".reg .b32 ra;\n"
+      "mapa.shared::cluster.u32 ra, %0, %1;\n"
+      "mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [ra];\n"
+      "}\n" ::"r"(bar), "r"(rank)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar & kPeerBitMask), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2,
+                                                 int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar & kPeerBitMask), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Arrive (once every MMA issued so far by this thread has retired) on the mbarrier at this offset in BOTH CTAs.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          bar & kPeerBitMask),
+      "h"(static_cast<uint16_t>(3))
+      : "memory");
+}
+// K block of up to four K = 16 steps issued for the CTA pair (M = 256 over both CTAs).
+__device__ __forceinline__ void umma_f16_ksteps_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                     uint32_t accumulate_first, uint32_t nsteps) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p0, p1, q1, q2, q3;\n"
+      ".reg .b64 a1, a2, a3, b1, b2, b3;\n"
+      "setp.ne.b32 p0, %4, 0;\n"
+      "setp.eq.u32 p1, %3, %3;\n"
+      "setp.gt.u32 q1, %5, 1;\n"
+      "setp.gt.u32 q2, %5, 2;\n"
+      "setp.gt.u32 q3, %5, 3;\n"
+      "add.s64 a1, %1, 2;\n"
+      "add.s64 b1, %2, 2;\n"
+      "add.s64 a2, %1, 4;\n"
+      "add.s64 b2, %2, 4;\n"
+      "add.s64 a3, %1, 6;\n"
+      "add.s64 b3, %2, 6;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p0;\n"
+      "@q1 tcgen05.mma.cta_group::2.kind::f16 [%0], a1, b1, %3, p1;\n"
+      "@q2 tcgen05.mma.cta_group::2.kind::f16 [%0], a2, b2, %3, p1;\n"
+      "@q3 tcgen05.mma.cta_group::2.kind::f16 [%0], a3, b3, %3, p1;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate_first), "r"(nsteps)
+      : "memory");
+}
+
 // ---------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor for a K-major operand tile whose rows are
 // `row_bytes` (32/64/128) wide and stored with the matching TMA swizzle.

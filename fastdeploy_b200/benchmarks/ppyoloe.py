@@ -96,8 +96,10 @@ def run(ctx: Context, args) -> dict:
     clocks = sampler.stop()
 
     extra = {}
-    if args.scheduler_mode and ctx.world >= 1:
+    if not args.no_scheduler_mode:
         from . import ppyoloe_scheduler
+        del model
+        torch.cuda.empty_cache()
         extra["scheduler_mode"] = ppyoloe_scheduler.run(ctx, args, model_dir, host_sets)
 
     ms_dev, ms_e2e = median(dev_ms), median(e2e_ms)

@@ -43,6 +43,7 @@ class _ConvGemmDesc(ctypes.Structure):
         ("peer_ptrs", ctypes.c_void_p * 8), ("peer_counters", ctypes.c_void_p * 8),
         ("peer_ready", ctypes.c_void_p), ("peer_copiers", ctypes.c_int),
         ("scale_a", ctypes.c_void_p), ("scale_b", ctypes.c_void_p),
+        ("pair_mode", ctypes.c_int),
     ]
 
 
@@ -86,13 +87,14 @@ class ConvGemm(NativeOp):
                  x_ld: Optional[int] = None, y_ld: Optional[int] = None, res_ld: Optional[int] = None,
                  status: Optional[StatusWord] = None, tile: Tuple[int, int] = (0, 0), block_n: int = 0,
                  max_ctas: int = 0, x_n_stride: int = 0, y_n_stride: int = 0, res_n_stride: int = 0,
-                 halo_mode: int = -1, w_batched: bool = False, w_ld: int = 0, w_h_stride: int = 0,
+                 halo_mode: int = -1, w_batched: int = 0, w_ld: int = 0, w_h_stride: int = 0,
                  w_n_stride: int = 0, x_h_stride: int = 0, y_h_stride: int = 0, res_h_stride: int = 0,
                  y_tma_mode: int = -1, trace: Optional[torch.Tensor] = None, name: str = "conv_gemm",
                  peer_mode: int = 0, peer_rows: int = 0, peer_rank: int = 0, peer_world: int = 0,
                  peer_ptrs: Optional[Sequence[int]] = None, peer_counters: Optional[Sequence[int]] = None,
                  peer_ready: Optional[torch.Tensor] = None, peer_copiers: int = 0,
-                 scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None):
+                 scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None,
+                 pair_mode: int = -1):
         n, h, w_, cin = in_shape
         d = _ConvGemmDesc()
         self.status = status or StatusWord(x.device)
@@ -128,6 +130,7 @@ class ConvGemm(NativeOp):
         d.scale_a = scale_a.data_ptr() if scale_a is not None else None
         d.scale_b = scale_b.data_ptr() if scale_b is not None else None
         self.scales = (scale_a, scale_b)
+        d.pair_mode = pair_mode
         if bias is not None:
             assert bias.dtype == torch.float32
         if residual is not None:

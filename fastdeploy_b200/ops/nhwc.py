@@ -208,3 +208,13 @@ def spp_maxpool(x: torch.Tensor, outs: Sequence[torch.Tensor], kernels: Sequence
 
 def spp_fits(h: int, w: int, nk: int) -> bool:
     return h * w * 16 * (1 + nk) <= 96 * 1024
+
+
+def scale_weights(w_packed: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, *, n: int, cout: int, cin: int,
+                  plus: float = 0.0) -> NativeOp:
+    """``out[n, co, k] = w_packed[co, k] * (gate[n, k] + plus)``: a channel gate on the input of a 1x1 convolution
+    folded into per-image weights (``conv(x * g) = conv_{W diag(g)}(x)``)."""
+    kp = w_packed.shape[1]
+    assert gate.dtype == torch.float32 and out.dtype == w_packed.dtype and out.numel() == n * cout * kp
+    return _make_fused(3, [w_packed, gate, out], [n, cout, kp, cin, gate.stride(0), _bf(w_packed)], [plus],
+                       name="scale_weights")

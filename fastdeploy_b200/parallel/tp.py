@@ -115,7 +115,7 @@ class RowParallelLinear:
         self.op = self.ops[0]
         info = self.op.info()
         n_tiles = (n + info["block_n"] - 1) // info["block_n"]
-        blks_per_tile = [(min(n, (t + 1) * info["block_n"]) - t * info["block_n"] + 63) // 64 for t in range(n_tiles)]
+        blks_per_tile = [(min(n, (t + 1) * info["block_n"]) - t * info["block_n"] + 31) // 32 for t in range(n_tiles)]
         self.stores_per_block = sum(blks_per_tile)      # TMA stores one source rank makes per 128-row block
         self.calls = 0
 

@@ -221,7 +221,7 @@ class TensorParallelViT:
         info = op.info()
         bn = info["block_n"]
         n_tiles = (self.H + bn - 1) // bn
-        op.stores_per_block = sum((min(self.H, (t + 1) * bn) - t * bn + 63) // 64 for t in range(n_tiles))
+        op.stores_per_block = sum((min(self.H, (t + 1) * bn) - t * bn + 31) // 32 for t in range(n_tiles))
         return op
 
     def _reduce_into_residual(self, which: int, op, bias: torch.Tensor, ln=None) -> None:

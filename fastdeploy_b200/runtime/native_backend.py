@@ -146,7 +146,8 @@ class Plan:
         torch.cuda.current_stream(self.device).wait_stream(s)
         torch.cuda.synchronize(self.device)
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=s):
+        # thread-local capture: worker threads of other GPUs keep allocating and launching meanwhile
+        with torch.cuda.graph(g, stream=s, capture_error_mode="thread_local"):
             self._run_eager()
         self.graph = g
 
@@ -177,6 +178,7 @@ class Lowering:
         self.prod = graph.producers()
         self.preassigned: Dict[str, Val] = {}
         self.fused_away: set = set()        # ids of nodes that an earlier node's lowering has already covered
+        self.pending_gate: Dict[str, Tuple[str, str]] = {}   # gated map -> (feature, gate) folded into its consumer
         self.input_shapes = {k: list(v) for k, v in input_shapes.items()}
 
     # ------------------------------------------------------------------ helpers
@@ -362,6 +364,9 @@ class Lowering:
         if strides[0] != strides[1]:
             return False
         cout, cin, kh, kw = w.shape
+        gated = self.pending_gate.pop(x_name, None)
+        if gated is not None:
+            x_name = gated[0]             # read the un-gated feature map; the gate goes into per-image weights
         x = self.as_nhwc(x_name)
         n, cx, h, wd = x.logical_shape
         n_o, c_o, ho, wo = self.info.shapes[node.outputs[0]]
@@ -410,8 +415,18 @@ class Lowering:
             op.launch()
             self.vals[out_name] = y
             return None
+        wkw = {}
+        if gated is not None:
+            gate = self.get(gated[1]).t                        # fp32 [n, 1, 1, c]
+            kp = wp.shape[1]
+            wn = torch.zeros(n, cout, kp, dtype=self.dtype, device=self.device)
+            sw = K.scale_weights(wp, gate.reshape(n, -1), wn, n=n, cout=cout, cin=cin)
+            self.plan.add_native(sw, node)
+            sw.launch()
+            wp = wn
+            wkw = dict(w_batched=2, w_ld=kp, w_n_stride=cout * kp)
         op = ConvGemm(x.t, wp, y.t, in_shape=(n, h, wd, cin_phys), out_hw=(ho, wo), cout=cout, kernel=(kh, kw),
-                      stride=strides[0], pad=(pad_t, pad_l), bias=bias,
+                      stride=strides[0], pad=(pad_t, pad_l), bias=bias, **wkw,
                       residual=res.t if res is not None else None, res_mode=node.attr("res_mode", 0),
                       act=node.attr("activation", "none"), act_alpha=node.attr("act_alpha", 0.0),
                       act_beta=node.attr("act_beta", 0.0), x_ld=x.ld, y_ld=y.ld,
@@ -599,20 +614,20 @@ class Lowering:
         part = K.gap_partial(x.t, scratch, n=n, hw=h * w, c=cp, x_ld=x.ld, x_n_stride=x.n_stride, splits=splits)
         self.plan.add_native(part, node)
         part.launch()
-        gate = self._ese_consumer(node, c, cp)
-        if gate is not None:
-            # squeeze-excite: the pooled vector only feeds a 1x1 convolution whose result scales a feature map;
-            # one kernel finishes the mean, applies the 1x1 weights, the bias and the activation
-            conv, wt, bias, cout = gate
-            y = self.new_nhwc(n, 1, 1, cout, torch.float32)
-            op = K.ese_gate(scratch, wt, bias, y.t, n=n, cin=cp, cout=cout, splits=splits, hw=h * w,
-                            act=conv.attr("activation", "none"), alpha=conv.attr("act_alpha", 0.0),
-                            beta=conv.attr("act_beta", 0.0), out_ld=y.t.stride(0))
-            op.keep += [wt, bias]
-            self.plan.add_native(op, conv)
-            op.launch()
-            self.fused_away.add(id(conv))
-            self.vals[conv.outputs[0]] = y
+        gates = self._ese_consumers(node, c, cp)
+        if gates:
+            # squeeze-excite: the pooled vector only feeds 1x1 convolutions whose results scale feature maps;
+            # one kernel per gate finishes the mean, applies the 1x1 weights, the bias and the activation
+            for conv, wt, bias, cout in gates:
+                y = self.new_nhwc(n, 1, 1, cout, torch.float32)
+                op = K.ese_gate(scratch, wt, bias, y.t, n=n, cin=cp, cout=cout, splits=splits, hw=h * w,
+                                act=conv.attr("activation", "none"), alpha=conv.attr("act_alpha", 0.0),
+                                beta=conv.attr("act_beta", 0.0), out_ld=y.t.stride(0))
+                op.keep += [wt, bias]
+                self.plan.add_native(op, conv)
+                op.launch()
+                self.fused_away.add(id(conv))
+                self.vals[conv.outputs[0]] = y
             return None
         y = self.out_nhwc(node.outputs[0])
         fin = K.make_simple(K.K_GAP_FINALIZE, [scratch, y.t], [n, cp, splits, K.dtype_code(y.t.dtype), y.t.stride(0)],
@@ -621,13 +636,16 @@ class Lowering:
         fin.launch()
         self.vals[node.outputs[0]] = y
 
-    def _ese_consumer(self, node: Node, c: int, cp: int):
-        """The 1x1 convolution that turns this pooled vector into a channel gate, if that is all it feeds."""
+    def _ese_consumers(self, node: Node, c: int, cp: int):
+        """The 1x1 convolutions that turn this pooled vector into channel gates, if that is all it feeds."""
         out = node.outputs[0]
         cons = self.cons.get(out, [])
-        if len(cons) != 1 or out in self.g.output_names() or out in self.preassigned:
+        if not cons or out in self.g.output_names() or out in self.preassigned:
             return None
-        conv = cons[0]
+        gates = [self._ese_gate_of(conv, out, c, cp) for conv in cons]
+        return gates if all(g is not None for g in gates) else None
+
+    def _ese_gate_of(self, conv: Node, out: str, c: int, cp: int):
         if conv.op not in ("FusedConv", "Conv") or conv.inputs[0] != out or conv.attr("group", 1) != 1:
             return None
         if len(conv.inputs) > 3 and conv.inputs[3]:
@@ -719,7 +737,36 @@ class Lowering:
         op.launch()
         self.vals[node.outputs[0]] = y
 
+    def _gate_folds_into_consumer(self, node: Node, x_name: str, s_name: str) -> bool:
+        """True when ``x * gate`` only feeds a 1x1 convolution and scaling that convolution's weights per image is
+        cheaper than writing and re-reading the scaled map (pixels per image well above the output channels)."""
+        out = node.outputs[0]
+        cons = self.cons.get(out, [])
+        if len(cons) != 1 or out in self.g.output_names() or out in self.preassigned:
+            return False
+        conv = cons[0]
+        if conv.op not in ("FusedConv", "Conv") or conv.inputs[0] != out or conv.attr("group", 1) != 1:
+            return False
+        if len(conv.inputs) > 3 and conv.inputs[3] == out:
+            return False
+        w = self.g.initializers.get(conv.inputs[1])
+        if w is None or w.ndim != 4 or tuple(w.shape[2:]) != (1, 1):
+            return False
+        if list(conv.attr("strides", [1, 1])) != [1, 1] or any(p != 0 for p in conv.attr("pads", [0, 0, 0, 0])) \
+                or conv.attr("auto_pad", "NOTSET") not in ("NOTSET", ""):
+            return False
+        n, c, h, wd = self.info.shapes[x_name]
+        s = self.vals.get(s_name)
+        if s is None or not s.nhwc or s.t.dtype != torch.float32 or c % 8 != 0 or w.shape[1] != c:
+            return False
+        if s.t.shape[1:3] != (1, 1) or s.t.stride(3) != 1:
+            return False
+        return h * wd >= 2 * w.shape[0] and n > 1 and stem_conv is not None
+
     def _lower_scale(self, node: Node, x_name: str, s_name: str):
+        if self._gate_folds_into_consumer(node, x_name, s_name):
+            self.pending_gate[node.outputs[0]] = (x_name, s_name)
+            return None
         x = self.as_nhwc(x_name)
         s = self.get(s_name)
         n, c, h, w = x.logical_shape

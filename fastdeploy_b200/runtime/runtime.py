@@ -57,6 +57,11 @@ def load_graph(option: RuntimeOption) -> Graph:
     raise ValueError(f"model format {fmt.name} is not supported by this runtime (ONNX and PADDLE are)")
 
 
+# Plan building allocates, packs weights and captures a CUDA graph: one at a time per process, so that the
+# worker threads of a multi-GPU scheduler do not interleave their captures.
+_PLAN_BUILD_LOCK = threading.Lock()
+
+
 class Runtime:
     def __init__(self, runtime_option: Optional[RuntimeOption] = None, _graph: Optional[Graph] = None):
         self.option = runtime_option or RuntimeOption()
@@ -122,15 +127,16 @@ class Runtime:
         if plan is None:
             from .native_backend import build_plan
             t0 = time.time()
-            plan = build_plan(self.graph, {k: list(v) for k, v in shapes.items()}, self.device, self.dtype,
-                              opt_level=self.option.native_option.opt_level,
-                              cache_dir=self.option.native_option.plan_cache_dir)
-            if self.option.native_option.use_cuda_graph:
-                try:
-                    plan.capture()
-                except Exception as e:   # capture is an optimisation; eager replay stays correct
-                    log.warning(f"CUDA graph capture failed ({e}); running the plan eagerly")
-                    plan.graph = None
+            with _PLAN_BUILD_LOCK:
+                plan = build_plan(self.graph, {k: list(v) for k, v in shapes.items()}, self.device, self.dtype,
+                                  opt_level=self.option.native_option.opt_level,
+                                  cache_dir=self.option.native_option.plan_cache_dir)
+                if self.option.native_option.use_cuda_graph:
+                    try:
+                        plan.capture()
+                    except Exception as e:   # capture is an optimisation; eager replay stays correct
+                        log.warning(f"CUDA graph capture failed ({e}); running the plan eagerly")
+                        plan.graph = None
             if len(self._plans) >= self.option.native_option.max_plans:
                 self._plans.pop(next(iter(self._plans)))
             self._plans[key] = plan

@@ -72,8 +72,39 @@ class ModelManager:
             return self._handler.process(self._predictors[i], data, parameters)
 
 
+def batched_runtime_fn(rt, payloads):
+    """Execute step of the serving back end: the requests a worker took from its queue are gathered along the
+    batch dimension into ONE ``Runtime.infer`` call and the outputs are sliced back per request - what the
+    reference's Triton back end does with ``BackendInputCollector`` / ``BackendOutputResponder``
+    (serving/src/fastdeploy_runtime.cc:1158-1313). Requests whose non-batch dimensions differ run one by one."""
+    if len(payloads) == 1:
+        return [rt.infer(payloads[0])]
+    names = list(payloads[0].keys())
+    arrays = [[np.asarray(p[n]) for n in names] for p in payloads]
+    same = all(set(p.keys()) == set(names) for p in payloads) and all(
+        a[k].ndim >= 1 and a[k].shape[1:] == arrays[0][k].shape[1:] and a[k].dtype == arrays[0][k].dtype
+        for a in arrays for k in range(len(names)))
+    rows = [a[0].shape[0] if a and a[0].ndim else 1 for a in arrays]
+    same = same and all(x.shape[0] == r for a, r in zip(arrays, rows) for x in a)
+    if not same:
+        return [rt.infer(p) for p in payloads]
+    feeds = {n: np.concatenate([a[k] for a in arrays], 0) for k, n in enumerate(names)}
+    outs = rt.infer(feeds)
+    total = sum(rows)
+    res, pos = [], 0
+    for r in rows:
+        res.append([np.asarray(o)[pos:pos + r] if np.asarray(o).ndim and np.asarray(o).shape[0] == total else o
+                    for o in outs])
+        pos += r
+    return res
+
+
 _TRITON_DTYPES = {"FP32": np.float32, "FP16": np.float16, "INT64": np.int64, "INT32": np.int32, "UINT8": np.uint8,
                   "INT8": np.int8, "BOOL": np.bool_, "FP64": np.float64}
+
+
+def _metric_name(name: str) -> str:
+    return "".join(ch if ch.isalnum() else "_" for ch in name)
 
 
 def _build_app():
@@ -89,6 +120,19 @@ def _build_app():
             @self.get("/health")
             def health():
                 return {"status": "ok", "models": sorted(list(self._managers) + list(self._runtimes))}
+
+            @self.get("/metrics")
+            def metrics():
+                """Prometheus text: per model and worker request / failure / deadline counters, queue depth,
+                queueing and compute time, and the histogram of executed batch sizes."""
+                from fastapi.responses import PlainTextResponse
+                parts = []
+                for name, m in sorted(self._managers.items()):
+                    if m._scheduler is not None:
+                        parts.append(m._scheduler.metrics_text(prefix="fdb_" + _metric_name(name)))
+                for name, (_, sched, _) in sorted(self._runtimes.items()):
+                    parts.append(sched.metrics_text(prefix="fdb_" + _metric_name(name)))
+                return PlainTextResponse("".join(parts), media_type="text/plain; version=0.0.4")
 
         def register(self, task_name: str, model_handler, predictor):
             manager = ModelManager(model_handler, predictor)
@@ -115,9 +159,7 @@ def _build_app():
                     insts = [("gpu", d) for d in device_ids]
                 rts = [Runtime(cfg.runtime_option(kind, dev)) for kind, dev in insts]
 
-                def batch_fn(rt, payloads):
-                    return [rt.infer(p) for p in payloads]
-                sched = Scheduler(lambda i, rts=rts: rts[i], batch_fn, num_workers=len(rts),
+                sched = Scheduler(lambda i, rts=rts: rts[i], batched_runtime_fn, num_workers=len(rts),
                                   max_batch_size=max(cfg.max_batch_size, 1), max_queue_delay_us=cfg.max_queue_delay_us)
                 self._runtimes[name] = (cfg, sched, rts)
             if not getattr(self, "_v2_routes", False):
@@ -130,6 +172,12 @@ def _build_app():
                     cfg = self._runtimes[name][0]
                     return {"name": cfg.name, "versions": [str(v) for v in cfg.versions()], "platform": cfg.backend,
                             "inputs": cfg.inputs, "outputs": cfg.outputs}
+
+                @self.get("/v2/models/{name}/stats")
+                def stats(name: str):
+                    if name not in self._runtimes:
+                        raise HTTPException(status_code=404, detail="unknown model")
+                    return {"model_name": name, **self._runtimes[name][1].stats()}
 
                 @self.post("/v2/models/{name}/infer")
                 async def infer(name: str, request: Request):

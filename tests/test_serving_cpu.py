@@ -85,6 +85,63 @@ def test_dying_worker_hands_its_queue_over_without_a_later_submit():
     s.close()
 
 
+def test_deadline_cancellation_pipelining_and_metrics():
+    release = threading.Event()
+
+    class Handle:
+        def __init__(self, xs):
+            self.xs = xs
+
+        def result(self):
+            return [x + 1 for x in self.xs]
+
+    def batch_fn(m, xs):
+        if xs and xs[0] == "block":
+            release.wait(5)
+            return ["unblocked"] * len(xs)
+        return Handle(xs)                                 # asynchronous handle: resolved later, in order
+    s = Scheduler(lambda i: object(), batch_fn, num_workers=1, max_batch_size=4, max_queue_delay_us=100,
+                  pipeline_depth=3)
+    blocker = s.submit("block")
+    time.sleep(0.05)                                      # the only worker is now stuck inside batch_fn
+    late = s.submit(1, timeout=0.05)                      # deadline passes while it is queued
+    cancelled = s.submit(2)
+    assert cancelled.cancel()                             # never started: the future can be cancelled
+    time.sleep(0.1)
+    release.set()
+    assert blocker.result(5) == "unblocked"
+    with pytest.raises(TimeoutError):
+        late.result(5)
+    assert s.map(list(range(20)), timeout=5) == [i + 1 for i in range(20)]
+    text = s.metrics_text()
+    assert 'fdb_scheduler_expired_total{worker="0"} 1' in text
+    assert 'fdb_scheduler_batch_size_bucket{worker="0",le="+Inf"}' in text
+    st = s.stats()["workers"][0]
+    assert st["requests"] >= 21 and st["expired"] == 1 and sum(st["batch_histogram"].values()) == st["batches"]
+    s.close()
+    with pytest.raises(RuntimeError, match="closed"):
+        s.submit(3)
+
+
+def test_repository_execute_step_batches_requests():
+    from fastdeploy_b200.serving.server import batched_runtime_fn
+
+    class FakeRuntime:
+        calls = []
+
+        def infer(self, feeds):
+            self.calls.append({k: v.shape for k, v in feeds.items()})
+            return [feeds["x"] * 2.0, feeds["x"].sum(axis=1)]
+    rt = FakeRuntime()
+    reqs = [{"x": np.full((n, 3), float(n), np.float32)} for n in (1, 2, 4)]
+    outs = batched_runtime_fn(rt, reqs)
+    assert rt.calls == [{"x": (7, 3)}]                     # one inference for the three requests
+    assert [o[0].shape for o in outs] == [(1, 3), (2, 3), (4, 3)]
+    assert np.allclose(outs[2][0], 8.0) and np.allclose(outs[1][1], 6.0)
+    outs = batched_runtime_fn(rt, [{"x": np.zeros((1, 3), np.float32)}, {"x": np.zeros((1, 5), np.float32)}])
+    assert len(rt.calls) == 3 and outs[1][0].shape == (1, 5)   # shapes differ: run one by one
+
+
 def test_all_workers_dead_is_an_error_not_a_hang():
     with pytest.raises(RuntimeError, match="no worker could be started"):
         Scheduler(lambda i: (_ for _ in ()).throw(RuntimeError("gone")), lambda m, xs: xs, num_workers=2)
