@@ -13,6 +13,7 @@
 // serving/src/fastdeploy_runtime.cc); this file has no counterpart there.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include "fdb_common.h"
 
@@ -173,11 +174,13 @@ __device__ __forceinline__ void ld8f(const float* p, float (&f)[8]) {
   f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
 }
 
-template <typename T, int WORLD>
+// OUT8: y is e4m3 (one byte per element, y_ld in bytes), the normalised row is multiplied by out_scale first.
+template <typename T, int WORLD, bool OUT8>
 __global__ void __launch_bounds__(256) slot_reduce_ln_kernel(const T* slots, const unsigned* counters, unsigned target,
                                                              T* x, const float* bias, int rows, int cols,
                                                              int* status, const float* gamma, const float* beta,
-                                                             float eps, T* y, int y_ld) {
+                                                             float eps, void* y_, int y_ld, float out_scale) {
+  T* y = static_cast<T*>(y_);
   __shared__ int ok;
   const int blk = blockIdx.x >> 2;                 // four CTAs share a 128-row block, 32 rows each
   if (threadIdx.x == 0) ok = wait_ge(counters + blk, target, status) ? 1 : 0;
@@ -244,11 +247,25 @@ __global__ void __launch_bounds__(256) slot_reduce_ln_kernel(const T* slots, con
         float g[8], bt[8];
         ld8f(gamma + c, g);
         ld8f(beta + c, bt);
-        uint4 o;
-        T* oe = reinterpret_cast<T*>(&o);
+        if (OUT8) {
+          uint32_t w[2];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) oe[j] = from_f<T>((v[k][j] - mean) * rstd * g[j] + bt[j]);
-        *reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * y_ld + c) = o;
+          for (int h = 0; h < 2; ++h) {
+            float t[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) t[j] = ((v[k][4 * h + j] - mean) * rstd * g[4 * h + j] + bt[4 * h + j]) * out_scale;
+            const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(t[0], t[1]), __NV_SATFINITE, __NV_E4M3);
+            const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(t[2], t[3]), __NV_SATFINITE, __NV_E4M3);
+            w[h] = lo | (hi << 16);
+          }
+          *reinterpret_cast<uint2*>(static_cast<uint8_t*>(y_) + static_cast<size_t>(row) * y_ld + c) = make_uint2(w[0], w[1]);
+        } else {
+          uint4 o;
+          T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) oe[j] = from_f<T>((v[k][j] - mean) * rstd * g[j] + bt[j]);
+          *reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * y_ld + c) = o;
+        }
       }
     }
   }
@@ -355,9 +372,11 @@ FDB_API int fdb_comm_slot_reduce(const void* slots, const unsigned* counters, un
 }
 
 // x [rows, cols] += bias + sum of slots [world, rows, cols]; y [rows, y_ld] = LayerNorm(x) * gamma + beta.
+// out_fp8 != 0: y is e4m3 with row pitch y_ld bytes, the normalised rows are scaled by out_scale first.
 FDB_API int fdb_comm_slot_reduce_ln(const void* slots, const unsigned* counters, unsigned target, void* x,
                                     const float* bias, int rows, int cols, int world, int dtype, int* status,
-                                    const float* gamma, const float* beta, float eps, void* y, int y_ld, void* stream) {
+                                    const float* gamma, const float* beta, float eps, void* y, int y_ld, void* stream,
+                                    int out_fp8, float out_scale) {
   if (cols % 8 != 0 || cols > 2048 || y_ld % 8 != 0 || gamma == nullptr || beta == nullptr) {
     set_error("comm: fused slot reduce + LayerNorm needs cols a multiple of 8 up to 2048, gamma and beta"); return -1;
   }
@@ -366,8 +385,12 @@ FDB_API int fdb_comm_slot_reduce_ln(const void* slots, const unsigned* counters,
   const int grid = 4 * ((rows + 127) / 128);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define FDB_SRLN(T, W)                                                                                              \
-  slot_reduce_ln_kernel<T, W><<<grid, 256, 0, st>>>(static_cast<const T*>(slots), counters, target, static_cast<T*>(x), \
-                                                    bias, rows, cols, status, gamma, beta, eps, static_cast<T*>(y), y_ld)
+  if (out_fp8)                                                                                                      \
+    slot_reduce_ln_kernel<T, W, true><<<grid, 256, 0, st>>>(static_cast<const T*>(slots), counters, target, static_cast<T*>(x), \
+                                                            bias, rows, cols, status, gamma, beta, eps, y, y_ld, out_scale);     \
+  else                                                                                                              \
+    slot_reduce_ln_kernel<T, W, false><<<grid, 256, 0, st>>>(static_cast<const T*>(slots), counters, target, static_cast<T*>(x), \
+                                                             bias, rows, cols, status, gamma, beta, eps, y, y_ld, 1.f)
 #define FDB_SRLN_W(T)                                              \
   switch (world) {                                                 \
     case 1: FDB_SRLN(T, 1); break;                                 \

@@ -19,6 +19,7 @@
 // (fastdeploy/runtime/backends/tensorrt/trt_backend.cc:347 enqueueV2).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include <algorithm>
 #include <vector>
@@ -86,6 +87,9 @@ struct ConvGemmDesc {
   // CTA pairs (cta_group::2): -1 choose, 0 never, 1 force. A pair computes two 128-row tiles of the same
   // column tile with one M = 256 MMA; each CTA stages half of the weight tile.
   int pair_mode;
+  // out_dtype = kF8E4M3: the result (after bias, activation and residual) is multiplied by out_scale - the
+  // reciprocal of the consumer's activation scale - and stored as e4m3, so the next GEMM reads fp8 directly
+  float out_scale;
 };
 
 // Device-resident table of the peers' tensor maps and counters (host-written before any launch).
@@ -130,6 +134,8 @@ struct ConvGemmParams {
   long long* trace;  // optional: CTA 0 records clock64() at pipeline events of its first tiles
   int pair;          // launched as clusters of two CTAs that share every MMA
   int n_images;      // N: tiles decoded to an image index past it are padding of an odd tile count (pairs)
+  int epi_teams;     // TMA-store epilogue: 1 = the two warp halves drain alternate tiles, 0 = both drain every tile
+  float out_scale;   // applied before an e4m3 store
 };
 
 // Tile index -> (column tile, tile column, tile row, image). Integer division by the three runtime
@@ -322,6 +328,22 @@ __device__ __noinline__ void store8_general(void* ptr, int out_dtype, bool vec, 
     }
     return;
   }
+  if (out_dtype == kF8E4M3) {
+    if (nvalid == 8 && (reinterpret_cast<uintptr_t>(ptr) & 7) == 0) {
+      uint32_t w[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(x[4 * h], x[4 * h + 1]), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(x[4 * h + 2], x[4 * h + 3]), __NV_SATFINITE, __NV_E4M3);
+        w[h] = lo | (hi << 16);
+      }
+      *reinterpret_cast<uint2*>(ptr) = make_uint2(w[0], w[1]);
+    } else {
+      for (int j = 0; j < nvalid; ++j)
+        reinterpret_cast<uint8_t*>(ptr)[j] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(x[j], __NV_SATFINITE, __NV_E4M3));
+    }
+    return;
+  }
   for (int j = 0; j < nvalid; ++j) {
     if (out_dtype == kBF16) reinterpret_cast<__nv_bfloat16*>(ptr)[j] = __float2bfloat16_rn(x[j]);
     else reinterpret_cast<__half*>(ptr)[j] = __float2half_rn(x[j]);
@@ -370,7 +392,7 @@ __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParam
     }
   }
   // staged rows go out through a TMA store that clips channel tails, so tails may take this path too
-  const bool fast16 = p.out_dtype != kF32 && (stage_addr != 0 || (p.y_vec != 0 && nvalid == 8));
+  const bool fast16 = (p.out_dtype == kF16 || p.out_dtype == kBF16) && (stage_addr != 0 || (p.y_vec != 0 && nvalid == 8));
   if (fast16) {
     const bool out_bf16 = p.out_dtype == kBF16;
     uint32_t w[4];
@@ -445,8 +467,9 @@ __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParam
   // The out-of-line store takes an address, which would pin its argument in local memory for the
   // whole function, fast paths included: hand it a copy so that x itself stays in registers.
   float xs[8];
+  const float os = p.out_dtype == kF8E4M3 ? p.out_scale : 1.f;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) xs[j] = x[j];
+  for (int j = 0; j < 8; ++j) xs[j] = x[j] * os;
   store8_general(yrow + static_cast<size_t>(co) * out_es, p.out_dtype, p.y_vec != 0, nvalid, xs);
 }
 
@@ -455,18 +478,73 @@ __device__ __forceinline__ void epilogue8(const uint32_t* v, const ConvGemmParam
 // data-type and residual decisions are template parameters: with two or three warps per scheduler
 // nothing hides branch latency, and a dozen uniform branches per 8 columns used to cost more than
 // the arithmetic. Columns past Cout carry padding that the TMA store clips.
-template <int ACT, bool BF16, bool RES>
-__device__ __forceinline__ void staged_chunk(const uint32_t (&v)[32], const float* bias_s, const uint4 (&rpre)[4],
-                                             uint32_t srow, uint32_t row_sw, const ConvGemmParams& p) {
+// bias (+ dequantisation scale) of one group of eight columns
+template <bool SCALE>
+__device__ __forceinline__ void chunk_affine(const uint32_t* v8, const float* bias8, const float* scale8, float (&x)[8]) {
+  const float4 b0 = *reinterpret_cast<const float4*>(bias8);
+  const float4 b1 = *reinterpret_cast<const float4*>(bias8 + 4);
+  if (SCALE) {   // fp8 operands: accumulator * (activation scale * weight scale of the column) + bias
+    const float4 s0 = *reinterpret_cast<const float4*>(scale8);
+    const float4 s1 = *reinterpret_cast<const float4*>(scale8 + 4);
+    x[0] = fmaf(__uint_as_float(v8[0]), s0.x, b0.x); x[1] = fmaf(__uint_as_float(v8[1]), s0.y, b0.y);
+    x[2] = fmaf(__uint_as_float(v8[2]), s0.z, b0.z); x[3] = fmaf(__uint_as_float(v8[3]), s0.w, b0.w);
+    x[4] = fmaf(__uint_as_float(v8[4]), s1.x, b1.x); x[5] = fmaf(__uint_as_float(v8[5]), s1.y, b1.y);
+    x[6] = fmaf(__uint_as_float(v8[6]), s1.z, b1.z); x[7] = fmaf(__uint_as_float(v8[7]), s1.w, b1.w);
+  } else {
+    x[0] = __uint_as_float(v8[0]) + b0.x; x[1] = __uint_as_float(v8[1]) + b0.y;
+    x[2] = __uint_as_float(v8[2]) + b0.z; x[3] = __uint_as_float(v8[3]) + b0.w;
+    x[4] = __uint_as_float(v8[4]) + b1.x; x[5] = __uint_as_float(v8[5]) + b1.y;
+    x[6] = __uint_as_float(v8[6]) + b1.z; x[7] = __uint_as_float(v8[7]) + b1.w;
+  }
+}
+
+// e4m3 output: one 32-column chunk becomes 32 bytes of the staging row (32-byte rows, 32-byte swizzle).
+template <int ACT, bool SCALE>
+__device__ __forceinline__ void staged_chunk_e4m3(const uint32_t (&v)[32], const float* bias_s, const float* scale_s,
+                                                  uint32_t srow, uint32_t row_sw1, const ConvGemmParams& p) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint32_t w[4];
+#pragma unroll
+    for (int gg = 0; gg < 2; ++gg) {
+      const int g = 2 * h + gg;
+      float x[8];
+      chunk_affine<SCALE>(v + g * 8, bias_s + g * 8, scale_s + g * 8, x);
+      if (ACT == kTplGeneric) apply_act8(x, p.act, p.act_alpha, p.act_beta);
+      if (ACT == kActGelu) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = gelu_erf_fast(x[j]);
+      }
+      if (ACT == kActSilu) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = silu_f32(x[j]);
+      }
+      if (ACT == kActRelu) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = fmaxf(x[j], 0.f);
+      }
+#pragma unroll
+      for (int q2 = 0; q2 < 2; ++q2) {
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(x[4 * q2] * p.out_scale, x[4 * q2 + 1] * p.out_scale),
+                                                     __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(x[4 * q2 + 2] * p.out_scale, x[4 * q2 + 3] * p.out_scale),
+                                                     __NV_SATFINITE, __NV_E4M3);
+        w[2 * gg + q2] = lo | (hi << 16);
+      }
+    }
+    const uint32_t addr = srow + ((static_cast<uint32_t>(h) ^ row_sw1) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]));
+  }
+}
+
+template <int ACT, bool BF16, bool RES, bool SCALE>
+__device__ __forceinline__ void staged_chunk(const uint32_t (&v)[32], const float* bias_s, const float* scale_s,
+                                             const uint4 (&rpre)[4], uint32_t srow, uint32_t row_sw,
+                                             const ConvGemmParams& p) {
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
-    const float4 b0 = *reinterpret_cast<const float4*>(bias_s + g * 8);
-    const float4 b1 = *reinterpret_cast<const float4*>(bias_s + g * 8 + 4);
     float x[8];
-    x[0] = __uint_as_float(v[g * 8 + 0]) + b0.x; x[1] = __uint_as_float(v[g * 8 + 1]) + b0.y;
-    x[2] = __uint_as_float(v[g * 8 + 2]) + b0.z; x[3] = __uint_as_float(v[g * 8 + 3]) + b0.w;
-    x[4] = __uint_as_float(v[g * 8 + 4]) + b1.x; x[5] = __uint_as_float(v[g * 8 + 5]) + b1.y;
-    x[6] = __uint_as_float(v[g * 8 + 6]) + b1.z; x[7] = __uint_as_float(v[g * 8 + 7]) + b1.w;
+    chunk_affine<SCALE>(v + g * 8, bias_s + g * 8, scale_s + g * 8, x);
     if (ACT == kTplGeneric) apply_act8(x, p.act, p.act_alpha, p.act_beta);
     if (ACT == kActGelu) {
 #pragma unroll
@@ -492,14 +570,17 @@ __device__ __forceinline__ void staged_chunk(const uint32_t (&v)[32], const floa
 // Epilogue role shared by the convolution kernels: drains the double-buffered TMEM
 // accumulators tile by tile. `tfull0` / `tempty0` are the shared-memory addresses of
 // tmem_full[0] and tmem_empty[0]; index 1 of each follows 8 bytes later.
+constexpr int kTeamWarps = 4;                         // warps of one half of the epilogue
 constexpr int kChunkCols = 32;                        // output columns per staged chunk (one tcgen05.ld)
 constexpr int kChunkBytes = kBM * kChunkCols * 2;     // 128 rows x 32 channels (16-bit) = 8 KB
 constexpr int kStagingBytes = 4 * kChunkBytes;        // two chunk buffers for each half of the epilogue warps
 
-// Output path for 16-bit results. All eight epilogue warps drain ONE tile together, so an accumulator
-// goes back to the MMA issuer after half the time two independent four-warp teams would hold it (the
-// accumulator cycle - MMA, then drain - is what bounds narrow layers). Warps w and w + 4 read the same
-// TMEM lane quarter and take alternate 32-column chunks; each thread owns one accumulator row. A chunk
+// Output path for 16-bit results, in two forms chosen per layer. Wide column tiles (more than 64
+// columns): all eight epilogue warps drain ONE tile together, so an accumulator goes back to the MMA
+// issuer after half the time a four-warp team would hold it (the accumulator cycle - MMA, then drain - is
+// what bounds such layers); warps w and w + 4 read the same TMEM lane quarter and take alternate
+// 32-column chunks. Narrow tiles (p.epi_teams): one or two chunks cannot be split usefully, so the two
+// halves drain alternate tiles, each half its own accumulator. Each thread owns one accumulator row. A chunk
 // is assembled in one of the half's two staging buffers (64-byte rows, 64-byte swizzle) and handed to a
 // TMA tensor store by the half's leader, which writes whole lines and clips ragged tile edges and channel
 // tails; with two buffers the next chunk is staged while the previous store still reads shared memory.
@@ -519,15 +600,24 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
   const bool out_bf16 = p.out_dtype == kBF16;
   // after-activation residual rows can be fetched while the accumulator is still being produced
   const bool res_pre = p.res_mode == 2 && p.res_vec != 0 && in_bf16 == out_bf16;
-  const bool simple = (p.res_mode == 0 || res_pre) && !p.fp8;   // everything else takes the general per-group path
+  // fp8 operands with a per-column scale only (static activation scale folded in) ride the straight-line path too
+  const bool col_scale = p.fp8 != 0 && p.scale_a == nullptr && p.scale_b != nullptr;
+  const bool simple = (p.res_mode == 0 || res_pre) && (!p.fp8 || col_scale);   // else: general per-group path
+  const bool out8 = p.out_dtype == kF8E4M3;
+  const int row_bytes = out8 ? 32 : 64;                       // staging row of one chunk
+  const uint32_t row_sw1 = static_cast<uint32_t>((row >> 2) & 1);
   const uint32_t buf0 = stage0 + half * (2 * kChunkBytes);
   const uint32_t row_sw = static_cast<uint32_t>((row >> 1) & 3);
   volatile int* abort_sample = abort_flag + 1 + half;
   bool aborted = false;
   uint32_t par = 0;                             // staging buffer of this half's next chunk
   float* bias_s = s_bias + half * 256;          // each half keeps the bias slice of the current column tile
+  float* scale_s = s_bias + 512 + half * 256;   // ... and, for fp8 operands, the dequantisation scale slice
   if (p.n_tiles == 1) {
-    for (int i = tt; i < BN; i += 128) bias_s[i] = (p.bias != nullptr && i < p.Cout) ? __ldg(p.bias + i) : 0.f;
+    for (int i = tt; i < BN; i += 128) {
+      bias_s[i] = (p.bias != nullptr && i < p.Cout) ? __ldg(p.bias + i) : 0.f;
+      scale_s[i] = (col_scale && i < p.Cout) ? __ldg(p.scale_b + i) : 1.f;
+    }
     asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
   }
   unsigned int* pending_counter = nullptr;   // issuer only: stores of the previous tile not yet signalled
@@ -543,7 +633,9 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
     }
   };
   const uint32_t pair_rank = p.pair ? cluster_ctarank() : 0u;
-  for (int it = 0; !aborted; ++it) {
+  const bool teams = p.epi_teams != 0;
+  const int c_first = teams ? 0 : half, c_step = teams ? 1 : 2;
+  for (int it = teams ? half : 0; !aborted; it += teams ? 2 : 1) {
     const long long tile_ll = static_cast<long long>(work_first(p)) + static_cast<long long>(it) * p.gemm_ctas;
     if (tile_ll >= p.total_tiles) break;
     if (issuer) flush_signal();
@@ -572,7 +664,10 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
                                 ? __ldg(p.scale_a + (static_cast<long long>(img) * p.Ho + oh) * p.Wo + ow) : 1.f;
     if (p.n_tiles > 1) {
       // the previous tile's chunks of this half were all staged before its last barrier, so the slice is free
-      for (int i = tt; i < BN; i += 128) bias_s[i] = (p.bias != nullptr && colbase + i < p.Cout) ? __ldg(p.bias + colbase + i) : 0.f;
+      for (int i = tt; i < BN; i += 128) {
+        bias_s[i] = (p.bias != nullptr && colbase + i < p.Cout) ? __ldg(p.bias + colbase + i) : 0.f;
+        scale_s[i] = (col_scale && colbase + i < p.Cout) ? __ldg(p.scale_b + colbase + i) : 1.f;
+      }
     }
     // The leader warp waits for the accumulator; the other warps sleep at the named barrier, which wakes
     // them faster than separate polls would. Every half waits here, also one without a chunk in this tile:
@@ -586,7 +681,7 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
     asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
     if (*abort_sample != 0) { aborted = true; break; }
     tc_fence_after();
-    for (int c = half; c < nchunks; c += 2) {
+    for (int c = c_first; c < nchunks; c += c_step) {
       const int co0 = colbase + c * kChunkCols;
       uint4 rpre[4];
 #pragma unroll
@@ -602,8 +697,8 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
       uint32_t v[32];
       tmem_ld_32x32(t_row + c * kChunkCols, v);
       tmem_ld_wait_dep(v);
-      if (issuer && c + 2 >= nchunks) trace_mark(p, it, 9);
-      const bool last = c + 2 >= nchunks;
+      const bool last = c + c_step >= nchunks;
+      if (issuer && last) trace_mark(p, it, 9);
       if (last) {        // this half's last TMEM read of the accumulator
         tc_fence_before();
         __syncwarp();
@@ -615,16 +710,23 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
       }
       // buffer `par` is free: the store that last read it was waited for before the previous chunk's barrier
       const uint32_t buf = buf0 + par * kChunkBytes;
-      const uint32_t srow = buf + row * 64;
+      const uint32_t srow = buf + row * row_bytes;
       if (valid) {
         const float* bs = bias_s + c * kChunkCols;
-        if (simple) {
+        const float* ss = scale_s + c * kChunkCols;
+        if (out8) {          // host side: only planned with simple == true and no residual
+          if (col_scale) staged_chunk_e4m3<ACT, true>(v, bs, ss, srow, row_sw1, p);
+          else staged_chunk_e4m3<ACT, false>(v, bs, ss, srow, row_sw1, p);
+        } else if (simple && col_scale) {
+          if (out_bf16) staged_chunk<ACT, true, false, true>(v, bs, ss, rpre, srow, row_sw, p);
+          else staged_chunk<ACT, false, false, true>(v, bs, ss, rpre, srow, row_sw, p);
+        } else if (simple) {
           if (out_bf16) {
-            if (res_pre) staged_chunk<ACT, true, true>(v, bs, rpre, srow, row_sw, p);
-            else staged_chunk<ACT, true, false>(v, bs, rpre, srow, row_sw, p);
+            if (res_pre) staged_chunk<ACT, true, true, false>(v, bs, ss, rpre, srow, row_sw, p);
+            else staged_chunk<ACT, true, false, false>(v, bs, ss, rpre, srow, row_sw, p);
           } else {
-            if (res_pre) staged_chunk<ACT, false, true>(v, bs, rpre, srow, row_sw, p);
-            else staged_chunk<ACT, false, false>(v, bs, rpre, srow, row_sw, p);
+            if (res_pre) staged_chunk<ACT, false, true, false>(v, bs, ss, rpre, srow, row_sw, p);
+            else staged_chunk<ACT, false, false, false>(v, bs, ss, rpre, srow, row_sw, p);
           }
         } else {
 #pragma unroll
@@ -671,7 +773,7 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
       }
       par ^= 1;
     }
-    if (half >= nchunks) {   // nothing to drain in this tile: hand the accumulator back at once
+    if (!teams && half >= nchunks) {   // nothing to drain in this tile: hand the accumulator back at once
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
@@ -699,7 +801,7 @@ __device__ __forceinline__ void epilogue_loop(const ConvGemmParams& p, uint32_t 
   const int c_begin = half == 0 ? 0 : kChunksHalf0;
   const int c_end = half == 0 ? kChunksHalf0 : kChunks;
   const bool in_bf16 = p.in_bf16 != 0;
-  const int out_es = p.out_dtype == kF32 ? 4 : 2;
+  const int out_es = p.out_dtype == kF32 ? 4 : (p.out_dtype == kF8E4M3 ? 1 : 2);
   int acc = 0;
   uint32_t acc_ph = 0;
   const uint32_t pair_rank = p.pair ? cluster_ctarank() : 0u;
@@ -768,8 +870,8 @@ __device__ __forceinline__ void epilogue_loop(const ConvGemmParams& p, uint32_t 
   }
 }
 
-constexpr int kMaxSmem = 232448 - 3072;  // 227 KB opt-in limit per CTA less the static shared memory
-constexpr int kBiasFloats = 512;      // shared-memory bias: two tile slices of up to 256 columns
+constexpr int kMaxSmem = 232448 - 5120;  // 227 KB opt-in limit per CTA less the static shared memory
+constexpr int kBiasFloats = 1024;     // shared memory: per epilogue half a bias slice and a column-scale slice of up to 256 columns
 constexpr int kBarBytes = 256;
 
 constexpr int next_pow2_cols(int c) { return c <= 32 ? 32 : c <= 64 ? 64 : c <= 128 ? 128 : c <= 256 ? 256 : 512; }
@@ -820,7 +922,7 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
       // a pair's accumulator is handed back by the epilogue warps of both CTAs
-      mbar_init(tempty_bar(a), kEpiWarps * (PAIR ? 2 : 1));
+      mbar_init(tempty_bar(a), ((p.y_tma && p.epi_teams) ? kTeamWarps : kEpiWarps) * (PAIR ? 2 : 1));
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -837,13 +939,14 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (!PAIR && blockIdx.x >= p.gemm_ctas) {
+  const int first_copier = PAIR ? 2 * p.gemm_ctas : p.gemm_ctas;   // GEMM CTAs come first, in pairs when PAIR
+  if (static_cast<int>(blockIdx.x) >= first_copier) {
     // ------------------------------------------------------------ copier CTA (all-gather -> GEMM)
     // Pulls the remote shards of A over NVLink into this rank's gathered buffer, one 128-row block
     // at a time in the order the GEMM CTAs will want them, and publishes a flag per block. Each
     // remote row crosses NVLink exactly once however many column tiles later read it from HBM / L2.
-    const int copiers = static_cast<int>(gridDim.x) - p.gemm_ctas;
-    const int c = static_cast<int>(blockIdx.x) - p.gemm_ctas;
+    const int copiers = static_cast<int>(gridDim.x) - first_copier;
+    const int c = static_cast<int>(blockIdx.x) - first_copier;
     const int per_shard = p.peer_rows / p.tw;
     const long long blk_vecs = static_cast<long long>(p.tw) * p.gather_row_bytes / 16;
     for (int j = per_shard + c; j < p.tiles_w; j += copiers) {      // rotated order, remote blocks only
@@ -879,7 +982,7 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const TileCoord tc = decode_tile(p, tile);
         const int n_tile = tc.n_tile, thi = tc.thi, img = tc.img;
         int twi = tc.twi;
-        if (!PAIR && p.peer_mode == 1) {
+        if (p.peer_mode == 1) {
           // local rows first, then the shards in the order the copier CTAs bring them in
           twi += p.peer_rot;
           if (twi >= p.tiles_w) twi -= p.tiles_w;
@@ -981,7 +1084,8 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint64_t adesc = desc_hi | ((a_addr & 0x3FFFF) >> 4);
           const uint64_t bdesc = desc_hi | (((a_addr + Cfg::kABytes) & 0x3FFFF) >> 4);
           if (PAIR) {
-            umma_f16_ksteps_pair(d_tmem, adesc, bdesc, p.idesc, k != 0 ? 1u : 0u, ksteps);
+            if (p.fp8) umma_f8_ksteps_pair(d_tmem, adesc, bdesc, p.idesc, k != 0 ? 1u : 0u, ksteps);
+            else umma_f16_ksteps_pair(d_tmem, adesc, bdesc, p.idesc, k != 0 ? 1u : 0u, ksteps);
             umma_commit_pair(empty_bar(s));      // frees the stage in both CTAs
           } else {
             if (p.fp8) umma_f8_ksteps(d_tmem, adesc, bdesc, p.idesc, k != 0 ? 1u : 0u, ksteps);
@@ -1075,7 +1179,7 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (int s = 0; s < SB; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull0 + 8u * a, 1);
-      mbar_init(tempty0 + 8u * a, kEpiWarps * (PAIR ? 2 : 1));
+      mbar_init(tempty0 + 8u * a, ((p.y_tma && p.epi_teams) ? kTeamWarps : kEpiWarps) * (PAIR ? 2 : 1));
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -1283,6 +1387,7 @@ static int launch_pair_inst(ConvGemmOp* op, cudaStream_t stream) {
                                      Cfg::kSmemBytes));
     attr_set[dev] = true;
   }
+  if (op->prm.peer_mode == 1) ++op->prm.peer_epoch;   // the ready flags of this launch
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(op->grid, 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
@@ -1455,8 +1560,11 @@ using namespace fdb;
 FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   const bool fp8 = d->dtype == kF8E4M3;
   if (d->dtype != kF16 && d->dtype != kBF16 && !fp8) { set_error("conv_gemm: dtype must be fp16, bf16 or fp8 e4m3"); return nullptr; }
-  if (fp8 && (d->residual != nullptr || d->w_batched || d->peer_mode != 0 || d->halo_mode == 1)) {
-    set_error("conv_gemm: fp8 operands take the plain kernel without residual, batched weights or peer modes"); return nullptr;
+  if (fp8 && (d->residual != nullptr || d->w_batched || d->halo_mode == 1)) {
+    set_error("conv_gemm: fp8 operands take the plain kernel without residual or batched weights"); return nullptr;
+  }
+  if (d->out_dtype == kF8E4M3 && (d->peer_mode == 2 || d->residual != nullptr)) {
+    set_error("conv_gemm: an e4m3 output cannot be combined with a residual or the reduce-scatter mode"); return nullptr;
   }
   const int es = fp8 ? 1 : 2;                 // operand element size
   const int kblk = fp8 ? 2 * kBK : kBK;       // K elements per 128-byte stage row
@@ -1522,6 +1630,7 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   p.Ho = d->Ho; p.Wo = d->Wo; p.Cout = d->Cout; p.y_ld = d->y_ld;
   p.res_ld = d->res_ld; p.res_mode = d->residual ? d->res_mode : 0;
   p.out_dtype = d->out_dtype; p.in_bf16 = d->dtype == kBF16;
+  p.out_scale = d->out_scale != 0.f ? d->out_scale : 1.f;
   p.KH = d->KH; p.KW = d->KW; p.stride = d->stride; p.pad_h = d->pad_h; p.pad_w = d->pad_w;
   p.act = d->act; p.act_alpha = d->act_alpha; p.act_beta = d->act_beta;
   p.b_batched = d->w_batched;
@@ -1532,7 +1641,7 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   p.res_n_stride = d->res_n_stride > 0 ? d->res_n_stride : static_cast<long long>(d->Ho) * d->Wo * d->res_ld;
   p.a_bytes = static_cast<uint32_t>(tw * th * kBK * 2);
   p.idesc = make_idesc(d->dtype == kBF16 ? 1u : 0u, kBM, bn);   // format 0 = F16 (kind::f16) or E4M3 (kind::f8f6f4)
-  const int out_es = d->out_dtype == kF32 ? 4 : 2;
+  const int out_es = d->out_dtype == kF32 ? 4 : (d->out_dtype == kF8E4M3 ? 1 : 2);
   p.y_vec = (reinterpret_cast<uintptr_t>(d->y) % 16 == 0) && ((d->y_ld * out_es) % 16 == 0) &&
             (d->bias == nullptr || reinterpret_cast<uintptr_t>(d->bias) % 16 == 0);
   p.res_vec = d->residual && (reinterpret_cast<uintptr_t>(d->residual) % 16 == 0) && (d->res_ld % 8 == 0);
@@ -1597,9 +1706,9 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   // ---- CTA pairs: two pixel tiles of one column tile per MMA, half of the weight tile staged per CTA
   if (!op->halo && d->pair_mode != 0) {
     const long mt = static_cast<long>(p.tiles_w) * p.tiles_h * d->N;
-    const bool can = !fp8 && !d->w_batched && d->peer_mode == 0 && bn >= 64 && mt >= 2 && d->max_ctas != 1;
+    const bool can = !d->w_batched && bn >= 64 && mt >= 2 && d->max_ctas != 1;
     if (d->pair_mode == 1 && !can) {
-      set_error("conv_gemm: CTA pairs need 16-bit operands, shared weights, block_n >= 64, no peer mode, 2+ tiles");
+      set_error("conv_gemm: CTA pairs need shared weights, block_n >= 64, 2+ tiles");
       delete op; return nullptr;
     }
     // worthwhile when the weight tile is a large share of the operand traffic and there is work for every pair
@@ -1663,21 +1772,27 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   p.y_tma = 0;
   {
     const bool out16 = d->out_dtype == kF16 || d->out_dtype == kBF16;
-    const bool aligned = reinterpret_cast<uintptr_t>(d->y) % 16 == 0 && (d->y_ld * 2) % 16 == 0 &&
-                         (p.y_h_stride * 2) % 16 == 0 && (p.y_n_stride * 2) % 16 == 0;
+    // e4m3 results take the same staged path (32-byte rows) when nothing but bias, column scale and activation
+    // sits between the accumulator and the store
+    const bool out8 = d->out_dtype == kF8E4M3 && d->residual == nullptr && (!fp8 || d->scale_a == nullptr);
+    const int yes = out8 ? 1 : 2;
+    const bool aligned = reinterpret_cast<uintptr_t>(d->y) % 16 == 0 && (d->y_ld * yes) % 16 == 0 &&
+                         (p.y_h_stride * yes) % 16 == 0 && (p.y_n_stride * yes) % 16 == 0;
     const bool cols_ok = p.n_tiles == 1 || bn % kChunkCols == 0;
-    if (out16 && aligned && cols_ok && d->y_tma_mode != 0) {
-      const CUtensorMapDataType ydt =
-          d->out_dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    if ((out16 || out8) && aligned && cols_ok && d->y_tma_mode != 0) {
+      const CUtensorMapDataType ydt = out8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+          : d->out_dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
       cuuint64_t dims[4] = {(cuuint64_t)d->Cout, (cuuint64_t)d->Wo, (cuuint64_t)d->Ho, (cuuint64_t)d->N};
-      cuuint64_t strides[3] = {(cuuint64_t)d->y_ld * 2, (cuuint64_t)p.y_h_stride * 2, (cuuint64_t)p.y_n_stride * 2};
+      cuuint64_t strides[3] = {(cuuint64_t)d->y_ld * yes, (cuuint64_t)p.y_h_stride * yes, (cuuint64_t)p.y_n_stride * yes};
       cuuint32_t box[4] = {kChunkCols, (cuuint32_t)p.tw, (cuuint32_t)p.th, 1};
       cuuint32_t estr[4] = {1, 1, 1, 1};
       CUresult r = enc(&op->tmY, ydt, 4, d->y, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                       CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                       out8 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       if (r == CUDA_SUCCESS) p.y_tma = 1;
     }
     if (!p.y_tma) op->tmY = op->tmA;   // a valid map is still passed; the kernel does not touch it
+    p.epi_teams = bn <= 64 ? 1 : 0;
   }
   p.peer = nullptr;
   p.peer_mode = 0; p.peer_rows = 0; p.peer_rank = 0;
@@ -1729,19 +1844,32 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
     p.peer_mode = d->peer_mode; p.peer_rows = d->peer_rows; p.peer_rank = d->peer_rank;
     p.peer_world = d->peer_world;
     if (d->peer_mode == 1) {
-      if (d->peer_ready == nullptr || (static_cast<long long>(d->x_ld) * 2) % 16 != 0) {
+      if (d->peer_ready == nullptr || (static_cast<long long>(d->x_ld) * es) % 16 != 0) {
         set_error("conv_gemm: all-gather mode needs ready flags and 16-byte rows"); delete op; return nullptr;
       }
       const int remote_blocks = p.tiles_w - d->peer_rows / p.tw;
       int copiers = d->peer_copiers > 0 ? d->peer_copiers : 20;
       copiers = std::min(copiers, std::min(remote_blocks, op->grid / 2));
-      op->grid = std::max(op->grid, copiers + 1);
-      p.gemm_ctas = op->grid - std::max(copiers, 0);
+      if (op->pair) {
+        // clusters of two throughout: an even number of copier CTAs behind the GEMM pairs
+        copiers = (std::max(copiers, 0) + 1) / 2 * 2;
+        const int total = std::max(op->grid, copiers + 2);
+        op->grid = (total - copiers) / 2 * 2 + copiers;
+        p.gemm_ctas = (op->grid - copiers) / 2;
+      } else {
+        op->grid = std::max(op->grid, copiers + 1);
+        p.gemm_ctas = op->grid - std::max(copiers, 0);
+      }
+      // the copier CTAs and the GEMM CTAs wait on one another inside this launch: all of them must be resident
+      if (op->grid > sms) {
+        set_error("conv_gemm: the all-gather GEMM needs every CTA resident at once (grid <= SM count)");
+        delete op; return nullptr;
+      }
       p.peer_rot = d->peer_rank * (d->peer_rows / p.tw);
       p.peer_epoch = 0;
       p.ready = d->peer_ready;
       p.gather_dst = static_cast<uint8_t*>(const_cast<void*>(d->x));
-      p.gather_row_bytes = static_cast<long long>(d->x_ld) * 2;
+      p.gather_row_bytes = static_cast<long long>(d->x_ld) * es;
     }
   }
   if (p.peer_mode != 1) p.gemm_ctas = op->pair ? op->grid / 2 : op->grid;

@@ -15,6 +15,7 @@
 // own pooling kernel is the adaptive pool of runtime/backends/common/cuda/adaptive_pool2d_kernel.cu:20-59.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include <algorithm>
 #include <functional>
@@ -275,6 +276,29 @@ __global__ void __launch_bounds__(256) scale_weights_kernel(const uint8_t* __res
   }
 }
 
+// ---- static quantisation to e4m3: y[r][c] = e4m3(x[r][c] * scale) ----------------------------------
+// 16-bit rows in, byte rows out (8 elements per thread step). Used where a GEMM's fp8 input comes from a
+// kernel that cannot quantise in its own epilogue (the attention output in front of the projection).
+template <bool BF16>
+__global__ void __launch_bounds__(256) quantize_e4m3_kernel(const uint8_t* __restrict__ x, uint8_t* __restrict__ y,
+                                                            long long total, int C8, int x_ld, int y_ld, float scale) {
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int cg = static_cast<int>(idx % C8);
+    const long long r = idx / C8;
+    float f[8];
+    unpack8f<BF16>(__ldg(reinterpret_cast<const uint4*>(x + (r * x_ld + cg * 8) * 2)), f);
+    uint32_t w[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * h] * scale, f[4 * h + 1] * scale), __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * h + 2] * scale, f[4 * h + 3] * scale), __NV_SATFINITE, __NV_E4M3);
+      w[h] = lo | (hi << 16);
+    }
+    *reinterpret_cast<uint2*>(y + r * y_ld + cg * 8) = make_uint2(w[0], w[1]);
+  }
+}
+
 }  // namespace fdb
 
 using namespace fdb;
@@ -387,6 +411,24 @@ FDB_API void* fdb_fused_create(int kind, const FusedDesc* dp) {
         const int grid = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));
         if (bf) scale_weights_kernel<true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (const float*)d.p[1], (uint8_t*)d.p[2], total, Cout, Kp / 8, Cin, gld, plus);
         else scale_weights_kernel<false><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (const float*)d.p[1], (uint8_t*)d.p[2], total, Cout, Kp / 8, Cin, gld, plus);
+        FDB_FUSED_CHECK();
+      };
+      break;
+    }
+    case 4: {
+      // quantize_e4m3: p0 x 16-bit [rows][x_ld], p1 y e4m3 [rows][y_ld]; i0 rows, i1 C, i2 x_ld, i3 y_ld, i4 bf16; f0 scale
+      const long long rows = d.i[0];
+      const int C = d.i[1], x_ld = d.i[2], y_ld = d.i[3];
+      const bool bf = d.i[4] != 0;
+      const float scale = d.f[0];
+      if (C % 8 || x_ld % 8 || y_ld % 8 || (reinterpret_cast<uintptr_t>(d.p[0]) & 15) || (reinterpret_cast<uintptr_t>(d.p[1]) & 7)) {
+        set_error("quantize_e4m3: C and row pitches must be multiples of 8, pointers aligned"); delete op; return nullptr;
+      }
+      const long long total = rows * (C / 8);
+      op->fn = [=](cudaStream_t s) {
+        const int grid = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));
+        if (bf) quantize_e4m3_kernel<true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], total, C / 8, x_ld, y_ld, scale);
+        else quantize_e4m3_kernel<false><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], total, C / 8, x_ld, y_ld, scale);
         FDB_FUSED_CHECK();
       };
       break;

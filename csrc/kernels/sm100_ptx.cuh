@@ -394,6 +394,33 @@ __device__ __forceinline__ void umma_f16_ksteps_pair(uint32_t tmem_d, uint64_t a
       : "memory");
 }
 
+// The same K block for e4m3 operands (K = 32 per step) on a CTA pair.
+__device__ __forceinline__ void umma_f8_ksteps_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                    uint32_t accumulate_first, uint32_t nsteps) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p0, p1, q1, q2, q3;\n"
+      ".reg .b64 a1, a2, a3, b1, b2, b3;\n"
+      "setp.ne.b32 p0, %4, 0;\n"
+      "setp.eq.u32 p1, %3, %3;\n"
+      "setp.gt.u32 q1, %5, 1;\n"
+      "setp.gt.u32 q2, %5, 2;\n"
+      "setp.gt.u32 q3, %5, 3;\n"
+      "add.s64 a1, %1, 2;\n"
+      "add.s64 b1, %2, 2;\n"
+      "add.s64 a2, %1, 4;\n"
+      "add.s64 b2, %2, 4;\n"
+      "add.s64 a3, %1, 6;\n"
+      "add.s64 b3, %2, 6;\n"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p0;\n"
+      "@q1 tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], a1, b1, %3, p1;\n"
+      "@q2 tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], a2, b2, %3, p1;\n"
+      "@q3 tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], a3, b3, %3, p1;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate_first), "r"(nsteps)
+      : "memory");
+}
+
 // ---------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor for a K-major operand tile whose rows are
 // `row_bytes` (32/64/128) wide and stored with the matching TMA swizzle.

@@ -7,6 +7,7 @@
 // (fastdeploy/runtime/backends/paddle/paddle_backend.cc:426 predictor_->Run()).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include <functional>
 
@@ -107,10 +108,25 @@ __global__ void layernorm_kernel(const uint8_t* __restrict__ x, uint8_t* __restr
 
 // ---- LayerNorm with the row held in registers (C <= 2048): every load of the row is in flight before the
 // first use, the row is read from memory once, and the statistics take two register passes.
-template <bool BF16>
+// Eight floats -> eight e4m3 bytes (saturating).
+__device__ __forceinline__ uint2 pack8_e4m3(const float (&f)[8]) {
+  uint32_t w[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * h], f[4 * h + 1]), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * h + 2], f[4 * h + 3]), __NV_SATFINITE, __NV_E4M3);
+    w[h] = lo | (hi << 16);
+  }
+  return make_uint2(w[0], w[1]);
+}
+
+// OUT8: the normalised row is multiplied by out_scale (the reciprocal of the consumer GEMM's activation
+// scale) and stored as e4m3, one byte per element (y_ld counts bytes then).
+template <bool BF16, bool OUT8>
 __global__ void __launch_bounds__(256) layernorm_reg_kernel(const uint8_t* __restrict__ x, uint8_t* __restrict__ y,
                                                             const float* __restrict__ gamma, const float* __restrict__ beta,
-                                                            long long rows, int C, int x_ld, int y_ld, float eps) {
+                                                            long long rows, int C, int x_ld, int y_ld, float eps,
+                                                            float out_scale) {
   const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -138,7 +154,7 @@ __global__ void __launch_bounds__(256) layernorm_reg_kernel(const uint8_t* __res
     }
   }
   const float rstd = rsqrtf(warp_sum(ss) / C + eps);
-  uint8_t* yr = y + row * y_ld * 2;
+  uint8_t* yr = y + row * y_ld * (OUT8 ? 1 : 2);
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     const int c = lane * 8 + k * 256;
@@ -158,9 +174,10 @@ __global__ void __launch_bounds__(256) layernorm_reg_kernel(const uint8_t* __res
         float t = (v[k][j] - mean) * rstd;
         if (gamma) t *= g[j];
         if (beta) t += b[j];
-        f[j] = t;
+        f[j] = OUT8 ? t * out_scale : t;
       }
-      *reinterpret_cast<uint4*>(yr + c * 2) = pack8<BF16>(f);
+      if (OUT8) *reinterpret_cast<uint2*>(yr + c) = pack8_e4m3(f);
+      else *reinterpret_cast<uint4*>(yr + c * 2) = pack8<BF16>(f);
     }
   }
 }
@@ -326,13 +343,19 @@ FDB_API void* fdb_transformer_create(int kind, const TfDesc* dp) {
       const long long rows = d.i[0];
       const int C = d.i[1], x_ld = d.i[2], y_ld = d.i[3];
       const bool bf = d.i[4] != 0;
-      const float eps = d.f[0];
+      const bool out8 = d.i[5] != 0;        // e4m3 output, scaled by f1
+      const float eps = d.f[0], out_scale = d.f[1];
       if (C % 8 || x_ld % 8 || y_ld % 8) { set_error("layernorm: C/ld must be multiples of 8"); delete op; return nullptr; }
+      if (out8 && (C > 2048 || reinterpret_cast<uintptr_t>(d.p[2]) % 16 || reinterpret_cast<uintptr_t>(d.p[3]) % 16)) {
+        set_error("layernorm: the e4m3 output form needs C <= 2048 and aligned gamma / beta"); delete op; return nullptr;
+      }
       op->fn = [=](cudaStream_t s) {
         const int grid = static_cast<int>((rows * 32 + 255) / 256);
         const bool regs = C <= 2048 && (reinterpret_cast<uintptr_t>(d.p[2]) % 16 == 0) && (reinterpret_cast<uintptr_t>(d.p[3]) % 16 == 0);
-        if (regs && bf) layernorm_reg_kernel<true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps);
-        else if (regs) layernorm_reg_kernel<false><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps);
+        if (out8 && bf) layernorm_reg_kernel<true, true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps, out_scale);
+        else if (out8) layernorm_reg_kernel<false, true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps, out_scale);
+        else if (regs && bf) layernorm_reg_kernel<true, false><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps, 1.f);
+        else if (regs) layernorm_reg_kernel<false, false><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps, 1.f);
         else if (bf) layernorm_kernel<true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps);
         else layernorm_kernel<false><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps);
         FDB_TF_CHECK();

@@ -20,14 +20,20 @@ def run(ctx: Context, args) -> dict:
     cfg = VIT_SIZES[size]
     T = (image // cfg["patch"]) ** 2 + 1
     m_pad = (B * T + world * 128 - 1) // (world * 128) * (world * 128)
-    heap = 4 * m_pad * cfg["hidden"] * 2 + (64 << 20)
+    heap = (2 if dtype_name == "fp8" else 1) * 4 * m_pad * cfg["hidden"] * 2 + (64 << 20)
     comm = Communicator(heap_bytes=heap)
     w = random_vit_weights(cfg, image, 1000, seed=0)
-    model = TensorParallelViT(comm, w, cfg, batch=B, image=image, dtype=dtype,
-                              **({"precision": "fp8"} if dtype_name == "fp8" else {}))
     g = torch.Generator(device="cpu").manual_seed(1)
     host_sets = [torch.rand(B, 3, image, image, generator=g).to(dtype).pin_memory() for _ in range(2)]
     dev_sets = [t.to(dev) for t in host_sets]
+    model = TensorParallelViT(comm, w, cfg, batch=B, image=image, dtype=dtype)
+    if dtype_name == "fp8":
+        # post-training quantisation: static activation scales from one calibration batch of the 16-bit model
+        scales = model.calibrate(dev_sets[0])
+        del model
+        torch.cuda.empty_cache()
+        model = TensorParallelViT(comm, w, cfg, batch=B, image=image, dtype=dtype, precision="fp8", act_scales=scales,
+                                  name="tpvit8")
     sampler = ClockSampler(physical_gpu_index(ctx.local_rank))
     sampler.start()
 

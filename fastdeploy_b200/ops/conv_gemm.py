@@ -43,7 +43,7 @@ class _ConvGemmDesc(ctypes.Structure):
         ("peer_ptrs", ctypes.c_void_p * 8), ("peer_counters", ctypes.c_void_p * 8),
         ("peer_ready", ctypes.c_void_p), ("peer_copiers", ctypes.c_int),
         ("scale_a", ctypes.c_void_p), ("scale_b", ctypes.c_void_p),
-        ("pair_mode", ctypes.c_int),
+        ("pair_mode", ctypes.c_int), ("out_scale", ctypes.c_float),
     ]
 
 
@@ -94,7 +94,7 @@ class ConvGemm(NativeOp):
                  peer_ptrs: Optional[Sequence[int]] = None, peer_counters: Optional[Sequence[int]] = None,
                  peer_ready: Optional[torch.Tensor] = None, peer_copiers: int = 0,
                  scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None,
-                 pair_mode: int = -1):
+                 pair_mode: int = -1, out_scale: float = 1.0):
         n, h, w_, cin = in_shape
         d = _ConvGemmDesc()
         self.status = status or StatusWord(x.device)
@@ -131,6 +131,7 @@ class ConvGemm(NativeOp):
         d.scale_b = scale_b.data_ptr() if scale_b is not None else None
         self.scales = (scale_a, scale_b)
         d.pair_mode = pair_mode
+        d.out_scale = out_scale
         if bias is not None:
             assert bias.dtype == torch.float32
         if residual is not None:

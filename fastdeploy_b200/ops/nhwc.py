@@ -218,3 +218,11 @@ def scale_weights(w_packed: torch.Tensor, gate: torch.Tensor, out: torch.Tensor,
     assert gate.dtype == torch.float32 and out.dtype == w_packed.dtype and out.numel() == n * cout * kp
     return _make_fused(3, [w_packed, gate, out], [n, cout, kp, cin, gate.stride(0), _bf(w_packed)], [plus],
                        name="scale_weights")
+
+
+def quantize_e4m3(x: torch.Tensor, y: torch.Tensor, *, rows: int, c: int, scale: float, x_ld: Optional[int] = None,
+                  y_ld: Optional[int] = None) -> NativeOp:
+    """``y = e4m3(x * scale)`` for 16-bit rows ``x [rows, c]`` (static quantisation: ``scale`` is the reciprocal of
+    the activation scale the consuming fp8 GEMM dequantises with)."""
+    assert y.dtype == torch.float8_e4m3fn
+    return _make_fused(4, [x, y], [rows, c, x_ld or c, y_ld or c, _bf(x)], [scale], name="quantize_e4m3")

@@ -51,8 +51,13 @@ def _bf(t) -> int:
 
 
 def layernorm(x: torch.Tensor, y: torch.Tensor, gamma: Optional[torch.Tensor], beta: Optional[torch.Tensor], *,
-              rows: int, c: int, eps: float = 1e-5, x_ld: Optional[int] = None, y_ld: Optional[int] = None) -> NativeOp:
-    return _make(K_LAYERNORM, [x, y, gamma, beta], [rows, c, x_ld or c, y_ld or c, _bf(x)], [eps], "layernorm")
+              rows: int, c: int, eps: float = 1e-5, x_ld: Optional[int] = None, y_ld: Optional[int] = None,
+              out_scale: float = 1.0) -> NativeOp:
+    """``y = LayerNorm(x) * gamma + beta``. With an e4m3 ``y`` the result is multiplied by ``out_scale`` (the
+    reciprocal of the consumer GEMM's activation scale) and stored as fp8."""
+    out8 = hasattr(torch, "float8_e4m3fn") and y.dtype == torch.float8_e4m3fn
+    return _make(K_LAYERNORM, [x, y, gamma, beta], [rows, c, x_ld or c, y_ld or c, _bf(x), int(out8)], [eps, out_scale],
+                 "layernorm")
 
 
 def embed_layernorm(ids: List[Optional[torch.Tensor]], tables: List[torch.Tensor], y: torch.Tensor,

@@ -109,7 +109,9 @@ def main(argv=None):
     ap.add_argument("--check", action="store_true")
     ap.add_argument("--no-baseline", action="store_true")
     ap.add_argument("--breakdown", action="store_true", help="one rank only: device time of each launch kind")
-    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp8"],
+                    help="fp8: e4m3 operands in the four linears of every block (bf16 elsewhere), static activation "
+                         "scales calibrated on the first batch")
     a = ap.parse_args(argv)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -118,16 +120,22 @@ def main(argv=None):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    dtype = torch.bfloat16 if a.dtype == "bf16" else torch.float16
+    dtype = torch.float16 if a.dtype == "fp16" else torch.bfloat16
     cfg = VIT_SIZES[a.size]
     T = (a.image // cfg["patch"]) ** 2 + 1
     m_pad = (a.batch * T + world * 128 - 1) // (world * 128) * (world * 128)
-    heap = 2 * m_pad * cfg["hidden"] * 2 + 2 * m_pad * cfg["hidden"] * 2 + (64 << 20)
+    heap = (2 if a.dtype == "fp8" else 1) * (2 * m_pad * cfg["hidden"] * 2 + 2 * m_pad * cfg["hidden"] * 2) + (64 << 20)
     comm = Communicator(heap_bytes=heap)
     w = random_vit_weights(cfg, a.image, a.classes, seed=0)
-    model = TensorParallelViT(comm, w, cfg, batch=a.batch, image=a.image, dtype=dtype)
     g = torch.Generator(device="cpu").manual_seed(1)
     images = torch.rand(a.batch, 3, a.image, a.image, generator=g).to(dev).to(dtype)
+    model = TensorParallelViT(comm, w, cfg, batch=a.batch, image=a.image, dtype=dtype)
+    if a.dtype == "fp8":
+        scales = model.calibrate(images)
+        comm.check("tp vit calibration")
+        del model
+        model = TensorParallelViT(comm, w, cfg, batch=a.batch, image=a.image, dtype=dtype, precision="fp8",
+                                  act_scales=scales, name="tpvit8")
     out = {"world": world, "size": a.size, "batch": a.batch, "tokens": a.batch * T, "dtype": a.dtype}
     probs = model.forward(images)
     comm.check("tp vit forward")

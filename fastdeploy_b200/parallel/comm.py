@@ -50,7 +50,8 @@ def _lib():
         lib.fdb_comm_slot_reduce_ln.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint, ctypes.c_void_p,
                                                 ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                                 ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float,
-                                                ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+                                                ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                                                ctypes.c_float]
         lib._comm_ready = True
     return lib
 

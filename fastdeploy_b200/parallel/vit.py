@@ -31,7 +31,8 @@ import torch
 
 from .. import _native
 from ..ops.base import current_stream_ptr, dtype_code
-from ..ops.conv_gemm import ConvGemm, pack_linear_weight
+from ..ops.conv_gemm import ConvGemm, pack_linear_weight, pack_linear_weight_fp8
+from ..ops.nhwc import quantize_e4m3
 from ..ops.transformer import Attention, layernorm
 from .comm import Communicator, _lib
 
@@ -96,8 +97,19 @@ class TensorParallelViT:
 
     def __init__(self, comm: Communicator, weights: Dict[str, torch.Tensor], cfg: Dict[str, int], *, batch: int,
                  image: int = 224, dtype: torch.dtype = torch.bfloat16, eps: float = 1e-6, name: str = "tpvit",
-                 copiers: int = 0):
+                 copiers: int = 0, precision: str = "", act_scales: Optional[Dict[str, float]] = None):
+        """``precision="fp8"``: the four linears of every block run on e4m3 operands (``tcgen05.mma.kind::f8f6f4``,
+        fp32 accumulation). Weights are quantised per output channel; activations with one static scale per
+        tensor and layer (``act_scales``, from :meth:`calibrate` of a 16-bit instance or from a quantised model
+        file): the LayerNorms and the fc1 epilogue write e4m3 directly, the attention output passes through one
+        quantise kernel, so the gathered activations cross NVLink as bytes. The residual stream, attention and
+        the partial sums of the row-parallel GEMMs stay in ``dtype``."""
         self.comm, self.cfg, self.dtype, self.eps = comm, cfg, dtype, eps
+        self.fp8 = precision == "fp8"
+        if self.fp8 and act_scales is None:
+            raise ValueError("precision='fp8' needs act_scales (see TensorParallelViT.calibrate)")
+        self.act_scales = act_scales or {}
+        self.calib: Optional[Dict[str, float]] = None
         ws, r, dev = comm.world, comm.rank, comm.device
         H, NH, F, P, L = cfg["hidden"], cfg["heads"], cfg["mlp"], cfg["patch"], cfg["layers"]
         assert NH % ws == 0 and F % ws == 0 and H % 8 == 0
@@ -139,12 +151,14 @@ class TensorParallelViT:
 
         # ---- shared activation buffers
         self.xres = torch.zeros(rows, H, dtype=dtype, device=dev)            # residual stream, this rank's rows
+        gdt = torch.float8_e4m3fn if self.fp8 else dtype          # what the all-gather GEMMs read
         self.gather_blocks = [comm.alloc(f"{name}.gather{i}", M * H * es) for i in range(2)]
-        self.gathered = [comm.tensor(b, (M, H), dtype) for b in self.gather_blocks]
+        self.gathered = [comm.tensor(b, (M, H), gdt) for b in self.gather_blocks]
         self.shard = [g[r * rows:(r + 1) * rows] for g in self.gathered]
         self.qkv = torch.zeros(M, 3 * hd, dtype=dtype, device=dev)
         self.ctx = torch.zeros(M, hd, dtype=dtype, device=dev)
-        self.ffn = torch.zeros(M, fl, dtype=dtype, device=dev)
+        self.ffn = torch.zeros(M, fl, dtype=gdt, device=dev)
+        self.ctx_q = torch.zeros(M, hd, dtype=gdt, device=dev) if self.fp8 else None
         slot_bytes = ws * rows * H * es
         self.blocks128 = rows // 128
         cnt_bytes = (self.blocks128 * 4 + 1023) // 1024 * 1024
@@ -173,19 +187,42 @@ class TensorParallelViT:
             lay = {}
             lay["ln1_gb"] = (dv(lw["ln1_g"]).float().contiguous(), dv(lw["ln1_b"]).float().contiguous())
             lay["ln2_gb"] = (dv(lw["ln2_g"]).float().contiguous(), dv(lw["ln2_b"]).float().contiguous())
-            lay["ln1"] = layernorm(self.xres, self.shard[0], dv(lw["ln1_g"]).float(), dv(lw["ln1_b"]).float(), rows=rows,
-                                   c=H, eps=eps)
-            lay["ln2"] = layernorm(self.xres, self.shard[1], dv(lw["ln2_g"]).float(), dv(lw["ln2_b"]).float(), rows=rows,
-                                   c=H, eps=eps)
-            lay["qkv"] = self._col(0, gptr[0], pack_linear_weight(w_qkv, dtype), b_qkv, self.qkv, 3 * hd, None,
-                                   f"{name}.{l}.qkv", copiers)
             fs = slice(r * fl, (r + 1) * fl)
-            lay["fc1"] = self._col(1, gptr[1], pack_linear_weight(dv(lw["fc1_w"][fs]), dtype),
-                                   dv(lw["fc1_b"][fs]).float().contiguous(), self.ffn, fl, "gelu", f"{name}.{l}.fc1", copiers)
-            lay["proj"] = self._row(0, sptr[0], cptr[0], self.ctx, hd, pack_linear_weight(dv(lw["proj_w"][:, sl]), dtype),
-                                    f"{name}.{l}.proj")
-            lay["fc2"] = self._row(1, sptr[1], cptr[1], self.ffn, fl, pack_linear_weight(dv(lw["fc2_w"][:, fs]), dtype),
-                                   f"{name}.{l}.fc2")
+            if self.fp8:
+                sc = self.act_scales
+                s_h1, s_ctx, s_h2, s_ffn = sc[f"h1.{l}"], sc[f"ctx.{l}"], sc[f"h2.{l}"], sc[f"ffn.{l}"]
+                lay["scales"] = (s_h1, s_ctx, s_h2, s_ffn)
+                lay["ln1"] = layernorm(self.xres, self.shard[0], dv(lw["ln1_g"]).float(), dv(lw["ln1_b"]).float(),
+                                       rows=rows, c=H, eps=eps, out_scale=1.0 / s_h1)
+                lay["ln2"] = layernorm(self.xres, self.shard[1], dv(lw["ln2_g"]).float(), dv(lw["ln2_b"]).float(),
+                                       rows=rows, c=H, eps=eps, out_scale=1.0 / s_h2)
+                wq, sw = pack_linear_weight_fp8(w_qkv)
+                lay["qkv"] = self._col(0, gptr[0], wq, b_qkv, self.qkv, 3 * hd, None, f"{name}.{l}.qkv", copiers,
+                                       scale_b=(sw * s_h1).contiguous())
+                wq, sw = pack_linear_weight_fp8(dv(lw["fc1_w"][fs]))
+                lay["fc1"] = self._col(1, gptr[1], wq, dv(lw["fc1_b"][fs]).float().contiguous(), self.ffn, fl, "gelu",
+                                       f"{name}.{l}.fc1", copiers, scale_b=(sw * s_h2).contiguous(), out_scale=1.0 / s_ffn)
+                lay["ctx_q"] = quantize_e4m3(self.ctx, self.ctx_q, rows=M, c=hd, scale=1.0 / s_ctx)
+                wq, sw = pack_linear_weight_fp8(dv(lw["proj_w"][:, sl]))
+                lay["proj"] = self._row(0, sptr[0], cptr[0], self.ctx_q, hd, wq, f"{name}.{l}.proj",
+                                        scale_b=(sw * s_ctx).contiguous())
+                wq, sw = pack_linear_weight_fp8(dv(lw["fc2_w"][:, fs]))
+                lay["fc2"] = self._row(1, sptr[1], cptr[1], self.ffn, fl, wq, f"{name}.{l}.fc2",
+                                       scale_b=(sw * s_ffn).contiguous())
+            else:
+                lay["ln1"] = layernorm(self.xres, self.shard[0], dv(lw["ln1_g"]).float(), dv(lw["ln1_b"]).float(),
+                                       rows=rows, c=H, eps=eps)
+                lay["ln2"] = layernorm(self.xres, self.shard[1], dv(lw["ln2_g"]).float(), dv(lw["ln2_b"]).float(),
+                                       rows=rows, c=H, eps=eps)
+                lay["qkv"] = self._col(0, gptr[0], pack_linear_weight(w_qkv, dtype), b_qkv, self.qkv, 3 * hd, None,
+                                       f"{name}.{l}.qkv", copiers)
+                lay["fc1"] = self._col(1, gptr[1], pack_linear_weight(dv(lw["fc1_w"][fs]), dtype),
+                                       dv(lw["fc1_b"][fs]).float().contiguous(), self.ffn, fl, "gelu", f"{name}.{l}.fc1",
+                                       copiers)
+                lay["proj"] = self._row(0, sptr[0], cptr[0], self.ctx, hd,
+                                        pack_linear_weight(dv(lw["proj_w"][:, sl]), dtype), f"{name}.{l}.proj")
+                lay["fc2"] = self._row(1, sptr[1], cptr[1], self.ffn, fl,
+                                       pack_linear_weight(dv(lw["fc2_w"][:, fs]), dtype), f"{name}.{l}.fc2")
             lay["proj_b"] = dv(lw["proj_b"]).float().contiguous()
             lay["fc2_b"] = dv(lw["fc2_b"]).float().contiguous()
             self.layers.append(lay)
@@ -204,20 +241,30 @@ class TensorParallelViT:
         self.head_b = dv(weights["head_b"]).float()
 
     # ------------------------------------------------------------------ op builders
-    def _col(self, which, ptrs, w, bias, y, n_local, act, name, copiers):
-        ready = torch.zeros(self.M // 128, dtype=torch.int32, device=self.comm.device)
+    def _col(self, which, ptrs, w, bias, y, n_local, act, name, copiers, scale_b=None, out_scale=1.0):
         c = self.comm
+        if c.world == 1:      # nothing to gather: a plain GEMM on the local buffer
+            return ConvGemm(self.gathered[which], w, y, in_shape=(1, 1, self.M, self.H), out_hw=(1, self.M),
+                            cout=n_local, bias=bias, act=act, x_ld=self.H, y_ld=y.stride(0), status=c.status, name=name,
+                            scale_b=scale_b, out_scale=out_scale)
+        ready = torch.zeros(self.M // 128, dtype=torch.int32, device=self.comm.device)
         return ConvGemm(self.gathered[which], w, y, in_shape=(1, 1, self.M, self.H), out_hw=(1, self.M), cout=n_local,
                         bias=bias, act=act, x_ld=self.H, y_ld=y.stride(0), status=c.status, name=name, peer_mode=1,
                         peer_rows=self.rows, peer_rank=c.rank, peer_world=c.world, peer_ptrs=ptrs, peer_ready=ready,
-                        peer_copiers=copiers)
+                        peer_copiers=copiers, scale_b=scale_b, out_scale=out_scale)
 
-    def _row(self, which, slot_ptrs, cnt_ptrs, x, k_local, w, name):
+    def _row(self, which, slot_ptrs, cnt_ptrs, x, k_local, w, name, scale_b=None):
         c = self.comm
+        if c.world == 1:      # the only slot is local: a plain GEMM writes it, stream order replaces the counters
+            op = ConvGemm(x, w, self.slots[which].view(self.rows, self.H), in_shape=(1, 1, self.M, k_local),
+                          out_hw=(1, self.M), cout=self.H, x_ld=x.stride(0), y_ld=self.H, status=c.status, name=name,
+                          scale_b=scale_b)
+            op.stores_per_block = 0
+            return op
         op = ConvGemm(x, w, self.slots[which].view(c.world * self.rows, self.H), in_shape=(1, 1, self.M, k_local),
                       out_hw=(1, self.M), cout=self.H, x_ld=x.stride(0), y_ld=self.H, status=c.status, name=name,
                       peer_mode=2, peer_rows=self.rows, peer_rank=c.rank, peer_world=c.world, peer_ptrs=slot_ptrs,
-                      peer_counters=cnt_ptrs)
+                      peer_counters=cnt_ptrs, scale_b=scale_b)
         info = op.info()
         bn = info["block_n"]
         n_tiles = (self.H + bn - 1) // bn
@@ -232,12 +279,14 @@ class TensorParallelViT:
         self.targets[which] += c.world * op.stores_per_block
         P = ctypes.c_void_p
         if ln is not None:
-            gamma, beta, out = ln
+            gamma, beta, out = ln[:3]
+            out_scale = ln[3] if len(ln) > 3 else 1.0
+            out8 = out.dtype == torch.float8_e4m3fn
             rc = _lib().fdb_comm_slot_reduce_ln(
                 P(self.slots[which].data_ptr()), P(self.counters[which].data_ptr()), self.targets[which],
                 P(self.xres.data_ptr()), P(bias.data_ptr()), self.rows, self.H, c.world, dtype_code(self.dtype),
                 c.status.ptr, P(gamma.data_ptr()), P(beta.data_ptr()), self.eps, P(out.data_ptr()), out.stride(0),
-                P(current_stream_ptr()))
+                P(current_stream_ptr()), int(out8), float(out_scale))
         else:
             rc = _lib().fdb_comm_slot_reduce_res(
                 P(self.slots[which].data_ptr()), P(self.counters[which].data_ptr()), self.targets[which],
@@ -270,28 +319,65 @@ class TensorParallelViT:
         rides on the slot reduction in front of it (``fuse_ln``)."""
         c = self.comm
         n = len(self.layers)
+        real = max(self.row1 - self.row0, 0)          # this rank's rows that carry tokens (the rest is padding)
+        rec = self._record if self.calib is not None else (lambda *a: None)
         for l, lay in enumerate(self.layers):
             if l == 0 or not self.fuse_ln:
                 lay["ln1"].launch()
+            rec(f"h1.{l}", self.shard[0][:real])
             c.barrier()
             lay["qkv"].launch()
             self.attn.launch()
+            rec(f"ctx.{l}", self.ctx[:self.m_real])
+            if self.fp8:
+                lay["ctx_q"].launch()
             lay["proj"].launch()
             if self.fuse_ln:
-                self._reduce_into_residual(0, lay["proj"], lay["proj_b"], lay["ln2_gb"] + (self.shard[1],))
+                ln2 = lay["ln2_gb"] + (self.shard[1],) + ((1.0 / lay["scales"][2],) if self.fp8 else ())
+                self._reduce_into_residual(0, lay["proj"], lay["proj_b"], ln2)
             else:
                 self._reduce_into_residual(0, lay["proj"], lay["proj_b"])
                 lay["ln2"].launch()
+            rec(f"h2.{l}", self.shard[1][:real])
             c.barrier()
             lay["fc1"].launch()
+            rec(f"ffn.{l}", self.ffn[:self.m_real])
             lay["fc2"].launch()
             if self.fuse_ln:
-                nxt = self.layers[l + 1]["ln1_gb"] + (self.shard[0],) if l + 1 < n else self.ln_f_gb + (self.final,)
+                if l + 1 < n:
+                    nxt = self.layers[l + 1]["ln1_gb"] + (self.shard[0],) + \
+                        ((1.0 / self.layers[l + 1]["scales"][0],) if self.fp8 else ())
+                else:
+                    nxt = self.ln_f_gb + (self.final,)
                 self._reduce_into_residual(1, lay["fc2"], lay["fc2_b"], nxt)
             else:
                 self._reduce_into_residual(1, lay["fc2"], lay["fc2_b"])
         if not self.fuse_ln:
             self.ln_f.launch()
+
+    # ------------------------------------------------------------------ fp8 calibration
+    def _record(self, key: str, t: torch.Tensor) -> None:
+        v = float(t.float().abs().max()) if t.numel() else 0.0
+        self.calib[key] = max(self.calib.get(key, 0.0), v)
+
+    def calibrate(self, images: torch.Tensor, margin: float = 1.0) -> Dict[str, float]:
+        """Runs one forward of this (16-bit) model on sample ``images`` and returns the static activation scales
+        of the fp8 form: per layer the absolute maximum of the four GEMM inputs (both LayerNorm outputs, the
+        attention output, the GELU output), maximum over the ranks, divided by the e4m3 range 448 (times
+        ``margin``). This is the post-training-quantisation recipe of the reference's int8 path (static
+        per-tensor activation scales from calibration data) with fp8 as the storage type."""
+        assert not self.fp8, "calibrate a 16-bit instance"
+        self.calib = {}
+        try:
+            self.forward(images)
+            torch.cuda.synchronize()
+            keys = sorted(self.calib)
+            t = torch.tensor([self.calib[k] for k in keys], device=self.comm.device, dtype=torch.float32)
+            if self.comm.world > 1:
+                self.comm.dist.all_reduce(t, op=self.comm.dist.ReduceOp.MAX, group=self.comm.group)
+            return {k: max(float(v), 1e-6) * margin / 448.0 for k, v in zip(keys, t.tolist())}
+        finally:
+            self.calib = None
 
     def head(self) -> torch.Tensor:
         self.cls_feat.zero_()
@@ -310,7 +396,7 @@ class TensorParallelViT:
     def launches_per_forward(self) -> int:
         """Native kernel launches per forward: per layer 2 barriers, 4 GEMMs, 2 attention launches and 2 slot
         reductions (with the LayerNorms inside), plus the patch GEMM and the first LayerNorm."""
-        per_layer = 2 + 4 + len(self.attn.ops) + 2 + (0 if self.fuse_ln else 2)
+        per_layer = 2 + 4 + len(self.attn.ops) + 2 + (0 if self.fuse_ln else 2) + (1 if self.fp8 else 0)
         return len(self.layers) * per_layer + 2
 
     def flops(self) -> float:

@@ -69,7 +69,7 @@ def test_slot_reduce_with_residual_and_layernorm_matches_fp32(world):
     P = ctypes.c_void_p
     rc = _lib().fdb_comm_slot_reduce_ln(P(slots.data_ptr()), P(counters.data_ptr()), 7, P(x.data_ptr()), P(bias.data_ptr()),
                                         rows, cols, world, dtype_code(torch.bfloat16), st.ptr, P(gamma.data_ptr()),
-                                        P(beta.data_ptr()), 1e-6, P(y.data_ptr()), cols, P(current_stream_ptr()))
+                                        P(beta.data_ptr()), 1e-6, P(y.data_ptr()), cols, P(current_stream_ptr()), 0, 1.0)
     assert rc == 0
     torch.cuda.synchronize()
     st.check("slot_reduce_ln")

@@ -36,3 +36,25 @@ def test_vit_two_ranks_match_fp32_reference():
     assert r["world"] == 2
     assert r["max_abs_err"] < 0.03 * r["ref_max_prob"], r
     assert r["top1_agree"] >= 0.75, r
+
+
+def test_vit_fp8_one_rank_close_to_fp32_reference():
+    """e4m3 linears with calibrated static activation scales: the class probabilities stay close to the fp32
+    forward and the arg-max class agrees on most images (random weights give nearly flat distributions, so the
+    agreement bound is loose and the error bound carries the check)."""
+    p = subprocess.run([sys.executable] + ARGS + ["--dtype", "fp8"], capture_output=True, text=True, timeout=600, cwd=ROOT)
+    r = _result(p)
+    assert r["dtype"] == "fp8"
+    assert r["max_abs_err"] < 0.12 * r["ref_max_prob"], r
+    assert r["top1_agree"] >= 0.6, r
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_vit_fp8_two_ranks_close_to_fp32_reference():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29544"] + ARGS + ["--dtype", "fp8"]
+    r = _result(subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT))
+    assert r["world"] == 2 and r["dtype"] == "fp8"
+    assert r["max_abs_err"] < 0.12 * r["ref_max_prob"], r
+    assert r["top1_agree"] >= 0.6, r
