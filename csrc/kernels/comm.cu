@@ -175,8 +175,12 @@ __device__ __forceinline__ void ld8f(const float* p, float (&f)[8]) {
 }
 
 // OUT8: y is e4m3 (one byte per element, y_ld in bytes), the normalised row is multiplied by out_scale first.
+// The partial results come from `src`: src.p[s] is the first of this rank's rows in rank s's buffer - slots in
+// this rank's own memory for the push form of the reduce-scatter, or the peers' own result buffers, read
+// straight over NVLink, for the pull form (every load of a row chunk is issued before the first use, so a
+// thread keeps WORLD 16-byte peer loads in flight per chunk and a CTA well over 100 KB).
 template <typename T, int WORLD, bool OUT8>
-__global__ void __launch_bounds__(256) slot_reduce_ln_kernel(const T* slots, const unsigned* counters, unsigned target,
+__global__ void __launch_bounds__(256) slot_reduce_ln_kernel(PeerPtrs src, const unsigned* counters, unsigned target,
                                                              T* x, const float* bias, int rows, int cols,
                                                              int* status, const float* gamma, const float* beta,
                                                              float eps, void* y_, int y_ld, float out_scale) {
@@ -200,7 +204,7 @@ __global__ void __launch_bounds__(256) slot_reduce_ln_kernel(const T* slots, con
         raw[0] = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * cols + c);
 #pragma unroll
         for (int s = 0; s < WORLD; ++s)
-          raw[s + 1] = *reinterpret_cast<const uint4*>(slots + (static_cast<size_t>(s) * rows + row) * cols + c);
+          raw[s + 1] = *reinterpret_cast<const uint4*>(static_cast<const T*>(src.p[s]) + static_cast<size_t>(row) * cols + c);
         float bv[8];
         if (bias != nullptr) ld8f(bias + c, bv);
 #pragma unroll
@@ -384,12 +388,15 @@ FDB_API int fdb_comm_slot_reduce_ln(const void* slots, const unsigned* counters,
   if (!al16(gamma) || !al16(beta) || (bias != nullptr && !al16(bias))) { set_error("comm: bias, gamma and beta must be 16-byte aligned"); return -1; }
   const int grid = 4 * ((rows + 127) / 128);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  PeerPtrs src{};
+  for (int s2 = 0; s2 < world && s2 < kMaxPeers; ++s2)
+    src.p[s2] = const_cast<uint8_t*>(static_cast<const uint8_t*>(slots)) + static_cast<size_t>(s2) * rows * cols * 2;
 #define FDB_SRLN(T, W)                                                                                              \
   if (out_fp8)                                                                                                      \
-    slot_reduce_ln_kernel<T, W, true><<<grid, 256, 0, st>>>(static_cast<const T*>(slots), counters, target, static_cast<T*>(x), \
+    slot_reduce_ln_kernel<T, W, true><<<grid, 256, 0, st>>>(src, counters, target, static_cast<T*>(x),              \
                                                             bias, rows, cols, status, gamma, beta, eps, y, y_ld, out_scale);     \
   else                                                                                                              \
-    slot_reduce_ln_kernel<T, W, false><<<grid, 256, 0, st>>>(static_cast<const T*>(slots), counters, target, static_cast<T*>(x), \
+    slot_reduce_ln_kernel<T, W, false><<<grid, 256, 0, st>>>(src, counters, target, static_cast<T*>(x),             \
                                                              bias, rows, cols, status, gamma, beta, eps, y, y_ld, 1.f)
 #define FDB_SRLN_W(T)                                              \
   switch (world) {                                                 \
@@ -405,4 +412,45 @@ FDB_API int fdb_comm_slot_reduce_ln(const void* slots, const unsigned* counters,
 #undef FDB_SRLN_W
 #undef FDB_SRLN
   return check_launch("slot_reduce_ln");
+}
+
+// Pull form: part_ptrs[s] points at this rank's rows inside rank s's partial-result buffer ([rows][cols], peer
+// memory for s != this rank). Everything else as fdb_comm_slot_reduce_ln.
+FDB_API int fdb_comm_slot_reduce_ln_pull(void* const* part_ptrs, const unsigned* counters, unsigned target, void* x,
+                                         const float* bias, int rows, int cols, int world, int dtype, int* status,
+                                         const float* gamma, const float* beta, float eps, void* y, int y_ld,
+                                         void* stream, int out_fp8, float out_scale) {
+  if (cols % 8 != 0 || cols > 2048 || y_ld % 8 != 0 || gamma == nullptr || beta == nullptr) {
+    set_error("comm: fused slot reduce + LayerNorm needs cols a multiple of 8 up to 2048, gamma and beta"); return -1;
+  }
+  auto al16 = [](const void* q) { return reinterpret_cast<uintptr_t>(q) % 16 == 0; };
+  if (!al16(gamma) || !al16(beta) || (bias != nullptr && !al16(bias))) { set_error("comm: bias, gamma and beta must be 16-byte aligned"); return -1; }
+  PeerPtrs src{};
+  for (int s2 = 0; s2 < world && s2 < kMaxPeers; ++s2) {
+    if (part_ptrs[s2] == nullptr || !al16(part_ptrs[s2])) { set_error("comm: partial-result pointers must be set and 16-byte aligned"); return -1; }
+    src.p[s2] = part_ptrs[s2];
+  }
+  const int grid = 4 * ((rows + 127) / 128);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define FDB_SRLN(T, W)                                                                                              \
+  if (out_fp8)                                                                                                      \
+    slot_reduce_ln_kernel<T, W, true><<<grid, 256, 0, st>>>(src, counters, target, static_cast<T*>(x),              \
+                                                            bias, rows, cols, status, gamma, beta, eps, y, y_ld, out_scale);     \
+  else                                                                                                              \
+    slot_reduce_ln_kernel<T, W, false><<<grid, 256, 0, st>>>(src, counters, target, static_cast<T*>(x),             \
+                                                             bias, rows, cols, status, gamma, beta, eps, y, y_ld, 1.f)
+#define FDB_SRLN_W(T)                                              \
+  switch (world) {                                                 \
+    case 1: FDB_SRLN(T, 1); break;                                 \
+    case 2: FDB_SRLN(T, 2); break;                                 \
+    case 4: FDB_SRLN(T, 4); break;                                 \
+    case 8: FDB_SRLN(T, 8); break;                                 \
+    default: set_error("comm: fused slot reduce + LayerNorm takes 1, 2, 4 or 8 ranks"); return -1; \
+  }
+  if (dtype == kBF16) { FDB_SRLN_W(__nv_bfloat16) }
+  else if (dtype == kF16) { FDB_SRLN_W(__half) }
+  else { set_error("comm: slot reduce takes fp16 or bf16"); return -1; }
+#undef FDB_SRLN_W
+#undef FDB_SRLN
+  return check_launch("slot_reduce_ln_pull");
 }

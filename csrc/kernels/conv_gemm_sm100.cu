@@ -768,6 +768,14 @@ __device__ __forceinline__ void epilogue_loop_tma(const ConvGemmParams& p, const
               "r"(buf), "r"(co0), "r"(twi * p.tw), "r"(thi * p.th), "r"(img)
               : "memory");
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          if (p.peer_mode == 3) {
+            // pull form of the reduce-scatter: the partial block stays in this rank's memory; only the arrival
+            // count goes to the rank that owns the rows, which then reads the block over NVLink itself
+            const int grow = twi * p.tw;
+            const int owner = grow / p.peer_rows;
+            pending_counter = p.peer->counters[owner] + (grow - owner * p.peer_rows) / kBM;
+            ++pending_stores;
+          }
         }
         if (last) trace_mark(p, it, 7);
       }
@@ -948,26 +956,63 @@ conv_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int copiers = static_cast<int>(gridDim.x) - first_copier;
     const int c = static_cast<int>(blockIdx.x) - first_copier;
     const int per_shard = p.peer_rows / p.tw;
-    const long long blk_vecs = static_cast<long long>(p.tw) * p.gather_row_bytes / 16;
-    for (int j = per_shard + c; j < p.tiles_w; j += copiers) {      // rotated order, remote blocks only
-      int b = j + p.peer_rot;
-      if (b >= p.tiles_w) b -= p.tiles_w;
-      const int owner = b / per_shard;
-      const long long off = static_cast<long long>(b) * p.tw * p.gather_row_bytes;
-      const uint4* from = reinterpret_cast<const uint4*>(p.peer_src[owner] + off);
-      uint4* to = reinterpret_cast<uint4*>(p.gather_dst + off);
-      long long i = threadIdx.x;
-      for (; i + 3 * kThreads < blk_vecs; i += 4 * kThreads) {      // four loads in flight per thread
-        const uint4 v0 = from[i], v1 = from[i + kThreads], v2 = from[i + 2 * kThreads], v3 = from[i + 3 * kThreads];
-        to[i] = v0; to[i + kThreads] = v1; to[i + 2 * kThreads] = v2; to[i + 3 * kThreads] = v3;
+    // One thread drives a ring of bulk copies: peer memory -> shared memory -> this rank's buffer, 16 KB per
+    // stage. The copy engine keeps every stage in flight at once (a CTA holds well over 100 KB in transit, which
+    // is what it takes to fill an NVLink round trip), where ordinary loads are limited by the registers that can
+    // wait for them.
+    if (threadIdx.x == 0) {
+      constexpr int kCopyStage = 16384;
+      constexpr int kLag = 2;          // a stage is refilled this many chunks after its store was issued
+      const int ring_max = (S * Cfg::kStageBytes + kStagingBytes) / kCopyStage;
+      const int NS = min(min(2 * S, ring_max), 12);       // the operand ring's 2 * S mbarriers serve as stage barriers
+      const long long blk_bytes = static_cast<long long>(p.tw) * p.gather_row_bytes;
+      const int n_chunks = static_cast<int>((blk_bytes + kCopyStage - 1) / kCopyStage);
+      uint32_t phase_bits = 0;         // parity per stage
+      bool ok = true;
+      for (int j = per_shard + c; ok && j < p.tiles_w; j += copiers) {      // rotated order, remote blocks only
+        int b = j + p.peer_rot;
+        if (b >= p.tiles_w) b -= p.tiles_w;
+        const int owner = b / per_shard;
+        const long long off = static_cast<long long>(b) * p.tw * p.gather_row_bytes;
+        const uint8_t* from = p.peer_src[owner] + off;
+        uint8_t* to = p.gather_dst + off;
+        auto chunk_bytes = [&](int i) {
+          return static_cast<uint32_t>(min(static_cast<long long>(kCopyStage), blk_bytes - static_cast<long long>(i) * kCopyStage));
+        };
+        auto issue_load = [&](int i) {
+          const int st = i % NS;
+          const uint32_t bar = bar0 + 8u * st;
+          mbar_arrive_expect_tx(bar, chunk_bytes(i));
+          bulk_load(tile0 + st * kCopyStage, from + static_cast<long long>(i) * kCopyStage, chunk_bytes(i), bar);
+        };
+        const int ahead = NS - kLag;
+        for (int i = 0; i < min(ahead, n_chunks); ++i) issue_load(i);
+        for (int i = 0; i < n_chunks; ++i) {
+          const int st = i % NS;
+          if (!mbar_wait(bar0 + 8u * st, (phase_bits >> st) & 1u, abort_flag, kStatusTimeoutPeer)) { ok = false; break; }
+          phase_bits ^= 1u << st;
+          bulk_store(to + static_cast<long long>(i) * kCopyStage, tile0 + st * kCopyStage, chunk_bytes(i));
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          if (i + ahead < n_chunks) {
+            // the stage of chunk i + ahead last held chunk i - kLag: all but the newest kLag stores have read theirs
+            asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kLag) : "memory");
+            issue_load(i + ahead);
+          }
+        }
+        // every byte of the block is in this rank's memory before the flag says so
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (!ok) {
+          // aborting: give the loads still in flight a bounded chance to land before this CTA's shared memory
+          // is handed on
+          for (int st = 0; st < NS; ++st)
+            for (int spin = 0; spin < (1 << 14); ++spin)
+              if (mbar_try_wait(bar0 + 8u * st, (phase_bits >> st) & 1u)) break;
+          break;
+        }
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __threadfence();
+        st_release_gpu(p.ready + b, p.peer_epoch);
       }
-      for (; i < blk_vecs; i += kThreads) to[i] = from[i];
-      // The rows were written through the generic proxy and will be read by TMA (async proxy) in
-      // another CTA: each writer orders its stores before async-proxy accesses, then the flag is released.
-      asm volatile("fence.proxy.async;" ::: "memory");
-      __threadfence();
-      __syncthreads();
-      if (threadIdx.x == 0) st_release_gpu(p.ready + b, p.peer_epoch);
     }
   } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -1563,7 +1608,7 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
   if (fp8 && (d->residual != nullptr || d->w_batched || d->halo_mode == 1)) {
     set_error("conv_gemm: fp8 operands take the plain kernel without residual or batched weights"); return nullptr;
   }
-  if (d->out_dtype == kF8E4M3 && (d->peer_mode == 2 || d->residual != nullptr)) {
+  if (d->out_dtype == kF8E4M3 && (d->peer_mode >= 2 || d->residual != nullptr)) {
     set_error("conv_gemm: an e4m3 output cannot be combined with a residual or the reduce-scatter mode"); return nullptr;
   }
   const int es = fp8 ? 1 : 2;                 // operand element size
@@ -1803,22 +1848,24 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
                             d->pad_h == 0 && d->pad_w == 0 && !op->halo && !d->w_batched && p.tw == kBM && p.th == 1;
     if (!gemm_shape || d->peer_world < 1 || d->peer_world > 8 || d->peer_rows % kBM != 0 ||
         d->W != d->peer_rows * d->peer_world || d->peer_rank < 0 || d->peer_rank >= d->peer_world ||
-        (d->peer_mode != 1 && d->peer_mode != 2)) {
+        (d->peer_mode != 1 && d->peer_mode != 2 && d->peer_mode != 3)) {
       set_error("conv_gemm: peer modes take a plain GEMM whose M is world * peer_rows, peer_rows a multiple of 128");
       delete op; return nullptr;
     }
-    if (d->peer_mode == 2 && !p.y_tma) {
+    if (d->peer_mode >= 2 && !p.y_tma) {
       set_error("conv_gemm: reduce-scatter mode needs the TMA store path (16-bit output, aligned rows)");
       delete op; return nullptr;
     }
     PeerTable host{};
     for (int r = 0; r < d->peer_world; ++r) {
-      if (d->peer_ptrs[r] == nullptr || (d->peer_mode == 2 && d->peer_counters[r] == nullptr)) {
+      if ((d->peer_mode != 3 && d->peer_ptrs[r] == nullptr) || (d->peer_mode >= 2 && d->peer_counters[r] == nullptr)) {
         set_error("conv_gemm: missing peer pointer"); delete op; return nullptr;
       }
       CUresult res = CUDA_SUCCESS;
       if (d->peer_mode == 1) {
         p.peer_src[r] = static_cast<const uint8_t*>(d->peer_ptrs[r]);
+      } else if (d->peer_mode == 3) {
+        host.counters[r] = d->peer_counters[r];      // the result goes through the ordinary local store
       } else {
         const CUtensorMapDataType ydt =
             d->out_dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -1848,7 +1895,7 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
         set_error("conv_gemm: all-gather mode needs ready flags and 16-byte rows"); delete op; return nullptr;
       }
       const int remote_blocks = p.tiles_w - d->peer_rows / p.tw;
-      int copiers = d->peer_copiers > 0 ? d->peer_copiers : 20;
+      int copiers = d->peer_copiers > 0 ? d->peer_copiers : 12;
       copiers = std::min(copiers, std::min(remote_blocks, op->grid / 2));
       if (op->pair) {
         // clusters of two throughout: an even number of copier CTAs behind the GEMM pairs

@@ -157,6 +157,22 @@ def main(argv=None):
         nv = 4.0 * len(model.layers) * (world - 1) / world * model.M * cfg["hidden"] * 2
         out["roofline_ms"] = max(fl / world / 1404.3e12, nv / 770e9) * 1e3
         out["roofline_frac"] = out["roofline_ms"] / enc
+        if a.breakdown and world > 1:
+            # every rank runs the same launch sequence, so each piece synchronises itself through the device
+            # barriers / counters it contains; times are device time, max over ranks
+            lay = model.layers[0]
+            nxt = model.layers[1]["ln1_gb"] + (model.shard[0],) + ((1.0 / model.layers[1]["scales"][0],) if model.fp8 else ())
+            ln2 = lay["ln2_gb"] + (model.shard[1],) + ((1.0 / lay["scales"][2],) if model.fp8 else ())
+            parts = {
+                "barrier+allgather_qkv": lambda: (comm.barrier(), lay["qkv"].launch()),
+                "attention": model.attn.launch,
+                "proj_reducescatter+reduce_ln": lambda: (lay["proj"].launch(), model._reduce_into_residual(0, lay["proj"], lay["proj_b"], ln2)),
+                "barrier+allgather_fc1": lambda: (comm.barrier(), lay["fc1"].launch()),
+                "fc2_reducescatter+reduce_ln": lambda: (lay["fc2"].launch(), model._reduce_into_residual(1, lay["fc2"], lay["fc2_b"], nxt)),
+                "barrier": comm.barrier,
+            }
+            out["breakdown_ms"] = {k: round(_timed(f, a.steps, a.warmup, world), 4) for k, f in parts.items()}
+            comm.check("tp vit breakdown")
         if a.breakdown and world == 1:
             lay = model.layers[0]
             parts = {"ln": lay["ln1"].launch, "qkv": lay["qkv"].launch, "fc1": lay["fc1"].launch,

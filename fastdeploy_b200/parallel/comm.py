@@ -52,6 +52,11 @@ def _lib():
                                                 ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float,
                                                 ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
                                                 ctypes.c_float]
+        lib.fdb_comm_slot_reduce_ln_pull.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint, ctypes.c_void_p,
+                                                     ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                                     ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                                     ctypes.c_float, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
+                                                     ctypes.c_int, ctypes.c_float]
         lib._comm_ready = True
     return lib
 

@@ -41,6 +41,7 @@ VIT_SIZES = {
     "large16": dict(patch=16, layers=24, hidden=1024, heads=16, mlp=4096),
     "base16": dict(patch=16, layers=12, hidden=768, heads=12, mlp=3072),
     "test": dict(patch=14, layers=2, hidden=128, heads=4, mlp=256),
+    "test8": dict(patch=14, layers=2, hidden=256, heads=8, mlp=512),     # divisible over 8 ranks
 }
 
 
@@ -167,6 +168,9 @@ class TensorParallelViT:
         self.slots = [comm.tensor(b, (ws, rows, H), dtype) for b in self.slot_blocks]
         self.counters = [comm.tensor(b, (self.blocks128,), torch.int32) for b in self.cnt_blocks]
         self.targets = [0, 0]
+        # this rank's rows inside every rank's partial-result buffer (the pull form of the reduce-scatter)
+        row_off = r * rows * H * es
+        self.part_ptrs = [(ctypes.c_void_p * 8)(*[comm.ptr(k, b) + row_off for k in range(ws)]) for b in self.slot_blocks]
 
         q3 = self.qkv[:m_real].view(batch, T, 3 * hd)
         self.attn = Attention(q3[:, :, 0:hd], q3[:, :, hd:2 * hd], q3[:, :, 2 * hd:3 * hd],
@@ -174,6 +178,7 @@ class TensorParallelViT:
                               status=comm.status)
 
         # ---- per-layer ops
+        self.fuse_ln = H <= 2048 and ws in (1, 2, 4, 8)     # slot reduction + residual + LayerNorm in one kernel
         self.layers = []
         gptr = [[comm.ptr(k, b) for k in range(ws)] for b in self.gather_blocks]
         sptr = [[comm.ptr(k, b) for k in range(ws)] for b in self.slot_blocks]
@@ -231,7 +236,6 @@ class TensorParallelViT:
         self.final = torch.zeros(rows, H, dtype=dtype, device=dev)
         self.ln_f_gb = (dv(weights["norm_g"]).float().contiguous(), dv(weights["norm_b"]).float().contiguous())
         self.ln_f = layernorm(self.xres, self.final, self.ln_f_gb[0], self.ln_f_gb[1], rows=rows, c=H, eps=eps)
-        self.fuse_ln = H <= 2048 and ws in (1, 2, 4, 8)
         cls_rows = torch.arange(batch, device=dev) * T
         mine = (cls_rows >= self.row0) & (cls_rows < self.row0 + rows)
         self.cls_img = torch.nonzero(mine).flatten()
@@ -261,9 +265,13 @@ class TensorParallelViT:
                           scale_b=scale_b)
             op.stores_per_block = 0
             return op
+        # reduce-scatter by pulling: the partial [M, H] result stays in this rank's heap block (same layout as the
+        # slot buffer: row block o belongs to rank o); the epilogue only bumps the owner's arrival counters, and
+        # each rank's reduction kernel reads its rows from every peer over NVLink
         op = ConvGemm(x, w, self.slots[which].view(c.world * self.rows, self.H), in_shape=(1, 1, self.M, k_local),
                       out_hw=(1, self.M), cout=self.H, x_ld=x.stride(0), y_ld=self.H, status=c.status, name=name,
-                      peer_mode=2, peer_rows=self.rows, peer_rank=c.rank, peer_world=c.world, peer_ptrs=slot_ptrs,
+                      peer_mode=3 if self.fuse_ln else 2, peer_rows=self.rows, peer_rank=c.rank, peer_world=c.world,
+                      peer_ptrs=slot_ptrs,
                       peer_counters=cnt_ptrs, scale_b=scale_b)
         info = op.info()
         bn = info["block_n"]
@@ -278,7 +286,16 @@ class TensorParallelViT:
         c = self.comm
         self.targets[which] += c.world * op.stores_per_block
         P = ctypes.c_void_p
-        if ln is not None:
+        if ln is not None and c.world > 1:
+            gamma, beta, out = ln[:3]
+            out_scale = ln[3] if len(ln) > 3 else 1.0
+            out8 = out.dtype == torch.float8_e4m3fn
+            rc = _lib().fdb_comm_slot_reduce_ln_pull(
+                self.part_ptrs[which], P(self.counters[which].data_ptr()), self.targets[which],
+                P(self.xres.data_ptr()), P(bias.data_ptr()), self.rows, self.H, c.world, dtype_code(self.dtype),
+                c.status.ptr, P(gamma.data_ptr()), P(beta.data_ptr()), self.eps, P(out.data_ptr()), out.stride(0),
+                P(current_stream_ptr()), int(out8), float(out_scale))
+        elif ln is not None:
             gamma, beta, out = ln[:3]
             out_scale = ln[3] if len(ln) > 3 else 1.0
             out8 = out.dtype == torch.float8_e4m3fn
