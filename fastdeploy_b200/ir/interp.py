@@ -132,7 +132,10 @@ def _conv_transpose(node, x, w, b=None):
     for i in range(nd):
         end = y.shape[2 + i] - pads[nd + i]
         sl.append(slice(pads[i], end))
-    return y[tuple(sl)]
+    y = y[tuple(sl)]
+    if node.attr("activation", None) is not None:       # set by the deconvolution + activation fusion pass
+        y = ACTIVATIONS[node.attr("activation")](y, node.attr("act_alpha", 0.0), node.attr("act_beta", 0.0))
+    return y
 
 
 @op("BatchNormalization")

@@ -124,11 +124,13 @@ def eliminate_identity(graph: Graph) -> int:
 
 # --------------------------------------------------------------------------- conv folding
 def fold_batchnorm(graph: Graph) -> int:
-    """Conv -> BatchNormalization  =>  Conv with scaled weights and folded bias."""
+    """Conv / ConvTranspose -> BatchNormalization  =>  the convolution with scaled weights and folded bias."""
     changed = 0
     cons = graph.consumers()
     for conv in list(graph.nodes):
-        if conv.op != "Conv" or conv.inputs[1] not in graph.initializers:
+        if conv.op not in ("Conv", "ConvTranspose") or conv.inputs[1] not in graph.initializers:
+            continue
+        if conv.op == "ConvTranspose" and conv.attr("group", 1) != 1:
             continue
         bn = _single_consumer(cons, graph, conv.outputs[0])
         if bn is None or bn.op != "BatchNormalization" or bn.inputs[0] != conv.outputs[0]:
@@ -139,7 +141,9 @@ def fold_batchnorm(graph: Graph) -> int:
         b = graph.initializers[conv.inputs[2]].astype(np.float64) if len(conv.inputs) > 2 and conv.inputs[2] else 0.0
         scale, bias, mean, var = (graph.initializers[i].astype(np.float64) for i in bn.inputs[1:5])
         k = scale / np.sqrt(var + bn.attr("epsilon", 1e-5))
-        w2 = (w * k.reshape([-1] + [1] * (w.ndim - 1))).astype(np.float32)
+        # output channels are dimension 0 of a Conv weight and dimension 1 of a ConvTranspose weight
+        kshape = [-1] + [1] * (w.ndim - 1) if conv.op == "Conv" else [1, -1] + [1] * (w.ndim - 2)
+        w2 = (w * k.reshape(kshape)).astype(np.float32)
         b2 = ((b - mean) * k + bias).astype(np.float32)
         conv.inputs = [conv.inputs[0], graph.const(w2, prefix="w_bnfold"), graph.const(b2, prefix="b_bnfold")]
         conv.outputs = [bn.outputs[0]]
@@ -409,6 +413,26 @@ def fuse_conv_activation(graph: Graph) -> int:
     return changed
 
 
+def fuse_deconv_activation(graph: Graph) -> int:
+    """ConvTranspose + activation => ConvTranspose carrying ``activation`` / ``act_alpha`` / ``act_beta`` attributes
+    (applied by the interpreter and fused into the epilogue by the native backend)."""
+    changed = 0
+    cons = graph.consumers()
+    for dc in list(graph.nodes):
+        if dc.op != "ConvTranspose" or dc.attr("activation", None) is not None:
+            continue
+        nxt = _single_consumer(cons, graph, dc.outputs[0])
+        act = _act_of(nxt, graph) if nxt is not None else None
+        if act is None:
+            continue
+        dc.attrs["activation"], dc.attrs["act_alpha"], dc.attrs["act_beta"] = act
+        dc.outputs = [nxt.outputs[0]]
+        _remove(graph, [nxt])
+        cons = graph.consumers()
+        changed += 1
+    return changed
+
+
 def fuse_gemm(graph: Graph, info: Optional[ShapeInfo] = None) -> int:
     """MatMul(x, W) | Gemm (+Add bias) (+activation) (+Add residual) => FusedGemm with W as [N, K]."""
     changed = 0
@@ -666,6 +690,7 @@ def optimize(graph: Graph, input_shapes: Optional[Dict[str, Sequence[int]]] = No
             fuse_attention(g, info)
         fuse_embed_layernorm(g)
         fuse_conv_activation(g)
+        fuse_deconv_activation(g)
         fuse_gemm(g, info)
         if info is not None and any(n.op == "MultiClassNMS" for n in g.nodes):
             info = infer_shapes(g, input_shapes, input_values)

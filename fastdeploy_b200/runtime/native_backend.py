@@ -10,8 +10,11 @@ this backend keeps one plan per shape bucket and builds a new one in millisecond
 Layout and precision: 4-D activations live as NHWC fp16/bf16 tensors (logically NCHW),
 channel counts are padded to multiples of 8, concat / split along channels are
 realised as channel-slice views so producers write straight into the concatenated
-buffer. Operators without a hand-written kernel run through the interpreter's torch
-implementation on the GPU in fp32 (shape plumbing and tiny tensors only).
+buffer. View-like operators (Reshape, Transpose, Slice ...) become torch views recorded at
+build time; casts, broadcasting arithmetic, soft-max, reductions and gathers run on the
+stride-generic kernels of ``lower_generic.py``. Only operators that neither path covers
+(LSTM, TopK, NonZero ...) run through the interpreter's torch implementation; such a step
+shows up in the plan under the name ``torch:<op>``.
 """
 from __future__ import annotations
 
@@ -33,6 +36,7 @@ from ..ops import stem_conv
 from ..ops.base import NativeOp, StatusWord, current_stream_ptr
 from ..ops.conv_gemm import ConvGemm, pack_conv_weight, pack_linear_weight
 from ..ops.nms import MulticlassNMS
+from .lower_generic import GenericLowering
 
 
 def _round8(c: int) -> int:
@@ -161,7 +165,7 @@ class Plan:
             pass
 
 
-class Lowering:
+class Lowering(GenericLowering):
     """Builds a :class:`Plan` from an optimised graph and concrete input shapes."""
 
     def __init__(self, graph: Graph, input_shapes: Dict[str, Sequence[int]], device: torch.device,
@@ -210,14 +214,17 @@ class Lowering:
         if v.nhwc and v.t.dtype == self.dtype and v.t.stride(3) == 1 and v.ld % 8 == 0 \
                 and v.t.data_ptr() % 16 == 0:
             return v
+        if not v.nhwc and v.t.dim() == 4:
+            # a view whose memory already is channel-innermost (e.g. a reshape of an NHWC buffer)
+            p = v.t.permute(0, 2, 3, 1)
+            if p.dtype == self.dtype and p.stride(3) == 1 and p.stride(2) % 8 == 0 and p.data_ptr() % 16 == 0 \
+                    and p.stride(1) == p.stride(2) * p.shape[2]:
+                nv = Val(p, True)
+                self.vals[name] = nv
+                return nv
         n, c, h, w = v.logical_shape
         dst = self.new_nhwc(n, h, w, c)
-        src = v
-
-        def conv():
-            dst.t.copy_(src.logical().permute(0, 2, 3, 1))
-        self.plan.add_py(conv, f"to_nhwc({name})")
-        conv()
+        self.copy(v.logical(), dst.logical(), f"to_nhwc({name})")
         self.vals[name] = dst
         return dst
 
@@ -299,6 +306,8 @@ class Lowering:
 
     # ------------------------------------------------------------------ fallback
     def lower_fallback(self, node: Node) -> None:
+        if self.lower_generic(node):
+            return
         fn = interp._OPS.get(node.op)
         if fn is None:
             raise NotImplementedError(f"native backend: unsupported op {node.op}")
@@ -341,12 +350,7 @@ class Lowering:
 
     def _copy_into_slice(self, name: str) -> None:
         dst = self.preassigned[name]
-        src = self.vals[name]
-
-        def cp():
-            dst.t.copy_(src.logical().permute(0, 2, 3, 1))
-        self.plan.add_py(cp, f"to_slice({name})")
-        cp()
+        self.copy(self.vals[name].logical(), dst.logical(), f"to_slice({name})")
         self.vals[name] = dst
 
     # ------------------------------------------------------------------ conv
@@ -439,6 +443,45 @@ class Lowering:
 
     lower_Conv = lower_FusedConv
 
+    def lower_ConvTranspose(self, node: Node):
+        """Transposed convolution whose kernel equals its stride (the 2x2 / stride-2 up-sampling of segmentation and
+        text-detection heads): every output pixel has exactly one contributing tap, so the layer is ``kh * kw`` 1x1
+        GEMMs on the tensor cores, each writing the output pixels ``(kh * y + i, kw * x + j)`` through a strided
+        output view, with bias and activation fused."""
+        x_name, w_name = node.inputs[0], node.inputs[1]
+        w = self.g.initializers.get(w_name)
+        if w is None or w.ndim != 4 or not self.is4d(x_name) or node.attr("group", 1) != 1:
+            return False
+        cin, cout, kh, kw = w.shape
+        strides = node.attr("strides", [1, 1])
+        if list(strides) != [kh, kw] or any(p != 0 for p in node.attr("pads", [0, 0, 0, 0])) \
+                or any(p != 0 for p in node.attr("output_padding", [0, 0])) \
+                or any(d != 1 for d in node.attr("dilations", [1, 1])) \
+                or node.attr("auto_pad", "NOTSET") not in ("NOTSET", ""):
+            return False
+        x = self.as_nhwc(x_name)
+        n, cx, h, wd = x.logical_shape
+        cin_phys = _round8(cin)
+        bias = self.const_f32(node.inputs[2]).float().contiguous() if len(node.inputs) > 2 and node.inputs[2] else None
+        y = self.out_nhwc(node.outputs[0])
+        for i in range(kh):
+            for j in range(kw):
+                key = (w_name, f"deconv{cin_phys}_{i}_{j}")
+                if key not in self.packed:
+                    wt = torch.from_numpy(np.ascontiguousarray(w[:, :, i, j].T)).float().reshape(cout, cin, 1, 1)
+                    if cin_phys != cin:
+                        wt = torch.nn.functional.pad(wt, (0, 0, 0, 0, 0, cin_phys - cin))
+                    self.packed[key] = pack_conv_weight(wt.to(self.device), self.dtype)
+                yv = y.t[:, i::kh, j::kw, :]
+                op = ConvGemm(x.t, self.packed[key], yv, in_shape=(n, h, wd, cin_phys), out_hw=(h, wd), cout=cout,
+                              bias=bias, act=node.attr("activation", "none"), act_alpha=node.attr("act_alpha", 0.0),
+                              act_beta=node.attr("act_beta", 0.0), x_ld=x.ld, y_ld=yv.stride(2), x_n_stride=x.n_stride,
+                              y_n_stride=yv.stride(0), y_h_stride=yv.stride(1), status=self.plan.status,
+                              name=f"deconv{i}{j}:{node.name}")
+                self.plan.add_native(op, node)
+                op.launch()
+        self.vals[node.outputs[0]] = y
+
     def _lower_depthwise(self, node: Node, w: np.ndarray, group: int):
         """Depthwise convolution (one filter per channel): CUDA-core kernel, bias and activation fused."""
         cout, cpg, kh, kw = w.shape
@@ -522,12 +565,7 @@ class Lowering:
             except RuntimeError:
                 pass
         dst = torch.zeros(rows, cols, dtype=self.dtype, device=self.device)
-        src = t
-
-        def cp():
-            dst.copy_(src.reshape(rows, cols))
-        self.plan.add_py(cp, f"to_rows({name})")
-        cp()
+        self.copy(t, dst.view(t.shape), f"to_rows({name})")
         return dst
 
     # ------------------------------------------------------------------ pooling / resize / elementwise
@@ -701,12 +739,7 @@ class Lowering:
             sl = dst.t[..., off:off + ci]
             same = v.nhwc and v.t.data_ptr() == sl.data_ptr() and v.t.stride() == sl.stride()
             if not same:
-                src = v
-
-                def cp(src=src, sl=sl):
-                    sl.copy_(src.logical().permute(0, 2, 3, 1))
-                self.plan.add_py(cp, f"concat_copy({i})", node)
-                cp()
+                self.copy(v.logical(), sl.permute(0, 3, 1, 2), f"concat_copy({i})", node)
             off += ci
         self.vals[out] = dst
 
@@ -772,12 +805,7 @@ class Lowering:
         n, c, h, w = x.logical_shape
         if not (s.nhwc and s.t.dtype == torch.float32 and s.t.stride(0) == _round8(c) and _round8(c) == c):
             sv = torch.zeros(n, c, dtype=torch.float32, device=self.device)
-            src = s
-
-            def cp():
-                sv.copy_(src.logical().reshape(n, c))
-            self.plan.add_py(cp, f"gate_to_f32({s_name})", node)
-            cp()
+            self.copy(s.logical(), sv.view(n, c, 1, 1), f"gate_to_f32({s_name})", node)
             s_t = sv
         else:
             s_t = s.t
@@ -840,21 +868,14 @@ class Lowering:
         boxes = self.as_torch(node.inputs[0])
         scores = self.as_torch(node.inputs[1])
         n, m, _ = boxes.shape
-        bx = torch.zeros(n, m, 4, dtype=torch.float32, device=self.device)
-        src = boxes
-
-        def cp():
-            bx.copy_(src)
-        self.plan.add_py(cp, "nms_boxes_f32", node)
-        cp()
+        if boxes.dtype == torch.float32 and boxes.is_contiguous():
+            bx = boxes
+        else:
+            bx = torch.zeros(n, m, 4, dtype=torch.float32, device=self.device)
+            self.copy(boxes, bx, "nms_boxes_f32", node)
         if not scores.is_contiguous():
             sc = torch.zeros(scores.shape, dtype=scores.dtype, device=self.device)
-            ssrc = scores
-
-            def cp2():
-                sc.copy_(ssrc)
-            self.plan.add_py(cp2, "nms_scores", node)
-            cp2()
+            self.copy(scores, sc, "nms_scores", node)
             scores = sc
         self._emit_nms(node, bx, scores, class_major=True)
 
@@ -919,12 +940,7 @@ class Lowering:
                 v = self.get(name)
                 view = buf[:, off:off + h * w, :ch].unflatten(1, (h, w))
                 if not (v.nhwc and v.t.data_ptr() == view.data_ptr()):
-                    src = v
-
-                    def cp(src=src, view=view):
-                        view.copy_(src.logical().permute(0, 2, 3, 1))
-                    self.plan.add_py(cp, "ppyoloe_gather", node)
-                    cp()
+                    self.copy(v.logical(), view.permute(0, 3, 1, 2), "ppyoloe_gather", node)
             levels.append((off, w, node.attr("strides")[i]))
             off += h * w
         sf = self.get(node.inputs[2 * nl]).t
@@ -1047,13 +1063,7 @@ def _lower_EmbedLayerNorm(self: Lowering, node: Node):
         v = self.get(nm).t
         if v.dtype != torch.int64 or not v.is_contiguous() or v.numel() != rows:
             buf = torch.zeros(rows, dtype=torch.int64, device=self.device)
-            src = v
-            shape_b = out_shape[:-1]
-
-            def cp(src=src, buf=buf, shape_b=shape_b):
-                buf.copy_(src.expand(shape_b).reshape(-1))
-            self.plan.add_py(cp, f"ids_i64({nm})", node)
-            cp()
+            self.copy(v, buf.view(out_shape[:-1]), f"ids_i64({nm})", node)
             v = buf
         ids.append(v.reshape(-1))
     tabs = []
@@ -1077,11 +1087,19 @@ def _lower_Attention(self: Lowering, node: Node):
     b, s, hd = shp
     heads = node.attr("num_heads")
     d = hd // heads
-    if d % 8 != 0 or s > 1024:
+    if s > 1024:
         return False
+    dp = _round8(d)
 
     def view3(name):
         v = self.get(name).t
+        if d != dp:
+            # head size not a multiple of 8 (SVTR: 120 / 8 = 15): zero-padded per head; zeros change neither the
+            # scores nor the first d output columns
+            buf = torch.zeros(b, s, heads * dp, dtype=self.dtype, device=self.device)
+            self.copy(self.as_torch(name).unflatten(2, (heads, d)), buf.view(b, s, heads, dp)[..., :d],
+                      f"pad_heads({name})", node)
+            return buf
         if v.dtype == self.dtype and v.dim() == 3 and v.stride(2) == 1 and v.stride(1) % 8 == 0 \
                 and v.data_ptr() % 16 == 0:
             return v
@@ -1093,20 +1111,22 @@ def _lower_Attention(self: Lowering, node: Node):
         if int(np.prod(mshape)) not in (b * s, b * s * s):
             return False
         mv = self.as_torch(node.inputs[3])
-        mask = torch.zeros(mshape, dtype=torch.float32, device=self.device)
-        src = mv
-
-        def cpm(src=src, mask=mask):
-            mask.copy_(src)
-        self.plan.add_py(cpm, "attn_mask_f32", node)
-        cpm()
-    out = torch.zeros(b, s, hd, dtype=self.dtype, device=self.device)
+        if mv.dtype == torch.float32 and mv.is_contiguous():
+            mask = mv
+        else:
+            mask = torch.zeros(mshape, dtype=torch.float32, device=self.device)
+            self.copy(mv, mask, "attn_mask_f32", node)
+    out = torch.zeros(b, s, heads * dp, dtype=self.dtype, device=self.device)
     att = Attention(q, k, v, out, heads=heads, scale=node.attr("scale", 1.0 / math.sqrt(d)), mask=mask,
                     status=self.plan.status)
     for op in att.ops:
         self.plan.add_native(op, node)
         op.launch()
     self.plan.extra.setdefault("attention", []).append(att)
+    if d != dp:
+        trimmed = torch.zeros(b, s, hd, dtype=self.dtype, device=self.device)
+        self.copy(out.view(b, s, heads, dp)[..., :d], trimmed.view(b, s, heads, d), "trim_heads", node)
+        out = trimmed
     self.vals[node.outputs[0]] = Val(out, False)
 
 

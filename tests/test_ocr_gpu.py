@@ -30,8 +30,8 @@ def test_stage_matches_cpu(stage, shape, tmp_path):
         if dev == "gpu":
             plan = rt.plan_for_shapes({rt.get_input_info(0).name: shape})
             native = plan.native_kernel_launches
-            torch_steps = sum(1 for s in plan.steps if s.name.startswith("torch"))
-            assert native > 5 * max(torch_steps, 1), (native, torch_steps)
+            assert [s.name for s in plan.steps if s.native is None] == []
+            assert native > 20
     a, b = outs["cpu"], outs["gpu"]
     assert a.shape == b.shape
     if stage == "det":
