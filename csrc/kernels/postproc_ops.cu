@@ -11,6 +11,9 @@
 //                       canvas, bilinear, replicated or constant border: OCR text crops, face
 //                       alignment, key-point crops (cv::warpPerspective / cv::warpAffine in
 //                       fastdeploy/vision/ocr/ppocr/utils/get_rotate_crop_image.cc:21-81)
+//   warp_normalize      N perspective crops of one frame resized, normalised and right-padded straight into the
+//                       16-bit NHWC input of the OCR classifier / recogniser, optional 180-degree turn per crop
+//                       (get_rotate_crop_image.cc + cls_preprocessor.cc / rec_preprocessor.cc in one pass)
 //   hard_voxelize       points -> voxels in order of first appearance, at most max_points per voxel
 //                       (fastdeploy/vision/perception/paddle3d/centerpoint ops, voxelize_op.cu)
 #include "fdb_common.h"
@@ -205,6 +208,116 @@ FDB_API int fdb_warp_batch(const void* src, int H, int W, int C, const float* ma
   warp_batch_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(src), H, W, C, mats, sizes, static_cast<uint8_t*>(out), N, OH, OW, border, fill);
   return pp_check("warp_batch");
+}
+
+// ------------------------------------------------------------------ warp + resize + normalise into network inputs
+namespace fdb {
+
+// out[n, y, x, 0..2] = alpha[c] * bilinear(src at M_n * (x', y', 1)) + beta[c] for x < valid_w[n], else 0; channels
+// 3..CP-1 are 0. (x', y') = (x, y), or (valid_w - 1 - x, OH - 1 - y) when flip[n] != 0 (the crop turned by 180 degrees).
+// One pass from the source frame to the 16-bit NHWC input of the classifier / recogniser: perspective rectification,
+// resize to the input height, normalisation and right padding in a single read of the source pixels.
+template <typename T>
+__global__ void warp_normalize_kernel(const uint8_t* src_all, int H, int W, const int* page, long long page_stride,
+                                      const float* mats, const int* valid_w, const int* flip, T* out, int OH, int OW,
+                                      int CP, float a0, float a1, float a2, float b0, float b1, float b2) {
+  const int n = blockIdx.z;
+  const int x = blockIdx.x * blockDim.x + threadIdx.x;
+  const int y = blockIdx.y * blockDim.y + threadIdx.y;
+  if (x >= OW || y >= OH) return;
+  T* o = out + ((static_cast<size_t>(n) * OH + y) * OW + x) * CP;
+  const int vw = min(valid_w[n], OW);
+  const uint8_t* src = src_all + (page != nullptr ? page[n] * page_stride : 0);
+  float v[3] = {0.f, 0.f, 0.f};
+  if (x < vw) {
+    const bool fl = flip != nullptr && flip[n] != 0;
+    const float fx = static_cast<float>(fl ? vw - 1 - x : x), fy = static_cast<float>(fl ? OH - 1 - y : y);
+    const float* m = mats + 9 * n;
+    float wz = m[6] * fx + m[7] * fy + m[8];
+    wz = wz != 0.f ? 1.f / wz : 0.f;
+    const float sx = fminf(fmaxf((m[0] * fx + m[1] * fy + m[2]) * wz, -2.f), static_cast<float>(W) + 1.f);
+    const float sy = fminf(fmaxf((m[3] * fx + m[4] * fy + m[5]) * wz, -2.f), static_cast<float>(H) + 1.f);
+    const int x0 = static_cast<int>(floorf(sx)), y0 = static_cast<int>(floorf(sy));
+    const float ax = sx - x0, ay = sy - y0;
+    const int xa = min(max(x0, 0), W - 1), xb = min(max(x0 + 1, 0), W - 1);       // replicated border
+    const int ya = min(max(y0, 0), H - 1), yb = min(max(y0 + 1, 0), H - 1);
+    const uint8_t* r0 = src + static_cast<size_t>(ya) * W * 3;
+    const uint8_t* r1 = src + static_cast<size_t>(yb) * W * 3;
+    const float al[3] = {a0, a1, a2}, be[3] = {b0, b1, b2};
+#pragma unroll
+    for (int c = 0; c < 3; ++c) {
+      const float t = (r0[xa * 3 + c] * (1.f - ax) + r0[xb * 3 + c] * ax) * (1.f - ay) +
+                      (r1[xa * 3 + c] * (1.f - ax) + r1[xb * 3 + c] * ax) * ay;
+      v[c] = al[c] * t + be[c];
+    }
+  }
+  for (int c = 0; c < CP; ++c) o[c] = static_cast<T>(c < 3 ? v[c] : 0.f);
+}
+
+// flip[n] = 1 when the arg-max class of row n is odd (180 degrees) and its probability exceeds thresh
+// (fastdeploy/vision/ocr/ppocr/ppocr_v2.cc:150-160)
+template <typename T>
+__global__ void cls_flip_kernel(const T* probs, long long ld, int n, int ncls, float thresh, int* flip, int* label,
+                                float* score) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int best = 0;
+  float bv = -INFINITY;
+  for (int c = 0; c < ncls; ++c) {
+    const float v = pp_to_f<T>(probs[i * ld + c]);
+    if (v > bv) { bv = v; best = c; }
+  }
+  flip[i] = ((best & 1) == 1 && bv > thresh) ? 1 : 0;
+  if (label != nullptr) label[i] = best;
+  if (score != nullptr) score[i] = bv;
+}
+
+}  // namespace fdb
+
+// src: uint8 frames of [H, W, 3] on the device, frame k at byte offset k * page_stride; page: device int32 [N] = frame
+// of each crop (null: all from frame 0); mats: device fp32 [N, 9] (output pixel -> source pixel); valid_w, flip: device
+// int32 [N] (flip may be null); out: [N, OH, OW, CP] fp16 / bf16 / fp32 (out_dtype code).
+FDB_API int fdb_warp_normalize_batch(const void* src, int H, int W, const int* page, long long page_stride, const float* mats,
+                                     const int* valid_w, const int* flip, void* out, int out_dtype, int N, int OH, int OW,
+                                     int CP, const float* alpha, const float* beta, void* stream) {
+  if (N <= 0) return 0;
+  if (H < 1 || W < 1 || OH < 1 || OW < 1 || CP < 3 || CP > 16 || N > 65535) { set_error("warp_normalize_batch: bad shape"); return -1; }
+  const dim3 block(32, 8), grid((OW + 31) / 32, (OH + 7) / 8, N);
+  auto st = static_cast<cudaStream_t>(stream);
+  const uint8_t* s8 = static_cast<const uint8_t*>(src);
+  switch (out_dtype) {
+    case kF16:
+      warp_normalize_kernel<__half><<<grid, block, 0, st>>>(s8, H, W, page, page_stride, mats, valid_w, flip, static_cast<__half*>(out), OH, OW,
+                                                            CP, alpha[0], alpha[1], alpha[2], beta[0], beta[1], beta[2]);
+      break;
+    case kBF16:
+      warp_normalize_kernel<__nv_bfloat16><<<grid, block, 0, st>>>(s8, H, W, page, page_stride, mats, valid_w, flip,
+                                                                   static_cast<__nv_bfloat16*>(out), OH, OW, CP, alpha[0],
+                                                                   alpha[1], alpha[2], beta[0], beta[1], beta[2]);
+      break;
+    case kF32:
+      warp_normalize_kernel<float><<<grid, block, 0, st>>>(s8, H, W, page, page_stride, mats, valid_w, flip, static_cast<float*>(out), OH, OW,
+                                                           CP, alpha[0], alpha[1], alpha[2], beta[0], beta[1], beta[2]);
+      break;
+    default:
+      set_error("warp_normalize_batch: fp16 / bf16 / fp32 output");
+      return -1;
+  }
+  return pp_check("warp_normalize_batch");
+}
+
+FDB_API int fdb_cls_flip(const void* probs, int dtype, long long ld, int n, int ncls, float thresh, int* flip, int* label,
+                         float* score, void* stream) {
+  if (n <= 0) return 0;
+  auto st = static_cast<cudaStream_t>(stream);
+  const int grid = (n + 127) / 128;
+  switch (dtype) {
+    case kF32: cls_flip_kernel<float><<<grid, 128, 0, st>>>(static_cast<const float*>(probs), ld, n, ncls, thresh, flip, label, score); break;
+    case kF16: cls_flip_kernel<__half><<<grid, 128, 0, st>>>(static_cast<const __half*>(probs), ld, n, ncls, thresh, flip, label, score); break;
+    case kBF16: cls_flip_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(probs), ld, n, ncls, thresh, flip, label, score); break;
+    default: set_error("cls_flip: fp32 / fp16 / bf16 probabilities"); return -1;
+  }
+  return pp_check("cls_flip");
 }
 
 // ------------------------------------------------------------------ hard voxelisation

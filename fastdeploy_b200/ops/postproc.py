@@ -7,6 +7,7 @@ before it has been reduced to the few numbers the caller wants.
 from __future__ import annotations
 
 import ctypes
+import math
 from typing import List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -30,6 +31,18 @@ def _lib():
         lib.fdb_hard_voxelize_workspace.argtypes = [ctypes.c_int]
         lib.fdb_hard_voxelize.argtypes = [_P, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_float), ctypes.c_int,
                                           ctypes.c_int, _P, _P, _P, _P, _P, ctypes.c_longlong, _P]
+        lib.fdb_db_postprocess_workspace.restype = ctypes.c_longlong
+        lib.fdb_db_postprocess_workspace.argtypes = [ctypes.c_int] * 4
+        lib.fdb_db_postprocess.argtypes = [_P, ctypes.c_int, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong,
+                                           ctypes.c_int, ctypes.c_int, ctypes.c_int, _P, ctypes.c_float, ctypes.c_float,
+                                           ctypes.c_float, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P, ctypes.c_longlong,
+                                           _P, _P, _P, _P]
+        lib.fdb_warp_normalize_batch.argtypes = [_P, ctypes.c_int, ctypes.c_int, _P, ctypes.c_longlong, _P, _P, _P, _P,
+                                                 ctypes.c_int, ctypes.c_int,
+                                                 ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_float),
+                                                 ctypes.POINTER(ctypes.c_float), _P]
+        lib.fdb_cls_flip.argtypes = [_P, ctypes.c_int, ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_float, _P, _P,
+                                     _P, _P]
         lib._postproc_ready = True
     return lib
 
@@ -130,6 +143,131 @@ def rotate_crop_batch(image: torch.Tensor, boxes: Sequence[Sequence[int]]) -> Tu
     oh = max((s[1] for s in sizes), default=1)
     out = warp_batch(image, np.asarray(mats).reshape(-1, 3, 3), (oh, ow), np.asarray(sizes, np.int32).reshape(-1, 2))
     return out, sizes
+
+
+class DBPostprocess:
+    """Device DB post-processing for maps of one fixed size: owns the scratch and the result buffers, so a call is
+    eight launches and no allocation. ``run`` leaves everything on the device; ``boxes`` reads the results back
+    (one small copy) as per-image lists of ``[x0, y0, ..., x3, y3]``.
+
+    Counterpart of ``DBPostProcessor::BoxesFromBitmap`` (ocr_postprocess_op.cc:238-318) on the host."""
+
+    def __init__(self, n: int, h: int, w: int, device, *, thresh: float = 0.3, box_thresh: float = 0.6,
+                 unclip_ratio: float = 1.5, score_mode: str = "slow", use_dilation: bool = False, max_candidates: int = 1000):
+        self.n, self.h, self.w, self.max_candidates = n, h, w, max_candidates
+        self.thresh, self.box_thresh, self.unclip_ratio = thresh, box_thresh, unclip_ratio
+        self.score_fast, self.dilate = int(score_mode == "fast"), int(use_dilation)
+        nbytes = _lib().fdb_db_postprocess_workspace(n, h, w, max_candidates)
+        self.workspace = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        self.out_boxes = torch.zeros(n, max_candidates, 8, dtype=torch.int32, device=device)
+        self.out_scores = torch.zeros(n, max_candidates, dtype=torch.float32, device=device)
+        self.out_count = torch.zeros(n, dtype=torch.int32, device=device)
+        self.info = torch.zeros(n, 4, dtype=torch.int32, device=device)
+        self.launches = 9          # two clears + seven kernels
+
+    def set_info(self, infos: Sequence[Sequence[int]]) -> None:
+        """``infos[i] = (source width, source height, valid map width, valid map height)``."""
+        self.info.copy_(torch.tensor([list(i) for i in infos], dtype=torch.int32).reshape(self.n, 4), non_blocking=True)
+
+    def run(self, prob: torch.Tensor) -> None:
+        """``prob``: ``[n, h, w]`` view (any strides) of fp32 / fp16 / bf16 probabilities on the device."""
+        assert prob.is_cuda and tuple(prob.shape) == (self.n, self.h, self.w), tuple(prob.shape)
+        _ok(_lib().fdb_db_postprocess(prob.data_ptr(), dtype_code(prob.dtype), prob.stride(2), prob.stride(1),
+                                      prob.stride(0), self.n, self.h, self.w, self.info.data_ptr(), self.thresh,
+                                      self.box_thresh, self.unclip_ratio, self.dilate, self.score_fast, self.max_candidates,
+                                      self.workspace.data_ptr(), self.workspace.numel(), self.out_boxes.data_ptr(),
+                                      self.out_scores.data_ptr(), self.out_count.data_ptr(), current_stream_ptr()),
+            "db_postprocess")
+
+    def boxes(self) -> Tuple[List[List[List[int]]], List[List[float]]]:
+        counts = self.out_count.cpu().tolist()
+        m = max(counts) if counts else 0
+        if m == 0:
+            return [[] for _ in counts], [[] for _ in counts]
+        b = self.out_boxes[:, :m].cpu().numpy()
+        s = self.out_scores[:, :m].cpu().numpy()
+        return [b[i, :c].tolist() for i, c in enumerate(counts)], [s[i, :c].tolist() for i, c in enumerate(counts)]
+
+
+def warp_normalize_batch(image: torch.Tensor, mats: torch.Tensor, valid_w: torch.Tensor, out: torch.Tensor,
+                         alpha: Sequence[float], beta: Sequence[float], flip: Optional[torch.Tensor] = None,
+                         page: Optional[torch.Tensor] = None) -> None:
+    """``out[n] = normalise(warp_n(image))``: ``image`` uint8 ``[H, W, 3]`` or a stack ``[P, H, W, 3]`` with ``page``
+    int32 ``[N]`` naming each crop's frame, ``mats`` fp32 ``[N, 9]`` (output pixel -> source pixel), ``valid_w`` int32
+    ``[N]`` (columns at and beyond it are zero), ``out`` ``[N, OH, OW, CP]`` 16-bit or fp32, ``flip`` int32 ``[N]``
+    (non-zero: the crop is turned by 180 degrees inside its valid width). All on the device."""
+    assert image.is_cuda and image.dtype == torch.uint8 and image.is_contiguous() and image.shape[-1] == 3
+    assert out.is_contiguous() and mats.dtype == torch.float32 and valid_w.dtype == torch.int32
+    assert image.dim() == 3 or (image.dim() == 4 and page is not None and page.dtype == torch.int32)
+    n, oh, ow, cp = out.shape
+    assert mats.numel() >= 9 * n and valid_w.numel() >= n
+    a = (ctypes.c_float * 3)(*[float(v) for v in alpha])
+    b = (ctypes.c_float * 3)(*[float(v) for v in beta])
+    _ok(_lib().fdb_warp_normalize_batch(image.data_ptr(), image.shape[-3], image.shape[-2],
+                                        page.data_ptr() if page is not None else None,
+                                        image.stride(0) if image.dim() == 4 else 0, mats.data_ptr(), valid_w.data_ptr(), flip.data_ptr() if flip is not None else None, out.data_ptr(),
+                                        dtype_code(out.dtype), n, oh, ow, cp, a, b, current_stream_ptr()),
+        "warp_normalize_batch")
+
+
+def cls_flip(probs: torch.Tensor, thresh: float, flip: torch.Tensor, label: Optional[torch.Tensor] = None,
+             score: Optional[torch.Tensor] = None) -> None:
+    """``flip[i] = 1`` when row ``i`` of ``probs [n, classes]`` has an odd arg-max class with probability above
+    ``thresh``; optionally also writes the arg-max ``label`` (int32) and its ``score`` (fp32)."""
+    assert probs.dim() == 2 and probs.stride(1) == 1 and flip.dtype == torch.int32
+    _ok(_lib().fdb_cls_flip(probs.data_ptr(), dtype_code(probs.dtype), probs.stride(0), probs.shape[0], probs.shape[1],
+                            float(thresh), flip.data_ptr(), label.data_ptr() if label is not None else None,
+                            score.data_ptr() if score is not None else None, current_stream_ptr()), "cls_flip")
+
+
+def crop_matrices(boxes: Sequence[Sequence[int]], out_h: int, max_w: int) -> Tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """For each quad: the 3x3 map from a pixel of its ``out_h``-high network input to the source frame (perspective
+    rectification to ``(|p0 p1|, |p0 p3|)``, a 90-degree turn for crops at least 1.5x taller than wide, and the resize
+    to ``out_h`` rows, composed), the valid width ``min(max_w, ceil(out_h * w / h))`` and the aspect ratio ``w / h``."""
+    n = len(boxes)
+    if n == 0:
+        return np.zeros((0, 9), np.float32), np.zeros(0, np.int32), np.zeros(0, np.float32)
+    p = np.asarray(boxes, np.float64).reshape(n, 4, 2)
+    w = np.maximum(np.hypot(*(p[:, 0] - p[:, 1]).T).astype(np.int64), 1).astype(np.float64)
+    h = np.maximum(np.hypot(*(p[:, 0] - p[:, 3]).T).astype(np.int64), 1).astype(np.float64)
+    # homography crop -> frame, solved directly from the four corner pairs (all boxes in one batched solve)
+    zero = np.zeros(n)
+    crop = np.stack([np.stack([zero, zero], 1), np.stack([w, zero], 1), np.stack([w, h], 1), np.stack([zero, h], 1)], 1)
+    a = np.zeros((n, 8, 8))
+    rhs = np.zeros((n, 8))
+    for i in range(4):
+        x, y, u, v = crop[:, i, 0], crop[:, i, 1], p[:, i, 0], p[:, i, 1]
+        a[:, 2 * i, 0], a[:, 2 * i, 1], a[:, 2 * i, 2] = x, y, 1.0
+        a[:, 2 * i, 6], a[:, 2 * i, 7] = -x * u, -y * u
+        a[:, 2 * i + 1, 3], a[:, 2 * i + 1, 4], a[:, 2 * i + 1, 5] = x, y, 1.0
+        a[:, 2 * i + 1, 6], a[:, 2 * i + 1, 7] = -x * v, -y * v
+        rhs[:, 2 * i], rhs[:, 2 * i + 1] = u, v
+    try:
+        sol = np.linalg.solve(a, rhs[..., None])[..., 0]
+    except np.linalg.LinAlgError:           # a degenerate quad somewhere: solve one by one, identity for the bad ones
+        sol = np.zeros((n, 8))
+        for k in range(n):
+            try:
+                sol[k] = np.linalg.solve(a[k], rhs[k])
+            except np.linalg.LinAlgError:
+                sol[k] = [1, 0, 0, 0, 1, 0, 0, 0]
+    inv = np.concatenate([sol, np.ones((n, 1))], 1).reshape(n, 3, 3)
+    tall = h >= w * 1.5
+    if tall.any():
+        # turned output pixel (x', y') of the (h wide, w tall) crop shows upright pixel (w - 1 - y', x')
+        rot = np.zeros((n, 3, 3))
+        rot[:, 0, 1], rot[:, 0, 2], rot[:, 1, 0], rot[:, 2, 2] = -1.0, w - 1, 1.0, 1.0
+        inv = np.where(tall[:, None, None], inv @ rot, inv)
+        w, h = np.where(tall, h, w), np.where(tall, w, h)
+    vw = np.minimum(max_w, np.ceil(out_h * w / h)).astype(np.int64)
+    sx, sy = w / np.maximum(vw, 1), h / out_h
+    # centre-aligned resize: input pixel (x, y) shows crop position ((x + 0.5) * sx - 0.5, (y + 0.5) * sy - 0.5)
+    rs = np.zeros((n, 3, 3))
+    rs[:, 0, 0], rs[:, 0, 2], rs[:, 1, 1], rs[:, 1, 2], rs[:, 2, 2] = sx, 0.5 * sx - 0.5, sy, 0.5 * sy - 0.5, 1.0
+    inv = inv @ rs
+    scale = np.where(np.abs(inv[:, 2, 2]) > 1e-12, inv[:, 2, 2], 1.0)
+    mats = (inv / scale[:, None, None]).reshape(n, 9).astype(np.float32)
+    return mats, vw.astype(np.int32), (w / h).astype(np.float32)
 
 
 def hard_voxelize_device(points: torch.Tensor, voxel_size: Sequence[float], pc_range: Sequence[float],

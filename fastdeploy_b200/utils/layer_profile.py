@@ -113,7 +113,8 @@ def main(argv=None) -> int:
                 fl = conv_flops(meta)
                 row.update(shape=f'{meta["in_shape"][0]}x{meta["in_shape"][1]}x{meta["in_shape"][2]}x{meta["cin_logical"]}'
                                  f'->{meta["cout"]} k{meta["kernel"][0]} s{meta["stride"]}',
-                           variant={0: "generic", 1: "halo", 2: "halo-resident", 3: "pair"}.get(info["variant"], "?"),
+                           variant={0: "generic", 1: "halo", 2: "halo-resident", 3: "pair", 4: "halo-pair",
+                                    5: "halo-pair-resident"}.get(info["variant"], "?"),
                            tile=f'{info["tile_w"]}x{info["tile_h"]}xN{info["block_n"]}', grid=info["grid"],
                            gflop=fl / 1e9, tflops=fl / ms / 1e9, bytes=meta["bytes"])
             rows.append(row)

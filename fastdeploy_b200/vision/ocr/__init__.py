@@ -358,11 +358,33 @@ class PPOCRv2:
         self.detector, self.classifier, self.recognizer = det_model, cls_model, rec_model
         self.cls_batch_size = 1
         self.rec_batch_size = 6
+        # on a GPU the pages stay on the device from the detector's input to the decoded text
+        # (device_pipeline.DeviceOCR); set to False for the host path with OpenCV between the stages
+        self.use_device_pipeline = True
+        self._device_ocr = None
 
     def predict(self, im: np.ndarray) -> OCRResult:
         return self.batch_predict([im])[0]
 
+    def _device_path(self, images):
+        if not self.use_device_pipeline or self.recognizer is None or len(images) == 0:
+            return None
+        stages = [m for m in (self.detector, self.classifier, self.recognizer) if m is not None]
+        if not all(getattr(m.runtime, "on_gpu", False) for m in stages):
+            return None
+        if len({m.runtime.device for m in stages}) != 1 or len({tuple(im.shape) for im in images}) != 1:
+            return None
+        if images[0].ndim != 3 or images[0].shape[2] != 3 or images[0].dtype != np.uint8:
+            return None
+        if self._device_ocr is None:
+            from .device_pipeline import DeviceOCR
+            self._device_ocr = DeviceOCR(self.detector, self.classifier, self.recognizer)
+        return self._device_ocr
+
     def batch_predict(self, images: Sequence[np.ndarray]) -> List[OCRResult]:
+        dev = self._device_path(images)
+        if dev is not None:
+            return dev.predict_pages(list(images))
         import cv2
         results = []
         all_boxes = self.detector.batch_predict(images)
