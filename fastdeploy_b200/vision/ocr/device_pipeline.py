@@ -80,6 +80,9 @@ class DeviceOCR:
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
         self.stage_counts: Dict[str, int] = {}
+        self.rec_streams = 4
+        self._side: List[torch.cuda.Stream] = []
+        self._plan_stream: Dict[Tuple[int, int], int] = {}
 
     # ------------------------------------------------------------------ start-up
     def warm_up(self, page_hw: Tuple[int, int], pages: int) -> None:
@@ -131,7 +134,7 @@ class DeviceOCR:
                       label=torch.zeros(full, dtype=torch.int32, device=dev),
                       score=torch.zeros(full, dtype=torch.float32, device=dev),
                       stage=torch.zeros(2, cap, 11, dtype=torch.float32, device=dev),
-                      vw_pad=torch.zeros(max(self.batches), dtype=torch.int32, device=dev),
+                      vw_pad=torch.zeros(self.rec_streams, max(self.batches), dtype=torch.int32, device=dev),
                       order=torch.zeros(cap, dtype=torch.int64, device=dev),
                       order_host=torch.zeros(cap, dtype=torch.int64).pin_memory(),
                       host=torch.zeros(2, cap, 11, dtype=torch.float32).pin_memory())
@@ -221,32 +224,55 @@ class DeviceOCR:
         # crops travel in sorted order, so each group's matrices are one contiguous slice
         sorted_vw = np.minimum(rec_vw[order], [_bucket(int(v), self.rec_widths) for v in need_w]).astype(np.int32)
         self._upload(cs, rec_mats[order], sorted_vw, page_idx[order], total, keep_flip_order=order)
+        # The recogniser plans of different (batch, width) buckets own separate buffers, and each is a chain of
+        # small launches that leaves most SMs idle: the buckets run side by side on a few streams. A plan always
+        # runs on the same stream, so two chunks that share a plan stay ordered.
         pieces = []
         pos = 0
+        main = torch.cuda.current_stream(self.device)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        if not self._side:
+            self._side = [torch.cuda.Stream(self.device) for _ in range(self.rec_streams)]
+        used = {}
         for wb, idx in groups:
             done = 0
             while done < len(idx):
                 b = _bucket(len(idx) - done, self.batches)
                 k = min(b, len(idx) - done)
                 plan = self.rec.plan(b, self.rec_h, wb)
+                key = (b, wb)
+                if key not in self._plan_stream:
+                    self._plan_stream[key] = len(self._plan_stream) % len(self._side)
+                si = self._plan_stream[key]
+                side = self._side[si]
+                if si not in used:
+                    side.wait_event(ready)
+                    used[si] = side
                 x = self.rec.input_nhwc(plan)
                 s = pos + done
-                if k < b:
-                    cs["vw_pad"][:b].copy_(cs["vw"][s:s + b])
-                    cs["vw_pad"][k:b].zero_()
-                    vw = cs["vw_pad"]
-                else:
-                    vw = cs["vw"][s:]
-                PP.warp_normalize_batch(pages_dev, cs["mats"][s:], vw, x, alpha_r, beta_r, flip=cs["flip_sorted"][s:],
-                                        page=cs["page"][s:])
-                plan.run()
-                probs = self.rec.output(plan)
-                ids, lens, scores = PP.ctc_greedy_decode_device(probs[:k].contiguous() if k < b else probs)
+                with torch.cuda.stream(side):
+                    if k < b:
+                        pad = cs["vw_pad"][si]
+                        pad[:b].copy_(cs["vw"][s:s + b])
+                        pad[k:b].zero_()
+                        vw = pad
+                    else:
+                        vw = cs["vw"][s:]
+                    PP.warp_normalize_batch(pages_dev, cs["mats"][s:], vw, x, alpha_r, beta_r, flip=cs["flip_sorted"][s:],
+                                            page=cs["page"][s:])
+                    plan.run()
+                    probs = self.rec.output(plan)
+                    ids, lens, scores = PP.ctc_greedy_decode_device(probs[:k].contiguous() if k < b else probs)
                 pieces.append((idx[done:done + k], ids[:k], lens[:k], scores[:k]))
                 self.gpu_launches += 3 + plan.native_kernel_launches
                 self.stage_counts[f"rec_b{b}_w{wb}"] = self.stage_counts.get(f"rec_b{b}_w{wb}", 0) + 1
                 done += k
             pos += len(idx)
+        for side in used.values():
+            ev = torch.cuda.Event()
+            ev.record(side)
+            main.wait_event(ev)
         # ---- one read-back of everything the host needs
         labels = self.rec_model.postprocessor.label_list
         texts, rscores = [""] * total, [0.0] * total
