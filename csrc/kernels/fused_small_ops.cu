@@ -299,6 +299,44 @@ __global__ void __launch_bounds__(256) quantize_e4m3_kernel(const uint8_t* __res
   }
 }
 
+// Dynamic per-row (per-token) quantisation: one warp per row finds the row's absolute maximum, maps it onto 448 and
+// writes e4m3 plus the fp32 scale the consuming GEMM multiplies back in its epilogue. Columns C..CP-1 (the padding up
+// to the GEMM's K block) are written as zeros. The row is read twice; the second read hits L1 / L2.
+template <bool BF16>
+__global__ void __launch_bounds__(256) quantize_rows_e4m3_kernel(const uint8_t* __restrict__ x, uint8_t* __restrict__ y,
+                                                                 float* __restrict__ scales, long long rows, int C8,
+                                                                 int CP8, int x_ld, int y_ld) {
+  const long long r = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  float amax = 0.f;
+  for (int cg = lane; cg < C8; cg += 32) {
+    float f[8];
+    unpack8f<BF16>(__ldg(reinterpret_cast<const uint4*>(x + (r * x_ld + cg * 8) * 2)), f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(f[k]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  amax = fmaxf(amax, 1e-12f);
+  const float inv = 448.f / amax;
+  if (lane == 0) scales[r] = amax / 448.f;
+  for (int cg = lane; cg < CP8; cg += 32) {
+    uint32_t w[2] = {0u, 0u};
+    if (cg < C8) {
+      float f[8];
+      unpack8f<BF16>(__ldg(reinterpret_cast<const uint4*>(x + (r * x_ld + cg * 8) * 2)), f);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * h] * inv, f[4 * h + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * h + 2] * inv, f[4 * h + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+        w[h] = lo | (hi << 16);
+      }
+    }
+    *reinterpret_cast<uint2*>(y + r * y_ld + cg * 8) = make_uint2(w[0], w[1]);
+  }
+}
+
 }  // namespace fdb
 
 using namespace fdb;
@@ -429,6 +467,26 @@ FDB_API void* fdb_fused_create(int kind, const FusedDesc* dp) {
         const int grid = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));
         if (bf) quantize_e4m3_kernel<true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], total, C / 8, x_ld, y_ld, scale);
         else quantize_e4m3_kernel<false><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], total, C / 8, x_ld, y_ld, scale);
+        FDB_FUSED_CHECK();
+      };
+      break;
+    }
+    case 5: {
+      // quantize_rows_e4m3: p0 x 16-bit [rows][x_ld], p1 y e4m3 [rows][y_ld], p2 scales fp32 [rows];
+      //                     i0 rows, i1 C, i2 x_ld, i3 y_ld, i4 bf16, i5 CP (padded row length written, >= C)
+      const long long rows = d.i[0];
+      const int C = d.i[1], x_ld = d.i[2], y_ld = d.i[3], CP = d.i[5] > 0 ? d.i[5] : d.i[1];
+      const bool bf = d.i[4] != 0;
+      if (C % 8 || CP % 8 || CP < C || CP > y_ld || x_ld % 8 || y_ld % 8 || (reinterpret_cast<uintptr_t>(d.p[0]) & 15) ||
+          (reinterpret_cast<uintptr_t>(d.p[1]) & 7)) {
+        set_error("quantize_rows_e4m3: C, CP and row pitches must be multiples of 8, C <= CP <= y_ld, pointers aligned");
+        delete op; return nullptr;
+      }
+      op->fn = [=](cudaStream_t s) {
+        if (rows == 0) return 0;
+        const int grid = static_cast<int>((rows * 32 + 255) / 256);
+        if (bf) quantize_rows_e4m3_kernel<true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (float*)d.p[2], rows, C / 8, CP / 8, x_ld, y_ld);
+        else quantize_rows_e4m3_kernel<false><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (float*)d.p[2], rows, C / 8, CP / 8, x_ld, y_ld);
         FDB_FUSED_CHECK();
       };
       break;

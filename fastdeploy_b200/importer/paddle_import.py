@@ -783,3 +783,6 @@ def load_paddle(model_bytes: bytes, params_bytes: Optional[bytes], name: str = "
     prog = parse_program(model_bytes)
     params = parse_params(prog, params_bytes) if params_bytes else {}
     return import_program(prog, params, name)
+
+
+from . import paddle_ops_extra  # noqa: E402,F401  (registers the second batch of mappers)

@@ -547,7 +547,12 @@ def _scatter_nd(node, x, idx, upd):
     idx = idx.long()
     k = idx.shape[-1]
     flat = idx.reshape(-1, k)
-    y[tuple(flat[:, i] for i in range(k))] = upd.reshape([-1] + list(x.shape[k:]))
+    where = tuple(flat[:, i] for i in range(k))
+    upd = upd.reshape([-1] + list(x.shape[k:])).to(x.dtype)
+    if node.attr("reduction", "none") == "add":
+        y.index_put_(where, upd, accumulate=True)
+    else:
+        y[where] = upd
     return y
 
 
@@ -832,3 +837,6 @@ class Interpreter:
         if keep_all:
             return {k: v for k, v in env.items() if v is not None}
         return {n: env[n] for n in names}
+
+
+from . import interp_extra  # noqa: E402,F401  (registers the second batch of operators)

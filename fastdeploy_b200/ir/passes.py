@@ -122,6 +122,56 @@ def eliminate_identity(graph: Graph) -> int:
     return changed
 
 
+# --------------------------------------------------------------------------- quantised models
+ACT_SCALES_KEY = "fdb_act_scales"
+
+
+def get_act_scales(graph: Graph) -> Dict[str, float]:
+    """Static activation ranges recorded by :func:`fold_qdq` (or loaded from a calibration file): tensor name ->
+    absolute maximum the tensor was calibrated to. Kept as a JSON string so that it survives the on-disk graph cache."""
+    import json
+    raw = graph.metadata.get(ACT_SCALES_KEY, "")
+    return {k: float(v) for k, v in json.loads(raw).items()} if raw else {}
+
+
+def set_act_scales(graph: Graph, scales: Dict[str, float]) -> None:
+    import json
+    graph.metadata[ACT_SCALES_KEY] = json.dumps({k: float(v) for k, v in scales.items()})
+
+
+def fold_qdq(graph: Graph) -> int:
+    """``x -> QuantizeLinear(s) -> DequantizeLinear(s) -> consumer``  =>  ``x -> consumer`` with the calibrated range
+    ``s * 127`` of ``x`` recorded for the executor, which quantises ``x`` to e4m3 with that static range when it runs
+    the consumer as an fp8 GEMM (and simply drops the fake quantisation at 16-bit precision). Weight-side
+    ``DequantizeLinear`` nodes have constant inputs and are folded into float weights by constant folding before this
+    pass. The reference rewrites the same pattern for TensorRT / ONNX Runtime int8
+    (paddle2onnx/mapper/quantize_helper.cc:80-190, 348-620)."""
+    changed = 0
+    prod = graph.producers()
+    scales = get_act_scales(graph)
+    for dq in list(graph.nodes):
+        if dq.op != "DequantizeLinear":
+            continue
+        q = prod.get(dq.inputs[0])
+        if q is None or q.op != "QuantizeLinear" or q.inputs[1] not in graph.initializers:
+            continue
+        s_q = np.asarray(graph.initializers[q.inputs[1]], np.float64).reshape(-1)
+        s_d = np.asarray(graph.initializers.get(dq.inputs[1], s_q), np.float64).reshape(-1)
+        if s_q.size != 1 or s_d.size != 1 or abs(s_q[0] - s_d[0]) > 1e-12 * max(1.0, abs(s_q[0])):
+            continue                      # per-channel activation scales or a re-scaling pair: keep the fake quantisation
+        if len(graph.consumers().get(q.outputs[0], [])) != 1:
+            continue
+        x = q.inputs[0]
+        scales[x] = float(s_q[0]) * 127.0
+        _replace_uses(graph, dq.outputs[0], x)
+        _remove(graph, [q, dq])
+        prod = graph.producers()
+        changed += 1
+    if changed:
+        set_act_scales(graph, scales)
+    return changed
+
+
 # --------------------------------------------------------------------------- conv folding
 def fold_batchnorm(graph: Graph) -> int:
     """Conv / ConvTranspose -> BatchNormalization  =>  the convolution with scaled weights and folded bias."""
@@ -677,6 +727,10 @@ def optimize(graph: Graph, input_shapes: Optional[Dict[str, Sequence[int]]] = No
     for _ in range(4):
         if not fold_constants(g, info):
             break
+    if fold_qdq(g):
+        for _ in range(2):
+            if not fold_constants(g, info):
+                break
     fold_conv_bias_add(g)
     fold_batchnorm(g)
     fold_conv_bias_add(g)

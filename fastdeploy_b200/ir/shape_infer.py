@@ -24,6 +24,22 @@ VALUE_ARGS = {
     "Unsqueeze": (1,), "CumSum": (1,), "Clip": (1, 2), "OneHot": (1,), "ReduceSum": (1,), "ReduceMean": (1,),
     "ReduceMax": (1,), "ReduceMin": (1,),
 }
+
+
+def _meta(shape, dtype=torch.float32):
+    return torch.empty([int(d) for d in shape], dtype=dtype, device="meta")
+
+
+# output shapes of operators whose reference implementation loops over values and cannot run on meta tensors
+SHAPE_RULES = {
+    "RoiAlign": lambda node, x, rois, idx: _meta([rois.shape[0], x.shape[1], node.attr("output_height", 1),
+                                                  node.attr("output_width", 1)], x.dtype),
+    "YoloBox": lambda node, x, img: (
+        _meta([x.shape[0], (len(node.attr("anchors")) // 2) * x.shape[2] * x.shape[3], 4], x.dtype),
+        _meta([x.shape[0], (len(node.attr("anchors")) // 2) * x.shape[2] * x.shape[3], node.attr("class_num")], x.dtype)),
+    "SetValue": lambda node, x, *v: _meta(x.shape, x.dtype),
+    "TemporalShift": lambda node, x: _meta(x.shape, x.dtype),
+}
 # a real tensor larger than this is treated as data, not as a shape tensor
 MAX_REAL_ELEMS = 4096
 
@@ -90,6 +106,8 @@ def infer_shapes(graph: Graph, input_shapes: Dict[str, Sequence[int]],
                 k = k if k > 0 else m
                 res = (torch.empty(n * k, 6, device="meta"), torch.empty(n * k, 1, dtype=torch.int64, device="meta"),
                        torch.empty(n, dtype=torch.int32, device="meta"))
+            elif any_meta and node.op in SHAPE_RULES:
+                res = SHAPE_RULES[node.op](node, *args)
             else:
                 if any_meta:
                     args = [(_to_meta(a) if (a is not None and k not in value_pos) else a) for k, a in enumerate(args)]

@@ -226,3 +226,11 @@ def quantize_e4m3(x: torch.Tensor, y: torch.Tensor, *, rows: int, c: int, scale:
     the activation scale the consuming fp8 GEMM dequantises with)."""
     assert y.dtype == torch.float8_e4m3fn
     return _make_fused(4, [x, y], [rows, c, x_ld or c, y_ld or c, _bf(x)], [scale], name="quantize_e4m3")
+
+
+def quantize_rows_e4m3_op(x: torch.Tensor, y: torch.Tensor, scales: torch.Tensor, *, rows: int, c: int,
+                          x_ld: Optional[int] = None, y_ld: Optional[int] = None, c_padded: Optional[int] = None) -> NativeOp:
+    """Dynamic per-row quantisation ``y[r] = e4m3(x[r] * 448 / max|x[r]|)``, ``scales[r] = max|x[r]| / 448``; columns
+    ``c .. c_padded - 1`` of ``y`` are zeroed (the consuming fp8 GEMM's K padding)."""
+    assert y.dtype == torch.float8_e4m3fn and scales.dtype == torch.float32 and scales.numel() >= rows
+    return _make_fused(5, [x, y, scales], [rows, c, x_ld or c, y_ld or c, _bf(x), c_padded or c], name="quantize_rows_e4m3")

@@ -169,10 +169,18 @@ class Lowering(GenericLowering):
     """Builds a :class:`Plan` from an optimised graph and concrete input shapes."""
 
     def __init__(self, graph: Graph, input_shapes: Dict[str, Sequence[int]], device: torch.device,
-                 dtype: torch.dtype = torch.float16, input_values: Optional[Dict[str, np.ndarray]] = None):
+                 dtype: torch.dtype = torch.float16, input_values: Optional[Dict[str, np.ndarray]] = None,
+                 fp8: bool = False, act_scales: Optional[Dict[str, float]] = None):
         self.g = graph
         self.device = device
         self.dtype = dtype
+        # fp8: linear layers run as e4m3 GEMMs (per-output-channel weight scales; activations quantised with the
+        # calibrated static range when one is known for the tensor, else per row on the fly)
+        self.fp8 = fp8
+        self.act_scales = dict(passes.get_act_scales(graph))
+        self.act_scales.update(act_scales or {})
+        self.q8: Dict[str, Tuple[torch.Tensor, Optional[torch.Tensor], float]] = {}
+        self.fp8_gemms = 0
         self.info: ShapeInfo = infer_shapes(graph, input_shapes, input_values)
         self.plan = Plan(device)
         self.vals: Dict[str, Val] = {}
@@ -536,6 +544,10 @@ class Lowering(GenericLowering):
         out_shape = self.info.shapes[node.outputs[0]]
         is_output = node.outputs[0] in self.g.output_names()
         y = torch.zeros(rows, _round8(nout), dtype=torch.float32 if is_output else self.dtype, device=self.device)
+        if self.fp8 and not (len(node.inputs) > 3 and node.inputs[3]) and kdim % 16 == 0 and nout >= 16 and kdim >= 64:
+            self._lower_gemm_fp8(node, x_name, x2, w, w_name, bias, y, rows, kdim, nout)
+            self.vals[node.outputs[0]] = Val(y[:, :nout].unflatten(0, out_shape[:-1]), False)
+            return None
         res = None
         if len(node.inputs) > 3 and node.inputs[3]:
             res = self.rows_view(node.inputs[3], rows, nout)
@@ -547,6 +559,43 @@ class Lowering(GenericLowering):
         self.plan.add_native(op, node)
         op.launch()
         self.vals[node.outputs[0]] = Val(y[:, :nout].unflatten(0, out_shape[:-1]), False)
+
+    def _lower_gemm_fp8(self, node: Node, x_name: str, x2: torch.Tensor, w: np.ndarray, w_name: str, bias, y: torch.Tensor,
+                        rows: int, kdim: int, nout: int) -> None:
+        """Linear layer on e4m3 operands (``kind::f8f6f4`` MMAs, fp32 accumulation). Weights: one scale per output
+        channel. Activations: the tensor's calibrated range when the graph or a calibration file gives one (static
+        quantisation, the scale folds into the per-channel scale and the epilogue takes its straight path), else a
+        per-row range found on the fly. The quantised copy of an activation is shared by all its consumers.
+        The reference's int8 counterpart is TensorRT's calibrated engine build
+        (fastdeploy/runtime/backends/tensorrt/trt_backend.cc:619-631)."""
+        from ..ops.conv_gemm import FP8_MAX, pack_linear_weight_fp8
+        key = (w_name, "lin8")
+        if key not in self.packed:
+            wq, sw = pack_linear_weight_fp8(torch.from_numpy(np.ascontiguousarray(w)).float().to(self.device))
+            self.packed[key] = (wq, sw.float().contiguous())
+        wq, sw = self.packed[key]
+        if x_name not in self.q8:
+            xq = torch.zeros(rows, kdim, dtype=torch.float8_e4m3fn, device=self.device)
+            amax = self.act_scales.get(x_name)
+            if amax is not None and amax > 0:
+                s_act = float(amax) / FP8_MAX
+                op = K.quantize_e4m3(x2, xq, rows=rows, c=kdim, scale=1.0 / s_act, x_ld=x2.stride(0), y_ld=kdim)
+                self.q8[x_name] = (xq, None, s_act)
+            else:
+                sa = torch.zeros(rows, dtype=torch.float32, device=self.device)
+                op = K.quantize_rows_e4m3_op(x2, xq, sa, rows=rows, c=kdim, x_ld=x2.stride(0), y_ld=kdim)
+                self.q8[x_name] = (xq, sa, 1.0)
+            self.plan.add_native(op, node)
+            op.launch()
+        xq, sa, s_act = self.q8[x_name]
+        scale_b = sw if sa is not None else (sw * s_act).contiguous()
+        op = ConvGemm(xq, wq, y, in_shape=(1, 1, rows, kdim), out_hw=(1, rows), cout=nout, bias=bias,
+                      act=node.attr("activation", "none"), act_alpha=node.attr("act_alpha", 0.0),
+                      act_beta=node.attr("act_beta", 0.0), x_ld=kdim, y_ld=y.stride(0), scale_a=sa, scale_b=scale_b,
+                      status=self.plan.status, name=f"gemm_fp8:{node.name}")
+        self.plan.add_native(op, node)
+        op.launch()
+        self.fp8_gemms += 1
 
     def rows_view(self, name: str, rows: int, cols: int) -> torch.Tensor:
         """``[rows, cols]`` 16-bit view with unit inner stride and 8-aligned row stride."""
@@ -1002,17 +1051,20 @@ def optimize_cached(graph: Graph, input_shapes, input_values, opt_level: int, dt
 
 
 def build_plan(graph: Graph, input_shapes: Dict[str, Sequence[int]], device, dtype=torch.float16,
-               input_values: Optional[Dict[str, np.ndarray]] = None, opt_level: int = 2, cache_dir: str = "") -> Plan:
-    """Optimises ``graph`` for the given shapes and lowers it to a plan on ``device``."""
+               input_values: Optional[Dict[str, np.ndarray]] = None, opt_level: int = 2, cache_dir: str = "",
+               fp8: bool = False, act_scales: Optional[Dict[str, float]] = None) -> Plan:
+    """Optimises ``graph`` for the given shapes and lowers it to a plan on ``device``. ``fp8`` runs the linear layers on
+    e4m3 operands; ``act_scales`` (tensor name -> calibrated absolute maximum) adds to the ranges the graph carries."""
     device = torch.device(device)
     with torch.cuda.device(device):
         g = optimize_cached(graph, input_shapes, input_values, opt_level, dtype, cache_dir)
-        low = Lowering(g, input_shapes, device, dtype, input_values)
+        low = Lowering(g, input_shapes, device, dtype, input_values, fp8=fp8, act_scales=act_scales)
         for node in g.nodes:
             if node.op == "PPYOLOEPost":
                 low.plan_PPYOLOEPost(node)
         plan = low.build()
         plan.extra["graph"] = g
+        plan.extra["fp8_gemms"] = low.fp8_gemms
     return plan
 
 
@@ -1058,7 +1110,7 @@ def _lower_EmbedLayerNorm(self: Lowering, node: Node):
                 ids.append(None)
                 continue
             full = np.broadcast_to(self.g.initializers[nm], out_shape[:-1]).reshape(-1)
-            ids.append(torch.from_numpy(np.ascontiguousarray(full)).long().to(self.device))
+            ids.append(torch.from_numpy(np.array(full, dtype=np.int64)).to(self.device))
             continue
         v = self.get(nm).t
         if v.dtype != torch.int64 or not v.is_contiguous() or v.numel() != rows:

@@ -19,10 +19,11 @@ from ..utils import log
 @dataclass
 class NativeOption:
     """Knobs of the sm_100a backend."""
-    precision: str = "fp16"            # fp16 | bf16 | fp8 (block-scaled weights + activations where supported)
+    precision: str = "fp16"            # fp16 | bf16 | fp8 (bf16 activations, e4m3 operands with per-channel / per-token scales in the linear layers)
     use_cuda_graph: bool = True
     opt_level: int = 2
     max_plans: int = 8                 # shape buckets kept alive
+    quant_scales_file: str = ""        # calibrated activation ranges for precision "fp8" (default: quant_scales.json next to the model)
     tp_degree: int = 1
     dp_gpus: List[int] = field(default_factory=list)
     plan_cache_dir: str = ""

@@ -85,8 +85,11 @@ class Runtime:
             from .. import _native
             _native.kernels()           # fail loudly when the kernel library is missing
             self.device = torch.device("cuda", self.option.device_id)
-            self.dtype = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp8": torch.float16}[
+            # fp8: 16-bit (bf16) activations between layers, e4m3 operands inside the linear layers
+            self.dtype = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp8": torch.bfloat16}[
                 self.option.native_option.precision]
+            self.fp8 = self.option.native_option.precision == "fp8"
+            self.act_scales = self._load_quant_scales() if self.fp8 else {}
             if self.option.trt_shapes:
                 shapes = {k: v["opt"] for k, v in self.option.trt_shapes.items()}
                 if all(vi.name in shapes for vi in self.graph.inputs):
@@ -120,6 +123,29 @@ class Runtime:
     def get_output_infos(self) -> List[TensorInfo]:
         return [self.get_output_info(i) for i in range(self.num_outputs())]
 
+    def _load_quant_scales(self) -> Dict[str, float]:
+        """Static activation ranges from a calibration file: ``quant_scales.json`` next to the model (what
+        ``fastdeploy compress`` writes) or the file named by ``native_option.quant_scales_file``. Layers are keyed by
+        node name there; the executor wants the range of each layer's *input tensor*, which the file records as
+        ``input``."""
+        import json
+        import os
+        path = getattr(self.option.native_option, "quant_scales_file", "") or ""
+        if not path and getattr(self.option, "model_file", ""):
+            cand = os.path.join(os.path.dirname(self.option.model_file), "quant_scales.json")
+            path = cand if os.path.exists(cand) else ""
+        if not path:
+            return {}
+        with open(path) as f:
+            doc = json.load(f)
+        out: Dict[str, float] = {}
+        for entry in doc.get("layers", {}).values():
+            name, amax = entry.get("input"), entry.get("act_absmax")
+            if name and amax and amax > 0:
+                out[name] = max(out.get(name, 0.0), float(amax))
+        log.info(f"loaded {len(out)} calibrated activation ranges from {path}")
+        return out
+
     # ------------------------------------------------------------------ plans
     def _plan_for(self, shapes: Dict[str, Sequence[int]]):
         key = tuple((k, tuple(int(d) for d in shapes[k])) for k in sorted(shapes))
@@ -130,7 +156,8 @@ class Runtime:
             with _PLAN_BUILD_LOCK:
                 plan = build_plan(self.graph, {k: list(v) for k, v in shapes.items()}, self.device, self.dtype,
                                   opt_level=self.option.native_option.opt_level,
-                                  cache_dir=self.option.native_option.plan_cache_dir)
+                                  cache_dir=self.option.native_option.plan_cache_dir,
+                                  fp8=getattr(self, "fp8", False), act_scales=getattr(self, "act_scales", None))
                 if self.option.native_option.use_cuda_graph:
                     try:
                         plan.capture()

@@ -83,7 +83,8 @@ def calibrate(graph, feeds_list: List[Dict[str, np.ndarray]]) -> Dict[str, Dict[
     for n in nodes:
         key = n.name or n.outputs[0]
         w = graph.initializers.get(n.inputs[1]) if len(n.inputs) > 1 else None
-        entry = {"op": n.op, "act_absmax": amax[key], "act_scale": (amax[key] / 448.0) if amax[key] > 0 else 1.0}
+        entry = {"op": n.op, "input": n.inputs[0], "act_absmax": amax[key],
+                 "act_scale": (amax[key] / 448.0) if amax[key] > 0 else 1.0}
         if w is not None:
             wa = np.abs(np.asarray(w, np.float32)).reshape(w.shape[0], -1).max(1)
             entry["weight"] = n.inputs[1]
