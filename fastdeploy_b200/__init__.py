@@ -5,7 +5,8 @@ from __future__ import annotations
 
 __version__ = "0.1.0"
 
-from .core.types import Backend, Device, FDDataType, ModelFormat, TensorInfo
+from .core.types import (Backend, Device, FDDataType, ModelFormat, TensorInfo, get_available_backends,
+                         is_backend_available)
 from .runtime.option import RuntimeOption
 from .runtime.runtime import Runtime
 from .runtime.model import FastDeployModel

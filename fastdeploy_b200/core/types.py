@@ -92,3 +92,32 @@ class TensorInfo:
 
     def __repr__(self) -> str:
         return f"TensorInfo(name: {self.name}, shape: {self.shape}, dtype: {self.dtype.name})"
+
+
+# Which back ends can serve a model format / a device (fastdeploy/runtime/enum_variables.h:82-108). Every selector the
+# reference knows is accepted; on this build they all resolve to the native sm_100a executor on a GPU and to the
+# reference interpreter on the CPU, so the tables list those two routes under the names a user may ask for.
+DEFAULT_BACKENDS_BY_FORMAT = {
+    "PADDLE": ["PDINFER", "ORT", "TRT", "NATIVE"],
+    "ONNX": ["ORT", "TRT", "NATIVE"],
+}
+DEFAULT_BACKENDS_BY_DEVICE = {
+    "CPU": ["PDINFER", "ORT", "OPENVINO", "NATIVE"],
+    "GPU": ["PDINFER", "ORT", "TRT", "NATIVE"],
+}
+
+
+def get_available_backends() -> List["Backend"]:
+    """Back ends a ``RuntimeOption`` may select (fastdeploy/runtime/enum_variables.cc:101-134)."""
+    return [Backend.ORT, Backend.TRT, Backend.PDINFER, Backend.OPENVINO, Backend.NATIVE]
+
+
+def is_backend_available(backend) -> bool:
+    return Backend(backend) in get_available_backends()
+
+
+def supported(format_or_device, backend) -> bool:
+    """``Supported(format, backend)`` / ``Supported(device, backend)`` of the reference."""
+    name = getattr(format_or_device, "name", str(format_or_device)).upper()
+    table = DEFAULT_BACKENDS_BY_FORMAT.get(name) or DEFAULT_BACKENDS_BY_DEVICE.get(name)
+    return table is not None and Backend(backend).name in table

@@ -217,14 +217,17 @@ class _GpuSlot:
     """Staging buffers of one in-flight batch."""
 
     def __init__(self, device, raw_bytes: int, n: int, out_rows: int):
+        from ...core.allocator import pinned_tensor
         from ...ops.preproc import IMAGE_META
         self.raw = torch.empty(raw_bytes, dtype=torch.uint8, device=device)
-        self.meta_host = torch.empty(n * IMAGE_META.itemsize, dtype=torch.uint8).pin_memory()
+        # page-locked staging from the caching pool: a new slot (a new batch shape) costs no cudaHostAlloc after the
+        # pool has warmed up
+        self.meta_host = pinned_tensor([n * IMAGE_META.itemsize], torch.uint8)
         self.meta_dev = torch.empty(n * IMAGE_META.itemsize, dtype=torch.uint8, device=device)
-        self.sf_host = torch.empty(n, 2, dtype=torch.float32).pin_memory()
-        self.out_host = torch.empty(n, out_rows, 6, dtype=torch.float32).pin_memory()
-        self.num_host = torch.empty(n, dtype=torch.int32).pin_memory()
-        self.status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.sf_host = pinned_tensor([n, 2], torch.float32)
+        self.out_host = pinned_tensor([n, out_rows, 6], torch.float32)
+        self.num_host = pinned_tensor([n], torch.int32)
+        self.status_host = pinned_tensor([1], torch.int32).zero_()
         self.copied = torch.cuda.Event()
         self.done = torch.cuda.Event()
         self.pre = None

@@ -93,3 +93,30 @@ def test_math_sort_softmax_quantile_gather():
     a = fn.gaussian_random([1000], 1.0, 2.0, seed=3).cpu_data()
     assert abs(a.mean() - 1.0) < 0.3 and abs(a.std() - 2.0) < 0.3
     assert np.array_equal(a, fn.gaussian_random([1000], 1.0, 2.0, seed=3).cpu_data())
+
+
+def test_scalar_ue8m0_timecounter_and_backend_tables():
+    import math
+    import time
+    import fastdeploy_b200 as fd
+    from fastdeploy_b200.core.scalar import Scalar, ue8m0_from_float, ue8m0_to_float
+    from fastdeploy_b200.core.types import supported
+    from fastdeploy_b200.utils.perf import TimeCounter
+    assert Scalar(3).dtype == fd.FDDataType.INT64 and Scalar(3).to(int) == 3 and Scalar(2.5).to(float) == 2.5
+    assert Scalar(True).dtype == fd.FDDataType.BOOL and Scalar(7.9, fd.FDDataType.INT32).to(int) == 7
+    assert Scalar("-inf").to(float) == -math.inf and math.isnan(Scalar("nan").to(float))
+    assert Scalar(2 ** 40 + 1).to(int) == 2 ** 40 + 1
+    with pytest.raises(ValueError):
+        Scalar("twelve")
+    # ue8m0: powers of two are exact, everything else rounds up so a scaled block cannot overflow
+    assert ue8m0_to_float(ue8m0_from_float(1.0)) == 1.0 and ue8m0_to_float(ue8m0_from_float(0.25)) == 0.25
+    assert ue8m0_to_float(ue8m0_from_float(3.0)) == 4.0 and ue8m0_to_float(ue8m0_from_float(0.3)) == 0.5
+    assert ue8m0_from_float(float("nan")) == 255 and math.isnan(ue8m0_to_float(255))
+    t = TimeCounter()
+    t.start()
+    time.sleep(0.02)
+    t.end()
+    assert 0.015 < t.duration() < 0.5
+    assert fd.Backend.NATIVE in fd.get_available_backends() and fd.is_backend_available(fd.Backend.TRT)
+    assert supported(fd.ModelFormat.ONNX, fd.Backend.ORT) and not supported(fd.ModelFormat.ONNX, fd.Backend.PDINFER)
+    assert supported(fd.Device.GPU, fd.Backend.TRT)
