@@ -23,7 +23,7 @@ from ...ops.nms import multiclass_nms_reference
 from ...runtime.model import FastDeployModel
 from ...runtime.option import RuntimeOption
 from ...utils import log
-from ..result import DetectionResult
+from ..result import DetectionResult, Mask
 
 
 class NMSOption:
@@ -183,10 +183,111 @@ class PaddleDetPostprocessor:
     def set_nms_rotated_option(self, option):
         self.nms_rotated_option = option
 
+    def set_scale_factor(self, scale_factor) -> None:
+        """(scale_h, scale_w) the pre-processor resized the image by; rotated boxes are divided by it."""
+        self.scale_factor = [float(scale_factor[0]), float(scale_factor[1])]
+
     def run(self, tensors: Sequence[np.ndarray]) -> List[DetectionResult]:
+        """Dispatch of the reference (fastdeploy/vision/detection/ppdet/postprocessor.cc:318-357): SOLOv2 (boxes from
+        masks), PP-YOLOE-R (8-value boxes -> rotated multiclass NMS), boxes with or without NMS in the graph, and the
+        mask output of Mask R-CNN cropped to each box."""
+        if self.arch == "SOLOv2":
+            return self._solov2(tensors)
+        first = tensors[0]
+        if getattr(first, "ndim", 0) == 3 and first.shape[2] == 8:
+            return self._rotated(first, tensors[1])
         if self.with_nms_:
-            return self._with_nms(np.asarray(tensors[0]), np.asarray(tensors[1]))
-        return self._without_nms(np.asarray(tensors[0]), np.asarray(tensors[1]))
+            results = self._with_nms(np.asarray(tensors[0]), np.asarray(tensors[1]))
+        else:
+            results = self._without_nms(np.asarray(tensors[0]), np.asarray(tensors[1]))
+        if len(tensors) > 2:
+            masks = np.asarray(tensors[2])
+            if masks.shape[0] != np.asarray(tensors[0]).reshape(-1, 6).shape[0]:
+                raise ValueError(f"mask output has {masks.shape[0]} entries for "
+                                 f"{np.asarray(tensors[0]).reshape(-1, 6).shape[0]} boxes")
+            self._process_mask(masks, results)
+        return results
+
+    @staticmethod
+    def _process_mask(masks: np.ndarray, results: List[DetectionResult]) -> None:
+        """Every box keeps the part of its full-image mask that lies inside the (rounded) box (postprocessor.cc:24-59)."""
+        masks = np.asarray(masks).astype(np.uint8)
+        index = 0
+        for res in results:
+            res.contain_masks = True
+            res.masks = []
+            for box in res.boxes:
+                x1, y1, x2, y2 = (int(round(float(v))) for v in box)
+                h, w = max(y2 - y1, 0), max(x2 - x1, 0)
+                crop = masks[index, max(y1, 0):max(y1, 0) + h, max(x1, 0):max(x1, 0) + w]
+                full = np.zeros((h, w), np.uint8)
+                full[:crop.shape[0], :crop.shape[1]] = crop
+                res.masks.append(Mask(data=full.reshape(-1).tolist(), shape=[h, w]))
+                index += 1
+
+    def _solov2(self, tensors: Sequence[np.ndarray]) -> List[DetectionResult]:
+        """SOLOv2 exports (count, labels, scores, full-image masks) for one image; a box is the extent of its mask
+        (postprocessor.cc:180-262)."""
+        if len(tensors) != 4:
+            raise ValueError("SOLOv2 post-processing needs 4 output tensors")
+        count = int(np.asarray(tensors[0]).reshape(-1)[0])
+        labels, scores = np.asarray(tensors[1]).reshape(-1), np.asarray(tensors[2]).reshape(-1)
+        masks = np.asarray(tensors[3]).astype(np.uint8)
+        res = DetectionResult()
+        res.contain_masks = True
+        kept = []
+        for i in range(count):
+            if scores[i] < self.nms_option.score_threshold:
+                continue
+            rows = np.nonzero(masks[i].sum(1) > 0.5)[0]
+            cols = np.nonzero(masks[i].sum(0) > 0.5)[0]
+            y1, y2 = (float(rows[0]), float(rows[-1] + 1)) if len(rows) else (float(masks.shape[1]), 0.0)
+            x1, x2 = (float(cols[0]), float(cols[-1] + 1)) if len(cols) else (float(masks.shape[2]), 0.0)
+            res.label_ids.append(int(labels[i]))
+            res.scores.append(float(scores[i]))
+            res.boxes.append([x1, y1, x2, y2])
+            kept.append(i)
+        self._process_mask(masks[kept] if kept else masks[:0], [res])
+        return [res]
+
+    def _rotated(self, boxes, scores) -> List[DetectionResult]:
+        """PP-YOLOE-R: ``boxes [N, M, 8]`` quadrilaterals and ``scores [N, C, M]`` through the rotated multiclass NMS
+        (on the GPU when the tensors live there), then divided by the resize factors (postprocessor.cc:264-316; the
+        x coordinates are divided by the width factor and the y coordinates by the height factor)."""
+        from ...ops import perception as PR
+        opt = getattr(self, "nms_rotated_option", None) or self.nms_option
+        on_gpu = hasattr(boxes, "is_cuda") and boxes.is_cuda
+        n = boxes.shape[0]
+        results = []
+        for i in range(n):
+            if on_gpu:
+                key = (int(scores.shape[1]), int(boxes.shape[1]), str(boxes.device))
+                if getattr(self, "_rot_key", None) != key:
+                    self._rot_nms = PR.MulticlassNMSRotated(key[0], key[1], boxes.device, score_threshold=opt.score_threshold,
+                                                            nms_threshold=opt.nms_threshold, nms_top_k=opt.nms_top_k,
+                                                            keep_top_k=opt.keep_top_k, background_label=opt.background_label)
+                    self._rot_key = key
+                try:
+                    rows, _ = self._rot_nms.run(boxes[i], scores[i])
+                except OverflowError:
+                    rows, _ = PR.multiclass_nms_rotated_numpy(boxes[i].float().cpu().numpy(), scores[i].float().cpu().numpy(),
+                                                              opt.score_threshold, opt.nms_threshold, opt.nms_top_k,
+                                                              opt.keep_top_k, opt.background_label)
+            else:
+                rows, _ = PR.multiclass_nms_rotated_numpy(np.asarray(boxes[i], np.float32), np.asarray(scores[i], np.float32),
+                                                          opt.score_threshold, opt.nms_threshold, opt.nms_top_k,
+                                                          opt.keep_top_k, opt.background_label)
+            res = DetectionResult()
+            sf = getattr(self, "scale_factor", None)
+            for r in rows:
+                quad = [float(v) for v in r[2:10]]
+                if sf and sf[0] != 0:
+                    quad = [v / (sf[1] if j % 2 == 0 else sf[0]) for j, v in enumerate(quad)]
+                res.label_ids.append(int(round(float(r[0]))))
+                res.scores.append(float(r[1]))
+                res.rotated_boxes.append(quad)
+            results.append(res)
+        return results
 
     @staticmethod
     def _rows_to_results(rows: np.ndarray, counts: np.ndarray) -> List[DetectionResult]:
@@ -286,6 +387,11 @@ class PPDetBase(FastDeployModel):
         feeds = self._name_inputs(tensors)
         outs = self.infer(feeds)
         names = [vi.name for vi in self.runtime.graph.outputs]
+        self.postprocessor.set_scale_factor(np.asarray(tensors[1], np.float32).reshape(-1, 2)[0])
+        first = outs[names[0]]
+        if hasattr(first, "is_cuda") and first.is_cuda and first.dim() == 3 and first.shape[2] == 8:
+            # rotated boxes stay on the device for the rotated NMS
+            return self.postprocessor.run([outs[n] for n in names])
         arrs = [self.runtime._to_numpy(outs[n]) for n in names]
         return self.postprocessor.run(arrs)
 
@@ -411,6 +517,14 @@ FCOS = _subclass("FCOS", "FCOS (model.h:394-412).")
 TTFNet = _subclass("TTFNet", "TTFNet (model.h:414-432).")
 TOOD = _subclass("TOOD", "TOOD (model.h:434-452).")
 GFL = _subclass("GFL", "GFL (model.h:454-472).")
-SOLOv2 = _subclass("SOLOv2", "SOLOv2 (model.h:24-50 family).")
+
+
+class SOLOv2(PPDetBase):
+    """SOLOv2 instance segmentation (fastdeploy/vision/detection/ppdet/model.h:24-50 family): the graph's four outputs
+    (count, labels, scores, full-image masks) become boxes from the mask extents plus per-box mask crops."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.postprocessor.arch = "SOLOv2"
 PaddleDetectionModel = _subclass("PaddleDetectionModel", "Any PaddleDetection export (model.h:474-492).")
 PPYOLOER = _subclass("PPYOLOER", "PP-YOLOE-R rotated detector.")

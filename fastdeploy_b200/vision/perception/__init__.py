@@ -264,6 +264,16 @@ class Centerpoint(FastDeployModel):
         if len(outs) == 3 and outs[0].ndim == 2:   # already decoded: boxes, scores, labels
             return _fill(outs[0], outs[1].reshape(-1), outs[2].reshape(-1), self.with_velocity)
         hm, reg, height, dim, vel, rot = (o[0] for o in outs[:6])
+        if getattr(self.runtime, "on_gpu", False):
+            # decode, candidate sort and rotated bird's-eye-view NMS on the device
+            import torch
+            from ...ops.perception import centerpoint_decode_device
+            dev = self.runtime.device
+            t = [torch.from_numpy(np.ascontiguousarray(a)).to(dev) for a in (hm, reg, height, dim, vel, rot)]
+            b, s, l = centerpoint_decode_device(*t, self.voxel_size, self.point_cloud_range, self.down_ratio,
+                                                self.score_threshold, self.nms_iou_threshold,
+                                                with_velocity=self.with_velocity)
+            return _fill(b.cpu().numpy(), s.cpu().numpy(), l.cpu().numpy(), self.with_velocity)
         b, s, l = centerpoint_decode(hm, reg, height, dim, vel, rot, self.voxel_size, self.point_cloud_range,
                                      self.down_ratio, self.score_threshold, self.nms_iou_threshold,
                                      with_velocity=self.with_velocity)

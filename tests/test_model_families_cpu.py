@@ -101,3 +101,41 @@ def test_voxelize_and_bev_nms():
     assert abs(P.rotated_iou_bev((0, 0, 2, 2, 0), (0, 0, 2, 2, np.pi / 4)) - 0.70710678) < 1e-4
     boxes = np.array([[0, 0, 2, 4, 0], [0.2, 0, 2, 4, 0], [10, 10, 2, 4, 1.0]], np.float32)
     assert P.nms_bev(boxes, np.array([0.9, 0.8, 0.7]), 0.5) == [0, 2]
+
+
+def test_detection_postprocessor_rotated_masks_and_solov2():
+    from fastdeploy_b200.ops.perception import multiclass_nms_rotated_numpy
+    from fastdeploy_b200.vision.detection.ppdet import NMSOption, PaddleDetPostprocessor
+    rng = np.random.default_rng(0)
+    # PP-YOLOE-R: [N, M, 8] quadrilaterals + [N, C, M] scores -> rotated boxes divided by the resize factors
+    quads = np.array([[10, 10, 50, 10, 50, 30, 10, 30], [12, 11, 52, 11, 52, 31, 12, 31], [100, 100, 140, 120, 130, 140, 90, 120]],
+                     np.float32)
+    scores = np.array([[0.9, 0.8, 0.1], [0.05, 0.02, 0.7]], np.float32)
+    post = PaddleDetPostprocessor()
+    opt = NMSOption()
+    opt.score_threshold, opt.nms_threshold, opt.nms_top_k, opt.keep_top_k = 0.3, 0.3, 100, 10
+    post.set_nms_rotated_option(opt)
+    post.set_scale_factor([2.0, 4.0])
+    res = post.run([quads[None], scores[None]])[0]
+    assert res.label_ids == [0, 1] and [round(s, 2) for s in res.scores] == [0.9, 0.7]     # box 1 is suppressed by box 0
+    assert res.rotated_boxes[0] == [2.5, 5.0, 12.5, 5.0, 12.5, 15.0, 2.5, 15.0]
+    rows, idx = multiclass_nms_rotated_numpy(quads, scores, 0.3, 0.3, 100, 10)
+    assert idx.tolist() == [0, 2] and rows.shape == (2, 10)
+    # Mask R-CNN: the third output is one full-image mask per box, cropped to the rounded box
+    boxes = np.array([[1, 0.9, 2.2, 3.4, 6.1, 7.0], [0, 0.8, 0.0, 0.0, 4.0, 2.0]], np.float32)
+    masks = rng.integers(0, 2, (2, 10, 12)).astype(np.int32)
+    post = PaddleDetPostprocessor()
+    res = post.run([boxes, np.array([2], np.int32), masks])[0]
+    assert res.contain_masks and res.masks[0].shape == [4, 4] and res.masks[1].shape == [2, 4]
+    assert res.masks[0].data == masks[0, 3:7, 2:6].reshape(-1).tolist()
+    assert res.masks[1].data == masks[1, 0:2, 0:4].reshape(-1).tolist()
+    # SOLOv2: count, labels, scores, masks -> boxes are the mask extents
+    m = np.zeros((3, 8, 9), np.uint8)
+    m[0, 2:5, 1:7] = 1
+    m[1, 0:2, 3:4] = 1
+    m[2, 6:8, 6:9] = 1
+    post = PaddleDetPostprocessor("SOLOv2")
+    post.nms_option.score_threshold = 0.5
+    res = post.run([np.array([3], np.int32), np.array([4, 5, 6], np.int64), np.array([0.9, 0.2, 0.6], np.float32), m])[0]
+    assert res.label_ids == [4, 6] and res.boxes == [[1.0, 2.0, 7.0, 5.0], [6.0, 6.0, 9.0, 8.0]]
+    assert res.masks[0].shape == [3, 6] and sum(res.masks[0].data) == 18 and res.masks[1].shape == [2, 3]
