@@ -198,7 +198,11 @@ __global__ void __launch_bounds__(kNmsThreads) nms_class_kernel(const NmsDesc d)
   __shared__ int sel_remaining;
 
   const int tid = threadIdx.x;
-  const int K = min(d.nms_top_k < 0 ? kNmsMaxTopK : d.nms_top_k, kNmsMaxTopK);
+  // Candidates are taken in passes of at most 1024 (what the shared-memory arrays hold), best first: a pass selects
+  // the best remaining keys, sweeps them against everything kept so far and among themselves, and removes them from
+  // the key array. The passes stop when the class has produced max_keep boxes, when nms_top_k candidates have been
+  // considered, or when no candidate is left - so any nms_top_k is exact, and the common case is one pass.
+  int budget = d.nms_top_k < 0 ? d.M : d.nms_top_k;
   const long long base = static_cast<long long>(n) * d.s_n + static_cast<long long>(c) * d.s_c;
 
   NMS_PHASE_BEGIN;
@@ -214,6 +218,17 @@ __global__ void __launch_bounds__(kNmsThreads) nms_class_kernel(const NmsDesc d)
   block_excl_scan(local, warp_tmp, &total_pos);
 
   NMS_PHASE(0);
+  const bool normalized = d.normalized != 0;
+  const int max_keep = d.max_keep;
+  const float thr = d.nms_threshold;
+  __shared__ int s_nk[2];
+  float* o_score = d.cls_score + (static_cast<size_t>(n) * d.C + c) * max_keep;
+  int* o_index = d.cls_index + (static_cast<size_t>(n) * d.C + c) * max_keep;
+  const int lane = tid & 31, warp = tid >> 5;
+  const uint32_t lower = (1u << lane) - 1u;
+  int nkept = 0;
+  while (total_pos > 0 && budget > 0 && nkept < max_keep) {
+  const int K = min(budget, kNmsMaxTopK);
   // 2. radix select of the K-th largest key when there are more than K candidates
   uint32_t thr_key = 1u;   // admit keys >= thr_key ...
   int eq_budget = 1 << 30; // ... but only this many equal to thr_key (lowest indices first)
@@ -281,10 +296,10 @@ __global__ void __launch_bounds__(kNmsThreads) nms_class_kernel(const NmsDesc d)
       if (k == 0u) continue;
       const unsigned long long v = (static_cast<unsigned long long>(k) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(m));
       if (k > thr_key) {
-        if (pg < kNmsMaxTopK) cand[pg] = v;
+        if (pg < kNmsMaxTopK) { cand[pg] = v; keys[m] = 0u; }          // taken: out of the later passes
         ++pg;
       } else if (k == thr_key) {
-        if (pe < eq_taken && tot_gt + pe < kNmsMaxTopK) cand[tot_gt + pe] = v;
+        if (pe < eq_taken && tot_gt + pe < kNmsMaxTopK) { cand[tot_gt + pe] = v; keys[m] = 0u; }
         ++pe;
       }
     }
@@ -325,15 +340,6 @@ __global__ void __launch_bounds__(kNmsThreads) nms_class_kernel(const NmsDesc d)
   // candidates against just those new boxes. A candidate is therefore only ever compared with kept
   // boxes and with the members of its own group. Boxes past max_keep are dropped, which is exact
   // because a class contributes at most keep_top_k rows to the result.
-  const bool normalized = d.normalized != 0;
-  const int max_keep = d.max_keep;
-  const float thr = d.nms_threshold;
-  __shared__ int s_nk[2];
-  float* o_score = d.cls_score + (static_cast<size_t>(n) * d.C + c) * max_keep;
-  int* o_index = d.cls_index + (static_cast<size_t>(n) * d.C + c) * max_keep;
-  const int lane = tid & 31, warp = tid >> 5;
-  const uint32_t lower = (1u << lane) - 1u;
-  int nkept = 0;
   for (int b0 = 0; b0 < ncand && nkept < max_keep; b0 += kNmsThreads) {
     const int j = b0 + tid;
     bool alive = j < ncand;
@@ -384,6 +390,11 @@ __global__ void __launch_bounds__(kNmsThreads) nms_class_kernel(const NmsDesc d)
     __syncthreads();
     NMS_PHASE(6);
   }
+  total_pos -= ncand;
+  budget -= ncand;
+  if (ncand == 0) break;
+  __syncthreads();
+  }  // passes
   if (tid == 0) *count_out = nkept;
 }
 
@@ -699,8 +710,8 @@ FDB_API void* fdb_nms_create(const NmsDesc* dp) {
   if (d.C > 1024) { set_error("nms: at most 1024 classes"); return nullptr; }
   if (d.scores_t != nullptr && d.s_c != 1) { set_error("nms: the transposing path needs unit class stride"); return nullptr; }
   if (d.N > 65535) { set_error("nms: at most 65535 images per launch"); return nullptr; }
-  if (d.nms_top_k > kNmsMaxTopK || d.nms_top_k < 0) {
-    set_error("nms: nms_top_k must be in [0, 1024] for the device path"); return nullptr;
+  if (d.nms_top_k < -1 || d.nms_top_k == 0) {
+    set_error("nms: nms_top_k must be -1 (no limit) or positive"); return nullptr;
   }
   if (d.keep_top_k == 0) { set_error("nms: keep_top_k must be -1 or positive"); return nullptr; }
   if (d.max_keep < 1 || d.max_keep > kNmsMaxTopK) { set_error("nms: max_keep must be in [1, 1024]"); return nullptr; }

@@ -45,7 +45,7 @@ class MulticlassNMS:
     and ``out_num [N]``.
     """
 
-    MAX_TOP_K = 1024
+    MAX_KEEP = 1024          # boxes one class can contribute (min(keep_top_k, nms_top_k) must not exceed it)
 
     def __init__(self, boxes: torch.Tensor, scores: torch.Tensor, *, class_major: bool, score_threshold: float,
                  nms_threshold: float, nms_top_k: int = 1000, keep_top_k: int = 100, normalized: bool = True,
@@ -59,10 +59,11 @@ class MulticlassNMS:
             _, m2, c = scores.shape
             s_n, s_c, s_m = scores.stride(0), scores.stride(2), scores.stride(1)
         assert m2 == m
-        if nms_top_k < 0 or nms_top_k > self.MAX_TOP_K:
-            nms_top_k = self.MAX_TOP_K if nms_top_k < 0 and m <= self.MAX_TOP_K else nms_top_k
-        k = min(nms_top_k, m)
+        # any nms_top_k (the exporters' default is 10000): the class kernel takes candidates in passes of 1024
+        k = m if nms_top_k < 0 else min(nms_top_k, m)
         max_keep = min(keep_top_k, k) if keep_top_k > 0 else k
+        if max_keep > self.MAX_KEEP:
+            raise ValueError(f"multiclass NMS on the device keeps at most {self.MAX_KEEP} boxes per class; set keep_top_k")
         cap = keep_top_k if keep_top_k > 0 else c * max_keep
         dev = boxes.device
         self.cls_count = torch.zeros(n, c, dtype=torch.int32, device=dev)

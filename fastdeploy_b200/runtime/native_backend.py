@@ -912,7 +912,9 @@ class Lowering(GenericLowering):
 
     # ------------------------------------------------------------------ detection post-processing
     def lower_MultiClassNMS(self, node: Node):
-        if node.attr("nms_eta", 1.0) < 1.0 or not (0 <= node.attr("nms_top_k", 1000) <= MulticlassNMS.MAX_TOP_K):
+        top_k, keep = node.attr("nms_top_k", 1000), node.attr("keep_top_k", 100)
+        if node.attr("nms_eta", 1.0) < 1.0 or top_k == 0 or (min(keep, top_k) if keep > 0 and top_k > 0 else max(keep, top_k)) \
+                > MulticlassNMS.MAX_KEEP or (keep <= 0 and top_k < 0):
             return False
         boxes = self.as_torch(node.inputs[0])
         scores = self.as_torch(node.inputs[1])

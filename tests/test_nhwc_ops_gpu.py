@@ -187,6 +187,31 @@ def test_multiclass_nms_matches_reference(dense, class_major):
     assert np.allclose(got, ref_out, atol=1e-6)
 
 
+@pytest.mark.parametrize("top_k", [1025, 3000, 10000, -1])
+def test_multiclass_nms_top_k_beyond_one_pass(top_k):
+    """More candidates per class than one pass holds (1024): the exporters' default nms_top_k is 10000. Boxes are
+    packed so tightly that most candidates are suppressed and the later passes still add kept boxes."""
+    from fastdeploy_b200.ops.nms import MulticlassNMS, multiclass_nms_reference
+    rng = np.random.default_rng(11)
+    n, m, c = 2, 5000, 3
+    centre = rng.uniform(0, 60, (n, m, 2)).astype(np.float32)
+    size = rng.uniform(20, 40, (n, m, 2)).astype(np.float32)
+    boxes = np.concatenate([centre - size / 2, centre + size / 2], -1)
+    scores = rng.uniform(0.05, 1.0, (n, c, m)).astype(np.float32)
+    scores[:, :, ::9] = np.round(scores[:, :, ::9], 2)          # ties
+    kw = dict(score_threshold=0.1, nms_threshold=0.3, nms_top_k=top_k, keep_top_k=200)
+    ref_out, ref_idx, ref_num = multiclass_nms_reference(boxes, scores, normalized=True, **kw)
+    nms = MulticlassNMS(torch.from_numpy(boxes).cuda(), torch.from_numpy(scores).cuda(), class_major=True, **kw)
+    nms.launch()
+    torch.cuda.synchronize()
+    num = nms.out_num.cpu().numpy()
+    assert list(num) == list(ref_num) and num.min() > 5
+    gidx = np.concatenate([nms.out_index[i, :num[i]].cpu().numpy() + i * m for i in range(n)])
+    assert np.array_equal(gidx, ref_idx)
+    got = np.concatenate([nms.out[i, :num[i]].cpu().numpy() for i in range(n)])
+    assert np.allclose(got, ref_out, atol=1e-6)
+
+
 def test_multiclass_nms_keep_all_and_background():
     from fastdeploy_b200.ops.nms import MulticlassNMS, multiclass_nms_reference
     n, m, c = 1, 400, 4
