@@ -79,7 +79,7 @@ def build_kernels(verbose: bool = False, force: bool = False) -> str:
                 raise RuntimeError(f"nvcc failed on {futs[fut]}")
     if force or jobs or not os.path.exists(KERNEL_LIB):
         cmd = [nvcc, "-shared", "-o", KERNEL_LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a",
-                                                           "-cudart", "static"]
+                                                           "-cudart", "static", "-ldl"]
         rc, out = _compile(cmd, os.path.join(OBJ_DIR, "link_kernels.log"))
         if rc != 0:
             print(out)

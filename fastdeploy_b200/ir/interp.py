@@ -804,7 +804,10 @@ class Interpreter:
         self.consts = {}
         for k, v in graph.initializers.items():
             t = torch.from_numpy(np.ascontiguousarray(v))
-            if t.dtype in (torch.float16, torch.float64):
+            # half-precision weights are computed in fp32 (this is the reference path) unless the graph was
+            # converted to fp16 on purpose, in which case it carries its own casts
+            keep_half = str(graph.metadata.get("converted_fp16", "")) == "1"
+            if t.dtype == torch.float64 or (t.dtype == torch.float16 and not keep_half):
                 t = t.float()
             self.consts[k] = t.to(self.device)
 

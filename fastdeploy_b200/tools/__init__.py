@@ -137,6 +137,9 @@ def cmd_convert(args) -> int:
         from ..ir.passes import optimize
         shapes = ast.literal_eval(args.input_shape_dict) if args.input_shape_dict else None
         g = optimize(g, shapes, level=1) if shapes else g
+    if getattr(args, "to_fp16", False):
+        from ..ir.convert_fp16 import convert_fp32_to_fp16
+        g = convert_fp32_to_fp16(g, keep_io_types=not getattr(args, "fp16_io", False))
     from ..importer.onnx_format import save_onnx
     os.makedirs(args.save_dir, exist_ok=True)
     out = os.path.join(args.save_dir, "model.onnx")
@@ -192,6 +195,9 @@ def argsparser() -> argparse.ArgumentParser:
     p.add_argument("--model", default=None, help="model file or directory")
     p.add_argument("--input_shape_dict", default=None, help="e.g. \"{'image':[1,3,640,640]}\"")
     p.add_argument("--optimize", action="store_true", help="convert: run the IR optimiser before writing")
+    p.add_argument("--to_fp16", action="store_true", help="convert: store weights and compute in half precision "
+                                                           "(operators that need it stay fp32 between casts)")
+    p.add_argument("--fp16_io", action="store_true", help="convert --to_fp16: also make the graph inputs / outputs fp16")
     p.add_argument("--calib_batches", type=int, default=4)
     p.add_argument("--calib_npz", default=None, help="compress: .npz with one array per model input")
     p.add_argument("--app", default="server:app", help="simple_serving: module:attribute of the app")

@@ -148,3 +148,46 @@ def test_optimised_graph_disk_cache_round_trip(tmp_path):
     a, b = Interpreter(g1).run(feeds), Interpreter(g2).run(feeds)
     for k in a:
         assert np.array_equal(np.asarray(a[k]), np.asarray(b[k]))
+
+
+def test_fp32_to_fp16_converter_keeps_io_and_blocked_ops():
+    import numpy as np
+    import torch
+    from fastdeploy_b200.importer.onnx_format import load_onnx, save_onnx
+    from fastdeploy_b200.ir.convert_fp16 import convert_fp32_to_fp16
+    from fastdeploy_b200.ir.graph import Graph
+    from fastdeploy_b200.ir.interp import Interpreter
+    rng = np.random.RandomState(0)
+    g = Graph()
+    g.add_input("x", "float32", [2, 8, 12, 12])
+    w1 = g.const((rng.randn(16, 8, 3, 3) * 0.1).astype(np.float32), prefix="w1")
+    b1 = g.const(np.array([1e-9] * 8 + [0.1] * 8, np.float32), prefix="b1")         # tiny values must not flush to zero
+    g.add_node("Conv", ["x", w1, b1], ["c1"], kernel_shape=[3, 3], pads=[1, 1, 1, 1])
+    g.add_node("Relu", ["c1"], ["r1"])
+    scales = g.const(np.array([1, 1, 2, 2], np.float32), prefix="scales")
+    g.add_node("Resize", ["r1", "", scales], ["up"], mode="nearest")                    # stays fp32, its scales too
+    g.add_node("GlobalAveragePool", ["up"], ["gap"])
+    g.add_node("Flatten", ["gap"], ["flat"], axis=1)
+    w2 = g.const((rng.randn(16, 5) * 0.2).astype(np.float32), prefix="w2")
+    g.add_node("MatMul", ["flat", w2], ["logits"])
+    g.add_node("Softmax", ["logits"], ["prob"], axis=-1)                                 # stays fp32
+    g.add_node("ArgMax", ["prob"], ["label"], axis=1, keepdims=0)
+    g.add_output("prob", "float32", [2, 5])
+    g.add_output("label", "int64", [2])
+    h = convert_fp32_to_fp16(g)
+    assert h.initializers[w1].dtype == np.float16 and h.initializers[w2].dtype == np.float16
+    assert h.initializers[scales].dtype == np.float32
+    assert float(np.abs(h.initializers[b1][:8]).min()) > 0            # raised to the smallest kept magnitude
+    ops = [n.op for n in h.nodes]
+    assert ops.count("Cast") >= 4 and [vi.dtype for vi in h.inputs] == ["float32"]
+    x = rng.rand(2, 8, 12, 12).astype(np.float32)
+    ref = Interpreter(g).run({"x": x})
+    got = Interpreter(load_onnx(save_onnx(h))).run({"x": x})          # survives serialisation
+    assert got["prob"].dtype == torch.float32 and got["label"].dtype == torch.int64
+    assert torch.allclose(got["prob"], ref["prob"], atol=3e-3)
+    resize = [n for n in h.nodes if n.op == "Resize"][0]
+    prod = h.producers()
+    assert prod[resize.inputs[0]].op == "Cast" and prod[resize.inputs[0]].attr("to") == 1
+    # without kept i/o types the graph takes and returns half precision
+    h2 = convert_fp32_to_fp16(g, keep_io_types=False)
+    assert h2.inputs[0].dtype == "float16"

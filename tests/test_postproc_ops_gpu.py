@@ -69,3 +69,30 @@ def test_hard_voxelize_matches_host():
         assert np.array_equal(c.cpu().numpy(), c_ref)
         assert np.array_equal(n.cpu().numpy(), n_ref)
         assert np.array_equal(v.cpu().numpy(), v_ref)
+
+
+def test_nvjpeg_decodes_into_a_device_buffer():
+    import cv2
+    from fastdeploy_b200.vision.common.image_decoder import ImageDecoder, ImageDecoderLib, jpeg_info, nvjpeg_available
+    if not nvjpeg_available():
+        pytest.skip("libnvjpeg is not installed")
+    yy, xx = np.mgrid[0:120, 0:200]
+    im = np.stack([(xx * 1.2) % 256, (yy * 2.0) % 256, (xx + yy) % 256], -1).astype(np.uint8)
+    im = cv2.GaussianBlur(im, (0, 0), 1.5)
+    ok, enc = cv2.imencode(".jpg", im, [cv2.IMWRITE_JPEG_QUALITY, 95])
+    assert ok and jpeg_info(enc.tobytes()) == (120, 200, 3)
+    host = ImageDecoder(ImageDecoderLib.OPENCV).decode(enc.tobytes())
+    dec = ImageDecoder(ImageDecoderLib.NVJPEG)
+    dev = dec.decode(enc.tobytes())
+    assert dev.is_cuda and tuple(dev.shape) == (120, 200, 3)
+    diff = np.abs(dev.cpu().numpy().astype(np.int32) - host.astype(np.int32))
+    assert diff.mean() < 1.0 and diff.max() <= 12            # IDCT and up-sampling differ slightly between decoders
+    # into the middle of a larger staging buffer, RGB order
+    buf = torch.zeros(3 * 120 * 200 * 3, dtype=torch.uint8, device="cuda")
+    h, w = dec.decode_into(enc.tobytes(), buf[120 * 200 * 3:], bgr=False)
+    torch.cuda.synchronize()
+    got = buf[120 * 200 * 3:2 * 120 * 200 * 3].view(h, w, 3).cpu().numpy()
+    assert np.abs(got[:, :, ::-1].astype(np.int32) - host.astype(np.int32)).mean() < 1.0
+    assert int(buf[:120 * 200 * 3].sum()) == 0 and int(buf[2 * 120 * 200 * 3:].sum()) == 0
+    with pytest.raises(ValueError):
+        dec.decode(b"not a jpeg")
