@@ -6,6 +6,7 @@ keep_top_k 100), data-parallel over N GPUs:
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         bench.py --gpus N --steps K --warmup W
     python bench.py --config ernie | ocr | vit_tp  ...        (same flags, same JSON schema)
+    python bench.py --config ppyoloe_library                  (context: the same network on PyTorch / cuDNN fp16)
 
 ``value``   : device-timed (CUDA events, max over ranks) rate of the on-device step, inputs resident on the GPU.
 ``e2e``     : the same metric through the public API, each step copying its inputs from pinned host memory and
@@ -28,7 +29,7 @@ REF_UNAVAILABLE = ("refused by a safety check: building the reference (its pytho
                    "install of the reference tree fails before that (no setup.py at its root, python/ needs the "
                    "CMake build first)")
 
-CONFIGS = ("ppyoloe", "ernie", "ocr", "vit_tp")
+CONFIGS = ("ppyoloe", "ernie", "ocr", "vit_tp", "ppyoloe_library")
 
 
 def main() -> int:

@@ -378,6 +378,231 @@ FD_C_Bool FD_C_PaddleClasModelWrapperPredict(FD_C_PaddleClasModelWrapper* w, FD_
   return ok ? 1 : 0;
 }
 
+// ---------------------------------------------------------------- batch predict, segmentation, OCR, visualisation
+static bool detection_from_py(PyObject* r, FD_C_DetectionResult* out) {
+  PyObject *boxes = PyObject_GetAttrString(r, "boxes"), *scores = PyObject_GetAttrString(r, "scores"),
+           *labels = PyObject_GetAttrString(r, "label_ids");
+  bool ok = boxes && scores && labels && floats_from_seq(scores, &out->scores) && ints_from_seq(labels, &out->label_ids);
+  if (ok) {
+    const Py_ssize_t n = PySequence_Size(boxes);
+    out->boxes.size = static_cast<size_t>(n);
+    out->boxes.data = static_cast<FD_C_OneDimArrayFloat*>(std::calloc(n > 0 ? n : 1, sizeof(FD_C_OneDimArrayFloat)));
+    for (Py_ssize_t i = 0; i < n && ok; ++i) {
+      PyObject* b = PySequence_GetItem(boxes, i);
+      ok = floats_from_seq(b, &out->boxes.data[i]);
+      Py_DECREF(b);
+    }
+  } else if (PyErr_Occurred()) {
+    fetch_py_error("DetectionResult");
+  }
+  Py_XDECREF(boxes); Py_XDECREF(scores); Py_XDECREF(labels);
+  return ok;
+}
+
+FD_C_Bool FD_C_DetectionModelWrapperBatchPredict(FD_C_ModelWrapper* w, const FD_C_Mat* imgs, int n_imgs,
+                                                 FD_C_DetectionResult* results) {
+  Gil g;
+  PyObject* list = PyList_New(n_imgs);
+  for (int i = 0; i < n_imgs; ++i) {
+    PyObject* arr = mat_to_numpy(imgs[i]);
+    if (arr == nullptr) { Py_DECREF(list); return 0; }
+    PyList_SET_ITEM(list, i, arr);
+  }
+  PyObject* r = call_method(w->obj, "batch_predict", "(O)", list);
+  Py_DECREF(list);
+  if (r == nullptr) return 0;
+  bool ok = PySequence_Check(r) && PySequence_Size(r) == n_imgs;
+  for (int i = 0; i < n_imgs && ok; ++i) {
+    PyObject* item = PySequence_GetItem(r, i);
+    ok = item != nullptr && detection_from_py(item, &results[i]);
+    Py_XDECREF(item);
+  }
+  if (!ok && g_err.empty()) set_err("batch_predict: unexpected result");
+  Py_DECREF(r);
+  return ok ? 1 : 0;
+}
+
+FD_C_PaddleSegModelWrapper* FD_C_CreatePaddleSegModelWrapper(const char* m, const char* p, const char* c,
+                                                             FD_C_RuntimeOptionWrapper* o, FD_C_ModelFormat f) {
+  return create_model("vision.segmentation.PaddleSegModel", m, p, c, o, f);
+}
+FD_C_Bool FD_C_PaddleSegModelWrapperPredict(FD_C_PaddleSegModelWrapper* w, FD_C_Mat img, FD_C_SegmentationResult* out) {
+  Gil g;
+  PyObject* arr = mat_to_numpy(img);
+  if (arr == nullptr) return 0;
+  PyObject* r = call_method(w->obj, "predict", "(O)", arr);
+  Py_DECREF(arr);
+  if (r == nullptr) return 0;
+  PyObject *lm = PyObject_GetAttrString(r, "label_map"), *sm = PyObject_GetAttrString(r, "score_map"),
+           *shape = PyObject_GetAttrString(r, "shape"), *has = PyObject_GetAttrString(r, "contain_score_map");
+  bool ok = lm && sm && shape && ints_from_seq(lm, &out->label_map) && floats_from_seq(sm, &out->score_map) &&
+            PySequence_Check(shape) && PySequence_Size(shape) >= 2;
+  if (ok) {
+    PyObject *h = PySequence_GetItem(shape, 0), *wd = PySequence_GetItem(shape, 1);
+    out->height = static_cast<int>(PyLong_AsLong(h));
+    out->width = static_cast<int>(PyLong_AsLong(wd));
+    Py_XDECREF(h); Py_XDECREF(wd);
+    out->contain_score_map = has != nullptr && PyObject_IsTrue(has) ? 1 : 0;
+  } else if (PyErr_Occurred()) {
+    fetch_py_error("SegmentationResult");
+  }
+  Py_XDECREF(lm); Py_XDECREF(sm); Py_XDECREF(shape); Py_XDECREF(has); Py_DECREF(r);
+  return ok ? 1 : 0;
+}
+void FD_C_DestroySegmentationResult(FD_C_SegmentationResult* r) {
+  if (r == nullptr) return;
+  std::free(r->label_map.data); std::free(r->score_map.data);
+  r->label_map.data = nullptr; r->score_map.data = nullptr;
+}
+
+FD_C_PPOCRv3Wrapper* FD_C_CreatePPOCRv3Wrapper(const char* det_m, const char* det_p, const char* cls_m, const char* cls_p,
+                                               const char* rec_m, const char* rec_p, const char* rec_label,
+                                               FD_C_RuntimeOptionWrapper* option) {
+  Gil g;
+  if (g_pkg == nullptr) return nullptr;
+  auto make = [&](const char* dotted, PyObject* args) -> PyObject* {
+    PyObject* cls = get_class(dotted);
+    if (cls == nullptr) { Py_DECREF(args); return nullptr; }
+    PyObject* kwargs = PyDict_New();
+    if (option != nullptr) PyDict_SetItemString(kwargs, "runtime_option", option->obj);
+    PyObject* o = PyObject_Call(cls, args, kwargs);
+    Py_DECREF(args); Py_DECREF(kwargs); Py_DECREF(cls);
+    if (o == nullptr) fetch_py_error(dotted);
+    return o;
+  };
+  PyObject* det = make("vision.ocr.DBDetector", Py_BuildValue("(ss)", det_m, det_p ? det_p : ""));
+  if (det == nullptr) return nullptr;
+  PyObject* cls = nullptr;
+  if (cls_m != nullptr && cls_m[0] != 0) {
+    cls = make("vision.ocr.Classifier", Py_BuildValue("(ss)", cls_m, cls_p ? cls_p : ""));
+    if (cls == nullptr) { Py_DECREF(det); return nullptr; }
+  }
+  PyObject* rec = make("vision.ocr.Recognizer", Py_BuildValue("(sss)", rec_m, rec_p ? rec_p : "", rec_label ? rec_label : ""));
+  if (rec == nullptr) { Py_DECREF(det); Py_XDECREF(cls); return nullptr; }
+  PyObject* pipe_cls = get_class("vision.ocr.PPOCRv3");
+  PyObject* pipe = pipe_cls != nullptr ? PyObject_CallFunctionObjArgs(pipe_cls, det, cls != nullptr ? cls : Py_None, rec, nullptr)
+                                       : nullptr;
+  Py_XDECREF(pipe_cls); Py_DECREF(det); Py_XDECREF(cls); Py_DECREF(rec);
+  if (pipe == nullptr) { fetch_py_error("PPOCRv3"); return nullptr; }
+  return new FD_C_ModelWrapper{pipe};
+}
+FD_C_Bool FD_C_PPOCRv3WrapperPredict(FD_C_PPOCRv3Wrapper* w, FD_C_Mat img, FD_C_OCRResult* out) {
+  Gil g;
+  std::memset(out, 0, sizeof(*out));
+  PyObject* arr = mat_to_numpy(img);
+  if (arr == nullptr) return 0;
+  PyObject* r = call_method(w->obj, "predict", "(O)", arr);
+  Py_DECREF(arr);
+  if (r == nullptr) return 0;
+  PyObject *boxes = PyObject_GetAttrString(r, "boxes"), *text = PyObject_GetAttrString(r, "text"),
+           *rs = PyObject_GetAttrString(r, "rec_scores"), *cs = PyObject_GetAttrString(r, "cls_scores"),
+           *cl = PyObject_GetAttrString(r, "cls_labels");
+  bool ok = boxes && text && rs && cs && cl && floats_from_seq(rs, &out->rec_scores) && floats_from_seq(cs, &out->cls_scores) &&
+            ints_from_seq(cl, &out->cls_labels);
+  if (ok) {
+    const Py_ssize_t n = PySequence_Size(boxes);
+    out->boxes.size = static_cast<size_t>(n);
+    out->boxes.data = static_cast<FD_C_OneDimArrayFloat*>(std::calloc(n > 0 ? n : 1, sizeof(FD_C_OneDimArrayFloat)));
+    for (Py_ssize_t i = 0; i < n && ok; ++i) {
+      PyObject* b = PySequence_GetItem(boxes, i);
+      ok = floats_from_seq(b, &out->boxes.data[i]);
+      Py_DECREF(b);
+    }
+    const Py_ssize_t nt = PySequence_Size(text);
+    out->n_text = static_cast<size_t>(nt);
+    out->text = static_cast<char**>(std::calloc(nt > 0 ? nt : 1, sizeof(char*)));
+    for (Py_ssize_t i = 0; i < nt && ok; ++i) {
+      PyObject* t = PySequence_GetItem(text, i);
+      const char* c = t != nullptr ? PyUnicode_AsUTF8(t) : nullptr;
+      out->text[i] = strdup(c != nullptr ? c : "");
+      Py_XDECREF(t);
+    }
+  } else if (PyErr_Occurred()) {
+    fetch_py_error("OCRResult");
+  }
+  Py_XDECREF(boxes); Py_XDECREF(text); Py_XDECREF(rs); Py_XDECREF(cs); Py_XDECREF(cl); Py_DECREF(r);
+  return ok ? 1 : 0;
+}
+void FD_C_DestroyOCRResult(FD_C_OCRResult* r) {
+  if (r == nullptr) return;
+  for (size_t i = 0; i < r->boxes.size; ++i) std::free(r->boxes.data[i].data);
+  std::free(r->boxes.data);
+  for (size_t i = 0; i < r->n_text; ++i) std::free(r->text[i]);
+  std::free(r->text);
+  std::free(r->rec_scores.data); std::free(r->cls_scores.data); std::free(r->cls_labels.data);
+  std::memset(r, 0, sizeof(*r));
+}
+
+static bool copy_image_back(PyObject* arr, FD_C_Mat* out) {
+  PyObject* bytes = call_method(arr, "tobytes");
+  if (bytes == nullptr) return false;
+  char* buf = nullptr;
+  Py_ssize_t n = 0;
+  const bool ok = PyBytes_AsStringAndSize(bytes, &buf, &n) == 0 &&
+                  n == static_cast<Py_ssize_t>(out->height) * out->width * out->channels;
+  if (ok) std::memcpy(out->data, buf, static_cast<size_t>(n));
+  else set_err("visualisation: the result image does not fit the output buffer");
+  Py_DECREF(bytes);
+  return ok;
+}
+
+static PyObject* py_list_of_floats(const float* v, size_t n) {
+  PyObject* l = PyList_New(static_cast<Py_ssize_t>(n));
+  for (size_t i = 0; i < n; ++i) PyList_SET_ITEM(l, i, PyFloat_FromDouble(v[i]));
+  return l;
+}
+
+FD_C_Bool FD_C_VisDetection(FD_C_Mat img, const FD_C_DetectionResult* result, float score_threshold, int line_size,
+                            float font_size, FD_C_Mat* out) {
+  Gil g;
+  PyObject* res_cls = get_class("vision.DetectionResult");
+  PyObject* vis = get_class("vision.vis_detection");
+  if (res_cls == nullptr || vis == nullptr) { Py_XDECREF(res_cls); Py_XDECREF(vis); return 0; }
+  PyObject* res = PyObject_CallObject(res_cls, nullptr);
+  Py_DECREF(res_cls);
+  if (res == nullptr) { fetch_py_error("DetectionResult"); Py_DECREF(vis); return 0; }
+  PyObject* boxes = PyList_New(static_cast<Py_ssize_t>(result->boxes.size));
+  for (size_t i = 0; i < result->boxes.size; ++i)
+    PyList_SET_ITEM(boxes, i, py_list_of_floats(result->boxes.data[i].data, result->boxes.data[i].size));
+  PyObject* scores = py_list_of_floats(result->scores.data, result->scores.size);
+  PyObject* labels = PyList_New(static_cast<Py_ssize_t>(result->label_ids.size));
+  for (size_t i = 0; i < result->label_ids.size; ++i) PyList_SET_ITEM(labels, i, PyLong_FromLong(result->label_ids.data[i]));
+  PyObject_SetAttrString(res, "boxes", boxes);
+  PyObject_SetAttrString(res, "scores", scores);
+  PyObject_SetAttrString(res, "label_ids", labels);
+  Py_DECREF(boxes); Py_DECREF(scores); Py_DECREF(labels);
+  PyObject* arr = mat_to_numpy(img);
+  PyObject* drawn = arr != nullptr ? PyObject_CallFunction(vis, "OOfif", arr, res, score_threshold, line_size, font_size) : nullptr;
+  Py_XDECREF(arr); Py_DECREF(res); Py_DECREF(vis);
+  if (drawn == nullptr) { fetch_py_error("vis_detection"); return 0; }
+  const bool ok = copy_image_back(drawn, out);
+  Py_DECREF(drawn);
+  return ok ? 1 : 0;
+}
+
+FD_C_Bool FD_C_VisSegmentation(FD_C_Mat img, const FD_C_SegmentationResult* result, float weight, FD_C_Mat* out) {
+  Gil g;
+  PyObject* res_cls = get_class("vision.SegmentationResult");
+  PyObject* vis = get_class("vision.vis_segmentation");
+  if (res_cls == nullptr || vis == nullptr) { Py_XDECREF(res_cls); Py_XDECREF(vis); return 0; }
+  PyObject* res = PyObject_CallObject(res_cls, nullptr);
+  Py_DECREF(res_cls);
+  if (res == nullptr) { fetch_py_error("SegmentationResult"); Py_DECREF(vis); return 0; }
+  PyObject* lm = PyList_New(static_cast<Py_ssize_t>(result->label_map.size));
+  for (size_t i = 0; i < result->label_map.size; ++i) PyList_SET_ITEM(lm, i, PyLong_FromLong(result->label_map.data[i]));
+  PyObject* shape = Py_BuildValue("[ii]", result->height, result->width);
+  PyObject_SetAttrString(res, "label_map", lm);
+  PyObject_SetAttrString(res, "shape", shape);
+  Py_DECREF(lm); Py_DECREF(shape);
+  PyObject* arr = mat_to_numpy(img);
+  PyObject* drawn = arr != nullptr ? PyObject_CallFunction(vis, "OOf", arr, res, weight) : nullptr;
+  Py_XDECREF(arr); Py_DECREF(res); Py_DECREF(vis);
+  if (drawn == nullptr) { fetch_py_error("vis_segmentation"); return 0; }
+  const bool ok = copy_image_back(drawn, out);
+  Py_DECREF(drawn);
+  return ok ? 1 : 0;
+}
+
 void FD_C_DestroyClassifyResult(FD_C_ClassifyResult* r) {
   if (r == nullptr) return;
   std::free(r->label_ids.data); std::free(r->scores.data);

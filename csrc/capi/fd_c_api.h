@@ -108,6 +108,51 @@ FD_C_EXPORT FD_C_ModelWrapper* FD_C_CreateDetectionModelWrapper(const char* clas
 FD_C_EXPORT FD_C_Bool FD_C_DetectionModelWrapperPredict(FD_C_ModelWrapper* w, FD_C_Mat img, FD_C_DetectionResult* result);
 FD_C_EXPORT void FD_C_DestroyModelWrapper(FD_C_ModelWrapper* w);
 
+/* a batch of images through any detection model (c_api/fastdeploy_capi/vision/detection/ppdet/base_define.h:73-115):
+ * results[i] is filled for every image; release each with FD_C_DestroyDetectionResult */
+FD_C_EXPORT FD_C_Bool FD_C_DetectionModelWrapperBatchPredict(FD_C_ModelWrapper* w, const FD_C_Mat* imgs, int n_imgs,
+                                                             FD_C_DetectionResult* results);
+
+/* ---- segmentation (c_api/fastdeploy_capi/vision/segmentation/ppseg/model.h) */
+typedef struct FD_C_SegmentationResult {
+  FD_C_OneDimArrayInt32 label_map;    /* height * width class ids */
+  FD_C_OneDimArrayFloat score_map;    /* empty unless the model returns scores */
+  int height, width;
+  FD_C_Bool contain_score_map;
+} FD_C_SegmentationResult;
+typedef FD_C_ModelWrapper FD_C_PaddleSegModelWrapper;
+FD_C_EXPORT FD_C_PaddleSegModelWrapper* FD_C_CreatePaddleSegModelWrapper(const char* model_file, const char* params_file,
+                                                                         const char* config_file,
+                                                                         FD_C_RuntimeOptionWrapper* option,
+                                                                         FD_C_ModelFormat format);
+FD_C_EXPORT FD_C_Bool FD_C_PaddleSegModelWrapperPredict(FD_C_PaddleSegModelWrapper* w, FD_C_Mat img,
+                                                        FD_C_SegmentationResult* result);
+FD_C_EXPORT void FD_C_DestroySegmentationResult(FD_C_SegmentationResult* r);
+
+/* ---- OCR (c_api/fastdeploy_capi/vision/ocr/ppocr/model.h): detector + optional classifier + recogniser */
+typedef struct FD_C_OCRResult {
+  FD_C_TwoDimArrayFloat boxes;        /* n x 8 corner coordinates */
+  size_t n_text;
+  char** text;                        /* n_text UTF-8 strings */
+  FD_C_OneDimArrayFloat rec_scores;
+  FD_C_OneDimArrayFloat cls_scores;
+  FD_C_OneDimArrayInt32 cls_labels;
+} FD_C_OCRResult;
+typedef FD_C_ModelWrapper FD_C_PPOCRv3Wrapper;
+/* cls_model_file may be NULL or "" for a pipeline without the angle classifier */
+FD_C_EXPORT FD_C_PPOCRv3Wrapper* FD_C_CreatePPOCRv3Wrapper(const char* det_model_file, const char* det_params_file,
+                                                           const char* cls_model_file, const char* cls_params_file,
+                                                           const char* rec_model_file, const char* rec_params_file,
+                                                           const char* rec_label_file, FD_C_RuntimeOptionWrapper* option);
+FD_C_EXPORT FD_C_Bool FD_C_PPOCRv3WrapperPredict(FD_C_PPOCRv3Wrapper* w, FD_C_Mat img, FD_C_OCRResult* result);
+FD_C_EXPORT void FD_C_DestroyOCRResult(FD_C_OCRResult* r);
+
+/* ---- visualisation (c_api/fastdeploy_capi/vision/visualize.h): draws into `out`, an image of the input's size that
+ * the caller owns (out->data must hold height * width * channels bytes) */
+FD_C_EXPORT FD_C_Bool FD_C_VisDetection(FD_C_Mat img, const FD_C_DetectionResult* result, float score_threshold,
+                                        int line_size, float font_size, FD_C_Mat* out);
+FD_C_EXPORT FD_C_Bool FD_C_VisSegmentation(FD_C_Mat img, const FD_C_SegmentationResult* result, float weight, FD_C_Mat* out);
+
 /* ---- results */
 FD_C_EXPORT void FD_C_DestroyClassifyResult(FD_C_ClassifyResult* r);
 FD_C_EXPORT void FD_C_DestroyDetectionResult(FD_C_DetectionResult* r);

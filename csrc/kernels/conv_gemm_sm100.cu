@@ -1707,22 +1707,31 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
     if (d->pair_mode == 1 && !pair_can) {
       set_error("conv_gemm: CTA pairs need block_n >= 64, no peer mode and 2+ tiles"); delete op; return nullptr;
     }
-    const bool use_pair = pair_can && (d->pair_mode == 1 || (bn >= 96 && items_pair >= sms / 2));
-    const int b_bytes = 3 * (use_pair ? bn / 2 : bn) * kBK * 2;   // one filter row (3 taps) per weight stage
+    bool use_pair = pair_can && (d->pair_mode == 1 || (bn >= 96 && items_pair >= sms / 2));
     const int all_b = 3 * p.kb_per_tap;
     HaloParams hp{};
-    // Activation patches come from DRAM, weights from L2: bytes in flight matter for the patches,
-    // so they get the deeper ring.
-    if (p.n_tiles == 1 && all_b <= kHaloMaxB && 3 * kHaloABytes + all_b * b_bytes <= budget) {
-      hp.b_resident = 1;
-      hp.b_stages = all_b;
-      hp.a_stages = std::min(kHaloMaxA, (budget - all_b * b_bytes) / kHaloABytes);
-    } else {
-      hp.b_resident = 0;
-      // three patch stages first, the rest of the budget to the weight ring (at least two stages)
-      hp.b_stages = std::max(2, std::min(kHaloMaxB, (budget - 3 * kHaloABytes) / b_bytes));
-      hp.a_stages = std::min(kHaloMaxA, (budget - hp.b_stages * b_bytes) / kHaloABytes);
-      if (hp.a_stages < 2) { hp.a_stages = 2; hp.b_stages = (budget - 2 * kHaloABytes) / b_bytes; }
+    auto plan_rings = [&](bool pair_now) {
+      const int b_bytes = 3 * (pair_now ? bn / 2 : bn) * kBK * 2;   // one filter row (3 taps) per weight stage
+      hp = HaloParams{};
+      // Activation patches come from DRAM, weights from L2: bytes in flight matter for the patches,
+      // so they get the deeper ring.
+      if (p.n_tiles == 1 && all_b <= kHaloMaxB && 3 * kHaloABytes + all_b * b_bytes <= budget) {
+        hp.b_resident = 1;
+        hp.b_stages = all_b;
+        hp.a_stages = std::min(kHaloMaxA, (budget - all_b * b_bytes) / kHaloABytes);
+      } else {
+        hp.b_resident = 0;
+        // three patch stages first, the rest of the budget to the weight ring (at least two stages)
+        hp.b_stages = std::max(2, std::min(kHaloMaxB, (budget - 3 * kHaloABytes) / b_bytes));
+        hp.a_stages = std::min(kHaloMaxA, (budget - hp.b_stages * b_bytes) / kHaloABytes);
+        if (hp.a_stages < 2) { hp.a_stages = 2; hp.b_stages = (budget - 2 * kHaloABytes) / b_bytes; }
+      }
+    };
+    plan_rings(use_pair);
+    if (hp.b_stages < 2 && !use_pair && pair_can) {
+      // a wide filter row that one CTA cannot double-buffer fits when a CTA pair splits it
+      use_pair = true;
+      plan_rings(true);
     }
     if (use_pair && hp.b_stages >= 2) {
       op->pair = p.pair = 1;
@@ -1744,6 +1753,7 @@ FDB_API void* fdb_conv_gemm_create(const ConvGemmDesc* d) {
       op->grid = std::max(1, static_cast<int>(std::min<long>(p.total_tiles, d->max_ctas > 0 ? d->max_ctas : sms)));
     } else {
       op->hp = hp;
+      const int b_bytes = 3 * (use_pair ? bn / 2 : bn) * kBK * 2;
       op->halo_smem = hp.a_stages * kHaloABytes + hp.b_stages * b_bytes + kStagingBytes + kHaloBarBytes + 1024;
     }
   }

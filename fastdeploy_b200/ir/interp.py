@@ -820,7 +820,10 @@ class Interpreter:
                 raise KeyError(f"missing input {vi.name!r}")
             t = feeds[vi.name]
             t = torch.from_numpy(np.ascontiguousarray(t)) if isinstance(t, np.ndarray) else t
-            if t.dtype in (torch.float16, torch.bfloat16, torch.float64):
+            # the reference path computes in fp32; a graph converted to fp16 takes the dtype it declares
+            if str(self.graph.metadata.get("converted_fp16", "")) == "1":
+                t = t.to(NP2TORCH.get(vi.dtype, t.dtype)) if t.is_floating_point() else t
+            elif t.dtype in (torch.float16, torch.bfloat16, torch.float64):
                 t = t.float()
             env[vi.name] = t.to(self.device)
         opset = self.graph.opset

@@ -149,12 +149,12 @@ def test_linear_activations(act, dtype):
 
 
 @pytest.mark.parametrize("cfg", [
-    # n, h, w, cin, cout, act, expected variant (1 streamed weights, 2 resident weights)
+    # n, h, w, cin, cout, act, expected variant (1 streamed weights, 2 resident weights, 4 streamed on a CTA pair)
     (2, 16, 16, 64, 64, "silu", 2),
     (2, 32, 24, 48, 48, "silu", 2),
     (1, 33, 21, 32, 40, None, 2),          # ragged edges in both directions
     (2, 16, 16, 96, 96, "relu", 1),        # two channel slabs -> streamed weights
-    (2, 24, 16, 192, 192, "silu", 1),
+    (2, 24, 16, 192, 192, "silu", 4),      # a 192-wide filter row only double-buffers when a CTA pair splits it
     (1, 16, 16, 128, 320, None, 1),        # two column tiles
     (3, 40, 40, 8, 32, "silu", 2),         # stem-like: 8 physical input channels
 ])
