@@ -730,8 +730,13 @@ FDB_API void* fdb_nms_create(const NmsDesc* dp) {
   while (sort_n < d.C * d.max_keep && sort_n < kMergeMax) sort_n <<= 1;
   op->smem2 = d.keep_top_k > -1 ? static_cast<size_t>(sort_n) * 8 : 16;
   if (op->smem1 > 200 * 1024) { set_error("nms: too many boxes per image for shared memory"); delete op; return nullptr; }
-  // The opt-in limit is per function: only ever raise it, other ops may need more.
-  static size_t max1 = 0, max2 = 0;
+  // The opt-in limit is per function AND per device (one process may drive several GPUs): only ever raise it, other
+  // ops on the same device may need more.
+  static size_t max_dev[64][2] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { set_error("nms: no current device"); delete op; return nullptr; }
+  size_t& max1 = max_dev[dev][0];
+  size_t& max2 = max_dev[dev][1];
   cudaError_t e = cudaSuccess;
   if (op->smem1 > max1) {
     e = cudaFuncSetAttribute(nms_class_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)op->smem1);
