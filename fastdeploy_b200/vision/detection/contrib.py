@@ -92,6 +92,66 @@ class YOLOPreprocessor:
         return np.stack(outs), infos
 
 
+def letterbox_geometry(h: int, w: int, size: Sequence[int], *, scale_up: bool = True, center: bool = True) -> Dict[str, Any]:
+    """Placement of an ``h x w`` image on a ``size = [w, h]`` canvas (the fixed-size form of :func:`letterbox`)."""
+    scale = min(size[1] / h, size[0] / w)
+    if not scale_up:
+        scale = min(scale, 1.0)
+    rw, rh = int(round(w * scale)), int(round(h * scale))
+    pad_w, pad_h = size[0] - rw, size[1] - rh
+    if center:
+        top, left = int(round(pad_h / 2.0 - 0.1)), int(round(pad_w / 2.0 - 0.1))
+    else:
+        top, left = 0, 0
+    return {"scale": scale, "pad_w": left, "pad_h": top, "in_hw": (h, w), "out_hw": (size[1], size[0]), "rw": rw, "rh": rh}
+
+
+class DeviceLetterbox:
+    """Letterbox + BGR->RGB + 1/255 on the GPU in one launch per batch (csrc/kernels/preproc.cu): raw frames are copied
+    to the device as they are, the kernel resizes each into its place on the padded canvas and writes the network's
+    16-bit NHWC input directly. The reference's version is fastdeploy/vision/utils/yolo_preprocess.cu:37-113."""
+
+    def __init__(self, pre: "YOLOPreprocessor", device):
+        self.pre, self.device = pre, device
+        self._state: Dict[Tuple, Dict[str, Any]] = {}
+
+    def supported(self) -> bool:
+        return not (self.pre.is_mini_pad or self.pre.is_no_pad)
+
+    def run(self, images: Sequence[np.ndarray], dst) -> List[Dict[str, Any]]:
+        """``dst``: the plan's input as a dense ``[n, H, W, c_phys]`` 16-bit tensor. Returns the letterbox infos."""
+        import torch
+        from ...ops import preproc as P
+        n = len(images)
+        size = self.pre.size
+        infos = [letterbox_geometry(int(im.shape[0]), int(im.shape[1]), size, scale_up=self.pre.is_scale_up,
+                                    center=self.pre.center) for im in images]
+        sizes = [int(im.shape[0]) * int(im.shape[1]) * 3 for im in images]
+        offs = np.concatenate([[0], np.cumsum([(s + 255) // 256 * 256 for s in sizes])]).astype(np.int64)
+        key = (n, int(offs[-1]), dst.data_ptr(), tuple(dst.shape))
+        st = self._state.get(key)
+        if st is None:
+            a = 1.0 / 255.0 if self.pre.normalize else 1.0
+            raw = torch.empty(int(offs[-1]), dtype=torch.uint8, device=self.device)
+            meta_host = torch.empty(n * P.IMAGE_META.itemsize, dtype=torch.uint8).pin_memory()
+            meta_dev = torch.empty(n * P.IMAGE_META.itemsize, dtype=torch.uint8, device=self.device)
+            op = P.Preprocess(raw, meta_dev, dst, n=n, out_hw=(size[1], size[0]), layout="nhwc", c_out=dst.shape[3],
+                              interp="linear", swap_rb=self.pre.swap_rb, alpha=[a] * 3, beta=[0.0] * 3,
+                              pad_value=[float(v) * a for v in self.pre.padding_value])
+            st = self._state[key] = dict(raw=raw, meta_host=meta_host, meta_dev=meta_dev, op=op)
+            if len(self._state) > 8:
+                self._state.pop(next(iter(self._state)))
+        meta = np.frombuffer(st["meta_host"].numpy(), dtype=P.IMAGE_META)
+        for i, (im, g) in enumerate(zip(images, infos)):
+            t = im if isinstance(im, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(im))
+            st["raw"][int(offs[i]):int(offs[i]) + sizes[i]].copy_(t.reshape(-1), non_blocking=True)
+            P.fill_meta(meta, i, src_offset=int(offs[i]), src_hw=(int(im.shape[0]), int(im.shape[1])),
+                        src_stride=int(im.shape[1]) * 3, resized_hw=(g["rh"], g["rw"]), top_left=(g["pad_h"], g["pad_w"]))
+        st["meta_dev"].copy_(st["meta_host"], non_blocking=True)
+        st["op"].launch()
+        return infos
+
+
 def _xywh_to_xyxy(b: np.ndarray) -> np.ndarray:
     out = np.empty_like(b)
     out[:, 0], out[:, 1] = b[:, 0] - b[:, 2] / 2, b[:, 1] - b[:, 3] / 2
@@ -222,8 +282,27 @@ class _YOLOModel(FastDeployModel):
         return self.batch_predict([im])[0]
 
     def batch_predict(self, images: Sequence[np.ndarray]) -> List[DetectionResult]:
-        x, infos = self.preprocessor.run(images)
         name = self.runtime.get_input_info(0).name
+        if getattr(self.runtime, "on_gpu", False) and all(im.ndim == 3 and im.shape[2] == 3 and im.dtype == np.uint8
+                                                           for im in images):
+            # letterbox, channel swap and scaling on the device, straight into the plan's input buffer
+            import torch
+            rt = self.runtime
+            if getattr(self, "_device_pre", None) is None:
+                self._device_pre = DeviceLetterbox(self.preprocessor, rt.device)
+            if self._device_pre.supported():
+                w, h = self.preprocessor.size
+                with torch.cuda.device(rt.device):
+                    plan = rt.plan_for_shapes({name: [len(images), 3, h, w]})
+                    base = plan.inputs[name].t
+                    dst = torch.as_strided(base, (base.shape[0], base.shape[1], base.shape[2], base.stride(2)), base.stride())
+                    infos = self._device_pre.run(images, dst)
+                    plan.run()
+                    rt.gpu_launches += plan.native_kernel_launches + 1
+                    outs = [rt._to_numpy(plan.outputs[vi.name].logical()) for vi in rt.graph.outputs]
+                    plan.status.check("YOLO inference")
+                return self.postprocessor.run(outs, infos)
+        x, infos = self.preprocessor.run(images)
         outs = self.runtime.infer({name: x})
         return self.postprocessor.run(outs, infos)
 

@@ -291,16 +291,22 @@ class PaddleDetPostprocessor:
 
     @staticmethod
     def _rows_to_results(rows: np.ndarray, counts: np.ndarray) -> List[DetectionResult]:
+        # one conversion per column for the whole batch, then list slices per image: a batch of 32 images costs three
+        # array-to-list calls instead of ninety-six
+        rows = np.asarray(rows)
+        labels = rows[:, 0].astype(np.int32).tolist() if len(rows) else []
+        scores = rows[:, 1].astype(np.float32).tolist() if len(rows) else []
+        boxes = rows[:, 2:6].astype(np.float32).tolist() if len(rows) else []
         results = []
         pos = 0
         for c in counts:
-            r = rows[pos:pos + int(c)]
-            pos += int(c)
+            c = int(c)
             res = DetectionResult()
-            if len(r):
-                res.label_ids = r[:, 0].astype(np.int32).tolist()
-                res.scores = r[:, 1].astype(np.float32).tolist()
-                res.boxes = r[:, 2:6].astype(np.float32).tolist()
+            if c:
+                res.label_ids = labels[pos:pos + c]
+                res.scores = scores[pos:pos + c]
+                res.boxes = boxes[pos:pos + c]
+            pos += c
             results.append(res)
         return results
 
@@ -332,6 +338,7 @@ class _GpuSlot:
         self.copied = torch.cuda.Event()
         self.done = torch.cuda.Event()
         self.pre = None
+        self.layout_sig = None      # (frame size, count, packed) whose placement records the device copy holds
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
@@ -365,6 +372,7 @@ class PPDetBase(FastDeployModel):
             self.postprocessor.apply_nms()
         self._slots: Dict[Tuple, List[_GpuSlot]] = {}
         self._slot_rr = 0
+        self._geo_cache: Dict[Tuple[int, int], Dict[str, Any]] = {}
         self.slots_in_flight = 3        # batches whose copies / compute / read-back may overlap
         self._copy_stream = None
         self.h2d_bytes_last = 0
@@ -410,7 +418,16 @@ class PPDetBase(FastDeployModel):
         if not isinstance(images, (list, tuple)) and getattr(images, "ndim", 0) == 4:
             images = [images[i] for i in range(images.shape[0])]      # one [N,H,W,3] batch buffer
         n = len(images)
-        geo = [self.preprocessor.plan_image(int(im.shape[0]), int(im.shape[1])) for im in images]
+        # frames of one size (the common case: a camera, a video) share their geometry; it is planned once
+        hw0 = (int(images[0].shape[0]), int(images[0].shape[1])) if n else (0, 0)
+        uniform = all(int(im.shape[0]) == hw0[0] and int(im.shape[1]) == hw0[1] for im in images)
+        if uniform and n:
+            g0 = self._geo_cache.get(hw0)
+            if g0 is None:
+                g0 = self._geo_cache[hw0] = self.preprocessor.plan_image(*hw0)
+            geo = [g0] * n
+        else:
+            geo = [self.preprocessor.plan_image(int(im.shape[0]), int(im.shape[1])) for im in images]
         ch, cw = max(g["ch"] for g in geo), max(g["cw"] for g in geo)
         shapes = {}
         for vi in rt.graph.inputs:
@@ -439,11 +456,14 @@ class PPDetBase(FastDeployModel):
                 # Frames that sit back to back in one host (or device) buffer - a batch staged in one pinned
                 # allocation - travel as ONE copy: a copy per frame costs a launch each and keeps the link
                 # from streaming.
-                packed = n > 0 and all(t.is_contiguous() and t.dtype == torch.uint8 for t in tens) and all(
-                    tens[i + 1].data_ptr() == tens[i].data_ptr() + tens[i].numel() and
-                    tens[i + 1].device == tens[0].device for i in range(n - 1))
+                t0 = tens[0] if n else None
+                step = t0.numel() if n else 0
+                base_ptr = t0.data_ptr() if n else 0
+                packed = n > 0 and uniform and all(
+                    t.dtype == torch.uint8 and t.device == t0.device and t.data_ptr() == base_ptr + i * step and
+                    t.is_contiguous() for i, t in enumerate(tens))
                 if packed:
-                    total = sum(t.numel() for t in tens)
+                    total = step * n
                     try:
                         whole = torch.as_strided(tens[0].reshape(-1), (total,), (1,)) if n > 1 else tens[0].reshape(-1)
                     except RuntimeError:      # the frames are separate storages that merely happen to be adjacent
@@ -452,18 +472,23 @@ class PPDetBase(FastDeployModel):
                     slot.raw[:total].copy_(whole, non_blocking=True)
                     if whole.device.type == "cpu":
                         h2d += total
-                for i, (t, g) in enumerate(zip(tens, geo)):
-                    flat = t.reshape(-1)
-                    if not packed:
-                        slot.raw[off:off + flat.numel()].copy_(flat, non_blocking=True)
-                        if flat.device.type == "cpu":
-                            h2d += flat.numel()
-                    P.fill_meta(meta, i, src_offset=off, src_hw=(int(t.shape[0]), int(t.shape[1])),
-                                src_stride=int(t.shape[1]) * 3, resized_hw=(g["rh"], g["rw"]))
-                    slot.sf_host[i, 0], slot.sf_host[i, 1] = g["scale_factor"]
-                    off += flat.numel() if packed else (flat.numel() + 255) // 256 * 256
-                slot.meta_dev.copy_(slot.meta_host, non_blocking=True)
-                h2d += slot.meta_host.numel()
+                # per-frame placement records: identical for every batch of packed same-size frames, so a slot that
+                # has seen this layout before keeps what it already holds on the device
+                sig = (hw0, n, packed) if (packed and uniform) else None
+                if sig is None or slot.layout_sig != sig:
+                    for i, (t, g) in enumerate(zip(tens, geo)):
+                        flat = t.reshape(-1)
+                        if not packed:
+                            slot.raw[off:off + flat.numel()].copy_(flat, non_blocking=True)
+                            if flat.device.type == "cpu":
+                                h2d += flat.numel()
+                        P.fill_meta(meta, i, src_offset=off, src_hw=(int(t.shape[0]), int(t.shape[1])),
+                                    src_stride=int(t.shape[1]) * 3, resized_hw=(g["rh"], g["rw"]))
+                        slot.sf_host[i, 0], slot.sf_host[i, 1] = g["scale_factor"]
+                        off += flat.numel() if packed else (flat.numel() + 255) // 256 * 256
+                    slot.meta_dev.copy_(slot.meta_host, non_blocking=True)
+                    h2d += slot.meta_host.numel()
+                    slot.layout_sig = sig
                 slot.copied.record(self._copy_stream)
             # ---- compute stream: pre-process, network, NMS, read-back
             compute.wait_event(slot.copied)

@@ -255,3 +255,24 @@ def test_depthwise_conv_matches_fp32_reference(dtype, k, stride, act):
     ref = ref.permute(0, 2, 3, 1)
     tol = 3e-2 if dtype == torch.bfloat16 else 5e-3
     assert (y.float() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("scale_up,center", [(True, True), (False, True), (True, False)])
+def test_device_letterbox_matches_host_letterbox(scale_up, center):
+    from fastdeploy_b200.vision.detection.contrib import DeviceLetterbox, YOLOPreprocessor
+    rng = np.random.default_rng(4)
+    import cv2
+    images = [cv2.GaussianBlur(rng.integers(0, 256, (h, w, 3), dtype=np.uint8), (0, 0), 2.0)
+              for h, w in ((480, 640), (200, 300), (720, 405))]
+    pre = YOLOPreprocessor((320, 320))
+    pre.is_scale_up, pre.center = scale_up, center
+    ref, ref_infos = pre.run(images)                              # [3, 3, 320, 320] fp32, RGB, / 255, padded with 114
+    dst = torch.zeros(3, 320, 320, 8, dtype=torch.float16, device="cuda")
+    infos = DeviceLetterbox(pre, torch.device("cuda:0")).run(images, dst)
+    torch.cuda.synchronize()
+    got = dst[..., :3].permute(0, 3, 1, 2).float().cpu().numpy()
+    for a, b in zip(infos, ref_infos):
+        assert a["pad_w"] == b["pad_w"] and a["pad_h"] == b["pad_h"] and abs(a["scale"] - b["scale"]) < 1e-9
+    diff = np.abs(got - ref)
+    assert diff.max() <= 2.5 / 255 and diff.mean() < 0.6 / 255          # one rounding step of the resize + fp16
+    assert float(dst[..., 3:].abs().max()) == 0.0
