@@ -39,6 +39,9 @@ from ..ops.nms import MulticlassNMS
 from .lower_generic import GenericLowering
 
 
+_NVTX = __import__("os").environ.get("FDX_NVTX", "0") not in ("", "0")
+
+
 def _round8(c: int) -> int:
     return (c + 7) // 8 * 8
 
@@ -133,12 +136,51 @@ class Plan:
     def _run_eager(self) -> None:
         lib = _native.kernels()
         stream = ctypes.c_void_p(current_stream_ptr(self.device))
+        if _NVTX:
+            for s in self.steps:                   # one range per step instead of one native call per segment
+                torch.cuda.nvtx.range_push(s.name)
+                s.fn()
+                torch.cuda.nvtx.range_pop()
+            return
         for kind, obj, _ in self._segments:
             if kind == "native":
                 if lib.fdb_plan_run(obj, stream) != 0:
                     raise RuntimeError(f"native plan failed: {_native.last_error()}")
             else:
                 obj()
+
+    def trace(self, path: str = "", iters: int = 3) -> Dict[str, Any]:
+        """Runs the plan step by step with a CUDA event pair around every step and returns (and optionally writes) a
+        Chrome-trace document (``chrome://tracing`` / Perfetto): one complete event per step with its device time, on
+        a time axis of cumulative device time. With ``FDX_NVTX=1`` in the environment every step of an eager run is
+        also an NVTX range, so an external timeline tool shows the same names."""
+        import json
+        names = [s.name for s in self.steps]
+        best = [float("inf")] * len(self.steps)
+        for _ in range(max(1, iters)):
+            evs = []
+            for s in self.steps:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                s.fn()
+                e1.record()
+                evs.append((e0, e1))
+            torch.cuda.synchronize(self.device)
+            for k, (e0, e1) in enumerate(evs):
+                best[k] = min(best[k], e0.elapsed_time(e1) * 1e3)      # microseconds
+        events, ts = [], 0.0
+        for k, (name, dur) in enumerate(zip(names, best)):
+            node = self.steps[k].node
+            events.append({"name": name, "cat": "native" if self.steps[k].native is not None else "framework", "ph": "X",
+                           "ts": round(ts, 3), "dur": round(dur, 3), "pid": 0, "tid": int(self.device.index or 0),
+                           "args": {"step": k, "op": node.op if node is not None else ""}})
+            ts += dur
+        doc = {"traceEvents": events, "displayTimeUnit": "ms",
+               "otherData": {"steps": len(events), "sum_us": round(ts, 1), "launches": self.native_kernel_launches}}
+        if path:
+            with open(path, "w") as f:
+                json.dump(doc, f)
+        return doc
 
     def capture(self, warmup: int = 2) -> None:
         """Captures the whole plan into one CUDA graph (replay = one launch)."""

@@ -200,9 +200,18 @@ class Runtime:
     def _infer_dict(self, data: Dict[str, Any]) -> Dict[str, Any]:
         with self._lock:
             if not self.on_gpu:
-                res = self._interp.run({k: (np.ascontiguousarray(v) if isinstance(v, np.ndarray) else v)
-                                        for k, v in data.items()})
-                return res
+                feeds = {k: (np.ascontiguousarray(v) if isinstance(v, np.ndarray) else v) for k, v in data.items()}
+                prof = self.option.profiling
+                if prof["enable"]:
+                    # the CPU path has no copies to exclude: warm up, then time `repeat` runs on the host clock
+                    for _ in range(prof["warmup"]):
+                        self._interp.run(feeds)
+                    t0 = time.perf_counter()
+                    for _ in range(max(prof["repeat"], 1)):
+                        res = self._interp.run(feeds)
+                    self._profile_time = (time.perf_counter() - t0) / max(prof["repeat"], 1)
+                    return res
+                return self._interp.run(feeds)
             with torch.cuda.device(self.device):
                 shapes = {vi.name: list(data[vi.name].shape) for vi in self.graph.inputs}
                 plan = self._plan_for(shapes)
@@ -310,6 +319,13 @@ class Runtime:
 
     def get_profile_time(self) -> float:
         return self._profile_time
+
+    def export_trace(self, shapes: Dict[str, Sequence[int]], path: str = "", iters: int = 3) -> Dict[str, Any]:
+        """Per-step device timeline of the plan for ``shapes`` as a Chrome-trace JSON document (see ``Plan.trace``)."""
+        if not self.on_gpu:
+            raise RuntimeError("export_trace needs the GPU back end")
+        with torch.cuda.device(self.device):
+            return self._plan_for(shapes).trace(path, iters)
 
     def clone(self, stream=None, device_id: int = -1) -> "Runtime":
         opt = self.option.clone()

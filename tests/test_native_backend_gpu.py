@@ -109,3 +109,23 @@ def test_ernie_tiny_matches_interpreter(task):
         assert (out - r).abs().max().item() < 3e-2
     names = [s.name for s in plan.steps]
     assert any(n.startswith("attn_qk") or n == "attention" for n in names) and any(n == "layernorm" for n in names)
+
+
+def test_plan_trace_is_a_chrome_trace_document(tmp_path):
+    import json
+    import fastdeploy_b200 as fd
+    from fastdeploy_b200.models.resnet import resnet18_like_onnx
+    path = tmp_path / "m.onnx"
+    path.write_bytes(resnet18_like_onnx())
+    opt = fd.RuntimeOption()
+    opt.set_model_path(str(path), "", fd.ModelFormat.ONNX)
+    opt.use_gpu(0)
+    rt = fd.Runtime(opt)
+    out = tmp_path / "trace.json"
+    doc = rt.export_trace({"input": [4, 3, 64, 64]}, str(out))
+    loaded = json.loads(out.read_text())
+    assert loaded["otherData"]["steps"] == len(doc["traceEvents"]) >= 18
+    ev = loaded["traceEvents"]
+    assert all(e["ph"] == "X" and e["dur"] > 0 and e["cat"] == "native" for e in ev)
+    assert all(ev[i + 1]["ts"] >= ev[i]["ts"] for i in range(len(ev) - 1))
+    assert any(e["name"].startswith("conv") for e in ev)

@@ -41,3 +41,17 @@ def test_coco_map_and_miou():
     s = EV.segmentation_metrics(pred, label, 2)
     assert abs(s["acc"] - 0.8) < 1e-9 and abs(s["miou"] - (2 / 3 + 2 / 3) / 2) < 1e-9
     assert EV.topk_accuracy(np.array([[0.1, 0.9], [0.8, 0.2]]), [1, 1], 1) == 0.5
+
+
+def test_model_zoo_benchmark_driver_on_cpu(tmp_path):
+    from fastdeploy_b200.benchmarks import model_zoo
+    cfg_file = tmp_path / "config.cpu.txt"
+    cfg_file.write_text("device: cpu\ncpu_thread_nums: 1\nwarmup: 1\nrepeat: 2\nprofile_mode: end2end\n"
+                        "collect_memory_info: true\nsampling_interval: 1\nresult_path: %s\n" % (tmp_path / "result.txt"))
+    cfg = model_zoo.load_benchmark_config(str(cfg_file))
+    assert cfg["device"] == "cpu" and cfg["repeat"] == "2" and cfg["use_fp16"] == "true"
+    assert model_zoo.main(["--model", "ppocr_cls", "--config_path", str(cfg_file)]) == 0
+    text = (tmp_path / "result.txt").read_text()
+    assert "End2End(ms):" in text and "cpu_rss_mb:" in text
+    res = model_zoo.run_benchmark("ernie", dict(cfg, profile_mode="runtime", collect_memory_info="false", warmup="1", repeat="2"))
+    assert res["Runtime(ms)"] > 0
