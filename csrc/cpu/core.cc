@@ -2,6 +2,7 @@
 // Counterparts in the reference: fastdeploy/core/fd_scalar.h:25-115 (Scalar), fastdeploy/utils/perf.h:22-48 (TimeCounter).
 #include <chrono>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <limits>
 #include <string>
@@ -83,7 +84,9 @@ FDB_CPU_API int fdb_scalar_from_string(void* out, const char* text) {
   else if (t == "-inf") s.v.f64 = -std::numeric_limits<double>::infinity();
   else if (t == "nan") s.v.f64 = std::numeric_limits<double>::quiet_NaN();
   else {
-    try { s.v.f64 = std::stod(t); } catch (...) { fdbcpu::set_error("scalar: not a number"); return -1; }
+    char* end = nullptr;
+    s.v.f64 = std::strtod(t.c_str(), &end);
+    if (t.empty() || end == t.c_str() || *end != '\0') { fdbcpu::set_error("scalar: not a number"); return -1; }
   }
   std::memcpy(out, &s, sizeof(s));
   return 0;

@@ -29,16 +29,22 @@ namespace fdb {
 
 struct AttnDesc {
   const void* q; const void* k; const void* vt; void* out; const float* mask; int* status;
+  const int* seq_len;        // device, one per batch item: keys (and, when S == Sk, queries) that are real; may be null
+  const int* seq_start;      // device, one per batch item: first row of the item in q / k / out and first column
+                             // in vt (multiples of 8); null = items are S (Sk) rows apart
   int dtype;                 // kF16 or kBF16
   int B, H, S, Sk, D;
   int q_ld, k_ld, o_ld;      // row pitches in elements; rows of one batch item are S (Sk) consecutive rows
-  int skp;                   // row pitch of vt [B][H][D][skp]
+  int skp;                   // row pitch of vt [B][H][D][skp]; with seq_start: vt is [H][D][skp] over all rows
+  int total_rows;            // with seq_start: rows of q / k / out (all items together)
   long long m_b, m_s;        // mask element (b, s, k) at b * m_b + s * m_s + k; mask may be null
   float scale;
 };
 
 struct AttnParams {
   const float* mask; uint8_t* out; int* status;
+  const int* seq_len; const int* seq_start;
+  int total_rows;
   int H, S, Sk, D, o_ld;
   int sk_pad;                // keys rounded up: multiple of 16 (<= 256) or of 32 (> 256)
   int d_chunks;              // ceil(D / 64)
@@ -107,7 +113,26 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const uint32_t vt_chunk_bytes = static_cast<uint32_t>((p.D + 7) / 8 * 8) * 128u;
   const int col0 = h * p.D;
 
-  if (tid == 0) {
+  // Per-item lengths. Everything below sizes its loops by `len`; the loads keep the planned box sizes (rows past
+  // the item are other items' rows or the zero fill, and never reach a result: their probabilities are written
+  // as zero and their scores are never read).
+  int len = p.Sk, q_row0 = b * p.S, k_row0 = b * p.Sk, vt_x0 = 0, vt_y0 = (b * p.H + h) * p.D;
+  bool valid = true;
+  if (p.seq_len != nullptr) len = max(0, min(__ldg(p.seq_len + b), p.Sk));
+  if (p.seq_start != nullptr) {
+    const int st = __ldg(p.seq_start + b);
+    valid = st >= 0 && (st & 7) == 0 && st + len <= p.total_rows;
+    q_row0 = k_row0 = vt_x0 = st;
+    vt_y0 = h * p.D;
+  }
+  const int S_b = (p.seq_len != nullptr && p.S == p.Sk) ? len : p.S;
+  const int sk_pad = len <= 256 ? (len + 15) / 16 * 16 : (len + 31) / 32 * 32;
+  const int k_chunks = (sk_pad + 63) / 64;
+  const int q_tiles = (S_b + 127) / 128;
+  if (!valid && tid == 0) abort_word = kStatusBadShape;
+  const bool run = valid && len > 0;
+
+  if (run && tid == 0) {
     // K: d_chunks x k_loads boxes of [k_box rows x 64 cols]; V^T: k_chunks boxes of [D rows x 64 cols]
     const uint32_t bytes = static_cast<uint32_t>(p.d_chunks) * k_chunk_bytes +
                            static_cast<uint32_t>(p.k_chunks) * static_cast<uint32_t>(p.D) * 128u;
@@ -115,22 +140,22 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     for (int c = 0; c < p.d_chunks; ++c)
       for (int l = 0; l < p.k_loads; ++l)
         tma_load_2d(sK + c * k_chunk_bytes + static_cast<uint32_t>(l * p.k_box) * 128u, &tm_k, bar_kv, col0 + c * 64,
-                    b * p.Sk + l * p.k_box);
+                    k_row0 + l * p.k_box);
     for (int j = 0; j < p.k_chunks; ++j)
-      tma_load_2d(sVT + j * vt_chunk_bytes, &tm_vt, bar_kv, j * 64, (b * p.H + h) * p.D);
+      tma_load_2d(sVT + j * vt_chunk_bytes, &tm_vt, bar_kv, vt_x0 + j * 64, vt_y0);
     mbar_arrive_expect_tx(bar_q, static_cast<uint32_t>(p.d_chunks) * q_chunk_bytes);
-    for (int c = 0; c < p.d_chunks; ++c) tma_load_2d(sQ + c * q_chunk_bytes, &tm_q, bar_q, col0 + c * 64, b * p.S);
+    for (int c = 0; c < p.d_chunks; ++c) tma_load_2d(sQ + c * q_chunk_bytes, &tm_q, bar_q, col0 + c * 64, q_row0);
   }
 
   const uint32_t fmt = BF16 ? 1u : 0u;
-  const int n_first = p.sk_pad > 256 ? 256 : p.sk_pad;
-  const int n_second = p.sk_pad - n_first;
+  const int n_first = sk_pad > 256 ? 256 : sk_pad;
+  const int n_second = sk_pad - n_first;
   const int d_steps_last = ((p.D - (p.d_chunks - 1) * 64) + 15) / 16;
   const float sl2 = p.scale * 1.4426950408889634f;
   uint32_t o_phase = 0;
-  bool ok = mbar_wait(bar_kv, 0, abort_flag, kStatusTimeoutProducer);
+  bool ok = run && mbar_wait(bar_kv, 0, abort_flag, kStatusTimeoutProducer);
 
-  for (int qt = 0; ok && qt < p.q_tiles; ++qt) {
+  for (int qt = 0; ok && qt < q_tiles; ++qt) {
     ok = mbar_wait(bar_q, qt & 1, abort_flag, kStatusTimeoutProducer);
     if (!ok) break;
     // ---------------------------------------------------------------- S = Q K^T
@@ -152,11 +177,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (!ok) break;
     tc_fence_after();
     const int row = qt * 128 + r;
-    const float* mrow = p.mask != nullptr ? p.mask + b * p.m_b + static_cast<long long>(row < p.S ? row : 0) * p.m_s : nullptr;
+    const float* mrow = p.mask != nullptr ? p.mask + b * p.m_b + static_cast<long long>(row < S_b ? row : 0) * p.m_s : nullptr;
     // Warps whose 32 rows all lie beyond the last query take part in the barriers only.
-    const bool warp_active = qt * 128 + (warp & 3) * 32 < p.S;
+    const bool warp_active = qt * 128 + (warp & 3) * 32 < S_b;
     const bool masked = mrow != nullptr;
-    const int nblk = (p.sk_pad + 31) / 32;
+    const int nblk = (sk_pad + 31) / 32;
     constexpr float kLog2e = 1.4426950408889634f;
     uint32_t va[32], vb[32];
     // ---------------------------------------------------------------- pass 1: row maximum
@@ -165,14 +190,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // next 32 columns are already on their way out of tensor memory while these are compared.
     float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
     auto max_block = [&](const uint32_t (&v)[32], int c0) {
-      if (!masked && c0 + 32 <= p.Sk) {
+      if (!masked && c0 + 32 <= len) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[j]));
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int col = c0 + j;
-          if (col < p.Sk) {
+          if (col < len) {
             float sv = __uint_as_float(v[j]);
             if (masked) sv = fmaf(sv, sl2, __ldg(mrow + col) * kLog2e);
             m4[j & 3] = fmaxf(m4[j & 3], sv);
@@ -205,14 +230,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
     // ---------------------------------------------------------------- pass 2: P and O = P V, 4 key chunks at a time
     float s4[4] = {0.f, 0.f, 0.f, 0.f};
-    const int groups = (p.k_chunks + 3) / 4;
+    const int groups = (k_chunks + 3) / 4;
     const uint32_t prow = sP + static_cast<uint32_t>(r) * 128u;
     const uint32_t r7 = static_cast<uint32_t>(r & 7);
     const float neg_mx = -mx;
     // 32 probabilities -> 16 packed words -> four 16-byte stores into the swizzled row of chunk `lc`
     auto prob_block = [&](const uint32_t (&v)[32], int c0, int lc, int half) {
       uint32_t w[16];
-      if (!masked && c0 + 32 <= p.Sk) {
+      if (!masked && c0 + 32 <= len) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const float e0 = ex2_approx(fmaf(__uint_as_float(v[2 * j]), sl2, neg_mx));
@@ -228,8 +253,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           for (int t = 0; t < 2; ++t) {
             const int col = c0 + 2 * j + t;
             float off = neg_mx;
-            if (masked && col < p.Sk) off = fmaf(__ldg(mrow + col), kLog2e, neg_mx);
-            e[t] = col < p.Sk ? ex2_approx(fmaf(__uint_as_float(v[2 * j + t]), sl2, off)) : 0.f;
+            if (masked && col < len) off = fmaf(__ldg(mrow + col), kLog2e, neg_mx);
+            e[t] = col < len ? ex2_approx(fmaf(__uint_as_float(v[2 * j + t]), sl2, off)) : 0.f;
           }
           s4[j & 3] += e[0] + e[1];
           w[j] = pack2<BF16>(e[0], e[1]);
@@ -244,7 +269,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
     };
     for (int g = 0; ok && g < groups; ++g) {
-      const int ch0 = g * 4, ch1 = min(p.k_chunks, ch0 + 4);
+      const int ch0 = g * 4, ch1 = min(k_chunks, ch0 + 4);
       if (warp_active) {
         // 32-column blocks b0 .. b1-1 of this group; this warp takes every other one (blk & 1 == half), so
         // it always writes the same half of a 64-key chunk; blocks >= nblk are padding and written as zero
@@ -284,7 +309,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         tc_fence_after();
         const uint32_t idesc = make_idesc(fmt, 128, static_cast<uint32_t>((p.D + 15) / 16 * 16));
         for (int ch = ch0; ch < ch1; ++ch) {
-          const int keys = min(64, p.sk_pad - ch * 64);
+          const int keys = min(64, sk_pad - ch * 64);
           const uint64_t ad = make_kmajor_desc(sP + static_cast<uint32_t>(ch - ch0) * q_chunk_bytes, 128);
           const uint64_t bd = make_kmajor_desc(sVT + static_cast<uint32_t>(ch) * vt_chunk_bytes, 128);
           umma_f16_ksteps(tmem, ad, bd, idesc, ch != 0 ? 1u : 0u, static_cast<uint32_t>((keys + 15) / 16));
@@ -292,10 +317,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         umma_commit(bar_o);
         // Q is free since S was committed, and every thread is past its wait on this tile's Q barrier
         // (they all met at the barrier above): fetch the next tile's Q behind the rest of this one.
-        if (g == 0 && qt + 1 < p.q_tiles) {
+        if (g == 0 && qt + 1 < q_tiles) {
           mbar_arrive_expect_tx(bar_q, static_cast<uint32_t>(p.d_chunks) * q_chunk_bytes);
           for (int c = 0; c < p.d_chunks; ++c)
-            tma_load_2d(sQ + c * q_chunk_bytes, &tm_q, bar_q, col0 + c * 64, b * p.S + (qt + 1) * 128);
+            tma_load_2d(sQ + c * q_chunk_bytes, &tm_q, bar_q, col0 + c * 64, q_row0 + (qt + 1) * 128);
         }
       }
       ok = mbar_wait(bar_o, o_phase, abort_flag, kStatusTimeoutMma);
@@ -306,12 +331,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // ---------------------------------------------------------------- out = O / sum
     const float sum = warp_active ? red_sum[0][r] + red_sum[1][r] : 0.f;
     const float inv = sum > 0.f ? 1.f / sum : 0.f;
-    uint8_t* orow = p.out + ((static_cast<long long>(b) * p.S + row) * p.o_ld + col0) * 2;
+    uint8_t* orow = p.out + ((static_cast<long long>(q_row0) + row) * p.o_ld + col0) * 2;
     for (int c0 = half * 32; warp_active && c0 < p.D; c0 += 64) {
       uint32_t v[32];
       tmem_ld_32x32(lane_base + static_cast<uint32_t>(c0), v);
       tmem_ld_wait_dep(v);
-      if (row < p.S) {
+      if (row < S_b) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           if (c0 + u * 8 < p.D) {
@@ -375,6 +400,9 @@ FDB_API int fdb_attention_desc_size() { return static_cast<int>(sizeof(AttnDesc)
 
 // Plans one fused attention launch over fixed buffers. q [B*S rows, q_ld], k [B*Sk rows, k_ld] (head h in
 // columns h*D .. h*D+D-1), vt [B][H][D][skp] (V transposed per head, zero beyond Sk), out [B*S rows, o_ld].
+// seq_len (device) gives each item's real length; with seq_start (device, multiples of 8) the items are packed
+// back to back: q / k / out hold total_rows rows, vt is [H][D][skp] over all rows, S = Sk is the longest item
+// the plan admits, and B is the largest number of items (an item of length 0 costs an empty CTA).
 FDB_API void* fdb_attention_create(const AttnDesc* d) {
   if (d->dtype != kF16 && d->dtype != kBF16) { set_error("attention: dtype must be fp16 or bf16"); return nullptr; }
   if (!(d->scale > 0.f)) { set_error("attention: the score scale must be positive"); return nullptr; }
@@ -383,11 +411,16 @@ FDB_API void* fdb_attention_create(const AttnDesc* d) {
   }
   auto al16 = [](const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; };
   if (!al16(d->q) || !al16(d->k) || !al16(d->vt) || !al16(d->out) || d->q_ld % 8 || d->k_ld % 8 || d->o_ld % 8 ||
-      d->skp % 8 || d->skp < d->Sk) {
+      d->skp % 8 || (d->seq_start == nullptr && d->skp < d->Sk)) {
     set_error("attention: pointers must be 16-byte aligned and row pitches multiples of 8 elements"); return nullptr;
+  }
+  const bool packed = d->seq_start != nullptr;
+  if (packed && (d->seq_len == nullptr || d->S != d->Sk || d->total_rows < 1 || d->mask != nullptr)) {
+    set_error("attention: packed batches need seq_len, S == Sk, total_rows and no mask"); return nullptr;
   }
   auto* op = new AttnOp();
   AttnParams& p = op->prm;
+  p.seq_len = d->seq_len; p.seq_start = d->seq_start; p.total_rows = packed ? d->total_rows : d->B * d->S;
   p.mask = d->mask; p.out = static_cast<uint8_t*>(d->out); p.status = d->status;
   p.H = d->H; p.S = d->S; p.Sk = d->Sk; p.D = d->D; p.o_ld = d->o_ld;
   p.sk_pad = d->Sk <= 256 ? (d->Sk + 15) / 16 * 16 : (d->Sk + 31) / 32 * 32;
@@ -414,9 +447,12 @@ FDB_API void* fdb_attention_create(const AttnDesc* d) {
   op->grid = d->B * d->H;
   const CUtensorMapDataType dt = op->bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const unsigned long long width = static_cast<unsigned long long>(d->H) * d->D;
-  if (!encode_2d(&op->tq, dt, d->q, width, static_cast<unsigned long long>(d->B) * d->S, d->q_ld * 2ull, 128) ||
-      !encode_2d(&op->tk, dt, d->k, width, static_cast<unsigned long long>(d->B) * d->Sk, d->k_ld * 2ull, p.k_box) ||
-      !encode_2d(&op->tvt, dt, d->vt, d->skp, static_cast<unsigned long long>(d->B) * d->H * d->D, d->skp * 2ull, d->D)) {
+  const unsigned long long q_rows = packed ? d->total_rows : static_cast<unsigned long long>(d->B) * d->S;
+  const unsigned long long k_rows = packed ? d->total_rows : static_cast<unsigned long long>(d->B) * d->Sk;
+  const unsigned long long vt_rows = static_cast<unsigned long long>(packed ? 1 : d->B) * d->H * d->D;
+  if (!encode_2d(&op->tq, dt, d->q, width, q_rows, d->q_ld * 2ull, 128) ||
+      !encode_2d(&op->tk, dt, d->k, width, k_rows, d->k_ld * 2ull, p.k_box) ||
+      !encode_2d(&op->tvt, dt, d->vt, d->skp, vt_rows, d->skp * 2ull, d->D)) {
     set_error("attention: tensor map encoding failed"); delete op; return nullptr;
   }
   const void* fn = op->bf16 ? reinterpret_cast<const void*>(&attention_kernel<true>)

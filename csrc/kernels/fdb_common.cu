@@ -35,6 +35,10 @@ int sm_count() {
   return cached[dev];
 }
 
+struct OobUnit { const char* unit; OobReader fn; };
+static std::vector<OobUnit>& oob_units() { static std::vector<OobUnit> v; return v; }
+void register_oob_reader(const char* unit, OobReader fn) { oob_units().push_back({unit, fn}); }
+
 // A plan is an ordered launch list. The executor builds it once per
 // (model, shape bucket); replay is one native call that issues every kernel on
 // the given stream, so it can be captured into a CUDA graph as a whole.
@@ -47,6 +51,34 @@ struct Plan {
 }  // namespace fdb
 
 FDB_API const char* fdb_last_error() { return fdb::get_error(); }
+
+// 1 when the library was compiled with -DFDB_BOUNDS_CHECK.
+FDB_API int fdb_bounds_checked() {
+#ifdef FDB_BOUNDS_CHECK
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+// Synchronises the device and writes "count=<n>" (plus " unit=<file> site=<id> index=<i> extent=<n>" of the first
+// offender) into buf; returns the count of out-of-range indices seen since the last reset, -1 on a CUDA error.
+FDB_API long long fdb_bounds_report(char* buf, int buf_len, int reset) {
+  if (cudaDeviceSynchronize() != cudaSuccess) { fdb::set_error("fdb_bounds_report: device synchronise failed"); return -1; }
+  unsigned long long total = 0;
+  std::string first;
+  for (const fdb::OobUnit& u : fdb::oob_units()) {
+    fdb::OobRecord r = {};
+    if (u.fn(&r, reset) != 0) { fdb::set_error("fdb_bounds_report: cannot read a record"); return -1; }
+    if (r.count != 0 && first.empty())
+      first = std::string(" unit=") + u.unit + " site=" + std::to_string(r.site) + " index=" + std::to_string(r.index) +
+              " extent=" + std::to_string(r.extent);
+    total += r.count;
+  }
+  const std::string msg = "count=" + std::to_string(total) + first;
+  if (buf != nullptr && buf_len > 0) snprintf(buf, static_cast<size_t>(buf_len), "%s", msg.c_str());
+  return static_cast<long long>(total);
+}
 
 FDB_API void* fdb_plan_create() { return new fdb::Plan(); }
 

@@ -71,6 +71,40 @@ int sm_count();
 
 }  // namespace fdb
 
+// Checked build (-DFDB_BOUNDS_CHECK): a data-dependent index (a token id, a gather index) that the release
+// build silently clamps into range is also counted, and the first offender kept, in a record per .cu file;
+// fdb_bounds_report() sums the records and names the first site. A .cu file that uses FDB_NOTE_OOB puts
+// FDB_BOUNDS_TU("its name") once at namespace scope.
+namespace fdb {
+struct OobRecord { unsigned long long count; long long index; long long extent; int site; int pad; };
+typedef int (*OobReader)(OobRecord* out, int reset);
+void register_oob_reader(const char* unit, OobReader fn);
+}  // namespace fdb
+#ifdef FDB_BOUNDS_CHECK
+namespace fdb {
+static __device__ OobRecord g_oob_record;
+static __device__ __forceinline__ void note_oob(int site, long long i, long long n) {
+  if (atomicAdd(&g_oob_record.count, 1ull) == 0ull) { g_oob_record.index = i; g_oob_record.extent = n; g_oob_record.site = site; }
+}
+}  // namespace fdb
+#define FDB_NOTE_OOB(site, i, n) do { if ((i) < 0 || (i) >= (n)) fdb::note_oob((site), (i), (n)); } while (0)
+#define FDB_BOUNDS_TU(unit)                                                                      \
+  namespace {                                                                                    \
+  int fdb_read_oob_record(fdb::OobRecord* out, int reset) {                                      \
+    if (cudaMemcpyFromSymbol(out, fdb::g_oob_record, sizeof(fdb::OobRecord)) != cudaSuccess) return -1; \
+    if (reset) {                                                                                 \
+      fdb::OobRecord zero = {};                                                                  \
+      if (cudaMemcpyToSymbol(fdb::g_oob_record, &zero, sizeof(zero)) != cudaSuccess) return -1;  \
+    }                                                                                            \
+    return 0;                                                                                    \
+  }                                                                                              \
+  struct FdbOobRegistrar { FdbOobRegistrar() { fdb::register_oob_reader(unit, &fdb_read_oob_record); } } fdb_oob_registrar; \
+  }
+#else
+#define FDB_NOTE_OOB(site, i, n) do { } while (0)
+#define FDB_BOUNDS_TU(unit)
+#endif
+
 #define FDB_CUDA_OK(expr)                                                          \
   do {                                                                             \
     cudaError_t _e = (expr);                                                       \

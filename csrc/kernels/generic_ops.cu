@@ -275,10 +275,15 @@ __global__ void gather_rows_kernel(const void* __restrict__ table, const void* _
     const long long i = idx / row_elems, c = idx - i * row_elems;
     long long r = idt == kI64 ? static_cast<const long long*>(index)[i] : static_cast<const int*>(index)[i];
     if (r < 0) r += table_rows;
+    if (c == 0) FDB_NOTE_OOB(1, r, table_rows);
     r = r < 0 ? 0 : (r >= table_rows ? table_rows - 1 : r);      // clamp: an out-of-range id never reads outside
     store_from_double(out, odt, idx, load_as_double(table, tdt, r * row_elems + c));
   }
 }
+
+}  // namespace fdb
+FDB_BOUNDS_TU("generic_ops")
+namespace fdb {
 
 static int grid_of(long long total) {
   long long g = (total + 255) / 256;

@@ -185,16 +185,24 @@ __global__ void __launch_bounds__(256) layernorm_reg_kernel(const uint8_t* __res
 // ---- sum of up to 4 embedding lookups + LayerNorm: one warp per token ---------------------
 // p0..p3 ids (int64 [rows]) (null = position index row % i3), p4..p7 tables (16-bit [V][C]), p8 y;
 // gamma/beta fp32 are passed in a second descriptor call? No: p9 points at a fp32 block [gamma(C) | beta(C)].
-// i0 rows, i1 C, i2 num tables, i3 seq_len (for implicit positions), i4 bf16, i5 y_ld; f0 eps
+// i0 rows, i1 C, i2 num tables, i3 seq_len (for implicit positions), i4 bf16, i5 y_ld, i6..i9 rows of each table
+// (0 = not given); f0 eps. An id outside its table is clamped into it (a checked build also counts it).
 template <bool BF16>
 __global__ void embed_layernorm_kernel(const long long* const* __restrict__ ids4, const uint8_t* const* __restrict__ tabs4,
                                        uint8_t* __restrict__ y, const float* __restrict__ gb, long long rows, int C,
-                                       int ntab, int seq, int y_ld, float eps) {
+                                       int ntab, int seq, int y_ld, float eps, int4 table_rows) {
   const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
   long long idx[4];
-  for (int t = 0; t < ntab; ++t) idx[t] = ids4[t] ? ids4[t][row] : (row % seq);
+  const int vrows[4] = {table_rows.x, table_rows.y, table_rows.z, table_rows.w};
+  for (int t = 0; t < ntab; ++t) {
+    idx[t] = ids4[t] ? ids4[t][row] : (row % seq);
+    if (vrows[t] > 0) {
+      if (lane == 0) FDB_NOTE_OOB(2, idx[t], static_cast<long long>(vrows[t]));
+      idx[t] = idx[t] < 0 ? 0 : (idx[t] >= vrows[t] ? vrows[t] - 1 : idx[t]);
+    }
+  }
   float s = 0.f, ss = 0.f;
   // C <= 8 * 32 * 6 = 1536 keeps the row in registers
   float v[6][8];
@@ -321,6 +329,10 @@ __global__ void __launch_bounds__(256) head_transpose_vec_kernel(const uint16_t*
   }
 }
 
+}  // namespace fdb
+FDB_BOUNDS_TU("transformer_ops")
+namespace fdb {
+
 #define FDB_TF_CHECK()                              \
   do {                                              \
     cudaError_t _e = cudaGetLastError();            \
@@ -368,11 +380,12 @@ FDB_API void* fdb_transformer_create(int kind, const TfDesc* dp) {
       const int C = d.i[1], ntab = d.i[2], seq = d.i[3], y_ld = d.i[5];
       const bool bf = d.i[4] != 0;
       const float eps = d.f[0];
+      const int4 vr = make_int4(d.i[6], d.i[7], d.i[8], d.i[9]);
       if (C % 8 || C > 1536 || ntab < 1 || ntab > 4 || y_ld % 8) { set_error("embed_layernorm: C multiple of 8 and <= 1536, 1..4 tables"); delete op; return nullptr; }
       op->fn = [=](cudaStream_t s) {
         const int grid = static_cast<int>((rows * 32 + 255) / 256);
-        if (bf) embed_layernorm_kernel<true><<<grid, 256, 0, s>>>((const long long* const*)d.p[0], (const uint8_t* const*)d.p[1], (uint8_t*)d.p[2], (const float*)d.p[3], rows, C, ntab, seq, y_ld, eps);
-        else embed_layernorm_kernel<false><<<grid, 256, 0, s>>>((const long long* const*)d.p[0], (const uint8_t* const*)d.p[1], (uint8_t*)d.p[2], (const float*)d.p[3], rows, C, ntab, seq, y_ld, eps);
+        if (bf) embed_layernorm_kernel<true><<<grid, 256, 0, s>>>((const long long* const*)d.p[0], (const uint8_t* const*)d.p[1], (uint8_t*)d.p[2], (const float*)d.p[3], rows, C, ntab, seq, y_ld, eps, vr);
+        else embed_layernorm_kernel<false><<<grid, 256, 0, s>>>((const long long* const*)d.p[0], (const uint8_t* const*)d.p[1], (uint8_t*)d.p[2], (const float*)d.p[3], rows, C, ntab, seq, y_ld, eps, vr);
         FDB_TF_CHECK();
       };
       break;

@@ -14,6 +14,16 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 KERNEL_LIB = os.path.join(HERE, "libfdb200_kernels.so")
 CPU_LIB = os.path.join(HERE, "libfdb200_cpu.so")
 
+# FDX_NATIVE_VARIANT=boundscheck swaps in the checked kernel library, =asan / tsan / ubsan the sanitised host
+# library (both built by ``python -m fastdeploy_b200._native.build --mode <variant>``).
+VARIANT = os.environ.get("FDX_NATIVE_VARIANT", "")
+if VARIANT:
+    _vdir = os.path.join(os.path.dirname(os.path.dirname(HERE)), "build", VARIANT)
+    if VARIANT == "boundscheck":
+        KERNEL_LIB = os.path.join(_vdir, "libfdb200_kernels.so")
+    else:
+        CPU_LIB = os.path.join(_vdir, "libfdb200_cpu.so")
+
 _lock = threading.Lock()
 _kernels = None
 _cpu = None
@@ -74,3 +84,18 @@ def cpu_available() -> bool:
 def last_error() -> str:
     msg = kernels().fdb_last_error()
     return msg.decode() if msg else ""
+
+
+def bounds_report(reset: bool = True):
+    """(count, text) of out-of-range data-dependent indices seen by the checked kernel library since the last
+    reset; ``(0, "not a checked build")`` for the release library. Synchronises the device."""
+    lib = kernels()
+    if not lib.fdb_bounds_checked():
+        return 0, "not a checked build"
+    lib.fdb_bounds_report.restype = ctypes.c_longlong
+    lib.fdb_bounds_report.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.c_int]
+    buf = ctypes.create_string_buffer(256)
+    n = lib.fdb_bounds_report(buf, 256, 1 if reset else 0)
+    if n < 0:
+        raise NativeLibraryError(lib.fdb_last_error().decode())
+    return int(n), buf.value.decode()

@@ -9,6 +9,15 @@ Two shared objects are produced next to this file:
 
 Run ``python -m fastdeploy_b200._native.build`` to (re)build; objects are cached
 by source mtime under ``build/``.
+
+Checked variants (``--mode``) are written under ``build/<mode>/`` and never replace the release libraries:
+
+* ``boundscheck`` - the kernel library with ``-DFDB_BOUNDS_CHECK``: data-dependent indices that the release
+  build clamps are counted and the first offender kept (``fdb_bounds_report``). Load it with
+  ``FDX_NATIVE_VARIANT=boundscheck``.
+* ``asan`` / ``tsan`` / ``ubsan`` - the host library with the matching ``-fsanitize=`` flag and frame
+  pointers; run a host test with it by pre-loading the sanitizer runtime (``sanitizer_runtime(mode)``)
+  and ``FDX_NATIVE_VARIANT=<mode>``.
 """
 from __future__ import annotations
 
@@ -54,6 +63,71 @@ def _compile(cmd: list[str], log_path: str) -> tuple[int, str]:
     with open(log_path, "w") as f:
         f.write(" ".join(cmd) + "\n" + proc.stdout)
     return proc.returncode, proc.stdout
+
+
+SANITIZERS = {"asan": "address", "tsan": "thread", "ubsan": "undefined"}
+
+
+def variant_dir(mode: str) -> str:
+    return os.path.join(ROOT, "build", mode)
+
+
+def variant_lib(mode: str) -> str:
+    """Path of the checked library of ``mode`` (kernels for ``boundscheck``, the host library for sanitizers)."""
+    name = "libfdb200_kernels.so" if mode == "boundscheck" else "libfdb200_cpu.so"
+    return os.path.join(variant_dir(mode), name)
+
+
+def sanitizer_runtime(mode: str) -> str:
+    """Shared runtime of the sanitizer (to be put in LD_PRELOAD of the process that loads the checked library)."""
+    cxx = shutil.which("g++") or "g++"
+    name = {"asan": "libasan.so", "tsan": "libtsan.so", "ubsan": "libubsan.so"}[mode]
+    out = subprocess.run([cxx, "-print-file-name=" + name], stdout=subprocess.PIPE, text=True).stdout.strip()
+    return out if os.path.isabs(out) and os.path.exists(out) else ""
+
+
+def build_variant(mode: str, verbose: bool = False, force: bool = False) -> str:
+    """Builds one checked library into ``build/<mode>/`` (objects cached by source mtime) and returns its path."""
+    out_dir = variant_dir(mode)
+    os.makedirs(out_dir, exist_ok=True)
+    lib = variant_lib(mode)
+    if mode == "boundscheck":
+        nvcc = _nvcc()
+        srcs = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cu")))
+        jobs = [(s, [nvcc] + NVCC_FLAGS + ["-DFDB_BOUNDS_CHECK=1", "-I", os.path.join(CSRC, "kernels"), "-c", s, "-o",
+                                           os.path.join(out_dir, os.path.basename(s) + ".o")],
+                 os.path.join(out_dir, os.path.basename(s) + ".log")) for s in srcs]
+        link = [nvcc, "-shared", "-o", lib] + [j[1][-1] for j in jobs] + \
+               ["-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static", "-ldl"]
+    elif mode in SANITIZERS:
+        cxx = shutil.which("g++") or "g++"
+        flags = [f for f in CXX_FLAGS if f != "-O2"] + ["-O1", "-g", "-fno-omit-frame-pointer",
+                                                         "-fsanitize=" + SANITIZERS[mode]]
+        srcs = sorted(glob.glob(os.path.join(CSRC, "cpu", "*.cc")))
+        jobs = [(s, [cxx] + flags + ["-I", os.path.join(CSRC, "cpu"), "-I", os.path.join(CSRC, "capi"), "-c", s, "-o",
+                                     os.path.join(out_dir, "cpu_" + os.path.basename(s) + ".o")],
+                 os.path.join(out_dir, "cpu_" + os.path.basename(s) + ".log")) for s in srcs]
+        link = [cxx, "-shared", "-o", lib] + [j[1][-1] for j in jobs] + ["-pthread", "-fsanitize=" + SANITIZERS[mode]]
+    else:
+        raise ValueError(f"unknown build mode {mode!r}: boundscheck, asan, tsan or ubsan")
+    sub = "kernels" if mode == "boundscheck" else "cpu"
+    hdrs = [h for pat in ("*.h", "*.cuh") for h in glob.glob(os.path.join(CSRC, sub, pat))]
+    todo = [j for j in jobs if force or _newer(j[0], j[1][-1], hdrs)]
+    if not todo and os.path.exists(lib):
+        return lib
+    with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
+        futs = {ex.submit(_compile, cmd, log): src for src, cmd, log in todo}
+        for fut in cf.as_completed(futs):
+            rc, out = fut.result()
+            if verbose or rc != 0:
+                print(out)
+            if rc != 0:
+                raise RuntimeError(f"compiling {futs[fut]} for mode {mode} failed")
+    rc, out = _compile(link, os.path.join(out_dir, "link.log"))
+    if rc != 0:
+        print(out)
+        raise RuntimeError(f"linking {lib} failed")
+    return lib
 
 
 def build_kernels(verbose: bool = False, force: bool = False) -> str:
@@ -155,5 +229,9 @@ def build_all(verbose: bool = False, force: bool = False) -> None:
 
 
 if __name__ == "__main__":
-    build_all(verbose="-v" in sys.argv, force="-f" in sys.argv)
-    print("built:", KERNEL_LIB, CPU_LIB if os.path.exists(CPU_LIB) else "")
+    if "--mode" in sys.argv:
+        print("built:", build_variant(sys.argv[sys.argv.index("--mode") + 1], verbose="-v" in sys.argv,
+                                      force="-f" in sys.argv))
+    else:
+        build_all(verbose="-v" in sys.argv, force="-f" in sys.argv)
+        print("built:", KERNEL_LIB, CPU_LIB if os.path.exists(CPU_LIB) else "")

@@ -69,7 +69,8 @@ def embed_layernorm(ids: List[Optional[torch.Tensor]], tables: List[torch.Tensor
                        dtype=torch.int64, device=dev)
     tbp = torch.tensor([t.data_ptr() for t in tables] + [0] * (4 - len(tables)), dtype=torch.int64, device=dev)
     gb = torch.cat([gamma.float().reshape(-1), beta.float().reshape(-1)]).contiguous().to(dev)
-    return _make(K_EMBED_LN, [idp, tbp, y, gb], [rows, c, len(tables), seq, _bf(y), y_ld or c], [eps],
+    return _make(K_EMBED_LN, [idp, tbp, y, gb], [rows, c, len(tables), seq, _bf(y), y_ld or c] +
+                 [int(t.shape[0]) for t in tables] + [0] * (4 - len(tables)), [eps],
                  "embed_layernorm", keep=list(ids) + list(tables))
 
 
@@ -85,10 +86,11 @@ def head_transpose(v: torch.Tensor, vt: torch.Tensor, *, b: int, s: int, h: int,
 
 class _AttnDesc(ctypes.Structure):
     _fields_ = [("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("vt", ctypes.c_void_p), ("out", ctypes.c_void_p),
-                ("mask", ctypes.c_void_p), ("status", ctypes.c_void_p), ("dtype", ctypes.c_int),
+                ("mask", ctypes.c_void_p), ("status", ctypes.c_void_p), ("seq_len", ctypes.c_void_p),
+                ("seq_start", ctypes.c_void_p), ("dtype", ctypes.c_int),
                 ("B", ctypes.c_int), ("H", ctypes.c_int), ("S", ctypes.c_int), ("Sk", ctypes.c_int), ("D", ctypes.c_int),
                 ("q_ld", ctypes.c_int), ("k_ld", ctypes.c_int), ("o_ld", ctypes.c_int), ("skp", ctypes.c_int),
-                ("m_b", ctypes.c_longlong), ("m_s", ctypes.c_longlong), ("scale", ctypes.c_float)]
+                ("total_rows", ctypes.c_int), ("m_b", ctypes.c_longlong), ("m_s", ctypes.c_longlong), ("scale", ctypes.c_float)]
 
 
 def fused_attention_fits(s: int, sk: int, d: int) -> bool:
@@ -100,8 +102,11 @@ def fused_attention_fits(s: int, sk: int, d: int) -> bool:
     return dch * sk_pad * 128 + kch * d * 128 + dch * 16384 + min(kch, 4) * 16384 + 1024 + 4096 <= 227 * 1024
 
 
-def fused_attention_op(q, k, vt, out, mask, *, b, heads, s, sk, d, skp, scale, m_b, m_s, status) -> NativeOp:
-    """One launch of csrc/kernels/attention_sm100.cu: scores and probabilities stay in tensor / shared memory."""
+def fused_attention_op(q, k, vt, out, mask, *, b, heads, s, sk, d, skp, scale, m_b, m_s, status, seq_len=None,
+                       seq_start=None, total_rows=0) -> NativeOp:
+    """One launch of csrc/kernels/attention_sm100.cu: scores and probabilities stay in tensor / shared memory.
+    ``seq_len`` (int32, device, one per item) bounds each item's keys and, for self-attention, its queries;
+    with ``seq_start`` (int32, device, multiples of 8) the items are packed rows of 2-D ``q``/``k``/``out``."""
     lib = _native.kernels()
     if not getattr(lib, "_attn_ready", False):
         lib.fdb_attention_create.restype = ctypes.c_void_p
@@ -115,9 +120,16 @@ def fused_attention_op(q, k, vt, out, mask, *, b, heads, s, sk, d, skp, scale, m
     dd.status = status.ptr
     dd.dtype = dtype_code(q.dtype)
     dd.B, dd.H, dd.S, dd.Sk, dd.D = b, heads, s, sk, d
-    dd.q_ld, dd.k_ld, dd.o_ld, dd.skp = q.stride(1), k.stride(1), out.stride(1), skp
+    row = -2                                    # the token dimension of [B, S, C] and of packed [T, C] alike
+    dd.q_ld, dd.k_ld, dd.o_ld, dd.skp = q.stride(row), k.stride(row), out.stride(row), skp
     dd.m_b, dd.m_s, dd.scale = m_b, m_s, scale
-    return NativeOp(lib.fdb_attention_create(ctypes.byref(dd)), [q, k, vt, out, mask, status], "attention")
+    for name, t in (("seq_len", seq_len), ("seq_start", seq_start)):
+        if t is not None:
+            assert t.dtype == torch.int32 and t.is_contiguous() and t.numel() >= b and t.device == q.device, name
+            setattr(dd, name, t.data_ptr())
+    dd.total_rows = int(total_rows)
+    return NativeOp(lib.fdb_attention_create(ctypes.byref(dd)), [q, k, vt, out, mask, status, seq_len, seq_start],
+                    "attention")
 
 
 class Attention:
@@ -126,7 +138,7 @@ class Attention:
 
     def __init__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, *, heads: int,
                  scale: float, mask: Optional[torch.Tensor] = None, status: Optional[StatusWord] = None,
-                 fused: Optional[bool] = None):
+                 fused: Optional[bool] = None, seq_lens: Optional[torch.Tensor] = None):
         b, s, hd = q.shape
         sk = k.shape[1]
         d = hd // heads
@@ -144,6 +156,8 @@ class Attention:
         if fused and not can_fuse:
             raise ValueError("fused attention needs <= 512 keys, a head dim that is a multiple of 16 (<= 128) and "
                              "batch items stored as consecutive rows")
+        if seq_lens is not None and not fused:
+            raise ValueError("per-item lengths need the fused attention kernel")
         self.fused = fused
         if fused:
             m_b = m_s = 0
@@ -154,7 +168,7 @@ class Attention:
                 m_s = mm.stride(1) if mm.shape[1] > 1 else 0
             tr = head_transpose(v, self.vt, b=b, s=sk, h=heads, d=d, v_ld=v_ld, sp=skp)
             at = fused_attention_op(q, k, self.vt, out, mask, b=b, heads=heads, s=s, sk=sk, d=d, skp=skp, scale=scale,
-                                    m_b=m_b, m_s=m_s, status=self.status)
+                                    m_b=m_b, m_s=m_s, status=self.status, seq_len=seq_lens)
             self.ops = [tr, at]
             self.keep = [q, k, v, out, mask]
             return
@@ -178,6 +192,45 @@ class Attention:
                       w_h_stride=d * skp, w_n_stride=heads * d * skp, name="attn_pv")
         self.ops = [qk, sm, tr, pv]
         self.keep = [q, k, v, out, mask]
+
+    def launch(self, stream=None) -> None:
+        for op in self.ops:
+            op.launch(stream)
+
+
+def pack_offsets(lengths, align: int = 8):
+    """Row offsets of sequences stored back to back, each start rounded up to ``align`` rows (the attention kernel
+    reads V^T by TMA, whose column coordinate must sit on a 16-byte boundary). Returns (starts, total rows)."""
+    starts, at = [], 0
+    for n in lengths:
+        starts.append(at)
+        at += (int(n) + align - 1) // align * align
+    return starts, at
+
+
+class PackedAttention:
+    """Self-attention over padding-free batches: ``q``/``k``/``v``/``out`` are ``[T, H*D]`` views holding up to
+    ``max_seqs`` sequences back to back (``seq_start[i]`` a multiple of 8, ``seq_len[i] <= max_len``). The two
+    int32 device tensors are read at launch time, so one planned op (and one CUDA graph) serves every batch
+    composition that fits ``T`` rows. Rows between sequences must hold finite values."""
+
+    def __init__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, *, heads: int,
+                 scale: float, max_len: int, seq_start: torch.Tensor, seq_len: torch.Tensor,
+                 status: Optional[StatusWord] = None):
+        t, hd = q.shape
+        d = hd // heads
+        if not fused_attention_fits(max_len, max_len, d):
+            raise ValueError("packed attention needs <= 512 tokens per sequence and a head dim that is a multiple of 16")
+        assert t % 8 == 0, "the packed buffers must hold a multiple of 8 rows"
+        self.status = status or StatusWord(q.device)
+        self.vt = torch.zeros(1, heads, d, t, dtype=q.dtype, device=q.device)
+        n = int(seq_len.numel())
+        tr = head_transpose(v, self.vt, b=1, s=t, h=heads, d=d, v_ld=v.stride(0), sp=t)
+        at = fused_attention_op(q, k, self.vt, out, None, b=n, heads=heads, s=max_len, sk=max_len, d=d, skp=t,
+                                scale=scale, m_b=0, m_s=0, status=self.status, seq_len=seq_len, seq_start=seq_start,
+                                total_rows=t)
+        self.ops = [tr, at]
+        self.keep = [q, k, v, out, seq_start, seq_len]
 
     def launch(self, stream=None) -> None:
         for op in self.ops:

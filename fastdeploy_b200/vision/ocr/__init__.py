@@ -433,3 +433,5 @@ PPOCRSystemv2, PPOCRSystemv3, PPOCRSystemv4 = PPOCRv2, PPOCRv3, PPOCRv4
 
 from .structure import (PPStructureV2Table, StructureV2Layout, StructureV2LayoutPostprocessor, StructureV2Table,  # noqa: E402,F401
                         StructureV2TablePostprocessor, StructureV2TablePreprocessor, build_html)
+from .ser import (SERResult, StructureV2SERViLayoutXLM, StructureV2SERViLayoutXLMPostprocessor,  # noqa: E402,F401
+                  StructureV2SERViLayoutXLMPreprocessor)

@@ -139,3 +139,57 @@ def test_detection_postprocessor_rotated_masks_and_solov2():
     res = post.run([np.array([3], np.int32), np.array([4, 5, 6], np.int64), np.array([0.9, 0.2, 0.6], np.float32), m])[0]
     assert res.label_ids == [4, 6] and res.boxes == [[1.0, 2.0, 7.0, 5.0], [6.0, 6.0, 9.0, 8.0]]
     assert res.masks[0].shape == [3, 6] and sum(res.masks[0].data) == 18 and res.masks[1].shape == [2, 3]
+
+
+def test_ser_vi_layoutxlm_windows_reading_order_and_line_vote(tmp_path):
+    from fastdeploy_b200.vision.ocr import ser as S
+
+    class Tok:                       # one id per character, wrapped in cls / sep like a real tokenizer
+        def encode(self, text):
+            return [0] + [10 + ord(c) % 50 for c in text] + [2]
+
+    (tmp_path / "cls.txt").write_text("OTHER\nQUESTION\nANSWER\nHEADER\n")
+    labels = S.load_labels(str(tmp_path / "cls.txt"))
+    assert labels == ["O", "B-QUESTION", "I-QUESTION", "B-ANSWER", "I-ANSWER", "B-HEADER", "I-HEADER"]
+    lines = [{"bbox": [300, 105, 400, 130], "transcription": "bb"},
+             {"bbox": [10, 100, 200, 130], "transcription": "aaa"},          # same row, further left: comes first
+             {"bbox": [10, 10, 20, 30, 20, 40, 10, 40], "transcription": "h"},
+             {"bbox": [10, 400, 600, 430], "transcription": "c" * 600}]      # spills into a second window
+    pre = S.StructureV2SERViLayoutXLMPreprocessor(Tok(), max_seq_len=512)
+    b = pre.run(lines, height=500, width=1000)
+    assert [r["transcription"][:1] for r in b["ocr_info"]] == ["h", "a", "b", "c"]
+    assert b["segment_offset_id"] == [1, 4, 6, 606]
+    assert b["input_ids"].shape == (2, 512) and b["bbox"].shape == (2, 512, 4)
+    assert b["input_ids"][0, 0] == 0 and b["input_ids"][0, 511] == 2 and b["attention_mask"][0].sum() == 512
+    assert b["attention_mask"][1].sum() == 606 - 510 + 2 and b["input_ids"][1, 97] == 2 and b["input_ids"][1, 98] == 1
+    assert b["bbox"][0, 1].tolist() == [10, 20, 20, 80]                       # 8-number box -> xyxy on the 0..1000 grid
+    assert b["bbox"][0, 2].tolist() == [10, 200, 200, 260] and b["bbox"][1, 97].tolist() == [1000] * 4
+
+    post = S.StructureV2SERViLayoutXLMPostprocessor(labels=labels)
+    assert post.draw_names == ["O", "QUESTION", "ANSWER", "HEADER"]
+    logits = np.zeros((2, 512, len(labels)), np.float32)
+    logits[..., 0] = 0.1
+    logits[0, 1, 5] = 1                                   # "h": B-HEADER
+    logits[0, 2, 1] = 1; logits[0, 3, 2] = 1              # "aaa": B-Q, I-Q, O -> QUESTION
+    logits[0, 5, 3] = 1; logits[0, 6, 4] = 1              # "bb": B-A, I-A
+    logits[1, 1:97, 4] = 1                                # tail of the long line: 96 x I-ANSWER against 504 x O
+    r = post.run(logits, b)
+    assert r.pred == ["HEADER", "QUESTION", "ANSWER", "O"] and r.pred_id == [3, 1, 2, 0]
+
+    m = S.StructureV2SERViLayoutXLM.__new__(S.StructureV2SERViLayoutXLM)
+    m.preprocessor, m.postprocessor, m.ocr = pre, post, None
+
+    class Info:
+        def __init__(self, n): self.name = n
+
+    class FakeRuntime:
+        def num_inputs(self): return 4
+        def get_input_info(self, i): return Info(["x0", "x1", "x2", "x3"][i])
+        def infer(self, feeds):
+            assert feeds["x1"].shape == (4, 512, 4) and feeds["x0"].dtype == np.int64
+            return [np.concatenate([logits, logits])]
+    m.runtime = FakeRuntime()
+    two = m.batch_predict([np.zeros((500, 1000, 3), np.uint8)] * 2, [lines, lines])
+    assert [x.pred for x in two] == [r.pred, r.pred]
+    with pytest.raises(ValueError):
+        m.predict(np.zeros((500, 1000, 3), np.uint8))
