@@ -263,6 +263,27 @@ def _attention(node, q, k, v, mask=None):
     return torch.matmul(att, split(v)).permute(0, 2, 1, 3).reshape(b, s, hd)
 
 
+@op("PackedAttention")
+def _packed_attention(node, q, k, v, seq_start, seq_len):
+    """Self-attention inside each of the sequences stored back to back in ``q``/``k``/``v`` ``[1, T, heads*dh]``:
+    sequence ``i`` is rows ``seq_start[i] .. seq_start[i] + seq_len[i]``; rows outside every sequence are zero;
+    domain fdb."""
+    heads = node.attr("num_heads")
+    hd = q.shape[-1]
+    dh = hd // heads
+    scale = node.attr("scale", 1.0 / math.sqrt(dh))
+    out = torch.zeros_like(q)
+    q2, k2, v2, o2 = q.reshape(-1, hd), k.reshape(-1, hd), v.reshape(-1, hd), out.view(-1, hd)
+    for st, n in zip(seq_start.reshape(-1).tolist(), seq_len.reshape(-1).tolist()):
+        if n <= 0:
+            continue
+        def split(t):
+            return t[st:st + n].reshape(n, heads, dh).permute(1, 0, 2)
+        att = torch.softmax(torch.matmul(split(q2), split(k2).transpose(-1, -2)) * scale, dim=-1)
+        o2[st:st + n] = torch.matmul(att, split(v2)).permute(1, 0, 2).reshape(n, hd)
+    return out
+
+
 @op("EmbedLayerNorm")
 def _embed_ln(node, ids, *rest):
     """sum of embedding lookups followed by LayerNorm; domain fdb.

@@ -39,6 +39,7 @@ SHAPE_RULES = {
         _meta([x.shape[0], (len(node.attr("anchors")) // 2) * x.shape[2] * x.shape[3], node.attr("class_num")], x.dtype)),
     "SetValue": lambda node, x, *v: _meta(x.shape, x.dtype),
     "TemporalShift": lambda node, x: _meta(x.shape, x.dtype),
+    "PackedAttention": lambda node, q, *rest: _meta(q.shape, q.dtype),
 }
 # a real tensor larger than this is treated as data, not as a shape tensor
 MAX_REAL_ELEMS = 4096

@@ -1226,6 +1226,34 @@ def _lower_Attention(self: Lowering, node: Node):
     self.vals[node.outputs[0]] = Val(out, False)
 
 
+def _lower_PackedAttention(self: Lowering, node: Node):
+    """Padding-free self-attention (ir/packing.py): q / k / v are ``[1, T, H*D]``; the starts and lengths are int32
+    plan inputs read by the kernel at every launch."""
+    from ..ops.transformer import PackedAttention, fused_attention_fits
+    shp = self.info.shapes[node.inputs[0]]
+    heads = node.attr("num_heads")
+    max_len = int(node.attr("max_len", 512))
+    if len(shp) != 3 or shp[0] != 1:
+        return False
+    t, hd = shp[1], shp[2]
+    d = hd // heads
+    if t % 8 or not fused_attention_fits(max_len, max_len, d):
+        raise ValueError(f"packed attention: {t} rows (multiple of 8), head dim {d} (multiple of 16), "
+                         f"longest sequence {max_len} (<= 512) do not fit the fused kernel")
+    q, k, v = (self.rows_view(nm, t, hd) for nm in node.inputs[:3])
+    start, lens = self.get(node.inputs[3]).t, self.get(node.inputs[4]).t
+    if start.dtype != torch.int32 or lens.dtype != torch.int32:
+        raise ValueError("packed attention: seq_start and seq_len must be int32 plan inputs")
+    out = torch.zeros(t, hd, dtype=self.dtype, device=self.device)
+    att = PackedAttention(q, k, v, out, heads=heads, scale=node.attr("scale", 1.0 / math.sqrt(d)), max_len=max_len,
+                          seq_start=start.reshape(-1), seq_len=lens.reshape(-1), status=self.plan.status)
+    for op in att.ops:
+        self.plan.add_native(op, node)
+        op.launch()
+    self.plan.extra.setdefault("attention", []).append(att)
+    self.vals[node.outputs[0]] = Val(out.view(1, t, hd), False)
+
+
 def _lower_Gelu(self: Lowering, node: Node):
     if node.attr("approximate", "none") == "tanh":
         return False
@@ -1244,4 +1272,5 @@ def _lower_Gelu(self: Lowering, node: Node):
 Lowering.lower_LayerNormalization = _lower_LayerNormalization
 Lowering.lower_EmbedLayerNorm = _lower_EmbedLayerNorm
 Lowering.lower_Attention = _lower_Attention
+Lowering.lower_PackedAttention = _lower_PackedAttention
 Lowering.lower_Gelu = _lower_Gelu
