@@ -33,6 +33,30 @@ class _ErnieBase(FastDeployModel):
         self.tokenizer.enable_truncation(max_length)
         self.init_runtime()
 
+    def enable_padding_free(self, max_tokens: int = 16384, max_seqs: int = 64, bucket_rows: int = 2048) -> None:
+        """Runs batches without padding (text/packed.py): sequences back to back in plans of ``bucket_rows`` steps
+        up to ``max_tokens`` rows, at most ``max_seqs`` sequences per batch. Results are those of the padded run."""
+        from .packed import PackedEncoder
+        self._packed = PackedEncoder(self.runtime, max_tokens, max_seqs, self.max_length,
+                                     pad_values=[self.tokenizer.pad_id, 0],
+                                     token_buckets=range(bucket_rows, max_tokens + 1, bucket_rows))
+
+    def _logits(self, encs, feed) -> List[np.ndarray]:
+        """Per-sequence logits of the first output: through the packed plans when enabled, else the padded batch."""
+        packed = getattr(self, "_packed", None)
+        if packed is None:
+            return list(np.asarray(self.runtime.infer(feed)[0], dtype=np.float32))
+        arrays = list(feed.values())
+        out: List[np.ndarray] = []
+        for s in range(0, len(encs), packed.max_seqs):
+            seqs = []
+            for i in range(s, min(s + packed.max_seqs, len(encs))):
+                n = int(sum(encs[i].attention_mask))
+                seqs.append(tuple(a[i, :n] for a in arrays))
+            res = packed.infer(seqs)[0]
+            out += [np.asarray(r, np.float32) for r in res]
+        return out
+
     def encode(self, texts: Sequence[Union[str, Tuple[str, str]]], pad_to_max: bool = False):
         encs = self.tokenizer.encode_batch(list(texts), pad=True)
         if pad_to_max:
@@ -50,8 +74,8 @@ class ErnieSeqCls(_ErnieBase):
     def predict(self, texts: Sequence[Union[str, Tuple[str, str]]], batch_size: int = 32) -> List[Tuple[int, float]]:
         out: List[Tuple[int, float]] = []
         for s in range(0, len(texts), batch_size):
-            _, feed = self.encode(texts[s:s + batch_size])
-            logits = np.asarray(self.runtime.infer(feed)[0], dtype=np.float32)
+            encs, feed = self.encode(texts[s:s + batch_size])
+            logits = np.stack(self._logits(encs, feed))
             probs = softmax(logits.reshape(logits.shape[0], -1))
             for row in probs:
                 k = int(row.argmax())
@@ -67,8 +91,7 @@ class ErnieTokenCls(_ErnieBase):
         out = []
         for s in range(0, len(texts), batch_size):
             encs, feed = self.encode(texts[s:s + batch_size])
-            logits = np.asarray(self.runtime.infer(feed)[0], dtype=np.float32)
-            probs = softmax(logits, axis=-1)
+            probs = [softmax(l, axis=-1) for l in self._logits(encs, feed)]     # packed rows stop at the real length
             for e, p in zip(encs, probs):
                 row = []
                 for t, (off, m) in enumerate(zip(e.offsets, e.attention_mask)):

@@ -237,10 +237,29 @@ class UIEModel(FastDeployModel):
                 final.append(out)
         return final
 
+    def enable_padding_free(self, max_tokens: int = 16384, max_seqs: int = 64, bucket_rows: int = 2048) -> None:
+        """Runs the prompt + text batches without padding (text/packed.py); probabilities past a sequence's end,
+        which the padded run computes and the decoder ignores, come back as zero."""
+        from .packed import PackedEncoder
+        self._packed = PackedEncoder(self.runtime, max_tokens, max_seqs, self.max_length,
+                                     token_buckets=range(bucket_rows, max_tokens + 1, bucket_rows))
+
     def _infer_batched(self, feed: Dict[str, np.ndarray]) -> Tuple[np.ndarray, np.ndarray]:
         first = next(iter(feed.values()))
         n = first.shape[0]
         starts, ends = [], []
+        packed = getattr(self, "_packed", None)
+        if packed is not None:
+            arrays = list(feed.values())
+            lens = arrays[3].sum(axis=1).astype(np.int64)               # the attention mask is the fourth input
+            sp, ep = np.zeros(first.shape, np.float32), np.zeros(first.shape, np.float32)
+            for s in range(0, n, packed.max_seqs):
+                idx = range(s, min(s + packed.max_seqs, n))
+                outs = packed.infer([tuple(a[i, :lens[i]] for a in arrays) for i in idx])
+                for j, i in enumerate(idx):
+                    sp[i, :lens[i]] = np.asarray(outs[0][j]).reshape(-1)
+                    ep[i, :lens[i]] = np.asarray(outs[1][j]).reshape(-1)
+            return sp, ep
         for s in range(0, n, self.batch_size):
             chunk = {k: v[s:s + self.batch_size] for k, v in feed.items()}
             shape = next(iter(chunk.values())).shape

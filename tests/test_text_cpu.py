@@ -102,6 +102,22 @@ def test_uie_end_to_end_tiny(tmp_path):
                     assert texts[res.index(r)][it.start:it.end] == it.text
     d = m.predict(texts, return_dict=True)
     assert isinstance(d[0], dict)
+    m.enable_padding_free(max_tokens=256, max_seqs=4, bucket_rows=64)      # same spans without padded rows
+    d2 = m.predict(texts, return_dict=True)
+    assert d2.keys() == d.keys() if isinstance(d, dict) else len(d2) == len(d)
+    for a, b in zip(d, d2):
+        assert str(a) == str(b) or _close_results(a, b)
+
+
+def _close_results(a, b, tol=1e-4):
+    """Two UIE result dictionaries with the same spans and probabilities within ``tol``."""
+    if isinstance(a, dict):
+        return a.keys() == b.keys() and all(_close_results(a[k], b[k], tol) for k in a)
+    if isinstance(a, (list, tuple)):
+        return len(a) == len(b) and all(_close_results(x, y, tol) for x, y in zip(a, b))
+    if isinstance(a, float):
+        return abs(a - b) < tol
+    return a == b
 
 
 def test_ernie_seq_cls_tiny(tmp_path):
@@ -116,6 +132,9 @@ def test_ernie_seq_cls_tiny(tmp_path):
     assert len(out) == 3
     for k, p in out:
         assert k in (0, 1) and 0.5 <= p <= 1.0
+    m.enable_padding_free(max_tokens=128, max_seqs=2, bucket_rows=32)      # 3 inputs: two packed batches
+    out2 = m.predict([("the cat", "a cat sat"), "single sentence", "x"])
+    assert [k for k, _ in out2] == [k for k, _ in out] and max(abs(a[1] - b[1]) for a, b in zip(out, out2)) < 1e-5
 
 
 def test_packed_encoder_matches_padded_batches(tmp_path):
