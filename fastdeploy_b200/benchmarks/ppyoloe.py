@@ -128,6 +128,7 @@ def run(ctx: Context, args) -> dict:
                      "p99_batch1_ms": round(float(np.percentile(lat, 99)), 3), "iters": len(lat),
                      "what": "rank 0, PPYOLOE.predict on one pinned 1080x1920 frame, wall clock"} if lat else None),
         "gpu_launches": int(launches), "clocks": clocks, "cpu_affinity": ctx.affinity, "impl": "ours",
+        "activation_memory": model.runtime.memory_report(),
     }
     out.update(extra)
     return out

@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from dataclasses import dataclass
 from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
 
@@ -212,7 +213,7 @@ class Lowering(GenericLowering):
 
     def __init__(self, graph: Graph, input_shapes: Dict[str, Sequence[int]], device: torch.device,
                  dtype: torch.dtype = torch.float16, input_values: Optional[Dict[str, np.ndarray]] = None,
-                 fp8: bool = False, act_scales: Optional[Dict[str, float]] = None):
+                 fp8: bool = False, act_scales: Optional[Dict[str, float]] = None, reuse_buffers: bool = False):
         self.g = graph
         self.device = device
         self.dtype = dtype
@@ -233,6 +234,11 @@ class Lowering(GenericLowering):
         self.preassigned: Dict[str, Val] = {}
         self.fused_away: set = set()        # ids of nodes that an earlier node's lowering has already covered
         self.pending_gate: Dict[str, Tuple[str, str]] = {}   # gated map -> (feature, gate) folded into its consumer
+        # static memory plan (runtime/arena.py): activation buffers whose readers are all lowered are handed back
+        from .arena import Arena
+        self.arena: Optional[Arena] = Arena(device) if reuse_buffers else None
+        self.arena_open = False              # buffers made before the node loop (promised slices, heads) stay private
+        self.remaining: Dict[str, int] = {}
         self.input_shapes = {k: list(v) for k, v in input_shapes.items()}
 
     # ------------------------------------------------------------------ helpers
@@ -248,8 +254,31 @@ class Lowering(GenericLowering):
 
     def new_nhwc(self, n: int, h: int, w: int, c: int, dtype: Optional[torch.dtype] = None) -> Val:
         cp = _round8(c)
+        if self.arena is not None and self.arena_open and cp == c:
+            # (padding channels must read as zero for good, so padded buffers stay out of the shared arena)
+            return Val(self.arena.alloc((n, h, w, c), dtype or self.dtype), True)
         buf = torch.zeros(n, h, w, cp, dtype=dtype or self.dtype, device=self.device)
         return Val(buf[..., :c], True)
+
+    def _release_dead(self, node: Node) -> None:
+        """After ``node`` (lowered or covered by an earlier one): its inputs have one reader fewer; arena blocks that
+        no value with readers to come, output, promised slice or held-back gate operand touches are handed back."""
+        for nm in set(i for i in node.inputs if i):
+            if nm in self.remaining:
+                self.remaining[nm] -= 1
+        needed = []
+        outs = set(self.g.output_names())
+        held = set()
+        for gated, (feat, gate) in self.pending_gate.items():
+            if self.remaining.get(gated, 0) > 0:
+                held.update((feat, gate))
+        for nm, v in self.vals.items():
+            if self.remaining.get(nm, 0) > 0 or nm in outs or nm in held or nm in self.plan.inputs:
+                needed.append(v.t)
+        for nm, v in self.preassigned.items():
+            if self.remaining.get(nm, 0) > 0 or nm in outs:
+                needed.append(v.t)
+        self.arena.release_unreferenced(needed)
 
     def out_nhwc(self, name: str, dtype: Optional[torch.dtype] = None) -> Val:
         """Destination of a 4-D op output: the pre-assigned concat slice or a fresh buffer."""
@@ -314,14 +343,23 @@ class Lowering(GenericLowering):
             self.plan.inputs[vi.name] = v
         self._plan_concats()
         for node in g.nodes:
-            if id(node) in self.fused_away:
-                continue
-            fn = getattr(self, "lower_" + node.op, None)
-            done = False
-            if fn is not None:
-                done = fn(node) is not False
-            if not done:
-                self.lower_fallback(node)
+            for nm in set(i for i in node.inputs if i):
+                self.remaining[nm] = self.remaining.get(nm, 0) + 1
+        self.arena_open = True
+        for node in g.nodes:
+            if id(node) not in self.fused_away:
+                fn = getattr(self, "lower_" + node.op, None)
+                done = False
+                if fn is not None:
+                    done = fn(node) is not False
+                if not done:
+                    self.lower_fallback(node)
+            if self.arena is not None:
+                self._release_dead(node)
+        self.arena_open = False
+        if self.arena is not None:
+            self.plan.extra["memory"] = self.arena.report()
+            self.plan.extra["arena"] = self.arena
         for vi in g.outputs:
             self.plan.outputs[vi.name] = self.get(vi.name)
         self.plan.finalize()
@@ -1096,13 +1134,17 @@ def optimize_cached(graph: Graph, input_shapes, input_values, opt_level: int, dt
 
 def build_plan(graph: Graph, input_shapes: Dict[str, Sequence[int]], device, dtype=torch.float16,
                input_values: Optional[Dict[str, np.ndarray]] = None, opt_level: int = 2, cache_dir: str = "",
-               fp8: bool = False, act_scales: Optional[Dict[str, float]] = None) -> Plan:
+               fp8: bool = False, act_scales: Optional[Dict[str, float]] = None,
+               reuse_buffers: Optional[bool] = None) -> Plan:
     """Optimises ``graph`` for the given shapes and lowers it to a plan on ``device``. ``fp8`` runs the linear layers on
     e4m3 operands; ``act_scales`` (tensor name -> calibrated absolute maximum) adds to the ranges the graph carries."""
     device = torch.device(device)
     with torch.cuda.device(device):
         g = optimize_cached(graph, input_shapes, input_values, opt_level, dtype, cache_dir)
-        low = Lowering(g, input_shapes, device, dtype, input_values, fp8=fp8, act_scales=act_scales)
+        if reuse_buffers is None:
+            reuse_buffers = os.environ.get("FDX_REUSE_BUFFERS", "1") not in ("0", "false")
+        low = Lowering(g, input_shapes, device, dtype, input_values, fp8=fp8, act_scales=act_scales,
+                       reuse_buffers=reuse_buffers)
         for node in g.nodes:
             if node.op == "PPYOLOEPost":
                 low.plan_PPYOLOEPost(node)

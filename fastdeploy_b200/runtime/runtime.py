@@ -167,9 +167,17 @@ class Runtime:
             if len(self._plans) >= self.option.native_option.max_plans:
                 self._plans.pop(next(iter(self._plans)))
             self._plans[key] = plan
+            mem = plan.extra.get("memory")
             log.info(f"built plan for {dict(key)} in {time.time() - t0:.2f}s: {len(plan.steps)} steps, "
-                     f"{plan.native_kernel_launches} native kernel launches")
+                     f"{plan.native_kernel_launches} native kernel launches" +
+                     (f", activation arena {mem['arena_bytes'] / 2**20:.0f} MiB for {mem['requested_bytes'] / 2**20:.0f} "
+                      f"MiB of buffers" if mem else ""))
         return plan
+
+    def memory_report(self) -> Dict[str, Dict[str, int]]:
+        """Per built plan (keyed by its input shapes): bytes of the shared activation arena, bytes the same buffers
+        would take without reuse, and the largest amount live at once."""
+        return {str(dict(k)): dict(p.extra["memory"]) for k, p in self._plans.items() if "memory" in p.extra}
 
     def plan_for_shapes(self, shapes: Dict[str, Sequence[int]]):
         """Public access for model classes that write inputs straight into plan buffers."""

@@ -129,3 +129,36 @@ def test_plan_trace_is_a_chrome_trace_document(tmp_path):
     assert all(e["ph"] == "X" and e["dur"] > 0 and e["cat"] == "native" for e in ev)
     assert all(ev[i + 1]["ts"] >= ev[i]["ts"] for i in range(len(ev) - 1))
     assert any(e["name"].startswith("conv") for e in ev)
+
+
+def test_activation_arena_reuses_buffers_without_changing_results():
+    """Static memory plan: with buffer reuse the plan needs less activation memory than the sum of its buffers and
+    returns bit-identical outputs, eagerly and as a CUDA graph, run after run."""
+    from fastdeploy_b200.importer.paddle_import import load_paddle
+    from fastdeploy_b200.models.ppyoloe import build_ppyoloe
+    from fastdeploy_b200.runtime.native_backend import build_plan
+    net = build_ppyoloe("s", image=320, num_classes=16, with_nms=False)
+    m, p = net.serialize()
+    g = load_paddle(m, p)
+    rng = np.random.RandomState(2)
+    shapes = {"image": [4, 3, 320, 320], "scale_factor": [4, 2]}
+    feeds = [{"image": rng.rand(4, 3, 320, 320).astype(np.float32), "scale_factor": np.ones((4, 2), np.float32)}
+             for _ in range(2)]
+    plain = build_plan(g, shapes, "cuda:0", reuse_buffers=False)
+    pooled = build_plan(g, shapes, "cuda:0", reuse_buffers=True)
+    assert "memory" not in plain.extra
+    mem = pooled.extra["memory"]
+    assert 0 < mem["peak_live_bytes"] <= mem["arena_bytes"] < 0.7 * mem["requested_bytes"], mem
+    names = g.output_names()
+    pooled.capture()
+    for rep in range(3):
+        f = feeds[rep % 2]
+        outs = []
+        for plan in (plain, pooled):
+            _feed(plan, f)
+            plan.run()
+            torch.cuda.synchronize()
+            plan.status.check()
+            outs.append([plan.outputs[n].logical().float().cpu().clone() for n in names])
+        for a, b in zip(*outs):
+            assert torch.equal(a, b), rep
