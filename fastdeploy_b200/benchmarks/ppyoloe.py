@@ -65,6 +65,7 @@ def run(ctx: Context, args) -> dict:
     launches0 = model.runtime.gpu_launches
     dev_ms = ctx.time_blocks(lambda n: run_steps(dev_sets, n), args.steps, args.repeats)
     launches = (model.runtime.gpu_launches - launches0) // args.repeats
+    activation_memory = model.runtime.memory_report()
 
     # ---------------- end to end through the public API (pinned host frames in, detections out)
     run_steps(host_sets, warm)
@@ -128,7 +129,7 @@ def run(ctx: Context, args) -> dict:
                      "p99_batch1_ms": round(float(np.percentile(lat, 99)), 3), "iters": len(lat),
                      "what": "rank 0, PPYOLOE.predict on one pinned 1080x1920 frame, wall clock"} if lat else None),
         "gpu_launches": int(launches), "clocks": clocks, "cpu_affinity": ctx.affinity, "impl": "ours",
-        "activation_memory": model.runtime.memory_report(),
+        "activation_memory": activation_memory,
     }
     out.update(extra)
     return out
