@@ -23,6 +23,7 @@ class NativeOption:
     use_cuda_graph: bool = True
     opt_level: int = 2
     max_plans: int = 8                 # shape buckets kept alive
+    batch_buckets: List[int] = field(default_factory=list)   # batch sizes plans are built for: a batch runs padded in the smallest one that holds it
     quant_scales_file: str = ""        # calibrated activation ranges for precision "fp8" (default: quant_scales.json next to the model)
     tp_degree: int = 1
     dp_gpus: List[int] = field(default_factory=list)
@@ -155,6 +156,13 @@ class RuntimeOption:
         """Shape ranges seed the plan cache: a plan is pre-built for ``opt_shape``."""
         self.trt_shapes[tensor_name] = {"min": list(min_shape), "opt": list(opt_shape or min_shape),
                                         "max": list(max_shape or opt_shape or min_shape)}
+
+    def set_batch_buckets(self, buckets) -> None:
+        """Batch sizes the native back end builds plans for (e.g. ``[1, 2, 4, 8, 16, 32]``): a batch runs, padded, in
+        the smallest bucket that holds it, so a service with ragged batches builds a handful of plans instead of
+        one per batch size. The TensorRT back end of the reference covers this with a min / opt / max profile
+        (fastdeploy/runtime/backends/tensorrt/trt_backend.cc:327-339)."""
+        self.native_option.batch_buckets = sorted(int(b) for b in buckets)
 
     def set_trt_input_data(self, tensor_name: str, min_data, opt_data=None, max_data=None):
         self._vendor["trt"].values.setdefault("input_data", {})[tensor_name] = (min_data, opt_data, max_data)

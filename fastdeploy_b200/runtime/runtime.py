@@ -13,7 +13,7 @@ from __future__ import annotations
 import os
 import threading
 import time
-from typing import Any, Dict, List, Optional, Sequence, Union
+from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
 
 import numpy as np
 import torch
@@ -222,6 +222,9 @@ class Runtime:
                 return self._interp.run(feeds)
             with torch.cuda.device(self.device):
                 shapes = {vi.name: list(data[vi.name].shape) for vi in self.graph.inputs}
+                n_valid, bucket = self._batch_bucket(shapes)
+                if bucket is not None:
+                    shapes = {k: [bucket] + v[1:] for k, v in shapes.items()}
                 plan = self._plan_for(shapes)
                 self._last_plan = plan
                 prof = self.option.profiling
@@ -230,7 +233,7 @@ class Runtime:
                     ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
                     ev[0].record()
                 for vi in self.graph.inputs:
-                    self._copy_in(plan.inputs[vi.name], data[vi.name])
+                    self._copy_in(plan.inputs[vi.name], data[vi.name], n_valid if bucket is not None else None)
                 if prof["enable"] and not prof["include_h2d_d2h"]:
                     for _ in range(prof["warmup"]):
                         plan.run()
@@ -244,7 +247,7 @@ class Runtime:
                 else:
                     plan.run()
                 self.gpu_launches += plan.native_kernel_launches
-                outs = self._collect_outputs(plan)
+                outs = self._collect_outputs(plan, (n_valid, bucket) if bucket is not None else None)
                 if self._status_host is None:
                     self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
                     self._status_event = torch.cuda.Event()
@@ -265,17 +268,37 @@ class Runtime:
             self._status_event.synchronize()
             plan.status.check_snapshot(self._status_host, "inference")
 
-    def _copy_in(self, dst, src) -> None:
+    def _batch_bucket(self, shapes: Dict[str, List[int]]):
+        """``(n, bucket)``: with ``native_option.batch_buckets`` set and every input sharing its first dimension
+        ``n``, the smallest bucket that holds ``n`` (``None`` when ``n`` is a bucket itself, exceeds them all, or the
+        inputs do not share a batch dimension). The batch then runs in the bucket's plan: rows past ``n`` of the
+        plan inputs keep what an earlier batch left there, and outputs are cut back to ``n``."""
+        buckets = sorted(self.option.native_option.batch_buckets or [])
+        if not buckets or not shapes:
+            return None, None
+        firsts = {v[0] if len(v) else None for v in shapes.values()}
+        if len(firsts) != 1 or None in firsts:
+            return None, None
+        n = int(next(iter(firsts)))
+        for b in buckets:
+            if b >= n:
+                return n, (int(b) if b != n else None)
+        return n, None
+
+    def _copy_in(self, dst, src, n_valid: Optional[int] = None) -> None:
         if isinstance(src, np.ndarray):
             src = torch.from_numpy(np.ascontiguousarray(src))
         if src.device != dst.t.device:
             src = src.to(dst.t.device, non_blocking=True)
+        view = dst.t if n_valid is None else dst.t[:n_valid]
         if dst.nhwc:
-            dst.t.copy_(src.permute(0, 2, 3, 1))
+            view.copy_(src.permute(0, 2, 3, 1))
         else:
-            dst.t.copy_(src.reshape(dst.t.shape))
+            view.copy_(src.reshape(view.shape))
 
-    def _collect_outputs(self, plan) -> Dict[str, Any]:
+    def _collect_outputs(self, plan, cut: Optional[Tuple[int, int]] = None) -> Dict[str, Any]:
+        """``cut = (n, bucket)``: the plan ran a batch of ``n`` padded to ``bucket``; outputs whose first dimension
+        is the bucket are cut back to ``n`` (detections of the padding images are dropped)."""
         padded = plan.extra.get("padded_nms_outputs", {})
         outs: Dict[str, Any] = {}
         host: Dict[str, np.ndarray] = {}
@@ -285,7 +308,7 @@ class Runtime:
             if vi.name in padded:
                 host[vi.name] = self._to_numpy(t)
             else:
-                outs[vi.name] = t
+                outs[vi.name] = t[:cut[0]] if cut is not None and t.dim() > 0 and t.shape[0] == cut[1] else t
         if host:
             torch.cuda.synchronize(self.device)
             plan.status.check("inference")
@@ -294,6 +317,8 @@ class Runtime:
                 counts = self._to_numpy(plan.outputs[num_name].t) if num_name in plan.outputs else \
                     self._to_numpy(plan.extra["nms"][0].out_num)
                 rows = arr.reshape(len(counts), cap, -1)
+                if cut is not None:
+                    counts, rows = counts[:cut[0]], rows[:cut[0]]
                 outs[name] = np.concatenate([rows[i, :counts[i]] for i in range(len(counts))], 0) \
                     if len(counts) else rows.reshape(0, rows.shape[-1])
         return outs

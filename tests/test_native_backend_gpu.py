@@ -162,3 +162,33 @@ def test_activation_arena_reuses_buffers_without_changing_results():
             outs.append([plan.outputs[n].logical().float().cpu().clone() for n in names])
         for a, b in zip(*outs):
             assert torch.equal(a, b), rep
+
+
+def test_batch_buckets_pad_to_a_built_plan_and_cut_the_outputs_back(tmp_path):
+    """Ragged batches run in the smallest bucket plan: one plan for batches 3 and 4, the same answers as exact plans."""
+    import fastdeploy_b200 as fd
+    from fastdeploy_b200.models.ppyoloe import write_ppyoloe
+    paths = write_ppyoloe(str(tmp_path), "tiny", image=128, num_classes=8, score_threshold=0.005)
+    rng = np.random.RandomState(4)
+
+    def runtime(buckets):
+        opt = fd.RuntimeOption()
+        opt.use_gpu(0)
+        opt.set_model_path(paths["model"], paths["params"])
+        if buckets:
+            opt.set_batch_buckets(buckets)
+        return fd.Runtime(opt)
+    bucketed = runtime([1, 2, 4, 8])
+    names = [vi.name for vi in bucketed.graph.outputs]
+    for n in (3, 4, 1, 3):
+        img = rng.rand(4, 3, 128, 128).astype(np.float32)
+        part = bucketed.infer({"image": img[:n], "scale_factor": np.ones((n, 2), np.float32)})
+        if n == 1:
+            assert part[1].shape == (1,)
+            continue
+        # the same images as the head of a full bucket: every image's detections are its own
+        full = bucketed.infer({"image": img, "scale_factor": np.ones((4, 2), np.float32)})
+        counts = part[1].reshape(-1)
+        assert counts.shape == (n,) and np.array_equal(counts, full[1].reshape(-1)[:n]), names
+        assert part[0].shape[0] == counts.sum() and np.array_equal(part[0], full[0][:counts.sum()])
+    assert sorted(dict(k)["image"][0] for k in bucketed._plans) == [1, 4]
