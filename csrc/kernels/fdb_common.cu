@@ -134,3 +134,13 @@ FDB_API int fdb_op_launch(void* op, void* stream) {
 FDB_API void fdb_op_destroy(void* op) { delete static_cast<fdb::Op*>(op); }
 
 FDB_API int fdb_sm_count() { return fdb::sm_count(); }
+
+// Blocking copy of device memory to the host by raw address (plan export reads allocator blocks that no tensor
+// object covers as a whole).
+FDB_API int fdb_copy_to_host(void* dst, const void* src, unsigned long long bytes) {
+  if (cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost) != cudaSuccess) {
+    fdb::set_error(std::string("fdb_copy_to_host: ") + cudaGetErrorString(cudaGetLastError()));
+    return -1;
+  }
+  return 0;
+}

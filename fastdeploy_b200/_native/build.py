@@ -222,7 +222,32 @@ def build_capi(verbose: bool = False, force: bool = False) -> str:
     return CAPI_LIB
 
 
+RUNNER_LIB = os.path.join(HERE, "libfdb200_runner.so")
+RUNNER_TOOL = os.path.join(HERE, "fdplan_run")
+
+
+def build_runner(verbose: bool = False, force: bool = False) -> str:
+    """Plan runner: a library and a command-line tool that replay an exported plan without Python."""
+    src = os.path.join(CSRC, "runner", "plan_runner.cu")
+    if not os.path.exists(src):
+        return ""
+    nvcc = _nvcc()
+    common = ["-O2", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static", "-ldl"]
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    for out, extra in ((RUNNER_LIB, ["-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]),
+                       (RUNNER_TOOL, ["-DFDPLAN_MAIN"])):
+        if force or _newer(src, out, []):
+            rc, log_text = _compile([nvcc] + common + extra + ["-o", out, src],
+                                    os.path.join(OBJ_DIR, os.path.basename(out) + ".log"))
+            if verbose or rc != 0:
+                print(log_text)
+            if rc != 0:
+                raise RuntimeError(f"building {os.path.basename(out)} failed")
+    return RUNNER_LIB
+
+
 def build_all(verbose: bool = False, force: bool = False) -> None:
+    build_runner(verbose=verbose, force=force)
     build_kernels(verbose=verbose, force=force)
     build_cpu(verbose=verbose, force=force)
     build_capi(verbose=verbose, force=force)

@@ -47,6 +47,9 @@ class NativeOp:
         self.handle = ctypes.c_void_p(handle)
         self.keep = keep
         self.name = name
+        # (creation function, kind argument or None, descriptor): what a plan file needs to re-create this op in a
+        # process without Python (runtime/plan_file.py); filled in by the wrappers that build the descriptor
+        self.create: Optional[tuple] = None
 
     def launch(self, stream: Optional[int] = None) -> None:
         s = current_stream_ptr() if stream is None else stream

@@ -139,6 +139,7 @@ class ConvGemm(NativeOp):
         assert w_packed.dtype == x.dtype
         handle = _lib().fdb_conv_gemm_create(ctypes.byref(d))
         super().__init__(handle, [x, w_packed, y, bias, residual, self.status], name)
+        self.create = ("fdb_conv_gemm_create", None, d)
         es_in, es_out = x.element_size(), y.element_size()
         # shape record for profilers: algorithmic FLOPs and bytes of this launch
         self.meta = dict(in_shape=(n, h, w_, cin), cin_logical=cin, out_hw=tuple(out_hw), cout=cout,

@@ -66,7 +66,9 @@ def _make(kind: int, ptrs, ints, floats=(), name="generic") -> NativeOp:
         d.i[k] = int(v)
     for k, v in enumerate(floats):
         d.f[k] = float(v)
-    return NativeOp(_lib().fdb_generic_create(kind, ctypes.byref(d)), list(ptrs), name)
+    op = NativeOp(_lib().fdb_generic_create(kind, ctypes.byref(d)), list(ptrs), name)
+    op.create = ("fdb_generic_create", kind, d)
+    return op
 
 
 def coalesce(shape: Sequence[int], strides: Sequence[Sequence[int]]) -> Tuple[List[int], List[List[int]]]:

@@ -40,7 +40,9 @@ def make_simple(kind: int, ptrs: Sequence[Optional[torch.Tensor]], ints: Sequenc
         d.i[k] = int(v)
     for k, v in enumerate(floats):
         d.f[k] = float(v)
-    return NativeOp(_lib().fdb_simple_create(kind, ctypes.byref(d)), list(ptrs), name)
+    op = NativeOp(_lib().fdb_simple_create(kind, ctypes.byref(d)), list(ptrs), name)
+    op.create = ("fdb_simple_create", kind, d)
+    return op
 
 
 def _bf(t: torch.Tensor) -> int:
@@ -169,7 +171,9 @@ def _make_fused(kind: int, ptrs, ints, floats=(), name="fused") -> NativeOp:
         d.i[k] = int(v)
     for k, v in enumerate(floats):
         d.f[k] = float(v)
-    return NativeOp(_fused_lib().fdb_fused_create(kind, ctypes.byref(d)), list(ptrs), name)
+    op = NativeOp(_fused_lib().fdb_fused_create(kind, ctypes.byref(d)), list(ptrs), name)
+    op.create = ("fdb_fused_create", kind, d)
+    return op
 
 
 def gap_splits_v2(hw: int, n: int, c: int, sms: int = 148) -> int:

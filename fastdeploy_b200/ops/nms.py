@@ -96,6 +96,7 @@ class MulticlassNMS:
         self.launches = 2 + (1 if self.scores_t is not None else 0) + (2 if self.tau is not None else 0)
         self.op = NativeOp(_lib().fdb_nms_create(ctypes.byref(d)), [boxes, scores, self], "multiclass_nms")
         self.op.keep = [boxes, scores]  # avoid a reference cycle through self
+        self.op.create = ("fdb_nms_create", None, d)
 
     def launch(self, stream: Optional[int] = None) -> None:
         self.op.launch(stream)

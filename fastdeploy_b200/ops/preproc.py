@@ -82,3 +82,4 @@ class Preprocess(NativeOp):
         for c in range(3):
             d.alpha[c], d.beta[c], d.pad[c] = alpha[c], beta[c], pad_value[c]
         super().__init__(_lib().fdb_preproc_create(ctypes.byref(d)), [src, meta, dst], "preprocess")
+        self.create = ("fdb_preproc_create", None, d)

@@ -65,4 +65,5 @@ class StemConv(NativeOp):
         b = np.zeros(COUT, dtype=np.float32) if bias is None else np.asarray(bias, dtype=np.float32).reshape(COUT)
         ctypes.memmove(d.bias, np.ascontiguousarray(b).ctypes.data, b.nbytes)
         super().__init__(lib.fdb_stem_conv_create(ctypes.byref(d)), [x, y], name)
+        self.create = ("fdb_stem_conv_create", None, d)
         self.out_hw = (ho, wo)

@@ -43,7 +43,9 @@ def _make(kind, ptrs, ints, floats=(), name="tf", keep=None) -> NativeOp:
         d.i[k] = int(v)
     for k, v in enumerate(floats):
         d.f[k] = float(v)
-    return NativeOp(_lib().fdb_transformer_create(kind, ctypes.byref(d)), list(ptrs) + list(keep or []), name)
+    op = NativeOp(_lib().fdb_transformer_create(kind, ctypes.byref(d)), list(ptrs) + list(keep or []), name)
+    op.create = ("fdb_transformer_create", kind, d)
+    return op
 
 
 def _bf(t) -> int:
@@ -69,9 +71,11 @@ def embed_layernorm(ids: List[Optional[torch.Tensor]], tables: List[torch.Tensor
                        dtype=torch.int64, device=dev)
     tbp = torch.tensor([t.data_ptr() for t in tables] + [0] * (4 - len(tables)), dtype=torch.int64, device=dev)
     gb = torch.cat([gamma.float().reshape(-1), beta.float().reshape(-1)]).contiguous().to(dev)
-    return _make(K_EMBED_LN, [idp, tbp, y, gb], [rows, c, len(tables), seq, _bf(y), y_ld or c] +
-                 [int(t.shape[0]) for t in tables] + [0] * (4 - len(tables)), [eps],
-                 "embed_layernorm", keep=list(ids) + list(tables))
+    op = _make(K_EMBED_LN, [idp, tbp, y, gb], [rows, c, len(tables), seq, _bf(y), y_ld or c] +
+               [int(t.shape[0]) for t in tables] + [0] * (4 - len(tables)), [eps],
+               "embed_layernorm", keep=list(ids) + list(tables))
+    op.pointer_tables = [idp, tbp]        # device arrays of device pointers (a plan file relocates their elements)
+    return op
 
 
 def masked_softmax(scores: torch.Tensor, mask: Optional[torch.Tensor], *, b: int, h: int, s: int, sk: int, ld: int,
@@ -128,8 +132,10 @@ def fused_attention_op(q, k, vt, out, mask, *, b, heads, s, sk, d, skp, scale, m
             assert t.dtype == torch.int32 and t.is_contiguous() and t.numel() >= b and t.device == q.device, name
             setattr(dd, name, t.data_ptr())
     dd.total_rows = int(total_rows)
-    return NativeOp(lib.fdb_attention_create(ctypes.byref(dd)), [q, k, vt, out, mask, status, seq_len, seq_start],
-                    "attention")
+    op = NativeOp(lib.fdb_attention_create(ctypes.byref(dd)), [q, k, vt, out, mask, status, seq_len, seq_start],
+                  "attention")
+    op.create = ("fdb_attention_create", None, dd)
+    return op
 
 
 class Attention:
