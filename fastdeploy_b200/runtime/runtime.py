@@ -174,6 +174,15 @@ class Runtime:
                       f"MiB of buffers" if mem else ""))
         return plan
 
+    def export_plan(self, path: str, shapes: Dict[str, Sequence[int]]) -> Dict[str, Any]:
+        """Builds (or takes) the plan for ``shapes`` and writes it as a plan file that ``libfdb200_runner.so`` /
+        ``fdplan_run`` replay without Python (runtime/plan_file.py). Returns the export summary."""
+        from .plan_file import export_plan
+        if not self.on_gpu:
+            raise RuntimeError("plan files are written from GPU plans")
+        with torch.cuda.device(self.device):
+            return export_plan(self._plan_for({k: list(v) for k, v in shapes.items()}), path)
+
     def memory_report(self) -> Dict[str, Dict[str, int]]:
         """Per built plan (keyed by its input shapes): bytes of the shared activation arena, bytes the same buffers
         would take without reuse, and the largest amount live at once."""

@@ -184,9 +184,29 @@ def cmd_benchmark(args) -> int:
     return 0
 
 
+def cmd_export_plan(args) -> int:
+    """``fastdeploy export_plan --model dir --input_shape_dict "{...}" --save_dir out``: builds the GPU plan for the
+    given shapes and writes ``out/model.fdplan`` for the C++ runner (``fdplan_run``, ``libfdb200_runner.so``)."""
+    import fastdeploy_b200 as fd
+    from ..core.types import ModelFormat
+    model, params = _resolve(args.model)
+    opt = fd.RuntimeOption()
+    opt.set_model_path(model, params, ModelFormat.ONNX if model.endswith(".onnx") else ModelFormat.PADDLE)
+    opt.use_gpu(args.device_id)
+    rt = fd.Runtime(opt)
+    shapes = ast.literal_eval(args.input_shape_dict) if args.input_shape_dict else None
+    if not shapes:
+        raise SystemExit("export_plan needs --input_shape_dict with a static shape for every input")
+    os.makedirs(args.save_dir, exist_ok=True)
+    out = os.path.join(args.save_dir, "model.fdplan")
+    info = rt.export_plan(out, shapes)
+    print(json.dumps(dict(info, path=out)))
+    return 0
+
+
 def argsparser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(prog="fastdeploy", description=__doc__.split("\n\n")[0])
-    p.add_argument("tools", choices=["compress", "convert", "simple_serving", "benchmark"])
+    p.add_argument("tools", choices=["compress", "convert", "simple_serving", "benchmark", "export_plan"])
     p.add_argument("--config_path", default=None, help="compress: model directory (kept for command compatibility)")
     p.add_argument("--method", default="PTQ", help="compress: PTQ (post-training calibration)")
     p.add_argument("--save_dir", default="./output", help="directory to save the result")
@@ -214,4 +234,4 @@ def argsparser() -> argparse.ArgumentParser:
 def main(argv: Optional[List[str]] = None) -> int:
     args = argsparser().parse_args(argv)
     return {"compress": cmd_compress, "convert": cmd_convert, "simple_serving": cmd_simple_serving,
-            "benchmark": cmd_benchmark}[args.tools](args)
+            "benchmark": cmd_benchmark, "export_plan": cmd_export_plan}[args.tools](args)
