@@ -47,6 +47,7 @@ def main(argv=None) -> int:
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--s", type=int, default=257)
     ap.add_argument("--d", type=int, default=80)
+    ap.add_argument("--varlen", action="store_true", help="attention: packed sequences with lengths uniform in 16..s")
     a = ap.parse_args(argv)
     dt = torch.float16 if a.dtype == "fp16" else torch.bfloat16
     dev = "cuda"
@@ -65,6 +66,25 @@ def main(argv=None) -> int:
                       halo_mode=a.halo, block_n=a.block_n, y_tma_mode=a.y_tma, pair_mode=a.pair)
         flops = 2.0 * n * ho * ho * cout * cin * k * k
         nbytes = x.numel() * 2 + y.numel() * 2 + w.numel() * 2
+    elif a.kind == "attention" and a.varlen:
+        # padding-free batch: b sequences back to back, the kernel reads starts and lengths from device memory
+        from ..ops.transformer import PackedAttention, pack_offsets
+        b, h, s, d = a.b, a.heads, a.s, a.d
+        g = torch.Generator().manual_seed(0)
+        lens = torch.randint(16, s + 1, (b,), generator=g).tolist()
+        starts, rows = pack_offsets(lens)
+        rows = (rows + 127) // 128 * 128
+        qkv = (torch.randn(rows, 3 * h * d, device=dev) * 0.5).to(dt)
+        o = torch.zeros(rows, h * d, device=dev, dtype=dt)
+        att = PackedAttention(qkv[:, :h * d], qkv[:, h * d:2 * h * d], qkv[:, 2 * h * d:], o, heads=h, scale=d ** -0.5,
+                              max_len=s, seq_start=torch.tensor(starts, dtype=torch.int32, device=dev),
+                              seq_len=torch.tensor(lens, dtype=torch.int32, device=dev))
+        att.ops[0].launch()
+        op = att.ops[1]
+        op.status = att.status
+        op.info = lambda: {"kernel": "attention_sm100", "packed_rows": rows, "tokens": int(sum(lens))}
+        flops = 4.0 * h * d * sum(n * n for n in lens)
+        nbytes = (qkv.numel() + o.numel()) * 2
     elif a.kind == "attention":
         from ..ops.transformer import Attention
         b, h, s, d = a.b, a.heads, a.s, a.d

@@ -46,6 +46,28 @@ def build_model(args):
         opt.set_model_path(path, "", fd.ModelFormat.ONNX)
         rt = fd.Runtime(opt)
         return rt, {rt.graph.inputs[0].name: [args.batch, 3, args.image, args.image]}
+    if args.model == "ernie":
+        # ERNIE-3.0-base sequence classification, bf16; --packed runs the padding-free plan on sequences with lengths
+        # uniform in 16..512 (the bucket that holds them), otherwise the plan padded to 512 tokens
+        import numpy as np
+        from ..models.ernie import SIZES, write_ernie
+        if not os.path.exists(os.path.join(d, "model.pdiparams")):
+            write_ernie(d, args.variant if args.variant in SIZES else "base", "seq_cls", seed=0, vocab=False)
+        opt.native_option.precision = "bf16"
+        rt = fd.Runtime(_opt_with_model(opt, os.path.join(d, "model.pdmodel"), os.path.join(d, "model.pdiparams")))
+        names = [vi.name for vi in rt.graph.inputs]
+        if not args.packed:
+            return rt, {n: [args.batch, 512] for n in names}
+        from ..text.packed import PackedEncoder
+        rng = np.random.default_rng(99)
+        lens = rng.integers(16, 513, args.batch)
+        seqs = [(rng.integers(1, 40000, n), np.zeros(n, np.int64)) for n in lens]
+        enc = PackedEncoder(rt, max_tokens=args.batch * 512, max_seqs=args.batch, max_len=512,
+                            token_buckets=range(2048, args.batch * 512 + 1, 2048))
+        bk, feeds, _, _ = enc.pack(seqs)
+        enc.launch(bk, feeds)
+        print(f"packed: {int(lens.sum())} tokens of {args.batch} sequences in a bucket of {bk.rows} rows")
+        return rt, bk.plan
     raise SystemExit(f"unknown model {args.model}")
 
 
@@ -64,7 +86,8 @@ def conv_flops(meta) -> float:
 def main(argv=None) -> int:
     import torch
     ap = argparse.ArgumentParser()
-    ap.add_argument("--model", default="ppyoloe", choices=["ppyoloe", "resnet50"])
+    ap.add_argument("--model", default="ppyoloe", choices=["ppyoloe", "resnet50", "ernie"])
+    ap.add_argument("--packed", action="store_true", help="ernie: the padding-free plan instead of the padded one")
     ap.add_argument("--variant", default="l")
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--image", type=int, default=640)
@@ -78,7 +101,7 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
 
     rt, shapes = build_model(a)
-    plan = rt.plan_for_shapes(shapes)
+    plan = rt.plan_for_shapes(shapes) if isinstance(shapes, dict) else shapes
     dev = rt.device
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     rows = []
@@ -135,6 +158,15 @@ def main(argv=None) -> int:
                          f'{r["ms"]:.4f} | {r["tflops"]:.0f} | {frac} | {r["bytes"] / r["ms"] / 1e6:.0f} |')
         else:
             lines.append(f'| {r["idx"]} | {r["name"]} |  | {r["kind"]} |  |  | {r["ms"]:.4f} |  |  |  |')
+    kinds = {}
+    for r in rows:
+        k = r["name"].split(":")[0].split("(")[0]
+        kinds.setdefault(k, [0, 0.0])
+        kinds[k][0] += 1
+        kinds[k][1] += r["ms"]
+    lines += ["", "| kind | steps | ms | share |", "|---|---|---|---|"]
+    for k, (cnt, ms) in sorted(kinds.items(), key=lambda kv: -kv[1][1]):
+        lines.append(f"| {k} | {cnt} | {ms:.3f} | {100 * ms / total:.1f} % |")
     text = "\n".join(lines)
     print(text)
     if a.out:
