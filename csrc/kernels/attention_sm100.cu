@@ -44,6 +44,8 @@ struct AttnDesc {
 struct AttnParams {
   const float* mask; uint8_t* out; int* status;
   const int* seq_len; const int* seq_start;
+  const int* key_len;        // per item, derived from the mask by mask_prefix_kernel: >= 1 when the mask row is "that
+                             // many zeros, then only entries <= -1000" (a key-padding mask), else -1
   int total_rows;
   int H, S, Sk, D, o_ld;
   int sk_pad;                // keys rounded up: multiple of 16 (<= 256) or of 32 (> 256)
@@ -70,6 +72,28 @@ __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// One warp per batch item: key_len[b] = n when mask row b is n zeros followed only by entries <= -1000 (n >= 1),
+// else -1. Such a row is a key-padding mask, and the attention kernel then works from the count alone.
+__global__ void mask_prefix_kernel(const float* __restrict__ mask, long long m_b, int B, int Sk, int* __restrict__ key_len) {
+  const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (b >= B) return;
+  const float* row = mask + b * m_b;
+  int first_masked = Sk;          // first index whose entry is not zero
+  bool ok = true;
+  for (int c = lane; c < Sk; c += 32) {
+    const float v = __ldg(row + c);
+    if (v != 0.f) first_masked = min(first_masked, c);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) first_masked = min(first_masked, __shfl_xor_sync(0xffffffffu, first_masked, o));
+  for (int c = lane; c < Sk; c += 32) {
+    const float v = __ldg(row + c);
+    if (c >= first_masked && !(v <= -1000.f)) ok = false;
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  if (lane == 0) key_len[b] = (ok && first_masked >= 1) ? first_masked : -1;
 }
 
 template <bool BF16>
@@ -119,6 +143,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   int len = p.Sk, q_row0 = b * p.S, k_row0 = b * p.Sk, vt_x0 = 0, vt_y0 = (b * p.H + h) * p.D;
   bool valid = true;
   if (p.seq_len != nullptr) len = max(0, min(__ldg(p.seq_len + b), p.Sk));
+  // A key-padding mask is the same as a key count: masked keys get weight exp(-1000 or less) = 0 exactly in fp32,
+  // so they are left out (no mask loads, shorter loops); every query row is still computed.
+  bool mask_as_len = false;
+  if (p.key_len != nullptr) {
+    const int kl = __ldg(p.key_len + b);
+    if (kl >= 1) { len = min(kl, p.Sk); mask_as_len = true; }
+  }
   if (p.seq_start != nullptr) {
     const int st = __ldg(p.seq_start + b);
     valid = st >= 0 && (st & 7) == 0 && st + len <= p.total_rows;
@@ -133,15 +164,17 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const bool run = valid && len > 0;
 
   if (run && tid == 0) {
-    // K: d_chunks x k_loads boxes of [k_box rows x 64 cols]; V^T: k_chunks boxes of [D rows x 64 cols]
-    const uint32_t bytes = static_cast<uint32_t>(p.d_chunks) * k_chunk_bytes +
-                           static_cast<uint32_t>(p.k_chunks) * static_cast<uint32_t>(p.D) * 128u;
+    // K: d_chunks x k_loads boxes of [k_box rows x 64 cols]; V^T: k_chunks boxes of [D rows x 64 cols]. Only the
+    // boxes that hold keys of this item are fetched.
+    const int k_loads = sk_pad > p.k_box ? p.k_loads : 1;
+    const uint32_t bytes = static_cast<uint32_t>(p.d_chunks * k_loads) * static_cast<uint32_t>(p.k_box) * 128u +
+                           static_cast<uint32_t>(k_chunks) * static_cast<uint32_t>(p.D) * 128u;
     mbar_arrive_expect_tx(bar_kv, bytes);
     for (int c = 0; c < p.d_chunks; ++c)
-      for (int l = 0; l < p.k_loads; ++l)
+      for (int l = 0; l < k_loads; ++l)
         tma_load_2d(sK + c * k_chunk_bytes + static_cast<uint32_t>(l * p.k_box) * 128u, &tm_k, bar_kv, col0 + c * 64,
                     k_row0 + l * p.k_box);
-    for (int j = 0; j < p.k_chunks; ++j)
+    for (int j = 0; j < k_chunks; ++j)
       tma_load_2d(sVT + j * vt_chunk_bytes, &tm_vt, bar_kv, vt_x0 + j * 64, vt_y0);
     mbar_arrive_expect_tx(bar_q, static_cast<uint32_t>(p.d_chunks) * q_chunk_bytes);
     for (int c = 0; c < p.d_chunks; ++c) tma_load_2d(sQ + c * q_chunk_bytes, &tm_q, bar_q, col0 + c * 64, q_row0);
@@ -180,7 +213,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const float* mrow = p.mask != nullptr ? p.mask + b * p.m_b + static_cast<long long>(row < S_b ? row : 0) * p.m_s : nullptr;
     // Warps whose 32 rows all lie beyond the last query take part in the barriers only.
     const bool warp_active = qt * 128 + (warp & 3) * 32 < S_b;
-    const bool masked = mrow != nullptr;
+    const bool masked = mrow != nullptr && !mask_as_len;
     const int nblk = (sk_pad + 31) / 32;
     constexpr float kLog2e = 1.4426950408889634f;
     uint32_t va[32], vb[32];
@@ -372,7 +405,12 @@ struct AttnOp : Op {
   AttnParams prm;
   int grid = 0, smem = 0;
   bool bf16 = true;
+  int* key_len = nullptr;     // owned: filled from the mask before every launch (the mask is an input of the step)
+  int batch = 0;
+  ~AttnOp() override { if (key_len != nullptr) cudaFree(key_len); }
   int launch(cudaStream_t s) override {
+    if (key_len != nullptr)
+      mask_prefix_kernel<<<(batch + 7) / 8, 256, 0, s>>>(prm.mask, prm.m_b, batch, prm.Sk, key_len);
     if (bf16) attention_kernel<true><<<grid, kAttnThreads, smem, s>>>(tq, tk, tvt, prm);
     else attention_kernel<false><<<grid, kAttnThreads, smem, s>>>(tq, tk, tvt, prm);
     const cudaError_t e = cudaGetLastError();
@@ -433,6 +471,16 @@ FDB_API void* fdb_attention_create(const AttnDesc* d) {
   while (cols < std::max((p.sk_pad + 31) / 32 * 32, (d->D + 31) / 32 * 32)) cols *= 2;
   p.tmem_cols = cols;
   p.m_b = d->m_b; p.m_s = d->m_s; p.scale = d->scale;
+  p.key_len = nullptr;
+  op->batch = d->B;
+  if (d->mask != nullptr && d->m_s == 0 && d->seq_len == nullptr) {
+    // one mask row per item: worth a look whether it is a key-padding mask
+    if (cudaMalloc(&op->key_len, sizeof(int) * static_cast<size_t>(d->B)) != cudaSuccess) {
+      cudaGetLastError();
+      op->key_len = nullptr;
+    }
+    p.key_len = op->key_len;
+  }
   const uint32_t k_bytes = static_cast<uint32_t>(p.d_chunks) * p.sk_pad * 128u;
   const uint32_t vt_bytes = static_cast<uint32_t>(p.k_chunks) * d->D * 128u;
   const uint32_t q_bytes = static_cast<uint32_t>(p.d_chunks) * 16384u;

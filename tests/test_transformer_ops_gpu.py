@@ -148,3 +148,35 @@ def test_packed_attention_reports_a_misaligned_start():
     torch.cuda.synchronize()
     with pytest.raises(RuntimeError):
         att.status.check()
+
+
+@pytest.mark.parametrize("kind", ["prefix", "holes", "soft", "all_masked_item"])
+def test_attention_mask_kinds(kind):
+    """A key-padding mask (zeros, then <= -1000) runs from its key count; any other mask is added to the scores.
+    Both give softmax(q k^T * scale + mask) v for every query row, padded ones included."""
+    from fastdeploy_b200.ops.transformer import Attention
+    b, h, s, d = 3, 4, 200, 64
+    torch.manual_seed(9)
+    qkv = (torch.randn(b, s, 3 * h * d, device="cuda") * 0.5).half()
+    q, k, v = qkv[..., :h * d], qkv[..., h * d:2 * h * d], qkv[..., 2 * h * d:]
+    mask = torch.zeros(b, 1, 1, s, device="cuda")
+    mask[0, ..., 150:] = -1e4
+    mask[1, ..., 7:] = -1e4
+    if kind == "holes":
+        mask[2, ..., 50:60] = -1e4                  # not a prefix: the general path
+    elif kind == "soft":
+        mask[2, ..., 100:] = -3.0                   # finite bias: must be added, not dropped
+    elif kind == "all_masked_item":
+        mask[2] = -1e4                              # no key left: uniform weights, as the formula gives
+    out = torch.zeros(b, s, h * d, device="cuda", dtype=torch.float16)
+    att = Attention(q, k, v, out, heads=h, scale=1 / math.sqrt(d), mask=mask)
+    assert att.fused
+    for _ in range(2):                              # the key counts are recomputed at every launch
+        att.launch()
+    att.status.check()
+
+    def split(t):
+        return t.float().reshape(b, s, h, d).permute(0, 2, 1, 3)
+    sc = split(q) @ split(k).transpose(-1, -2) / math.sqrt(d) + mask
+    ref = (torch.softmax(sc, -1) @ split(v)).permute(0, 2, 1, 3).reshape(b, s, h * d)
+    assert (out.float() - ref).abs().max().item() < 6e-3
