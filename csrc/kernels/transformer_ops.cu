@@ -122,7 +122,8 @@ __device__ __forceinline__ uint2 pack8_e4m3(const float (&f)[8]) {
 
 // OUT8: the normalised row is multiplied by out_scale (the reciprocal of the consumer GEMM's activation
 // scale) and stored as e4m3, one byte per element (y_ld counts bytes then).
-template <bool BF16, bool OUT8>
+// NK = 256-column chunks a lane holds (C <= NK * 256): sized to the row so that short rows keep few registers.
+template <bool BF16, bool OUT8, int NK>
 __global__ void __launch_bounds__(256) layernorm_reg_kernel(const uint8_t* __restrict__ x, uint8_t* __restrict__ y,
                                                             const float* __restrict__ gamma, const float* __restrict__ beta,
                                                             long long rows, int C, int x_ld, int y_ld, float eps,
@@ -131,23 +132,23 @@ __global__ void __launch_bounds__(256) layernorm_reg_kernel(const uint8_t* __res
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
   const uint8_t* xr = x + row * x_ld * 2;
-  uint4 raw[8];
+  uint4 raw[NK];
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
+  for (int k = 0; k < NK; ++k) {
     const int c = lane * 8 + k * 256;
     raw[k] = c < C ? __ldg(reinterpret_cast<const uint4*>(xr + c * 2)) : make_uint4(0, 0, 0, 0);
   }
-  float v[8][8];
+  float v[NK][8];
   float s = 0.f, ss = 0.f;
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
+  for (int k = 0; k < NK; ++k) {
     unpack8<BF16>(raw[k], v[k]);
 #pragma unroll
     for (int j = 0; j < 8; ++j) s += v[k][j];
   }
   const float mean = warp_sum(s) / C;
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
+  for (int k = 0; k < NK; ++k) {
     if (lane * 8 + k * 256 < C) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) { const float d = v[k][j] - mean; ss += d * d; }
@@ -156,7 +157,7 @@ __global__ void __launch_bounds__(256) layernorm_reg_kernel(const uint8_t* __res
   const float rstd = rsqrtf(warp_sum(ss) / C + eps);
   uint8_t* yr = y + row * y_ld * (OUT8 ? 1 : 2);
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
+  for (int k = 0; k < NK; ++k) {
     const int c = lane * 8 + k * 256;
     if (c < C) {
       float g[8], b[8];
@@ -364,10 +365,23 @@ FDB_API void* fdb_transformer_create(int kind, const TfDesc* dp) {
       op->fn = [=](cudaStream_t s) {
         const int grid = static_cast<int>((rows * 32 + 255) / 256);
         const bool regs = C <= 2048 && (reinterpret_cast<uintptr_t>(d.p[2]) % 16 == 0) && (reinterpret_cast<uintptr_t>(d.p[3]) % 16 == 0);
-        if (out8 && bf) layernorm_reg_kernel<true, true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps, out_scale);
-        else if (out8) layernorm_reg_kernel<false, true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps, out_scale);
-        else if (regs && bf) layernorm_reg_kernel<true, false><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps, 1.f);
-        else if (regs) layernorm_reg_kernel<false, false><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps, 1.f);
+        if (out8 || regs) {
+          const int nk = (C + 255) / 256;
+#define FDB_LN_LAUNCH(NK)                                                                                              \
+  do {                                                                                                                 \
+    if (out8 && bf) layernorm_reg_kernel<true, true, NK><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps, out_scale); \
+    else if (out8) layernorm_reg_kernel<false, true, NK><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps, out_scale); \
+    else if (bf) layernorm_reg_kernel<true, false, NK><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps, 1.f); \
+    else layernorm_reg_kernel<false, false, NK><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps, 1.f); \
+  } while (0)
+          if (nk <= 1) FDB_LN_LAUNCH(1);
+          else if (nk == 2) FDB_LN_LAUNCH(2);
+          else if (nk == 3) FDB_LN_LAUNCH(3);
+          else if (nk == 4) FDB_LN_LAUNCH(4);
+          else if (nk <= 6) FDB_LN_LAUNCH(6);
+          else FDB_LN_LAUNCH(8);
+#undef FDB_LN_LAUNCH
+        }
         else if (bf) layernorm_kernel<true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps);
         else layernorm_kernel<false><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (uint8_t*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], rows, C, x_ld, y_ld, eps);
         FDB_TF_CHECK();

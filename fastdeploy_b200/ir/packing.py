@@ -118,6 +118,9 @@ def pack_graph(graph: Graph, max_len: int) -> Graph:
     for n in g.nodes:
         if n.op in ("PackedAttention", "EmbedLayerNorm") or n.op in ROW_WISE:
             continue
+        if n.op == "Slice" and len(n.inputs) >= 4 and n.inputs[3] in g.initializers and \
+                np.asarray(g.initializers[n.inputs[3]]).reshape(-1).tolist() in ([-1], [2]):
+            continue                      # a slice of the channels (the stacked q / k / v projection) keeps rows apart
         raise PackingError(f"operator {n.op} ({n.name}) is not known to treat token rows independently")
     g.metadata["packed"] = {"max_len": int(max_len), "position_ids": bool(swapped)}
     return g

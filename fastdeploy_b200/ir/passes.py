@@ -547,6 +547,55 @@ def fuse_gemm(graph: Graph, info: Optional[ShapeInfo] = None) -> int:
     return changed
 
 
+def fuse_qkv_gemms(graph: Graph) -> int:
+    """The query / key / value projections of an attention layer are three linear layers of the same input: one
+    FusedGemm with the weights stacked along the output dimension, and three Slice views of its output, reads the
+    activations once and gives the tensor cores a wider tile. Only projections whose sole reader is one
+    (Packed)Attention node are merged."""
+    changed = 0
+    cons = graph.consumers()
+    prod = graph.producers()
+    for att in [n for n in graph.nodes if n.op in ("Attention", "PackedAttention")]:
+        gemms = [prod.get(nm) for nm in att.inputs[:3]]
+        if any(g is None or g.op != "FusedGemm" or len(g.inputs) != 3 for g in gemms) or len({id(g) for g in gemms}) != 3:
+            continue
+        x = gemms[0].inputs[0]
+        if any(g.inputs[0] != x or g.attrs != gemms[0].attrs or g.attr("activation", "none") != "none" or
+               len(cons.get(g.outputs[0], [])) != 1 or g.outputs[0] in graph.output_names() for g in gemms):
+            continue
+        ws = [graph.initializers.get(g.inputs[1]) for g in gemms]
+        if any(w is None or w.ndim != 2 or w.shape[1] != ws[0].shape[1] or w.shape[0] % 8 for w in ws):
+            continue
+        bs = []
+        for g, w in zip(gemms, ws):
+            b = graph.initializers.get(g.inputs[2]) if g.inputs[2] else np.zeros(w.shape[0], np.float32)
+            if b is None:
+                break
+            bs.append(np.asarray(b, np.float32).reshape(-1))
+        if len(bs) != 3:
+            continue
+        w_all = graph.const(np.ascontiguousarray(np.concatenate(ws, 0)), prefix="w_qkv")
+        b_all = graph.const(np.concatenate(bs, 0), prefix="b_qkv")
+        fused_out = graph.unique("qkv")
+        first = min(graph.nodes.index(g) for g in gemms)
+        fused = Node("FusedGemm", [x, w_all, b_all], [fused_out], dict(gemms[0].attrs), graph.unique("n_FusedGemm_qkv"),
+                     "fdb")
+        slices, at = [], 0
+        for g, w in zip(gemms, ws):
+            st = graph.const(np.asarray([at], np.int64), prefix="qkv_start")
+            en = graph.const(np.asarray([at + w.shape[0]], np.int64), prefix="qkv_end")
+            ax = graph.const(np.asarray([-1], np.int64), prefix="qkv_axis")
+            slices.append(Node("Slice", [fused_out, st, en, ax], [g.outputs[0]], {}, graph.unique("n_Slice_qkv")))
+            at += w.shape[0]
+        for g in gemms:
+            graph.nodes.remove(g)
+        graph.nodes[first:first] = [fused] + slices
+        changed += 1
+    if changed:
+        graph.toposort()
+    return changed
+
+
 # --------------------------------------------------------------------------- transformer blocks
 def fuse_attention(graph: Graph, info: ShapeInfo) -> int:
     """Recognises multi-head self-attention written with Reshape/Transpose/MatMul/Softmax:
@@ -746,6 +795,7 @@ def optimize(graph: Graph, input_shapes: Optional[Dict[str, Sequence[int]]] = No
         fuse_conv_activation(g)
         fuse_deconv_activation(g)
         fuse_gemm(g, info)
+        fuse_qkv_gemms(g)
         if info is not None and any(n.op == "MultiClassNMS" for n in g.nodes):
             info = infer_shapes(g, input_shapes, input_values)
             fuse_ppyoloe_head(g, info)
