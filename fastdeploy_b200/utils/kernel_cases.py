@@ -24,7 +24,7 @@ def main(argv=None) -> int:
     import torch
     from ..ops.conv_gemm import ConvGemm, pack_conv_weight, pack_linear_weight
     ap = argparse.ArgumentParser()
-    ap.add_argument("kind", choices=["conv", "gemm", "attention", "nms", "preproc", "slot_reduce_ln", "db_postprocess"])
+    ap.add_argument("kind", choices=["conv", "gemm", "attention", "nms", "preproc", "slot_reduce_ln", "db_postprocess", "layernorm"])
     ap.add_argument("--n", type=int, default=16)
     ap.add_argument("--hw", type=int, default=160)
     ap.add_argument("--cin", type=int, default=48)
@@ -51,7 +51,7 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     dt = torch.float16 if a.dtype == "fp16" else torch.bfloat16
     dev = "cuda"
-    if a.kind in ("nms", "preproc", "slot_reduce_ln", "db_postprocess"):
+    if a.kind in ("nms", "preproc", "slot_reduce_ln", "db_postprocess", "layernorm"):
         return _aux_case(a, dt)
     if a.kind == "conv":
         n, h, cin, cout, k, s = a.n, a.hw, a.cin, a.cout, a.k, a.stride
@@ -188,6 +188,17 @@ def _aux_case(a, dt) -> int:
         op = _Launch(pre.launch)
         nbytes = raw.numel() + dst.numel() * 2
         info = {"kernel": "preproc", "frames": n, "src": [h, w], "dst": [640, 640]}
+    elif a.kind == "layernorm":
+        from ..ops import transformer as T
+        from ..ops.base import StatusWord
+        rows, cols = a.m, a.n if a.n != 16 else 768
+        x = (torch.randn(rows, cols, generator=g) * 0.5).to(dev).to(dt)
+        y = torch.zeros(rows, cols, device=dev, dtype=dt)
+        gamma, beta = (torch.rand(cols, generator=g) + 0.5).to(dev), torch.randn(cols, generator=g).to(dev)
+        ln = T.layernorm(x, y, gamma, beta, rows=rows, c=cols, eps=1e-5, x_ld=cols, y_ld=cols)
+        op = _Launch(ln.launch, StatusWord(torch.device(dev)))
+        nbytes = 2 * x.numel() * 2
+        info = {"kernel": "layernorm", "rows": rows, "cols": cols}
     elif a.kind == "slot_reduce_ln":
         import ctypes
         from ..ops.base import StatusWord, current_stream_ptr, dtype_code
