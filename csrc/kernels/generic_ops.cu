@@ -235,6 +235,81 @@ __global__ void __launch_bounds__(256) softmax_last_kernel(const void* __restric
   }
 }
 
+// Typed soft-max for floating inputs and outputs: TPR threads per row (a warp for short rows, a 256-thread block for
+// long ones such as a 6625-class recogniser head), one online pass for maximum and sum, one pass to write.
+template <typename T> __device__ __forceinline__ float sm_load(const T* p, long long i);
+template <> __device__ __forceinline__ float sm_load<float>(const float* p, long long i) { return p[i]; }
+template <> __device__ __forceinline__ float sm_load<__half>(const __half* p, long long i) { return __half2float(p[i]); }
+template <> __device__ __forceinline__ float sm_load<__nv_bfloat16>(const __nv_bfloat16* p, long long i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ void sm_store(float* p, long long i, float v) { p[i] = v; }
+__device__ __forceinline__ void sm_store(__half* p, long long i, float v) { p[i] = __float2half_rn(v); }
+__device__ __forceinline__ void sm_store(__nv_bfloat16* p, long long i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ void sm_combine(float& m, float& s, float om, float os) {
+  const float nm = fmaxf(m, om);
+  if (nm == -INFINITY) { s = 0.f; return; }
+  s = s * __expf(m - nm) + os * __expf(om - nm);
+  m = nm;
+}
+
+template <typename Tin, typename Tout, int TPR>
+__global__ void __launch_bounds__(256) softmax_last_fast_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, long long rows,
+                                                                int C, long long x_ld, long long y_ld, int log_form) {
+  __shared__ float red_m[8], red_s[8];
+  const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) / TPR;
+  const int t = threadIdx.x % TPR, lane = threadIdx.x & 31;
+  const bool live = row < rows;                     // TPR == 256: the whole block shares one row
+  const Tin* xr = x + (live ? row : 0) * x_ld;
+  float m = -INFINITY, s = 0.f;
+  if (live) {
+    for (int c = t; c < C; c += TPR) {
+      const float v = sm_load<Tin>(xr, c);
+      if (v > m) { s = s * __expf(m - v) + 1.f; m = v; }
+      else if (m > -INFINITY) s += __expf(v - m);      // (both -inf: a masked entry before any finite one adds nothing)
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sm_combine(m, s, __shfl_xor_sync(0xffffffffu, m, o), __shfl_xor_sync(0xffffffffu, s, o));
+  if (TPR > 32) {
+    if (lane == 0) { red_m[threadIdx.x >> 5] = m; red_s[threadIdx.x >> 5] = s; }
+    __syncthreads();
+    m = red_m[0]; s = red_s[0];
+#pragma unroll
+    for (int w = 1; w < TPR / 32; ++w) sm_combine(m, s, red_m[w], red_s[w]);
+  }
+  if (!live) return;
+  const float inv = 1.f / s, ls = __logf(s);
+  Tout* yr = y + row * y_ld;
+  for (int c = t; c < C; c += TPR) {
+    const float v = sm_load<Tin>(xr, c) - m;
+    sm_store(yr, c, log_form ? v - ls : __expf(v) * inv);
+  }
+}
+
+template <typename Tin, typename Tout>
+static void launch_softmax_fast(const void* x, void* y, long long rows, int C, long long x_ld, long long y_ld, int lf,
+                                cudaStream_t s) {
+  if (C >= 2048)
+    softmax_last_fast_kernel<Tin, Tout, 256><<<static_cast<unsigned>(rows), 256, 0, s>>>(
+        static_cast<const Tin*>(x), static_cast<Tout*>(y), rows, C, x_ld, y_ld, lf);
+  else
+    softmax_last_fast_kernel<Tin, Tout, 32><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, s>>>(
+        static_cast<const Tin*>(x), static_cast<Tout*>(y), rows, C, x_ld, y_ld, lf);
+}
+
+// false when the dtype pair has no typed kernel (the generic one then runs)
+static bool softmax_fast(const void* x, void* y, long long rows, int C, long long x_ld, long long y_ld, int xdt, int ydt,
+                         int lf, cudaStream_t s) {
+  if (rows > 0x7fffffffLL) return false;
+#define FDB_SM_CASE(XD, XT, YD, YT) \
+  if (xdt == XD && ydt == YD) { launch_softmax_fast<XT, YT>(x, y, rows, C, x_ld, y_ld, lf, s); return true; }
+  FDB_SM_CASE(kF16, __half, kF16, __half) FDB_SM_CASE(kF16, __half, kF32, float)
+  FDB_SM_CASE(kBF16, __nv_bfloat16, kBF16, __nv_bfloat16) FDB_SM_CASE(kBF16, __nv_bfloat16, kF32, float)
+  FDB_SM_CASE(kF32, float, kF32, float) FDB_SM_CASE(kF32, float, kF16, __half) FDB_SM_CASE(kF32, float, kBF16, __nv_bfloat16)
+#undef FDB_SM_CASE
+  return false;
+}
+
 // ---- reductions over the last axis: one warp per row -------------------------------------------------
 // mode 0 sum, 1 mean, 2 max, 3 min, 4 arg-max (first maximum), 5 arg-min, 6 product
 __global__ void __launch_bounds__(256) reduce_last_kernel(const void* __restrict__ x, void* __restrict__ y, long long rows,
@@ -349,7 +424,8 @@ FDB_API void* fdb_generic_create(int kind, const GenericDesc* dp) {
       if (C < 1) { set_error("softmax: empty axis"); delete op; return nullptr; }
       op->fn = [=](cudaStream_t s) {
         if (rows == 0) return 0;
-        softmax_last_kernel<<<static_cast<int>((rows * 32 + 255) / 256), 256, 0, s>>>(d.p[0], d.p[1], rows, C, x_ld, y_ld, xdt, ydt, lf);
+        if (!softmax_fast(d.p[0], d.p[1], rows, C, x_ld, y_ld, xdt, ydt, lf, s))
+          softmax_last_kernel<<<static_cast<int>((rows * 32 + 255) / 256), 256, 0, s>>>(d.p[0], d.p[1], rows, C, x_ld, y_ld, xdt, ydt, lf);
         FDB_GEN_CHECK();
       };
       break;

@@ -458,6 +458,74 @@ __global__ void depthwise_conv_kernel(const uint8_t* __restrict__ x, const float
   }
 }
 
+// The 3x3 and 5x5 depthwise layers of the light backbones: one thread = 8 channels x 4 neighbouring output pixels of a
+// row. Per filter row the K weight vectors sit in registers and every input column of the window is loaded once and
+// fed to all the outputs it reaches, so a 5x5 layer issues 8 input loads per filter row for 4 outputs instead of 20,
+// and the loops are unrolled at compile time (K and the horizontal stride are template parameters).
+template <bool BF16, int K, int SW>
+__global__ void __launch_bounds__(256) depthwise_conv_tiled_kernel(
+    const uint8_t* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias, uint8_t* __restrict__ y,
+    long long total, int H, int W, int C8, int x_ld, int Ho, int Wo, int y_ld, int sh, int pt, int pl, long long xns,
+    long long yns, int act, float alpha, float beta) {
+  constexpr int TW = 4, WIN = (TW - 1) * SW + K;
+  const int wt = (Wo + TW - 1) / TW;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int cg = static_cast<int>(i % C8);
+    long long r = i / C8;
+    const int ot = static_cast<int>(r % wt); r /= wt;
+    const int oh = static_cast<int>(r % Ho);
+    const int n = static_cast<int>(r / Ho);
+    const int c0 = cg * 8, C = C8 * 8, ow0 = ot * TW;
+    float acc[TW][8];
+#pragma unroll
+    for (int t = 0; t < TW; ++t)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[t][j] = bias != nullptr ? bias[c0 + j] : 0.f;
+    const uint8_t* xn = x + static_cast<size_t>(n) * xns * 2;
+    const int iw0 = ow0 * SW - pl;
+#pragma unroll
+    for (int kh = 0; kh < K; ++kh) {
+      const int ih = oh * sh - pt + kh;
+      if (ih < 0 || ih >= H) continue;
+      float wk[K][8];
+#pragma unroll
+      for (int kw = 0; kw < K; ++kw) {
+        const float4 w0 = __ldg(reinterpret_cast<const float4*>(w + static_cast<size_t>(kh * K + kw) * C + c0));
+        const float4 w1 = __ldg(reinterpret_cast<const float4*>(w + static_cast<size_t>(kh * K + kw) * C + c0 + 4));
+        wk[kw][0] = w0.x; wk[kw][1] = w0.y; wk[kw][2] = w0.z; wk[kw][3] = w0.w;
+        wk[kw][4] = w1.x; wk[kw][5] = w1.y; wk[kw][6] = w1.z; wk[kw][7] = w1.w;
+      }
+      const uint8_t* xrow = xn + (static_cast<size_t>(ih) * W * x_ld + c0) * 2;
+#pragma unroll
+      for (int j = 0; j < WIN; ++j) {
+        const int iw = iw0 + j;
+        if (iw < 0 || iw >= W) continue;
+        float f[8];
+        unpack8<BF16>(__ldg(reinterpret_cast<const uint4*>(xrow + static_cast<size_t>(iw) * x_ld * 2)), f);
+#pragma unroll
+        for (int t = 0; t < TW; ++t) {
+          const int kw = j - t * SW;               // resolved at compile time: j, t and SW are constants here
+          if (kw >= 0 && kw < K) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc[t][q] = fmaf(f[q], wk[kw][q], acc[t][q]);
+          }
+        }
+      }
+    }
+    uint8_t* yrow = y + (static_cast<size_t>(n) * yns + static_cast<size_t>(oh) * Wo * y_ld + c0) * 2;
+#pragma unroll
+    for (int t = 0; t < TW; ++t) {
+      if (ow0 + t >= Wo) break;
+      if (act != kActNone) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[t][q] = act_f32(acc[t][q], act, alpha, beta);
+      }
+      *reinterpret_cast<uint4*>(yrow + static_cast<size_t>(ow0 + t) * y_ld * 2) = pack8<BF16>(acc[t]);
+    }
+  }
+}
+
 FDB_API void* fdb_simple_create(int kind, const SimpleDesc* dp) {
   const SimpleDesc d = *dp;
   auto* op = new LambdaOp();
@@ -596,7 +664,25 @@ FDB_API void* fdb_simple_create(int kind, const SimpleDesc* dp) {
       const float al = d.f[0], be = d.f[1];
       if (C % 8 || x_ld % 8 || y_ld % 8) { set_error("depthwise_conv: C/ld must be multiples of 8"); delete op; return nullptr; }
       const long long total = static_cast<long long>(N) * Ho * Wo * (C / 8);
+      const bool tiled = KH == KW && (KH == 3 || KH == 5) && (sw == 1 || sw == 2) &&
+                         reinterpret_cast<uintptr_t>(d.p[0]) % 16 == 0 && reinterpret_cast<uintptr_t>(d.p[1]) % 16 == 0;
+      const long long total_tiled = static_cast<long long>(N) * Ho * ((Wo + 3) / 4) * (C / 8);
       op->fn = [=](cudaStream_t s) {
+        if (tiled) {
+          const int tgrid = grid_for(total_tiled, 256);
+#define FDB_DW_LAUNCH(BF, K, SW)                                                                                      \
+  depthwise_conv_tiled_kernel<BF, K, SW><<<tgrid, 256, 0, s>>>((const uint8_t*)d.p[0], (const float*)d.p[1],          \
+      (const float*)d.p[2], (uint8_t*)d.p[3], total_tiled, H, W, C / 8, x_ld, Ho, Wo, y_ld, sh, pt, pl, xns, yns, act, al, be)
+          if (bf) {
+            if (KH == 3 && sw == 1) FDB_DW_LAUNCH(true, 3, 1); else if (KH == 3) FDB_DW_LAUNCH(true, 3, 2);
+            else if (sw == 1) FDB_DW_LAUNCH(true, 5, 1); else FDB_DW_LAUNCH(true, 5, 2);
+          } else {
+            if (KH == 3 && sw == 1) FDB_DW_LAUNCH(false, 3, 1); else if (KH == 3) FDB_DW_LAUNCH(false, 3, 2);
+            else if (sw == 1) FDB_DW_LAUNCH(false, 5, 1); else FDB_DW_LAUNCH(false, 5, 2);
+          }
+#undef FDB_DW_LAUNCH
+          FDB_LAUNCH_CHECK();
+        }
         const int grid = grid_for(total, 256);
         if (bf) depthwise_conv_kernel<true><<<grid, 256, 0, s>>>((const uint8_t*)d.p[0], (const float*)d.p[1], (const float*)d.p[2],
                                                                  (uint8_t*)d.p[3], total, H, W, C / 8, x_ld, Ho, Wo, y_ld, KH, KW, sh,

@@ -105,6 +105,19 @@ def test_where_softmax_reduce_gather():
     torch.cuda.synchronize()
     torch.testing.assert_close(y, torch.softmax(x.float(), -1), rtol=1e-4, atol=1e-7)
     torch.testing.assert_close(ly, torch.log_softmax(x.float(), -1), rtol=1e-4, atol=1e-4)
+    # masked entries (-inf) at the front, in the middle and at the end of long and short rows, every dtype pair
+    for cols in (6625, 40):
+        for din, dout in ((torch.float16, torch.float16), (torch.bfloat16, torch.float32), (torch.float32, torch.bfloat16)):
+            xm = _dev(torch.randn(4, cols, generator=g)).to(din)
+            xm[0, :3] = float("-inf")
+            xm[1, cols // 2:cols // 2 + 5] = float("-inf")
+            xm[2, -2:] = float("-inf")
+            ym = torch.zeros(4, cols, device="cuda", dtype=dout)
+            G.softmax_last(xm, ym).launch()
+            torch.cuda.synchronize()
+            want = torch.softmax(xm.float(), -1)
+            tol = 1e-5 if dout == torch.float32 else 4e-3
+            assert (ym.float() - want).abs().max().item() < tol and not torch.isnan(ym.float()).any()
     xs = _dev(torch.randn(7, 33, generator=g))
     for mode, ref in (("sum", xs.sum(-1)), ("mean", xs.mean(-1)), ("max", xs.amax(-1)), ("min", xs.amin(-1))):
         r = torch.zeros(7, device="cuda")

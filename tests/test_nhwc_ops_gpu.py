@@ -229,7 +229,9 @@ def test_multiclass_nms_keep_all_and_background():
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("k,stride,act", [(3, 1, "relu"), (3, 2, "hard_swish"), (5, 1, None), (5, 2, "hard_sigmoid")])
+@pytest.mark.parametrize("k,stride,act", [(3, 1, "relu"), (3, 2, "hard_swish"), (5, 1, None), (5, 2, "hard_sigmoid"),
+                                          (3, (2, 1), "relu"), (5, (2, 1), "hard_swish"), (5, (1, 2), None),
+                                          (7, 1, None)])
 def test_depthwise_conv_matches_fp32_reference(dtype, k, stride, act):
     from fastdeploy_b200.ops import nhwc as K
     torch.manual_seed(0)
@@ -238,10 +240,11 @@ def test_depthwise_conv_matches_fp32_reference(dtype, k, stride, act):
     wt = torch.randn(c, 1, k, k, device="cuda") * 0.3
     b = torch.randn(c, device="cuda")
     pad = k // 2
-    ho, wo = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+    stride = (stride, stride) if isinstance(stride, int) else stride      # (rows, columns); 7x7 takes the generic kernel
+    ho, wo = (h + 2 * pad - k) // stride[0] + 1, (w + 2 * pad - k) // stride[1] + 1
     y = torch.empty(n, ho, wo, c, device="cuda", dtype=dtype)
     wk = wt.reshape(c, k * k).t().contiguous()
-    op = K.depthwise_conv(x, wk, b, y, n=n, h=h, w_in=w, c=c, kernel=(k, k), stride=(stride, stride), pad=(pad, pad),
+    op = K.depthwise_conv(x, wk, b, y, n=n, h=h, w_in=w, c=c, kernel=(k, k), stride=stride, pad=(pad, pad),
                           out_hw=(ho, wo), act=act, act_alpha=0.2, act_beta=0.5)
     op.launch()
     torch.cuda.synchronize()
