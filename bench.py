@@ -7,6 +7,7 @@ keep_top_k 100), data-parallel over N GPUs:
         bench.py --gpus N --steps K --warmup W
     python bench.py --config ernie | ocr | vit_tp  ...        (same flags, same JSON schema)
     python bench.py --config ppyoloe_library                  (context: the same network on PyTorch / cuDNN fp16)
+    python bench.py --config resnet50_cpu                     (ResNet-50 batch-1 latency through the CPU path; no GPU)
 
 ``value``   : device-timed (CUDA events, max over ranks) rate of the on-device step, inputs resident on the GPU.
 ``e2e``     : the same metric through the public API, each step copying its inputs from pinned host memory and
@@ -29,7 +30,7 @@ REF_UNAVAILABLE = ("refused by a safety check: building the reference (its pytho
                    "install of the reference tree fails before that (no setup.py at its root, python/ needs the "
                    "CMake build first)")
 
-CONFIGS = ("ppyoloe", "ernie", "ocr", "vit_tp", "ppyoloe_library")
+CONFIGS = ("ppyoloe", "ernie", "ocr", "vit_tp", "ppyoloe_library", "resnet50_cpu")
 
 
 def main() -> int:
@@ -52,6 +53,11 @@ def main() -> int:
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REF_UNAVAILABLE}))
+        return 0
+
+    if args.config == "resnet50_cpu":          # host only: no device context, no process group
+        from fastdeploy_b200.benchmarks.resnet50_cpu import run_cpu
+        print(json.dumps(run_cpu(args)))
         return 0
 
     import importlib

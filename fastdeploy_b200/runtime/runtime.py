@@ -98,7 +98,10 @@ class Runtime:
             self.device = torch.device("cpu")
             if self.option.cpu_thread_num > 0:
                 torch.set_num_threads(self.option.cpu_thread_num)
-            self._interp = Interpreter(self.graph)
+            # the CPU path runs the graph after the numerically safe rewrites (constant folding, batch-norm and bias
+            # folding) with channel-innermost convolution operands
+            from ..ir.passes import optimize
+            self._interp = Interpreter(optimize(self.graph, level=1), channels_last=True)
 
     # ------------------------------------------------------------------ introspection
     def num_inputs(self) -> int:
