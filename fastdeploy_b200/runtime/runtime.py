@@ -98,10 +98,10 @@ class Runtime:
             self.device = torch.device("cpu")
             if self.option.cpu_thread_num > 0:
                 torch.set_num_threads(self.option.cpu_thread_num)
-            # the CPU path runs the graph after the numerically safe rewrites (constant folding, batch-norm and bias
-            # folding) with channel-innermost convolution operands
+            # the CPU path runs the optimised graph (constant, batch-norm and bias folding, activations fused into
+            # their convolutions) with channel-innermost operands and weights packed once for the vendor primitive
             from ..ir.passes import optimize
-            self._interp = Interpreter(optimize(self.graph, level=1), channels_last=True)
+            self._interp = Interpreter(optimize(self.graph, level=2), channels_last=True)
 
     # ------------------------------------------------------------------ introspection
     def num_inputs(self) -> int:

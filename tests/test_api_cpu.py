@@ -117,3 +117,23 @@ def test_nonzero_device_status_raises_on_every_inference_path():
     rt._status_host[0] = 3
     with pytest.raises(RuntimeError, match="epilogue wait timed out"):
         m.infer({})
+
+
+def test_cpu_runtime_fast_path_matches_plain_interpreter(tmp_path):
+    """The CPU runtime (optimised graph, channel-innermost operands, packed fused convolutions) returns what the plain
+    interpreter returns on the imported graph."""
+    import numpy as np
+    import fastdeploy_b200 as fd
+    from fastdeploy_b200.ir.interp import Interpreter
+    from fastdeploy_b200.models.resnet import resnet18_like_onnx
+    path = tmp_path / "r.onnx"
+    path.write_bytes(resnet18_like_onnx())
+    opt = fd.RuntimeOption()
+    opt.use_cpu()
+    opt.set_model_path(str(path), "", fd.ModelFormat.ONNX)
+    rt = fd.Runtime(opt)
+    for n in (1, 3):                                   # two input shapes: the packed weights are kept per shape
+        x = np.random.RandomState(n).rand(n, 3, 64, 64).astype(np.float32)
+        ref = Interpreter(rt.graph).run({"input": x})["output"].numpy()
+        got = rt.infer({"input": x})[0]
+        assert got.shape == ref.shape and np.abs(got - ref).max() < 1e-4 * max(1.0, np.abs(ref).max())
