@@ -102,7 +102,7 @@ class Arena:
         bases = [int(s.data_ptr()) for s in self.slabs]
         ranges: List[Tuple[int, int]] = []
         for t in needed:
-            if t is None or not t.is_cuda:
+            if t is None or t.device.type != self.device.type:
                 continue
             lo, hi = self.span(t)
             if hi > lo:
