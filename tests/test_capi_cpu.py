@@ -42,3 +42,27 @@ def test_c_program_runs_a_model(tmp_path):
     chk = float(lines[1].split("checksum=")[1])
     assert abs(chk - ref) <= 1e-3 * max(1.0, abs(ref)), (chk, ref)
     assert lines[2] == "bad=null err=set"
+
+
+@pytest.mark.skipif(shutil.which("gcc") is None, reason="no C compiler")
+def test_plan_runner_header_links_and_reports_errors(tmp_path):
+    """The plan runner is a plain C library: a C program links it without Python and gets messages, not crashes."""
+    from fastdeploy_b200 import _native
+    from fastdeploy_b200._native import build
+    if not os.path.exists(build.RUNNER_LIB):
+        build.build_runner()
+    exe = str(tmp_path / "plan_runner_smoke")
+    subprocess.run(["gcc", os.path.join(ROOT, "tests", "plan_runner_smoke.c"), "-I", os.path.join(ROOT, "csrc", "runner"),
+                    "-o", exe, "-L", os.path.dirname(build.RUNNER_LIB), "-lfdb200_runner",
+                    f"-Wl,-rpath,{os.path.dirname(build.RUNNER_LIB)}"], check=True)
+    junk = tmp_path / "junk.fdplan"
+    junk.write_bytes(b"not a plan file at all")
+    p = subprocess.run([exe, _native.KERNEL_LIB, str(tmp_path / "absent.fdplan"), str(junk)], capture_output=True,
+                       text=True, timeout=120)
+    assert p.returncode == 0, p.stdout + p.stderr
+    lines = p.stdout.strip().splitlines()
+    assert lines[0].startswith("missing: null | cannot open") and lines[1] == "garbage: null | not a plan file"
+    assert lines[2] == "nolib: null | message"
+    # the library itself does not depend on the interpreter
+    deps = subprocess.run(["ldd", build.RUNNER_LIB], capture_output=True, text=True).stdout
+    assert "python" not in deps.lower()

@@ -9,7 +9,8 @@ import pytest
 from fastdeploy_b200._native import build as B
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-HOST_TESTS = ["tests/test_text_cpu.py", "tests/test_serving_cpu.py", "tests/test_core_functions.py"]
+HOST_TESTS = ["tests/test_text_cpu.py", "tests/test_serving_cpu.py", "tests/test_core_functions.py",
+              "tests/test_function_native_cpu.py"]
 
 
 def _env(mode):
