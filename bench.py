@@ -1,4 +1,4 @@
-"""Benchmarks of the BASELINE configurations. The headline (no ``--config``) is end-to-end images/s of
+"""Benchmarks of the five headline configurations. The headline (no ``--config``) is end-to-end images/s of
 PP-YOLOE+-L (fp16, 640x640 from 1080x1920 uint8 frames, batch 32 per GPU, multiclass NMS score 0.01 / IoU 0.6 /
 keep_top_k 100), data-parallel over N GPUs:
 
