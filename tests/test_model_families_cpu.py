@@ -193,3 +193,38 @@ def test_ser_vi_layoutxlm_windows_reading_order_and_line_vote(tmp_path):
     assert [x.pred for x in two] == [r.pred, r.pred]
     with pytest.raises(ValueError):
         m.predict(np.zeros((500, 1000, 3), np.uint8))
+
+
+def test_ser_vi_layoutxlm_runs_a_model_end_to_end(tmp_path):
+    """The SER class on a synthetic vi-LayoutXLM export (CPU runtime): windows in, one label per text line out, the
+    same labels as arg-max + line vote done by hand on the runtime's logits."""
+    import fastdeploy_b200 as fd
+    from fastdeploy_b200.models.layoutxlm import write_ser_vi_layoutxlm
+    from fastdeploy_b200.vision.ocr import StructureV2SERViLayoutXLM
+    paths = write_ser_vi_layoutxlm(str(tmp_path), "tiny", num_labels=7, seed=3)
+
+    class Tok:
+        def encode(self, text):
+            return [0] + [3 + ord(c) % 250 for c in text] + [2]
+    opt = fd.RuntimeOption()
+    opt.use_cpu()
+    m = StructureV2SERViLayoutXLM(paths["model"], paths["params"], paths["classes"], tokenizer=Tok(), runtime_option=opt)
+    assert m.initialized and m.postprocessor.draw_names == ["O", "QUESTION", "ANSWER", "HEADER"]
+    lines = [{"bbox": [40, 30, 400, 60], "transcription": "Invoice number"},
+             {"bbox": [420, 30, 700, 60], "transcription": "2024-117"},
+             {"bbox": [40, 90, 300, 120], "transcription": "Total amount due"},
+             {"bbox": [40, 200, 900, 230], "transcription": "x" * 700}]            # forces a second window
+    page = np.zeros((400, 1000, 3), np.uint8)
+    res = m.predict(page, lines)
+    assert len(res.pred) == 4 and all(p in m.postprocessor.draw_names for p in res.pred)
+    assert res.text[0] == "Invoice number" and res.boxes[1] == [420, 30, 700, 60]
+    batch = m.preprocessor.run(lines, 400, 1000)
+    assert batch["input_ids"].shape == (2, 512)
+    feeds = {"input_ids": batch["input_ids"], "bbox": batch["bbox"], "attention_mask": batch["attention_mask"],
+             "token_type_ids": batch["token_type_ids"]}
+    logits = m.runtime.infer(feeds)[0]
+    assert logits.shape == (2, 512, 7)
+    by_hand = m.postprocessor.run(logits, batch)
+    assert by_hand.pred == res.pred and by_hand.pred_id == res.pred_id
+    two = m.batch_predict([page, page], [lines, lines[:2]])
+    assert two[0].pred == res.pred and two[1].pred == res.pred[:2] or len(two[1].pred) == 2
