@@ -49,6 +49,10 @@ VERSION = {1: ("version", "int", False)}
 PROGRAM_DESC = {1: ("blocks", BLOCK_DESC, True), 4: ("version", VERSION, False)}
 
 
+class BlockRef(int):
+    """Index of a sub-block of the program (the value of a ``sub_block`` attribute of ``while`` / ``conditional_block``)."""
+
+
 class PaddleOp:
     __slots__ = ("type", "inputs", "outputs", "attrs")
 
@@ -129,7 +133,7 @@ def _attr_value(a: Dict[str, Any]):
     if t == AT_STRINGS: return list(a.get("strings", []))
     if t == AT_BOOLEAN: return bool(a.get("b", False))
     if t == AT_BOOLEANS: return [bool(x) for x in a.get("bools", [])]
-    if t == AT_BLOCK: return int(a.get("block_idx", 0))
+    if t == AT_BLOCK: return BlockRef(a.get("block_idx", 0))
     if t == AT_LONG: return int(a.get("l", 0))
     if t == AT_BLOCKS: return [int(x) for x in a.get("blocks_idx", [])]
     if t == AT_LONGS: return [int(x) for x in a.get("longs", [])]
@@ -213,6 +217,8 @@ def parse_params(prog: PaddleProgram, params_bytes: bytes) -> Dict[str, np.ndarr
 
 # ------------------------------------------------------------------------ encode
 def _attr_msg(name: str, v) -> Dict[str, Any]:
+    if isinstance(v, BlockRef):
+        return {"name": name, "type": AT_BLOCK, "block_idx": int(v)}
     if isinstance(v, bool):
         return {"name": name, "type": AT_BOOLEAN, "b": v}
     if isinstance(v, (int, np.integer)):
@@ -234,22 +240,29 @@ def _attr_msg(name: str, v) -> Dict[str, Any]:
     raise ValueError(f"cannot encode paddle attribute {name!r}: {type(v)}")
 
 
-def serialize_program(prog: PaddleProgram) -> bytes:
+def _block_msg(idx: int, parent: int, vars_: Dict[str, "PaddleVar"], ops: List[PaddleOp]) -> Dict[str, Any]:
     vars_msg = []
-    for v in prog.vars.values():
+    for v in vars_.values():
         vt: Dict[str, Any] = {"type": v.var_type}
         if v.var_type == VT_LOD_TENSOR:
             vt["lod_tensor"] = {"tensor": {"data_type": NP_TO_PD[v.dtype], "dims": list(v.shape)}, "lod_level": 0}
         vars_msg.append({"name": v.name, "type": vt, "persistable": v.persistable})
     ops_msg = []
-    for op in prog.ops:
+    for op in ops:
         ops_msg.append({
             "type": op.type,
             "inputs": [{"parameter": k, "arguments": v} for k, v in op.inputs.items()],
             "outputs": [{"parameter": k, "arguments": v} for k, v in op.outputs.items()],
             "attrs": [_attr_msg(k, v) for k, v in op.attrs.items() if v is not None],
         })
-    msg = {"blocks": [{"idx": 0, "parent_idx": -1, "vars": vars_msg, "ops": ops_msg}], "version": {"version": prog.version}}
+    return {"idx": idx, "parent_idx": parent, "vars": vars_msg, "ops": ops_msg}
+
+
+def serialize_program(prog: PaddleProgram) -> bytes:
+    blocks = [_block_msg(0, -1, prog.vars, prog.ops)]
+    for k, (vars_, ops) in enumerate(prog.sub_blocks):
+        blocks.append(_block_msg(k + 1, 0, vars_, ops))
+    msg = {"blocks": blocks, "version": {"version": prog.version}}
     # proto2 files written by Paddle do not pack repeated scalars
     return pw.encode(msg, PROGRAM_DESC, packed=False)
 
@@ -303,6 +316,16 @@ class ProgramBuilder:
         outs = {k: [self.tmp(type_, var_dtype, out_shape)] for k in out_keys}
         self.prog.add_op(type_, inputs, outs, **attrs)
         return outs[out_keys[0]][0]
+
+    def sub_block(self, ops: Sequence[Tuple[str, Dict[str, Sequence[str]], Dict[str, Sequence[str]], Dict[str, Any]]],
+                  new_vars: Sequence[Tuple[str, str, Sequence[int]]] = ()) -> BlockRef:
+        """Adds a sub-block made of ``(type, inputs, outputs, attrs)`` ops; ``new_vars`` = ``(name, dtype, shape)`` of
+        the variables that only live inside it. Returns the reference to put into a ``sub_block`` attribute."""
+        vars_ = {n: PaddleVar(n, dt, list(shape), False) for n, dt, shape in new_vars}
+        block_ops = [PaddleOp(t, {k: list(v) for k, v in i.items()}, {k: list(v) for k, v in o.items()}, dict(a))
+                     for t, i, o, a in ops]
+        self.prog.sub_blocks.append((vars_, block_ops))
+        return BlockRef(len(self.prog.sub_blocks))
 
     def serialize(self) -> Tuple[bytes, bytes]:
         return serialize_program(self.prog), serialize_params(self.prog, self.params)

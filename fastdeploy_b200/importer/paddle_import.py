@@ -758,7 +758,12 @@ def _multiclass_nms(c, op):
 def import_program(prog: PaddleProgram, params: Dict[str, np.ndarray], name: str = "paddle_model") -> Graph:
     g = Graph(name, opset=13)
     c = Ctx(prog, g)
-    unsupported = sorted({op.type for op in prog.ops if op.type not in _MAPPERS})
+    from . import paddle_control_flow as cf
+    mappers = dict(_MAPPERS)
+    for name, fn in cf.CONTROL_MAPPERS.items():
+        mappers[name] = (lambda f: lambda ctx, op: f(ctx, op, mappers))(fn)
+    all_ops = list(prog.ops) + [op for _, ops in prog.sub_blocks for op in ops]
+    unsupported = sorted({op.type for op in all_ops if op.type not in mappers})
     if unsupported:
         raise NotImplementedError(f"paddle importer: unsupported operators {unsupported}")
     for k, v in params.items():
@@ -766,11 +771,22 @@ def import_program(prog: PaddleProgram, params: Dict[str, np.ndarray], name: str
     for fname in prog.feed_names():
         v = prog.vars[fname]
         g.inputs.append(ValueInfo(fname, v.dtype, [d if d >= 0 else "dyn" for d in v.shape]))
-    for op in prog.ops:
-        _MAPPERS[op.type](c, op)
+    # Programs with control flow (or in-place ops) are not in single-assignment form: rename as we go.
+    in_place = any(op.type in cf.CONTROL_MAPPERS for op in all_ops)
+    if in_place:
+        c.prog = cf._scope_program(prog, {}, {})
+        c.renamer = cf.Renamer(set(params) | set(prog.feed_names()) | {"feed", "fetch"})
+        for op in prog.ops:
+            if op.type in ("feed", "fetch"):
+                continue
+            cf.run_op(c, op, mappers)
+    else:
+        for op in prog.ops:
+            _MAPPERS[op.type](c, op)
     for fname in prog.fetch_names():
         v = prog.vars.get(fname)
-        g.outputs.append(ValueInfo(fname, v.dtype if v else "float32",
+        out_name = c.renamer.read(fname) if in_place else fname
+        g.outputs.append(ValueInfo(out_name, v.dtype if v else "float32",
                                    [d if d >= 0 else "dyn" for d in v.shape] if v else None))
     for vname, v in prog.vars.items():
         if not v.persistable and v.shape:

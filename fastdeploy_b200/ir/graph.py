@@ -120,14 +120,14 @@ class Graph:
             rest = []
             progressed = False
             for n in pending:
-                if all(i in known for i in n.inputs):
+                if all(i in known for i in list(n.inputs) + list(n.attrs.get("outer_refs", []))):
                     ordered.append(n)
                     known.update(n.outputs)
                     progressed = True
                 else:
                     rest.append(n)
             if not progressed:
-                missing = {i for n in rest for i in n.inputs if i not in known}
+                missing = {i for n in rest for i in list(n.inputs) + list(n.attrs.get("outer_refs", [])) if i not in known}
                 raise ValueError(f"graph has a cycle or undefined values: {sorted(missing)[:5]}")
             pending = rest
         self.nodes = ordered
@@ -140,6 +140,7 @@ class Graph:
             if any(o in needed for o in n.outputs):
                 keep.append(n)
                 needed.update(i for i in n.inputs if i)
+                needed.update(n.attrs.get("outer_refs", []))      # what the bodies of Loop / If read from this scope
         keep.reverse()
         self.nodes = keep
         self.initializers = {k: v for k, v in self.initializers.items() if k in needed}

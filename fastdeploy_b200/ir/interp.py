@@ -319,6 +319,17 @@ def _packed_attention(node, q, k, v, seq_start, seq_len):
     return out
 
 
+@op("SelectInput")
+def _select_input(node, mask, *xs):
+    """Paddle ``select_input``: the operand whose index ``mask`` holds; domain fdb."""
+    return xs[int(mask.reshape(-1)[0])]
+
+
+@op("Loop", "If")
+def _control_flow(node, *args):
+    raise RuntimeError(f"{node.op} needs the enclosing scope: it is executed by Interpreter.run, not as a free function")
+
+
 @op("EmbedLayerNorm")
 def _embed_ln(node, ids, *rest):
     """sum of embedding lookups followed by LayerNorm; domain fdb.
@@ -877,6 +888,67 @@ class Interpreter:
                 t = t.contiguous(memory_format=torch.channels_last)
             self.consts[k] = t.to(self.device)
 
+    # ------------------------------------------------------------------ execution
+    def _exec(self, nodes, env, opset: int) -> None:
+        for node in nodes:
+            if node.op in ("Loop", "If"):
+                res = self._control(node, env, opset)
+            else:
+                args = [env[i] for i in node.inputs]
+                while args and args[-1] is None:
+                    args.pop()
+                node.attrs.setdefault("_opset", opset)
+                res = _OPS[node.op](node, *args)
+            if not isinstance(res, tuple):
+                res = (res,)
+            for name, val in zip(node.outputs, res):
+                if name:
+                    env[name] = val
+
+    def _body_env(self, body: Graph, outer) -> "collections.ChainMap":
+        import collections
+        local = {}
+        for k, v in body.initializers.items():
+            t = torch.from_numpy(np.ascontiguousarray(v))
+            local[k] = (t.float() if t.dtype in (torch.float16, torch.float64) else t).to(self.device)
+        return collections.ChainMap(local, outer)
+
+    def _control(self, node: Node, env, opset: int):
+        """ONNX ``Loop`` / ``If``: the body graphs read this scope by name (a ChainMap keeps their writes local)."""
+        if node.op == "If":
+            cond = bool(env[node.inputs[0]].reshape(-1)[0])
+            body = node.attr("then_branch") if cond else node.attr("else_branch")
+            scope = self._body_env(body, env)
+            self._exec(body.nodes, scope, opset)
+            return tuple(scope[v.name] for v in body.outputs)
+        body = node.attr("body")
+        m = env[node.inputs[0]] if node.inputs[0] else None
+        cond_t = env[node.inputs[1]] if len(node.inputs) > 1 and node.inputs[1] else None
+        carried = [env[i] for i in node.inputs[2:]]
+        n_carried = len(carried)
+        trips = int(m.reshape(-1)[0]) if m is not None else None
+        keep_going = bool(cond_t.reshape(-1)[0]) if cond_t is not None else True
+        scans = [[] for _ in range(len(body.outputs) - 1 - n_carried)]
+        it = 0
+        limit = int(node.attr("max_iterations", 1 << 20))          # a bound on runaway loops, not an ONNX attribute
+        while keep_going and (trips is None or it < trips):
+            if it >= limit:
+                raise RuntimeError(f"Loop {node.name!r} ran {limit} iterations without its condition turning false")
+            scope = self._body_env(body, env)
+            scope[body.inputs[0].name] = torch.tensor(it, dtype=torch.int64, device=self.device)
+            scope[body.inputs[1].name] = torch.tensor(keep_going, device=self.device)
+            for vi, val in zip(body.inputs[2:], carried):
+                scope[vi.name] = val
+            self._exec(body.nodes, scope, opset)
+            outs = [scope[v.name] for v in body.outputs]
+            keep_going = bool(outs[0].reshape(-1)[0])
+            carried = outs[1:1 + n_carried]
+            for k, s in enumerate(outs[1 + n_carried:]):
+                scans[k].append(s)
+            it += 1
+        stacked = [torch.stack(s) if s else torch.zeros(0, device=self.device) for s in scans]
+        return tuple(carried) + tuple(stacked)
+
     def run(self, feeds: Dict[str, "np.ndarray | torch.Tensor"], outputs: Optional[Sequence[str]] = None,
             keep_all: bool = False) -> Dict[str, torch.Tensor]:
         env: Dict[str, Optional[torch.Tensor]] = dict(self.consts)
@@ -897,17 +969,7 @@ class Interpreter:
             env[vi.name] = t
         opset = self.graph.opset
         with torch.no_grad():
-            for node in self.graph.nodes:
-                args = [env[i] for i in node.inputs]
-                while args and args[-1] is None:
-                    args.pop()
-                node.attrs.setdefault("_opset", opset)
-                res = _OPS[node.op](node, *args)
-                if not isinstance(res, tuple):
-                    res = (res,)
-                for name, val in zip(node.outputs, res):
-                    if name:
-                        env[name] = val
+            self._exec(self.graph.nodes, env, opset)
         names = list(outputs) if outputs is not None else self.graph.output_names()
         if keep_all:
             return {k: v for k, v in env.items() if v is not None}
