@@ -117,3 +117,6 @@ def test_gpu_lowering_refuses_control_flow_with_a_clear_message():
     model, params = _while_program()
     g = load_paddle(model, params)
     assert [n.op for n in optimize(g, level=2).nodes] == [n.op for n in g.nodes]      # runs as imported
+    from fastdeploy_b200.runtime.native_backend import build_plan
+    with pytest.raises(NotImplementedError, match="control flow"):
+        build_plan(g, {"x": [2, 3], "n": [1]}, "cpu")
