@@ -188,7 +188,7 @@ class Worker:
                     if not self.alive:
                         break
                 continue
-            items = [it for it in (sched._take(out[k]) for k in range(n)) if it is not None]
+            items = sched._take_many(out, n)
             live = [it for it in items if it.future.set_running_or_notify_cancel()]
             dropped = n - len(live)
             if dropped:
@@ -247,6 +247,13 @@ class Scheduler:
     def _take(self, ticket: int) -> Optional[_Item]:
         with self._items_lock:
             return self._items.pop(int(ticket), None)
+
+    def _take_many(self, tickets, n: int) -> List[_Item]:
+        """The items of a whole batch under one acquisition of the lock (tickets whose item is gone are skipped)."""
+        pop = self._items.pop
+        with self._items_lock:
+            found = [pop(tickets[k], None) for k in range(n)]
+        return [it for it in found if it is not None]
 
     def _fail_orphans(self, why: str) -> None:
         buf = (_I64 * 256)()
