@@ -13,8 +13,11 @@ def _roundtrip(plan, feeds, tmp_path, tag):
     """Runs ``plan`` in Python on ``feeds`` (name -> tensor in the plan input's own layout), exports it, replays it
     with the command-line runner on the same bytes and compares every output bit for bit."""
     from fastdeploy_b200._native import KERNEL_LIB
+    from fastdeploy_b200._native import build
     from fastdeploy_b200._native.build import RUNNER_TOOL
     from fastdeploy_b200.runtime.plan_file import export_plan
+    if not os.path.exists(RUNNER_TOOL):
+        build.build_runner()
     path = str(tmp_path / f"{tag}.fdplan")
     info = export_plan(plan, path)
     assert info["ops"] == len(plan.steps) and info["constant_bytes"] > 0
