@@ -56,10 +56,116 @@ def _core():
     return lib
 
 
+_FUTURE_LOCK = threading.Lock()
+
+
+class RequestFuture:
+    """The result handle of one request: the methods of ``concurrent.futures.Future`` that callers of a scheduler use
+    (``result``, ``exception``, ``done``, ``cancel``, ``cancelled``, ``running``, ``add_done_callback``), without the
+    condition variable that class allocates for every instance - a request that has finished before anybody waits for
+    it (the common case of a pipelined client) never allocates a waitable object at all."""
+
+    __slots__ = ("_state", "_value", "_error", "_event", "_callbacks")
+    _PENDING, _RUNNING, _CANCELLED, _FINISHED = 0, 1, 2, 3
+
+    def __init__(self):
+        self._state = self._PENDING
+        self._value = None
+        self._error: Optional[BaseException] = None
+        self._event: Optional[threading.Event] = None
+        self._callbacks = None
+
+    # ---- producer side
+    def set_running_or_notify_cancel(self) -> bool:
+        with _FUTURE_LOCK:
+            if self._state == self._CANCELLED:
+                return False
+            self._state = self._RUNNING
+            return True
+
+    def _finish(self, value, error) -> None:
+        with _FUTURE_LOCK:
+            if self._state in (self._CANCELLED, self._FINISHED):
+                return
+            self._value, self._error, self._state = value, error, self._FINISHED
+            ev, cbs, self._callbacks = self._event, self._callbacks, None
+        if ev is not None:
+            ev.set()
+        for fn in cbs or ():
+            try:
+                fn(self)
+            except Exception:       # a callback's failure is its own
+                pass
+
+    def set_result(self, value) -> None:
+        self._finish(value, None)
+
+    def set_exception(self, error: BaseException) -> None:
+        self._finish(None, error)
+
+    # ---- consumer side
+    def cancel(self) -> bool:
+        with _FUTURE_LOCK:
+            if self._state in (self._RUNNING, self._FINISHED):
+                return False
+            self._state = self._CANCELLED
+            ev, cbs, self._callbacks = self._event, self._callbacks, None
+        if ev is not None:
+            ev.set()
+        for fn in cbs or ():
+            try:
+                fn(self)
+            except Exception:
+                pass
+        return True
+
+    def cancelled(self) -> bool:
+        return self._state == self._CANCELLED
+
+    def running(self) -> bool:
+        return self._state == self._RUNNING
+
+    def done(self) -> bool:
+        return self._state in (self._CANCELLED, self._FINISHED)
+
+    def _wait(self, timeout: Optional[float]) -> None:
+        with _FUTURE_LOCK:
+            if self._state in (self._CANCELLED, self._FINISHED):
+                return
+            if self._event is None:
+                self._event = threading.Event()
+            ev = self._event
+        if not ev.wait(timeout):
+            raise TimeoutError("the request has not finished in time")
+
+    def result(self, timeout: Optional[float] = None):
+        self._wait(timeout)
+        if self._state == self._CANCELLED:
+            from concurrent.futures import CancelledError
+            raise CancelledError()
+        if self._error is not None:
+            raise self._error
+        return self._value
+
+    def exception(self, timeout: Optional[float] = None) -> Optional[BaseException]:
+        self._wait(timeout)
+        if self._state == self._CANCELLED:
+            from concurrent.futures import CancelledError
+            raise CancelledError()
+        return self._error
+
+    def add_done_callback(self, fn) -> None:
+        with _FUTURE_LOCK:
+            if self._state not in (self._CANCELLED, self._FINISHED):
+                self._callbacks = (self._callbacks or []) + [fn]
+                return
+        fn(self)
+
+
 class _Item:
     __slots__ = ("payload", "future")
 
-    def __init__(self, payload: Any, future: Future):
+    def __init__(self, payload: Any, future: "RequestFuture"):
         self.payload, self.future = payload, future
 
 
@@ -277,12 +383,12 @@ class Scheduler:
         return [w for w in self.workers if w.alive]
 
     def submit_many(self, payloads: Sequence[Any], timeout: Optional[float] = None,
-                    together: bool = False) -> List[Future]:
+                    together: bool = False) -> List[RequestFuture]:
         """Enqueues the payloads in one call. ``timeout`` (seconds) is a deadline for leaving the queue: a request
         still waiting when it passes fails with ``TimeoutError`` and is never run. ``together`` sends the whole
         burst to one worker (the least loaded one), keeping its requests adjacent in the executed batches."""
         n = len(payloads)
-        futs = [Future() for _ in range(n)]
+        futs = [RequestFuture() for _ in range(n)]
         if n == 0:
             return futs
         tickets = (_I64 * n)()
@@ -303,7 +409,7 @@ class Scheduler:
                 f.set_exception(RuntimeError(msg))
         return futs
 
-    def submit(self, payload: Any, timeout: Optional[float] = None) -> Future:
+    def submit(self, payload: Any, timeout: Optional[float] = None) -> RequestFuture:
         return self.submit_many([payload], timeout)[0]
 
     def infer(self, payload: Any, timeout: Optional[float] = None) -> Any:

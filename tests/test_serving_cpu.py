@@ -204,3 +204,46 @@ def test_simple_server_routes():
     assert c.post("/add", json={"data": {"values": ["x", 1]}}).status_code == 400
     assert c.post("/add", json={"nope": 1}).status_code == 422
     assert c.get("/health").json()["models"] == ["add"]
+
+
+def test_request_future_semantics():
+    """The scheduler's light future behaves like concurrent.futures.Future where callers can see it."""
+    import concurrent.futures as cf
+    from fastdeploy_b200.serving.scheduler import RequestFuture
+    f = RequestFuture()
+    assert not f.done() and not f.running() and not f.cancelled()
+    with pytest.raises(TimeoutError):
+        f.result(0.01)
+    seen = []
+    f.add_done_callback(lambda fut: seen.append(fut.result()))
+    assert f.set_running_or_notify_cancel() and f.running() and not f.cancel()      # a running request stays
+    threading.Timer(0.02, lambda: f.set_result(41)).start()
+    assert f.result(5) == 41 and f.done() and seen == [41] and f.exception() is None
+    f.set_result(99)                                                                # a second result is ignored
+    assert f.result() == 41
+    late = []
+    f.add_done_callback(lambda fut: late.append(1))                                 # already done: called at once
+    assert late == [1]
+    g = RequestFuture()
+    g.set_exception(ValueError("boom"))
+    assert isinstance(g.exception(), ValueError)
+    with pytest.raises(ValueError):
+        g.result()
+    h = RequestFuture()
+    waiter = threading.Thread(target=lambda: seen.append("woken" if h.cancelled() or _wait_cancel(h) else "no"))
+    waiter.start()
+    time.sleep(0.02)
+    assert h.cancel() and h.cancelled() and h.done() and not h.set_running_or_notify_cancel()
+    waiter.join(5)
+    assert "woken" in seen
+    with pytest.raises(cf.CancelledError):
+        h.result()
+
+
+def _wait_cancel(fut):
+    import concurrent.futures as cf
+    try:
+        fut.result(5)
+    except cf.CancelledError:
+        return True
+    return False
