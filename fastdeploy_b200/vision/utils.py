@@ -34,23 +34,53 @@ def _iou_one_to_many(b, boxes):
     return inter / np.maximum(a + areas - inter, 1e-12)
 
 
-def nms(result, iou_threshold: float = 0.5) -> None:
-    """In-place hard NMS on a DetectionResult / FaceDetectionResult sorted by score
-    (fastdeploy/vision/utils/nms.cc:24-145)."""
-    if not result.boxes:
-        return
-    order = np.argsort(-np.asarray(result.scores), kind="stable")
-    boxes = np.asarray(result.boxes, np.float32)[order]
+def nms_indices(boxes: np.ndarray, scores: np.ndarray, iou_threshold: float = 0.5, max_keep: int = 0) -> np.ndarray:
+    """Indices kept by greedy hard NMS over ``boxes [n, 4]`` (x1, y1, x2, y2), visited in descending, stable score
+    order. Runs in the native host library (csrc/cpu/vision_utils.cc); the numpy loop below is the fallback when the
+    library is not built and the oracle of its test."""
+    boxes = np.ascontiguousarray(boxes, np.float32).reshape(-1, 4)
+    scores = np.ascontiguousarray(scores, np.float32).reshape(-1)
+    n = len(scores)
+    if n == 0:
+        return np.zeros(0, np.int64)
+    from .. import _native
+    if _native.cpu_available():
+        import ctypes
+        lib = _native.cpu()
+        if not getattr(lib, "_fdv_ready", False):
+            P = ctypes.c_void_p
+            lib.fdv_hard_nms.restype = ctypes.c_longlong
+            lib.fdv_hard_nms.argtypes = [P, P, ctypes.c_longlong, ctypes.c_float, ctypes.c_longlong, P]
+            lib._fdv_ready = True
+        keep = np.empty(n, np.int64)
+        k = lib.fdv_hard_nms(boxes.ctypes.data, scores.ctypes.data, n, float(iou_threshold), int(max_keep), keep.ctypes.data)
+        return keep[:k]
+    return _nms_indices_numpy(boxes, scores, iou_threshold, max_keep)
+
+
+def _nms_indices_numpy(boxes: np.ndarray, scores: np.ndarray, iou_threshold: float, max_keep: int = 0) -> np.ndarray:
+    order = np.argsort(-scores, kind="stable")
+    sorted_boxes = boxes[order]
     keep = []
     suppressed = np.zeros(len(order), bool)
     for i in range(len(order)):
         if suppressed[i]:
             continue
         keep.append(i)
+        if max_keep > 0 and len(keep) >= max_keep:
+            break
         if i + 1 < len(order):
-            iou = _iou_one_to_many(boxes[i], boxes[i + 1:])
+            iou = _iou_one_to_many(sorted_boxes[i], sorted_boxes[i + 1:])
             suppressed[i + 1:] |= iou > iou_threshold
-    idx = order[keep]
+    return order[keep].astype(np.int64)
+
+
+def nms(result, iou_threshold: float = 0.5) -> None:
+    """In-place hard NMS on a DetectionResult / FaceDetectionResult sorted by score
+    (fastdeploy/vision/utils/nms.cc:24-145)."""
+    if not result.boxes:
+        return
+    idx = nms_indices(np.asarray(result.boxes, np.float32), np.asarray(result.scores, np.float32), iou_threshold)
     result.boxes = [result.boxes[i] for i in idx]
     result.scores = [result.scores[i] for i in idx]
     if isinstance(result, DetectionResult):

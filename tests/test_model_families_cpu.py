@@ -228,3 +228,17 @@ def test_ser_vi_layoutxlm_runs_a_model_end_to_end(tmp_path):
     assert by_hand.pred == res.pred and by_hand.pred_id == res.pred_id
     two = m.batch_predict([page, page], [lines, lines[:2]])
     assert two[0].pred == res.pred and two[1].pred == res.pred[:2] or len(two[1].pred) == 2
+
+
+def test_native_hard_nms_matches_the_numpy_scan():
+    rng = np.random.default_rng(5)
+    for n, thr in ((1, 0.5), (50, 0.3), (800, 0.6)):
+        c = rng.random((n, 2)) * 100
+        wh = rng.random((n, 2)) * 30 + 2
+        boxes = np.concatenate([c - wh / 2, c + wh / 2], 1).astype(np.float32)
+        scores = np.round(rng.random(n), 1).astype(np.float32)                 # many ties: the order must be stable
+        got = U.nms_indices(boxes, scores, thr)
+        want = U._nms_indices_numpy(boxes, scores, thr)
+        assert np.array_equal(got, want)
+        assert np.array_equal(U.nms_indices(boxes, scores, thr, max_keep=3), want[:3])
+    assert U.nms_indices(np.zeros((0, 4), np.float32), np.zeros(0, np.float32)).size == 0
