@@ -116,3 +116,82 @@ def eval_segmentation(model, samples: Iterable[Tuple[np.ndarray, np.ndarray]], n
     present = union > 0
     return {"miou": float((inter[present] / union[present]).mean()) if present.any() else 0.0,
             "acc": float(inter.sum() / max(conf.sum(), 1))}
+
+
+# ---------------------------------------------------------------------------- OCR (tests/acc_eval/ppocr in the reference)
+def ocr_detection_hmean(predictions: List[Sequence[Sequence[float]]], ground_truth: List[Sequence[Sequence[float]]],
+                        iou_thr: float = 0.5) -> Dict[str, float]:
+    """ICDAR-style detection score. Both lists are per image lists of quadrilaterals (8 numbers, x0 y0 ... x3 y3).
+    A prediction matches an unmatched ground-truth box when their polygon IoU is at least ``iou_thr`` (greedy, in
+    prediction order, best IoU first); precision, recall and their harmonic mean are over the whole set."""
+    from ..ops.perception import quad_iou_numpy
+    matched = n_pred = n_gt = 0
+    for preds, gts in zip(predictions, ground_truth):
+        preds = [np.asarray(p, np.float64).reshape(4, 2) for p in preds]
+        gts = [np.asarray(g, np.float64).reshape(4, 2) for g in gts]
+        n_pred += len(preds)
+        n_gt += len(gts)
+        taken = set()
+        for p in preds:
+            best, best_j = 0.0, -1
+            for j, g in enumerate(gts):
+                if j in taken:
+                    continue
+                v = float(quad_iou_numpy(p, g))
+                if v > best:
+                    best, best_j = v, j
+            if best_j >= 0 and best >= iou_thr:
+                taken.add(best_j)
+                matched += 1
+    precision = matched / n_pred if n_pred else 0.0
+    recall = matched / n_gt if n_gt else 0.0
+    hmean = 2 * precision * recall / (precision + recall) if precision + recall > 0 else 0.0
+    return {"precision": precision, "recall": recall, "hmean": hmean}
+
+
+def edit_distance(a: str, b: str) -> int:
+    """Levenshtein distance (insert, delete, substitute at cost one)."""
+    if len(a) < len(b):
+        a, b = b, a
+    prev = list(range(len(b) + 1))
+    for i, ca in enumerate(a, 1):
+        cur = [i]
+        for j, cb in enumerate(b, 1):
+            cur.append(min(prev[j] + 1, cur[j - 1] + 1, prev[j - 1] + (ca != cb)))
+        prev = cur
+    return prev[-1]
+
+
+def ocr_recognition_metrics(predictions: Sequence[str], ground_truth: Sequence[str], ignore_case: bool = False,
+                            ignore_space: bool = True) -> Dict[str, float]:
+    """Exact-match accuracy and 1 - normalised edit distance over text lines."""
+    def norm(t: str) -> str:
+        t = t.replace(" ", "") if ignore_space else t
+        return t.lower() if ignore_case else t
+    correct, ned = 0, 0.0
+    for p, g in zip(predictions, ground_truth):
+        p, g = norm(p), norm(g)
+        correct += p == g
+        ned += edit_distance(p, g) / max(len(p), len(g), 1)
+    n = max(len(ground_truth), 1)
+    return {"acc": correct / n, "norm_edit_dis": 1.0 - ned / n}
+
+
+def eval_ocr(pipeline, samples: Iterable[Tuple[np.ndarray, Sequence[Sequence[float]], Sequence[str]]]) -> Dict[str, float]:
+    """``samples`` yields (image, ground-truth quadrilaterals, their texts). Detection is scored over all boxes;
+    recognition over the predicted boxes that matched a ground-truth box (IoU >= 0.5), text against text."""
+    from ..ops.perception import quad_iou_numpy
+    all_p, all_g, texts_p, texts_g = [], [], [], []
+    for im, quads, texts in samples:
+        r = pipeline.predict(im)
+        all_p.append(r.boxes)
+        all_g.append(list(quads))
+        for box, text in zip(r.boxes, r.text):
+            ious = [float(quad_iou_numpy(np.asarray(box, np.float64).reshape(4, 2), np.asarray(q, np.float64).reshape(4, 2)))
+                    for q in quads]
+            if ious and max(ious) >= 0.5:
+                texts_p.append(text)
+                texts_g.append(texts[int(np.argmax(ious))])
+    out = ocr_detection_hmean(all_p, all_g)
+    out.update({"rec_" + k: v for k, v in ocr_recognition_metrics(texts_p, texts_g).items()})
+    return out

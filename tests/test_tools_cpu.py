@@ -55,3 +55,25 @@ def test_model_zoo_benchmark_driver_on_cpu(tmp_path):
     assert "End2End(ms):" in text and "cpu_rss_mb:" in text
     res = model_zoo.run_benchmark("ernie", dict(cfg, profile_mode="runtime", collect_memory_info="false", warmup="1", repeat="2"))
     assert res["Runtime(ms)"] > 0
+
+
+def test_ocr_evaluation_metrics():
+    sq = lambda x, y, s: [x, y, x + s, y, x + s, y + s, x, y + s]
+    gt = [[sq(0, 0, 10), sq(20, 0, 10)], [sq(5, 5, 10)]]
+    pred = [[sq(1, 0, 10), sq(50, 50, 10), sq(20, 1, 10)], []]            # two hits, one false alarm, one image missed
+    m = EV.ocr_detection_hmean(pred, gt)
+    assert abs(m["precision"] - 2 / 3) < 1e-9 and abs(m["recall"] - 2 / 3) < 1e-9 and abs(m["hmean"] - 2 / 3) < 1e-9
+    assert EV.ocr_detection_hmean([[sq(0, 0, 10)]], [[sq(6, 0, 10)]])["hmean"] == 0.0       # IoU 0.25 < 0.5
+    assert EV.edit_distance("kitten", "sitting") == 3 and EV.edit_distance("", "abc") == 3
+    r = EV.ocr_recognition_metrics(["he llo", "wrld", "X"], ["hello", "world", "x"])
+    assert abs(r["acc"] - 1 / 3) < 1e-9 and abs(r["norm_edit_dis"] - (1 - (0 + 0.2 + 1.0) / 3)) < 1e-9
+    assert EV.ocr_recognition_metrics(["X"], ["x"], ignore_case=True)["acc"] == 1.0
+
+    class FakeOCR:
+        def predict(self, im):
+            from fastdeploy_b200.vision.result import OCRResult
+            r = OCRResult()
+            r.boxes, r.text = [sq(0, 0, 10), sq(40, 40, 8)], ["abc", "zzz"]
+            return r
+    out = EV.eval_ocr(FakeOCR(), [(np.zeros((64, 64, 3), np.uint8), [sq(0, 1, 10)], ["abd"])])
+    assert out["recall"] == 1.0 and out["precision"] == 0.5 and out["rec_acc"] == 0.0 and abs(out["rec_norm_edit_dis"] - 2 / 3) < 1e-9
