@@ -4,7 +4,45 @@
 // into one CUDA graph after the first run. Plain C ABI (fdplan_*), plus a command-line tool when compiled with
 // -DFDPLAN_MAIN. The reference's counterpart is its C++ runtime loading a serialised engine
 // (fastdeploy/runtime/backends/tensorrt/trt_backend.cc:61-114).
+#ifdef FDPLAN_HOST_ONLY
+// Test build without a GPU: device memory is host memory, streams and graphs are immediate. It exists so that the
+// file reader, the address relocation, the pointer tables and the input / output staging can be exercised against a
+// stand-in kernel library on a machine that has no device (tests/test_plan_runner_host_cpu.py).
+#include <stdlib.h>
+#include <string.h>
+typedef int cudaError_t;
+typedef void* cudaStream_t;
+typedef void* cudaGraph_t;
+typedef void* cudaGraphExec_t;
+typedef void* cudaEvent_t;
+enum { cudaSuccess = 0, cudaMemcpyHostToDevice = 1, cudaMemcpyDeviceToHost = 2, cudaStreamNonBlocking = 1,
+       cudaStreamCaptureModeThreadLocal = 1 };
+static cudaError_t cudaMalloc(void** p, size_t n) { *p = malloc(n ? n : 1); return *p ? 0 : 2; }
+static cudaError_t cudaFree(void* p) { free(p); return 0; }
+static cudaError_t cudaMemcpy(void* d, const void* s, size_t n, int) { memcpy(d, s, n); return 0; }
+static cudaError_t cudaMemcpyAsync(void* d, const void* s, size_t n, int, cudaStream_t) { memcpy(d, s, n); return 0; }
+static cudaError_t cudaMemset(void* d, int v, size_t n) { memset(d, v, n); return 0; }
+static cudaError_t cudaStreamCreateWithFlags(cudaStream_t* s, unsigned) { *s = nullptr; return 0; }
+static cudaError_t cudaStreamDestroy(cudaStream_t) { return 0; }
+static cudaError_t cudaStreamSynchronize(cudaStream_t) { return 0; }
+static cudaError_t cudaDeviceSynchronize() { return 0; }
+static cudaError_t cudaGetLastError() { return 0; }
+static const char* cudaGetErrorString(cudaError_t) { return "host-only build"; }
+// no capture on the host: the "graph" stays null and every run walks the launch list
+static cudaError_t cudaStreamBeginCapture(cudaStream_t, int) { return 1; }
+static cudaError_t cudaStreamEndCapture(cudaStream_t, cudaGraph_t* g) { *g = nullptr; return 1; }
+static cudaError_t cudaGraphInstantiate(cudaGraphExec_t*, cudaGraph_t, unsigned long long) { return 1; }
+static cudaError_t cudaGraphDestroy(cudaGraph_t) { return 0; }
+static cudaError_t cudaGraphExecDestroy(cudaGraphExec_t) { return 0; }
+static cudaError_t cudaGraphLaunch(cudaGraphExec_t, cudaStream_t) { return 1; }
+static cudaError_t cudaEventCreate(cudaEvent_t*) { return 0; }
+static cudaError_t cudaEventRecord(cudaEvent_t, cudaStream_t) { return 0; }
+static cudaError_t cudaEventSynchronize(cudaEvent_t) { return 0; }
+static cudaError_t cudaEventElapsedTime(float* ms, cudaEvent_t, cudaEvent_t) { *ms = 0.f; return 0; }
+static cudaError_t cudaEventDestroy(cudaEvent_t) { return 0; }
+#else
 #include <cuda_runtime.h>
+#endif
 #include <dlfcn.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -16,6 +54,12 @@
 #define FDPLAN_API extern "C" __attribute__((visibility("default")))
 
 namespace {
+
+#ifdef FDPLAN_HOST_ONLY
+constexpr bool kHostOnly = true;
+#else
+constexpr bool kHostOnly = false;
+#endif
 
 thread_local std::string g_error;
 void fail(const std::string& m) { g_error = m; }
@@ -283,7 +327,7 @@ FDPLAN_API int fdplan_run(void* h) {
   auto* p = static_cast<LoadedPlan*>(h);
   if (p->graph != nullptr) {
     if (cudaGraphLaunch(p->graph, p->stream) != cudaSuccess) { fail("graph launch failed"); return -1; }
-  } else if (!p->ran_once) {
+  } else if (!p->ran_once || kHostOnly) {
     if (p->plan_run(p->plan, p->stream) != 0) { fail(p->last_error()); return -1; }
     p->ran_once = true;
   } else {
@@ -319,7 +363,10 @@ FDPLAN_API double fdplan_time(void* h, int iters) {
   cudaEvent_t e0, e1;
   cudaEventCreate(&e0); cudaEventCreate(&e1);
   cudaEventRecord(e0, p->stream);
-  for (int k = 0; k < iters; ++k) cudaGraphLaunch(p->graph, p->stream);
+  for (int k = 0; k < iters; ++k) {
+    if (p->graph != nullptr) cudaGraphLaunch(p->graph, p->stream);
+    else if (p->plan_run(p->plan, p->stream) != 0) break;
+  }
   cudaEventRecord(e1, p->stream);
   float ms = -1.f;
   if (cudaEventSynchronize(e1) == cudaSuccess) cudaEventElapsedTime(&ms, e0, e1);
