@@ -10,7 +10,7 @@ from typing import Any, Dict, List
 
 import numpy as np
 
-from ..ir.graph import Graph, Node, ValueInfo
+from ..ir.graph import Graph, Node, ValueInfo, body_outer_refs
 from . import protowire as pw
 
 # ---- TensorProto.DataType <-> numpy
@@ -151,6 +151,14 @@ def _graph_from_msg(g: Dict[str, Any], opset: int) -> Graph:
         graph.value_info[vi.name] = vi
     for n in g.get("node", []):
         attrs = {a["name"]: _attr_value(a) for a in n.get("attribute", [])}
+        bodies = [a for a in attrs.values() if isinstance(a, Graph)]
+        if bodies and "outer_refs" not in attrs:
+            # Loop / If from another exporter: note what the bodies read from this scope, so that pruning and
+            # sorting see those dependencies
+            refs: List[str] = []
+            for b in bodies:
+                refs += [r for r in body_outer_refs(b) if r not in refs]
+            attrs["outer_refs"] = refs
         graph.nodes.append(Node(n.get("op_type", ""), list(n.get("input", [])), list(n.get("output", [])), attrs,
                                 n.get("name", ""), n.get("domain", "")))
     return graph

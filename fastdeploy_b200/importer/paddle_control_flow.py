@@ -20,7 +20,7 @@ from typing import Dict, List, Optional, Sequence, Set
 
 import numpy as np
 
-from ..ir.graph import Graph, Node, ValueInfo
+from ..ir.graph import Graph, Node, ValueInfo, body_outer_refs
 from .paddle_format import PaddleOp, PaddleProgram, PaddleVar
 
 CONTROL_OPS = ("while", "conditional_block", "select_input")
@@ -99,19 +99,7 @@ def _import_block(ctx, block_idx: int, body: Graph, renamer: Renamer, mappers) -
     ctx.g._uid = body._uid
 
 
-def _outer_refs(body: Graph) -> List[str]:
-    """Names a body graph reads that it neither defines nor takes as an input (nested bodies included)."""
-    defined = set(body.initializers) | {v.name for v in body.inputs} | {""}
-    refs: List[str] = []
-    for n in body.nodes:
-        for i in list(n.inputs) + list(n.attrs.get("outer_refs", [])):
-            if i not in defined and i not in refs:
-                refs.append(i)
-        defined.update(n.outputs)
-    for v in body.outputs:
-        if v.name not in defined and v.name not in refs:
-            refs.append(v.name)
-    return refs
+_outer_refs = body_outer_refs
 
 
 def map_while(ctx, op: PaddleOp, mappers) -> None:

@@ -43,6 +43,23 @@ class Node:
         return self.attrs.get(key, default)
 
 
+def body_outer_refs(body: "Graph") -> List[str]:
+    """Names that a Loop / If body graph reads from the enclosing scope: what it neither defines nor takes as an
+    input (bodies nested inside it included)."""
+    defined = set(body.initializers) | {v.name for v in body.inputs} | {""}
+    refs: List[str] = []
+    for n in body.nodes:
+        nested = [r for a in n.attrs.values() if isinstance(a, Graph) for r in body_outer_refs(a)]
+        for i in list(n.inputs) + list(n.attrs.get("outer_refs", [])) + nested:
+            if i not in defined and i not in refs:
+                refs.append(i)
+        defined.update(n.outputs)
+    for v in body.outputs:
+        if v.name not in defined and v.name not in refs:
+            refs.append(v.name)
+    return refs
+
+
 class Graph:
     def __init__(self, name: str = "graph", opset: int = 11):
         self.name = name

@@ -120,3 +120,29 @@ def test_gpu_lowering_refuses_control_flow_with_a_clear_message():
     from fastdeploy_b200.runtime.native_backend import build_plan
     with pytest.raises(NotImplementedError, match="control flow"):
         build_plan(g, {"x": [2, 3], "n": [1]}, "cpu")
+
+
+def test_onnx_loop_with_trip_count_and_scan_outputs():
+    """ONNX Loop semantics beyond what Paddle's while needs: a trip count, no condition input, scan outputs."""
+    from fastdeploy_b200.ir.graph import Graph, ValueInfo
+    body = Graph("body", 13)
+    body.inputs += [ValueInfo("it", "int64", []), ValueInfo("c_in", "bool", []), ValueInfo("acc_in", "float32", [2])]
+    body.add_node("Cast", ["it"], ["it_f"], to=1)
+    body.add_node("Add", ["acc_in", "it_f"], ["acc_out"])
+    body.add_node("Mul", ["acc_out", "outer_scale"], ["scan0"])               # reads the enclosing scope
+    body.add_node("Identity", ["c_in"], ["c_out"])
+    body.outputs += [ValueInfo("c_out", "bool", []), ValueInfo("acc_out", "float32", [2]), ValueInfo("scan0", "float32", [2])]
+    g = Graph("main", 13)
+    g.inputs.append(ValueInfo("x", "float32", [2]))
+    g.initializers["trips"] = np.asarray(4, np.int64)
+    g.initializers["outer_scale"] = np.asarray([10.0, 100.0], np.float32)
+    g.add_node("Loop", ["trips", "", "x"], ["acc", "scans"], body=body)       # no outer_refs: the reader works them out
+    g.outputs += [ValueInfo("acc", "float32", [2]), ValueInfo("scans", "float32", [4, 2])]
+    g2 = load_onnx(save_onnx(g))
+    out = Interpreter(g2).run({"x": np.asarray([1.0, 2.0], np.float32)})
+    assert out["acc"].tolist() == [7.0, 8.0]                                   # + 0 + 1 + 2 + 3
+    want = np.asarray([[1, 2], [2, 3], [4, 5], [7, 8]], np.float32) * np.asarray([10.0, 100.0], np.float32)
+    assert np.allclose(out["scans"].numpy(), want)
+    assert g2.nodes[0].attr("outer_refs") == ["outer_scale"]
+    g2.prune()
+    assert "outer_scale" in g2.initializers
