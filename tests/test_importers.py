@@ -123,3 +123,41 @@ def test_paddle_importer_rejects_unknown_op():
     with pytest.raises(NotImplementedError):
         load_paddle(*b.serialize())
     assert len(supported_paddle_ops()) >= 120
+
+
+def test_converter_entry_points():
+    """export / is_exportable / readers / remove_multiclass_nms / fp16 conversion, as the reference's converter offers."""
+    from fastdeploy_b200 import importer as I
+    from fastdeploy_b200.ir.interp import Interpreter
+    from fastdeploy_b200.models.ppyoloe import build_ppyoloe
+    net = build_ppyoloe("tiny", image=64, num_classes=4, with_nms=True, score_threshold=0.05)
+    model, params = net.serialize()
+    assert I.is_exportable(model, params) and I.unsupported_ops(model) == []
+    pr = I.PaddleReader(model)
+    assert [t.name for t in pr.inputs] == ["image", "scale_factor"] and pr.num_outputs == 2 and pr.has_nms
+    assert not pr.is_quantize_model and pr.inputs[0].shape[1:] == [3, 64, 64]
+    onnx_bytes = I.export(model, params)
+    orr = I.OnnxReader(onnx_bytes)
+    assert orr.num_inputs == 2 and orr.num_outputs == 2 and orr.inputs[0].dtype == "float32"
+    cut, p = I.remove_multiclass_nms(onnx_bytes)
+    assert p is not None and abs(p.score_threshold - 0.05) < 1e-9 and p.keep_top_k > 0
+    g = I.load_onnx(cut)
+    assert not any(n.op == "MultiClassNMS" for n in g.nodes) and len(g.outputs) == 2
+    x = np.random.RandomState(0).rand(1, 3, 64, 64).astype(np.float32)
+    out = Interpreter(g).run({"image": x, "scale_factor": np.ones((1, 2), np.float32)})
+    boxes, scores = (out[v.name].numpy() for v in g.outputs)
+    assert boxes.shape[0] == 1 and boxes.shape[-1] == 4 and scores.shape[1] == 4          # [N, M, 4] and [N, C, M]
+    again, none = I.remove_multiclass_nms(cut)
+    assert none is None and again == cut
+    half = I.convert_fp32_to_fp16(cut)
+    gh = I.load_onnx(half)
+    assert any(v.dtype == np.float16 for v in gh.initializers.values())
+    out_h = Interpreter(gh).run({"image": x, "scale_factor": np.ones((1, 2), np.float32)})
+    assert np.abs(out_h[g.outputs[1].name].float().numpy() - scores).max() < 5e-2
+    # an operator the importer does not know makes the model non-exportable, and is named
+    from fastdeploy_b200.importer.paddle_format import ProgramBuilder
+    b = ProgramBuilder()
+    xin = b.feed("x", "float32", [1, 4])
+    b.fetch(b.op("some_future_op", {"X": [xin]}, ("Out",), [1, 4]))
+    m2, _ = b.serialize()
+    assert not I.is_exportable(m2) and I.unsupported_ops(m2) == ["some_future_op"]
