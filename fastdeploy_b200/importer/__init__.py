@@ -83,12 +83,14 @@ def is_exportable(model: bytes, params: Optional[bytes] = None) -> bool:
 
 
 def export(model: bytes, params: Optional[bytes], enable_optimize: bool = True, export_fp16_model: bool = False,
-           input_shapes: Optional[Dict[str, Sequence[int]]] = None, keep_io_types: bool = True) -> bytes:
+           input_shapes: Optional[Dict[str, Sequence[int]]] = None, keep_io_types: bool = True,
+           custom_ops: Optional[Dict[str, str]] = None) -> bytes:
     """Paddle inference model -> ONNX model bytes. ``enable_optimize`` runs the numerically safe graph rewrites
     (constant, batch-norm and bias folding); ``export_fp16_model`` stores weights and computes in half precision with
-    casts around the operators that need fp32."""
-    g = load_paddle(model, params)
-    if enable_optimize:
+    casts around the operators that need fp32; ``custom_ops`` passes the named Paddle operators through as custom
+    nodes (the graph is then written as imported: the rewrites evaluate nodes, and a custom node has no evaluator)."""
+    g = load_paddle(model, params, custom_ops=custom_ops)
+    if enable_optimize and not custom_ops:
         from ..ir.passes import optimize
         g = optimize(g, dict(input_shapes) if input_shapes else None, level=1)
     if export_fp16_model:

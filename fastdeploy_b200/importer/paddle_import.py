@@ -755,11 +755,29 @@ def _multiclass_nms(c, op):
 
 
 # ------------------------------------------------------------------------- driver
-def import_program(prog: PaddleProgram, params: Dict[str, np.ndarray], name: str = "paddle_model") -> Graph:
+def _custom_mapper(export_name: str):
+    """A Paddle operator the caller deploys as a custom operator of its own (paddle2onnx/converter.h:24-34): it goes
+    through as one node of domain ``custom`` with every input and output in the order of the op's slots and the
+    scalar / list attributes copied."""
+    def fn(c: Ctx, op: PaddleOp):
+        ins = [a for k in sorted(op.inputs) for a in op.inputs[k]]
+        outs = [a for k in sorted(op.outputs) for a in op.outputs[k]]
+        attrs = {k: v for k, v in op.attrs.items()
+                 if isinstance(v, (bool, int, float, str)) or (isinstance(v, list) and v and not isinstance(v[0], dict))}
+        attrs["input_slots"] = [f"{k}:{len(op.inputs[k])}" for k in sorted(op.inputs)]
+        attrs["output_slots"] = [f"{k}:{len(op.outputs[k])}" for k in sorted(op.outputs)]
+        c.g.add_node(export_name, ins, outs, domain="custom", **attrs)
+    return fn
+
+
+def import_program(prog: PaddleProgram, params: Dict[str, np.ndarray], name: str = "paddle_model",
+                   custom_ops: Optional[Dict[str, str]] = None) -> Graph:
     g = Graph(name, opset=13)
     c = Ctx(prog, g)
     from . import paddle_control_flow as cf
     mappers = dict(_MAPPERS)
+    for pd_type, export_name in (custom_ops or {}).items():
+        mappers[pd_type] = _custom_mapper(export_name or pd_type)
     for name, fn in cf.CONTROL_MAPPERS.items():
         mappers[name] = (lambda f: lambda ctx, op: f(ctx, op, mappers))(fn)
     all_ops = list(prog.ops) + [op for _, ops in prog.sub_blocks for op in ops]
@@ -782,7 +800,7 @@ def import_program(prog: PaddleProgram, params: Dict[str, np.ndarray], name: str
             cf.run_op(c, op, mappers)
     else:
         for op in prog.ops:
-            _MAPPERS[op.type](c, op)
+            mappers[op.type](c, op)
     for fname in prog.fetch_names():
         v = prog.vars.get(fname)
         out_name = c.renamer.read(fname) if in_place else fname
@@ -795,10 +813,13 @@ def import_program(prog: PaddleProgram, params: Dict[str, np.ndarray], name: str
     return g
 
 
-def load_paddle(model_bytes: bytes, params_bytes: Optional[bytes], name: str = "paddle_model") -> Graph:
+def load_paddle(model_bytes: bytes, params_bytes: Optional[bytes], name: str = "paddle_model",
+                custom_ops: Optional[Dict[str, str]] = None) -> Graph:
+    """``custom_ops``: Paddle operator type -> name of the custom operator it is exported as (for operators the
+    deployment provides itself)."""
     prog = parse_program(model_bytes)
     params = parse_params(prog, params_bytes) if params_bytes else {}
-    return import_program(prog, params, name)
+    return import_program(prog, params, name, custom_ops)
 
 
 from . import paddle_ops_extra  # noqa: E402,F401  (registers the second batch of mappers)

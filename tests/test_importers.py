@@ -161,3 +161,20 @@ def test_converter_entry_points():
     b.fetch(b.op("some_future_op", {"X": [xin]}, ("Out",), [1, 4]))
     m2, _ = b.serialize()
     assert not I.is_exportable(m2) and I.unsupported_ops(m2) == ["some_future_op"]
+
+
+def test_custom_operators_pass_through_the_export():
+    from fastdeploy_b200 import importer as I
+    from fastdeploy_b200.importer.paddle_format import ProgramBuilder
+    b = ProgramBuilder()
+    x = b.feed("x", "float32", [1, 4])
+    y = b.op("relu", {"X": [x]}, ("Out",), [1, 4])
+    z = b.op("my_plugin", {"X": [y], "Aux": [x]}, ("Out",), [1, 4], radius=3, mode="fast", taps=[1, 2, 3])
+    b.fetch(b.op("scale", {"X": [z]}, ("Out",), [1, 4], scale=2.0, bias=0.0, bias_after_scale=True))
+    model, params = b.serialize()
+    assert not I.is_exportable(model)
+    g = I.load_onnx(I.export(model, params, custom_ops={"my_plugin": "MyPluginV2"}))
+    node = [n for n in g.nodes if n.op == "MyPluginV2"][0]
+    assert node.domain == "custom" and node.inputs == [x, y] and node.attr("radius") == 3 and node.attr("mode") == "fast"
+    assert node.attr("taps") == [1, 2, 3] and node.attr("input_slots") == ["Aux:1", "X:1"]
+    assert [n.op for n in g.nodes] == ["Relu", "MyPluginV2", "Mul"] or len(g.nodes) >= 3
