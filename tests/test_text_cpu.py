@@ -179,3 +179,34 @@ def test_packed_encoder_matches_padded_batches(tmp_path):
         enc.infer([(np.zeros(200, np.int64),) * 4])           # longer than max_len
     with pytest.raises(PackingError):
         pack_graph(rt.graph, 128)                             # not optimised: no fused attention node
+
+
+def test_xlm_roberta_sentencepiece_tokenizer(tmp_path):
+    """A SentencePiece model trained on the spot: ids follow the XLM-R convention, offsets point into the text, and
+    the SER pre-processor takes the tokenizer as it is."""
+    import sentencepiece as spm
+    from fastdeploy_b200.text import XLMRobertaTokenizer
+    corpus = tmp_path / "corpus.txt"
+    corpus.write_text("\n".join(["invoice number total amount due date", "name address phone email",
+                                 "the quick brown fox jumps over the lazy dog", "total 42 invoice 2024"] * 20))
+    spm.SentencePieceTrainer.train(input=str(corpus), model_prefix=str(tmp_path / "m"), vocab_size=38, model_type="unigram",
+                                   character_coverage=1.0, minloglevel=2)
+    tok = XLMRobertaTokenizer(str(tmp_path / "m.model"), max_length=64)
+    text = "invoice total 42"
+    e = tok.encode(text)
+    assert e.ids[0] == 0 and e.ids[-1] == 2 and 1 not in e.ids and len(e.ids) == len(e.offsets) == len(e.attention_mask)
+    assert all(i > 3 or i == 3 for i in e.ids[1:-1]) and max(e.ids) < tok.vocab_size
+    pieces = tok.tokenize(text)
+    assert len(pieces) == len(e.ids) - 2
+    covered = "".join(text[a:b] for a, b in e.offsets[1:-1])
+    assert covered.replace(" ", "") == text.replace(" ", "")
+    assert tok.decode(e.ids) == text
+    long = tok.encode("invoice number total amount due date " * 5, max_length=16)
+    assert len(long.ids) == 16 and long.ids[-1] == 2
+    pair = tok.encode("name", "address phone")
+    assert pair.ids.count(2) == 3 and pair.ids[0] == 0
+    from fastdeploy_b200.vision.ocr.ser import StructureV2SERViLayoutXLMPreprocessor
+    pre = StructureV2SERViLayoutXLMPreprocessor(tok, max_seq_len=32)
+    b = pre.run([{"bbox": [0, 0, 50, 10], "transcription": "invoice number"}], 100, 100)
+    n = len(tok.encode("invoice number").ids) - 2
+    assert b["segment_offset_id"] == [n] and b["input_ids"][0, 0] == 0 and b["input_ids"][0, 1 + n] == 2
