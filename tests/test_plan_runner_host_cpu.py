@@ -39,6 +39,7 @@ def libs(tmp_path_factory):
     lib.fdplan_get_output.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_ulonglong]
     lib.fdplan_time.restype = ctypes.c_double
     lib.fdplan_time.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    lib._paths = (runner, fake)
     return lib, fake.encode()
 
 
@@ -126,3 +127,32 @@ def test_corrupt_plan_files_are_refused_not_followed(libs, tmp_path):
         h = lib.fdplan_load(str(p).encode(), fake)
         assert not h, name
         assert len(lib.fdplan_last_error()) > 0, name
+
+
+def test_python_front_of_the_runner(libs, tmp_path):
+    from fastdeploy_b200.runtime.plan_runner import PlanRunner
+    lib, _ = libs
+    runner_path, fake_path = lib._paths
+    blob, w = _plan_bytes()
+    path = tmp_path / "toy.fdplan"
+    path.write_bytes(blob)
+    with PlanRunner(str(path), kernels_lib=fake_path, runner_lib=runner_path) as r:
+        assert r.num_ops == 3 and [t.name for t in r.inputs] == ["x"] and r.outputs[0].shape == [4, 6]
+        assert r.inputs[0].dtype == "float32" and "x" in repr(r.inputs[0])
+        x = np.arange(24, dtype=np.float64).reshape(4, 6)                  # converted to the plan's float32
+        out = r.infer({"x": x})[0]
+        t = 2 * x.reshape(-1) + 1
+        assert out.dtype == np.float32 and np.allclose(out.reshape(-1), t + w + t)
+        out2 = r.infer([x.astype(np.float32) * 0])[0]
+        assert np.allclose(out2.reshape(-1), 2 + w)
+        with pytest.raises(ValueError):
+            r.set_input("x", np.zeros((2, 2), np.float32))
+        with pytest.raises(KeyError):
+            r.set_input("nope", x)
+        assert r.time(2) >= 0.0
+    with pytest.raises(FileNotFoundError):
+        PlanRunner(str(tmp_path / "absent.fdplan"), kernels_lib=fake_path, runner_lib=runner_path)
+    junk = tmp_path / "junk.fdplan"
+    junk.write_bytes(b"nope")
+    with pytest.raises(RuntimeError, match="not a plan file"):
+        PlanRunner(str(junk), kernels_lib=fake_path, runner_lib=runner_path)
