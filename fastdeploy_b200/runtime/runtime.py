@@ -62,6 +62,25 @@ def load_graph(option: RuntimeOption) -> Graph:
 _PLAN_BUILD_LOCK = threading.Lock()
 
 
+_META_READY = False
+
+
+def _import_meta_kernels() -> None:
+    """Shape inference runs the graph on meta tensors. The first meta operation of a process makes PyTorch import
+    (and, without a bytecode cache, compile) its Python meta registrations and symbolic-shape modules: seconds that
+    belong to process start, not to the first plan. Doing it here keeps the plan-build time that is logged per shape
+    free of it, and says what it cost."""
+    global _META_READY
+    if _META_READY:
+        return
+    t0 = time.time()
+    torch.empty(1, device="meta") + 1
+    _META_READY = True
+    dt = time.time() - t0
+    if dt > 0.2:
+        log.info(f"PyTorch meta kernels imported in {dt:.2f}s (once per process)")
+
+
 class Runtime:
     def __init__(self, runtime_option: Optional[RuntimeOption] = None, _graph: Optional[Graph] = None):
         self.option = runtime_option or RuntimeOption()
@@ -90,6 +109,7 @@ class Runtime:
                 self.option.native_option.precision]
             self.fp8 = self.option.native_option.precision == "fp8"
             self.act_scales = self._load_quant_scales() if self.fp8 else {}
+            _import_meta_kernels()
             if self.option.trt_shapes:
                 shapes = {k: v["opt"] for k, v in self.option.trt_shapes.items()}
                 if all(vi.name in shapes for vi in self.graph.inputs):
