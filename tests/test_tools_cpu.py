@@ -77,3 +77,24 @@ def test_ocr_evaluation_metrics():
             return r
     out = EV.eval_ocr(FakeOCR(), [(np.zeros((64, 64, 3), np.uint8), [sq(0, 1, 10)], ["abd"])])
     assert out["recall"] == 1.0 and out["precision"] == 0.5 and out["rec_acc"] == 0.0 and abs(out["rec_norm_edit_dis"] - 2 / 3) < 1e-9
+
+
+def test_cpu_resnet50_benchmark_line(tmp_path):
+    """`bench.py --config resnet50_cpu` prints the benchmark line with the keys every configuration prints."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--config", "resnet50_cpu", "--steps", "5", "--warmup",
+                        "3", "--model-dir", str(tmp_path)], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    line = json.loads(p.stdout.strip().splitlines()[-1])
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "dtype", "data",
+                "config", "vs_baseline", "impl"):
+        assert key in line, key
+    assert line["unit"] == "ms" and line["higher_is_better"] is False and line["n_gpus"] == 0 and line["value"] > 0
+    assert set(line["by_threads"]) >= {"1"} and line["by_threads"]["1"]["runtime_ms"] <= line["by_threads"]["1"]["e2e_ms"] * 1.2
+    ref = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference"], capture_output=True, text=True,
+                         timeout=120)
+    out = json.loads(ref.stdout.strip().splitlines()[-1])
+    assert ref.returncode == 0 and out["impl"] == "reference" and "unavailable" in out
