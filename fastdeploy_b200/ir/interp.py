@@ -977,3 +977,4 @@ class Interpreter:
 
 
 from . import interp_extra  # noqa: E402,F401  (registers the second batch of operators)
+from . import interp_onnx_more  # noqa: E402,F401  (the rest of the standard ONNX operator set)
