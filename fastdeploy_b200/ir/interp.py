@@ -325,7 +325,7 @@ def _select_input(node, mask, *xs):
     return xs[int(mask.reshape(-1)[0])]
 
 
-@op("Loop", "If")
+@op("Loop", "If", "Scan")
 def _control_flow(node, *args):
     raise RuntimeError(f"{node.op} needs the enclosing scope: it is executed by Interpreter.run, not as a free function")
 
@@ -891,7 +891,7 @@ class Interpreter:
     # ------------------------------------------------------------------ execution
     def _exec(self, nodes, env, opset: int) -> None:
         for node in nodes:
-            if node.op in ("Loop", "If"):
+            if node.op in ("Loop", "If", "Scan"):
                 res = self._control(node, env, opset)
             else:
                 args = [env[i] for i in node.inputs]
@@ -921,6 +921,8 @@ class Interpreter:
             scope = self._body_env(body, env)
             self._exec(body.nodes, scope, opset)
             return tuple(scope[v.name] for v in body.outputs)
+        if node.op == "Scan":
+            return self._scan(node, env, opset)
         body = node.attr("body")
         m = env[node.inputs[0]] if node.inputs[0] else None
         cond_t = env[node.inputs[1]] if len(node.inputs) > 1 and node.inputs[1] else None
@@ -948,6 +950,40 @@ class Interpreter:
             it += 1
         stacked = [torch.stack(s) if s else torch.zeros(0, device=self.device) for s in scans]
         return tuple(carried) + tuple(stacked)
+
+    def _scan(self, node: Node, env, opset: int):
+        """ONNX ``Scan`` (opset 9+): ``N`` state values and ``M`` scanned inputs; the body maps
+        ``(states..., slices...)`` to ``(states..., output slices...)``; the slices of every scan output are stacked."""
+        body = node.attr("body")
+        m = int(node.attr("num_scan_inputs"))
+        args = [env[i] for i in node.inputs]
+        n = len(args) - m
+        states, scans = args[:n], args[n:]
+        in_axes = node.attr("scan_input_axes", [0] * m)
+        in_dirs = node.attr("scan_input_directions", [0] * m)
+        k_out = len(body.outputs) - n
+        out_axes = node.attr("scan_output_axes", [0] * k_out)
+        out_dirs = node.attr("scan_output_directions", [0] * k_out)
+        steps = scans[0].shape[in_axes[0]] if scans else 0
+        collected = [[] for _ in range(k_out)]
+        for t in range(steps):
+            scope = self._body_env(body, env)
+            for vi, val in zip(body.inputs[:n], states):
+                scope[vi.name] = val
+            for j, (vi, val) in enumerate(zip(body.inputs[n:], scans)):
+                idx = steps - 1 - t if in_dirs[j] else t
+                scope[vi.name] = val.select(in_axes[j], idx)
+            self._exec(body.nodes, scope, opset)
+            outs = [scope[v.name] for v in body.outputs]
+            states = outs[:n]
+            for j, o in enumerate(outs[n:]):
+                collected[j].append(o)
+        stacked = []
+        for j, parts in enumerate(collected):
+            if out_dirs[j]:
+                parts = parts[::-1]
+            stacked.append(torch.stack(parts, dim=out_axes[j]) if parts else torch.zeros(0, device=self.device))
+        return tuple(states) + tuple(stacked)
 
     def run(self, feeds: Dict[str, "np.ndarray | torch.Tensor"], outputs: Optional[Sequence[str]] = None,
             keep_all: bool = False) -> Dict[str, torch.Tensor]:

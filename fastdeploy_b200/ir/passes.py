@@ -768,7 +768,7 @@ def optimize(graph: Graph, input_shapes: Optional[Dict[str, Sequence[int]]] = No
     g = graph.clone()
     if level <= 0:
         return g
-    if any(n.op in ("Loop", "If") for n in g.nodes):
+    if any(n.op in ("Loop", "If", "Scan") for n in g.nodes):
         # the bodies of control-flow nodes read values of this scope by name: rewrites that rename or remove values
         # would have to follow them into the bodies, so such graphs run as imported
         return g

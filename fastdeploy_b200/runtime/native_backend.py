@@ -1139,8 +1139,8 @@ def build_plan(graph: Graph, input_shapes: Dict[str, Sequence[int]], device, dty
     """Optimises ``graph`` for the given shapes and lowers it to a plan on ``device``. ``fp8`` runs the linear layers on
     e4m3 operands; ``act_scales`` (tensor name -> calibrated absolute maximum) adds to the ranges the graph carries."""
     device = torch.device(device)
-    if any(n.op in ("Loop", "If") for n in graph.nodes):
-        raise NotImplementedError("graphs with control flow (Loop / If) have no static launch plan: run them on the CPU "
+    if any(n.op in ("Loop", "If", "Scan") for n in graph.nodes):
+        raise NotImplementedError("graphs with control flow (Loop / If / Scan) have no static launch plan: run them on the CPU "
                                   "path (RuntimeOption.use_cpu())")
     with torch.cuda.device(device):
         g = optimize_cached(graph, input_shapes, input_values, opt_level, dtype, cache_dir)

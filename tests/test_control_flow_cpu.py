@@ -146,3 +146,25 @@ def test_onnx_loop_with_trip_count_and_scan_outputs():
     assert g2.nodes[0].attr("outer_refs") == ["outer_scale"]
     g2.prune()
     assert "outer_scale" in g2.initializers
+
+
+def test_onnx_scan_running_sum_with_a_reversed_input():
+    """The ONNX operator's own example (running sum of the rows of x), plus a second, reversed scan input."""
+    from fastdeploy_b200.ir.graph import Graph, ValueInfo
+    body = Graph("scan_body", 13)
+    body.inputs += [ValueInfo("sum_in", "float32", [2]), ValueInfo("row", "float32", [2]), ValueInfo("rev_row", "float32", [2])]
+    body.add_node("Add", ["sum_in", "row"], ["sum_out"])
+    body.add_node("Identity", ["sum_out"], ["scan_out"])
+    body.add_node("Mul", ["rev_row", "two"], ["scaled"])
+    body.initializers["two"] = np.asarray(2.0, np.float32)
+    body.outputs += [ValueInfo("sum_out", "float32", [2]), ValueInfo("scan_out", "float32", [2]), ValueInfo("scaled", "float32", [2])]
+    g = Graph("main", 13)
+    g.inputs += [ValueInfo("init", "float32", [2]), ValueInfo("x", "float32", [3, 2])]
+    g.add_node("Scan", ["init", "x", "x"], ["final", "sums", "scaled_rev"], body=body, num_scan_inputs=2,
+               scan_input_directions=[0, 1])
+    g.outputs += [ValueInfo("final", "float32", [2]), ValueInfo("sums", "float32", [3, 2]), ValueInfo("scaled_rev", "float32", [3, 2])]
+    x = np.asarray([[1, 2], [3, 4], [5, 6]], np.float32)
+    out = Interpreter(load_onnx(save_onnx(g))).run({"init": np.zeros(2, np.float32), "x": x})
+    assert out["final"].tolist() == [9.0, 12.0]
+    assert out["sums"].tolist() == [[1, 2], [4, 6], [9, 12]]
+    assert out["scaled_rev"].tolist() == (x[::-1] * 2).tolist()
