@@ -431,3 +431,90 @@ def _multinomial(node, x):
     dt = ONNX_DT2TORCH[node.attr("dtype", 6)]
     p = torch.softmax(x.float(), dim=-1)                      # the input holds unnormalised log-probabilities
     return torch.multinomial(p, node.attr("sample_size", 1), replacement=True, generator=_generator(node)).to(dt)
+
+
+# --------------------------------------------------------------------------------------------- newer opsets (17 - 20)
+for _name, _fn in (("BitwiseAnd", torch.bitwise_and), ("BitwiseOr", torch.bitwise_or), ("BitwiseXor", torch.bitwise_xor)):
+    op(_name)((lambda f: (lambda node, a, b: f(a, b)))(_fn))
+
+
+@op("BitwiseNot")
+def _bitwise_not(node, x):
+    return torch.bitwise_not(x)
+
+
+@op("CastLike")
+def _cast_like(node, x, target):
+    return x.to(target.dtype)
+
+
+@op("Bernoulli")
+def _bernoulli(node, x):
+    dt = ONNX_DT2TORCH[node.attr("dtype")] if node.attr("dtype") is not None else x.dtype
+    return torch.bernoulli(x.float(), generator=_generator(node)).to(dt)
+
+
+def _window(node, size, a0: float, a1: float, a2: float):
+    n = int(size.reshape(-1)[0])
+    dt = ONNX_DT2TORCH[node.attr("output_datatype", 1)]
+    denom = n if node.attr("periodic", 1) else max(n - 1, 1)
+    k = torch.arange(n, dtype=torch.float64)
+    w = a0 - a1 * torch.cos(2 * math.pi * k / denom) + a2 * torch.cos(4 * math.pi * k / denom)
+    return w.to(dt)
+
+
+@op("HannWindow")
+def _hann(node, size):
+    return _window(node, size, 0.5, 0.5, 0.0)
+
+
+@op("HammingWindow")
+def _hamming(node, size):
+    return _window(node, size, 25.0 / 46.0, 21.0 / 46.0, 0.0)
+
+
+@op("BlackmanWindow")
+def _blackman(node, size):
+    return _window(node, size, 0.42, 0.5, 0.08)
+
+
+@op("CenterCropPad")
+def _center_crop_pad(node, x, shape):
+    axes = node.attr("axes", list(range(x.dim())))
+    out = x
+    for ax, want in zip(axes, _ints(shape)):
+        have = out.shape[ax]
+        if want < have:
+            start = (have - want) // 2
+            out = out.narrow(ax, start, want)
+        elif want > have:
+            before = (want - have) // 2
+            pad = [0, 0] * out.dim()
+            pad[2 * (out.dim() - 1 - ax)] = before
+            pad[2 * (out.dim() - 1 - ax) + 1] = want - have - before
+            out = F.pad(out, pad)
+    return out
+
+
+@op("Col2Im")
+def _col2im(node, x, image_shape, block_shape):
+    return F.fold(x, _ints(image_shape), _ints(block_shape), dilation=node.attr("dilations", 1),
+                  padding=node.attr("pads", [0, 0, 0, 0])[:2], stride=node.attr("strides", 1))
+
+
+@op("DFT")
+def _dft(node, x, dft_length=None, axis=None):
+    """Input [..., 1] (real) or [..., 2] (real, imaginary); the transformed axis is ``axis`` (attribute before opset 20)."""
+    ax = int(axis.reshape(-1)[0]) if axis is not None else node.attr("axis", 1)
+    n = int(dft_length.reshape(-1)[0]) if dft_length is not None else None
+    z = torch.complex(x[..., 0], x[..., 1]) if x.shape[-1] == 2 else x[..., 0].to(torch.complex64 if x.dtype == torch.float32 else torch.complex128)
+    ax = ax if ax >= 0 else ax + x.dim()
+    if node.attr("inverse", 0):
+        out = torch.fft.ifft(z, n=n, dim=ax)
+    elif node.attr("onesided", 0):
+        out = torch.fft.fft(z, n=n, dim=ax)
+        keep = out.shape[ax] // 2 + 1
+        out = out.narrow(ax, 0, keep)
+    else:
+        out = torch.fft.fft(z, n=n, dim=ax)
+    return torch.view_as_real(out).to(x.dtype)

@@ -183,3 +183,32 @@ def test_random_operators_have_the_asked_shape_type_and_range():
     logits = np.log(np.array([[0.0001, 0.0001, 0.9998]], np.float32))
     m = run("Multinomial", [logits], sample_size=20, seed=2.0)
     assert m.shape == (1, 20) and m.dtype == np.int32 and (m == 2).mean() > 0.9
+
+
+def test_newer_opset_operators():
+    a, b = np.array([12, 10, 255], np.uint8), np.array([10, 3, 15], np.uint8)
+    assert run("BitwiseAnd", [a, b]).tolist() == (a & b).tolist() and run("BitwiseOr", [a, b]).tolist() == (a | b).tolist()
+    assert run("BitwiseXor", [a, b]).tolist() == (a ^ b).tolist() and run("BitwiseNot", [a]).tolist() == (~a).tolist()
+    assert run("CastLike", [np.array([1.7, -2.2], np.float32), np.zeros(1, np.int64)]).tolist() == [1, -2]
+    bern = run("Bernoulli", [np.full((4000,), 0.25, np.float32)], seed=1.0)
+    assert bern.dtype == np.float32 and abs(bern.mean() - 0.25) < 0.03
+    n = np.array(8, np.int64)
+    assert np.allclose(run("HannWindow", [n]), np.hanning(9)[:8], atol=1e-6)                  # periodic by default
+    assert np.allclose(run("HannWindow", [n], periodic=0), np.hanning(8), atol=1e-6)
+    assert np.allclose(run("HammingWindow", [n], periodic=0), 25 / 46 - 21 / 46 * np.cos(2 * np.pi * np.arange(8) / 7), atol=1e-6)
+    assert np.allclose(run("BlackmanWindow", [n], periodic=0), np.blackman(8), atol=1e-6)
+    x = np.arange(20, dtype=np.float32).reshape(4, 5)
+    assert np.array_equal(run("CenterCropPad", [x, np.array([2, 7], np.int64)]), np.pad(x[1:3], [(0, 0), (1, 1)]))
+    img = rng.standard_normal((1, 2, 5, 5)).astype(np.float32)
+    cols = torch.nn.functional.unfold(torch.from_numpy(img), (2, 2)).numpy()
+    back = run("Col2Im", [cols, np.array([5, 5], np.int64), np.array([2, 2], np.int64)])
+    ones = torch.nn.functional.fold(torch.nn.functional.unfold(torch.ones(1, 2, 5, 5), (2, 2)), (5, 5), (2, 2)).numpy()
+    assert np.allclose(back / ones, img, atol=1e-6)
+    sig = rng.standard_normal((2, 16, 1)).astype(np.float32)
+    spec = run("DFT", [sig], axis=1)
+    ref = np.fft.fft(sig[..., 0], axis=1)
+    assert spec.shape == (2, 16, 2) and np.allclose(spec[..., 0], ref.real, atol=1e-4) and np.allclose(spec[..., 1], ref.imag, atol=1e-4)
+    half = run("DFT", [sig], axis=1, onesided=1)
+    assert half.shape == (2, 9, 2) and np.allclose(half[..., 0], ref.real[:, :9], atol=1e-4)
+    inv = run("DFT", [spec], axis=1, inverse=1)
+    assert np.allclose(inv[..., 0], sig[..., 0], atol=1e-5)
