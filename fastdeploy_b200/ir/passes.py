@@ -139,6 +139,133 @@ def set_act_scales(graph: Graph, scales: Dict[str, float]) -> None:
     graph.metadata[ACT_SCALES_KEY] = json.dumps({k: float(v) for k, v in scales.items()})
 
 
+_QLINEAR_UNARY = {"QLinearGlobalAveragePool": "GlobalAveragePool", "QLinearAveragePool": "AveragePool",
+                  "QLinearLeakyRelu": "LeakyRelu", "QLinearSigmoid": "Sigmoid", "QLinearSoftmax": "Softmax"}
+_QLINEAR_BINARY = {"QLinearAdd": "Add", "QLinearMul": "Mul"}
+
+
+def expand_qlinear(graph: Graph) -> int:
+    """Integer operators of quantised ONNX models (``QLinearConv`` / ``QLinearMatMul`` of the standard set and the
+    ``QLinear*`` operators ONNX Runtime's quantiser writes in the ``com.microsoft`` domain) rewritten as
+    ``DequantizeLinear -> float operator -> QuantizeLinear``. Constant weights become float weights here, the int32
+    bias is scaled by ``x_scale * w_scale``; the ``Quantize -> Dequantize`` pairs between consecutive layers are then
+    removed by :func:`fold_qdq`, which leaves a float graph with a calibrated range per activation - the form the
+    e4m3 path takes. The reference runs such models through ONNX Runtime's int8 kernels
+    (fastdeploy/runtime/backends/ort/ort_backend.cc:391)."""
+    changed = 0
+    for node in list(graph.nodes):
+        op_name = node.op
+        if op_name not in ("QLinearConv", "QLinearMatMul", "QLinearConcat") and op_name not in _QLINEAR_UNARY \
+                and op_name not in _QLINEAR_BINARY:
+            continue
+        new_nodes: List[Node] = []
+
+        def dq(x, s_name, z_name):
+            out = graph.unique("dq")
+            new_nodes.append(Node("DequantizeLinear", [x, s_name] + ([z_name] if z_name else []), [out], {},
+                                  graph.unique("n_DequantizeLinear")))
+            return out
+
+        def const_float(x, s_name, z_name, axis):
+            """Float value of a quantised constant (None when it is not constant)."""
+            if x not in graph.initializers or s_name not in graph.initializers:
+                return None
+            v = graph.initializers[x].astype(np.float64)
+            sc = np.asarray(graph.initializers[s_name], np.float64).reshape(-1)
+            zp = np.asarray(graph.initializers[z_name], np.float64).reshape(-1) if z_name and z_name in graph.initializers \
+                else np.zeros(1)
+            shape = [1] * v.ndim
+            if sc.size > 1:
+                shape[axis] = sc.size
+            return ((v - zp.reshape(shape if zp.size > 1 else [1] * v.ndim)) * sc.reshape(shape)).astype(np.float32)
+        i = node.inputs
+        attrs = {k: v for k, v in node.attrs.items() if not k.startswith("_")}
+        if op_name == "QLinearConv":
+            x = dq(i[0], i[1], i[2])
+            wf = const_float(i[3], i[4], i[5], 0)
+            w = graph.const(wf, prefix="w_deq") if wf is not None else dq(i[3], i[4], i[5])
+            ins = [x, w]
+            if len(i) > 8 and i[8]:
+                if i[8] not in graph.initializers or i[1] not in graph.initializers or i[4] not in graph.initializers:
+                    continue
+                bias = graph.initializers[i[8]].astype(np.float64) * float(np.asarray(graph.initializers[i[1]]).reshape(-1)[0]) * \
+                    np.asarray(graph.initializers[i[4]], np.float64).reshape(-1)
+                ins.append(graph.const(bias.astype(np.float32), prefix="b_deq"))
+            y = graph.unique("conv_f")
+            new_nodes.append(Node("Conv", ins, [y], attrs, graph.unique("n_Conv")))
+            ys, yz = i[6], i[7]
+        elif op_name == "QLinearMatMul":
+            a = dq(i[0], i[1], i[2])
+            bf = const_float(i[3], i[4], i[5], -1)
+            b = graph.const(bf, prefix="w_deq") if bf is not None else dq(i[3], i[4], i[5])
+            y = graph.unique("matmul_f")
+            new_nodes.append(Node("MatMul", [a, b], [y], {}, graph.unique("n_MatMul")))
+            ys, yz = i[6], i[7]
+        elif op_name in _QLINEAR_BINARY:
+            a, b = dq(i[0], i[1], i[2] if len(i) > 2 else ""), dq(i[3], i[4], i[5] if len(i) > 5 else "")
+            y = graph.unique("bin_f")
+            new_nodes.append(Node(_QLINEAR_BINARY[op_name], [a, b], [y], {}, graph.unique("n_" + _QLINEAR_BINARY[op_name])))
+            ys, yz = i[6], i[7] if len(i) > 7 else ""
+        elif op_name == "QLinearConcat":
+            ys, yz = i[0], i[1]
+            parts = [dq(i[k], i[k + 1], i[k + 2]) for k in range(2, len(i), 3)]
+            y = graph.unique("concat_f")
+            new_nodes.append(Node("Concat", parts, [y], {"axis": attrs.get("axis", 1)}, graph.unique("n_Concat")))
+        else:
+            if attrs.pop("channels_last", 0):
+                continue                                    # NHWC variant of the contrib pools: left as it is
+            x = dq(i[0], i[1], i[2] if len(i) > 2 else "")
+            y = graph.unique("unary_f")
+            new_nodes.append(Node(_QLINEAR_UNARY[op_name], [x], [y], attrs, graph.unique("n_" + _QLINEAR_UNARY[op_name])))
+            ys, yz = i[3], i[4] if len(i) > 4 else ""
+        new_nodes.append(Node("QuantizeLinear", [y, ys] + ([yz] if yz else []), list(node.outputs), {},
+                              graph.unique("n_QuantizeLinear")))
+        at = graph.nodes.index(node)
+        graph.nodes[at:at + 1] = new_nodes
+        changed += 1
+    if changed:
+        graph.toposort()
+    return changed
+
+
+_LAYOUT_ONLY = ("Flatten", "Reshape", "Transpose", "Squeeze", "Unsqueeze", "Identity")
+
+
+def hoist_dequantize_over_layout_ops(graph: Graph) -> int:
+    """``q -> Flatten / Reshape / Transpose / ... -> DequantizeLinear(per-tensor)``  =>  ``q -> DequantizeLinear ->
+    the same layout operator``: moving elements around commutes with a per-tensor dequantisation, and afterwards the
+    quantise / dequantise pair is adjacent and :func:`fold_qdq` can take it out."""
+    changed = 0
+    again = True
+    while again:
+        again = False
+        prod, cons = graph.producers(), graph.consumers()
+        for dq in list(graph.nodes):
+            if dq.op != "DequantizeLinear" or len(dq.inputs) < 2:
+                continue
+            sc = graph.initializers.get(dq.inputs[1])
+            if sc is None or np.asarray(sc).size != 1:
+                continue
+            view = prod.get(dq.inputs[0])
+            if view is None or view.op not in _LAYOUT_ONLY or len(cons.get(view.outputs[0], [])) != 1 or \
+                    view.outputs[0] in graph.output_names():
+                continue
+            moved = graph.unique("dq_moved")
+            new_dq = Node("DequantizeLinear", [view.inputs[0]] + list(dq.inputs[1:]), [moved], dict(dq.attrs),
+                          graph.unique("n_DequantizeLinear"))
+            new_view = Node(view.op, [moved] + list(view.inputs[1:]), list(dq.outputs), dict(view.attrs),
+                            graph.unique("n_" + view.op), view.domain)
+            at = graph.nodes.index(view)
+            graph.nodes[at] = new_dq
+            graph.nodes[graph.nodes.index(dq)] = new_view
+            changed += 1
+            again = True
+            break
+    if changed:
+        graph.toposort()
+    return changed
+
+
 def fold_qdq(graph: Graph) -> int:
     """``x -> QuantizeLinear(s) -> DequantizeLinear(s) -> consumer``  =>  ``x -> consumer`` with the calibrated range
     ``s * 127`` of ``x`` recorded for the executor, which quantises ``x`` to e4m3 with that static range when it runs
@@ -149,22 +276,47 @@ def fold_qdq(graph: Graph) -> int:
     changed = 0
     prod = graph.producers()
     scales = get_act_scales(graph)
-    for dq in list(graph.nodes):
-        if dq.op != "DequantizeLinear":
+
+    def const_scalar(name):
+        v = graph.initializers.get(name) if name else None
+        return None if v is None or np.asarray(v).size != 1 else np.asarray(v).reshape(-1)[0]
+    for q in list(graph.nodes):
+        if q.op != "QuantizeLinear" or q not in graph.nodes or q.inputs[1] not in graph.initializers:
             continue
-        q = prod.get(dq.inputs[0])
-        if q is None or q.op != "QuantizeLinear" or q.inputs[1] not in graph.initializers:
+        s_q = const_scalar(q.inputs[1])
+        if s_q is None:
+            continue                      # per-channel activation scales: keep the fake quantisation
+        readers = graph.consumers().get(q.outputs[0], [])
+        if not readers or q.outputs[0] in graph.output_names():
             continue
-        s_q = np.asarray(graph.initializers[q.inputs[1]], np.float64).reshape(-1)
-        s_d = np.asarray(graph.initializers.get(dq.inputs[1], s_q), np.float64).reshape(-1)
-        if s_q.size != 1 or s_d.size != 1 or abs(s_q[0] - s_d[0]) > 1e-12 * max(1.0, abs(s_q[0])):
-            continue                      # per-channel activation scales or a re-scaling pair: keep the fake quantisation
-        if len(graph.consumers().get(q.outputs[0], [])) != 1:
-            continue
+        zp_q = const_scalar(q.inputs[2]) if len(q.inputs) > 2 and q.inputs[2] else None
+
+        def same(dq):
+            if dq.op != "DequantizeLinear" or len(dq.inputs) < 2:
+                return False
+            s_d = const_scalar(dq.inputs[1])
+            zp_d = const_scalar(dq.inputs[2]) if len(dq.inputs) > 2 and dq.inputs[2] else None
+            return dq.op == "DequantizeLinear" and dq.inputs[0] == q.outputs[0] and s_d is not None and \
+                abs(float(s_d) - float(s_q)) <= 1e-12 * max(1.0, abs(float(s_q))) and \
+                int(zp_d if zp_d is not None else 0) == int(zp_q if zp_q is not None else 0)
+        if not all(same(dq) for dq in readers):
+            continue                      # a re-scaling pair or a reader that wants the integers: keep it
         x = q.inputs[0]
-        scales[x] = float(s_q[0]) * 127.0
-        _replace_uses(graph, dq.outputs[0], x)
-        _remove(graph, [q, dq])
+        if zp_q is not None and np.asarray(graph.initializers[q.inputs[2]]).dtype == np.uint8:
+            reach = max(int(zp_q), 255 - int(zp_q))           # asymmetric uint8: the larger side of the zero point
+        else:
+            z = int(zp_q) if zp_q is not None else 0
+            reach = max(128 + z, 127 - z) if z else 127
+        scales[x] = float(s_q) * float(reach)
+        dead = [q]
+        for dq in readers:
+            if dq.outputs[0] in graph.output_names():
+                # a graph output keeps its name: the pair becomes a plain copy of the float value
+                graph.nodes[graph.nodes.index(dq)] = Node("Identity", [x], list(dq.outputs), {}, graph.unique("n_Identity"))
+            else:
+                _replace_uses(graph, dq.outputs[0], x)
+                dead.append(dq)
+        _remove(graph, dead)
         prod = graph.producers()
         changed += 1
     if changed:
@@ -774,12 +926,14 @@ def optimize(graph: Graph, input_shapes: Optional[Dict[str, Sequence[int]]] = No
         return g
     g.toposort()
     eliminate_identity(g)
+    expand_qlinear(g)                      # before shape inference: the integer operators have no shape rules of their own
     info = None
     if input_shapes is not None:
         info = infer_shapes(g, input_shapes, input_values)
     for _ in range(4):
         if not fold_constants(g, info):
             break
+    hoist_dequantize_over_layout_ops(g)
     if fold_qdq(g):
         for _ in range(2):
             if not fold_constants(g, info):

@@ -193,3 +193,70 @@ def test_fp32_to_fp16_converter_keeps_io_and_blocked_ops():
     # without kept i/o types the graph takes and returns half precision
     h2 = convert_fp32_to_fp16(g, keep_io_types=False)
     assert h2.inputs[0].dtype == "float16"
+
+
+def test_qlinear_model_becomes_a_float_graph_with_calibrated_ranges():
+    """A quantised ONNX model in operator form (QuantizeLinear -> QLinearConv x 2 -> QLinearGlobalAveragePool ->
+    QLinearMatMul -> DequantizeLinear, with a branch through QLinearAdd): the expansion gives the same integers as
+    the integer operators, and the optimiser turns it into a float graph that stays within quantisation noise."""
+    from fastdeploy_b200.ir.graph import Graph, ValueInfo
+    from fastdeploy_b200.ir.interp import Interpreter
+    from fastdeploy_b200.ir.passes import expand_qlinear, get_act_scales, optimize
+    rng = np.random.RandomState(7)
+    g = Graph("q", 13)
+    g.inputs.append(ValueInfo("x", "float32", [2, 3, 8, 8]))
+
+    def c(name, v):
+        g.initializers[name] = np.asarray(v)
+        return name
+    xs, xz = c("xs", np.float32(0.02)), c("xz", np.uint8(128))
+    g.add_node("QuantizeLinear", ["x", xs, xz], ["xq"])
+    w1 = c("w1", rng.randint(-90, 90, (4, 3, 3, 3)).astype(np.int8))
+    w1s, w1z = c("w1s", (rng.rand(4) * 0.0005 + 0.0008).astype(np.float32)), c("w1z", np.zeros(4, np.int8))
+    b1 = c("b1", rng.randint(-3000, 3000, 4).astype(np.int32))
+    y1s, y1z = c("y1s", np.float32(0.012)), c("y1z", np.uint8(125))
+    g.add_node("QLinearConv", ["xq", xs, xz, w1, w1s, w1z, y1s, y1z, b1], ["y1q"], pads=[1, 1, 1, 1])
+    w2 = c("w2", rng.randint(-90, 90, (4, 4, 1, 1)).astype(np.int8))
+    w2s, w2z = c("w2s", np.float32(0.01)), c("w2z", np.int8(0))
+    y2s, y2z = c("y2s", np.float32(0.025)), c("y2z", np.uint8(128))
+    g.add_node("QLinearConv", ["y1q", y1s, y1z, w2, w2s, w2z, y2s, y2z], ["y2q"])
+    ys3, yz3 = c("y3s", np.float32(0.035)), c("y3z", np.uint8(127))
+    g.add_node("QLinearAdd", ["y1q", y1s, y1z, "y2q", y2s, y2z, ys3, yz3], ["y3q"], domain="com.microsoft")
+    ps, pz = c("ps", np.float32(0.03)), c("pz", np.uint8(118))
+    g.add_node("QLinearGlobalAveragePool", ["y3q", ys3, yz3, ps, pz], ["pq"], domain="com.microsoft", channels_last=0)
+    g.add_node("Flatten", ["pq"], ["fq"], axis=1)
+    w3 = c("w3", rng.randint(0, 255, (4, 5)).astype(np.uint8))
+    w3s, w3z = c("w3s", np.float32(0.004)), c("w3z", np.uint8(127))
+    os_, oz = c("os", np.float32(0.01)), c("oz", np.uint8(128))
+    g.add_node("QLinearMatMul", ["fq", ps, pz, w3, w3s, w3z, os_, oz], ["oq"])
+    g.add_node("DequantizeLinear", ["oq", os_, oz], ["out"])
+    g.outputs.append(ValueInfo("out", "float32", [2, 5]))
+    x = (rng.rand(2, 3, 8, 8).astype(np.float32) - 0.5) * 4
+
+    # (1) the expansion alone keeps the integer arithmetic to within one step of the last scale
+    e = g.clone()
+    assert expand_qlinear(e) == 5
+    assert not any(n.op.startswith("QLinear") for n in e.nodes)
+    out_e = Interpreter(e).run({"x": x})["out"].numpy()
+    # the standard-set operators exist in the interpreter: run the two convolutions of the original as a cross-check
+    head = Graph("head", 13)
+    head.inputs, head.initializers = list(g.inputs), dict(g.initializers)
+    head.nodes = [n for n in g.clone().nodes[:3]]
+    head.outputs.append(ValueInfo("y2q", "uint8", None))
+    head_e = Graph("head_e", 13)
+    head_e.inputs, head_e.initializers = list(e.inputs), dict(e.initializers)
+    head_e.nodes = list(e.clone().nodes)
+    head_e.outputs.append(ValueInfo("y2q", "uint8", None))
+    head_e.prune()
+    a = Interpreter(head).run({"x": x})["y2q"].numpy().astype(int)
+    b = Interpreter(head_e).run({"x": x})["y2q"].numpy().astype(int)
+    assert np.abs(a - b).max() <= 1
+    # (2) the optimiser leaves a float graph: no quantise / dequantise node, ranges recorded for the activations
+    f = optimize(g, {"x": [2, 3, 8, 8]}, level=2)
+    ops = {n.op for n in f.nodes}
+    assert not any(o in ops for o in ("QuantizeLinear", "DequantizeLinear", "QLinearConv", "QLinearMatMul")), ops
+    ranges = get_act_scales(f)
+    assert abs(ranges["x"] - 0.02 * 128) < 1e-6 and len(ranges) >= 5
+    out_f = Interpreter(f).run({"x": x})["out"].numpy()
+    assert out_f.shape == (2, 5) and np.abs(out_f - out_e).max() < 0.06                # a few output steps of 0.01
+    assert np.abs(out_e).max() > 0.05                                                    # (and the outputs are not all zero)
