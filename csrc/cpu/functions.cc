@@ -43,6 +43,13 @@ inline double load_f(const void* p, int dt, long long i) {
   }
 }
 
+inline long long to_int64_fwd(double v) {
+  if (v != v) return 0;
+  if (v >= 9.2233720368547748e18) return std::numeric_limits<long long>::max();
+  if (v <= -9.2233720368547758e18) return std::numeric_limits<long long>::min();
+  return static_cast<long long>(v);
+}
+
 inline long long load_i(const void* p, int dt, long long i) {
   switch (dt) {
     case kBool: case kU8: return static_cast<const uint8_t*>(p)[i];
@@ -54,13 +61,22 @@ inline long long load_i(const void* p, int dt, long long i) {
   }
 }
 
+// A floating value on its way into an integer type: NaN becomes 0 and the value is clamped to what int64 holds
+// before the conversion (converting an out-of-range double is undefined); narrowing from int64 then wraps.
+inline long long to_int64(double v) {
+  if (v != v) return 0;
+  if (v >= 9.2233720368547748e18) return std::numeric_limits<long long>::max();
+  if (v <= -9.2233720368547758e18) return std::numeric_limits<long long>::min();
+  return static_cast<long long>(v);
+}
+
 inline void store_f(void* p, int dt, long long i, double v) {
   switch (dt) {
     case kBool: static_cast<uint8_t*>(p)[i] = v != 0.0 ? 1 : 0; break;
-    case kU8: static_cast<uint8_t*>(p)[i] = static_cast<uint8_t>(v); break;
-    case kI8: static_cast<int8_t*>(p)[i] = static_cast<int8_t>(v); break;
-    case kI32: static_cast<int32_t*>(p)[i] = static_cast<int32_t>(v); break;
-    case kI64: static_cast<int64_t*>(p)[i] = static_cast<int64_t>(v); break;
+    case kU8: static_cast<uint8_t*>(p)[i] = static_cast<uint8_t>(static_cast<unsigned long long>(to_int64(v))); break;
+    case kI8: static_cast<int8_t*>(p)[i] = static_cast<int8_t>(static_cast<uint8_t>(static_cast<unsigned long long>(to_int64(v)))); break;
+    case kI32: static_cast<int32_t*>(p)[i] = static_cast<int32_t>(static_cast<uint32_t>(static_cast<unsigned long long>(to_int64(v)))); break;
+    case kI64: static_cast<int64_t*>(p)[i] = to_int64(v); break;
     case kF32: static_cast<float*>(p)[i] = static_cast<float>(v); break;
     default: static_cast<double*>(p)[i] = v; break;
   }
@@ -133,7 +149,7 @@ FDB_CPU_API int fdf_copy(const FnTensor* in, const FnTensor* out) {
   for_each<2>(in->ndim, in->shape, st, [&](const long long* o) {
     if (via_int) store_i(out->data, out->dtype, o[1], load_i(in->data, in->dtype, o[0]));
     else if (out->dtype == kBool) store_i(out->data, out->dtype, o[1], load_f(in->data, in->dtype, o[0]) != 0.0 ? 1 : 0);
-    else if (!is_float(out->dtype)) store_i(out->data, out->dtype, o[1], static_cast<long long>(std::trunc(load_f(in->data, in->dtype, o[0]))));
+    else if (!is_float(out->dtype)) store_i(out->data, out->dtype, o[1], to_int64(std::trunc(load_f(in->data, in->dtype, o[0]))));
     else store_f(out->data, out->dtype, o[1], load_f(in->data, in->dtype, o[0]));
   });
   return 0;

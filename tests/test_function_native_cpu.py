@@ -115,3 +115,13 @@ def fd_int32():
 def fd_bool():
     import fastdeploy_b200 as fd
     return fd.FDDataType.BOOL
+
+
+def test_float_to_integer_conversions_are_defined_for_every_input():
+    """NaN, infinities and values outside the target type do not depend on the compiler's mood: NaN -> 0, the value is
+    clamped to int64 and then wraps into the narrower type."""
+    import fastdeploy_b200 as fd
+    x = np.array([np.nan, np.inf, -np.inf, 300.7, -1.7, 1e30], np.float64)
+    assert _np(fn.cast(x, fd.FDDataType.INT64)).tolist() == [0, 2 ** 63 - 1, -2 ** 63, 300, -1, 2 ** 63 - 1]
+    assert _np(fn.cast(x, fd.FDDataType.UINT8)).tolist() == [0, 255, 0, 44, 255, 255]
+    assert _np(fn.cast(x, fd.FDDataType.INT32)).tolist()[3:5] == [300, -1]
