@@ -104,10 +104,28 @@ divide = _binary("divide", lambda a, b: torch.div(a, b, rounding_mode="trunc") i
 maximum = _binary("maximum", torch.maximum)
 
 
+def _native_fill(shape, value, tdtype) -> Optional[np.ndarray]:
+    """Filled natively when the type is one the host library stores and the value passes through a double unchanged."""
+    if tdtype in (torch.float16, torch.bfloat16) or tdtype.is_complex:
+        return None
+    ndt = torch.empty(0, dtype=tdtype).numpy().dtype
+    if not native.usable(np.empty(0, ndt)) or len(shape) > native.MAX_DIMS:
+        return None
+    if isinstance(value, int) and not isinstance(value, bool) and _bi.abs(value) > 2 ** 53:
+        return None
+    return native.fill(list(shape), value, ndt)
+
+
 def full(value, shape: Sequence[int], dtype: FDDataType = FDDataType.FP32, out=None):
+    a = _native_fill(shape, value, _FD2TORCH[dtype])
+    if a is not None:
+        return _nout(a, out)
     return _out(torch.full(list(shape), value, dtype=_FD2TORCH[dtype]), out)
 def full_like(x, value, dtype: Optional[FDDataType] = None, out=None):
     t = _t(x)
+    a = _native_fill(list(t.shape), value, _FD2TORCH[dtype] if dtype is not None else t.dtype) if t.device.type == "cpu" else None
+    if a is not None:
+        return _nout(a, out)
     return _out(torch.full_like(t, value, dtype=_FD2TORCH[dtype] if dtype is not None else t.dtype), out)
 
 
@@ -237,17 +255,22 @@ def argmin(x, axis: int, output_dtype: FDDataType = FDDataType.INT64, keep_dim: 
 
 def slice(x, axes: Sequence[int], starts: Sequence[int], ends: Optional[Sequence[int]] = None, out=None):   # noqa: A001
     """With ``ends``: ranges per axis; without: picks index ``starts[i]`` on ``axes[i]`` and drops the axis."""
-    t = _t(x)
+    arr = _np(x)
+    t = _t(x) if arr is None else arr
     if ends is None:
-        for a, s in sorted(zip(axes, starts), reverse=True):
-            t = t.select(a, s)
-        return _out(t, out)
-    sl = [builtins_slice(None)] * t.dim()
+        sel = [builtins_slice(None)] * len(t.shape)
+        for a, s in zip(axes, starts):
+            sel[a] = s
+        picked = t[tuple(sel)]
+        return _nout(native.materialise(picked), out) if arr is not None else _out(picked, out)
+    sl = [builtins_slice(None)] * len(t.shape)
     for a, s, e in zip(axes, starts, ends):
         dim = t.shape[a]
         s = s + dim if s < 0 else s
         e = e + dim if e < 0 else e
         sl[a] = builtins_slice(builtins_max(s, 0), builtins_min(e, dim))
+    if arr is not None:
+        return _nout(native.materialise(arr[tuple(sl)]), out)
     return _out(t[tuple(sl)], out)
 
 
@@ -279,15 +302,28 @@ def argsort(x, axis: int = -1, descending: bool = False, out=None):
 
 
 def split(x, num_or_sections: Union[int, Sequence[int]], axis: int = 0) -> List[FDTensor]:
+    arr = _np(x)
     t = _t(x)
     if isinstance(num_or_sections, int):
-        parts = torch.chunk(t, num_or_sections, dim=axis)
+        if arr is None:
+            return [_out(p) for p in torch.chunk(t, num_or_sections, dim=axis)]
+        each = -(-t.shape[axis] // num_or_sections)            # chunk: equal parts, the last one takes what is left
+        secs = [builtins_min(each, t.shape[axis] - i * each) for i in range(num_or_sections) if i * each < t.shape[axis]] or [0]
     else:
         secs = list(num_or_sections)
         if -1 in secs:
             secs[secs.index(-1)] = t.shape[axis] - _bi.sum(s for s in secs if s > 0)
-        parts = torch.split(t, secs, dim=axis)
-    return [_out(p) for p in parts]
+        if arr is None:
+            return [_out(p) for p in torch.split(t, secs, dim=axis)]
+    if _bi.sum(secs) != arr.shape[axis]:
+        raise ValueError(f"split: sections {secs} do not add up to the axis length {arr.shape[axis]}")
+    parts, at = [], 0
+    for n in secs:
+        sel = [builtins_slice(None)] * arr.ndim
+        sel[axis] = builtins_slice(at, at + n)
+        parts.append(_nout(native.materialise(arr[tuple(sel)])))
+        at += n
+    return parts
 
 
 def tile(x, repeat_times: Sequence[int], out=None):

@@ -81,6 +81,12 @@ def materialise(view: np.ndarray, dtype=None) -> np.ndarray:
     return copy(view, np.empty(view.shape, dtype or view.dtype))
 
 
+def fill(shape: Sequence[int], value: float, dtype) -> np.ndarray:
+    out = np.empty(tuple(shape), dtype)
+    _check(_lib().fdf_fill(ctypes.byref(_view(out)), float(value)), "fill")
+    return out
+
+
 def unary(op: str, x: np.ndarray, out_dtype=None, a: float = 0.0, b: float = 0.0) -> np.ndarray:
     out = np.empty(x.shape, out_dtype or x.dtype)
     _check(_lib().fdf_unary(UNARY[op], ctypes.byref(_view(x)), ctypes.byref(_view(out)), a, b), op)

@@ -125,3 +125,27 @@ def test_float_to_integer_conversions_are_defined_for_every_input():
     assert _np(fn.cast(x, fd.FDDataType.INT64)).tolist() == [0, 2 ** 63 - 1, -2 ** 63, 300, -1, 2 ** 63 - 1]
     assert _np(fn.cast(x, fd.FDDataType.UINT8)).tolist() == [0, 255, 0, 44, 255, 255]
     assert _np(fn.cast(x, fd.FDDataType.INT32)).tolist()[3:5] == [300, -1]
+
+
+def test_slice_split_and_full_run_natively_and_match_torch():
+    import torch
+    import fastdeploy_b200 as fd
+    x = np.arange(2 * 7 * 5, dtype=np.float32).reshape(2, 7, 5)
+    t = torch.from_numpy(x)
+    assert np.array_equal(_np(fn.slice(x, [1, 2], [1, -4], [6, 100])), x[:, 1:6, 1:5])
+    assert np.array_equal(_np(fn.slice(x, [0, 2], [1, 3])), x[1, :, 3])
+    assert _np(fn.slice(x, [1], [5], [2])).shape == (2, 0, 5)
+    for n in (1, 2, 3, 7, 9):
+        got = fn.split(x, n, axis=1)
+        want = torch.chunk(t, n, dim=1)
+        assert len(got) == len(want) and all(np.array_equal(_np(g), w.numpy()) for g, w in zip(got, want)), n
+    got = fn.split(x, [2, -1, 1], axis=1)
+    assert [g.shape[1] for g in got] == [2, 4, 1] and np.array_equal(_np(got[1]), x[:, 2:6])
+    with pytest.raises(ValueError, match="add up"):
+        fn.split(x, [2, 2], axis=1)
+    f = fn.full(3, [2, 3], fd.FDDataType.INT32)
+    assert _np(f).dtype == np.int32 and _np(f).tolist() == [[3, 3, 3], [3, 3, 3]]
+    assert _np(fn.full(0.25, [], fd.FDDataType.FP64)).shape == () and float(_np(fn.full(0.25, [], fd.FDDataType.FP64))) == 0.25
+    fl = fn.full_like(x, 7)
+    assert _np(fl).dtype == np.float32 and _np(fl).shape == x.shape and (_np(fl) == 7).all()
+    assert _np(fn.full_like(x, 1, fd.FDDataType.UINT8)).dtype == np.uint8
