@@ -13,7 +13,8 @@ from .runtime.model import FastDeployModel
 from .utils.log import set_logger
 from . import vision
 from . import download as _download_module  # noqa: F401
-from .download import download, download_and_decompress, download_model  # noqa: F401
+from .download import download, download_and_decompress, download_model, get_model_list  # noqa: F401
+from . import c_lib_wrap as C  # noqa: F401,N812
 
 
 def is_built_with_gpu() -> bool:

@@ -1,5 +1,5 @@
 """Download helpers with the reference's names (python/fastdeploy/download.py:30-230:
-``download``, ``download_and_decompress``, ``download_model``). This build runs without network
+``download``, ``download_and_decompress``, ``download_model``, ``get_model_list``). This build runs without network
 access: a request is served from a local directory of pre-fetched files (``FASTDEPLOY_MODEL_CACHE``,
 default ``~/.fastdeploy/models``) when the file is there and fails with a clear error otherwise, and
 ``file://`` / plain paths are copied. Archives are unpacked with the standard library."""
@@ -63,3 +63,31 @@ def download_model(name: str, path: Optional[str] = None, format: Optional[str] 
         if os.path.exists(base + ext):
             return decompress(base + ext, path or cache_dir())
     raise RuntimeError(f"model {name!r} is not in {cache_dir()} and there is no network access in this build")
+
+
+def get_model_list(category: Optional[str] = None) -> dict:
+    """The models :func:`download_model` can serve, by category (python/fastdeploy/download.py:216-237). The reference
+    asks its model hub; here the list is what the local cache holds: ``<cache>/index.json`` (``{category: [{"name": ...,
+    "format": ..., "version": ...}]}``) when present, else every directory or archive of the cache under the category
+    ``"local"``."""
+    import json
+    root = cache_dir()
+    index = os.path.join(root, "index.json")
+    if os.path.exists(index):
+        with open(index) as f:
+            listing = json.load(f)
+    else:
+        names = set()
+        for entry in sorted(os.listdir(root)) if os.path.isdir(root) else []:
+            stem = entry
+            for ext in (".tar.gz", ".tgz", ".tar", ".zip"):
+                if entry.endswith(ext):
+                    stem = entry[:-len(ext)]
+            if stem != "index.json":
+                names.add(stem)
+        listing = {"local": [{"name": n} for n in sorted(names)]} if names else {}
+    if category is None:
+        return listing
+    if category in listing:
+        return {category: listing[category]}
+    raise ValueError(f"No pretrained model in category {category} can be downloaded now.")

@@ -17,9 +17,27 @@ import numpy as np
 class FDMat:
     """HWC image with layout / device bookkeeping (fastdeploy/vision/common/processors/mat.h:34-169)."""
 
-    def __init__(self, mat: np.ndarray, layout: str = "HWC"):
+    def __init__(self, mat: Optional[np.ndarray] = None, layout: str = "HWC"):
         self.mat = mat
         self.layout = layout
+
+    def from_numpy(self, image: np.ndarray) -> "FDMat":
+        """Takes an HWC image (the array is shared, not copied)."""
+        self.mat, self.layout = np.asarray(image), "HWC"
+        return self
+
+    def numpy(self) -> np.ndarray:
+        return self.mat
+
+    def print_info(self, flag: str = "") -> str:
+        """One line with type, channels, size and the per-channel mean (fastdeploy/vision/common/processors/mat.cc:149-188)."""
+        chans = self.channels()
+        means = (self.mat.reshape(self.height(), self.width(), -1).mean((0, 1)) if self.layout == "HWC" or self.mat.ndim < 3
+                 else self.mat.reshape(chans, -1).mean(1))
+        msg = (f"{flag}: DataType={self.mat.dtype}, Channel={chans}, Height={self.height()}, Width={self.width()}, Mean="
+               + " ".join(f"{float(m):g}" for m in means))
+        print(msg)
+        return msg
 
     def height(self) -> int:
         return self.mat.shape[0] if self.layout == "HWC" else self.mat.shape[1]
@@ -32,12 +50,33 @@ class FDMat:
 
     Height, Width, Channels = height, width, channels
 
-    def print_info(self, flag: str = "") -> str:
-        m = self.mat.astype(np.float64)
-        msg = (f"{flag}: Channel={self.channels()}, height={self.height()}, width={self.width()}, "
-               f"mean=" + ", ".join(f"{v:.6f}" for v in m.reshape(-1, self.channels()).mean(0)))
-        print(msg)
-        return msg
+
+class FDMatBatch:
+    """A list of images that the processors treat as one batch
+    (fastdeploy/vision/common/processors/mat_batch.h:27-110). ``tensor()`` stacks them once every image has the same
+    shape."""
+
+    def __init__(self, mats: Optional[Sequence[FDMat]] = None):
+        self.mats: List[FDMat] = list(mats) if mats is not None else []
+        self.input_cache = None
+        self.output_cache = None
+
+    def from_mats(self, mats: Sequence) -> "FDMatBatch":
+        self.mats = [m if isinstance(m, FDMat) else FDMat(np.asarray(m)) for m in mats]
+        return self
+
+    def __len__(self) -> int:
+        return len(self.mats)
+
+    @property
+    def layout(self) -> str:
+        return "N" + (self.mats[0].layout if self.mats else "HWC")
+
+    def tensor(self) -> np.ndarray:
+        shapes = {m.mat.shape for m in self.mats}
+        if len(shapes) != 1:
+            raise ValueError(f"the images of the batch differ in shape: {sorted(shapes)}")
+        return np.stack([m.mat for m in self.mats])
 
 
 class Processor:
@@ -46,7 +85,12 @@ class Processor:
 
     Name = name
 
-    def __call__(self, mat: FDMat) -> bool:
+    def __call__(self, mat) -> bool:
+        if isinstance(mat, FDMatBatch):         # image by image, as base.cc:24-60 does without a batched kernel
+            ok = True
+            for m in mat.mats:
+                ok = self.impl(m) and ok
+            return ok
         return self.impl(mat)
 
     def impl(self, mat: FDMat) -> bool:

@@ -66,7 +66,9 @@ def _dev(arr, dtype, device):
 
 # ------------------------------------------------------------------ detection
 def vis_detection(im, result: DetectionResult, labels: Optional[Sequence[str]] = None, score_threshold: float = 0.0,
-                  line_size: int = 1, font_size: float = 0.5):
+                  line_size: int = 1, font_size: float = 0.5, font_color: Sequence[int] = (255, 255, 255), font_thickness: int = 1):
+    """Boxes (and instance masks) in the class colour; on the host path each box also gets a ``label,score`` caption in
+    ``font_color`` on a patch of the class colour (fastdeploy/vision/visualize/detection.cc:27-130)."""
     keep = [i for i, s in enumerate(result.scores) if s >= score_threshold]
     if _is_cuda(im):
         import torch
@@ -97,7 +99,12 @@ def vis_detection(im, result: DetectionResult, labels: Optional[Sequence[str]] =
             roi[mm] = (roi[mm] * 0.5 + np.asarray(c) * 0.5).astype(np.uint8)
         cv2.rectangle(out, (b[0], b[1]), (b[2], b[3]), c, line_size)
         name = labels[result.label_ids[i]] if labels and result.label_ids[i] < len(labels) else str(result.label_ids[i])
-        cv2.putText(out, f"{name},{result.scores[i]:.2f}", (b[0], max(b[1] - 2, 8)), cv2.FONT_HERSHEY_SIMPLEX, font_size, c, 1)
+        text = f"{name},{result.scores[i]:.2f}"
+        (tw, th), _ = cv2.getTextSize(text, cv2.FONT_HERSHEY_SIMPLEX, font_size, font_thickness)
+        y0 = max(b[1] - th - 2, 0)
+        cv2.rectangle(out, (b[0], y0), (b[0] + tw, y0 + th + 2), c, -1)
+        cv2.putText(out, text, (b[0], y0 + th), cv2.FONT_HERSHEY_SIMPLEX, font_size, tuple(int(v) for v in font_color),
+                    font_thickness)
     return out
 
 
@@ -321,3 +328,125 @@ def vis_ppocr(im, result: OCRResult):
 
 
 vis_ocr = vis_ppocr
+
+
+# ------------------------------------------------------------------ face alignment, head pose, 3-D boxes
+def _host_image(im):
+    """(host copy as numpy, put-back function): the drawing below is a handful of primitives, done on the host."""
+    if _is_cuda(im):
+        import torch
+        return im.cpu().numpy().copy(), lambda a: torch.as_tensor(a).to(im.device)
+    return im.copy(), lambda a: a
+
+
+def vis_face_alignment(im, result, line_size: int = 1):
+    """A filled green dot of radius ``line_size`` on every landmark (fastdeploy/vision/visualize/face_alignment.cc:21-33)."""
+    import cv2
+    out, back = _host_image(im)
+    for lm in result.landmarks:
+        cv2.circle(out, (int(lm[0]), int(lm[1])), line_size, (0, 255, 0), -1)
+    return back(out)
+
+
+def headpose_axes(euler_angles: Sequence[float], size: int, centre: Sequence[int]) -> np.ndarray:
+    """End points [3, 2] (x, y; integer) of the head's X, Y and Z axes drawn from ``centre``. The angles are
+    (pitch, yaw, roll) in degrees as the model gives them; yaw is mirrored because the image x axis runs the other way
+    (fastdeploy/vision/visualize/headpose.cc:27-49)."""
+    p, y, r = (np.deg2rad(np.float32(euler_angles[0])), -np.deg2rad(np.float32(euler_angles[1])),
+               np.deg2rad(np.float32(euler_angles[2])))
+    sp, cp, sy, cy, sr, cr = np.sin(p), np.cos(p), np.sin(y), np.cos(y), np.sin(r), np.cos(r)
+    ends = np.array([[size * cy * cr, size * (cp * sr + cr * sp * sy)],
+                     [-size * cy * sr, size * (cp * cr - sp * sy * sr)],
+                     [size * sy, -size * cy * sp]], np.float64)
+    return np.trunc(ends).astype(np.int64) + np.asarray(centre, np.int64)[None, :]
+
+
+def vis_headpose(im, result, size: int = 50, line_size: int = 1):
+    """The three head axes from the image centre: X red, Y green, Z blue."""
+    import cv2
+    out, back = _host_image(im)
+    c = (out.shape[1] // 2, out.shape[0] // 2)
+    for end, col in zip(headpose_axes(result.euler_angles, size, c), ((0, 0, 255), (0, 255, 0), (255, 0, 0))):
+        cv2.line(out, c, (int(end[0]), int(end[1])), col, line_size)
+    return back(out)
+
+
+_BOX3D_EDGES = ((1, 0), (2, 7), (3, 6), (4, 5), (1, 2), (2, 3), (3, 4), (4, 1), (0, 7), (7, 6), (6, 5), (5, 0))
+
+
+def project_boxes_3d(result, k_data: Sequence[float]) -> np.ndarray:
+    """Image-plane corners [N, 8, 2] of the 3-D boxes of a :class:`PerceptionResult` under the pinhole matrix ``k_data``
+    (9 values, row major). A box is (h, w, l) = ``boxes[i][4:7]`` around the bottom-centre ``center[i]``, turned by
+    ``yaw_angle[i]`` about the vertical axis; the rotation keeps the reference's sign convention
+    (fastdeploy/vision/visualize/perception.cc:104-139)."""
+    n = len(result.scores)
+    if n == 0:
+        return np.zeros((0, 8, 2), np.float32)
+    K = np.asarray(k_data, np.float32).reshape(3, 3)
+    b = np.asarray(result.boxes, np.float32).reshape(n, -1)
+    h, w, l = b[:, 4:5], b[:, 5:6], b[:, 6:7]
+    xs = np.array([0, 1, 1, 1, 1, 0, 0, 0], np.float32)[None] * l - l / 2
+    ys = np.array([0, 0, 1, 1, 0, 0, 1, 1], np.float32)[None] * h - h
+    zs = np.array([0, 0, 0, 1, 1, 1, 1, 0], np.float32)[None] * w - w / 2
+    ry = np.asarray(result.yaw_angle, np.float32)[:, None]
+    c, s = np.cos(ry), np.sin(ry)
+    ctr = np.asarray(result.center, np.float32).reshape(n, 3)
+    pts = np.stack([c * xs + s * zs + ctr[:, 0:1], ys + ctr[:, 1:2], s * xs + c * zs + ctr[:, 2:3]], axis=-1)   # [N, 8, 3]
+    proj = pts @ K.T
+    with np.errstate(divide="ignore", invalid="ignore"):
+        return proj[..., :2] / proj[..., 2:3]
+
+
+def vis_perception(im, result, config_file: str, score_threshold: float = 0.0, line_size: int = 1, font_size: float = 0.5):
+    """Wire-frame 3-D boxes on the frame resized to the model's input size; the camera matrix (``k_data``) and the size
+    (``Preprocess: Resize.target_size``) come from the model's yaml. Boxes below a score of 0.5 are left out, as in the
+    reference, whatever ``score_threshold`` says (fastdeploy/vision/visualize/perception.cc:46-190)."""
+    import cv2
+    import yaml
+    if not result.scores:
+        return im
+    with open(config_file) as f:
+        cfg = yaml.safe_load(f)
+    k_data = cfg.get("k_data")
+    if k_data is None or len(k_data) != 9:
+        raise ValueError(f"{config_file}: k_data must hold the 9 values of the camera matrix")
+    target = next((op["target_size"] for op in cfg.get("Preprocess", []) if op.get("type") == "Resize"), None)
+    out, back = _host_image(im)
+    if target is not None:
+        out = cv2.resize(out, (int(target[1]), int(target[0])), interpolation=cv2.INTER_NEAREST)
+    corners = project_boxes_3d(result, k_data)
+    for i, score in enumerate(result.scores):
+        if score < 0.5 or not np.isfinite(corners[i]).all():
+            continue
+        lo, hi = corners[i].min(0), corners[i].max(0)
+        if not (lo.any() or hi.any()):
+            continue
+        col = tuple(int(v) for v in _COLORS[result.label_ids[i] % 256])
+        for a, b_ in _BOX3D_EDGES:
+            cv2.line(out, tuple(int(round(v)) for v in corners[i, a]), tuple(int(round(v)) for v in corners[i, b_]), col, line_size)
+        cv2.putText(out, f"{result.label_ids[i]}, {str(float(score))[:4]}", (int(lo[0]), int(lo[1])), cv2.FONT_HERSHEY_SIMPLEX,
+                    font_size, (255, 255, 255), 1)
+    return back(out)
+
+
+# ------------------------------------------------------------------ names kept from older releases
+def _deprecated(old: str, new: str) -> None:
+    from ..utils import log
+    log.warning(f"DEPRECATED: fastdeploy.vision.{old} is deprecated, please use fastdeploy.vision.{new} instead.")
+
+
+def vis_matting_alpha(im, result: MattingResult, remove_small_connected_area: bool = False):
+    _deprecated("vis_matting_alpha", "vis_matting")
+    return vis_matting(im, result, remove_small_connected_area=remove_small_connected_area)
+
+
+def swap_background_matting(im, background, result, remove_small_connected_area: bool = False):
+    _deprecated("swap_background_matting", "swap_background")
+    assert isinstance(result, MattingResult), "The result must be MattingResult type"
+    return swap_background(im, background, result, remove_small_connected_area=remove_small_connected_area)
+
+
+def swap_background_segmentation(im, background, background_label: int, result):
+    _deprecated("swap_background_segmentation", "swap_background")
+    assert isinstance(result, SegmentationResult), "The result must be SegmentationResult type"
+    return swap_background(im, background, result, background_label=background_label)
