@@ -22,12 +22,17 @@ class PaddleClasPreprocessor(ProcessorManager):
 
     def __init__(self, config_file: str):
         super().__init__()
-        with open(config_file) as f:
+        self.config_file = config_file
+        self.disable_normalize_ = False
+        self.disable_permute_ = False
+        self.initial_resize_on_cpu_ = False
+        self._build()
+
+    def _build(self) -> None:
+        with open(self.config_file) as f:
             cfg = yaml.safe_load(f)
         ops = cfg["PreProcess"]["transform_ops"]
         procs = [BGR2RGB()]
-        self.disable_normalize_ = False
-        self.disable_permute_ = False
         for op in ops:
             (name, args), = op.items()
             args = args or {}
@@ -43,12 +48,33 @@ class PaddleClasPreprocessor(ProcessorManager):
                 size = [size, size] if isinstance(size, int) else size
                 procs.append(CenterCrop(int(size[0]), int(size[1])))
             elif name == "NormalizeImage":
-                procs.append(Normalize(list(args["mean"]), list(args["std"]), True))
+                if not self.disable_normalize_:
+                    scale = float(args.get("scale", 0.00392157))
+                    if abs(scale - 0.00392157) >= 1e-6:
+                        raise ValueError("Only support scale in Normalize be 0.00392157, means the pixel is in range of [0, 255].")
+                    procs.append(Normalize(list(args["mean"]), list(args["std"]), True))
             elif name == "ToCHWImage":
-                procs.append(HWC2CHW())
+                if not self.disable_permute_:
+                    procs.append(HWC2CHW())
             else:
                 raise ValueError(f"Unexcepted preprocess operator: {name}.")
         self.processors = fuse_transforms(procs)
+
+    def disable_normalize(self) -> None:
+        """For a model whose graph normalises by itself: the chain is rebuilt without NormalizeImage, so it hands over
+        uint8 pixels (fastdeploy/vision/classification/ppcls/preprocessor.cc:102-110)."""
+        self.disable_normalize_ = True
+        self._build()
+
+    def disable_permute(self) -> None:
+        """Leaves the image HWC (preprocessor.cc:111-119)."""
+        self.disable_permute_ = True
+        self._build()
+
+    def initial_resize_on_cpu(self, v: bool) -> None:
+        """The reference can run the first resize on the host so that a smaller image crosses to the GPU. The device path
+        here reads the source image once inside the fused kernel, so the flag is recorded and changes nothing."""
+        self.initial_resize_on_cpu_ = bool(v)
 
     def run(self, images):
         return super().run([np.asarray(im) for im in images])
@@ -145,22 +171,50 @@ class YOLOv5Cls(ResNet):
     (fastdeploy/vision/classification/contrib/yolov5cls)."""
 
 
+class PPShiTuV2RecognizerPreprocessor(PaddleClasPreprocessor):
+    """The recogniser reads the same ``inference_cls.yaml`` transform list as a PaddleClas classifier
+    (fastdeploy/vision/classification/ppshitu/ppshituv2_rec_preprocessor.cc:25-120)."""
+
+
+class PPShiTuV2RecognizerPostprocessor:
+    """Copies each row of the embedding into ``ClassifyResult.feature`` and, with ``feature_norm`` (the default),
+    divides it by its L2 norm (fastdeploy/vision/classification/ppshitu/ppshituv2_rec_postprocessor.cc:24-53)."""
+
+    def __init__(self, topk: int = 1):
+        self.topk = topk            # unused by a feature extractor; kept because the classifier interface sets it
+        self.feature_norm = True
+
+    def run(self, tensors) -> List[ClassifyResult]:
+        t = tensors[0]
+        if hasattr(t, "detach"):
+            t = t.detach().float().cpu().numpy()
+        feats = np.asarray(t, np.float32)
+        feats = feats.reshape(feats.shape[0], -1)
+        return [ClassifyResult(feature=l2_normalize(f) if self.feature_norm else f.tolist()) for f in feats]
+
+
 class PPShiTuV2Recognizer(_ClsBase):
-    """Feature extractor of PP-ShiTuV2: PaddleClas pre-processing, L2-normalised embedding in ``feature``."""
+    """Feature extractor of PP-ShiTuV2: PaddleClas pre-processing, L2-normalised embedding in ``feature``
+    (fastdeploy/vision/classification/ppshitu/ppshituv2_rec.cc:22-110)."""
 
     def __init__(self, model_file: str, params_file: str, config_file: str,
                  runtime_option: Optional[RuntimeOption] = None, model_format: ModelFormat = ModelFormat.PADDLE):
         super().__init__(runtime_option)
         self.runtime_option.set_model_path(model_file, params_file, model_format)
-        self.preprocessor = PaddleClasPreprocessor(config_file)
-        self.feature_norm = True
-        self.postprocessor = self
-        self.topk = 1
+        self.preprocessor = PPShiTuV2RecognizerPreprocessor(config_file)
+        self.postprocessor = PPShiTuV2RecognizerPostprocessor()
         self._finish_init()
 
-    def run(self, tensors):
-        feats = np.asarray(tensors[0], np.float32)
-        return [ClassifyResult(feature=l2_normalize(f) if self.feature_norm else f.tolist()) for f in feats]
+    @property
+    def feature_norm(self) -> bool:
+        return self.postprocessor.feature_norm
+
+    @feature_norm.setter
+    def feature_norm(self, v: bool) -> None:
+        self.postprocessor.feature_norm = bool(v)
+
+    def predict(self, im: np.ndarray) -> ClassifyResult:
+        return self.batch_predict([im])[0]
 
 
 from ..detection.ppdet import PicoDet as PPShiTuV2Detector   # noqa: E402  (alias, as in the reference)
