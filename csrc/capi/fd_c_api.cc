@@ -426,13 +426,8 @@ FD_C_PaddleSegModelWrapper* FD_C_CreatePaddleSegModelWrapper(const char* m, cons
                                                              FD_C_RuntimeOptionWrapper* o, FD_C_ModelFormat f) {
   return create_model("vision.segmentation.PaddleSegModel", m, p, c, o, f);
 }
-FD_C_Bool FD_C_PaddleSegModelWrapperPredict(FD_C_PaddleSegModelWrapper* w, FD_C_Mat img, FD_C_SegmentationResult* out) {
-  Gil g;
-  PyObject* arr = mat_to_numpy(img);
-  if (arr == nullptr) return 0;
-  PyObject* r = call_method(w->obj, "predict", "(O)", arr);
-  Py_DECREF(arr);
-  if (r == nullptr) return 0;
+static bool seg_from_py(PyObject* r, FD_C_SegmentationResult* out) {
+  std::memset(out, 0, sizeof(*out));
   PyObject *lm = PyObject_GetAttrString(r, "label_map"), *sm = PyObject_GetAttrString(r, "score_map"),
            *shape = PyObject_GetAttrString(r, "shape"), *has = PyObject_GetAttrString(r, "contain_score_map");
   bool ok = lm && sm && shape && ints_from_seq(lm, &out->label_map) && floats_from_seq(sm, &out->score_map) &&
@@ -446,7 +441,18 @@ FD_C_Bool FD_C_PaddleSegModelWrapperPredict(FD_C_PaddleSegModelWrapper* w, FD_C_
   } else if (PyErr_Occurred()) {
     fetch_py_error("SegmentationResult");
   }
-  Py_XDECREF(lm); Py_XDECREF(sm); Py_XDECREF(shape); Py_XDECREF(has); Py_DECREF(r);
+  Py_XDECREF(lm); Py_XDECREF(sm); Py_XDECREF(shape); Py_XDECREF(has);
+  return ok;
+}
+FD_C_Bool FD_C_PaddleSegModelWrapperPredict(FD_C_PaddleSegModelWrapper* w, FD_C_Mat img, FD_C_SegmentationResult* out) {
+  Gil g;
+  PyObject* arr = mat_to_numpy(img);
+  if (arr == nullptr) return 0;
+  PyObject* r = call_method(w->obj, "predict", "(O)", arr);
+  Py_DECREF(arr);
+  if (r == nullptr) return 0;
+  const bool ok = seg_from_py(r, out);
+  Py_DECREF(r);
   return ok ? 1 : 0;
 }
 void FD_C_DestroySegmentationResult(FD_C_SegmentationResult* r) {
@@ -455,9 +461,9 @@ void FD_C_DestroySegmentationResult(FD_C_SegmentationResult* r) {
   r->label_map.data = nullptr; r->score_map.data = nullptr;
 }
 
-FD_C_PPOCRv3Wrapper* FD_C_CreatePPOCRv3Wrapper(const char* det_m, const char* det_p, const char* cls_m, const char* cls_p,
-                                               const char* rec_m, const char* rec_p, const char* rec_label,
-                                               FD_C_RuntimeOptionWrapper* option) {
+static FD_C_ModelWrapper* create_ocr_pipeline(const char* pipeline, const char* det_m, const char* det_p, const char* cls_m,
+                                              const char* cls_p, const char* rec_m, const char* rec_p, const char* rec_label,
+                                              FD_C_RuntimeOptionWrapper* option) {
   Gil g;
   if (g_pkg == nullptr) return nullptr;
   auto make = [&](const char* dotted, PyObject* args) -> PyObject* {
@@ -479,21 +485,25 @@ FD_C_PPOCRv3Wrapper* FD_C_CreatePPOCRv3Wrapper(const char* det_m, const char* de
   }
   PyObject* rec = make("vision.ocr.Recognizer", Py_BuildValue("(sss)", rec_m, rec_p ? rec_p : "", rec_label ? rec_label : ""));
   if (rec == nullptr) { Py_DECREF(det); Py_XDECREF(cls); return nullptr; }
-  PyObject* pipe_cls = get_class("vision.ocr.PPOCRv3");
+  PyObject* pipe_cls = get_class(pipeline);
   PyObject* pipe = pipe_cls != nullptr ? PyObject_CallFunctionObjArgs(pipe_cls, det, cls != nullptr ? cls : Py_None, rec, nullptr)
                                        : nullptr;
   Py_XDECREF(pipe_cls); Py_DECREF(det); Py_XDECREF(cls); Py_DECREF(rec);
-  if (pipe == nullptr) { fetch_py_error("PPOCRv3"); return nullptr; }
+  if (pipe == nullptr) { fetch_py_error(pipeline); return nullptr; }
   return new FD_C_ModelWrapper{pipe};
 }
-FD_C_Bool FD_C_PPOCRv3WrapperPredict(FD_C_PPOCRv3Wrapper* w, FD_C_Mat img, FD_C_OCRResult* out) {
-  Gil g;
+FD_C_PPOCRv3Wrapper* FD_C_CreatePPOCRv3Wrapper(const char* det_m, const char* det_p, const char* cls_m, const char* cls_p,
+                                               const char* rec_m, const char* rec_p, const char* rec_label,
+                                               FD_C_RuntimeOptionWrapper* option) {
+  return create_ocr_pipeline("vision.ocr.PPOCRv3", det_m, det_p, cls_m, cls_p, rec_m, rec_p, rec_label, option);
+}
+FD_C_PPOCRv2Wrapper* FD_C_CreatePPOCRv2Wrapper(const char* det_m, const char* det_p, const char* cls_m, const char* cls_p,
+                                               const char* rec_m, const char* rec_p, const char* rec_label,
+                                               FD_C_RuntimeOptionWrapper* option) {
+  return create_ocr_pipeline("vision.ocr.PPOCRv2", det_m, det_p, cls_m, cls_p, rec_m, rec_p, rec_label, option);
+}
+static bool ocr_from_py(PyObject* r, FD_C_OCRResult* out) {
   std::memset(out, 0, sizeof(*out));
-  PyObject* arr = mat_to_numpy(img);
-  if (arr == nullptr) return 0;
-  PyObject* r = call_method(w->obj, "predict", "(O)", arr);
-  Py_DECREF(arr);
-  if (r == nullptr) return 0;
   PyObject *boxes = PyObject_GetAttrString(r, "boxes"), *text = PyObject_GetAttrString(r, "text"),
            *rs = PyObject_GetAttrString(r, "rec_scores"), *cs = PyObject_GetAttrString(r, "cls_scores"),
            *cl = PyObject_GetAttrString(r, "cls_labels");
@@ -520,7 +530,19 @@ FD_C_Bool FD_C_PPOCRv3WrapperPredict(FD_C_PPOCRv3Wrapper* w, FD_C_Mat img, FD_C_
   } else if (PyErr_Occurred()) {
     fetch_py_error("OCRResult");
   }
-  Py_XDECREF(boxes); Py_XDECREF(text); Py_XDECREF(rs); Py_XDECREF(cs); Py_XDECREF(cl); Py_DECREF(r);
+  Py_XDECREF(boxes); Py_XDECREF(text); Py_XDECREF(rs); Py_XDECREF(cs); Py_XDECREF(cl);
+  return ok;
+}
+FD_C_Bool FD_C_PPOCRv3WrapperPredict(FD_C_PPOCRv3Wrapper* w, FD_C_Mat img, FD_C_OCRResult* out) {
+  Gil g;
+  std::memset(out, 0, sizeof(*out));
+  PyObject* arr = mat_to_numpy(img);
+  if (arr == nullptr) return 0;
+  PyObject* r = call_method(w->obj, "predict", "(O)", arr);
+  Py_DECREF(arr);
+  if (r == nullptr) return 0;
+  const bool ok = ocr_from_py(r, out);
+  Py_DECREF(r);
   return ok ? 1 : 0;
 }
 void FD_C_DestroyOCRResult(FD_C_OCRResult* r) {
@@ -613,6 +635,342 @@ void FD_C_DestroyDetectionResult(FD_C_DetectionResult* r) {
   for (size_t i = 0; i < r->boxes.size; ++i) std::free(r->boxes.data[i].data);
   std::free(r->boxes.data); std::free(r->scores.data); std::free(r->label_ids.data);
   r->boxes.data = nullptr; r->scores.data = nullptr; r->label_ids.data = nullptr;
+}
+
+
+// ---------------------------------------------------------------- the remaining option entry points
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperUseTimVX, "use_timvx")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperUseAscend, "use_ascend")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperUseSophgo, "use_sophgo")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperUseSophgoBackend, "use_sophgo_backend")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperUsePorosBackend, "use_poros_backend")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperUseLiteBackend, "use_lite_backend")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperUsePaddleLiteBackend, "use_paddle_lite_backend")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperEnablePaddleToTrt, "enable_paddle_to_trt")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperEnablePaddleLogInfo, "enable_paddle_log_info")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperDisablePaddleLogInfo, "disable_paddle_log_info")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperEnableLiteFP16, "enable_lite_fp16")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperDisableLiteFP16, "disable_lite_fp16")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperEnableLiteInt8, "enable_lite_int8")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperDisableLiteInt8, "disable_lite_int8")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperEnablePaddleTrtCollectShape, "enable_paddle_trt_collect_shape")
+FD_OPT_CALL0(FD_C_RuntimeOptionWrapperDisablePaddleTrtCollectShape, "disable_paddle_trt_collect_shape")
+#define FD_OPT_CALL_INT(cname, pyname)                                 \
+  void cname(FD_C_RuntimeOptionWrapper* w, int v) {                    \
+    Gil g;                                                             \
+    PyObject* r = call_method(w->obj, pyname, "(i)", v);               \
+    Py_XDECREF(r);                                                     \
+  }
+#define FD_OPT_CALL_STR(cname, pyname)                                 \
+  void cname(FD_C_RuntimeOptionWrapper* w, const char* v) {            \
+    Gil g;                                                             \
+    PyObject* r = call_method(w->obj, pyname, "(s)", v ? v : "");      \
+    Py_XDECREF(r);                                                     \
+  }
+FD_OPT_CALL_INT(FD_C_RuntimeOptionWrapperSetOrtGraphOptLevel, "set_ort_graph_opt_level")
+FD_OPT_CALL_INT(FD_C_RuntimeOptionWrapperSetPaddleMKLDNNCacheSize, "set_paddle_mkldnn_cache_size")
+FD_OPT_CALL_INT(FD_C_RuntimeOptionWrapperSetOpenVINOStreams, "set_openvino_streams")
+FD_OPT_CALL_INT(FD_C_RuntimeOptionWrapperSetLitePowerMode, "set_lite_power_mode")
+FD_OPT_CALL_STR(FD_C_RuntimeOptionWrapperDeletePaddleBackendPass, "delete_paddle_backend_pass")
+FD_OPT_CALL_STR(FD_C_RuntimeOptionWrapperSetOpenVINODevice, "set_openvino_device")
+FD_OPT_CALL_STR(FD_C_RuntimeOptionWrapperSetLiteOptimizedModelDir, "set_lite_optimized_model_dir")
+FD_OPT_CALL_STR(FD_C_RuntimeOptionWrapperSetLiteSubgraphPartitionPath, "set_lite_subgraph_partition_path")
+FD_OPT_CALL_STR(FD_C_RuntimeOptionWrapperSetLiteSubgraphPartitionConfigBuffer, "set_lite_subgraph_partition_config_buffer")
+FD_OPT_CALL_STR(FD_C_RuntimeOptionWrapperSetLiteContextProperties, "set_lite_context_properties")
+FD_OPT_CALL_STR(FD_C_RuntimeOptionWrapperSetLiteModelCacheDir, "set_lite_model_cache_dir")
+FD_OPT_CALL_STR(FD_C_RuntimeOptionWrapperSetLiteMixedPrecisionQuantizationConfigPath,
+                "set_lite_mixed_precision_quantization_config_path")
+void FD_C_RuntimeOptionWrapperSetPaddleMKLDNN(FD_C_RuntimeOptionWrapper* w, FD_C_Bool on) {
+  Gil g;
+  PyObject* r = call_method(w->obj, "set_paddle_mkldnn", "(O)", on ? Py_True : Py_False);
+  Py_XDECREF(r);
+}
+void FD_C_RuntimeOptionWrapperSetExternalStream(FD_C_RuntimeOptionWrapper* w, void* stream) {
+  Gil g;
+  PyObject* r = call_method(w->obj, "set_external_raw_stream", "(K)", static_cast<unsigned long long>(reinterpret_cast<uintptr_t>(stream)));
+  Py_XDECREF(r);
+}
+void FD_C_RuntimeOptionWrapperSetModelBuffer(FD_C_RuntimeOptionWrapper* w, const char* model, size_t model_size, const char* params,
+                                             size_t params_size, FD_C_ModelFormat format) {
+  Gil g;
+  PyObject* r = call_method(w->obj, "set_model_buffer", "(y#y#i)", model, static_cast<Py_ssize_t>(model_size), params ? params : "",
+                            static_cast<Py_ssize_t>(params ? params_size : 0), static_cast<int>(format));
+  Py_XDECREF(r);
+}
+void FD_C_RuntimeOptionWrapperUseKunlunXin(FD_C_RuntimeOptionWrapper* w, int id, int l3, FD_C_Bool locked, FD_C_Bool autotune,
+                                           const char* autotune_file, const char* precision, FD_C_Bool adaptive_seqlen,
+                                           FD_C_Bool multi_stream, int64_t gm_default_size) {
+  Gil g;
+  PyObject* r = call_method(w->obj, "use_kunlunxin", "(iiiissiiL)", id, l3, static_cast<int>(locked), static_cast<int>(autotune),
+                            autotune_file ? autotune_file : "", precision ? precision : "", static_cast<int>(adaptive_seqlen),
+                            static_cast<int>(multi_stream), static_cast<long long>(gm_default_size));
+  Py_XDECREF(r);
+}
+void FD_C_RuntimeOptionWrapperUseIpu(FD_C_RuntimeOptionWrapper* w, int device_num, int micro_batch_size, FD_C_Bool pipelining,
+                                     int batches_per_step) {
+  Gil g;
+  PyObject* r = call_method(w->obj, "use_ipu", "(iiii)", device_num, micro_batch_size, static_cast<int>(pipelining), batches_per_step);
+  Py_XDECREF(r);
+}
+
+// ---------------------------------------------------------------- detection classes by name
+static FD_C_Bool model_initialized(FD_C_ModelWrapper* w) {
+  Gil g;
+  PyObject* r = call_method(w->obj, "initialized");
+  const FD_C_Bool v = r != nullptr && PyObject_IsTrue(r) ? 1 : 0;
+  Py_XDECREF(r);
+  return v;
+}
+#define FD_C_IMPLEMENT_DETECTION_COMMON(T)                                                                                   \
+  void FD_C_Destroy##T##Wrapper(FD_C_##T##Wrapper* w) { FD_C_DestroyModelWrapper(w); }                                       \
+  FD_C_Bool FD_C_##T##WrapperPredict(FD_C_##T##Wrapper* w, FD_C_Mat img, FD_C_DetectionResult* r) {                          \
+    return predict_detection(w, img, r);                                                                                     \
+  }                                                                                                                          \
+  FD_C_Bool FD_C_##T##WrapperInitialized(FD_C_##T##Wrapper* w) { return model_initialized(w); }                              \
+  FD_C_Bool FD_C_##T##WrapperBatchPredict(FD_C_##T##Wrapper* w, const FD_C_Mat* imgs, int n, FD_C_DetectionResult* r) {      \
+    return FD_C_DetectionModelWrapperBatchPredict(w, imgs, n, r);                                                            \
+  }
+#define FD_C_IMPLEMENT_PPDET(T)                                                                                              \
+  FD_C_IMPLEMENT_DETECTION_COMMON(T)                                                                                         \
+  FD_C_##T##Wrapper* FD_C_Create##T##Wrapper(const char* m, const char* p, const char* c, FD_C_RuntimeOptionWrapper* o,      \
+                                             FD_C_ModelFormat f) {                                                           \
+    return create_model("vision.detection." #T, m, p, c, o, f);                                                              \
+  }
+#define FD_C_IMPLEMENT_YOLO(T)                                                                                               \
+  FD_C_IMPLEMENT_DETECTION_COMMON(T)                                                                                         \
+  FD_C_##T##Wrapper* FD_C_Create##T##Wrapper(const char* m, const char* p, FD_C_RuntimeOptionWrapper* o, FD_C_ModelFormat f) { \
+    return create_model("vision.detection." #T, m, p, nullptr, o, f);                                                        \
+  }
+FD_C_PPDET_MODELS(FD_C_IMPLEMENT_PPDET)
+FD_C_YOLO_MODELS(FD_C_IMPLEMENT_YOLO)
+FD_C_Bool FD_C_PPYOLOEWrapperBatchPredict(FD_C_PPYOLOEWrapper* w, const FD_C_Mat* imgs, int n, FD_C_DetectionResult* r) {
+  return FD_C_DetectionModelWrapperBatchPredict(w, imgs, n, r);
+}
+
+// ---------------------------------------------------------------- batches of the other model kinds
+// Runs `batch_predict` on the images and hands each item of the returned list to `convert(item, index)`.
+}  // extern "C"
+template <typename Convert>
+static FD_C_Bool batch_predict_generic(FD_C_ModelWrapper* w, const FD_C_Mat* imgs, int n_imgs, Convert convert) {
+  Gil g;
+  PyObject* list = PyList_New(n_imgs);
+  for (int i = 0; i < n_imgs; ++i) {
+    PyObject* arr = mat_to_numpy(imgs[i]);
+    if (arr == nullptr) { Py_DECREF(list); return 0; }
+    PyList_SET_ITEM(list, i, arr);
+  }
+  PyObject* r = call_method(w->obj, "batch_predict", "(O)", list);
+  Py_DECREF(list);
+  if (r == nullptr) return 0;
+  bool ok = PySequence_Check(r) && PySequence_Size(r) == n_imgs;
+  for (int i = 0; i < n_imgs && ok; ++i) {
+    PyObject* item = PySequence_GetItem(r, i);
+    ok = item != nullptr && convert(item, i);
+    Py_XDECREF(item);
+  }
+  if (!ok && g_err.empty()) set_err("batch_predict: unexpected result");
+  Py_DECREF(r);
+  return ok ? 1 : 0;
+}
+extern "C" {
+static bool classify_from_py(PyObject* r, FD_C_ClassifyResult* out) {
+  PyObject *ids = PyObject_GetAttrString(r, "label_ids"), *scores = PyObject_GetAttrString(r, "scores");
+  const bool ok = ids && scores && ints_from_seq(ids, &out->label_ids) && floats_from_seq(scores, &out->scores);
+  Py_XDECREF(ids); Py_XDECREF(scores);
+  return ok;
+}
+FD_C_Bool FD_C_PaddleClasModelWrapperInitialized(FD_C_PaddleClasModelWrapper* w) { return model_initialized(w); }
+FD_C_Bool FD_C_PaddleClasModelWrapperBatchPredict(FD_C_PaddleClasModelWrapper* w, const FD_C_Mat* imgs, int n, FD_C_ClassifyResult* out) {
+  return batch_predict_generic(w, imgs, n, [&](PyObject* item, int i) { return classify_from_py(item, &out[i]); });
+}
+void FD_C_DestroyPaddleSegModelWrapper(FD_C_PaddleSegModelWrapper* w) { FD_C_DestroyModelWrapper(w); }
+FD_C_Bool FD_C_PaddleSegModelWrapperInitialized(FD_C_PaddleSegModelWrapper* w) { return model_initialized(w); }
+FD_C_Bool FD_C_PaddleSegModelWrapperBatchPredict(FD_C_PaddleSegModelWrapper* w, const FD_C_Mat* imgs, int n, FD_C_SegmentationResult* out) {
+  return batch_predict_generic(w, imgs, n, [&](PyObject* item, int i) { return seg_from_py(item, &out[i]); });
+}
+FD_C_Bool FD_C_PPOCRv2WrapperPredict(FD_C_PPOCRv2Wrapper* w, FD_C_Mat img, FD_C_OCRResult* out) {
+  return FD_C_PPOCRv3WrapperPredict(w, img, out);
+}
+FD_C_Bool FD_C_PPOCRv3WrapperBatchPredict(FD_C_PPOCRv3Wrapper* w, const FD_C_Mat* imgs, int n, FD_C_OCRResult* out) {
+  return batch_predict_generic(w, imgs, n, [&](PyObject* item, int i) { return ocr_from_py(item, &out[i]); });
+}
+FD_C_Bool FD_C_PPOCRv2WrapperBatchPredict(FD_C_PPOCRv2Wrapper* w, const FD_C_Mat* imgs, int n, FD_C_OCRResult* out) {
+  return FD_C_PPOCRv3WrapperBatchPredict(w, imgs, n, out);
+}
+void FD_C_DestroyPPOCRv2Wrapper(FD_C_PPOCRv2Wrapper* w) { FD_C_DestroyModelWrapper(w); }
+void FD_C_DestroyPPOCRv3Wrapper(FD_C_PPOCRv3Wrapper* w) { FD_C_DestroyModelWrapper(w); }
+
+// ---------------------------------------------------------------- images
+FD_C_Mat FD_C_Imread(const char* path) {
+  FD_C_Mat m{nullptr, 0, 0, 0};
+  Gil g;
+  PyObject* cv2 = PyImport_ImportModule("cv2");
+  if (cv2 == nullptr) { fetch_py_error("import cv2"); return m; }
+  PyObject* img = PyObject_CallMethod(cv2, "imread", "s", path);
+  Py_DECREF(cv2);
+  if (img == nullptr) { fetch_py_error("imread"); return m; }
+  if (img == Py_None) { Py_DECREF(img); set_err(std::string("imread: cannot read ") + path); return m; }
+  PyObject* shp = PyObject_GetAttrString(img, "shape");
+  PyObject* bytes = call_method(img, "tobytes");
+  if (shp != nullptr && bytes != nullptr && PyTuple_Size(shp) == 3) {
+    m.height = static_cast<int>(PyLong_AsLong(PyTuple_GET_ITEM(shp, 0)));
+    m.width = static_cast<int>(PyLong_AsLong(PyTuple_GET_ITEM(shp, 1)));
+    m.channels = static_cast<int>(PyLong_AsLong(PyTuple_GET_ITEM(shp, 2)));
+    char* buf = nullptr;
+    Py_ssize_t n = 0;
+    PyBytes_AsStringAndSize(bytes, &buf, &n);
+    m.data = static_cast<uint8_t*>(std::malloc(n > 0 ? n : 1));
+    std::memcpy(m.data, buf, static_cast<size_t>(n));
+  } else {
+    set_err("imread: unexpected image layout");
+  }
+  Py_XDECREF(shp); Py_XDECREF(bytes); Py_DECREF(img);
+  return m;
+}
+FD_C_Bool FD_C_Imwrite(const char* path, FD_C_Mat img) {
+  Gil g;
+  PyObject* cv2 = PyImport_ImportModule("cv2");
+  if (cv2 == nullptr) { fetch_py_error("import cv2"); return 0; }
+  PyObject* arr = mat_to_numpy(img);
+  PyObject* r = arr != nullptr ? PyObject_CallMethod(cv2, "imwrite", "sO", path, arr) : nullptr;
+  Py_DECREF(cv2); Py_XDECREF(arr);
+  if (r == nullptr) { if (PyErr_Occurred()) fetch_py_error("imwrite"); return 0; }
+  const FD_C_Bool ok = PyObject_IsTrue(r) ? 1 : 0;
+  if (!ok) set_err(std::string("imwrite: cannot write ") + path);
+  Py_DECREF(r);
+  return ok;
+}
+void FD_C_DestroyMat(FD_C_Mat img) { std::free(img.data); }
+
+// ---------------------------------------------------------------- result text
+static PyObject* py_detection_result(const FD_C_DetectionResult* result) {
+  PyObject* res_cls = get_class("vision.DetectionResult");
+  if (res_cls == nullptr) return nullptr;
+  PyObject* res = PyObject_CallObject(res_cls, nullptr);
+  Py_DECREF(res_cls);
+  if (res == nullptr) { fetch_py_error("DetectionResult"); return nullptr; }
+  PyObject* boxes = PyList_New(static_cast<Py_ssize_t>(result->boxes.size));
+  for (size_t i = 0; i < result->boxes.size; ++i)
+    PyList_SET_ITEM(boxes, i, py_list_of_floats(result->boxes.data[i].data, result->boxes.data[i].size));
+  PyObject* scores = py_list_of_floats(result->scores.data, result->scores.size);
+  PyObject* labels = PyList_New(static_cast<Py_ssize_t>(result->label_ids.size));
+  for (size_t i = 0; i < result->label_ids.size; ++i) PyList_SET_ITEM(labels, i, PyLong_FromLong(result->label_ids.data[i]));
+  PyObject_SetAttrString(res, "boxes", boxes);
+  PyObject_SetAttrString(res, "scores", scores);
+  PyObject_SetAttrString(res, "label_ids", labels);
+  Py_DECREF(boxes); Py_DECREF(scores); Py_DECREF(labels);
+  return res;
+}
+static PyObject* py_ocr_result(const FD_C_OCRResult* result) {
+  PyObject* res_cls = get_class("vision.OCRResult");
+  if (res_cls == nullptr) return nullptr;
+  PyObject* res = PyObject_CallObject(res_cls, nullptr);
+  Py_DECREF(res_cls);
+  if (res == nullptr) { fetch_py_error("OCRResult"); return nullptr; }
+  PyObject* boxes = PyList_New(static_cast<Py_ssize_t>(result->boxes.size));
+  for (size_t i = 0; i < result->boxes.size; ++i) {
+    PyObject* b = PyList_New(static_cast<Py_ssize_t>(result->boxes.data[i].size));
+    for (size_t k = 0; k < result->boxes.data[i].size; ++k)
+      PyList_SET_ITEM(b, k, PyLong_FromLong(static_cast<long>(result->boxes.data[i].data[k])));
+    PyList_SET_ITEM(boxes, i, b);
+  }
+  PyObject* text = PyList_New(static_cast<Py_ssize_t>(result->n_text));
+  for (size_t i = 0; i < result->n_text; ++i) PyList_SET_ITEM(text, i, PyUnicode_FromString(result->text[i] ? result->text[i] : ""));
+  PyObject* rs = py_list_of_floats(result->rec_scores.data, result->rec_scores.size);
+  PyObject* cs = py_list_of_floats(result->cls_scores.data, result->cls_scores.size);
+  PyObject* cl = PyList_New(static_cast<Py_ssize_t>(result->cls_labels.size));
+  for (size_t i = 0; i < result->cls_labels.size; ++i) PyList_SET_ITEM(cl, i, PyLong_FromLong(result->cls_labels.data[i]));
+  PyObject_SetAttrString(res, "boxes", boxes); PyObject_SetAttrString(res, "text", text);
+  PyObject_SetAttrString(res, "rec_scores", rs); PyObject_SetAttrString(res, "cls_scores", cs);
+  PyObject_SetAttrString(res, "cls_labels", cl);
+  Py_DECREF(boxes); Py_DECREF(text); Py_DECREF(rs); Py_DECREF(cs); Py_DECREF(cl);
+  return res;
+}
+// str(obj) into the caller's buffer; steals the reference
+static size_t str_into(PyObject* obj, char* buffer, size_t capacity) {
+  if (obj == nullptr) return 0;
+  PyObject* s = PyObject_Str(obj);
+  Py_DECREF(obj);
+  if (s == nullptr) { fetch_py_error("str"); return 0; }
+  Py_ssize_t n = 0;
+  const char* c = PyUnicode_AsUTF8AndSize(s, &n);
+  if (c != nullptr && buffer != nullptr && capacity > 0) {
+    const size_t k = static_cast<size_t>(n) < capacity - 1 ? static_cast<size_t>(n) : capacity - 1;
+    std::memcpy(buffer, c, k);
+    buffer[k] = 0;
+  }
+  Py_DECREF(s);
+  return static_cast<size_t>(n) + 1;
+}
+size_t FD_C_DetectionResultStr(const FD_C_DetectionResult* r, char* buffer, size_t capacity) {
+  Gil g;
+  return str_into(py_detection_result(r), buffer, capacity);
+}
+size_t FD_C_OCRResultStr(const FD_C_OCRResult* r, char* buffer, size_t capacity) {
+  Gil g;
+  return str_into(py_ocr_result(r), buffer, capacity);
+}
+size_t FD_C_ClassifyResultStr(const FD_C_ClassifyResult* r, char* buffer, size_t capacity) {
+  Gil g;
+  PyObject* res_cls = get_class("vision.ClassifyResult");
+  if (res_cls == nullptr) return 0;
+  PyObject* res = PyObject_CallObject(res_cls, nullptr);
+  Py_DECREF(res_cls);
+  if (res == nullptr) { fetch_py_error("ClassifyResult"); return 0; }
+  PyObject* ids = PyList_New(static_cast<Py_ssize_t>(r->label_ids.size));
+  for (size_t i = 0; i < r->label_ids.size; ++i) PyList_SET_ITEM(ids, i, PyLong_FromLong(r->label_ids.data[i]));
+  PyObject* sc = py_list_of_floats(r->scores.data, r->scores.size);
+  PyObject_SetAttrString(res, "label_ids", ids); PyObject_SetAttrString(res, "scores", sc);
+  Py_DECREF(ids); Py_DECREF(sc);
+  return str_into(res, buffer, capacity);
+}
+size_t FD_C_SegmentationResultStr(const FD_C_SegmentationResult* r, char* buffer, size_t capacity) {
+  Gil g;
+  PyObject* res_cls = get_class("vision.SegmentationResult");
+  if (res_cls == nullptr) return 0;
+  PyObject* res = PyObject_CallObject(res_cls, nullptr);
+  Py_DECREF(res_cls);
+  if (res == nullptr) { fetch_py_error("SegmentationResult"); return 0; }
+  PyObject* lm = PyList_New(static_cast<Py_ssize_t>(r->label_map.size));
+  for (size_t i = 0; i < r->label_map.size; ++i) PyList_SET_ITEM(lm, i, PyLong_FromLong(r->label_map.data[i]));
+  PyObject* sm = py_list_of_floats(r->score_map.data, r->score_map.size);
+  PyObject* shape = Py_BuildValue("[ii]", r->height, r->width);
+  PyObject_SetAttrString(res, "label_map", lm); PyObject_SetAttrString(res, "score_map", sm);
+  PyObject_SetAttrString(res, "shape", shape);
+  PyObject_SetAttrString(res, "contain_score_map", r->contain_score_map ? Py_True : Py_False);
+  Py_DECREF(lm); Py_DECREF(sm); Py_DECREF(shape);
+  return str_into(res, buffer, capacity);
+}
+
+// ---------------------------------------------------------------- more visualisers
+FD_C_Bool FD_C_VisDetectionWithLabel(FD_C_Mat img, const FD_C_DetectionResult* result, const char* const* labels, int n_labels,
+                                     float score_threshold, int line_size, float font_size, FD_C_Mat* out) {
+  Gil g;
+  PyObject* vis = get_class("vision.vis_detection");
+  PyObject* res = vis != nullptr ? py_detection_result(result) : nullptr;
+  if (res == nullptr) { Py_XDECREF(vis); return 0; }
+  PyObject* names = PyList_New(n_labels);
+  for (int i = 0; i < n_labels; ++i) PyList_SET_ITEM(names, i, PyUnicode_FromString(labels[i] ? labels[i] : ""));
+  PyObject* arr = mat_to_numpy(img);
+  PyObject* drawn = arr != nullptr ? PyObject_CallFunction(vis, "OOOfif", arr, res, names, score_threshold, line_size, font_size) : nullptr;
+  Py_XDECREF(arr); Py_DECREF(res); Py_DECREF(names); Py_DECREF(vis);
+  if (drawn == nullptr) { fetch_py_error("vis_detection"); return 0; }
+  const bool ok = copy_image_back(drawn, out);
+  Py_DECREF(drawn);
+  return ok ? 1 : 0;
+}
+FD_C_Bool FD_C_VisOcr(FD_C_Mat img, const FD_C_OCRResult* result, FD_C_Mat* out) {
+  Gil g;
+  PyObject* vis = get_class("vision.vis_ppocr");
+  PyObject* res = vis != nullptr ? py_ocr_result(result) : nullptr;
+  if (res == nullptr) { Py_XDECREF(vis); return 0; }
+  PyObject* arr = mat_to_numpy(img);
+  PyObject* drawn = arr != nullptr ? PyObject_CallFunction(vis, "OO", arr, res) : nullptr;
+  Py_XDECREF(arr); Py_DECREF(res); Py_DECREF(vis);
+  if (drawn == nullptr) { fetch_py_error("vis_ppocr"); return 0; }
+  const bool ok = copy_image_back(drawn, out);
+  Py_DECREF(drawn);
+  return ok ? 1 : 0;
 }
 
 }  // extern "C"

@@ -75,6 +75,47 @@ FD_C_EXPORT void FD_C_RuntimeOptionWrapperEnablePinnedMemory(FD_C_RuntimeOptionW
 FD_C_EXPORT void FD_C_RuntimeOptionWrapperDisablePinnedMemory(FD_C_RuntimeOptionWrapper* w);
 FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetEncryptionKey(FD_C_RuntimeOptionWrapper* w, const char* key);
 
+/* the rest of the reference's option entry points (c_api/fastdeploy_capi/runtime/runtime_option.h:40-500). Options that
+ * name another vendor's device or library are recorded on the option object and change nothing about execution. */
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetModelBuffer(FD_C_RuntimeOptionWrapper* w, const char* model_buffer, size_t model_size,
+                                                         const char* params_buffer, size_t params_size, FD_C_ModelFormat format);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperUseTimVX(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperUseAscend(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperUseSophgo(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperUseKunlunXin(FD_C_RuntimeOptionWrapper* w, int kunlunxin_id, int l3_workspace_size,
+                                                       FD_C_Bool locked, FD_C_Bool autotune, const char* autotune_file,
+                                                       const char* precision, FD_C_Bool adaptive_seqlen,
+                                                       FD_C_Bool enable_multi_stream, int64_t gm_default_size);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperUseIpu(FD_C_RuntimeOptionWrapper* w, int device_num, int micro_batch_size,
+                                                 FD_C_Bool enable_pipelining, int batches_per_step);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetExternalStream(FD_C_RuntimeOptionWrapper* w, void* external_stream);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetOrtGraphOptLevel(FD_C_RuntimeOptionWrapper* w, int level);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperUseSophgoBackend(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperUsePorosBackend(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperUseLiteBackend(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperUsePaddleLiteBackend(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetPaddleMKLDNN(FD_C_RuntimeOptionWrapper* w, FD_C_Bool pd_mkldnn);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperEnablePaddleToTrt(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperDeletePaddleBackendPass(FD_C_RuntimeOptionWrapper* w, const char* delete_pass_name);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperEnablePaddleLogInfo(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperDisablePaddleLogInfo(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetPaddleMKLDNNCacheSize(FD_C_RuntimeOptionWrapper* w, int size);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetOpenVINODevice(FD_C_RuntimeOptionWrapper* w, const char* name);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetOpenVINOStreams(FD_C_RuntimeOptionWrapper* w, int num_streams);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetLiteOptimizedModelDir(FD_C_RuntimeOptionWrapper* w, const char* dir);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetLiteSubgraphPartitionPath(FD_C_RuntimeOptionWrapper* w, const char* path);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetLiteSubgraphPartitionConfigBuffer(FD_C_RuntimeOptionWrapper* w, const char* buffer);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetLiteContextProperties(FD_C_RuntimeOptionWrapper* w, const char* properties);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetLiteModelCacheDir(FD_C_RuntimeOptionWrapper* w, const char* dir);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetLiteMixedPrecisionQuantizationConfigPath(FD_C_RuntimeOptionWrapper* w, const char* path);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperEnableLiteFP16(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperDisableLiteFP16(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperEnableLiteInt8(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperDisableLiteInt8(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperSetLitePowerMode(FD_C_RuntimeOptionWrapper* w, int mode);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperEnablePaddleTrtCollectShape(FD_C_RuntimeOptionWrapper* w);
+FD_C_EXPORT void FD_C_RuntimeOptionWrapperDisablePaddleTrtCollectShape(FD_C_RuntimeOptionWrapper* w);
+
 /* ---- Runtime (generic tensors in, tensors out) */
 FD_C_EXPORT FD_C_RuntimeWrapper* FD_C_CreateRuntimeWrapper(FD_C_RuntimeOptionWrapper* option);
 FD_C_EXPORT void FD_C_DestroyRuntimeWrapper(FD_C_RuntimeWrapper* w);
@@ -152,6 +193,75 @@ FD_C_EXPORT void FD_C_DestroyOCRResult(FD_C_OCRResult* r);
 FD_C_EXPORT FD_C_Bool FD_C_VisDetection(FD_C_Mat img, const FD_C_DetectionResult* result, float score_threshold,
                                         int line_size, float font_size, FD_C_Mat* out);
 FD_C_EXPORT FD_C_Bool FD_C_VisSegmentation(FD_C_Mat img, const FD_C_SegmentationResult* result, float weight, FD_C_Mat* out);
+
+/* ---- the detection classes by name (c_api/fastdeploy_capi/vision/detection/ppdet/model.h,
+ * vision/detection/contrib/yolo/model.h): FD_C_Create<T>Wrapper, FD_C_Destroy<T>Wrapper, FD_C_<T>WrapperPredict,
+ * FD_C_<T>WrapperInitialized, FD_C_<T>WrapperBatchPredict for every T below. The PaddleDetection exports take a config
+ * file; the YOLO family (ONNX exports) does not. */
+#define FD_C_PPDET_MODELS(X)                                                                                              \
+  X(PicoDet) X(PPYOLO) X(YOLOv3) X(PaddleYOLOX) X(FasterRCNN) X(MaskRCNN) X(SSD) X(PaddleYOLOv5) X(PaddleYOLOv6)          \
+  X(PaddleYOLOv7) X(PaddleYOLOv8) X(RTMDet) X(CascadeRCNN) X(PSSDet) X(RetinaNet) X(FCOS) X(TTFNet) X(TOOD) X(GFL)
+#define FD_C_YOLO_MODELS(X) X(YOLOv5) X(YOLOv7) X(YOLOv8) X(YOLOv6) X(YOLOR) X(YOLOX)
+
+#define FD_C_DECLARE_DETECTION_COMMON(T)                                                                                  \
+  typedef FD_C_ModelWrapper FD_C_##T##Wrapper;                                                                            \
+  FD_C_EXPORT void FD_C_Destroy##T##Wrapper(FD_C_##T##Wrapper* w);                                                        \
+  FD_C_EXPORT FD_C_Bool FD_C_##T##WrapperPredict(FD_C_##T##Wrapper* w, FD_C_Mat img, FD_C_DetectionResult* result);       \
+  FD_C_EXPORT FD_C_Bool FD_C_##T##WrapperInitialized(FD_C_##T##Wrapper* w);                                               \
+  FD_C_EXPORT FD_C_Bool FD_C_##T##WrapperBatchPredict(FD_C_##T##Wrapper* w, const FD_C_Mat* imgs, int n_imgs,             \
+                                                      FD_C_DetectionResult* results);
+#define FD_C_DECLARE_PPDET(T)                                                                                             \
+  FD_C_DECLARE_DETECTION_COMMON(T)                                                                                        \
+  FD_C_EXPORT FD_C_##T##Wrapper* FD_C_Create##T##Wrapper(const char* model_file, const char* params_file,                 \
+                                                         const char* config_file, FD_C_RuntimeOptionWrapper* option,      \
+                                                         FD_C_ModelFormat format);
+#define FD_C_DECLARE_YOLO(T)                                                                                              \
+  FD_C_DECLARE_DETECTION_COMMON(T)                                                                                        \
+  FD_C_EXPORT FD_C_##T##Wrapper* FD_C_Create##T##Wrapper(const char* model_file, const char* params_file,                 \
+                                                         FD_C_RuntimeOptionWrapper* option, FD_C_ModelFormat format);
+FD_C_PPDET_MODELS(FD_C_DECLARE_PPDET)
+FD_C_YOLO_MODELS(FD_C_DECLARE_YOLO)
+FD_C_EXPORT FD_C_Bool FD_C_PPYOLOEWrapperBatchPredict(FD_C_PPYOLOEWrapper* w, const FD_C_Mat* imgs, int n_imgs,
+                                                      FD_C_DetectionResult* results);
+
+/* ---- classification and segmentation: batches and the initialised flag */
+FD_C_EXPORT FD_C_Bool FD_C_PaddleClasModelWrapperInitialized(FD_C_PaddleClasModelWrapper* w);
+FD_C_EXPORT FD_C_Bool FD_C_PaddleClasModelWrapperBatchPredict(FD_C_PaddleClasModelWrapper* w, const FD_C_Mat* imgs, int n_imgs,
+                                                              FD_C_ClassifyResult* results);
+FD_C_EXPORT void FD_C_DestroyPaddleSegModelWrapper(FD_C_PaddleSegModelWrapper* w);
+FD_C_EXPORT FD_C_Bool FD_C_PaddleSegModelWrapperInitialized(FD_C_PaddleSegModelWrapper* w);
+FD_C_EXPORT FD_C_Bool FD_C_PaddleSegModelWrapperBatchPredict(FD_C_PaddleSegModelWrapper* w, const FD_C_Mat* imgs, int n_imgs,
+                                                             FD_C_SegmentationResult* results);
+
+/* ---- OCR: the pipeline of the previous generation and batches (c_api/fastdeploy_capi/vision/ocr/ppocr/model.h:330-460) */
+typedef FD_C_ModelWrapper FD_C_PPOCRv2Wrapper;
+FD_C_EXPORT FD_C_PPOCRv2Wrapper* FD_C_CreatePPOCRv2Wrapper(const char* det_model_file, const char* det_params_file,
+                                                           const char* cls_model_file, const char* cls_params_file,
+                                                           const char* rec_model_file, const char* rec_params_file,
+                                                           const char* rec_label_file, FD_C_RuntimeOptionWrapper* option);
+FD_C_EXPORT FD_C_Bool FD_C_PPOCRv2WrapperPredict(FD_C_PPOCRv2Wrapper* w, FD_C_Mat img, FD_C_OCRResult* result);
+FD_C_EXPORT FD_C_Bool FD_C_PPOCRv2WrapperBatchPredict(FD_C_PPOCRv2Wrapper* w, const FD_C_Mat* imgs, int n_imgs, FD_C_OCRResult* results);
+FD_C_EXPORT FD_C_Bool FD_C_PPOCRv3WrapperBatchPredict(FD_C_PPOCRv3Wrapper* w, const FD_C_Mat* imgs, int n_imgs, FD_C_OCRResult* results);
+FD_C_EXPORT void FD_C_DestroyPPOCRv2Wrapper(FD_C_PPOCRv2Wrapper* w);
+FD_C_EXPORT void FD_C_DestroyPPOCRv3Wrapper(FD_C_PPOCRv3Wrapper* w);
+
+/* ---- images (c_api/fastdeploy_capi/core/fd_type.h:150-165). FD_C_Imread returns a BGR image whose pixels the library
+ * owns (data is NULL on failure); release it with FD_C_DestroyMat. */
+FD_C_EXPORT FD_C_Mat FD_C_Imread(const char* path);
+FD_C_EXPORT FD_C_Bool FD_C_Imwrite(const char* path, FD_C_Mat img);
+FD_C_EXPORT void FD_C_DestroyMat(FD_C_Mat img);
+
+/* ---- result text, the reference's Str(): writes at most `capacity` bytes including the terminator and returns the
+ * length the whole text needs (c_api/fastdeploy_capi/vision/result.h: FD_C_*ResultStr) */
+FD_C_EXPORT size_t FD_C_ClassifyResultStr(const FD_C_ClassifyResult* r, char* buffer, size_t capacity);
+FD_C_EXPORT size_t FD_C_DetectionResultStr(const FD_C_DetectionResult* r, char* buffer, size_t capacity);
+FD_C_EXPORT size_t FD_C_OCRResultStr(const FD_C_OCRResult* r, char* buffer, size_t capacity);
+FD_C_EXPORT size_t FD_C_SegmentationResultStr(const FD_C_SegmentationResult* r, char* buffer, size_t capacity);
+
+/* ---- more visualisers (c_api/fastdeploy_capi/vision/visualize.h:40-100) */
+FD_C_EXPORT FD_C_Bool FD_C_VisDetectionWithLabel(FD_C_Mat img, const FD_C_DetectionResult* result, const char* const* labels,
+                                                 int n_labels, float score_threshold, int line_size, float font_size, FD_C_Mat* out);
+FD_C_EXPORT FD_C_Bool FD_C_VisOcr(FD_C_Mat img, const FD_C_OCRResult* result, FD_C_Mat* out);
 
 /* ---- results */
 FD_C_EXPORT void FD_C_DestroyClassifyResult(FD_C_ClassifyResult* r);

@@ -195,6 +195,10 @@ class RuntimeOption:
     def set_lite_subgraph_partition_config_buffer(self, v): self._vendor["lite"].nnadapter_subgraph_partition_config_buffer = v
     def set_lite_mixed_precision_quantization_config_path(self, v): self._vendor["lite"].nnadapter_mixed_precision_quantization_config_path = v
     def set_lite_power_mode(self, mode): self._vendor["lite"].power_mode = mode
+    def set_lite_optimized_model_dir(self, v): self._vendor["lite"].optimized_model_dir = v
+    def enable_lite_int8(self): self._vendor["lite"].enable_int8 = True
+    def disable_lite_int8(self): self._vendor["lite"].enable_int8 = False
+    def set_openvino_streams(self, num_streams): self._vendor["openvino"].num_streams = int(num_streams)
 
     @property
     def trt_option(self): return self._vendor["trt"]

@@ -66,3 +66,52 @@ def test_plan_runner_header_links_and_reports_errors(tmp_path):
     # the library itself does not depend on the interpreter
     deps = subprocess.run(["ldd", build.RUNNER_LIB], capture_output=True, text=True).stdout
     assert "python" not in deps.lower()
+
+
+@pytest.mark.skipif(shutil.which("gcc") is None, reason="no C compiler")
+def test_c_program_uses_models_by_name_batches_text_and_image_files(tmp_path):
+    from fastdeploy_b200._native import build
+    if not build.build_capi():
+        pytest.skip("interpreter headers not available")
+    import fastdeploy_b200 as fd
+    from fastdeploy_b200.models.ppyoloe import write_ppyoloe
+    from fastdeploy_b200.models.vit import write_vit
+    det = write_ppyoloe(str(tmp_path / "det"), "tiny", image=96, num_classes=6, score_threshold=0.005)
+    cls = write_vit(str(tmp_path / "cls"), "tiny", image=32, num_classes=10, seed=3)
+    exe = str(tmp_path / "capi_models")
+    subprocess.run(["gcc", "-Wall", "-Werror", os.path.join(ROOT, "tests", "capi_models.c"), "-I", os.path.join(ROOT, "csrc", "capi"),
+                    "-o", exe, "-L", os.path.dirname(LIB), "-lfastdeploy_capi", f"-Wl,-rpath,{os.path.dirname(LIB)}"], check=True)
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.pathsep.join(p for p in sys.path if p))
+    env.pop("PYTHONHOME", None)
+    png = str(tmp_path / "drawn.png")
+    p = subprocess.run([exe, det["model"], det["params"], det["config"], cls["model"], cls["params"], cls["config"], png],
+                       capture_output=True, text=True, env=env, timeout=600)
+    assert p.returncode == 0, p.stdout + p.stderr
+    out = dict(line.split("=", 1) for line in p.stdout.strip().splitlines() if "=" in line)
+    assert out["options"] == "ok" and out["initialized"] == "1"
+    assert out["boxes"].endswith("batch_equals_single=1")
+    n0 = int(out["boxes"].split(",")[0])
+    # the same two images through the Python class
+    opt = fd.RuntimeOption(); opt.use_cpu()
+    m = fd.vision.detection.PicoDet(det["model"], det["params"], det["config"], runtime_option=opt)
+
+    def image(h, w, seed):
+        vals = []
+        for _ in range(h * w * 3):
+            seed = (seed * 1664525 + 1013904223) & 0xFFFFFFFF
+            vals.append(seed >> 24)
+        return np.asarray(vals, np.uint8).reshape(h, w, 3)
+
+    ims = [image(60, 120, 1), image(70, 120, 2)]
+    want = m.batch_predict(ims)
+    assert n0 == len(want[0].scores)
+    text = str(want[0])
+    assert out["str_need"].startswith(f"{len(text.encode()) + 1} head=DetectionResult: [xmin, ymin, xmax, ymax")
+    assert out["tiny"] == "Detecti"                                   # 7 characters and the terminator
+    assert out["png_roundtrip"] == "1" and os.path.getsize(png) > 0
+    assert out["missing"] == "null err=set" and out["yolov5"] == "null"
+    c = fd.vision.classification.PaddleClasModel(cls["model"], cls["params"], cls["config"], runtime_option=opt)
+    labels = [r.label_ids[0] for r in c.batch_predict(ims)]
+    assert out["cls_initialized"] == f"1 labels={labels[0]},{labels[1]} single={labels[0]}"
+    assert out["cls_str"] == "ClassifyResult("
+    assert int(out["empty_ocr_str_len"]) >= 0
