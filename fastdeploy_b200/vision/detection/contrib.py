@@ -201,6 +201,10 @@ class YOLOPostprocessor:
         self.multi_label = True
         self.max_wh = 7680.0
         self.strides = [8, 16, 32]
+        # kept for models exported without the decode step (yolov5lite.cc:190-240); the exports handled here are decoded
+        self.is_decode_exported = True
+        self.anchor_config = [[10.0, 13.0, 16.0, 30.0, 33.0, 23.0], [30.0, 61.0, 62.0, 45.0, 59.0, 119.0],
+                              [116.0, 90.0, 156.0, 198.0, 373.0, 326.0]]
 
     def _candidates(self, out: np.ndarray, info: Dict[str, Any]):
         if self.kind == "v8":
@@ -252,18 +256,53 @@ class YOLOPostprocessor:
         return results
 
 
+def _forwarded(owner: str, attr: str, doc: str = ""):
+    """A model attribute of older releases that now lives on the pre- or post-processor
+    (e.g. ``model.size`` -> ``model.preprocessor.size``; python/fastdeploy/vision/detection/contrib/yolov5.py:130-230)."""
+    def get(self):
+        return getattr(getattr(self, owner), attr)
+
+    def put(self, value):
+        setattr(getattr(self, owner), attr, value)
+    return property(get, put, doc=doc)
+
+
 class _YOLOModel(FastDeployModel):
     KIND = "v5"
     SIZE = (640, 640)
+    PRE = None          # processor classes; a family below names its own
+    POST = None
 
     def __init__(self, model_file: str, params_file: str = "", runtime_option: Optional[RuntimeOption] = None,
                  model_format: int = ModelFormat.ONNX):
         super().__init__(runtime_option)
         self.runtime_option.set_model_path(model_file, params_file, model_format)
-        self.preprocessor = YOLOPreprocessor(self.SIZE)
-        self.postprocessor = YOLOPostprocessor(self.KIND)
+        self.preprocessor = self.PRE() if self.PRE is not None else YOLOPreprocessor(self.SIZE)
+        self.postprocessor = self.POST() if self.POST is not None else YOLOPostprocessor(self.KIND)
         self._configure()
         self.init_runtime()
+
+    size = _forwarded("preprocessor", "size", "[width, height] of the network input")
+    padding_value = _forwarded("preprocessor", "padding_value")
+    is_mini_pad = _forwarded("preprocessor", "is_mini_pad")
+    is_no_pad = _forwarded("preprocessor", "is_no_pad")
+    is_scale_up = _forwarded("preprocessor", "is_scale_up")
+    stride = _forwarded("preprocessor", "stride")
+    max_wh = _forwarded("postprocessor", "max_wh")
+    multi_label = _forwarded("postprocessor", "multi_label")
+    conf_threshold = _forwarded("postprocessor", "conf_threshold")
+    nms_threshold = _forwarded("postprocessor", "nms_threshold")
+    downsample_strides = _forwarded("postprocessor", "strides", "strides of the head levels")
+    is_decode_exported = _forwarded("postprocessor", "is_decode_exported")
+    anchor_config = _forwarded("postprocessor", "anchor_config")
+
+    @property
+    def keep_ratio(self) -> bool:
+        return not self.preprocessor.is_no_pad
+
+    @keep_ratio.setter
+    def keep_ratio(self, v: bool) -> None:
+        self.preprocessor.is_no_pad = not v
 
     def _configure(self) -> None:
         pass
@@ -307,27 +346,47 @@ class _YOLOModel(FastDeployModel):
         return self.postprocessor.run(outs, infos)
 
 
-def _model(name: str, kind: str, doc: str, **cfg):
+def _model(name: str, kind: str, doc: str, pre=None, post=None, **cfg):
     def _configure(self):
         for k, v in cfg.items():
             target = self.preprocessor if hasattr(self.preprocessor, k) else self.postprocessor
             setattr(target, k, v)
-    return type(name, (_YOLOModel,), {"KIND": kind, "__doc__": doc, "_configure": _configure})
+    return type(name, (_YOLOModel,), {"KIND": kind, "__doc__": doc, "_configure": _configure, "PRE": pre, "POST": post})
 
 
-YOLOv5 = _model("YOLOv5", "v5", "YOLOv5 (contrib/yolov5/yolov5.cc).")
+def _processor_pair(family: str, kind: str, where: str):
+    """The pre- and post-processor classes a family exposes under its own name (``YOLOv5Preprocessor`` ...); they are the
+    shared letterbox and decoder with the family's defaults."""
+    pre = type(f"{family}Preprocessor", (YOLOPreprocessor,),
+               {"__doc__": f"Letterbox to 640 x 640, BGR->RGB, 1/255, CHW ({where}/preprocessor.cc)."})
+
+    def post_init(self):
+        YOLOPostprocessor.__init__(self, kind)
+    post = type(f"{family}Postprocessor", (YOLOPostprocessor,),
+                {"__init__": post_init, "__doc__": f"Confidence filter, class-aware NMS, boxes back to the source image ({where}/postprocessor.cc)."})
+    return pre, post
+
+
+YOLOv5Preprocessor, YOLOv5Postprocessor = _processor_pair("YOLOv5", "v5", "contrib/yolov5")
+YOLOv7Preprocessor, YOLOv7Postprocessor = _processor_pair("YOLOv7", "v5", "contrib/yolov7")
+YOLOv8Preprocessor, YOLOv8Postprocessor = _processor_pair("YOLOv8", "v8", "contrib/yolov8")
+RKYOLOPreprocessor, RKYOLOPostprocessor = _processor_pair("RKYOLO", "v5", "contrib/rknpu2")
+
+YOLOv5 = _model("YOLOv5", "v5", "YOLOv5 (contrib/yolov5/yolov5.cc).", YOLOv5Preprocessor, YOLOv5Postprocessor)
 YOLOv5Lite = _model("YOLOv5Lite", "v5", "YOLOv5-Lite with decoded export (contrib/yolov5lite.cc).", conf_threshold=0.45)
 YOLOv6 = _model("YOLOv6", "v5", "YOLOv6 (contrib/yolov6.cc).")
-YOLOv7 = _model("YOLOv7", "v5", "YOLOv7 (contrib/yolov7/yolov7.cc).")
-YOLOv8 = _model("YOLOv8", "v8", "YOLOv8 (contrib/yolov8/yolov8.cc): [4 + classes, anchors] head without objectness.")
+YOLOv7 = _model("YOLOv7", "v5", "YOLOv7 (contrib/yolov7/yolov7.cc).", YOLOv7Preprocessor, YOLOv7Postprocessor)
+YOLOv8 = _model("YOLOv8", "v8", "YOLOv8 (contrib/yolov8/yolov8.cc): [4 + classes, anchors] head without objectness.",
+                YOLOv8Preprocessor, YOLOv8Postprocessor)
 YOLOR = _model("YOLOR", "v5", "YOLOR (contrib/yolor.cc).")
 ScaledYOLOv4 = _model("ScaledYOLOv4", "v5", "Scaled-YOLOv4 (contrib/scaledyolov4.cc).")
 YOLOX = _model("YOLOX", "x", "YOLOX (contrib/yolox.cc): grid decode, bottom-right padding, no 1/255 scaling.",
                center=False, normalize=False, swap_rb=False)
 YOLOv7End2EndORT = _model("YOLOv7End2EndORT", "e2e", "YOLOv7 exported with the NMS plugin for ORT (yolov7end2end_ort.cc).")
 YOLOv7End2EndTRT = _model("YOLOv7End2EndTRT", "e2e", "YOLOv7 exported with EfficientNMS for TensorRT (yolov7end2end_trt.cc).")
-RKYOLOV5 = _model("RKYOLOV5", "v5", "YOLOv5 head layout of the Rockchip export (contrib/rknpu2/rkyolo.cc).")
-RKYOLOV7 = _model("RKYOLOV7", "v5", "YOLOv7 head layout of the Rockchip export.")
+RKYOLOV5 = _model("RKYOLOV5", "v5", "YOLOv5 head layout of the Rockchip export (contrib/rknpu2/rkyolo.cc).",
+                  RKYOLOPreprocessor, RKYOLOPostprocessor)
+RKYOLOV7 = _model("RKYOLOV7", "v5", "YOLOv7 head layout of the Rockchip export.", RKYOLOPreprocessor, RKYOLOPostprocessor)
 RKYOLOX = _model("RKYOLOX", "x", "YOLOX head layout of the Rockchip export.", center=False, normalize=False, swap_rb=False)
 
 
@@ -384,21 +443,22 @@ class NanoDetPlus(_YOLOModel):
         return res
 
 
-class FastestDet(_YOLOModel):
-    """FastestDet (contrib/fastestdet/postprocessor.cc): one 22x22 map of ``[obj, tanh dx, tanh dy,
-    sigmoid w, sigmoid h, cls...]``; score = obj^0.6 * cls^0.4; boxes normalised to the input."""
-    SIZE = (352, 352)
+class FastestDetPreprocessor(YOLOPreprocessor):
+    """Plain resize to 352 x 352 (no letterbox), BGR kept, 1/255, CHW (contrib/fastestdet/preprocessor.cc:27-80)."""
 
-    def _configure(self) -> None:
-        self.preprocessor.is_no_pad = True
-        self.preprocessor.swap_rb = False
-        self.postprocessor.conf_threshold = 0.65
-        self.postprocessor.nms_threshold = 0.45
+    def __init__(self):
+        super().__init__((352, 352))
+        self.is_no_pad = True
+        self.swap_rb = False
 
-    def batch_predict(self, images):
-        x, infos = self.preprocessor.run(images)
-        out = np.asarray(self.runtime.infer({self.runtime.get_input_info(0).name: x})[0], np.float32)
-        return [self.decode(out[i], info) for i, info in enumerate(infos)]
+
+class FastestDetPostprocessor:
+    """One 22 x 22 map of ``[obj, tanh dx, tanh dy, sigmoid w, sigmoid h, cls...]``; score = obj^0.6 * cls^0.4; boxes
+    normalised to the input, scaled to the source image (contrib/fastestdet/postprocessor.cc:30-110)."""
+
+    def __init__(self):
+        self.conf_threshold = 0.65
+        self.nms_threshold = 0.45
 
     def decode(self, out: np.ndarray, info: Dict[str, Any]) -> DetectionResult:
         c, fh, fw = out.shape
@@ -414,30 +474,51 @@ class FastestDet(_YOLOModel):
         bh = 1.0 / (1.0 + np.exp(-out[4]))
         ih, iw = info["in_hw"]
         boxes = np.stack([(cx - bw / 2) * iw, (cy - bh / 2) * ih, (cx + bw / 2) * iw, (cy + bh / 2) * ih], -1).reshape(-1, 4)
-        m = score.ravel() > self.postprocessor.conf_threshold
+        m = score.ravel() > self.conf_threshold
         inf = {"scale": 1.0, "pad_w": 0, "pad_h": 0, "in_hw": (ih, iw)}
-        return finish(boxes[m], score.ravel()[m], labels.ravel()[m], inf, self.postprocessor.nms_threshold)[0]
+        return finish(boxes[m], score.ravel()[m], labels.ravel()[m], inf, self.nms_threshold)[0]
+
+    def run(self, outputs: Sequence[np.ndarray], infos: List[Dict[str, Any]]) -> List[DetectionResult]:
+        out = np.asarray(outputs[0], np.float32)
+        return [self.decode(out[i], info) for i, info in enumerate(infos)]
 
 
-class YOLOv5Seg(_YOLOModel):
-    """YOLOv5 instance segmentation (contrib/yolov5seg/postprocessor.cc): rows carry 32 mask
-    coefficients after the class scores; masks = sigmoid(coeff @ protos) cropped to the box, resized
-    to the source image and thresholded at 0.5."""
-
-    def _configure(self) -> None:
-        self.mask_nums = 32
-        self.mask_threshold = 0.5
+class FastestDet(_YOLOModel):
+    """FastestDet (contrib/fastestdet/fastestdet.cc)."""
+    SIZE = (352, 352)
+    PRE = FastestDetPreprocessor
+    POST = FastestDetPostprocessor
 
     def batch_predict(self, images):
         x, infos = self.preprocessor.run(images)
-        outs = self.runtime.infer({self.runtime.get_input_info(0).name: x})
-        det, protos = np.asarray(outs[0], np.float32), np.asarray(outs[1], np.float32)
+        return self.postprocessor.run(self.runtime.infer({self.runtime.get_input_info(0).name: x}), infos)
+
+    def decode(self, out: np.ndarray, info: Dict[str, Any]) -> DetectionResult:
+        return self.postprocessor.decode(out, info)
+
+
+class YOLOv5SegPreprocessor(YOLOPreprocessor):
+    """The YOLOv5 letterbox (contrib/yolov5seg/preprocessor.cc)."""
+
+
+class YOLOv5SegPostprocessor(YOLOPostprocessor):
+    """YOLOv5 instance segmentation (contrib/yolov5seg/postprocessor.cc:30-190): rows carry ``mask_nums`` mask
+    coefficients after the class scores; masks = sigmoid(coeff @ protos) cropped to the box, resized to the source image
+    and thresholded at ``mask_threshold``."""
+
+    def __init__(self):
+        super().__init__("v5")
+        self.mask_nums = 32
+        self.mask_threshold = 0.5
+
+    def run(self, outputs: Sequence[np.ndarray], infos: List[Dict[str, Any]]) -> List[DetectionResult]:
+        det, protos = np.asarray(outputs[0], np.float32), np.asarray(outputs[1], np.float32)
         res = []
         for i, info in enumerate(infos):
             rows = det[i]
             ncls = rows.shape[1] - 5 - self.mask_nums
-            boxes, conf, labels, idx = self.postprocessor._candidates(rows[:, :5 + ncls], info)
-            r, keep = finish(boxes, conf, labels, info, self.postprocessor.nms_threshold)
+            boxes, conf, labels, idx = self._candidates(rows[:, :5 + ncls], info)
+            r, keep = finish(boxes, conf, labels, info, self.nms_threshold)
             r.contain_masks = True
             if len(keep):
                 coeff = rows[idx[keep], 5 + ncls:]
@@ -464,3 +545,16 @@ class YOLOv5Seg(_YOLOModel):
         out.data = (full > self.mask_threshold).astype(np.uint8)
         out.shape = [h, w]
         return out
+
+
+class YOLOv5Seg(_YOLOModel):
+    """YOLOv5 instance segmentation (contrib/yolov5seg/yolov5seg.cc)."""
+    PRE = YOLOv5SegPreprocessor
+    POST = YOLOv5SegPostprocessor
+
+    mask_nums = _forwarded("postprocessor", "mask_nums")
+    mask_threshold = _forwarded("postprocessor", "mask_threshold")
+
+    def batch_predict(self, images):
+        x, infos = self.preprocessor.run(images)
+        return self.postprocessor.run(self.runtime.infer({self.runtime.get_input_info(0).name: x}), infos)

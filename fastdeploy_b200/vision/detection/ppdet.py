@@ -39,6 +39,19 @@ class NMSOption:
         self.score_threshold = 0.3
 
 
+class NMSRotatedOption:
+    """Defaults of fastdeploy/vision/detection/ppdet/multiclass_nms_rotated.h:32-41 (PP-YOLOE-R)."""
+
+    def __init__(self):
+        self.background_label = -1
+        self.keep_top_k = -1
+        self.nms_eta = 1.0
+        self.nms_threshold = 0.1
+        self.nms_top_k = 2000
+        self.normalized = False
+        self.score_threshold = 0.1
+
+
 class PaddleDetPreprocessor:
     def __init__(self, config_file: str):
         self.config_file = config_file
