@@ -46,6 +46,85 @@ def _finish(boxes, scores, lms, k, nms_iou, info=None, clip_hw=None) -> FaceDete
     return r
 
 
+def _defaults(obj, size) -> None:
+    """Settings every face detector has; the letterbox ones carry the names of the reference's attributes
+    (python/fastdeploy/vision/facedet/contrib/scrfd.py:60-190)."""
+    obj.size = list(size)
+    obj.conf_threshold = 0.25
+    obj.nms_iou_threshold = 0.4
+    obj.padding_value = [0.0, 0.0, 0.0]
+    obj.is_mini_pad = False
+    obj.is_no_pad = False
+    obj.is_scale_up = True
+    obj.stride = 32
+    obj.max_nms = 30000
+    obj.normalize = True
+    obj.permute = True
+
+
+class _FaceProcessor:
+    """Pre- or post-processing half of a face detector as a separate object
+    (fastdeploy/vision/facedet/contrib/yolov7face/{preprocessor,postprocessor}.h, facedet/ppdet/blazeface/,
+    facedet/contrib/centerface/). Made on its own it holds its own settings; reached through ``model.preprocessor`` /
+    ``model.postprocessor`` it reads and writes the model's."""
+    MODEL = None
+    ROLE = "pre"
+
+    def __init__(self, _owner=None):
+        if _owner is None:
+            _owner = _Settings(self.MODEL)
+        object.__setattr__(self, "_state", _owner)
+
+    @classmethod
+    def view(cls, model, role: str) -> "_FaceProcessor":
+        named = _NAMED.get((type(model).__name__, role))
+        if named is None:
+            named = type(f"{type(model).__name__}{'Preprocessor' if role == 'pre' else 'Postprocessor'}", (_FaceProcessor,),
+                         {"MODEL": type(model), "ROLE": role})
+        return named(model)
+
+    def __getattr__(self, name):
+        return getattr(object.__getattribute__(self, "_state"), name)
+
+    def __setattr__(self, name, value):
+        setattr(object.__getattribute__(self, "_state"), name, value)
+
+    @property
+    def nms_threshold(self):
+        return self._state.nms_iou_threshold
+
+    @nms_threshold.setter
+    def nms_threshold(self, v):
+        self._state.nms_iou_threshold = v
+
+    def run(self, first, infos=None):
+        """Pre-processor: ``run(images) -> (batch [N, 3, H, W], infos)``. Post-processor: ``run(outputs, infos) ->
+        [FaceDetectionResult]`` with ``outputs`` the batched runtime outputs."""
+        st, model = self._state, self.MODEL
+        if self.ROLE == "pre":
+            pairs = [model.preprocess(st, im) for im in first]
+            return np.concatenate([p[0] for p in pairs]), [p[1] for p in pairs]
+        outs = [np.asarray(o, np.float32) for o in first]
+        return [model.postprocess(st, [o[i:i + 1] for o in outs], info) for i, info in enumerate(infos)]
+
+
+class _Settings:
+    """The attributes a detector's pre/post-processing reads, without a runtime behind them."""
+
+    def __init__(self, model_cls):
+        _defaults(self, model_cls.SIZE)
+        model_cls._configure(self)
+
+    def _letterbox(self, im, pad_value=None):
+        return _FaceDetBase._letterbox(self, im, pad_value)
+
+    def _layout(self, x):
+        return _FaceDetBase._layout(self, x)
+
+
+_NAMED: Dict[Tuple[str, str], type] = {}
+
+
 class _FaceDetBase(FastDeployModel):
     SIZE = (640, 640)
 
@@ -53,11 +132,41 @@ class _FaceDetBase(FastDeployModel):
                  model_format: int = ModelFormat.ONNX):
         super().__init__(runtime_option)
         self.runtime_option.set_model_path(model_file, params_file, model_format)
-        self.size = list(self.SIZE)
-        self.conf_threshold = 0.25
-        self.nms_iou_threshold = 0.4
+        _defaults(self, self.SIZE)
         self._configure()
         self.init_runtime()
+
+    @property
+    def preprocessor(self):
+        """The pre-processing half as an object of its own; its attributes are this model's."""
+        return _FaceProcessor.view(self, "pre")
+
+    @property
+    def postprocessor(self):
+        return _FaceProcessor.view(self, "post")
+
+    @property
+    def downsample_strides(self):
+        return self.strides
+
+    @downsample_strides.setter
+    def downsample_strides(self, v):
+        self.strides = list(v)
+
+    def disable_normalize(self) -> None:
+        """The graph normalises by itself: hand over RGB pixels as float, unscaled."""
+        self.normalize = False
+
+    def disable_permute(self) -> None:
+        """Hand over HWC instead of CHW."""
+        self.permute = False
+
+    def _letterbox(self, im, pad_value=None):
+        return letterbox(im, self.size, tuple(self.padding_value) if pad_value is None else pad_value, mini_pad=self.is_mini_pad,
+                         no_pad=self.is_no_pad, scale_up=self.is_scale_up, stride=self.stride)
+
+    def _layout(self, x: np.ndarray) -> np.ndarray:
+        return np.ascontiguousarray(x.transpose(2, 0, 1) if self.permute else x)[None]
 
     def _configure(self):
         pass
@@ -89,9 +198,11 @@ class SCRFD(_FaceDetBase):
         self.mean, self.scale = 127.5, 1.0 / 128.0
 
     def preprocess(self, im):
-        canvas, info = letterbox(im, self.size, (0, 0, 0))
-        x = (canvas[..., ::-1].astype(np.float32) - self.mean) * self.scale
-        return np.ascontiguousarray(x.transpose(2, 0, 1))[None], info
+        canvas, info = self._letterbox(im)
+        x = canvas[..., ::-1].astype(np.float32)
+        if self.normalize:
+            x = (x - self.mean) * self.scale
+        return self._layout(x), info
 
     def postprocess(self, outs, info):
         n_s = len(self.strides)
@@ -172,11 +283,14 @@ class YOLOv5Face(_FaceDetBase):
 
     def _configure(self):
         self.landmarks_per_face = 5
+        self.padding_value = [114.0, 114.0, 114.0]
 
     def preprocess(self, im):
-        canvas, info = letterbox(im, self.size, (114, 114, 114))
-        x = canvas[..., ::-1].astype(np.float32) / 255.0
-        return np.ascontiguousarray(x.transpose(2, 0, 1))[None], info
+        canvas, info = self._letterbox(im)
+        x = canvas[..., ::-1].astype(np.float32)
+        if self.normalize:
+            x = x / 255.0
+        return self._layout(x), info
 
     def postprocess(self, outs, info):
         rows = outs[0].reshape(-1, outs[0].shape[-1])
@@ -251,7 +365,10 @@ class BlazeFace(_FaceDetBase):
                 feeds[name] = np.asarray([[1.0 / info["sy"], 1.0 / info["sx"]]], np.float32)
             elif name == "im_shape":
                 feeds[name] = np.asarray([[self.size[1], self.size[0]]], np.float32)
-        rows = np.asarray(self.runtime.infer(feeds)[0], np.float32).reshape(-1, 6)
+        return self.postprocess([np.asarray(self.runtime.infer(feeds)[0], np.float32)], info)
+
+    def postprocess(self, outs, info):
+        rows = np.asarray(outs[0], np.float32).reshape(-1, 6)
         rows = rows[rows[:, 1] > self.conf_threshold]
         r = FaceDetectionResult()
         r.boxes, r.scores = rows[:, 2:6].tolist(), rows[:, 1].tolist()
@@ -268,9 +385,9 @@ class CenterFace(_FaceDetBase):
         self.landmarks_per_face = 5
 
     def preprocess(self, im):
-        canvas, info = letterbox(im, self.size, (0, 0, 0))
+        canvas, info = self._letterbox(im)
         x = canvas[..., ::-1].astype(np.float32)
-        return np.ascontiguousarray(x.transpose(2, 0, 1))[None], info
+        return self._layout(x), info
 
     def postprocess(self, outs, info):
         heat, scale, offset, lms = outs[0][0, 0], outs[1][0], outs[2][0], outs[3][0]
@@ -285,3 +402,18 @@ class CenterFace(_FaceDetBase):
             scores.append(heat[y, x])
             pts.append([[lms[2 * j + 1, y, x] * s1 + x1, lms[2 * j, y, x] * s0 + y1] for j in range(5)])
         return _finish(boxes, scores, pts, 5, self.nms_iou_threshold, info)
+
+
+def _named(model_cls, role: str, name: str):
+    cls = type(name, (_FaceProcessor,), {"MODEL": model_cls, "ROLE": role,
+                                          "__doc__": f"{'Pre' if role == 'pre' else 'Post'}-processing of :class:`{model_cls.__name__}`."})
+    _NAMED[(model_cls.__name__, role)] = cls
+    return cls
+
+
+BlazeFacePreprocessor = _named(BlazeFace, "pre", "BlazeFacePreprocessor")
+BlazeFacePostprocessor = _named(BlazeFace, "post", "BlazeFacePostprocessor")
+CenterFacePreprocessor = _named(CenterFace, "pre", "CenterFacePreprocessor")
+CenterFacePostprocessor = _named(CenterFace, "post", "CenterFacePostprocessor")
+Yolov7FacePreprocessor = _named(YOLOv7Face, "pre", "Yolov7FacePreprocessor")
+Yolov7FacePostprocessor = _named(YOLOv7Face, "post", "Yolov7FacePostprocessor")

@@ -92,3 +92,42 @@ def test_yolov5seg_masks_come_from_the_post_processor(tmp_path):
     mask = np.asarray(r.masks[0].data).reshape(r.masks[0].shape)
     assert mask.shape == (64, 64) and mask[32, 32] == 1 and mask[2, 2] == 0 and mask[60, 60] == 0
     assert 700 < int(mask.sum()) < 1400                       # about the 32 x 32 box
+
+
+def test_face_detector_processors_alone_and_through_the_model(tmp_path):
+    fdet = fd.vision.facedet
+    # standalone: CenterFace decode of one peak
+    pre = fdet.CenterFacePreprocessor()
+    assert pre.size == [640, 640]
+    pre.size = [64, 64]
+    x, infos = pre.run([np.zeros((64, 64, 3), np.uint8), np.zeros((32, 64, 3), np.uint8)])
+    assert x.shape == (2, 3, 64, 64) and infos[1]["pad_h"] == 16
+    heat = np.zeros((2, 1, 16, 16), np.float32); heat[0, 0, 8, 8] = 0.9
+    scale = np.zeros((2, 2, 16, 16), np.float32)                      # exp(0) * 4 = 4 pixels
+    offset = np.zeros((2, 2, 16, 16), np.float32)
+    lms = np.full((2, 10, 16, 16), 0.5, np.float32)
+    post = fdet.CenterFacePostprocessor()
+    assert post.conf_threshold == 0.5 and post.nms_threshold == pytest.approx(0.3)
+    res = post.run([heat, scale, offset, lms], infos)
+    assert len(res) == 2 and len(res[0].boxes) == 1 and len(res[1].boxes) == 0
+    assert np.allclose(res[0].boxes[0], [32, 32, 36, 36]) and np.allclose(res[0].landmarks[0], [34, 34])
+    assert fdet.Yolov7FacePreprocessor().padding_value == [114.0, 114.0, 114.0]
+    # through a model: the processors are views of the model's settings
+    rows = np.array([[0, 0.9, 10, 12, 40, 44], [0, 0.3, 1, 1, 5, 5]], np.float32)
+    m = fdet.BlazeFace(_head_model(str(tmp_path / "bf.onnx"), 64, rows), runtime_option=_opt())
+    m.size = [64, 64]
+    assert isinstance(m.preprocessor, fdet.BlazeFacePreprocessor) and isinstance(m.postprocessor, fdet.BlazeFacePostprocessor)
+    m.postprocessor.conf_threshold = 0.2
+    assert m.conf_threshold == 0.2
+    r = m.predict(np.zeros((64, 64, 3), np.uint8))
+    assert len(r.boxes) == 2
+    m.postprocessor.conf_threshold = 0.5
+    assert len(m.predict(np.zeros((64, 64, 3), np.uint8)).boxes) == 1
+    # attributes of older releases
+    s = fdet.SCRFD.__new__(fdet.SCRFD)
+    fdet._defaults(s, s.SIZE); s._configure()
+    assert s.downsample_strides == [8, 16, 32] and s.max_nms == 30000 and s.stride == 32 and not s.is_mini_pad
+    a = s.preprocess(np.full((40, 64, 3), 255, np.uint8))[0]
+    s.disable_normalize(); s.disable_permute()
+    b = s.preprocess(np.full((40, 64, 3), 255, np.uint8))[0]
+    assert a.shape == (1, 3, 640, 640) and b.shape == (1, 640, 640, 3) and b.max() == 255.0 and a.max() < 1.0
