@@ -22,6 +22,17 @@ class InsightFaceRecognitionPreprocessor:
         self.alpha = [1.0 / 128.0] * 3
         self.beta = [-127.5 / 128.0] * 3
         self.permute = True          # BGR -> RGB
+        self.normalize_ = True
+        self.chw_ = True
+
+    def disable_normalize(self) -> None:
+        """The graph applies ``alpha * x + beta`` itself: hand over the resized pixels as float
+        (fastdeploy/vision/faceid/contrib/insightface/preprocessor.cc:60-75)."""
+        self.normalize_ = False
+
+    def disable_permute(self) -> None:
+        """Leave the image HWC."""
+        self.chw_ = False
 
     def run(self, images: Sequence[np.ndarray]) -> np.ndarray:
         out = []
@@ -29,8 +40,10 @@ class InsightFaceRecognitionPreprocessor:
             x = im if im.shape[:2] == (self.size[1], self.size[0]) else _resize_bilinear(im, self.size[0], self.size[1])
             if self.permute:
                 x = x[..., ::-1]
-            x = x.astype(np.float32) * np.asarray(self.alpha, np.float32) + np.asarray(self.beta, np.float32)
-            out.append(np.ascontiguousarray(x.transpose(2, 0, 1)))
+            x = x.astype(np.float32)
+            if self.normalize_:
+                x = x * np.asarray(self.alpha, np.float32) + np.asarray(self.beta, np.float32)
+            out.append(np.ascontiguousarray(x.transpose(2, 0, 1) if self.chw_ else x))
         return np.stack(out)
 
 
@@ -85,9 +98,22 @@ class VPL(InsightFaceRecognitionBase):
     pass
 
 
+class AdaFacePreprocessor(InsightFaceRecognitionPreprocessor):
+    """AdaFace was trained on BGR crops: no channel swap (fastdeploy/vision/faceid/contrib/adaface/preprocessor.cc:25-70)."""
+
+    def __init__(self):
+        super().__init__()
+        self.permute = False
+
+
+class AdaFacePostprocessor(InsightFaceRecognitionPostprocessor):
+    """The embedding, optionally L2-normalised (fastdeploy/vision/faceid/contrib/adaface/postprocessor.cc)."""
+
+
 class AdaFace(InsightFaceRecognitionBase):
     def _configure(self):
-        self.preprocessor.permute = False
+        self.preprocessor = AdaFacePreprocessor()
+        self.postprocessor = AdaFacePostprocessor()
 
 
 def cosine_similarity(a, b, normalized: bool = True) -> float:

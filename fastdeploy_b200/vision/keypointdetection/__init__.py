@@ -110,6 +110,7 @@ class PPTinyPose(FastDeployModel):
         super().__init__(runtime_option)
         self.runtime_option.set_model_path(model_file, params_file, model_format)
         self.use_dark = True
+        self.normalize, self.permute = True, True
         with open(config_file) as f:
             cfg = yaml.safe_load(f)
         self.size = [192, 256]       # w, h
@@ -142,9 +143,11 @@ class PPTinyPose(FastDeployModel):
             center, scale = self._crop(im, b)
             m = get_affine(center, scale, self.size)
             crop = warp_affine(im, m, self.size)
-            x = crop[..., ::-1].astype(np.float32) / 255.0
-            x = (x - np.asarray(self.mean, np.float32)) / np.asarray(self.std, np.float32)
-            outs = self.runtime.infer({self.runtime.get_input_info(0).name: np.ascontiguousarray(x.transpose(2, 0, 1))[None]})
+            x = crop[..., ::-1].astype(np.float32)
+            if self.normalize:
+                x = (x / 255.0 - np.asarray(self.mean, np.float32)) / np.asarray(self.std, np.float32)
+            x = np.ascontiguousarray(x.transpose(2, 0, 1) if self.permute else x)[None]
+            outs = self.runtime.infer({self.runtime.get_input_info(0).name: x})
             heat = np.asarray(outs[0], np.float32)[0]
             pts, sc = decode_heatmaps(heat, center, scale, self.use_dark)
             res.keypoints += pts.tolist()
@@ -154,3 +157,12 @@ class PPTinyPose(FastDeployModel):
 
     def batch_predict(self, images, detection_results=None):
         return [self.predict(im, detection_results[i] if detection_results else None) for i, im in enumerate(images)]
+
+    def disable_normalize(self) -> None:
+        """The graph normalises by itself: the crop goes in as RGB float pixels
+        (python/fastdeploy/vision/keypointdetection/pptinypose/__init__.py:74-86)."""
+        self.normalize = False
+
+    def disable_permute(self) -> None:
+        """The crop goes in HWC."""
+        self.permute = False

@@ -18,8 +18,38 @@ from ...runtime.option import RuntimeOption
 from ..result import OCRResult
 
 
+class _NormalizeSwitches:
+    """``set_normalize`` / ``disable_normalize`` / ``disable_permute`` of the three OCR pre-processors
+    (fastdeploy/vision/ocr/ppocr/{det,cls,rec}_preprocessor.h). These act on the host path; the device pipeline always
+    feeds the network normalised CHW crops."""
+    normalize_ = True
+    permute_ = True
+
+    def set_normalize(self, mean, std, is_scale=True):
+        self.mean, self.scale, self.is_scale = list(mean), list(std), is_scale
+
+    def disable_normalize(self) -> None:
+        self.normalize_ = False
+
+    def disable_permute(self) -> None:
+        self.permute_ = False
+
+    def _finish(self, batch: np.ndarray) -> np.ndarray:
+        """``batch`` is NCHW as built; HWC is wanted after ``disable_permute``."""
+        return batch if self.permute_ else np.ascontiguousarray(batch.transpose(0, 2, 3, 1))
+
+
+def _forward(owner: str, attr: str):
+    def get(self):
+        return getattr(getattr(self, owner), attr)
+
+    def put(self, value):
+        setattr(getattr(self, owner), attr, value)
+    return property(get, put, doc=f"``{owner}.{attr}``, under the name older releases had on the model")
+
+
 # ---------------------------------------------------------------------------------- detection
-class DBDetectorPreprocessor:
+class DBDetectorPreprocessor(_NormalizeSwitches):
     def __init__(self):
         self.max_side_len = 960
         self.mean = [0.485, 0.456, 0.406]
@@ -27,9 +57,6 @@ class DBDetectorPreprocessor:
         self.is_scale = True
         self.static_shape_infer = False
         self.det_image_shape = [3, 960, 960]
-
-    def set_normalize(self, mean, std, is_scale=True):
-        self.mean, self.scale, self.is_scale = list(mean), list(std), is_scale
 
     def target_hw(self, h: int, w: int) -> Tuple[int, int]:
         """Limit the long side, then round both sides to multiples of 32 (min 32)."""
@@ -52,13 +79,13 @@ class DBDetectorPreprocessor:
             h, w = im.shape[:2]
             rh, rw = self.target_hw(h, w)
             r = cv2.resize(im, (rw, rh)) if (rh, rw) != (h, w) else im
-            mats.append(r.astype(np.float32) * np.float32(alpha) + np.float32(beta))
+            mats.append(r.astype(np.float32) * np.float32(alpha) + np.float32(beta) if self.normalize_ else r.astype(np.float32))
             infos.append([w, h, rw, rh])
         mh, mw = max(m.shape[0] for m in mats), max(m.shape[1] for m in mats)
         batch = np.zeros((len(mats), 3, mh, mw), np.float32)
         for i, m in enumerate(mats):
             batch[i, :, :m.shape[0], :m.shape[1]] = m.transpose(2, 0, 1)
-        return batch, infos
+        return self._finish(batch), infos
 
 
 def _order_clockwise(pts: np.ndarray) -> np.ndarray:
@@ -182,6 +209,13 @@ class DBDetector(_OcrStage):
         self.preprocessor = DBDetectorPreprocessor()
         self.postprocessor = DBDetectorPostprocessor()
 
+    max_side_len = _forward("preprocessor", "max_side_len")
+    det_db_thresh = _forward("postprocessor", "det_db_thresh")
+    det_db_box_thresh = _forward("postprocessor", "det_db_box_thresh")
+    det_db_unclip_ratio = _forward("postprocessor", "det_db_unclip_ratio")
+    det_db_score_mode = _forward("postprocessor", "det_db_score_mode")
+    use_dilation = _forward("postprocessor", "use_dilation")
+
     def predict(self, im: np.ndarray) -> List[List[int]]:
         return self.batch_predict([im])[0]
 
@@ -225,7 +259,7 @@ def get_rotate_crop_image(image: np.ndarray, box: Sequence[int]) -> np.ndarray:
 
 
 # ---------------------------------------------------------------------------------- classifier
-class ClassifierPreprocessor:
+class ClassifierPreprocessor(_NormalizeSwitches):
     def __init__(self):
         self.cls_image_shape = [3, 48, 192]
         self.mean, self.scale, self.is_scale = [0.5] * 3, [0.5] * 3, True
@@ -238,9 +272,10 @@ class ClassifierPreprocessor:
             ratio = im.shape[1] / im.shape[0]
             rw = W if math.ceil(H * ratio) > W else int(math.ceil(H * ratio))
             r = cv2.resize(im, (rw, H)).astype(np.float32)
-            r = (r / 255.0 - np.float32(self.mean)) / np.float32(self.scale)
+            if self.normalize_:
+                r = ((r / 255.0 if self.is_scale else r) - np.float32(self.mean)) / np.float32(self.scale)
             out[i, :, :, :rw] = r.transpose(2, 0, 1)
-        return out
+        return self._finish(out)
 
 
 class ClassifierPostprocessor:
@@ -259,6 +294,9 @@ class Classifier(_OcrStage):
         self.preprocessor = ClassifierPreprocessor()
         self.postprocessor = ClassifierPostprocessor()
 
+    cls_image_shape = _forward("preprocessor", "cls_image_shape")
+    cls_thresh = _forward("postprocessor", "cls_thresh")
+
     def predict(self, im):
         l, s = self.batch_predict([im])
         return l[0], s[0]
@@ -268,7 +306,7 @@ class Classifier(_OcrStage):
 
 
 # ---------------------------------------------------------------------------------- recogniser
-class RecognizerPreprocessor:
+class RecognizerPreprocessor(_NormalizeSwitches):
     def __init__(self):
         self.rec_image_shape = [3, 48, 320]
         self.mean, self.scale, self.is_scale = [0.5] * 3, [0.5] * 3, True
@@ -288,9 +326,11 @@ class RecognizerPreprocessor:
             r = cv2.resize(im, (rw, H))
             canvas = np.full((H, bw, 3), 127, np.uint8)
             canvas[:, :rw] = r
-            x = (canvas.astype(np.float32) / 255.0 - np.float32(self.mean)) / np.float32(self.scale)
+            x = canvas.astype(np.float32)
+            if self.normalize_:
+                x = ((x / 255.0 if self.is_scale else x) - np.float32(self.mean)) / np.float32(self.scale)
             out[i] = x.transpose(2, 0, 1)
-        return out
+        return self._finish(out)
 
 
 def ctc_greedy_decode(probs: np.ndarray, labels: Sequence[str]) -> Tuple[List[str], List[float]]:
@@ -337,6 +377,9 @@ class Recognizer(_OcrStage):
         super().__init__(model_file, params_file, runtime_option, model_format)
         self.preprocessor = RecognizerPreprocessor()
         self.postprocessor = RecognizerPostprocessor(label_path)
+
+    rec_image_shape = _forward("preprocessor", "rec_image_shape")
+    static_shape_infer = _forward("preprocessor", "static_shape_infer")
 
     def predict(self, im):
         t, s = self.batch_predict([im])
@@ -431,7 +474,15 @@ class PPOCRv4(PPOCRv3):
 PPOCRSystemv2, PPOCRSystemv3, PPOCRSystemv4 = PPOCRv2, PPOCRv3, PPOCRv4
 
 
-from .structure import (PPStructureV2Table, StructureV2Layout, StructureV2LayoutPostprocessor, StructureV2Table,  # noqa: E402,F401
+from .structure import (PPStructureV2Table, PPStructureV2TableSystem, StructureV2Layout,  # noqa: E402,F401
+                        StructureV2LayoutPostprocessor, StructureV2LayoutPreprocessor, StructureV2Table,
                         StructureV2TablePostprocessor, StructureV2TablePreprocessor, build_html)
 from .ser import (SERResult, StructureV2SERViLayoutXLM, StructureV2SERViLayoutXLMPostprocessor,  # noqa: E402,F401
                   StructureV2SERViLayoutXLMPreprocessor)
+from .ser_ops import (KeepKeys, NormalizeImage, Resize, ToCHWImage, VQAReTokenChunk, VQASerTokenChunk,  # noqa: E402,F401
+                      VQASerTokenLayoutLMPostProcess, VQATokenLabelEncode, VQATokenPad)
+
+# names of the reference's Python classes for the same three objects
+StructureV2SERViLayoutXLMModel = StructureV2SERViLayoutXLM
+StructureV2SERViLayoutXLMModelPreprocessor = StructureV2SERViLayoutXLMPreprocessor
+StructureV2SERViLayoutXLMModelPostprocessor = StructureV2SERViLayoutXLMPostprocessor

@@ -90,7 +90,7 @@ class StructureV2SERViLayoutXLMPreprocessor:
         return [int(i) for i in ids]
 
     def run(self, lines: Sequence[Dict[str, Any]], height: int, width: int) -> Dict[str, Any]:
-        lines = order_tb_yx([dict(r, bbox=_xyxy(r["bbox"])) for r in lines])
+        lines = order_tb_yx([dict(r, bbox=_xyxy(r["bbox"] if "bbox" in r else r["points"])) for r in lines])
         ids: List[int] = []
         boxes: List[List[int]] = []
         seg_end: List[int] = []

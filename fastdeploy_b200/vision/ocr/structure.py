@@ -158,22 +158,51 @@ class StructureV2LayoutPostprocessor:
         return out
 
 
+class StructureV2LayoutPreprocessor:
+    """Resize to 608 x 800 (w x h), BGR->RGB, ImageNet mean / std, CHW; remembers (w, h, resized w, resized h) per image
+    for the post-processor (fastdeploy/vision/ocr/ppocr/structurev2_layout_preprocessor.cc:25-90)."""
+
+    def __init__(self):
+        self.size = [608, 800]      # w, h
+        self.mean, self.std = [0.485, 0.456, 0.406], [0.229, 0.224, 0.225]
+        self.batch_layout_img_info: List[Tuple[int, int, int, int]] = []
+
+    def run(self, images: Sequence[np.ndarray]) -> np.ndarray:
+        out, self.batch_layout_img_info = [], []
+        for im in images:
+            h, w = im.shape[:2]
+            x = _resize_bilinear(im, *self.size)[..., ::-1].astype(np.float32) / 255.0
+            x = (x - np.asarray(self.mean, np.float32)) / np.asarray(self.std, np.float32)
+            out.append(np.ascontiguousarray(x.transpose(2, 0, 1)))
+            self.batch_layout_img_info.append((w, h, self.size[0], self.size[1]))
+        return np.stack(out)
+
+
 class StructureV2Layout(FastDeployModel):
     def __init__(self, model_file: str, params_file: str = "", runtime_option: Optional[RuntimeOption] = None,
                  model_format: int = ModelFormat.PADDLE):
         super().__init__(runtime_option)
         self.runtime_option.set_model_path(model_file, params_file, model_format)
-        self.size = [608, 800]      # w, h
-        self.mean, self.std = [0.485, 0.456, 0.406], [0.229, 0.224, 0.225]
+        self.preprocessor = StructureV2LayoutPreprocessor()
         self.postprocessor = StructureV2LayoutPostprocessor()
         self.init_runtime()
 
+    @property
+    def size(self):
+        return self.preprocessor.size
+
+    @size.setter
+    def size(self, v):
+        self.preprocessor.size = list(v)
+
+    def batch_predict(self, images: Sequence[np.ndarray]) -> List[DetectionResult]:
+        x = self.preprocessor.run(images)
+        outs = [np.asarray(o, np.float32) for o in self.runtime.infer({self.runtime.get_input_info(0).name: x})]
+        return [self.postprocessor.run([o[i:i + 1] for o in outs], info)
+                for i, info in enumerate(self.preprocessor.batch_layout_img_info)]
+
     def predict(self, im: np.ndarray) -> DetectionResult:
-        h, w = im.shape[:2]
-        x = _resize_bilinear(im, *self.size)[..., ::-1].astype(np.float32) / 255.0
-        x = (x - np.asarray(self.mean, np.float32)) / np.asarray(self.std, np.float32)
-        outs = self.runtime.infer({self.runtime.get_input_info(0).name: np.ascontiguousarray(x.transpose(2, 0, 1))[None]})
-        return self.postprocessor.run(outs, (w, h, self.size[0], self.size[1]))
+        return self.batch_predict([im])[0]
 
 
 def _box_distance(ocr_box: Sequence[float], cell: Sequence[float]) -> Tuple[float, float]:
@@ -230,3 +259,13 @@ class PPStructureV2Table:
         ocr.table_boxes, ocr.table_structure = t.table_boxes, t.table_structure
         ocr.table_html = build_html(t.table_structure, t.table_boxes, ocr.boxes, ocr.text)
         return ocr
+
+    def batch_predict(self, images: Sequence[np.ndarray]) -> List[OCRResult]:
+        return [self.predict(im) for im in images]
+
+    def clone(self) -> "PPStructureV2Table":
+        """A second pipeline over clones of the three models (they share weights, not buffers)."""
+        return PPStructureV2Table(self.detector.clone(), self.recognizer.clone(), self.table.clone())
+
+
+PPStructureV2TableSystem = PPStructureV2Table

@@ -17,17 +17,34 @@ from ..result import SegmentationResult
 class PaddleSegPreprocessor(ProcessorManager):
     def __init__(self, config_file: str):
         super().__init__()
-        with open(config_file) as f:
-            cfg = yaml.safe_load(f)
+        self.config_file = config_file
         self.is_vertical_screen = False
         self.disable_normalize_ = False
         self.disable_permute_ = False
+        self._build()
+
+    def disable_normalize(self) -> None:
+        """For a model that normalises inside its graph: the chain is rebuilt without Normalize
+        (fastdeploy/vision/segmentation/ppseg/preprocessor.cc:150-170)."""
+        self.disable_normalize_ = True
+        self._build()
+
+    def disable_permute(self) -> None:
+        """Leaves the image HWC."""
+        self.disable_permute_ = True
+        self._build()
+
+    def _build(self) -> None:
+        with open(self.config_file) as f:
+            cfg = yaml.safe_load(f)
         procs = [BGR2RGB()]
         self.is_contain_resize_op = False
         deploy = cfg.get("Deploy", {})
         for op in deploy.get("transforms", []) or []:
             t = op["type"]
             if t == "Normalize":
+                if self.disable_normalize_:
+                    continue
                 procs.append(Normalize(list(op.get("mean", [0.5] * 3)), list(op.get("std", [0.5] * 3))))
             elif t == "Resize":
                 self.is_contain_resize_op = True
@@ -37,7 +54,8 @@ class PaddleSegPreprocessor(ProcessorManager):
         if shape and not self.is_contain_resize_op and all(int(d) > 0 for d in shape[2:]):
             procs.insert(1, Resize(int(shape[3]), int(shape[2])))
             self.is_contain_resize_op = True
-        procs.append(HWC2CHW())
+        if not self.disable_permute_:
+            procs.append(HWC2CHW())
         self.processors = fuse_transforms(procs)
         self.with_softmax = deploy.get("output_op", "") == "softmax"
         self.with_argmax = deploy.get("output_op", "argmax") == "argmax"
