@@ -166,9 +166,61 @@ class _SoftmaxTopK(PaddleClasPostprocessor):
         return super().run([e / e.sum(1, keepdims=True)])
 
 
-class YOLOv5Cls(ResNet):
-    """YOLOv5 classification head: centre-crop resize to 224, ImageNet normalisation, softmax + top-k
-    (fastdeploy/vision/classification/contrib/yolov5cls)."""
+class YOLOv5ClsPreprocessor:
+    """Centre crop to the short side, resize to ``size`` (h, w), BGR->RGB, 1/255, ImageNet mean / std, CHW; ``run`` returns
+    the batch and, per image, the input and output shapes
+    (fastdeploy/vision/classification/contrib/yolov5cls/preprocessor.cc:23-90)."""
+
+    def __init__(self):
+        self.size = [224, 224]
+        self.mean, self.std = [0.485, 0.456, 0.406], [0.229, 0.224, 0.225]
+
+    def run(self, images: Sequence[np.ndarray]):
+        import cv2
+        if len(images) == 0:
+            raise ValueError("The size of input images should be greater than 0.")
+        out, infos = [], []
+        for im in images:
+            h, w = im.shape[:2]
+            c = min(h, w)
+            y, x = (h - c) // 2, (w - c) // 2
+            crop = cv2.resize(np.ascontiguousarray(im[y:y + c, x:x + c]), (self.size[1], self.size[0]), interpolation=cv2.INTER_LINEAR)
+            t = (crop[..., ::-1].astype(np.float32) / 255.0 - np.float32(self.mean)) / np.float32(self.std)
+            out.append(np.ascontiguousarray(t.transpose(2, 0, 1)))
+            infos.append({"input_shape": [float(h), float(w)], "output_shape": [float(self.size[0]), float(self.size[1])]})
+        return np.stack(out), infos
+
+
+class YOLOv5ClsPostprocessor(_SoftmaxTopK):
+    """Softmax over the classes, then the ``topk`` best (contrib/yolov5cls/postprocessor.cc:25-58)."""
+
+    def run(self, tensors, ims_info=None):
+        return super().run(tensors)
+
+
+class YOLOv5Cls(_ClsBase):
+    """YOLOv5 classification model (fastdeploy/vision/classification/contrib/yolov5cls/yolov5cls.cc)."""
+
+    def __init__(self, model_file: str, params_file: str = "", runtime_option: Optional[RuntimeOption] = None,
+                 model_format: ModelFormat = ModelFormat.ONNX):
+        super().__init__(runtime_option)
+        self.runtime_option.set_model_path(model_file, params_file, model_format)
+        self.preprocessor = YOLOv5ClsPreprocessor()
+        self.postprocessor = YOLOv5ClsPostprocessor()
+        self._finish_init()
+
+    @property
+    def size(self):
+        return self.preprocessor.size
+
+    @size.setter
+    def size(self, v):
+        self.preprocessor.size = list(v)
+
+    def batch_predict(self, images: Sequence[np.ndarray]) -> List[ClassifyResult]:
+        x, infos = self.preprocessor.run(images)
+        outs = self.runtime.infer({self.runtime.get_input_info(0).name: x})
+        return self.postprocessor.run([outs[0]], infos)
 
 
 class PPShiTuV2RecognizerPreprocessor(PaddleClasPreprocessor):

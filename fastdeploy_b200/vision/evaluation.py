@@ -195,3 +195,109 @@ def eval_ocr(pipeline, samples: Iterable[Tuple[np.ndarray, Sequence[Sequence[flo
     out = ocr_detection_hmean(all_p, all_g)
     out.update({"rec_" + k: v for k, v in ocr_recognition_metrics(texts_p, texts_g).items()})
     return out
+
+
+# ------------------------------------------------------------------ dataset readers and the streaming COCO metric
+class CocoDetection:
+    """A COCO-format detection set on disk (python/fastdeploy/vision/evaluation/utils/coco.py:35-180): ``data_dir`` holds
+    the images, ``ann_file`` is the json with ``images``, ``annotations`` (``bbox`` as x, y, w, h) and ``categories``.
+    ``file_list`` has one ``{"image", "im_id", "boxes" (x1, y1, x2, y2), "labels" (0-based, in category-id order),
+    "is_crowd"}`` per image; iterating yields ``(BGR image, ground truth dict)`` as :func:`eval_detection` wants."""
+
+    def __init__(self, data_dir: str, ann_file: str, num_workers: Any = "auto", shuffle: bool = False, allow_empty: bool = False,
+                 empty_ratio: float = 1.0):
+        import json
+        import os
+        self.data_dir, self.ann_file, self.shuffle, self.allow_empty, self.empty_ratio = data_dir, ann_file, shuffle, allow_empty, empty_ratio
+        self.num_max_boxes = 1000
+        with open(ann_file) as f:
+            self.coco_gt = json.load(f)
+        cats = sorted(self.coco_gt.get("categories", []), key=lambda c: c["id"])
+        self.catid2clsid = {c["id"]: i for i, c in enumerate(cats)}
+        self.clsid2catid = {i: c["id"] for i, c in enumerate(cats)}
+        self.labels = [c.get("name", str(c["id"])) for c in cats]
+        per_image: Dict[int, List[Dict[str, Any]]] = {}
+        for a in self.coco_gt.get("annotations", []):
+            per_image.setdefault(a["image_id"], []).append(a)
+        self.file_list: List[Dict[str, Any]] = []
+        for im in sorted(self.coco_gt.get("images", []), key=lambda r: r["id"]):
+            anns = [a for a in per_image.get(im["id"], []) if a.get("bbox") and a["bbox"][2] > 0 and a["bbox"][3] > 0]
+            if not anns and not allow_empty:
+                continue
+            self.file_list.append({
+                "image": os.path.join(data_dir, im["file_name"]), "im_id": im["id"],
+                "boxes": [[a["bbox"][0], a["bbox"][1], a["bbox"][0] + a["bbox"][2], a["bbox"][1] + a["bbox"][3]] for a in anns],
+                "labels": [self.catid2clsid[a["category_id"]] for a in anns],
+                "is_crowd": [int(a.get("iscrowd", 0)) for a in anns]})
+        self.num_samples = len(self.file_list)
+
+    def __len__(self) -> int:
+        return self.num_samples
+
+    def __iter__(self):
+        import cv2
+        for rec in self.file_list:
+            yield cv2.imread(rec["image"]), {"boxes": rec["boxes"], "labels": rec["labels"]}
+
+
+class COCOMetric:
+    """Collects detections image by image and reports the box mAP over IoU 0.50:0.95
+    (python/fastdeploy/vision/evaluation/utils/coco_metrics.py:25-120). ``update(im_id, outputs)`` takes a
+    ``DetectionResult`` or ``{"boxes", "labels" | "label_ids", "scores"}``; ``get()`` returns ``{"bbox_mmap": ...}``."""
+
+    def __init__(self, coco_gt: "CocoDetection", classwise: bool = False, **kwargs):
+        self.dataset = coco_gt
+        self.coco_gt = coco_gt.coco_gt
+        self.clsid2catid = dict(coco_gt.clsid2catid)
+        self.classwise = classwise
+        self.reset()
+
+    def reset(self) -> None:
+        self.details: Dict[int, Dict[str, Any]] = {}
+        self.eval_stats: Dict[str, float] = {}
+
+    def update(self, im_id: int, outputs: Any) -> None:
+        get = (lambda k, *alt: next((outputs[n] for n in (k,) + alt if n in outputs), [])) if isinstance(outputs, dict) else \
+              (lambda k, *alt: next((getattr(outputs, n) for n in (k,) + alt if hasattr(outputs, n)), []))
+        self.details[im_id] = {"boxes": [list(b)[:4] for b in get("boxes", "bbox")], "labels": [int(l) for l in get("labels", "label_ids")],
+                               "scores": [float(s) for s in get("scores")]}
+
+    def accumulate(self) -> Dict[str, float]:
+        recs = [r for r in self.dataset.file_list if r["im_id"] in self.details]
+        self.eval_stats = coco_map([self.details[r["im_id"]] for r in recs], [{"boxes": r["boxes"], "labels": r["labels"]} for r in recs]) \
+            if recs else {"bbox_mAP": 0.0, "bbox_mAP50": 0.0, "bbox_mAP75": 0.0}
+        return self.eval_stats
+
+    def get(self) -> Dict[str, float]:
+        if not self.eval_stats:
+            self.accumulate()
+        return {"bbox_mmap": self.eval_stats["bbox_mAP"], "bbox_map50": self.eval_stats["bbox_mAP50"]}
+
+
+class Cityscapes:
+    """The Cityscapes layout on disk (python/fastdeploy/vision/evaluation/utils/cityscapes.py:25-75):
+    ``leftImg8bit/<mode>/<city>/*_leftImg8bit.png`` with labels ``gtFine/<mode>/<city>/*_gtFine_labelTrainIds.png``.
+    ``file_list`` pairs them by sorted order; iterating yields ``(BGR image, label map)`` for :func:`eval_segmentation`."""
+    NUM_CLASSES = 19
+
+    def __init__(self, dataset_root: str, mode: str = "val"):
+        import glob
+        import os
+        if mode not in ("train", "val", "test"):
+            raise ValueError(f"mode should be 'train', 'val' or 'test', but got {mode}.")
+        self.dataset_root, self.mode = dataset_root, mode
+        self.num_classes, self.ignore_index = self.NUM_CLASSES, 255
+        img_dir, label_dir = os.path.join(dataset_root, "leftImg8bit"), os.path.join(dataset_root, "gtFine")
+        if not os.path.isdir(img_dir) or not os.path.isdir(label_dir):
+            raise ValueError("The dataset is not Found or the folder structure is nonconfoumance.")
+        labels = sorted(glob.glob(os.path.join(label_dir, mode, "*", "*_gtFine_labelTrainIds.png")))
+        images = sorted(glob.glob(os.path.join(img_dir, mode, "*", "*_leftImg8bit.png")))
+        self.file_list = [[i, l] for i, l in zip(images, labels)]
+
+    def __len__(self) -> int:
+        return len(self.file_list)
+
+    def __iter__(self):
+        import cv2
+        for image, label in self.file_list:
+            yield cv2.imread(image), cv2.imread(label, cv2.IMREAD_GRAYSCALE)

@@ -7,7 +7,7 @@ here on the host; their inputs and outputs keep the reference's layouts."""
 from __future__ import annotations
 
 import math
-from typing import List, Optional, Sequence, Tuple
+from typing import Any, List, Optional, Sequence, Tuple
 
 import numpy as np
 import yaml
@@ -152,13 +152,14 @@ def _fill(boxes: np.ndarray, scores: np.ndarray, labels: np.ndarray, with_veloci
     return r
 
 
-class _ImagePerception(FastDeployModel):
-    def __init__(self, model_file: str, params_file: str, config_file: str,
-                 runtime_option: Optional[RuntimeOption] = None, model_format: int = ModelFormat.PADDLE):
-        super().__init__(runtime_option)
-        self.runtime_option.set_model_path(model_file, params_file, model_format)
+class _ImagePreprocessor:
+    """Image half of the camera models' inputs, from the model's yaml: resize to ``Resize.target_size``, BGR->RGB, 1/255,
+    ``NormalizeImage`` mean / std, CHW (fastdeploy/vision/perception/paddle3d/{smoke,petr,caddn}/preprocessor.cc)."""
+
+    def __init__(self, config_file: str):
         with open(config_file) as f:
             cfg = yaml.safe_load(f) or {}
+        self.config_file = config_file
         self.size = [1280, 384]
         self.mean, self.std = [0.485, 0.456, 0.406], [0.229, 0.224, 0.225]
         for op in cfg.get("Preprocess", []) or []:
@@ -167,17 +168,105 @@ class _ImagePerception(FastDeployModel):
                 self.size = [ww, hh]
             elif op.get("type") == "NormalizeImage":
                 self.mean, self.std = list(op["mean"]), list(op["std"])
-        self.score_threshold = 0.25
-        self.init_runtime()
 
-    def _image_tensor(self, im: np.ndarray) -> np.ndarray:
+    def image_tensor(self, im: np.ndarray) -> np.ndarray:
         x = _resize_bilinear(im, *self.size)[..., ::-1].astype(np.float32) / 255.0
         x = (x - np.asarray(self.mean, np.float32)) / np.asarray(self.std, np.float32)
         return np.ascontiguousarray(x.transpose(2, 0, 1))
 
+    def run(self, images: Sequence[np.ndarray]) -> np.ndarray:
+        return np.stack([self.image_tensor(im) for im in images])
+
+
+class SmokePreprocessor(_ImagePreprocessor):
+    pass
+
+
+class PetrPreprocessor(_ImagePreprocessor):
+    pass
+
+
+class CaddnPreprocessor(_ImagePreprocessor):
+    pass
+
+
+class SmokePostprocessor:
+    """Rows ``[label, alpha, x1, y1, x2, y2, h, w, l, x, y, z, yaw, score]`` above the score threshold
+    (smoke/postprocessor.cc:40-90)."""
+
+    def __init__(self):
+        self.score_threshold = 0.25
+
+    def run(self, outputs: Sequence[np.ndarray]) -> List[PerceptionResult]:
+        rows = np.asarray(outputs[0], np.float32).reshape(-1, 14)
+        rows = rows[rows[:, 13] > self.score_threshold]
+        r = PerceptionResult()
+        for row in rows:
+            r.label_ids.append(int(row[0])); r.observation_angle.append(float(row[1]))
+            r.boxes.append([float(v) for v in (row[2], row[3], row[4], row[5], row[6], row[7], row[8])])
+            r.center.append([float(row[9]), float(row[10]), float(row[11])])
+            r.yaw_angle.append(float(row[12])); r.scores.append(float(row[13])); r.valid.append(True)
+        return [r]
+
+
+class PetrPostprocessor:
+    """Boxes ``[n, 9]`` (with velocity), scores, labels (petr/postprocessor.cc:30-80)."""
+
+    def __init__(self):
+        self.score_threshold = 0.25
+
+    def run(self, outputs: Sequence[np.ndarray]) -> List[PerceptionResult]:
+        b, s, l = (np.asarray(o) for o in outputs[:3])
+        m = s.reshape(-1) > self.score_threshold
+        return [_fill(b.reshape(len(m), -1)[m], s.reshape(-1)[m], l.reshape(-1)[m], with_velocity=True)]
+
+
+class CaddnPostprocessor:
+    """Boxes ``[n, 7]``, labels, scores (caddn/postprocessor.cc:30-75)."""
+
+    def __init__(self):
+        self.score_threshold = 0.25
+
+    def run(self, outputs: Sequence[np.ndarray]) -> List[PerceptionResult]:
+        b, l, s = (np.asarray(o) for o in outputs[:3])
+        m = s.reshape(-1) > self.score_threshold
+        return [_fill(b.reshape(len(m), -1)[m], s.reshape(-1)[m], l.reshape(-1)[m])]
+
+
+class _ImagePerception(FastDeployModel):
+    PRE = _ImagePreprocessor
+    POST = None
+
+    def __init__(self, model_file: str, params_file: str, config_file: str,
+                 runtime_option: Optional[RuntimeOption] = None, model_format: int = ModelFormat.PADDLE):
+        super().__init__(runtime_option)
+        self.runtime_option.set_model_path(model_file, params_file, model_format)
+        self.preprocessor = self.PRE(config_file)
+        self.postprocessor = self.POST()
+        self.init_runtime()
+
+    size = property(lambda self: self.preprocessor.size, lambda self, v: setattr(self.preprocessor, "size", list(v)))
+    mean = property(lambda self: self.preprocessor.mean)
+    std = property(lambda self: self.preprocessor.std)
+    score_threshold = property(lambda self: self.postprocessor.score_threshold,
+                               lambda self, v: setattr(self.postprocessor, "score_threshold", v))
+
+    def _image_tensor(self, im: np.ndarray) -> np.ndarray:
+        return self.preprocessor.image_tensor(im)
+
+    def batch_predict(self, items: Sequence[Any], *extras) -> List[PerceptionResult]:
+        """One :meth:`predict` per item; ``extras`` (camera matrices ...) are either one value for all items or a sequence
+        with one value per item."""
+        out = []
+        for i, it in enumerate(items):
+            args = [e[i] if isinstance(e, (list, tuple)) and len(e) == len(items) else e for e in extras]
+            out.append(self.predict(it, *args))
+        return out
+
 
 class Smoke(_ImagePerception):
-    """Monocular SMOKE: inputs image, camera intrinsics ``K [1,3,3]`` and ``down_ratios [1,2]``; output rows
+    PRE, POST = SmokePreprocessor, SmokePostprocessor
+    __doc__ = """Monocular SMOKE: inputs image, camera intrinsics ``K [1,3,3]`` and ``down_ratios [1,2]``; output rows
     ``[label, alpha, x1, y1, x2, y2, h, w, l, x, y, z, yaw, score]`` (smoke/postprocessor.cc:40-90)."""
 
     def predict(self, im: np.ndarray, k: Optional[np.ndarray] = None) -> PerceptionResult:
@@ -192,19 +281,12 @@ class Smoke(_ImagePerception):
                 feeds[name] = k[None]
             else:
                 feeds[name] = np.asarray([[w / self.size[0] * 4.0, h / self.size[1] * 4.0]], np.float32)
-        rows = np.asarray(self.runtime.infer(feeds)[0], np.float32).reshape(-1, 14)
-        rows = rows[rows[:, 13] > self.score_threshold]
-        r = PerceptionResult()
-        for row in rows:
-            r.label_ids.append(int(row[0])); r.observation_angle.append(float(row[1]))
-            r.boxes.append([float(v) for v in (row[2], row[3], row[4], row[5], row[6], row[7], row[8])])
-            r.center.append([float(row[9]), float(row[10]), float(row[11])])
-            r.yaw_angle.append(float(row[12])); r.scores.append(float(row[13])); r.valid.append(True)
-        return r
+        return self.postprocessor.run(self.runtime.infer(feeds))[0]
 
 
 class Petr(_ImagePerception):
-    """Multi-camera PETR: six images stacked ``[1, 6, 3, H, W]`` plus ``img2lidars [1, 6, 4, 4]``; outputs
+    PRE, POST = PetrPreprocessor, PetrPostprocessor
+    __doc__ = """Multi-camera PETR: six images stacked ``[1, 6, 3, H, W]`` plus ``img2lidars [1, 6, 4, 4]``; outputs
     boxes ``[n, 9]``, scores, labels."""
 
     def predict(self, images: Sequence[np.ndarray], img2lidars: Optional[np.ndarray] = None) -> PerceptionResult:
@@ -214,14 +296,12 @@ class Petr(_ImagePerception):
         if len(names) > 1:
             t = np.tile(np.eye(4, dtype=np.float32), (1, len(images), 1, 1)) if img2lidars is None else np.asarray(img2lidars, np.float32)
             feeds[names[1]] = t.reshape(1, len(images), 4, 4)
-        outs = self.runtime.infer(feeds)
-        b, s, l = (np.asarray(o) for o in outs[:3])
-        m = s.reshape(-1) > self.score_threshold
-        return _fill(b.reshape(len(m), -1)[m], s.reshape(-1)[m], l.reshape(-1)[m], with_velocity=True)
+        return self.postprocessor.run(self.runtime.infer(feeds))[0]
 
 
 class Caddn(_ImagePerception):
-    """CaDDN: image plus camera-to-image and lidar-to-camera matrices; outputs boxes ``[n, 7]``, labels, scores."""
+    PRE, POST = CaddnPreprocessor, CaddnPostprocessor
+    __doc__ = """CaDDN: image plus camera-to-image and lidar-to-camera matrices; outputs boxes ``[n, 7]``, labels, scores."""
 
     def predict(self, im: np.ndarray, cam2img: Optional[np.ndarray] = None, lidar2cam: Optional[np.ndarray] = None):
         names = [self.runtime.get_input_info(i).name for i in range(self.runtime.num_inputs())]
@@ -230,10 +310,21 @@ class Caddn(_ImagePerception):
             feeds[names[1]] = (np.eye(3, 4, dtype=np.float32) if cam2img is None else np.asarray(cam2img, np.float32)).reshape(1, 3, 4)
         if len(names) > 2:
             feeds[names[2]] = (np.eye(4, dtype=np.float32) if lidar2cam is None else np.asarray(lidar2cam, np.float32)).reshape(1, 4, 4)
-        outs = [np.asarray(o) for o in self.runtime.infer(feeds)]
-        b, l, s = outs[0], outs[1], outs[2]
-        m = s.reshape(-1) > self.score_threshold
-        return _fill(b.reshape(len(m), -1)[m], s.reshape(-1)[m], l.reshape(-1)[m])
+        return self.postprocessor.run(self.runtime.infer(feeds))[0]
+
+
+class CenterpointPreprocessor:
+    """Voxelisation settings of the lidar model and the host voxeliser (centerpoint/preprocessor.cc:25-90)."""
+
+    def __init__(self, config_file: str = ""):
+        self.config_file = config_file
+        self.voxel_size = [0.2, 0.2, 8.0]
+        self.point_cloud_range = [-51.2, -51.2, -5.0, 51.2, 51.2, 3.0]
+        self.max_points_in_voxel, self.max_voxel_num = 20, 30000
+
+    def run(self, points: np.ndarray):
+        return hard_voxelize(np.asarray(points, np.float32), self.voxel_size, self.point_cloud_range, self.max_points_in_voxel,
+                             self.max_voxel_num)
 
 
 class Centerpoint(FastDeployModel):
@@ -244,12 +335,25 @@ class Centerpoint(FastDeployModel):
                  runtime_option: Optional[RuntimeOption] = None, model_format: int = ModelFormat.PADDLE):
         super().__init__(runtime_option)
         self.runtime_option.set_model_path(model_file, params_file, model_format)
-        self.voxel_size = [0.2, 0.2, 8.0]
-        self.point_cloud_range = [-51.2, -51.2, -5.0, 51.2, 51.2, 3.0]
-        self.max_points_in_voxel, self.max_voxel_num = 20, 30000
+        self.preprocessor = CenterpointPreprocessor(config_file)
         self.down_ratio, self.score_threshold, self.nms_iou_threshold = 4, 0.1, 0.2
         self.with_velocity = True
         self.init_runtime()
+
+    voxel_size = property(lambda self: self.preprocessor.voxel_size, lambda self, v: setattr(self.preprocessor, "voxel_size", list(v)))
+    point_cloud_range = property(lambda self: self.preprocessor.point_cloud_range,
+                                 lambda self, v: setattr(self.preprocessor, "point_cloud_range", list(v)))
+    max_points_in_voxel = property(lambda self: self.preprocessor.max_points_in_voxel,
+                                   lambda self, v: setattr(self.preprocessor, "max_points_in_voxel", int(v)))
+    max_voxel_num = property(lambda self: self.preprocessor.max_voxel_num, lambda self, v: setattr(self.preprocessor, "max_voxel_num", int(v)))
+
+    @property
+    def postprocessor(self):
+        """Decoding is part of :meth:`predict` (it needs the voxel grid); the thresholds live on the model."""
+        return self
+
+    def batch_predict(self, sweeps: Sequence[np.ndarray]) -> List[PerceptionResult]:
+        return [self.predict(p) for p in sweeps]
 
     def predict(self, points: np.ndarray) -> PerceptionResult:
         pts = np.asarray(points, np.float32)

@@ -227,6 +227,19 @@ class JDETracker:
         return [t for t in self.tracked if t.activated]
 
 
+class TrailRecorder:
+    """Per track id, the centre points of its boxes frame after frame (fastdeploy/vision/tracking/pptracking/model.h:24-40);
+    ``vis_mot(..., records=recorder)`` draws them as trails."""
+
+    def __init__(self):
+        self.records: Dict[int, List[List[int]]] = {}
+
+    def add(self, track_id: int, point: Sequence[int]) -> None:
+        self.records.setdefault(int(track_id), []).append([int(point[0]), int(point[1])])
+
+    Add = add
+
+
 class PPTracking(FastDeployModel):
     """FairMOT / JDE models exported by PaddleDetection (pptracking/model.cc:150-330): letterbox to the
     yaml's ``target_size`` with value 127.5, /255 normalise, outputs ``pred_dets [n, 6]`` and embeddings."""
@@ -245,7 +258,15 @@ class PPTracking(FastDeployModel):
         tr = cfg.get("tracker", {})
         self.conf_thresh = tr.get("conf_thres", 0.4)
         self.tracker = JDETracker(det_thresh=tr.get("tracked_thresh", 0.4), min_box_area=tr.get("min_box_area", 200))
+        self.recorder: Optional[TrailRecorder] = None
         self.init_runtime()
+
+    def bind_recorder(self, recorder: TrailRecorder) -> None:
+        """From now on every returned track adds its box centre to ``recorder`` (model.cc:330-345)."""
+        self.recorder = recorder
+
+    def unbind_recorder(self) -> None:
+        self.recorder = None
 
     def predict(self, im: np.ndarray) -> MOTResult:
         canvas, info = letterbox(im, self.size, (127.5, 127.5, 127.5))
@@ -273,6 +294,8 @@ class PPTracking(FastDeployModel):
             if (b[2] - b[0]) * (b[3] - b[1]) <= self.tracker.min_box_area:
                 continue
             r.boxes.append([int(v) for v in b]); r.ids.append(t.id); r.scores.append(t.score); r.class_ids.append(t.cls_id)
+            if self.recorder is not None:
+                self.recorder.add(t.id, [(int(b[0]) + int(b[2])) // 2, (int(b[1]) + int(b[3])) // 2])
         return r
 
 

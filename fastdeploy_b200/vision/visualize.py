@@ -300,11 +300,23 @@ def vis_keypoint_detection(im, result: KeyPointDetectionResult, conf_threshold: 
 
 
 def vis_mot(im, result: MOTResult, score_threshold: float = 0.0, records=None):
+    """Track boxes coloured by id; with ``records`` (a ``tracking.TrailRecorder``) the recorded centre points of every
+    shown track are drawn as dots in the track's colour (fastdeploy/vision/visualize/mot.cc:25-78)."""
     det = DetectionResult()
     for b, i, s in zip(result.boxes, result.ids, result.scores):
         if s >= score_threshold:
             det.boxes.append([float(v) for v in b]); det.scores.append(float(s)); det.label_ids.append(int(i))
-    return vis_detection(im, det, None, 0.0, 2)
+    out = vis_detection(im, det, None, 0.0, 2)
+    trails = getattr(records, "records", records) if records is not None else None
+    if trails:
+        import cv2
+        canvas, back = _host_image(out)
+        for tid in det.label_ids:
+            col = tuple(int(v) for v in _COLORS[tid % 256])
+            for p in trails.get(tid, []):
+                cv2.circle(canvas, (int(p[0]), int(p[1])), 3, col, -1)
+        out = back(canvas)
+    return out
 
 
 def vis_ppocr(im, result: OCRResult):

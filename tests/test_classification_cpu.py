@@ -90,3 +90,22 @@ def test_onnx_resnet_softmax_topk(tmp_path):
     r = m.predict(_images(1)[0], topk=7)
     assert sorted(r.label_ids) == list(range(7)) and abs(sum(r.scores) - 1.0) < 1e-4
     assert r.scores == sorted(r.scores, reverse=True)
+
+
+def test_yolov5cls_centre_crops_before_resizing(tmp_path):
+    from fastdeploy_b200.models.resnet import resnet18_like_onnx
+    cls = fd.vision.classification
+    pre = cls.YOLOv5ClsPreprocessor()
+    pre.size = [32, 32]
+    im = np.zeros((40, 100, 3), np.uint8)
+    im[:, 30:70] = 255                                   # the centre 40 x 40 square is white, the sides black
+    x, infos = pre.run([im])
+    assert x.shape == (1, 3, 32, 32) and infos[0] == {"input_shape": [40.0, 100.0], "output_shape": [32.0, 32.0]}
+    assert np.allclose(x[0, 0], (1.0 - 0.485) / 0.229, atol=1e-5)          # only the white square is left
+    path = str(tmp_path / "c.onnx")
+    resnet18_like_onnx(path, seed=2, num_classes=5, width=8)
+    m = cls.YOLOv5Cls(path, runtime_option=_opt())
+    assert isinstance(m.postprocessor, cls.YOLOv5ClsPostprocessor)
+    m.size = [64, 64]
+    r = m.predict(_images(1)[0], topk=5)
+    assert sorted(r.label_ids) == list(range(5)) and abs(sum(r.scores) - 1.0) < 1e-4
