@@ -9,4 +9,10 @@ def __getattr__(name):
     if name == "SimpleServer":
         from . import server
         return server.SimpleServer
+    if name in ("BaseRouterManager", "HttpRouterManager", "RequestBase", "ResponseBase"):     # these import fastapi
+        from . import router
+        return getattr(router, name)
+    if name in ("router", "handler", "utils"):
+        import importlib
+        return importlib.import_module("." + name, __name__)
     raise AttributeError(name)

@@ -372,6 +372,21 @@ YOLOv7Preprocessor, YOLOv7Postprocessor = _processor_pair("YOLOv7", "v5", "contr
 YOLOv8Preprocessor, YOLOv8Postprocessor = _processor_pair("YOLOv8", "v8", "contrib/yolov8")
 RKYOLOPreprocessor, RKYOLOPostprocessor = _processor_pair("RKYOLO", "v5", "contrib/rknpu2")
 
+
+def _rk_set_anchor(self, anchors: Sequence[int], anchor_per_branch: int = 3) -> None:
+    """Anchor sizes as one flat list (w, h pairs, small to large stride), ``anchor_per_branch`` pairs per head level
+    (contrib/rknpu2/postprocessor.h:60-75)."""
+    flat = [float(a) for a in anchors]
+    per = 2 * int(anchor_per_branch)
+    if per <= 0 or len(flat) % per:
+        raise ValueError(f"{len(flat)} anchor values do not split into levels of {anchor_per_branch} pairs")
+    self.anchor_config = [flat[i:i + per] for i in range(0, len(flat), per)]
+    self.anchor_per_branch = int(anchor_per_branch)
+
+
+RKYOLOPostprocessor.set_anchor = _rk_set_anchor
+RKYOLOPostprocessor.class_num = 80
+
 YOLOv5 = _model("YOLOv5", "v5", "YOLOv5 (contrib/yolov5/yolov5.cc).", YOLOv5Preprocessor, YOLOv5Postprocessor)
 YOLOv5Lite = _model("YOLOv5Lite", "v5", "YOLOv5-Lite with decoded export (contrib/yolov5lite.cc).", conf_threshold=0.45)
 YOLOv6 = _model("YOLOv6", "v5", "YOLOv6 (contrib/yolov6.cc).")

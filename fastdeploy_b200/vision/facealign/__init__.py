@@ -61,6 +61,7 @@ class PIPNet(_AlignBase):
 
     def __init__(self, *a, num_landmarks: int = 19, num_nb: int = 10, **kw):
         self.num_landmarks, self.num_nb, self.net_stride = num_landmarks, num_nb, 32
+        self.mean_vals, self.std_vals = [0.485, 0.456, 0.406], [0.229, 0.224, 0.225]
         self.reverse_index: Optional[np.ndarray] = None     # [N, max_len] indices into the flattened nb arrays
         super().__init__(*a, **kw)
 
@@ -70,7 +71,7 @@ class PIPNet(_AlignBase):
     def predict(self, im: np.ndarray) -> FaceAlignmentResult:
         h, w = im.shape[:2]
         x = _resize_bilinear(im, *self.size)[..., ::-1].astype(np.float32) / 255.0
-        x = (x - np.asarray([0.485, 0.456, 0.406], np.float32)) / np.asarray([0.229, 0.224, 0.225], np.float32)
+        x = (x - np.asarray(self.mean_vals, np.float32)) / np.asarray(self.std_vals, np.float32)
         cls, ox, oy, nbx, nby = self._run(np.ascontiguousarray(x.transpose(2, 0, 1))[None])[:5]
         n, fh, fw = cls.shape[1:]
         flat = cls.reshape(n, -1)

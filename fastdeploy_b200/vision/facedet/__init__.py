@@ -87,7 +87,18 @@ class _FaceProcessor:
         return getattr(object.__getattribute__(self, "_state"), name)
 
     def __setattr__(self, name, value):
-        setattr(object.__getattribute__(self, "_state"), name, value)
+        if isinstance(getattr(type(self), name, None), property):
+            object.__setattr__(self, name, value)
+        else:
+            setattr(object.__getattribute__(self, "_state"), name, value)
+
+    @property
+    def padding_color_value(self):
+        return self._state.padding_value
+
+    @padding_color_value.setter
+    def padding_color_value(self, v):
+        self._state.padding_value = list(v)
 
     @property
     def nms_threshold(self):

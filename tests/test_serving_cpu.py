@@ -247,3 +247,38 @@ def _wait_cancel(fut):
     except cf.CancelledError:
         return True
     return False
+
+
+def test_router_manager_adds_a_task_route_to_a_plain_application():
+    fastapi = pytest.importorskip("fastapi")
+    import fastdeploy_b200 as fd
+    from fastdeploy_b200.serving import BaseRouterManager, HttpRouterManager, ModelManager, RequestBase, ResponseBase
+    from fastdeploy_b200.serving.handler import BaseModelHandler as H2
+    from fastdeploy_b200.serving.utils import base64_to_cv2, cv2_to_base64
+
+    class Handler(fd.serving.BaseModelHandler):
+        @classmethod
+        def process(cls, predictor, data, parameters):
+            return {"n": predictor(data), "p": parameters}
+
+    assert H2 is fd.serving.BaseModelHandler and issubclass(HttpRouterManager, BaseRouterManager)
+    with pytest.raises(TypeError):
+        BaseRouterManager(None)                          # abstract
+    app = fastapi.FastAPI()
+    app._model_manager = ModelManager(Handler, len)
+    HttpRouterManager(app).register_models_router("fd/count")
+    assert any(getattr(r, "path", "") == "/fd/count" for r in app.routes)
+    assert RequestBase(parameters={"a": 1}).parameters == {"a": 1} and ResponseBase().text is None
+    with pytest.raises(Exception):
+        RequestBase(parameters={}, other=1)              # unknown keys are refused
+    try:
+        from fastapi.testclient import TestClient
+        c = TestClient(app)
+    except RuntimeError as e:
+        pytest.skip(str(e))
+    r = c.post("/fd/count", json={"data": [1, 2, 3], "parameters": {"k": 2}})
+    assert r.status_code == 200 and r.json() == {"result": {"n": 3, "p": {"k": 2}}}
+    assert c.post("/fd/count", json={"data": 5}).status_code == 400           # len(5) raises inside the handler
+    assert c.post("/fd/count", json={"data": [1], "extra": 1}).status_code == 422
+    im = np.arange(48, dtype=np.uint8).reshape(4, 4, 3)
+    assert base64_to_cv2(cv2_to_base64(im)).shape == (4, 4, 3)
