@@ -152,3 +152,23 @@ def test_model_list_comes_from_the_local_cache(tmp_path, monkeypatch):
     assert fd.get_model_list("detection") == {"detection": [{"name": "ppyoloe_crn_l_300e_coco", "format": "paddle"}]}
     with pytest.raises(ValueError, match="No pretrained model in category"):
         fd.get_model_list("audio")
+
+
+def test_example_image_and_hub_directories(tmp_path, monkeypatch):
+    import importlib
+    import cv2
+    monkeypatch.setenv("HUB_HOME", str(tmp_path / "hub"))
+    monkeypatch.setenv("FASTDEPLOY_MODEL_CACHE", str(tmp_path / "cache"))
+    from fastdeploy_b200.utils import hub_env
+    importlib.reload(hub_env)
+    assert hub_env.MODEL_HOME == str(tmp_path / "hub" / "models") and not os.path.exists(hub_env.HUB_HOME)   # nothing created
+    p = fd.utils.get_detection_test_image()
+    assert p == str(tmp_path / "hub" / "resources" / "detection_test_image.jpg") and cv2.imread(p).shape == (720, 1280, 3)
+    first = os.path.getmtime(p)
+    assert fd.utils.get_detection_test_image() == p and os.path.getmtime(p) == first                           # kept, not redrawn
+    (tmp_path / "cache").mkdir()
+    cv2.imwrite(str(tmp_path / "cache" / "detection_test_image.jpg"), np.zeros((8, 8, 3), np.uint8))
+    q = fd.utils.get_detection_test_image(str(tmp_path / "elsewhere"))
+    assert cv2.imread(q).shape == (8, 8, 3)                                                                    # the cached file wins
+    monkeypatch.delenv("HUB_HOME")
+    importlib.reload(hub_env)
