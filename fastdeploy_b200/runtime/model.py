@@ -15,6 +15,17 @@ from .option import RuntimeOption
 from .runtime import Runtime
 
 
+class _Flag(int):
+    """A truth value that can also be called: the reference's Python class has ``initialized`` as a property and its C++
+    class as a method, and code written for either reads correctly."""
+
+    def __call__(self) -> bool:
+        return bool(self)
+
+    def __repr__(self) -> str:
+        return repr(bool(self))
+
+
 class FastDeployModel:
     valid_cpu_backends: List[Backend] = [Backend.ORT, Backend.PDINFER, Backend.OPENVINO, Backend.NATIVE]
     valid_gpu_backends: List[Backend] = [Backend.ORT, Backend.TRT, Backend.PDINFER, Backend.NATIVE]
@@ -36,8 +47,9 @@ class FastDeployModel:
         self.initialized_ = True
         return True
 
-    def initialized(self) -> bool:
-        return self.initialized_
+    @property
+    def initialized(self) -> _Flag:
+        return _Flag(bool(self.initialized_))
 
     def num_inputs_of_runtime(self) -> int:
         return self.runtime.num_inputs()

@@ -137,3 +137,11 @@ def test_cpu_runtime_fast_path_matches_plain_interpreter(tmp_path):
         ref = Interpreter(rt.graph).run({"input": x})["output"].numpy()
         got = rt.infer({"input": x})[0]
         assert got.shape == ref.shape and np.abs(got - ref).max() < 1e-4 * max(1.0, np.abs(ref).max())
+
+
+def test_initialized_reads_as_property_and_as_method():
+    import fastdeploy_b200 as fd
+    m = fd.FastDeployModel()
+    assert not m.initialized and m.initialized() is False and repr(m.initialized) == "False"
+    m.initialized_ = True
+    assert m.initialized and m.initialized() is True
