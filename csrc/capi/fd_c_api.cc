@@ -973,4 +973,97 @@ FD_C_Bool FD_C_VisOcr(FD_C_Mat img, const FD_C_OCRResult* result, FD_C_Mat* out)
   return ok ? 1 : 0;
 }
 
+
+// ---------------------------------------------------------------- OCR stages on their own
+FD_C_DBDetectorWrapper* FD_C_CreateDBDetectorWrapper(const char* m, const char* p, FD_C_RuntimeOptionWrapper* o, FD_C_ModelFormat f) {
+  return create_model("vision.ocr.DBDetector", m, p, nullptr, o, f);
+}
+FD_C_ClassifierWrapper* FD_C_CreateClassifierWrapper(const char* m, const char* p, FD_C_RuntimeOptionWrapper* o, FD_C_ModelFormat f) {
+  return create_model("vision.ocr.Classifier", m, p, nullptr, o, f);
+}
+FD_C_RecognizerWrapper* FD_C_CreateRecognizerWrapper(const char* m, const char* p, const char* label_path, FD_C_RuntimeOptionWrapper* o,
+                                                     FD_C_ModelFormat f) {
+  Gil g;
+  if (g_pkg == nullptr) return nullptr;
+  PyObject* cls = get_class("vision.ocr.Recognizer");
+  if (cls == nullptr) return nullptr;
+  PyObject* kwargs = PyDict_New();
+  if (o != nullptr) PyDict_SetItemString(kwargs, "runtime_option", o->obj);
+  PyObject* fmt = PyLong_FromLong(static_cast<long>(f));
+  PyDict_SetItemString(kwargs, "model_format", fmt);
+  Py_DECREF(fmt);
+  PyObject* args = Py_BuildValue("(sss)", m, p ? p : "", label_path ? label_path : "");     // the label file may be empty
+  PyObject* obj = PyObject_Call(cls, args, kwargs);
+  Py_DECREF(args); Py_DECREF(kwargs); Py_DECREF(cls);
+  if (obj == nullptr) { fetch_py_error("vision.ocr.Recognizer"); return nullptr; }
+  return new FD_C_ModelWrapper{obj};
+}
+void FD_C_DestroyDBDetectorWrapper(FD_C_DBDetectorWrapper* w) { FD_C_DestroyModelWrapper(w); }
+void FD_C_DestroyClassifierWrapper(FD_C_ClassifierWrapper* w) { FD_C_DestroyModelWrapper(w); }
+void FD_C_DestroyRecognizerWrapper(FD_C_RecognizerWrapper* w) { FD_C_DestroyModelWrapper(w); }
+FD_C_Bool FD_C_DBDetectorWrapperInitialized(FD_C_DBDetectorWrapper* w) { return model_initialized(w); }
+FD_C_Bool FD_C_ClassifierWrapperInitialized(FD_C_ClassifierWrapper* w) { return model_initialized(w); }
+FD_C_Bool FD_C_RecognizerWrapperInitialized(FD_C_RecognizerWrapper* w) { return model_initialized(w); }
+
+static PyObject* predict_on_image(FD_C_ModelWrapper* w, FD_C_Mat img) {
+  PyObject* arr = mat_to_numpy(img);
+  if (arr == nullptr) return nullptr;
+  PyObject* r = call_method(w->obj, "predict", "(O)", arr);
+  Py_DECREF(arr);
+  return r;
+}
+FD_C_Bool FD_C_DBDetectorWrapperPredict(FD_C_DBDetectorWrapper* w, FD_C_Mat img, FD_C_TwoDimArrayInt32* boxes) {
+  Gil g;
+  boxes->size = 0; boxes->data = nullptr;
+  PyObject* r = predict_on_image(w, img);
+  if (r == nullptr) return 0;
+  const Py_ssize_t n = PySequence_Size(r);
+  bool ok = n >= 0;
+  if (ok) {
+    boxes->size = static_cast<size_t>(n);
+    boxes->data = static_cast<FD_C_OneDimArrayInt32*>(std::calloc(n > 0 ? n : 1, sizeof(FD_C_OneDimArrayInt32)));
+    for (Py_ssize_t i = 0; i < n && ok; ++i) {
+      PyObject* b = PySequence_GetItem(r, i);
+      ok = b != nullptr && ints_from_seq(b, &boxes->data[i]);
+      Py_XDECREF(b);
+    }
+  } else {
+    fetch_py_error("DBDetector.predict");
+  }
+  Py_DECREF(r);
+  return ok ? 1 : 0;
+}
+FD_C_Bool FD_C_ClassifierWrapperPredict(FD_C_ClassifierWrapper* w, FD_C_Mat img, int32_t* cls_label, float* cls_score) {
+  Gil g;
+  PyObject* r = predict_on_image(w, img);
+  if (r == nullptr) return 0;
+  int label = 0;
+  float score = 0.0f;
+  const bool ok = PyArg_ParseTuple(r, "if", &label, &score) != 0;
+  if (!ok) fetch_py_error("Classifier.predict");
+  Py_DECREF(r);
+  if (ok) { *cls_label = label; *cls_score = score; }
+  return ok ? 1 : 0;
+}
+FD_C_Bool FD_C_RecognizerWrapperPredict(FD_C_RecognizerWrapper* w, FD_C_Mat img, char** text, float* rec_score) {
+  Gil g;
+  *text = nullptr;
+  PyObject* r = predict_on_image(w, img);
+  if (r == nullptr) return 0;
+  const char* t = nullptr;
+  float score = 0.0f;
+  const bool ok = PyArg_ParseTuple(r, "sf", &t, &score) != 0;
+  if (ok) { *text = strdup(t); *rec_score = score; }
+  else fetch_py_error("Recognizer.predict");
+  Py_DECREF(r);
+  return ok ? 1 : 0;
+}
+void FD_C_DestroyTwoDimArrayInt32(FD_C_TwoDimArrayInt32* a) {
+  if (a == nullptr) return;
+  for (size_t i = 0; i < a->size; ++i) std::free(a->data[i].data);
+  std::free(a->data);
+  a->data = nullptr; a->size = 0;
+}
+void FD_C_DestroyCstr(char* text) { std::free(text); }
+
 }  // extern "C"

@@ -245,6 +245,32 @@ FD_C_EXPORT FD_C_Bool FD_C_PPOCRv3WrapperBatchPredict(FD_C_PPOCRv3Wrapper* w, co
 FD_C_EXPORT void FD_C_DestroyPPOCRv2Wrapper(FD_C_PPOCRv2Wrapper* w);
 FD_C_EXPORT void FD_C_DestroyPPOCRv3Wrapper(FD_C_PPOCRv3Wrapper* w);
 
+/* ---- the three OCR stages on their own (c_api/fastdeploy_capi/vision/ocr/ppocr/model.h:30-330) */
+typedef struct FD_C_TwoDimArrayInt32 { size_t size; FD_C_OneDimArrayInt32* data; } FD_C_TwoDimArrayInt32;
+typedef FD_C_ModelWrapper FD_C_DBDetectorWrapper;
+typedef FD_C_ModelWrapper FD_C_ClassifierWrapper;
+typedef FD_C_ModelWrapper FD_C_RecognizerWrapper;
+FD_C_EXPORT FD_C_DBDetectorWrapper* FD_C_CreateDBDetectorWrapper(const char* model_file, const char* params_file,
+                                                                 FD_C_RuntimeOptionWrapper* option, FD_C_ModelFormat format);
+/* boxes->data[i] holds the 8 corner coordinates of text box i; release with FD_C_DestroyTwoDimArrayInt32 */
+FD_C_EXPORT FD_C_Bool FD_C_DBDetectorWrapperPredict(FD_C_DBDetectorWrapper* w, FD_C_Mat img, FD_C_TwoDimArrayInt32* boxes);
+FD_C_EXPORT FD_C_Bool FD_C_DBDetectorWrapperInitialized(FD_C_DBDetectorWrapper* w);
+FD_C_EXPORT void FD_C_DestroyDBDetectorWrapper(FD_C_DBDetectorWrapper* w);
+FD_C_EXPORT FD_C_ClassifierWrapper* FD_C_CreateClassifierWrapper(const char* model_file, const char* params_file,
+                                                                 FD_C_RuntimeOptionWrapper* option, FD_C_ModelFormat format);
+FD_C_EXPORT FD_C_Bool FD_C_ClassifierWrapperPredict(FD_C_ClassifierWrapper* w, FD_C_Mat img, int32_t* cls_label, float* cls_score);
+FD_C_EXPORT FD_C_Bool FD_C_ClassifierWrapperInitialized(FD_C_ClassifierWrapper* w);
+FD_C_EXPORT void FD_C_DestroyClassifierWrapper(FD_C_ClassifierWrapper* w);
+FD_C_EXPORT FD_C_RecognizerWrapper* FD_C_CreateRecognizerWrapper(const char* model_file, const char* params_file,
+                                                                 const char* label_path, FD_C_RuntimeOptionWrapper* option,
+                                                                 FD_C_ModelFormat format);
+/* *text is a UTF-8 string the library allocates; release with FD_C_DestroyCstr */
+FD_C_EXPORT FD_C_Bool FD_C_RecognizerWrapperPredict(FD_C_RecognizerWrapper* w, FD_C_Mat img, char** text, float* rec_score);
+FD_C_EXPORT FD_C_Bool FD_C_RecognizerWrapperInitialized(FD_C_RecognizerWrapper* w);
+FD_C_EXPORT void FD_C_DestroyRecognizerWrapper(FD_C_RecognizerWrapper* w);
+FD_C_EXPORT void FD_C_DestroyTwoDimArrayInt32(FD_C_TwoDimArrayInt32* a);
+FD_C_EXPORT void FD_C_DestroyCstr(char* text);
+
 /* ---- images (c_api/fastdeploy_capi/core/fd_type.h:150-165). FD_C_Imread returns a BGR image whose pixels the library
  * owns (data is NULL on failure); release it with FD_C_DestroyMat. */
 FD_C_EXPORT FD_C_Mat FD_C_Imread(const char* path);

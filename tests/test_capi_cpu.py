@@ -115,3 +115,39 @@ def test_c_program_uses_models_by_name_batches_text_and_image_files(tmp_path):
     assert out["cls_initialized"] == f"1 labels={labels[0]},{labels[1]} single={labels[0]}"
     assert out["cls_str"] == "ClassifyResult("
     assert int(out["empty_ocr_str_len"]) >= 0
+
+
+@pytest.mark.skipif(shutil.which("gcc") is None, reason="no C compiler")
+def test_c_program_runs_the_ocr_stages_one_by_one(tmp_path):
+    from fastdeploy_b200._native import build
+    if not build.build_capi():
+        pytest.skip("interpreter headers not available")
+    import fastdeploy_b200 as fd
+    from fastdeploy_b200.models.ppocr import write_ppocr
+    paths = write_ppocr(str(tmp_path / "ocr"), vocab=64)
+    exe = str(tmp_path / "capi_ocr_stages")
+    subprocess.run(["gcc", "-Wall", "-Werror", os.path.join(ROOT, "tests", "capi_ocr_stages.c"), "-I", os.path.join(ROOT, "csrc", "capi"),
+                    "-o", exe, "-L", os.path.dirname(LIB), "-lfastdeploy_capi", f"-Wl,-rpath,{os.path.dirname(LIB)}"], check=True)
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.pathsep.join(p for p in sys.path if p))
+    env.pop("PYTHONHOME", None)
+    p = subprocess.run([exe, paths["det_model"], paths["det_params"], paths["cls_model"], paths["cls_params"], paths["rec_model"],
+                        paths["rec_params"], paths["dict"]], capture_output=True, text=True, env=env, timeout=600)
+    assert p.returncode == 0, p.stdout + p.stderr
+    out = dict(line.split("=", 1) for line in p.stdout.strip().splitlines() if "=" in line)
+    assert out["initialized"] == "111" and out["bad"] == "null"
+    vals = []
+    seed = 7
+    for _ in range(64 * 160 * 3):
+        seed = (seed * 1664525 + 1013904223) & 0xFFFFFFFF
+        vals.append(seed >> 24)
+    page = np.asarray(vals, np.uint8).reshape(64, 160, 3)
+    opt = fd.RuntimeOption(); opt.use_cpu()
+    ocr = fd.vision.ocr
+    boxes = ocr.DBDetector(paths["det_model"], paths["det_params"], runtime_option=opt).predict(page)
+    assert out["boxes"] == f"{len(boxes)} all_have_8=1"
+    label, score = ocr.Classifier(paths["cls_model"], paths["cls_params"], runtime_option=opt).predict(page)
+    got_label, got_score = out["cls"].split()
+    assert int(got_label) == label and abs(float(got_score) - score) < 1e-5
+    text, rscore = ocr.Recognizer(paths["rec_model"], paths["rec_params"], paths["dict"], runtime_option=opt).predict(page)
+    nbytes, got_rscore = out["rec_bytes"].split()
+    assert int(nbytes) == len(text.encode()) and abs(float(got_rscore) - rscore) < 1e-5 and out.get("rec_text", "") == text
