@@ -399,10 +399,18 @@ YOLOX = _model("YOLOX", "x", "YOLOX (contrib/yolox.cc): grid decode, bottom-righ
                center=False, normalize=False, swap_rb=False)
 YOLOv7End2EndORT = _model("YOLOv7End2EndORT", "e2e", "YOLOv7 exported with the NMS plugin for ORT (yolov7end2end_ort.cc).")
 YOLOv7End2EndTRT = _model("YOLOv7End2EndTRT", "e2e", "YOLOv7 exported with EfficientNMS for TensorRT (yolov7end2end_trt.cc).")
+def _rk_init(self, model_file: str, runtime_option: Optional[RuntimeOption] = None, model_format: int = ModelFormat.ONNX,
+             params_file: str = ""):
+    """The Rockchip classes take no parameter file (python/fastdeploy/vision/detection/contrib/rkyolo/__init__.py:150-170)."""
+    _YOLOModel.__init__(self, model_file, params_file, runtime_option, model_format)
+
+
 RKYOLOV5 = _model("RKYOLOV5", "v5", "YOLOv5 head layout of the Rockchip export (contrib/rknpu2/rkyolo.cc).",
                   RKYOLOPreprocessor, RKYOLOPostprocessor)
 RKYOLOV7 = _model("RKYOLOV7", "v5", "YOLOv7 head layout of the Rockchip export.", RKYOLOPreprocessor, RKYOLOPostprocessor)
 RKYOLOX = _model("RKYOLOX", "x", "YOLOX head layout of the Rockchip export.", center=False, normalize=False, swap_rb=False)
+for _cls in (RKYOLOV5, RKYOLOV7, RKYOLOX):
+    _cls.__init__ = _rk_init
 
 
 class NanoDetPlus(_YOLOModel):

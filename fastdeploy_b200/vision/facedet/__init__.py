@@ -354,8 +354,26 @@ class BlazeFace(_FaceDetBase):
     rows ``[label, score, x1, y1, x2, y2]`` and a per-image count; only the score filter remains."""
     SIZE = (640, 640)
 
+    def __init__(self, model_file: str, params_file: str = "", config_file: str = "", runtime_option: Optional[RuntimeOption] = None,
+                 model_format: int = ModelFormat.PADDLE):
+        """``config_file`` is the PaddleDetection ``infer_cfg.yml`` of the export; a ``Resize.target_size`` in it sets the
+        input size (facedet/ppdet/blazeface/preprocessor.cc:30-70)."""
+        if isinstance(config_file, RuntimeOption):              # older call order: (model, params, option, format)
+            config_file, runtime_option = "", config_file
+        self.config_file = config_file
+        super().__init__(model_file, params_file, runtime_option, model_format)
+
     def _configure(self):
         self.conf_threshold = 0.5
+        cfg_path = getattr(self, "config_file", "")
+        if cfg_path:
+            import yaml
+            with open(cfg_path) as f:
+                cfg = yaml.safe_load(f) or {}
+            for op in cfg.get("Preprocess", []) or []:
+                if op.get("type") == "Resize" and op.get("target_size"):
+                    hh, ww = op["target_size"]
+                    self.size = [int(ww), int(hh)]
 
     def preprocess(self, im):
         h, w = im.shape[:2]

@@ -14,7 +14,8 @@ from ...runtime.option import RuntimeOption
 class AnimeGANPreprocessor:
     """BGR->RGB, ``x / 127.5 - 1``; NCHW by default, NHWC for exports that want it (contrib/preprocessor.cc:22-60)."""
 
-    def __init__(self):
+    def __init__(self, config_file: str = ""):
+        self.config_file = config_file          # the reference's signature has it; nothing is read from it
         self.nhwc = False
 
     def run(self, images: Sequence[np.ndarray]) -> np.ndarray:

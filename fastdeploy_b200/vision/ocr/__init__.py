@@ -477,12 +477,11 @@ PPOCRSystemv2, PPOCRSystemv3, PPOCRSystemv4 = PPOCRv2, PPOCRv3, PPOCRv4
 from .structure import (PPStructureV2Table, PPStructureV2TableSystem, StructureV2Layout,  # noqa: E402,F401
                         StructureV2LayoutPostprocessor, StructureV2LayoutPreprocessor, StructureV2Table,
                         StructureV2TablePostprocessor, StructureV2TablePreprocessor, build_html)
-from .ser import (SERResult, StructureV2SERViLayoutXLM, StructureV2SERViLayoutXLMPostprocessor,  # noqa: E402,F401
-                  StructureV2SERViLayoutXLMPreprocessor)
+from .ser import (SERResult, StructureV2SERViLayoutXLM, StructureV2SERViLayoutXLMModel,  # noqa: E402,F401
+                  StructureV2SERViLayoutXLMPostprocessor, StructureV2SERViLayoutXLMPreprocessor)
 from .ser_ops import (KeepKeys, NormalizeImage, Resize, ToCHWImage, VQAReTokenChunk, VQASerTokenChunk,  # noqa: E402,F401
                       VQASerTokenLayoutLMPostProcess, VQATokenLabelEncode, VQATokenPad)
 
 # names of the reference's Python classes for the same three objects
-StructureV2SERViLayoutXLMModel = StructureV2SERViLayoutXLM
 StructureV2SERViLayoutXLMModelPreprocessor = StructureV2SERViLayoutXLMPreprocessor
 StructureV2SERViLayoutXLMModelPostprocessor = StructureV2SERViLayoutXLMPostprocessor

@@ -196,3 +196,31 @@ class StructureV2SERViLayoutXLM(FastDeployModel):
             out.append(self.postprocessor.run(logits[at:at + w], b))
             at += w
         return out
+
+
+class StructureV2SERViLayoutXLMModel(StructureV2SERViLayoutXLM):
+    """The same model under the reference's class name and constructor order
+    (python/fastdeploy/vision/ocr/ppocr/__init__.py:1241-1300): ``(model_file, params_file, ser_dict_path, class_path,
+    config_file, runtime_option, model_format)``. The reference builds its tokenizer and its OCR engine from external
+    packages; here they are arguments: ``tokenizer`` (any object with ``encode(text)``), or a SentencePiece model file
+    named ``sentencepiece.bpe.model`` beside the model file, read in the XLM-R convention; ``ocr`` is a PP-OCR pipeline
+    for ``predict(image)`` without lines (``ser_dict_path`` is the recogniser dictionary the reference hands to its own
+    engine and is kept on the object)."""
+
+    def __init__(self, model_file: str, params_file: str = "", ser_dict_path: str = "", class_path: Optional[str] = None,
+                 config_file: str = "", runtime_option: Optional[RuntimeOption] = None, model_format: int = ModelFormat.PADDLE,
+                 *, tokenizer: Any = None, ocr: Any = None, labels: Optional[Sequence[str]] = None, max_seq_len: int = 512):
+        import os
+        if tokenizer is None:
+            spm_file = os.path.join(os.path.dirname(os.path.abspath(model_file)), "sentencepiece.bpe.model")
+            if not os.path.exists(spm_file):
+                raise ValueError(f"no tokenizer given and {spm_file} does not exist")
+            from ...text.spm_tokenizer import XLMRobertaTokenizer
+            tokenizer = XLMRobertaTokenizer(spm_file, max_seq_len)
+        self.ser_dict_path, self.config_file = ser_dict_path, config_file
+        super().__init__(model_file, params_file, class_path, tokenizer=tokenizer, ocr=ocr, labels=labels,
+                         runtime_option=runtime_option, model_format=model_format, max_seq_len=max_seq_len)
+
+    @property
+    def postprocesser(self):                # the reference's spelling of the attribute
+        return self.postprocessor

@@ -62,8 +62,15 @@ class PaddleSegPreprocessor(ProcessorManager):
 
 
 class PaddleSegPostprocessor:
-    def __init__(self, with_argmax: bool = True, with_softmax: bool = False):
-        self.is_with_argmax, self.is_with_softmax = with_argmax, with_softmax
+    def __init__(self, with_argmax=True, with_softmax: bool = False):
+        """``PaddleSegPostprocessor(config_file)`` reads ``Deploy.output_op`` of the model's ``deploy.yaml`` as the reference
+        does (fastdeploy/vision/segmentation/ppseg/postprocessor.cc:22-50); the two flags can also be given directly."""
+        if isinstance(with_argmax, str):
+            with open(with_argmax) as f:
+                deploy = (yaml.safe_load(f) or {}).get("Deploy", {})
+            with_softmax = deploy.get("output_op", "") == "softmax"
+            with_argmax = deploy.get("output_op", "argmax") == "argmax"
+        self.is_with_argmax, self.is_with_softmax = bool(with_argmax), bool(with_softmax)
         self.apply_softmax = False
         self.store_score_map = False
 

@@ -114,8 +114,11 @@ def test_face_detector_processors_alone_and_through_the_model(tmp_path):
     assert fdet.Yolov7FacePreprocessor().padding_value == [114.0, 114.0, 114.0]
     # through a model: the processors are views of the model's settings
     rows = np.array([[0, 0.9, 10, 12, 40, 44], [0, 0.3, 1, 1, 5, 5]], np.float32)
-    m = fdet.BlazeFace(_head_model(str(tmp_path / "bf.onnx"), 64, rows), runtime_option=_opt())
-    m.size = [64, 64]
+    cfg = tmp_path / "infer_cfg.yml"
+    cfg.write_text("Preprocess:\n- type: Resize\n  target_size: [64, 64]\n")
+    m = fdet.BlazeFace(_head_model(str(tmp_path / "bf.onnx"), 64, rows), "", str(cfg), runtime_option=_opt(),
+                       model_format=fd.ModelFormat.ONNX)
+    assert m.size == [64, 64]                               # from the yaml
     assert isinstance(m.preprocessor, fdet.BlazeFacePreprocessor) and isinstance(m.postprocessor, fdet.BlazeFacePostprocessor)
     m.postprocessor.conf_threshold = 0.2
     assert m.conf_threshold == 0.2

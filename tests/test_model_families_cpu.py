@@ -242,3 +242,25 @@ def test_native_hard_nms_matches_the_numpy_scan():
         assert np.array_equal(got, want)
         assert np.array_equal(U.nms_indices(boxes, scores, thr, max_keep=3), want[:3])
     assert U.nms_indices(np.zeros((0, 4), np.float32), np.zeros(0, np.float32)).size == 0
+
+
+def test_ser_model_under_the_reference_constructor_order(tmp_path):
+    from fastdeploy_b200.core.types import ModelFormat
+    from fastdeploy_b200.models.layoutxlm import write_ser_vi_layoutxlm
+    from fastdeploy_b200.runtime.option import RuntimeOption
+    from fastdeploy_b200.vision.ocr import StructureV2SERViLayoutXLM, StructureV2SERViLayoutXLMModel
+
+    class Tok:
+        def encode(self, text):
+            return [5 + (ord(c) % 50) for c in text if not c.isspace()]
+
+    paths = write_ser_vi_layoutxlm(str(tmp_path), "tiny", num_labels=7, seed=3)
+    opt = RuntimeOption(); opt.use_cpu()
+    a = StructureV2SERViLayoutXLM(paths["model"], paths["params"], paths["classes"], tokenizer=Tok(), runtime_option=opt)
+    b = StructureV2SERViLayoutXLMModel(paths["model"], paths["params"], "rec_dict.txt", paths["classes"], "", opt, ModelFormat.PADDLE,
+                                       tokenizer=Tok())
+    assert b.ser_dict_path == "rec_dict.txt" and b.postprocesser is b.postprocessor
+    im = np.zeros((200, 300, 3), np.uint8)
+    lines = [{"bbox": [10, 10, 120, 30], "transcription": "name"}, {"points": [[10, 50], [150, 50], [150, 70], [10, 70]], "transcription": "alice"}]
+    ra, rb = a.predict(im, lines), b.predict(im, lines)
+    assert ra.pred == rb.pred and ra.text == rb.text == ["name", "alice"]

@@ -48,7 +48,11 @@ def test_model_level_names_of_older_releases():
     rec.rec_image_shape, rec.static_shape_infer = [3, 32, 100], True
     assert rec.preprocessor.run([_img(20, 400)]).shape == (1, 3, 32, 100)
     assert ocr.PPStructureV2TableSystem is ocr.PPStructureV2Table
-    assert ocr.StructureV2SERViLayoutXLMModel is ocr.StructureV2SERViLayoutXLM
+    assert issubclass(ocr.StructureV2SERViLayoutXLMModel, ocr.StructureV2SERViLayoutXLM)
+    with pytest.raises(ValueError, match="sentencepiece.bpe.model"):
+        ocr.StructureV2SERViLayoutXLMModel("/nonexistent/model.pdmodel", "", "dict.txt", "classes.txt")
+    post = fd.vision.segmentation.PaddleSegPostprocessor
+    assert post().is_with_argmax and not post(False, True).is_with_argmax and post(False, True).is_with_softmax
 
 
 def test_layout_preprocessor_and_table_pipeline_batches():
