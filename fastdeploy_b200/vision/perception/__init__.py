@@ -187,7 +187,17 @@ class PetrPreprocessor(_ImagePreprocessor):
 
 
 class CaddnPreprocessor(_ImagePreprocessor):
-    pass
+    def run(self, input_ims: Sequence[np.ndarray], cam_data: Optional[Sequence[float]] = None,
+            lidar_data: Optional[Sequence[float]] = None):
+        """``[images [N, 3, H, W], cam2img [N, 3, 4], lidar2cam [N, 4, 4]]``: the two matrices (12 and 16 numbers, row
+        major) are shared by the images of the batch (caddn/preprocessor.cc:95-140)."""
+        x = _ImagePreprocessor.run(self, input_ims)
+        if cam_data is None and lidar_data is None:
+            return x
+        n = len(input_ims)
+        cam = np.eye(3, 4, dtype=np.float32) if cam_data is None else np.asarray(cam_data, np.float32).reshape(3, 4)
+        lidar = np.eye(4, dtype=np.float32) if lidar_data is None else np.asarray(lidar_data, np.float32).reshape(4, 4)
+        return [x, np.repeat(cam[None], n, 0), np.repeat(lidar[None], n, 0)]
 
 
 class SmokePostprocessor:
@@ -322,9 +332,33 @@ class CenterpointPreprocessor:
         self.point_cloud_range = [-51.2, -51.2, -5.0, 51.2, 51.2, 3.0]
         self.max_points_in_voxel, self.max_voxel_num = 20, 30000
 
-    def run(self, points: np.ndarray):
+    def voxelize(self, points: np.ndarray):
         return hard_voxelize(np.asarray(points, np.float32), self.voxel_size, self.point_cloud_range, self.max_points_in_voxel,
                              self.max_voxel_num)
+
+    @staticmethod
+    def read_points(point_dir, num_point_dim: int = 5, with_timelag: int = 0) -> np.ndarray:
+        """One sweep ``[N, num_point_dim]`` from a file of packed float32 values (or an array, passed through). The fifth
+        column is the time lag; it is zeroed when the file has one but the model was trained without it, and for sweeps
+        with more than five columns (centerpoint/preprocessor.cc:25-95)."""
+        if num_point_dim < 4:
+            raise ValueError(f"Point dimension must not be less than 4, but received num_point_dim is {num_point_dim}")
+        if isinstance(point_dir, (str, bytes)) or hasattr(point_dir, "__fspath__"):
+            data = np.fromfile(point_dir, dtype=np.float32)
+            if data.size % num_point_dim:
+                raise ValueError(f"Loaded file size ({data.size * 4}) is not evenly divisible by num_point_dim ({num_point_dim})")
+            pts = data.reshape(-1, num_point_dim).copy()
+        else:
+            pts = np.array(point_dir, np.float32, copy=True).reshape(-1, num_point_dim)
+        if (not with_timelag and num_point_dim == 5) or num_point_dim > 5:
+            pts[:, 4] = 0.0
+        return pts
+
+    def run(self, point_dirs, num_point_dim: int = 5, with_timelag: int = 0) -> List[np.ndarray]:
+        """Files (or arrays) -> one ``[N, num_point_dim]`` array per sweep."""
+        if isinstance(point_dirs, (str, bytes)) or isinstance(point_dirs, np.ndarray):
+            point_dirs = [point_dirs]
+        return [self.read_points(p, num_point_dim, with_timelag) for p in point_dirs]
 
 
 class Centerpoint(FastDeployModel):
@@ -338,6 +372,7 @@ class Centerpoint(FastDeployModel):
         self.preprocessor = CenterpointPreprocessor(config_file)
         self.down_ratio, self.score_threshold, self.nms_iou_threshold = 4, 0.1, 0.2
         self.with_velocity = True
+        self.num_point_dim, self.with_timelag = 5, 0
         self.init_runtime()
 
     voxel_size = property(lambda self: self.preprocessor.voxel_size, lambda self, v: setattr(self.preprocessor, "voxel_size", list(v)))
@@ -355,7 +390,10 @@ class Centerpoint(FastDeployModel):
     def batch_predict(self, sweeps: Sequence[np.ndarray]) -> List[PerceptionResult]:
         return [self.predict(p) for p in sweeps]
 
-    def predict(self, points: np.ndarray) -> PerceptionResult:
+    def predict(self, points) -> PerceptionResult:
+        """``points``: a sweep ``[N, 4 | 5]`` or the path of a file of packed float32 values."""
+        if isinstance(points, (str, bytes)) or hasattr(points, "__fspath__"):
+            points = self.preprocessor.read_points(points, self.num_point_dim, self.with_timelag)
         pts = np.asarray(points, np.float32)
         voxels, coords, num = hard_voxelize(pts, self.voxel_size, self.point_cloud_range, self.max_points_in_voxel,
                                             self.max_voxel_num)

@@ -42,8 +42,18 @@ def test_perception_processors_and_batches(tmp_path):
     assert Fake().batch_predict(["a", "b"], ["k1", "k2"]) == [1, 2] and calls == [("a", "k1"), ("b", "k2")]
     cp = V.perception.CenterpointPreprocessor()
     pts = np.array([[0.05, 0.05, 0.0, 1.0], [0.06, 0.04, 0.1, 1.0], [10.0, 10.0, 0.0, 1.0], [999.0, 0, 0, 1.0]], np.float32)
-    voxels, coords, num = cp.run(pts)
+    voxels, coords, num = cp.voxelize(pts)
     assert int(np.asarray(num).sum()) == 3 and len(np.asarray(num)) == 2          # two voxels, the far point dropped
+    sweep = np.arange(20, dtype=np.float32).reshape(4, 5)
+    path = tmp_path / "sweep.bin"
+    sweep.tofile(path)
+    got = cp.run([str(path)], 5, 0)[0]
+    assert got.shape == (4, 5) and np.array_equal(got[:, :4], sweep[:, :4]) and (got[:, 4] == 0).all()
+    assert np.array_equal(cp.run([str(path)], 5, 1)[0], sweep)                    # the model uses the time lag: kept
+    with pytest.raises(ValueError, match="divisible"):
+        cp.run([str(path)], 6, 0)
+    imgs, cam, lidar = V.perception.CaddnPreprocessor(str(cfg)).run([np.zeros((48, 96, 3), np.uint8)] * 2, list(range(12)), list(range(16)))
+    assert imgs.shape == (2, 3, 32, 64) and cam.shape == (2, 3, 4) and lidar.shape == (2, 4, 4) and cam[1, 2, 3] == 11
 
 
 def test_trail_recorder_and_mot_drawing():
