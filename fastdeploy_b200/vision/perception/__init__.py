@@ -313,13 +313,18 @@ class Caddn(_ImagePerception):
     PRE, POST = CaddnPreprocessor, CaddnPostprocessor
     __doc__ = """CaDDN: image plus camera-to-image and lidar-to-camera matrices; outputs boxes ``[n, 7]``, labels, scores."""
 
-    def predict(self, im: np.ndarray, cam2img: Optional[np.ndarray] = None, lidar2cam: Optional[np.ndarray] = None):
+    def predict(self, input_image: np.ndarray, cam_data: Optional[Sequence[float]] = None,
+                lidar_data: Optional[Sequence[float]] = None, *, cam2img=None, lidar2cam=None):
+        """``cam_data``: the 3 x 4 camera-to-image matrix (12 numbers), ``lidar_data``: the 4 x 4 lidar-to-camera matrix
+        (``cam2img`` / ``lidar2cam`` are the same two under the names of earlier versions of this class)."""
+        cam_data = cam2img if cam_data is None else cam_data
+        lidar_data = lidar2cam if lidar_data is None else lidar_data
         names = [self.runtime.get_input_info(i).name for i in range(self.runtime.num_inputs())]
-        feeds = {names[0]: self._image_tensor(im)[None]}
+        feeds = {names[0]: self._image_tensor(input_image)[None]}
         if len(names) > 1:
-            feeds[names[1]] = (np.eye(3, 4, dtype=np.float32) if cam2img is None else np.asarray(cam2img, np.float32)).reshape(1, 3, 4)
+            feeds[names[1]] = (np.eye(3, 4, dtype=np.float32) if cam_data is None else np.asarray(cam_data, np.float32)).reshape(1, 3, 4)
         if len(names) > 2:
-            feeds[names[2]] = (np.eye(4, dtype=np.float32) if lidar2cam is None else np.asarray(lidar2cam, np.float32)).reshape(1, 4, 4)
+            feeds[names[2]] = (np.eye(4, dtype=np.float32) if lidar_data is None else np.asarray(lidar_data, np.float32)).reshape(1, 4, 4)
         return self.postprocessor.run(self.runtime.infer(feeds))[0]
 
 
