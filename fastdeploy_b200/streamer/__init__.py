@@ -125,10 +125,15 @@ def tile_frames(frames: Sequence[np.ndarray], rows: int, cols: int, width: int, 
 
 
 class FDStreamer:
-    """``FDStreamer().Init(config); Run()`` like python/fastdeploy... streamer bindings
-    (streamer/src/fd_streamer.cc:22-110). ``config`` is a YAML path or a dict."""
+    """``FDStreamer(config).Run()`` as in the Python binding (streamer/python/streamer/fd_streamer.py:19-30), or
+    ``FDStreamer().Init(config); Run()`` as in C++ (streamer/src/fd_streamer.cc:22-110). ``config`` is a YAML path or a dict."""
 
-    def __init__(self):
+    def __init__(self, config_file: Any = None, model: Any = None):
+        self._construct()
+        if config_file is not None:
+            self.Init(config_file, model)
+
+    def _construct(self) -> None:
         self.cfg: Dict[str, Any] = {}
         self.model = None
         self.results: List[Frame] = []
