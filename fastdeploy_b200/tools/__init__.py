@@ -206,7 +206,7 @@ def cmd_export_plan(args) -> int:
 
 def argsparser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(prog="fastdeploy", description=__doc__.split("\n\n")[0])
-    p.add_argument("tools", choices=["compress", "convert", "simple_serving", "benchmark", "export_plan"])
+    p.add_argument("tools", choices=["compress", "convert", "simple_serving", "benchmark", "export_plan", "paddle2coreml"])
     p.add_argument("--config_path", default=None, help="compress: model directory (kept for command compatibility)")
     p.add_argument("--method", default="PTQ", help="compress: PTQ (post-training calibration)")
     p.add_argument("--save_dir", default="./output", help="directory to save the result")
@@ -226,12 +226,34 @@ def argsparser() -> argparse.ArgumentParser:
     p.add_argument("--device", default="cpu", choices=["cpu", "gpu"])
     p.add_argument("--device_id", type=int, default=0)
     p.add_argument("--fp16", action="store_true")
+    # flags of the reference's command line that have no meaning here; accepted so that existing scripts parse
+    for flag in ("--prototxt", "--weight", "--caffe_proto", "--p2c_paddle_model_dir", "--p2c_coreml_model_dir",
+                 "--p2c_coreml_model_name", "--p2c_input_names", "--p2c_input_dtypes", "--p2c_input_shapes", "--p2c_output_names"):
+        p.add_argument(flag, default=None, help=argparse.SUPPRESS)
+    p.add_argument("--enable_code_optim", default=None, help=argparse.SUPPRESS)
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--repeat", type=int, default=20)
     return p
 
 
+def cmd_paddle2coreml(args) -> int:
+    """The reference converts a Paddle model to Apple's CoreML with an external package
+    (tools/common_tools/common_tools.py:165-190). That format has no consumer on this hardware: say so and point at the
+    converter that exists."""
+    import sys
+    print("paddle2coreml is not available in this package: CoreML targets Apple devices. "
+          "Use `convert --framework paddle --model <dir> --save_dir <dir>` for an ONNX file.", file=sys.stderr)
+    return 2
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     args = argsparser().parse_args(argv)
+    if args.tools == "paddle2coreml":
+        return cmd_paddle2coreml(args)
+    if args.tools == "convert" and args.framework is not None and args.framework.lower() in ("caffe", "tensorflow"):
+        import sys
+        print(f"convert: framework {args.framework!r} needs the x2paddle converter, which is not part of this package; "
+              "paddle and onnx models are converted", file=sys.stderr)
+        return 2
     return {"compress": cmd_compress, "convert": cmd_convert, "simple_serving": cmd_simple_serving,
             "benchmark": cmd_benchmark, "export_plan": cmd_export_plan}[args.tools](args)

@@ -98,3 +98,11 @@ def test_cpu_resnet50_benchmark_line(tmp_path):
                          timeout=120)
     out = json.loads(ref.stdout.strip().splitlines()[-1])
     assert ref.returncode == 0 and out["impl"] == "reference" and "unavailable" in out
+
+
+def test_subcommands_without_a_counterpart_say_so(capsys):
+    from fastdeploy_b200.tools import main
+    assert main(["paddle2coreml", "--p2c_paddle_model_dir", "x", "--p2c_coreml_model_name", "m"]) == 2
+    assert "CoreML" in capsys.readouterr().err
+    assert main(["convert", "--framework", "caffe", "--prototxt", "a", "--weight", "b"]) == 2
+    assert "x2paddle" in capsys.readouterr().err
