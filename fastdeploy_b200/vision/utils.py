@@ -158,3 +158,73 @@ def fd_result_to_json(result: Any) -> str:
     d = conv(result)
     d["type"] = type(result).__name__
     return json.dumps(d)
+
+
+# ------------------------------------------------------------------ results <-> JSON, one pair of functions per result type
+# (python/fastdeploy/vision/utils.py:20-330; the serving handlers use them to put results on the wire)
+def _plain(o):
+    if isinstance(o, (np.floating, np.integer)):
+        return o.item()
+    if isinstance(o, np.ndarray):
+        return o.tolist()
+    if isinstance(o, (list, tuple)):
+        return [_plain(v) for v in o]
+    return o
+
+
+def _fields_to_json(result: Any) -> str:
+    out = {}
+    for k, v in result.__dict__.items():
+        if k == "masks":
+            out[k] = [mask_to_json(m) for m in v]          # each mask is a JSON document of its own, as in the reference
+        else:
+            out[k] = _plain(v)
+    return json.dumps(out)
+
+
+def _fields_from_json(cls_name: str, data: Any) -> Any:
+    from . import result as R
+    if isinstance(data, (str, bytes)):
+        data = json.loads(data)
+    obj = getattr(R, cls_name)()
+    for k, v in data.items():
+        if k == "type" or not hasattr(obj, k):
+            continue
+        if k == "masks":
+            v = [json_to_mask(m) for m in v]
+        setattr(obj, k, v)
+    return obj
+
+
+def mask_to_json(result: Any) -> str:
+    return json.dumps({"data": _plain(result.data), "shape": _plain(result.shape)})
+
+
+def json_to_mask(result: Any):
+    return _fields_from_json("Mask", result)
+
+
+def _pair(kind: str, cls_name: str):
+    def to_json(result: Any) -> str:
+        return _fields_to_json(result)
+
+    def from_json(result: Any):
+        return _fields_from_json(cls_name, result)
+    to_json.__name__, from_json.__name__ = f"{kind}_to_json", f"json_to_{kind}"
+    to_json.__doc__ = f"``{cls_name}`` -> JSON text with one key per field."
+    from_json.__doc__ = f"JSON text or the parsed dictionary -> ``{cls_name}``."
+    return to_json, from_json
+
+
+detection_to_json, json_to_detection = _pair("detection", "DetectionResult")
+perception_to_json, json_to_perception = _pair("perception", "PerceptionResult")
+classify_to_json, json_to_classify = _pair("classify", "ClassifyResult")
+keypoint_to_json, json_to_keypoint = _pair("keypoint", "KeyPointDetectionResult")
+ocr_to_json, json_to_ocr = _pair("ocr", "OCRResult")
+mot_to_json, json_to_mot = _pair("mot", "MOTResult")
+face_detection_to_json, json_to_face_detection = _pair("face_detection", "FaceDetectionResult")
+face_alignment_to_json, json_to_face_alignment = _pair("face_alignment", "FaceAlignmentResult")
+face_recognition_to_json, json_to_face_recognition = _pair("face_recognition", "FaceRecognitionResult")
+segmentation_to_json, json_to_segmentation = _pair("segmentation", "SegmentationResult")
+matting_to_json, json_to_matting = _pair("matting", "MattingResult")
+head_pose_to_json, json_to_head_pose = _pair("head_pose", "HeadPoseResult")

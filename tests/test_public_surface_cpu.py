@@ -172,3 +172,33 @@ def test_example_image_and_hub_directories(tmp_path, monkeypatch):
     assert cv2.imread(q).shape == (8, 8, 3)                                                                    # the cached file wins
     monkeypatch.delenv("HUB_HOME")
     importlib.reload(hub_env)
+
+
+def test_results_round_trip_through_json():
+    import json
+    U = fd.vision.utils
+    R = fd.vision
+    d = R.DetectionResult()
+    d.boxes, d.scores, d.label_ids, d.contain_masks = [[1.0, 2.0, 3.0, 4.0]], [0.5], [7], True
+    m = R.Mask(); m.data, m.shape = [0, 1, 1, 0], [2, 2]
+    d.masks = [m]
+    text = U.detection_to_json(d)
+    parsed = json.loads(text)
+    assert parsed["boxes"] == [[1.0, 2.0, 3.0, 4.0]] and json.loads(parsed["masks"][0]) == {"data": [0, 1, 1, 0], "shape": [2, 2]}
+    back = U.json_to_detection(parsed)
+    assert back.boxes == d.boxes and back.label_ids == [7] and back.masks[0].shape == [2, 2] and back.contain_masks
+    assert U.json_to_detection(text).scores == [0.5]                      # the text form is taken as well
+    o = R.OCRResult()
+    o.boxes, o.text, o.rec_scores = [[0, 0, 5, 0, 5, 5, 0, 5]], ["héllo"], [0.9]
+    assert U.json_to_ocr(U.ocr_to_json(o)).text == ["héllo"]
+    s = R.SegmentationResult()
+    s.label_map, s.shape = np.array([0, 1, 2, 1], np.uint8).tolist(), [2, 2]
+    assert U.json_to_segmentation(U.segmentation_to_json(s)).label_map == [0, 1, 2, 1]
+    for kind, cls in (("perception", "PerceptionResult"), ("classify", "ClassifyResult"), ("keypoint", "KeyPointDetectionResult"),
+                      ("mot", "MOTResult"), ("face_detection", "FaceDetectionResult"), ("face_alignment", "FaceAlignmentResult"),
+                      ("face_recognition", "FaceRecognitionResult"), ("matting", "MattingResult"), ("head_pose", "HeadPoseResult")):
+        obj = getattr(R, cls)()
+        again = getattr(U, f"json_to_{kind}")(getattr(U, f"{kind}_to_json")(obj))
+        assert type(again) is type(obj) and again.__dict__ == obj.__dict__, kind
+    h = R.HeadPoseResult(); h.euler_angles = [np.float32(1.5), 2.0, 3.0]
+    assert json.loads(U.head_pose_to_json(h))["euler_angles"] == [1.5, 2.0, 3.0]
