@@ -33,25 +33,31 @@ class RequestBase(BaseModel):
     parameters: Optional[dict] = {}
 
 
+def _body_models(task_name: str):
+    """Request and response schema of one task: ``data`` and ``result`` may hold anything; schema names must be unique
+    per application, so they carry a digest of the task name."""
+    tag = hashlib.md5(task_name.encode()).hexdigest()
+    request = create_model(f"RequestModel{tag}", __base__=RequestBase, data=(typing.Any, ...))
+    response = create_model(f"ResponseModel{tag}", __base__=ResponseBase, result=(typing.Any, ...))
+    return request, response
+
+
 class HttpRouterManager(BaseRouterManager):
     """``app`` needs a ``_model_manager`` with ``predict(data, parameters)`` by the time a request arrives."""
 
     def register_models_router(self, task_name: str):
-        unique = hashlib.md5(task_name.encode()).hexdigest()
-        req_model = create_model("RequestModel" + unique, data=(typing.Any, ...), __base__=RequestBase)
-        resp_model = create_model("ResponseModel" + unique, result=(typing.Any, ...), __base__=ResponseBase)
-        app = self._app
+        body_cls, answer_cls = _body_models(task_name)
+        owner = self._app
 
-        # (annotations must be the classes themselves here: the framework reads them to find the request body)
-        def predict(request: Request, inference_request: req_model):     # type: ignore[valid-type]
+        # (the annotation must be the class itself: the framework reads it to find the request body)
+        def serve(request: Request, payload: body_cls):     # type: ignore[valid-type]
             try:
-                result = app._model_manager.predict(inference_request.data, inference_request.parameters)
-            except Exception as e:
-                raise HTTPException(status_code=400, detail=f"Error occurred while running predict: {e}")
-            return {"result": result}
+                return {"result": owner._model_manager.predict(payload.data, payload.parameters)}
+            except Exception as exc:
+                raise HTTPException(status_code=400, detail=f"Error occurred while running predict: {exc}")
 
-        router = APIRouter()
-        router.add_api_route(f"/{task_name}", predict, methods=["post"], summary=task_name.title(), response_model=resp_model,
-                             response_model_exclude_unset=True, response_model_exclude_none=True)
-        app.include_router(router)
-        return router
+        routes = APIRouter()
+        routes.post(f"/{task_name}", summary=task_name.title(), response_model=answer_cls, response_model_exclude_unset=True,
+                    response_model_exclude_none=True)(serve)
+        owner.include_router(routes)
+        return routes
