@@ -144,18 +144,14 @@ def crop_image_by_box(image: np.ndarray, box: Sequence[float]) -> np.ndarray:
 
 
 def fd_result_to_json(result: Any) -> str:
-    """Result object -> JSON string (python/fastdeploy/vision/utils.py:137-172)."""
-    def conv(o):
-        if isinstance(o, (np.floating, np.integer)):
-            return o.item()
-        if isinstance(o, np.ndarray):
-            return o.tolist()
-        if hasattr(o, "__dict__"):
-            return {k: conv(v) for k, v in o.__dict__.items()}
-        if isinstance(o, (list, tuple)):
-            return [conv(v) for v in o]
-        return o
-    d = conv(result)
+    """Result object -> JSON text in the layout of the per-type converters below (one key per field, each instance mask a
+    JSON document of its own), plus a ``type`` key with the class name (python/fastdeploy/vision/utils.py:137-172). A list
+    of results gives a JSON list."""
+    if isinstance(result, (list, tuple)):
+        return json.dumps([json.loads(fd_result_to_json(r)) for r in result])
+    if not hasattr(result, "__dict__"):
+        raise TypeError(f"not a result object: {type(result).__name__}")
+    d = json.loads(_fields_to_json(result))
     d["type"] = type(result).__name__
     return json.dumps(d)
 

@@ -202,3 +202,19 @@ def test_results_round_trip_through_json():
         assert type(again) is type(obj) and again.__dict__ == obj.__dict__, kind
     h = R.HeadPoseResult(); h.euler_angles = [np.float32(1.5), 2.0, 3.0]
     assert json.loads(U.head_pose_to_json(h))["euler_angles"] == [1.5, 2.0, 3.0]
+
+
+def test_generic_result_serialiser_uses_the_per_type_layout():
+    import json
+    U, R = fd.vision.utils, fd.vision
+    d = R.DetectionResult()
+    d.boxes, d.scores, d.label_ids, d.contain_masks = [[1.0, 2.0, 3.0, 4.0]], [np.float32(0.5)], [7], True
+    m = R.Mask(); m.data, m.shape = [1, 0], [1, 2]
+    d.masks = [m]
+    parsed = json.loads(U.fd_result_to_json(d))
+    assert parsed["type"] == "DetectionResult" and isinstance(parsed["masks"][0], str) and parsed["scores"] == [0.5]
+    assert U.json_to_detection(parsed).masks[0].data == [1, 0]
+    both = json.loads(U.fd_result_to_json([d, R.ClassifyResult(label_ids=[1], scores=[0.25])]))
+    assert [b["type"] for b in both] == ["DetectionResult", "ClassifyResult"]
+    with pytest.raises(TypeError):
+        U.fd_result_to_json(3)
